@@ -1,0 +1,261 @@
+"""ctypes mirror of include/fkb200.h.
+
+Python here is harness only (tests, benchmark, smoke check): the product is the C-ABI
+shared library built from csrc/.  The structures below must match the header field for
+field; tests/test_abi_layout.py checks their sizes against the compiled library.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from pathlib import Path
+
+PKG_DIR = Path(__file__).resolve().parent
+LIB_PATH = PKG_DIR / "lib" / "libfkb200.so"
+
+# status codes -------------------------------------------------------------------------
+OK = 0
+ERR_INVALID_ARGUMENT = 1
+ERR_UNSUPPORTED = 2
+ERR_CUDA = 3
+ERR_TOO_LARGE = 4
+ERR_NO_DEVICE = 5
+
+# vocabulary ---------------------------------------------------------------------------
+SRC_U8X3, SRC_F32X3, SRC_NV12 = 1, 2, 3
+DST_F32X3_PACKED, DST_F32_PLANAR3, DST_U8X3_PACKED = 1, 2, 3
+RESIZE_NONE, RESIZE_IGNORE_AR, RESIZE_PRESERVE_AR = 0, 1, 2
+(OP_MUL, OP_SUB, OP_DIV, OP_ADD, OP_CAST_F32, OP_SWAP_RB, OP_SATURATE_CAST_U8,
+ OP_YUV_TO_RGB_BT709_FULL) = range(1, 9)
+
+
+class Op(C.Structure):
+    _fields_ = [("opcode", C.c_int32), ("p", C.c_float * 3)]
+
+
+class Sequence(C.Structure):
+    _fields_ = [
+        ("src_format", C.c_int32),
+        ("dst_format", C.c_int32),
+        ("resize_mode", C.c_int32),
+        ("n_ops", C.c_int32),
+        ("n_pre_ops", C.c_int32),
+        ("background", C.c_float * 3),
+        ("ops", C.POINTER(Op)),
+    ]
+
+
+class Plane(C.Structure):
+    _fields_ = [
+        ("src", C.c_void_p),
+        ("src_width", C.c_uint32),
+        ("src_height", C.c_uint32),
+        ("src_pitch", C.c_uint32),
+        ("crop_x", C.c_int32),
+        ("crop_y", C.c_int32),
+        ("crop_width", C.c_int32),
+        ("crop_height", C.c_int32),
+        ("dst", C.c_void_p),
+        ("dst_width", C.c_uint32),
+        ("dst_height", C.c_uint32),
+        ("dst_pitch", C.c_uint32),
+        ("dst_channel_stride", C.c_uint32),
+        ("sequence", C.c_int32),
+        ("reserved", C.c_int32),
+    ]
+
+
+class PlanDesc(C.Structure):
+    _fields_ = [
+        ("sequences", C.POINTER(Sequence)),
+        ("n_sequences", C.c_int32),
+        ("planes", C.POINTER(Plane)),
+        ("n_planes", C.c_int32),
+    ]
+
+
+class ResizeParams(C.Structure):
+    _fields_ = [
+        ("fx", C.c_float), ("fy", C.c_float),
+        ("x1", C.c_int32), ("y1", C.c_int32), ("x2", C.c_int32), ("y2", C.c_int32),
+        ("target_width", C.c_int32), ("target_height", C.c_int32),
+    ]
+
+
+class PlanInfo(C.Structure):
+    _fields_ = [
+        ("n_planes", C.c_int32),
+        ("n_sequences", C.c_int32),
+        ("n_launches", C.c_int32),
+        ("grid_x", C.c_uint32),
+        ("block_x", C.c_uint32),
+        ("output_pixels", C.c_uint64),
+        ("algorithmic_bytes", C.c_uint64),
+        ("device_bytes", C.c_uint64),
+    ]
+
+
+def op(opcode: int, p=(0.0, 0.0, 0.0)) -> Op:
+    if isinstance(p, (int, float)):
+        p = (p, p, p)
+    o = Op()
+    o.opcode = opcode
+    o.p[0], o.p[1], o.p[2] = (float(v) for v in p)
+    return o
+
+
+class HostPlan:
+    """Owns the ctypes arrays behind an fkb_plan_desc so they outlive the call."""
+
+    def __init__(self):
+        self._seqs: list[Sequence] = []
+        self._op_arrays = []
+        self._planes: list[Plane] = []
+        self._desc = None
+
+    def add_sequence(self, src_format, dst_format, resize_mode, ops, n_pre_ops=0,
+                     background=(0.0, 0.0, 0.0)) -> int:
+        arr = (Op * max(len(ops), 1))(*ops)
+        self._op_arrays.append(arr)
+        s = Sequence()
+        s.src_format, s.dst_format, s.resize_mode = src_format, dst_format, resize_mode
+        s.n_ops, s.n_pre_ops = len(ops), n_pre_ops
+        s.background[0], s.background[1], s.background[2] = (float(v) for v in background)
+        s.ops = C.cast(arr, C.POINTER(Op))
+        self._seqs.append(s)
+        self._desc = None
+        return len(self._seqs) - 1
+
+    def add_plane(self, *, src, src_width, src_height, src_pitch, dst, dst_width, dst_height,
+                  dst_pitch, dst_channel_stride=0, crop=None, sequence=0) -> int:
+        p = Plane()
+        p.src, p.src_width, p.src_height, p.src_pitch = src, src_width, src_height, src_pitch
+        cx, cy, cw, ch = crop if crop is not None else (0, 0, src_width, src_height)
+        p.crop_x, p.crop_y, p.crop_width, p.crop_height = int(cx), int(cy), int(cw), int(ch)
+        p.dst, p.dst_width, p.dst_height, p.dst_pitch = dst, dst_width, dst_height, dst_pitch
+        p.dst_channel_stride, p.sequence, p.reserved = dst_channel_stride, sequence, 0
+        self._planes.append(p)
+        self._desc = None
+        return len(self._planes) - 1
+
+    @property
+    def n_planes(self) -> int:
+        return len(self._planes)
+
+    @property
+    def planes(self) -> list:
+        return self._planes
+
+    def desc(self) -> PlanDesc:
+        if self._desc is None:
+            self._seq_arr = (Sequence * max(len(self._seqs), 1))(*self._seqs)
+            self._plane_arr = (Plane * max(len(self._planes), 1))(*self._planes)
+            d = PlanDesc()
+            d.sequences = C.cast(self._seq_arr, C.POINTER(Sequence))
+            d.n_sequences = len(self._seqs)
+            d.planes = C.cast(self._plane_arr, C.POINTER(Plane))
+            d.n_planes = len(self._planes)
+            self._desc = d
+        return self._desc
+
+
+class FkbError(RuntimeError):
+    """Non-zero status from the C ABI (the reference throws std::runtime_error,
+    core/utils/utils.h:95-109)."""
+
+    def __init__(self, status: int, where: str, message: str):
+        super().__init__(f"{where}: status {status} ({message})")
+        self.status = status
+
+
+_lib = None
+
+EXPORTS = [
+    "fkb_version", "fkb_status_string", "fkb_last_error", "fkb_derive_resize",
+    "fkb_reference_block_size", "fkb_plan_create", "fkb_plan_launch", "fkb_plan_get_info",
+    "fkb_plan_get_resize_params", "fkb_plan_destroy", "fkb_execute", "fkb_execute_host",
+]
+
+
+def load_library(path: os.PathLike | None = None) -> C.CDLL:
+    """Loads libfkb200.so.  There is no fallback: a missing library is an error."""
+    global _lib
+    if _lib is not None and path is None:
+        return _lib
+    p = Path(path) if path else LIB_PATH
+    if not p.exists():
+        raise FileNotFoundError(
+            f"{p} not found: build it with `python -m fusedkernellibrary_b200.build` "
+            "(there is no CPU or PyTorch fallback for this path)")
+    lib = C.CDLL(str(p))
+    lib.fkb_version.restype = C.c_int
+    lib.fkb_status_string.restype = C.c_char_p
+    lib.fkb_status_string.argtypes = [C.c_int]
+    lib.fkb_last_error.restype = C.c_char_p
+    lib.fkb_derive_resize.argtypes = [C.c_int32] * 5 + [C.POINTER(ResizeParams)]
+    lib.fkb_reference_block_size.argtypes = [C.c_uint32, C.c_uint32, C.POINTER(C.c_uint32),
+                                             C.POINTER(C.c_uint32)]
+    lib.fkb_plan_create.argtypes = [C.POINTER(PlanDesc), C.POINTER(C.c_void_p)]
+    lib.fkb_plan_launch.argtypes = [C.c_void_p, C.c_void_p]
+    lib.fkb_plan_get_info.argtypes = [C.c_void_p, C.POINTER(PlanInfo)]
+    lib.fkb_plan_get_resize_params.argtypes = [C.c_void_p, C.c_int32, C.POINTER(ResizeParams)]
+    lib.fkb_plan_destroy.argtypes = [C.c_void_p]
+    lib.fkb_execute.argtypes = [C.POINTER(PlanDesc), C.c_void_p]
+    lib.fkb_execute_host.argtypes = [C.POINTER(PlanDesc), C.c_void_p]
+    if path is None:
+        _lib = lib
+    return lib
+
+
+def check(status: int, where: str) -> None:
+    if status != OK:
+        lib = load_library()
+        raise FkbError(status, where, (lib.fkb_last_error() or b"").decode() or
+                       lib.fkb_status_string(status).decode())
+
+
+class DevicePlan:
+    """A plan resident on the current CUDA device (fkb_plan_create ... fkb_plan_destroy)."""
+
+    def __init__(self, host_plan: HostPlan):
+        self._lib = load_library()
+        self._h = C.c_void_p()
+        desc = host_plan.desc()
+        check(self._lib.fkb_plan_create(C.byref(desc), C.byref(self._h)), "fkb_plan_create")
+
+    def launch(self, stream: int | None = None) -> None:
+        check(self._lib.fkb_plan_launch(self._h, C.c_void_p(stream or 0)), "fkb_plan_launch")
+
+    def info(self) -> PlanInfo:
+        info = PlanInfo()
+        check(self._lib.fkb_plan_get_info(self._h, C.byref(info)), "fkb_plan_get_info")
+        return info
+
+    def resize_params(self, index: int) -> ResizeParams:
+        rp = ResizeParams()
+        check(self._lib.fkb_plan_get_resize_params(self._h, index, C.byref(rp)),
+              "fkb_plan_get_resize_params")
+        return rp
+
+    def destroy(self) -> None:
+        if self._h:
+            self._lib.fkb_plan_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
+
+def execute(host_plan: HostPlan, stream: int | None = None) -> None:
+    lib = load_library()
+    desc = host_plan.desc()
+    check(lib.fkb_execute(C.byref(desc), C.c_void_p(stream or 0)), "fkb_execute")
+
+
+def execute_host(host_plan: HostPlan, stream: int | None = None) -> None:
+    lib = load_library()
+    desc = host_plan.desc()
+    check(lib.fkb_execute_host(C.byref(desc), C.c_void_p(stream or 0)), "fkb_execute_host")

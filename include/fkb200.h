@@ -1,0 +1,213 @@
+/* fkb200 - C ABI of the B200-native fused-execution path.
+ *
+ * This is the boundary a host front end binds in place of the reference's single launch
+ * site: Executor<TransformDPP<ParArch::GPU_NVIDIA,TF>>::executeOperations_helper
+ * (core/execution_model/executors.h:252-287), reached from fk::executeOperations
+ * (fused_kernel.h:22-54).  The reference passes every instantiable operation by value
+ * as a kernel argument (executor_details/executor_kernels.h:25-29) and fixes the batch
+ * size at compile time (operation_model/batch_operations.h:98-102); here a sender chain
+ * plus its receiver is described by a plain-old-data plan whose batch size is a
+ * run-time value and whose per-plane descriptors live in device memory.
+ *
+ * Conventions: extern "C", plain pointers and sizes, int status return, no exceptions
+ * across the boundary, nothing on the device ever traps.  All image pointers inside a
+ * plan are DEVICE pointers of the current CUDA device unless a function says otherwise;
+ * the library never takes ownership of them (the reference's instantiable operations
+ * hold non-owning RawPtr values too, core/data/rawptr.h:124-157).  Launches are
+ * asynchronous on the caller's stream, like the reference's (executors.h:284-285).
+ */
+#ifndef FKB200_H
+#define FKB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------------------ */
+/* status codes                                                                         */
+/* ------------------------------------------------------------------------------------ */
+typedef enum fkb_status {
+    FKB_OK = 0,
+    FKB_ERR_INVALID_ARGUMENT = 1, /* null pointer, zero size, rect outside its image, ...     */
+    FKB_ERR_UNSUPPORTED = 2,      /* a chain shape the kernels do not implement               */
+    FKB_ERR_CUDA = 3,             /* a CUDA runtime call failed; see fkb_last_error()         */
+    FKB_ERR_TOO_LARGE = 4,        /* beyond a stated capacity (fixed-scratch entry point)     */
+    FKB_ERR_NO_DEVICE = 5         /* no usable CUDA device: there is no CPU fallback          */
+} fkb_status;
+
+/* ------------------------------------------------------------------------------------ */
+/* vocabulary                                                                           */
+/* ------------------------------------------------------------------------------------ */
+
+/* Pixel format of a source image (what the chain's read operation returns per element). */
+typedef enum fkb_src_format {
+    FKB_SRC_U8X3 = 1,  /* PerThreadRead<_2D, uchar3>  (memory_operations.h:71-112)            */
+    FKB_SRC_F32X3 = 2, /* PerThreadRead<_2D, float3>                                          */
+    FKB_SRC_NV12 = 3   /* ReadYUV<NV12> (color_conversion.h:314-346): `height` luma rows then */
+                       /* height/2 rows of interleaved U,V, chroma at data + pitch*height     */
+} fkb_src_format;
+
+/* Layout written by the receiver. */
+typedef enum fkb_dst_format {
+    FKB_DST_F32X3_PACKED = 1, /* PerThreadWrite<_2D,float3> / TensorWrite<float3>             */
+                              /* (memory_operations.h:114-137,173-193)                        */
+    FKB_DST_F32_PLANAR3 = 2,  /* TensorSplit<float3> (memory_operations.h:195-226): channel c */
+                              /* of a plane at byte offset c * channel_stride                 */
+    FKB_DST_U8X3_PACKED = 3   /* PerThreadWrite<_2D,uchar3> / TensorWrite<uchar3>             */
+} fkb_dst_format;
+
+/* Geometry stage between the read and the element-wise continuation. */
+typedef enum fkb_resize_mode {
+    FKB_RESIZE_NONE = 0,        /* output element (x,y) reads source element (x,y) of the crop */
+    FKB_RESIZE_IGNORE_AR = 1,   /* Resize<INTER_LINEAR, IGNORE_AR>   (resize.h:105-119)         */
+    FKB_RESIZE_PRESERVE_AR = 2  /* Resize<INTER_LINEAR, PRESERVE_AR> (resize.h:121-166)         */
+} fkb_resize_mode;
+
+/* Element-wise operations, applied per channel in IEEE-754 binary32 with no contraction.   */
+typedef enum fkb_opcode {
+    FKB_OP_MUL = 1,             /* Mul<float3>  v * p   (basic_ops/arithmetic.h:64-75)          */
+    FKB_OP_SUB = 2,             /* Sub<float3>  v - p   (arithmetic.h:52-62)                    */
+    FKB_OP_DIV = 3,             /* Div<float3>  v / p, true division (arithmetic.h:77-88)       */
+    FKB_OP_ADD = 4,             /* Add<float3>  v + p   (arithmetic.h:26-35)                    */
+    FKB_OP_CAST_F32 = 5,        /* Cast<uchar3,float3> (basic_ops/cast.h:23-33); exact          */
+    FKB_OP_SWAP_RB = 6,         /* ColorConversion<COLOR_RGB2BGR|COLOR_BGR2RGB> =               */
+                                /* VectorReorder<T,2,1,0> (basic_ops/cuda_vector.h:50-62)       */
+    FKB_OP_SATURATE_CAST_U8 = 7,/* SaturateCast<float3,uchar3> (image_processing/saturate.h)    */
+    FKB_OP_YUV_TO_RGB_BT709_FULL = 8 /* ConvertYUVToRGB<NV12,Full,bt709,false,float3>           */
+                                /* (color_conversion.h:250-309, matrix :143-146)                */
+} fkb_opcode;
+
+typedef struct fkb_op {
+    int32_t opcode; /* fkb_opcode */
+    float p[3];     /* per-channel parameter of MUL/SUB/DIV/ADD; ignored by the others */
+} fkb_op;
+
+/* One operation sequence = one sender chain closed by one receiver kind.
+ * ops[0 .. n_pre_ops) run on every tap BEFORE interpolation (they are part of the resize's
+ * back operation, as in Read.then(Cast).then(Resize) or ReadYUV.then(ConvertYUVToRGB).then(Resize));
+ * ops[n_pre_ops .. n_ops) run on the interpolated value.  With FKB_RESIZE_NONE the split is
+ * irrelevant and all ops run in order. */
+typedef struct fkb_sequence {
+    int32_t src_format;   /* fkb_src_format */
+    int32_t dst_format;   /* fkb_dst_format */
+    int32_t resize_mode;  /* fkb_resize_mode */
+    int32_t n_ops;
+    int32_t n_pre_ops;
+    float background[3];  /* PRESERVE_AR default value (resize.h:53, :158); the continuation */
+                          /* still applies to it (resize.h:84-86)                            */
+    const fkb_op* ops;    /* HOST pointer, n_ops entries (may be NULL when n_ops == 0)       */
+} fkb_sequence;
+
+/* One output plane (the reference's thread.z / blockIdx.z, data_parallel_patterns.h:260). */
+typedef struct fkb_plane {
+    const void* src;        /* source image of this plane                                     */
+    uint32_t src_width;     /* in pixels                                                      */
+    uint32_t src_height;
+    uint32_t src_pitch;     /* bytes between rows (core/data/rawptr.h:205-207)                */
+    int32_t crop_x;         /* Crop rect (image_processing/crop.h:35-38, core/data/rect.h);   */
+    int32_t crop_y;         /* the whole image when the chain has no Crop                     */
+    int32_t crop_width;
+    int32_t crop_height;
+    void* dst;              /* first element of this plane's output                           */
+    uint32_t dst_width;     /* in pixels                                                      */
+    uint32_t dst_height;
+    uint32_t dst_pitch;     /* bytes between output rows                                      */
+    uint32_t dst_channel_stride; /* FKB_DST_F32_PLANAR3: bytes between channel planes         */
+    int32_t sequence;       /* index into fkb_plan_desc.sequences (divergent horizontal fusion,*/
+                            /* data_parallel_patterns.h:315-323); 0 for an ordinary batch     */
+    int32_t reserved;
+} fkb_plane;
+
+typedef struct fkb_plan_desc {
+    const fkb_sequence* sequences; /* HOST pointer */
+    int32_t n_sequences;
+    const fkb_plane* planes;       /* HOST pointer */
+    int32_t n_planes;
+} fkb_plan_desc;
+
+/* Host-derived resize parameters of one plane (Resize::build, resize.h:105-166,196-221). */
+typedef struct fkb_resize_params {
+    float fx, fy;                    /* source step per output element                         */
+    int32_t x1, y1, x2, y2;          /* inclusive region of interest inside the output         */
+    int32_t target_width, target_height;
+} fkb_resize_params;
+
+/* What a plan will do when launched. */
+typedef struct fkb_plan_info {
+    int32_t n_planes;
+    int32_t n_sequences;
+    int32_t n_launches;          /* kernels launched by one fkb_plan_launch                    */
+    uint32_t grid_x;             /* grid of the (first) launch                                 */
+    uint32_t block_x;
+    uint64_t output_pixels;
+    uint64_t algorithmic_bytes;  /* source bytes inside the crop rects + output bytes          */
+    uint64_t device_bytes;       /* device memory held by the plan's descriptors               */
+} fkb_plan_info;
+
+typedef struct fkb_plan fkb_plan; /* opaque; owns only its own descriptor memory */
+
+/* ------------------------------------------------------------------------------------ */
+/* entry points                                                                         */
+/* ------------------------------------------------------------------------------------ */
+
+/* Library version, major*10000 + minor*100 + patch. */
+int fkb_version(void);
+
+/* Human-readable name of a status code. Never NULL. */
+const char* fkb_status_string(int status);
+
+/* Message of the last failure on the calling thread (empty string if none). */
+const char* fkb_last_error(void);
+
+/* Restates Resize::build's host arithmetic (resize.h:105-166) and compute_target_size
+ * (resize.h:196-221): float scale, cxp::round (constexpr_cmath.h:119-130), double
+ * reciprocal narrowed once.  mode is FKB_RESIZE_IGNORE_AR or FKB_RESIZE_PRESERVE_AR. */
+int fkb_derive_resize(int32_t src_width, int32_t src_height, int32_t dst_width, int32_t dst_height,
+                      int32_t mode, fkb_resize_params* out);
+
+/* Restates the reference's block-shape search getDefaultBlockSize (executors.h:176-242).
+ * The kernels here do not use it; it is kept so that a front end can report the grid the
+ * reference would have launched. */
+int fkb_reference_block_size(uint32_t active_x, uint32_t active_y, uint32_t* block_x, uint32_t* block_y);
+
+/* Validates a plan description, derives the per-plane resize parameters and copies the
+ * descriptors to the current device.  Replaces the work the reference does at compile
+ * time in Fuser::fuseAllIOps (operation_model/iop_fuser.h:44-129) and on the host in
+ * BatchRead::build (batch_operations.h:178-208).  The description and everything it
+ * points to may be released as soon as the call returns; image memory must stay valid
+ * until the launches that use it have finished. */
+int fkb_plan_create(const fkb_plan_desc* desc, fkb_plan** out_plan);
+
+/* Replaces launchTransformDPP_Kernel<<<grid, block, 0, stream>>> (executors.h:267,270,284)
+ * and, for plans with more than one sequence, launchDivergentBatchTransformDPP_Kernel
+ * (executor_kernels.h:20-23).  `stream` is a cudaStream_t (NULL = default stream).
+ * Asynchronous; returns the launch status only, like the reference's cudaGetLastError check. */
+int fkb_plan_launch(const fkb_plan* plan, void* stream);
+
+int fkb_plan_get_info(const fkb_plan* plan, fkb_plan_info* out_info);
+
+/* Copies the derived resize parameters of plane `index` out of a plan (for parity checks). */
+int fkb_plan_get_resize_params(const fkb_plan* plan, int32_t index, fkb_resize_params* out);
+
+/* Frees the plan's descriptor memory.  Call after the launches that use it have finished. */
+int fkb_plan_destroy(fkb_plan* plan);
+
+/* One-shot equivalent of fk::executeOperations(stream, sender, receiver) followed by
+ * stream.sync(): create, launch, synchronise the stream, destroy. */
+int fkb_execute(const fkb_plan_desc* desc, void* stream);
+
+/* Same as fkb_execute for callers whose images live in HOST memory: every pointer in
+ * desc->planes (src and dst) is a host pointer.  Distinct source images are copied to the
+ * device once each, the plan runs, every plane's output is copied back, and the call
+ * returns after the stream has been synchronised.  Rows of `src_pitch` / `dst_pitch` bytes
+ * are assumed; outputs of planes that share one allocation must not overlap. */
+int fkb_execute_host(const fkb_plan_desc* desc, void* stream);
+
+#ifdef __cplusplus
+} /* extern "C" */
+#endif
+
+#endif /* FKB200_H */

@@ -1,0 +1,111 @@
+/* extern "C" entry points around the UNMODIFIED reference headers (CPU backend).
+ *
+ * TEST INFRASTRUCTURE ONLY.  Compiled by oracle/Makefile against the reference's include
+ * tree where it lies (never copied); the shared objects go to oracle/_ref/.  Only tests,
+ * the smoke check and the CPU-baseline legs of the benchmark load them; the product path
+ * never does.
+ *
+ * Every entry point builds the sender chain a user of the reference would write
+ * (Op::build(...).then(...)), closes it with a receiver and runs it with
+ * fk::executeOperations<TransformDPP<ParArch::CPU>> (fused_kernel.h:22-25,
+ * core/execution_model/executors.h:147-173, data_parallel_patterns.h:272-299).
+ */
+#include "fklref_common.h"
+
+extern "C" {
+
+/* 1 when this library was built with the device-branch prelude, 0 for the literal CPU build. */
+int fklref_is_device_branch(void) {
+#ifdef FKLREF_DEVICE_BRANCH_PRELUDE_H
+    return 1;
+#else
+    return 0;
+#endif
+}
+
+/* PerThreadRead<uchar3> -> Cast<uchar3,float3> -> Mul -> Sub -> Div -> PerThreadWrite<float3> */
+void fklref_cast_mul_sub_div(const uint8_t* src, int w, int h, int spitch, const float* mul, const float* sub,
+                             const float* div, float* dst, int dpitch) {
+    CpuStream stream;
+    const auto sender = PerThreadRead<ND::_2D, uchar3>::build(raw_u8x3(src, w, h, spitch))
+                            .then(Cast<uchar3, float3>::build())
+                            .then(Mul<float3>::build(f3(mul)))
+                            .then(Sub<float3>::build(f3(sub)))
+                            .then(Div<float3>::build(f3(div)));
+    const auto receiver = PerThreadWrite<ND::_2D, float3>::build(raw_f32x3(dst, w, h, dpitch));
+    executeOperations<CpuDPP>(stream, sender, receiver);
+    stream.sync();
+}
+
+/* PerThreadRead<uchar3> -> Cast -> Mul -> Sub -> PerThreadWrite<float3> */
+void fklref_cast_mul_sub(const uint8_t* src, int w, int h, int spitch, const float* mul, const float* sub,
+                         float* dst, int dpitch) {
+    CpuStream stream;
+    const auto sender = PerThreadRead<ND::_2D, uchar3>::build(raw_u8x3(src, w, h, spitch))
+                            .then(Cast<uchar3, float3>::build())
+                            .then(Mul<float3>::build(f3(mul)))
+                            .then(Sub<float3>::build(f3(sub)));
+    const auto receiver = PerThreadWrite<ND::_2D, float3>::build(raw_f32x3(dst, w, h, dpitch));
+    executeOperations<CpuDPP>(stream, sender, receiver);
+    stream.sync();
+}
+
+/* PerThreadRead<uchar3> -> Cast -> Add -> Div -> PerThreadWrite<float3> */
+void fklref_cast_add_div(const uint8_t* src, int w, int h, int spitch, const float* add, const float* div,
+                         float* dst, int dpitch) {
+    CpuStream stream;
+    const auto sender = PerThreadRead<ND::_2D, uchar3>::build(raw_u8x3(src, w, h, spitch))
+                            .then(Cast<uchar3, float3>::build())
+                            .then(Add<float3>::build(f3(add)))
+                            .then(Div<float3>::build(f3(div)));
+    const auto receiver = PerThreadWrite<ND::_2D, float3>::build(raw_f32x3(dst, w, h, dpitch));
+    executeOperations<CpuDPP>(stream, sender, receiver);
+    stream.sync();
+}
+
+/* PerThreadRead<uchar3> -> RGB2BGR(uchar3) -> Cast -> Mul -> SaturateCast<float3,uchar3> -> PerThreadWrite<uchar3> */
+void fklref_bgr_cast_mul_saturate(const uint8_t* src, int w, int h, int spitch, const float* mul, uint8_t* dst,
+                                  int dpitch) {
+    CpuStream stream;
+    const auto sender = PerThreadRead<ND::_2D, uchar3>::build(raw_u8x3(src, w, h, spitch))
+                            .then(ColorConversion<ColorConversionCodes::COLOR_RGB2BGR, uchar3, uchar3>::build())
+                            .then(Cast<uchar3, float3>::build())
+                            .then(Mul<float3>::build(f3(mul)))
+                            .then(SaturateCast<float3, uchar3>::build());
+    const auto receiver = PerThreadWrite<ND::_2D, uchar3>::build(raw_u8x3(dst, w, h, dpitch));
+    executeOperations<CpuDPP>(stream, sender, receiver);
+    stream.sync();
+}
+
+/* PerThreadRead<uchar3> -> Cast<uchar3,float3> -> Resize<INTER_LINEAR, IGNORE_AR>(dw,dh) -> PerThreadWrite<float3> */
+void fklref_cast_resize(const uint8_t* src, int w, int h, int spitch, int dw, int dh, float* dst, int dpitch) {
+    CpuStream stream;
+    const auto sender = PerThreadRead<ND::_2D, uchar3>::build(raw_u8x3(src, w, h, spitch))
+                            .then(Cast<uchar3, float3>::build())
+                            .then(Resize<LINEAR>::build(Size(dw, dh)));
+    const auto receiver = PerThreadWrite<ND::_2D, float3>::build(raw_f32x3(dst, dw, dh, dpitch));
+    executeOperations<CpuDPP>(stream, sender, receiver);
+    stream.sync();
+}
+
+/* Host-side resize parameters exactly as Resize::build derives them (resize.h:105-166,196-221).
+   out = {fx, fy} as floats reinterpreted, then x1,y1,x2,y2 (PRESERVE_AR only; zeros otherwise). */
+void fklref_resize_params(int sw, int sh, int dw, int dh, int preserve_ar, float* fxy, int* roi) {
+    static uchar3 dummy;
+    const auto back = PerThreadRead<ND::_2D, uchar3>::build(
+        RawPtr<ND::_2D, uchar3>{&dummy, PtrDims<ND::_2D>((uint)sw, (uint)sh, (uint)(sw * 3))});
+    using BackT = std::decay_t<decltype(back)>;
+    if (preserve_ar) {
+        const auto r = Resize<LINEAR, AspectRatio::PRESERVE_AR, BackT>::build(back, Size(dw, dh), float3{0, 0, 0});
+        fxy[0] = r.params.src_conv_factors.x;
+        fxy[1] = r.params.src_conv_factors.y;
+        roi[0] = r.params.x1; roi[1] = r.params.y1; roi[2] = r.params.x2; roi[3] = r.params.y2;
+    } else {
+        const auto r = Resize<LINEAR, AspectRatio::IGNORE_AR, BackT>::build(back, Size(dw, dh));
+        fxy[0] = r.params.src_conv_factors.x;
+        fxy[1] = r.params.src_conv_factors.y;
+        roi[0] = roi[1] = roi[2] = roi[3] = 0;
+    }
+}
+
+}  // extern "C"

@@ -1,0 +1,69 @@
+/* extern "C" entry points around the UNMODIFIED reference headers (CPU backend).
+ *
+ * TEST INFRASTRUCTURE ONLY.  Compiled by oracle/Makefile against the reference's include
+ * tree where it lies (never copied); the shared objects go to oracle/_ref/.  Only tests,
+ * the smoke check and the CPU-baseline legs of the benchmark load them; the product path
+ * never does.
+ *
+ * Every entry point builds the sender chain a user of the reference would write
+ * (Op::build(...).then(...)), closes it with a receiver and runs it with
+ * fk::executeOperations<TransformDPP<ParArch::CPU>> (fused_kernel.h:22-25,
+ * core/execution_model/executors.h:147-173, data_parallel_patterns.h:272-299).
+ */
+#include "fklref_common.h"
+
+namespace {
+
+/* ---- NV12 -> RGB -> resize -> Div -> TensorWrite, one chunk ------------------------ */
+
+template <size_t B>
+void nv12_chunk(const uint8_t* const* frames, int w, int h, int pitch, int dw, int dh, const float* div,
+                float* out) {
+    CpuStream stream;
+    using Img = Image<PixelFormat::NV12>;
+    /* Wrap each frame as a view whose data height equals the image height so that the chroma
+       plane is addressed at data + pitch*h (color_conversion.h:336-341, image.h:35-38). */
+    auto make = [&](size_t i) {
+        Ptr<ND::_2D, uchar> view(const_cast<uint8_t*>(frames[i]), PtrDims<ND::_2D>((uint)w, (uint)h, (uint)pitch),
+                                 MemType::Host, 0);
+        return Img(view, (uint)w, (uint)h);
+    };
+    std::array<Img, B> imgs = [&]<size_t... I>(std::index_sequence<I...>) {
+        return std::array<Img, B>{make(I)...};
+    }(std::make_index_sequence<B>{});
+    const auto sender =
+        ReadYUV<PixelFormat::NV12>::build(imgs)
+            .then(ConvertYUVToRGB<PixelFormat::NV12, ColorRange::Full, ColorPrimitives::bt709, false, float3>::build())
+            .then(Resize<LINEAR>::build(Size(dw, dh)))
+            .then(Div<float3>::build(f3(div)));
+    const auto receiver = TensorWrite<float3>::build(raw_tensor<float3>(out, dw, dh, (int)B, 1));
+    executeOperations<CpuDPP>(stream, sender, receiver);
+    stream.sync();
+}
+
+}  // namespace
+
+extern "C" {
+
+/* ReadYUV<NV12>[B] -> ConvertYUVToRGB<NV12,Full,bt709,false,float3> -> Resize<INTER_LINEAR>(dw,dh) -> Div
+   -> TensorWrite<float3> (dw x dh x B).  Each frame: h rows of luma then h/2 rows of interleaved chroma, one pitch. */
+void fklref_nv12_resize(const uint8_t* const* frames, int w, int h, int pitch, int batch, int dw, int dh,
+                        const float* div, float* out) {
+    const size_t plane_floats = (size_t)dw * dh * 3;
+    int i = 0;
+    for (; i + 4 <= batch; i += 4) nv12_chunk<4>(frames + i, w, h, pitch, dw, dh, div, out + plane_floats * i);
+    for (; i + 2 <= batch; i += 2) nv12_chunk<2>(frames + i, w, h, pitch, dw, dh, div, out + plane_floats * i);
+    if (i < batch) {
+        if (batch >= 2) {
+            nv12_chunk<2>(frames + batch - 2, w, h, pitch, dw, dh, div, out + plane_floats * (batch - 2));
+        } else {
+            const uint8_t* two[2] = {frames[0], frames[0]};
+            float* scratch = new float[plane_floats * 2];
+            nv12_chunk<2>(two, w, h, pitch, dw, dh, div, scratch);
+            std::memcpy(out, scratch, plane_floats * sizeof(float));
+            delete[] scratch;
+        }
+    }
+}
+
+}  // extern "C"
