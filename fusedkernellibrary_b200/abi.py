@@ -173,7 +173,9 @@ _lib = None
 EXPORTS = [
     "fkb_version", "fkb_status_string", "fkb_last_error", "fkb_derive_resize",
     "fkb_reference_block_size", "fkb_plan_create", "fkb_plan_launch", "fkb_plan_get_info",
-    "fkb_plan_get_resize_params", "fkb_plan_destroy", "fkb_execute", "fkb_execute_host",
+    "fkb_plan_get_resize_params", "fkb_plan_destroy", "fkb_execute", "fkb_host_session_create",
+    "fkb_host_session_run", "fkb_host_session_get_traffic", "fkb_host_session_destroy",
+    "fkb_execute_host",
 ]
 
 
@@ -202,6 +204,10 @@ def load_library(path: os.PathLike | None = None) -> C.CDLL:
     lib.fkb_plan_destroy.argtypes = [C.c_void_p]
     lib.fkb_execute.argtypes = [C.POINTER(PlanDesc), C.c_void_p]
     lib.fkb_execute_host.argtypes = [C.POINTER(PlanDesc), C.c_void_p]
+    lib.fkb_host_session_create.argtypes = [C.POINTER(PlanDesc), C.POINTER(C.c_void_p)]
+    lib.fkb_host_session_run.argtypes = [C.c_void_p, C.c_void_p]
+    lib.fkb_host_session_get_traffic.argtypes = [C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
+    lib.fkb_host_session_destroy.argtypes = [C.c_void_p]
     if path is None:
         _lib = lib
     return lib
@@ -259,3 +265,33 @@ def execute_host(host_plan: HostPlan, stream: int | None = None) -> None:
     lib = load_library()
     desc = host_plan.desc()
     check(lib.fkb_execute_host(C.byref(desc), C.c_void_p(stream or 0)), "fkb_execute_host")
+
+
+class HostSession:
+    """Device mirrors for a plan whose images are host buffers (fkb_host_session_*)."""
+
+    def __init__(self, host_plan: HostPlan):
+        self._lib = load_library()
+        self._h = C.c_void_p()
+        desc = host_plan.desc()
+        check(self._lib.fkb_host_session_create(C.byref(desc), C.byref(self._h)), "fkb_host_session_create")
+
+    def run(self, stream: int | None = None) -> None:
+        check(self._lib.fkb_host_session_run(self._h, C.c_void_p(stream or 0)), "fkb_host_session_run")
+
+    def traffic(self) -> tuple[int, int]:
+        a, b = C.c_uint64(), C.c_uint64()
+        check(self._lib.fkb_host_session_get_traffic(self._h, C.byref(a), C.byref(b)),
+              "fkb_host_session_get_traffic")
+        return a.value, b.value
+
+    def destroy(self) -> None:
+        if self._h:
+            self._lib.fkb_host_session_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass

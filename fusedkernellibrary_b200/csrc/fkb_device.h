@@ -1,0 +1,84 @@
+/* Device-resident form of a plan: what fkb_plan_create uploads and the kernels read.
+ *
+ * The reference keeps the per-plane parameters in a compile-time-sized array inside the
+ * kernel arguments (operation_model/batch_operations.h:98-102, executor_kernels.h:25-29),
+ * which caps a launch at the 32 KB argument space.  Here they are rows of a table in
+ * global memory, read once per thread block, so the batch size is a run-time value.
+ */
+#ifndef FKB_DEVICE_H
+#define FKB_DEVICE_H
+
+#include <stdint.h>
+
+namespace fkb {
+
+/* How a plane is processed (chosen on the host from formats, sizes and alignment). */
+enum PlaneClass : uint32_t {
+    CLASS_GENERIC = 0,       /* one thread per output pixel, scalar accesses; always valid   */
+    CLASS_FLAT_U8_F32 = 1,   /* no geometry stage, 4 whole pixels per thread, vector accesses */
+    CLASS_FLAT_F32_F32 = 2,
+    CLASS_FLAT_U8_U8 = 3,
+    CLASS_RESIZE_U8_PLANAR = 4, /* bilinear, 4 adjacent output pixels per thread             */
+    CLASS_RESIZE_U8_PACKED = 5,
+    CLASS_RESIZE_NV12_PACKED = 6,
+    CLASS_COUNT = 7,
+    CLASS_MIXED = 0xFF       /* launch-level only: planes of several classes in one grid     */
+};
+
+struct alignas(16) DevPlane {
+    const uint8_t* src;      /* image base (not offset by the crop)                           */
+    uint8_t* dst;
+    uint32_t src_pitch;
+    uint32_t src_height;     /* NV12: chroma plane begins at src + src_pitch * src_height     */
+    int32_t crop_x, crop_y, crop_w, crop_h;
+    uint32_t dst_w, dst_h, dst_pitch, dst_cstride;
+    float fx, fy;            /* resize.h:108-112: source step per output element              */
+    int32_t x1, y1, x2, y2;  /* PRESERVE_AR region of interest, inclusive (resize.h:150-158)  */
+    uint32_t seq;
+    uint32_t plane_class;
+    uint32_t seg_pixels;     /* FLAT classes: pixels per contiguous segment                   */
+    uint32_t n_segs;         /* FLAT classes: 1 (dense plane) or dst_h (one segment per row)  */
+};
+static_assert(sizeof(DevPlane) == 96, "DevPlane layout");
+
+struct alignas(16) DevOp {
+    int32_t opcode;
+    float p[3];
+};
+static_assert(sizeof(DevOp) == 16, "DevOp layout");
+
+struct alignas(16) DevSeq {
+    int32_t src_format, dst_format, resize_mode;
+    int32_t n_ops, n_pre, ops_begin; /* ops_begin: index of the first op in the op table      */
+    int32_t pre_kind;                /* PRE_* below                                           */
+    int32_t pad;
+    float bg[4];
+};
+static_assert(sizeof(DevSeq) == 48, "DevSeq layout");
+
+enum PreKind : int32_t {
+    PRE_IDENTITY = 0, /* nothing, or only exact uchar->float casts, before interpolation      */
+    PRE_YUV_BT709 = 1,/* exactly ConvertYUVToRGB<NV12,Full,bt709,false,float3>                */
+    PRE_GENERAL = 2   /* any other chain: interpreted per tap (generic class only)           */
+};
+
+/* Kernel argument block (passed by value; 64 bytes). */
+struct LaunchArgs {
+    const DevPlane* planes;
+    const DevSeq* seqs;
+    const DevOp* ops;
+    const uint32_t* item_start; /* n_planes + 1 prefix sums of work items per plane          */
+    uint32_t n_planes;
+    uint32_t uniform_items;     /* > 0: every plane has this many work items                  */
+    uint32_t total_items;
+    uint32_t max_seq_ops;       /* longest sequence: sizes the shared-memory op cache         */
+};
+
+constexpr int BLOCK_THREADS = 256;
+constexpr int PX_PER_THREAD = 4;
+constexpr int ITEM_PIXELS_VEC = BLOCK_THREADS * PX_PER_THREAD; /* FLAT and RESIZE classes     */
+constexpr int ITEM_PIXELS_GENERIC = BLOCK_THREADS;
+
+}  // namespace fkb
+
+#endif

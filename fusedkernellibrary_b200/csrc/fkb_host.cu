@@ -1,0 +1,617 @@
+/* Host side of the C ABI: validation, host-derived parameters, plan upload and launch.
+ *
+ * Replaces, for this path, the reference's compile-time lowering of a sender chain
+ * (operation_model/iop_fuser.h:44-129, fused_operation.h), the batch builder
+ * (batch_operations.h:178-208) and the launch site (executors.h:252-287).
+ */
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "fkb200.h"
+#include "fkb_device.h"
+
+namespace fkb {
+cudaError_t launch_plan_kernel(uint32_t launch_class, const LaunchArgs& a, cudaStream_t stream);
+}
+
+using namespace fkb;
+
+/* ------------------------------------------------------------------------------------ */
+/* errors                                                                               */
+/* ------------------------------------------------------------------------------------ */
+static thread_local char g_last_error[512] = "";
+
+static int fail(int status, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_last_error, sizeof g_last_error, fmt, ap);
+    va_end(ap);
+    return status;
+}
+
+/* Same wording as the reference's gpuErrchk (core/utils/utils.h:95-109). */
+static int fail_cuda(cudaError_t e, const char* what, int line) {
+    return fail(FKB_ERR_CUDA, "GPU Error: %s (%s) File: %s Line: %d", cudaGetErrorString(e), what, "fkb_host.cu", line);
+}
+#define FKB_CUDA(call)                                                   \
+    do {                                                                 \
+        const cudaError_t e__ = (call);                                  \
+        if (e__ != cudaSuccess) return fail_cuda(e__, #call, __LINE__);  \
+    } while (0)
+
+/* ------------------------------------------------------------------------------------ */
+/* plan object                                                                          */
+/* ------------------------------------------------------------------------------------ */
+struct fkb_plan {
+    int device = -1;
+    void* d_block = nullptr; /* one allocation: planes | seqs | ops | item_start */
+    size_t d_bytes = 0;
+    LaunchArgs args{};
+    uint32_t launch_class = CLASS_GENERIC;
+    std::vector<fkb_resize_params> resize;
+    fkb_plan_info info{};
+};
+
+/* What one plan needs in device memory, laid out for a single copy. */
+struct HostImage {
+    std::vector<DevPlane> planes;
+    std::vector<DevSeq> seqs;
+    std::vector<DevOp> ops;
+    std::vector<uint32_t> item_start;
+    std::vector<fkb_resize_params> resize;
+    uint32_t launch_class = CLASS_GENERIC;
+    uint32_t uniform_items = 0;
+    uint32_t total_items = 0;
+    uint32_t max_seq_ops = 0;
+    uint64_t output_pixels = 0;
+    uint64_t algorithmic_bytes = 0;
+
+    size_t off_planes() const { return 0; }
+    size_t off_seqs() const { return planes.size() * sizeof(DevPlane); }
+    size_t off_ops() const { return off_seqs() + seqs.size() * sizeof(DevSeq); }
+    size_t off_items() const { return off_ops() + std::max<size_t>(ops.size(), 1) * sizeof(DevOp); }
+    size_t bytes() const { return off_items() + item_start.size() * sizeof(uint32_t); }
+
+    void serialize(unsigned char* dst) const {
+        std::memcpy(dst + off_planes(), planes.data(), planes.size() * sizeof(DevPlane));
+        std::memcpy(dst + off_seqs(), seqs.data(), seqs.size() * sizeof(DevSeq));
+        if (!ops.empty()) std::memcpy(dst + off_ops(), ops.data(), ops.size() * sizeof(DevOp));
+        std::memcpy(dst + off_items(), item_start.data(), item_start.size() * sizeof(uint32_t));
+    }
+    LaunchArgs args_for(const unsigned char* d_base) const {
+        LaunchArgs a{};
+        a.planes = reinterpret_cast<const DevPlane*>(d_base + off_planes());
+        a.seqs = reinterpret_cast<const DevSeq*>(d_base + off_seqs());
+        a.ops = reinterpret_cast<const DevOp*>(d_base + off_ops());
+        a.item_start = reinterpret_cast<const uint32_t*>(d_base + off_items());
+        a.n_planes = (uint32_t)planes.size();
+        a.uniform_items = uniform_items;
+        a.total_items = total_items;
+        a.max_seq_ops = max_seq_ops;
+        return a;
+    }
+};
+
+/* ------------------------------------------------------------------------------------ */
+/* host-derived parameters                                                              */
+/* ------------------------------------------------------------------------------------ */
+
+/* cxp::round (constexpr_libs/constexpr_cmath.h:119-130): add or subtract one half, truncate. */
+static float round_half_away(float x) {
+    return x > 0.0f ? static_cast<float>(static_cast<int>(x + 0.5f)) : static_cast<float>(static_cast<int>(x - 0.5f));
+}
+
+extern "C" FKB_API int fkb_derive_resize(int32_t sw, int32_t sh, int32_t dw, int32_t dh, int32_t mode,
+                                 fkb_resize_params* out) {
+    if (!out) return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_derive_resize: out is NULL");
+    if (sw <= 0 || sh <= 0 || dw <= 0 || dh <= 0)
+        return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_derive_resize: sizes must be positive (%d x %d -> %d x %d)", sw, sh,
+                    dw, dh);
+    int tw = dw, th = dh;
+    if (mode == FKB_RESIZE_PRESERVE_AR) {
+        /* compute_target_size (resize.h:196-221): fit the height first, fall back to fitting
+           the width when the scaled width overflows. */
+        volatile float scale = static_cast<float>(dh) / static_cast<float>(sh);
+        volatile float scaled_w = scale * static_cast<float>(sw);
+        tw = static_cast<int>(round_half_away(scaled_w));
+        if (tw > dw) {
+            volatile float scale_w = static_cast<float>(dw) / static_cast<float>(sw);
+            volatile float scaled_h = scale_w * static_cast<float>(sh);
+            tw = dw;
+            th = static_cast<int>(round_half_away(scaled_h));
+        }
+        out->x1 = (dw - tw) / 2; /* resize.h:150-151 */
+        out->y1 = (dh - th) / 2;
+        out->x2 = out->x1 + tw - 1;
+        out->y2 = out->y1 + th - 1;
+    } else if (mode == FKB_RESIZE_IGNORE_AR) {
+        out->x1 = 0; out->y1 = 0; out->x2 = dw - 1; out->y2 = dh - 1;
+    } else {
+        return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_derive_resize: mode %d is not a resize mode", mode);
+    }
+    /* resize.h:108-112 / :127-128,153-156: double quotient, double reciprocal, one narrowing */
+    const double cfx = static_cast<double>(tw) / static_cast<double>(sw);
+    const double cfy = static_cast<double>(th) / static_cast<double>(sh);
+    out->fx = static_cast<float>(1.0 / cfx);
+    out->fy = static_cast<float>(1.0 / cfy);
+    out->target_width = tw;
+    out->target_height = th;
+    return FKB_OK;
+}
+
+/* computeDiscardedThreads + the scan of computeBestSolution (executors.h:176-242). */
+extern "C" FKB_API int fkb_reference_block_size(uint32_t ax, uint32_t ay, uint32_t* bx, uint32_t* by) {
+    if (!bx || !by || ax == 0 || ay == 0) return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_reference_block_size: bad argument");
+    static const uint32_t X[4] = {32, 64, 128, 256};
+    static const uint32_t Y[2][4] = {{8, 4, 2, 1}, {6, 3, 3, 2}};
+    uint32_t best = UINT32_MAX, bi = 0, bj = 0;
+    bool done = false;
+    for (uint32_t i = 0; i < 4 && !done; ++i) {
+        for (uint32_t j = 0; j < 2 && !done; ++j) {
+            const uint32_t mx = ax % X[i], my = ay % Y[j][i];
+            const uint32_t idle_x = mx ? X[i] - mx : 0, idle_y = my ? Y[j][i] - my : 0;
+            const uint32_t idle = idle_x * (my ? ay + Y[j][i] : ay) + idle_y * ax;
+            if (idle < best) {
+                best = idle; bi = i; bj = j;
+                done = (idle == 0);
+            }
+        }
+    }
+    *bx = X[bi];
+    *by = Y[bj][bi];
+    return FKB_OK;
+}
+
+/* ------------------------------------------------------------------------------------ */
+/* validation and lowering                                                              */
+/* ------------------------------------------------------------------------------------ */
+enum ValueType { VT_U8 = 0, VT_F32 = 1, VT_YUV8 = 2 };
+
+static uint32_t src_pixel_bytes(int f) { return f == FKB_SRC_U8X3 ? 3u : f == FKB_SRC_F32X3 ? 12u : 1u; }
+static uint32_t dst_pixel_bytes(int f) { return f == FKB_DST_U8X3_PACKED ? 3u : f == FKB_DST_F32X3_PACKED ? 12u : 4u; }
+
+/* Walks a sequence's operations with the value type the reference's templates would have
+   (a mismatch there is a compile error; here it is FKB_ERR_INVALID_ARGUMENT). */
+static int check_sequence(const fkb_sequence& s, int index, DevSeq& ds) {
+    if (s.src_format < FKB_SRC_U8X3 || s.src_format > FKB_SRC_NV12)
+        return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d: unknown source format %d", index, s.src_format);
+    if (s.dst_format < FKB_DST_F32X3_PACKED || s.dst_format > FKB_DST_U8X3_PACKED)
+        return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d: unknown destination format %d", index, s.dst_format);
+    if (s.resize_mode < FKB_RESIZE_NONE || s.resize_mode > FKB_RESIZE_PRESERVE_AR)
+        return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d: unknown resize mode %d", index, s.resize_mode);
+    if (s.n_ops < 0 || s.n_ops > 4096) return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d: n_ops %d outside [0, 4096]", index, s.n_ops);
+    if (s.n_ops > 0 && !s.ops) return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d: ops is NULL", index);
+    const int n_pre = s.resize_mode == FKB_RESIZE_NONE ? 0 : s.n_pre_ops;
+    if (n_pre < 0 || n_pre > s.n_ops)
+        return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d: n_pre_ops %d outside [0, n_ops]", index, s.n_pre_ops);
+
+    ValueType t = s.src_format == FKB_SRC_U8X3 ? VT_U8 : s.src_format == FKB_SRC_F32X3 ? VT_F32 : VT_YUV8;
+    bool pre_only_casts = true, pre_is_yuv = (n_pre == 1);
+    for (int k = 0; k <= s.n_ops; ++k) {
+        if (k == n_pre && s.resize_mode != FKB_RESIZE_NONE) t = VT_F32; /* Interpolate returns float (interpolation.h:55-57) */
+        if (k == s.n_ops) break;
+        const int oc = s.ops[k].opcode;
+        if (k < n_pre) {
+            if (oc != FKB_OP_CAST_F32) pre_only_casts = false;
+            if (oc != FKB_OP_YUV_TO_RGB_BT709_FULL) pre_is_yuv = false;
+        }
+        switch (oc) {
+            case FKB_OP_MUL: case FKB_OP_SUB: case FKB_OP_DIV: case FKB_OP_ADD:
+                if (t != VT_F32) return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d op %d: arithmetic on a non-float value (add a Cast first)", index, k);
+                break;
+            case FKB_OP_CAST_F32:
+                if (t == VT_YUV8) return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d op %d: Cast on packed YUV is not part of this path", index, k);
+                t = VT_F32;
+                break;
+            case FKB_OP_SWAP_RB: break;
+            case FKB_OP_SATURATE_CAST_U8:
+                if (t != VT_F32) return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d op %d: SaturateCast<float3,uchar3> needs a float value", index, k);
+                t = VT_U8;
+                break;
+            case FKB_OP_YUV_TO_RGB_BT709_FULL:
+                if (t != VT_YUV8) return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d op %d: ConvertYUVToRGB needs the value read by ReadYUV", index, k);
+                t = VT_F32;
+                break;
+            default:
+                return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d op %d: unknown opcode %d", index, k, oc);
+        }
+    }
+    const bool dst_u8 = s.dst_format == FKB_DST_U8X3_PACKED;
+    if (dst_u8 != (t == VT_U8 || t == VT_YUV8))
+        return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d: chain ends in a %s value but the receiver writes %s", index,
+                    t == VT_F32 ? "float" : "uchar", dst_u8 ? "uchar3" : "float");
+
+    ds.src_format = s.src_format; ds.dst_format = s.dst_format; ds.resize_mode = s.resize_mode;
+    ds.n_ops = s.n_ops; ds.n_pre = n_pre; ds.ops_begin = 0; ds.pad = 0;
+    ds.pre_kind = (n_pre == 0 || pre_only_casts) ? PRE_IDENTITY : pre_is_yuv ? PRE_YUV_BT709 : PRE_GENERAL;
+    ds.bg[0] = s.background[0]; ds.bg[1] = s.background[1]; ds.bg[2] = s.background[2]; ds.bg[3] = 0.0f;
+    return FKB_OK;
+}
+
+static bool aligned(const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+static int lower(const fkb_plan_desc* d, HostImage& img) {
+    if (!d) return fail(FKB_ERR_INVALID_ARGUMENT, "plan description is NULL");
+    if (!d->sequences || d->n_sequences <= 0) return fail(FKB_ERR_INVALID_ARGUMENT, "plan has no sequences");
+    if (!d->planes || d->n_planes <= 0) return fail(FKB_ERR_INVALID_ARGUMENT, "plan has no planes (batch of 0)");
+
+    img.seqs.resize(d->n_sequences);
+    for (int s = 0; s < d->n_sequences; ++s) {
+        const int rc = check_sequence(d->sequences[s], s, img.seqs[s]);
+        if (rc) return rc;
+        img.seqs[s].ops_begin = (int32_t)img.ops.size();
+        for (int k = 0; k < d->sequences[s].n_ops; ++k) {
+            DevOp o;
+            o.opcode = d->sequences[s].ops[k].opcode;
+            o.p[0] = d->sequences[s].ops[k].p[0]; o.p[1] = d->sequences[s].ops[k].p[1]; o.p[2] = d->sequences[s].ops[k].p[2];
+            img.ops.push_back(o);
+        }
+        img.max_seq_ops = std::max<uint32_t>(img.max_seq_ops, (uint32_t)d->sequences[s].n_ops);
+    }
+
+    img.planes.resize(d->n_planes);
+    img.resize.assign(d->n_planes, fkb_resize_params{});
+    img.item_start.assign((size_t)d->n_planes + 1, 0);
+    uint64_t total = 0;
+    bool uniform = true;
+    uint32_t first_items = 0;
+    uint32_t common_class = CLASS_MIXED;
+    for (int i = 0; i < d->n_planes; ++i) {
+        const fkb_plane& p = d->planes[i];
+        if (p.sequence < 0 || p.sequence >= d->n_sequences)
+            return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: sequence index %d outside [0, %d)", i, p.sequence, d->n_sequences);
+        const DevSeq& s = img.seqs[p.sequence];
+        if (!p.src || !p.dst) return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: null image pointer", i);
+        if (p.src_width == 0 || p.src_height == 0 || p.dst_width == 0 || p.dst_height == 0)
+            return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: zero-sized image", i);
+        if (p.src_width > (1u << 24) || p.src_height > (1u << 24) || p.dst_width > (1u << 24) || p.dst_height > (1u << 24))
+            return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: image side beyond 2^24", i);
+        const uint32_t spx = src_pixel_bytes(s.src_format), dpx = dst_pixel_bytes(s.dst_format);
+        const uint64_t src_row = s.src_format == FKB_SRC_NV12 ? 2ull * ((p.src_width + 1) / 2) : (uint64_t)p.src_width * spx;
+        if (p.src_pitch < src_row)
+            return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: source pitch %u is less than a row of %llu bytes", i, p.src_pitch, (unsigned long long)src_row);
+        if ((uint64_t)p.src_pitch * p.src_height * 2 > 0xFFFFFFFFull)
+            return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: source image beyond 2 GiB", i);
+        if (p.dst_pitch < (uint64_t)p.dst_width * dpx)
+            return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: destination pitch %u is less than a row of %llu bytes", i, p.dst_pitch, (unsigned long long)p.dst_width * dpx);
+        if (p.crop_x < 0 || p.crop_y < 0 || p.crop_width <= 0 || p.crop_height <= 0 ||
+            (uint64_t)p.crop_x + (uint64_t)p.crop_width > p.src_width || (uint64_t)p.crop_y + (uint64_t)p.crop_height > p.src_height)
+            return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: crop rect (%d,%d,%d,%d) outside its %ux%u image", i, p.crop_x, p.crop_y, p.crop_width, p.crop_height, p.src_width, p.src_height);
+        if (s.resize_mode == FKB_RESIZE_NONE && ((uint32_t)p.crop_width != p.dst_width || (uint32_t)p.crop_height != p.dst_height))
+            return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: without a resize the output (%ux%u) must have the size of the crop (%dx%d)", i, p.dst_width, p.dst_height, p.crop_width, p.crop_height);
+        if (s.src_format == FKB_SRC_F32X3 && (!aligned(p.src, 4) || p.src_pitch % 4))
+            return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: float source must be 4-byte aligned", i);
+        if (s.dst_format != FKB_DST_U8X3_PACKED && (!aligned(p.dst, 4) || p.dst_pitch % 4 || p.dst_channel_stride % 4))
+            return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: float destination must be 4-byte aligned", i);
+        if (s.dst_format == FKB_DST_F32_PLANAR3 && p.dst_channel_stride < (uint64_t)p.dst_pitch * (p.dst_height - 1) + (uint64_t)p.dst_width * 4)
+            return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: channel stride %u overlaps the channel plane", i, p.dst_channel_stride);
+
+        DevPlane& dp = img.planes[i];
+        std::memset(&dp, 0, sizeof dp);
+        dp.src = static_cast<const uint8_t*>(p.src);
+        dp.dst = static_cast<uint8_t*>(p.dst);
+        dp.src_pitch = p.src_pitch; dp.src_height = p.src_height;
+        dp.crop_x = p.crop_x; dp.crop_y = p.crop_y; dp.crop_w = p.crop_width; dp.crop_h = p.crop_height;
+        dp.dst_w = p.dst_width; dp.dst_h = p.dst_height; dp.dst_pitch = p.dst_pitch; dp.dst_cstride = p.dst_channel_stride;
+        dp.seq = (uint32_t)p.sequence;
+        dp.fx = dp.fy = 1.0f;
+        dp.x2 = (int32_t)p.dst_width - 1; dp.y2 = (int32_t)p.dst_height - 1;
+        if (s.resize_mode != FKB_RESIZE_NONE) {
+            fkb_resize_params& rp = img.resize[i];
+            const int rc = fkb_derive_resize(p.crop_width, p.crop_height, (int32_t)p.dst_width, (int32_t)p.dst_height, s.resize_mode, &rp);
+            if (rc) return rc;
+            dp.fx = rp.fx; dp.fy = rp.fy; dp.x1 = rp.x1; dp.y1 = rp.y1; dp.x2 = rp.x2; dp.y2 = rp.y2;
+        }
+
+        /* choose the body */
+        const uint64_t out_px = (uint64_t)p.dst_width * p.dst_height;
+        uint32_t cls = CLASS_GENERIC;
+        uint64_t items = 0;
+        if (s.resize_mode == FKB_RESIZE_NONE && s.dst_format != FKB_DST_F32_PLANAR3 && s.src_format != FKB_SRC_NV12) {
+            const bool src_u8 = s.src_format == FKB_SRC_U8X3, dst_u8 = s.dst_format == FKB_DST_U8X3_PACKED;
+            const uintptr_t sa = src_u8 ? 4 : 16, da = dst_u8 ? 4 : 16;
+            const uint8_t* src0 = dp.src + (size_t)p.crop_y * p.src_pitch + (size_t)p.crop_x * spx;
+            const bool dense = (uint64_t)p.src_pitch == (uint64_t)p.dst_width * spx && (uint64_t)p.dst_pitch == (uint64_t)p.dst_width * dpx &&
+                               (uint32_t)p.crop_width == p.src_width;
+            const bool rows_ok = (p.src_pitch % sa) == 0 && (p.dst_pitch % da) == 0;
+            if (aligned(src0, sa) && aligned(dp.dst, da) && (dense || rows_ok) && !(src_u8 == false && dst_u8)) {
+                cls = src_u8 ? (dst_u8 ? CLASS_FLAT_U8_U8 : CLASS_FLAT_U8_F32) : CLASS_FLAT_F32_F32;
+                dp.n_segs = dense ? 1 : p.dst_height;
+                dp.seg_pixels = dense ? (uint32_t)out_px : p.dst_width;
+                if (dense && out_px > 0xFFFFFFFFull) return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: too many pixels", i);
+                items = (uint64_t)dp.n_segs * ((dp.seg_pixels + ITEM_PIXELS_VEC - 1) / ITEM_PIXELS_VEC);
+            }
+        } else if (s.resize_mode != FKB_RESIZE_NONE && (p.dst_width % PX_PER_THREAD) == 0 && aligned(dp.dst, 16) && (p.dst_pitch % 16) == 0 &&
+                   s.pre_kind != PRE_GENERAL) {
+            if (s.src_format == FKB_SRC_U8X3 && s.dst_format == FKB_DST_F32_PLANAR3 && (p.dst_channel_stride % 16) == 0) cls = CLASS_RESIZE_U8_PLANAR;
+            else if (s.src_format == FKB_SRC_U8X3 && s.dst_format == FKB_DST_F32X3_PACKED) cls = CLASS_RESIZE_U8_PACKED;
+            else if (s.src_format == FKB_SRC_NV12 && s.dst_format == FKB_DST_F32X3_PACKED) cls = CLASS_RESIZE_NV12_PACKED;
+            if (cls != CLASS_GENERIC) items = ((out_px / PX_PER_THREAD) + BLOCK_THREADS - 1) / BLOCK_THREADS;
+        }
+        if (cls == CLASS_GENERIC) items = (out_px + ITEM_PIXELS_GENERIC - 1) / ITEM_PIXELS_GENERIC;
+        dp.plane_class = cls;
+        if (i == 0) { common_class = cls; first_items = (uint32_t)items; }
+        else {
+            if (cls != common_class) common_class = CLASS_MIXED;
+            if (items != first_items) uniform = false;
+        }
+        img.item_start[i] = (uint32_t)total;
+        total += items;
+        if (total > 0x7FFFFFFFull) return fail(FKB_ERR_INVALID_ARGUMENT, "plan needs more than 2^31 thread blocks");
+
+        img.output_pixels += out_px;
+        const uint64_t crop_px = (uint64_t)p.crop_width * p.crop_height;
+        img.algorithmic_bytes += (s.src_format == FKB_SRC_NV12 ? crop_px + crop_px / 2 : crop_px * spx) + out_px * (s.dst_format == FKB_DST_F32_PLANAR3 ? 12 : dpx);
+    }
+    img.item_start[d->n_planes] = (uint32_t)total;
+    img.total_items = (uint32_t)total;
+    img.uniform_items = uniform ? first_items : 0;
+    img.launch_class = common_class;
+    return FKB_OK;
+}
+
+/* ------------------------------------------------------------------------------------ */
+/* entry points                                                                         */
+/* ------------------------------------------------------------------------------------ */
+extern "C" FKB_API int fkb_version(void) { return 100; }
+
+extern "C" FKB_API const char* fkb_status_string(int status) {
+    switch (status) {
+        case FKB_OK: return "ok";
+        case FKB_ERR_INVALID_ARGUMENT: return "invalid argument";
+        case FKB_ERR_UNSUPPORTED: return "unsupported";
+        case FKB_ERR_CUDA: return "CUDA error";
+        case FKB_ERR_TOO_LARGE: return "too large";
+        case FKB_ERR_NO_DEVICE: return "no CUDA device";
+        default: return "unknown status";
+    }
+}
+
+extern "C" FKB_API const char* fkb_last_error(void) { return g_last_error; }
+
+static int require_device(int* device) {
+    int n = 0;
+    const cudaError_t e = cudaGetDeviceCount(&n);
+    if (e != cudaSuccess || n == 0) {
+        (void)cudaGetLastError();
+        return fail(FKB_ERR_NO_DEVICE, "no usable CUDA device (%s); this library has no CPU fallback",
+                    e == cudaSuccess ? "device count is 0" : cudaGetErrorString(e));
+    }
+    FKB_CUDA(cudaGetDevice(device));
+    return FKB_OK;
+}
+
+extern "C" FKB_API int fkb_plan_create(const fkb_plan_desc* desc, fkb_plan** out_plan) {
+    if (!out_plan) return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_plan_create: out_plan is NULL");
+    *out_plan = nullptr;
+    HostImage img;
+    int rc = lower(desc, img);
+    if (rc) return rc;
+    int device = -1;
+    rc = require_device(&device);
+    if (rc) return rc;
+
+    fkb_plan* plan = new (std::nothrow) fkb_plan();
+    if (!plan) return fail(FKB_ERR_INVALID_ARGUMENT, "out of host memory");
+    plan->device = device;
+    plan->d_bytes = img.bytes();
+    std::vector<unsigned char> staging(plan->d_bytes);
+    img.serialize(staging.data());
+    cudaError_t e = cudaMalloc(&plan->d_block, plan->d_bytes);
+    if (e == cudaSuccess) e = cudaMemcpy(plan->d_block, staging.data(), plan->d_bytes, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        if (plan->d_block) cudaFree(plan->d_block);
+        delete plan;
+        return fail_cuda(e, "plan upload", __LINE__);
+    }
+    plan->args = img.args_for(static_cast<const unsigned char*>(plan->d_block));
+    plan->launch_class = img.launch_class;
+    plan->resize = std::move(img.resize);
+    plan->info.n_planes = desc->n_planes;
+    plan->info.n_sequences = desc->n_sequences;
+    plan->info.n_launches = 1;
+    plan->info.grid_x = img.total_items;
+    plan->info.block_x = BLOCK_THREADS;
+    plan->info.output_pixels = img.output_pixels;
+    plan->info.algorithmic_bytes = img.algorithmic_bytes;
+    plan->info.device_bytes = plan->d_bytes;
+    *out_plan = plan;
+    return FKB_OK;
+}
+
+extern "C" FKB_API int fkb_plan_launch(const fkb_plan* plan, void* stream) {
+    if (!plan) return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_plan_launch: plan is NULL");
+    const cudaError_t e = launch_plan_kernel(plan->launch_class, plan->args, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail_cuda(e, "kernel launch", __LINE__);
+    return FKB_OK;
+}
+
+extern "C" FKB_API int fkb_plan_get_info(const fkb_plan* plan, fkb_plan_info* out) {
+    if (!plan || !out) return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_plan_get_info: NULL argument");
+    *out = plan->info;
+    return FKB_OK;
+}
+
+extern "C" FKB_API int fkb_plan_get_resize_params(const fkb_plan* plan, int32_t index, fkb_resize_params* out) {
+    if (!plan || !out) return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_plan_get_resize_params: NULL argument");
+    if (index < 0 || (size_t)index >= plan->resize.size())
+        return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_plan_get_resize_params: plane %d outside [0, %zu)", index, plan->resize.size());
+    *out = plan->resize[index];
+    return FKB_OK;
+}
+
+extern "C" FKB_API int fkb_plan_destroy(fkb_plan* plan) {
+    if (!plan) return FKB_OK;
+    cudaError_t e = cudaSuccess;
+    if (plan->d_block) e = cudaFree(plan->d_block);
+    delete plan;
+    if (e != cudaSuccess) return fail_cuda(e, "cudaFree", __LINE__);
+    return FKB_OK;
+}
+
+extern "C" FKB_API int fkb_execute(const fkb_plan_desc* desc, void* stream) {
+    fkb_plan* plan = nullptr;
+    int rc = fkb_plan_create(desc, &plan);
+    if (rc) return rc;
+    rc = fkb_plan_launch(plan, stream);
+    const cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+    fkb_plan_destroy(plan);
+    if (rc) return rc;
+    if (e != cudaSuccess) return fail_cuda(e, "cudaStreamSynchronize", __LINE__);
+    return FKB_OK;
+}
+
+/* ------------------------------------------------------------------------------------ */
+/* host-buffer variant                                                                  */
+/* ------------------------------------------------------------------------------------ */
+/* The reference's counterpart is a Ptr allocated as MemType::DeviceAndPinned with
+ * upload(stream) before and download(stream) after executeOperations
+ * (core/data/ptr_nd.h:252-268,519-530): device mirrors are allocated once and every step
+ * copies in, launches and copies out. */
+struct fkb_host_session {
+    struct Source { const void* host; void* dev; size_t bytes; };
+    struct Download { void* host; const void* dev; size_t pitch, row_bytes, rows; };
+    std::vector<Source> sources;
+    std::vector<void*> dev_outputs;
+    std::vector<Download> downloads;
+    fkb_plan* plan = nullptr;
+    uint64_t h2d_bytes = 0, d2h_bytes = 0;
+};
+
+extern "C" FKB_API int fkb_host_session_destroy(fkb_host_session* s) {
+    if (!s) return FKB_OK;
+    if (s->plan) fkb_plan_destroy(s->plan);
+    for (auto& src : s->sources) if (src.dev) cudaFree(src.dev);
+    for (void* p : s->dev_outputs) if (p) cudaFree(p);
+    delete s;
+    return FKB_OK;
+}
+
+extern "C" FKB_API int fkb_host_session_create(const fkb_plan_desc* desc, fkb_host_session** out) {
+    if (!out) return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_host_session_create: out is NULL");
+    *out = nullptr;
+    {
+        HostImage probe; /* validates shapes before anything is allocated */
+        const int rc = lower(desc, probe);
+        if (rc) return rc;
+    }
+    int device = -1;
+    int rc = require_device(&device);
+    if (rc) return rc;
+    fkb_host_session* s = new (std::nothrow) fkb_host_session();
+    if (!s) return fail(FKB_ERR_INVALID_ARGUMENT, "out of host memory");
+
+    const int n = desc->n_planes;
+    std::vector<fkb_plane> planes(desc->planes, desc->planes + n);
+    std::map<const void*, size_t> src_index;
+
+    /* extent of every plane's output in host memory */
+    std::vector<size_t> out_bytes(n);
+    uintptr_t lo = UINTPTR_MAX, hi = 0;
+    size_t sum = 0;
+    for (int i = 0; i < n; ++i) {
+        const fkb_plane& p = desc->planes[i];
+        const fkb_sequence& q = desc->sequences[p.sequence];
+        const size_t row = (size_t)p.dst_width * dst_pixel_bytes(q.dst_format);
+        out_bytes[i] = (q.dst_format == FKB_DST_F32_PLANAR3 ? 2 * (size_t)p.dst_channel_stride : 0) +
+                       (size_t)p.dst_pitch * (p.dst_height - 1) + row;
+        lo = std::min(lo, reinterpret_cast<uintptr_t>(p.dst));
+        hi = std::max(hi, reinterpret_cast<uintptr_t>(p.dst) + out_bytes[i]);
+        sum += (q.dst_format == FKB_DST_F32_PLANAR3 ? 3 : 1) * row * p.dst_height;
+    }
+    /* Outputs that tile one host range without gaps (a dense tensor) get one device mirror
+       and one copy back; anything else is mirrored and copied plane by plane, row-exact. */
+    const bool one_block = (hi - lo) == sum;
+
+    auto bail = [&](int code) { fkb_host_session_destroy(s); return code; };
+    for (int i = 0; i < n; ++i) {
+        const fkb_plane& p = desc->planes[i];
+        const fkb_sequence& q = desc->sequences[p.sequence];
+        const size_t rows = q.src_format == FKB_SRC_NV12 ? (size_t)p.src_height + (p.src_height + 1) / 2 : p.src_height;
+        const size_t bytes = (size_t)p.src_pitch * rows;
+        auto it = src_index.find(p.src);
+        if (it == src_index.end()) {
+            fkb_host_session::Source sd{p.src, nullptr, bytes};
+            const cudaError_t e = cudaMalloc(&sd.dev, bytes);
+            if (e != cudaSuccess) return bail(fail_cuda(e, "source mirror allocation", __LINE__));
+            s->sources.push_back(sd);
+            s->h2d_bytes += bytes;
+            it = src_index.emplace(p.src, s->sources.size() - 1).first;
+        } else if (s->sources[it->second].bytes != bytes) {
+            return bail(fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: one source pointer is described with two sizes", i));
+        }
+        planes[i].src = s->sources[it->second].dev;
+    }
+    if (one_block) {
+        void* block = nullptr;
+        const cudaError_t e = cudaMalloc(&block, hi - lo);
+        if (e != cudaSuccess) return bail(fail_cuda(e, "output mirror allocation", __LINE__));
+        s->dev_outputs.push_back(block);
+        for (int i = 0; i < n; ++i)
+            planes[i].dst = static_cast<unsigned char*>(block) + (reinterpret_cast<uintptr_t>(desc->planes[i].dst) - lo);
+        s->downloads.push_back({reinterpret_cast<void*>(lo), block, hi - lo, hi - lo, 1});
+        s->d2h_bytes = hi - lo;
+    } else {
+        for (int i = 0; i < n; ++i) {
+            const fkb_plane& p = desc->planes[i];
+            const fkb_sequence& q = desc->sequences[p.sequence];
+            void* mirror = nullptr;
+            const cudaError_t e = cudaMalloc(&mirror, out_bytes[i]);
+            if (e != cudaSuccess) return bail(fail_cuda(e, "output mirror allocation", __LINE__));
+            s->dev_outputs.push_back(mirror);
+            planes[i].dst = mirror;
+            const size_t row = (size_t)p.dst_width * dst_pixel_bytes(q.dst_format);
+            const int channels = q.dst_format == FKB_DST_F32_PLANAR3 ? 3 : 1;
+            for (int c = 0; c < channels; ++c) {
+                const size_t off = (size_t)c * p.dst_channel_stride;
+                s->downloads.push_back({static_cast<unsigned char*>(p.dst) + off, static_cast<unsigned char*>(mirror) + off,
+                                        p.dst_pitch, row, p.dst_height});
+                s->d2h_bytes += row * p.dst_height;
+            }
+        }
+    }
+    fkb_plan_desc dd = *desc;
+    dd.planes = planes.data();
+    rc = fkb_plan_create(&dd, &s->plan);
+    if (rc) return bail(rc);
+    *out = s;
+    return FKB_OK;
+}
+
+extern "C" FKB_API int fkb_host_session_run(fkb_host_session* s, void* stream_) {
+    if (!s) return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_host_session_run: session is NULL");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    for (const auto& src : s->sources) FKB_CUDA(cudaMemcpyAsync(src.dev, src.host, src.bytes, cudaMemcpyHostToDevice, stream));
+    const int rc = fkb_plan_launch(s->plan, stream);
+    if (rc) return rc;
+    for (const auto& d : s->downloads) {
+        if (d.rows == 1) FKB_CUDA(cudaMemcpyAsync(d.host, d.dev, d.row_bytes, cudaMemcpyDeviceToHost, stream));
+        else FKB_CUDA(cudaMemcpy2DAsync(d.host, d.pitch, d.dev, d.pitch, d.row_bytes, d.rows, cudaMemcpyDeviceToHost, stream));
+    }
+    FKB_CUDA(cudaStreamSynchronize(stream));
+    return FKB_OK;
+}
+
+extern "C" FKB_API int fkb_host_session_get_traffic(const fkb_host_session* s, uint64_t* h2d_bytes, uint64_t* d2h_bytes) {
+    if (!s || !h2d_bytes || !d2h_bytes) return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_host_session_get_traffic: NULL argument");
+    *h2d_bytes = s->h2d_bytes;
+    *d2h_bytes = s->d2h_bytes;
+    return FKB_OK;
+}
+
+extern "C" FKB_API int fkb_execute_host(const fkb_plan_desc* desc, void* stream) {
+    fkb_host_session* s = nullptr;
+    int rc = fkb_host_session_create(desc, &s);
+    if (rc) return rc;
+    rc = fkb_host_session_run(s, stream);
+    fkb_host_session_destroy(s);
+    return rc;
+}

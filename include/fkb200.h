@@ -22,6 +22,12 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#if defined(__GNUC__)
+#define FKB_API __attribute__((visibility("default")))
+#else
+#define FKB_API
+#endif
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -154,24 +160,24 @@ typedef struct fkb_plan fkb_plan; /* opaque; owns only its own descriptor memory
 /* ------------------------------------------------------------------------------------ */
 
 /* Library version, major*10000 + minor*100 + patch. */
-int fkb_version(void);
+FKB_API int fkb_version(void);
 
 /* Human-readable name of a status code. Never NULL. */
-const char* fkb_status_string(int status);
+FKB_API const char* fkb_status_string(int status);
 
 /* Message of the last failure on the calling thread (empty string if none). */
-const char* fkb_last_error(void);
+FKB_API const char* fkb_last_error(void);
 
 /* Restates Resize::build's host arithmetic (resize.h:105-166) and compute_target_size
  * (resize.h:196-221): float scale, cxp::round (constexpr_cmath.h:119-130), double
  * reciprocal narrowed once.  mode is FKB_RESIZE_IGNORE_AR or FKB_RESIZE_PRESERVE_AR. */
-int fkb_derive_resize(int32_t src_width, int32_t src_height, int32_t dst_width, int32_t dst_height,
+FKB_API int fkb_derive_resize(int32_t src_width, int32_t src_height, int32_t dst_width, int32_t dst_height,
                       int32_t mode, fkb_resize_params* out);
 
 /* Restates the reference's block-shape search getDefaultBlockSize (executors.h:176-242).
  * The kernels here do not use it; it is kept so that a front end can report the grid the
  * reference would have launched. */
-int fkb_reference_block_size(uint32_t active_x, uint32_t active_y, uint32_t* block_x, uint32_t* block_y);
+FKB_API int fkb_reference_block_size(uint32_t active_x, uint32_t active_y, uint32_t* block_x, uint32_t* block_y);
 
 /* Validates a plan description, derives the per-plane resize parameters and copies the
  * descriptors to the current device.  Replaces the work the reference does at compile
@@ -179,32 +185,43 @@ int fkb_reference_block_size(uint32_t active_x, uint32_t active_y, uint32_t* blo
  * BatchRead::build (batch_operations.h:178-208).  The description and everything it
  * points to may be released as soon as the call returns; image memory must stay valid
  * until the launches that use it have finished. */
-int fkb_plan_create(const fkb_plan_desc* desc, fkb_plan** out_plan);
+FKB_API int fkb_plan_create(const fkb_plan_desc* desc, fkb_plan** out_plan);
 
 /* Replaces launchTransformDPP_Kernel<<<grid, block, 0, stream>>> (executors.h:267,270,284)
  * and, for plans with more than one sequence, launchDivergentBatchTransformDPP_Kernel
  * (executor_kernels.h:20-23).  `stream` is a cudaStream_t (NULL = default stream).
  * Asynchronous; returns the launch status only, like the reference's cudaGetLastError check. */
-int fkb_plan_launch(const fkb_plan* plan, void* stream);
+FKB_API int fkb_plan_launch(const fkb_plan* plan, void* stream);
 
-int fkb_plan_get_info(const fkb_plan* plan, fkb_plan_info* out_info);
+FKB_API int fkb_plan_get_info(const fkb_plan* plan, fkb_plan_info* out_info);
 
 /* Copies the derived resize parameters of plane `index` out of a plan (for parity checks). */
-int fkb_plan_get_resize_params(const fkb_plan* plan, int32_t index, fkb_resize_params* out);
+FKB_API int fkb_plan_get_resize_params(const fkb_plan* plan, int32_t index, fkb_resize_params* out);
 
 /* Frees the plan's descriptor memory.  Call after the launches that use it have finished. */
-int fkb_plan_destroy(fkb_plan* plan);
+FKB_API int fkb_plan_destroy(fkb_plan* plan);
 
 /* One-shot equivalent of fk::executeOperations(stream, sender, receiver) followed by
  * stream.sync(): create, launch, synchronise the stream, destroy. */
-int fkb_execute(const fkb_plan_desc* desc, void* stream);
+FKB_API int fkb_execute(const fkb_plan_desc* desc, void* stream);
 
-/* Same as fkb_execute for callers whose images live in HOST memory: every pointer in
- * desc->planes (src and dst) is a host pointer.  Distinct source images are copied to the
- * device once each, the plan runs, every plane's output is copied back, and the call
- * returns after the stream has been synchronised.  Rows of `src_pitch` / `dst_pitch` bytes
- * are assumed; outputs of planes that share one allocation must not overlap. */
-int fkb_execute_host(const fkb_plan_desc* desc, void* stream);
+/* Host-buffer sessions: for callers whose images live in HOST memory (preferably pinned).
+ * Every pointer in desc->planes (src and dst) is a host pointer.  The reference's
+ * counterpart is a Ptr of MemType::DeviceAndPinned with upload(stream) before and
+ * download(stream) after executeOperations (core/data/ptr_nd.h:252-268,519-530).
+ * create: allocates one device mirror per distinct source image and for the outputs.
+ * run:    copies every source in, launches the plan, copies every output back and
+ *         synchronises the stream; rows of src_pitch / dst_pitch bytes are assumed and
+ *         outputs that tile one host range without gaps come back as a single copy.
+ * The description may be released after create; the host images must stay valid. */
+typedef struct fkb_host_session fkb_host_session;
+FKB_API int fkb_host_session_create(const fkb_plan_desc* desc, fkb_host_session** out_session);
+FKB_API int fkb_host_session_run(fkb_host_session* session, void* stream);
+FKB_API int fkb_host_session_get_traffic(const fkb_host_session* session, uint64_t* h2d_bytes, uint64_t* d2h_bytes);
+FKB_API int fkb_host_session_destroy(fkb_host_session* session);
+
+/* One-shot fkb_host_session_create + run + destroy. */
+FKB_API int fkb_execute_host(const fkb_plan_desc* desc, void* stream);
 
 #ifdef __cplusplus
 } /* extern "C" */

@@ -1,0 +1,178 @@
+"""Seeded parity cases shared by the CPU and GPU tests.
+
+A case holds named host arrays (sources and zero-initialised outputs) and a function that
+lowers its sender chain to a plan given a `ptr(name) -> int` lookup, so that the same chain
+can be run by the checker on host pointers and by the CUDA path on device pointers.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable
+
+import numpy as np
+
+from fusedkernellibrary_b200 import abi, chains
+from fusedkernellibrary_b200.abi import op
+
+
+@dataclass
+class Case:
+    name: str
+    sources: dict
+    outputs: dict
+    build: Callable  # build(ptr) -> abi.HostPlan
+    float_outputs: bool = True
+    meta: dict = field(default_factory=dict)
+
+
+def _u8(rng, *shape):
+    return rng.integers(0, 256, shape, dtype=np.uint8)
+
+
+def padded_u8_image(rng, h, w, pitch):
+    """(h, w, 3) view with a row pitch of `pitch` bytes; the padding holds 0xEE."""
+    buf = np.full((h, pitch), 0xEE, np.uint8)
+    img = buf[:, :w * 3].reshape(h, w, 3)
+    img[...] = _u8(rng, h, w, 3)
+    return buf, img
+
+
+def elementwise_case(name, seed, w, h, ops, src_fmt=abi.SRC_U8X3, dst_fmt=abi.DST_F32X3_PACKED, src_pitch=None,
+                     dst_pitch=None, crop=None):
+    rng = np.random.default_rng(seed)
+    spx = 3 if src_fmt == abi.SRC_U8X3 else 12
+    dpx = 3 if dst_fmt == abi.DST_U8X3_PACKED else 12
+    sp = src_pitch or w * spx
+    ow, oh = (crop[2], crop[3]) if crop else (w, h)
+    dp = dst_pitch or ow * dpx
+    src = np.full((h, sp), 0xEE, np.uint8)
+    if src_fmt == abi.SRC_U8X3:
+        src[:, :w * 3] = _u8(rng, h, w * 3)
+    else:
+        src[:, :w * 12] = rng.random((h, w * 3), dtype=np.float32).view(np.uint8)
+    out = np.zeros((oh, dp), np.uint8)
+
+    def build(ptr):
+        return chains.elementwise(ops, src=ptr("src"), dst=ptr("out"), width=w, height=h, src_format=src_fmt,
+                                  dst_format=dst_fmt, src_pitch=sp, dst_pitch=dp, crop=crop)
+
+    return Case(name, {"src": src}, {"out": out}, build, float_outputs=dst_fmt != abi.DST_U8X3_PACKED,
+                meta=dict(w=ow, h=oh, dpx=dpx, dst_pitch=dp))
+
+
+def crop_resize_case(name, seed, n_frames, fw, fh, n_planes, dw, dh, planar, post_ops, rects=None, lo=4, hi=200,
+                     mode=abi.RESIZE_PRESERVE_AR, background=(0.0, 0.0, 0.0), src_pitch=None):
+    rng = np.random.default_rng(seed)
+    sp = src_pitch or fw * 3
+    sources = {}
+    for i in range(n_frames):
+        buf = np.full((fh, sp), 0xEE, np.uint8)
+        buf[:, :fw * 3] = _u8(rng, fh, fw * 3)
+        sources[f"frame{i}"] = buf
+    if rects is None:
+        rects = chains.random_rects(rng, n_planes, fw, fh, lo=lo, hi=hi)
+    rects = np.asarray(rects, np.int32)
+    frame_index = [i % n_frames for i in range(n_planes)]
+    out = np.zeros((n_planes, 3, dh, dw) if planar else (n_planes, dh, dw, 3), np.float32)
+
+    def build(ptr):
+        return chains.crop_resize_batch(frame_ptrs=[ptr(f"frame{i}") for i in range(n_frames)], frame_index=frame_index,
+                                        rects=rects, src_width=fw, src_height=fh, src_pitch=sp, dst=ptr("out"),
+                                        dst_width=dw, dst_height=dh, post_ops=post_ops, planar=planar, mode=mode,
+                                        background=background)
+
+    return Case(name, sources, {"out": out}, build, meta=dict(rects=rects, frame_index=frame_index))
+
+
+def nv12_case(name, seed, n_frames, w, h, dw, dh, pitch=None):
+    rng = np.random.default_rng(seed)
+    pitch = pitch or w
+    sources = {}
+    for i in range(n_frames):
+        buf = np.full((h + h // 2, pitch), 0xEE, np.uint8)
+        buf[:, :w] = _u8(rng, h + h // 2, w)
+        sources[f"frame{i}"] = buf
+    out = np.zeros((n_frames, dh, dw, 3), np.float32)
+
+    def build(ptr):
+        return chains.nv12_resize_batch(frame_ptrs=[ptr(f"frame{i}") for i in range(n_frames)], width=w, height=h,
+                                        pitch=pitch, dst=ptr("out"), dst_width=dw, dst_height=dh)
+
+    return Case(name, sources, {"out": out}, build)
+
+
+def divergent_case(name, seed, w, h, rw, rh, per_group):
+    rng = np.random.default_rng(seed)
+    sources = {f"img{i}": _u8(rng, h, w * 3) for i in range(4 * per_group)}
+    outputs = {
+        "g0": np.zeros((per_group, h, w, 3), np.float32),
+        "g1": np.zeros((per_group, h, w, 3), np.float32),
+        "g2": np.zeros((per_group, h, w, 3), np.uint8),
+        "g3": np.zeros((per_group, rh, rw, 3), np.float32),
+    }
+
+    def build(ptr):
+        return chains.divergent_four_groups(src_ptrs=[ptr(f"img{i}") for i in range(4 * per_group)], width=w, height=h,
+                                            dst_ptrs=[ptr(f"g{g}") for g in range(4)], resize_to=(rw, rh),
+                                            per_group=per_group)
+
+    return Case(name, sources, outputs, build)
+
+
+def small_cases():
+    """Cases the checker finishes in well under a second each."""
+    c1 = chains.cast_mul_sub_div_ops()
+    g3 = [op(abi.OP_SWAP_RB), op(abi.OP_CAST_F32), op(abi.OP_MUL, 1.4), op(abi.OP_SATURATE_CAST_U8)]
+    cases = [
+        elementwise_case("c1_dense_aligned", 11, 64, 33, c1),
+        elementwise_case("c1_odd_width", 12, 53, 37, c1),                      # rows not 4-byte multiples: generic
+        elementwise_case("c1_1x1", 13, 1, 1, c1),
+        elementwise_case("c1_1xN", 14, 1, 19, c1),
+        elementwise_case("c1_Nx1", 15, 1023, 1, c1),
+        elementwise_case("c1_pitched", 16, 100, 21, c1, src_pitch=304, dst_pitch=1216),  # row segments + tails
+        elementwise_case("c1_pitched_unaligned", 17, 100, 21, c1, src_pitch=301),
+        elementwise_case("c1_crop", 18, 96, 40, c1, crop=(8, 3, 64, 20)),
+        elementwise_case("c1_crop_unaligned", 19, 96, 40, c1, crop=(7, 3, 61, 20)),
+        elementwise_case("c1_tail", 20, 1027, 3, c1),                          # dense, pixel count not multiple of 4
+        elementwise_case("c5a_n1", 21, 40, 30, chains.addmul_ops(1), src_fmt=abi.SRC_F32X3),
+        elementwise_case("c5a_n16", 22, 40, 30, chains.addmul_ops(16), src_fmt=abi.SRC_F32X3),
+        elementwise_case("c5a_n64", 23, 40, 30, chains.addmul_ops(64), src_fmt=abi.SRC_F32X3),
+        elementwise_case("c5a_n256", 24, 41, 31, chains.addmul_ops(256), src_fmt=abi.SRC_F32X3),
+        elementwise_case("g3_saturate_u8", 25, 64, 32, g3, dst_fmt=abi.DST_U8X3_PACKED),
+        elementwise_case("g3_saturate_u8_odd", 26, 53, 37, g3, dst_fmt=abi.DST_U8X3_PACKED),
+        elementwise_case("copy_u8", 27, 300, 20, [], dst_fmt=abi.DST_U8X3_PACKED),
+        elementwise_case("copy_f32", 28, 32, 20, [], src_fmt=abi.SRC_F32X3),
+        crop_resize_case("c2_readme", 31, 1, 384, 216, 5, 60, 60, False, chains.readme_ops(), rects=chains.README_RECTS),
+        crop_resize_case("c2_readme_ignore_ar", 32, 1, 384, 216, 5, 60, 60, False, chains.readme_ops(),
+                         rects=chains.README_RECTS, mode=abi.RESIZE_IGNORE_AR),
+        crop_resize_case("c2_background", 33, 2, 200, 120, 7, 40, 28, False, chains.readme_ops(),
+                         background=(10.0, 20.0, 30.0)),
+        crop_resize_case("c3_small", 34, 3, 480, 270, 37, 48, 32, True, chains.normalize_ops()),
+        crop_resize_case("c3_odd_dst", 35, 2, 320, 200, 9, 45, 31, True, chains.normalize_ops()),  # generic path
+        crop_resize_case("c3_edges", 36, 1, 64, 48, 6, 32, 32, True, chains.normalize_ops(),
+                         rects=[(0, 0, 64, 48), (0, 0, 1, 1), (63, 47, 1, 1), (0, 47, 64, 1), (63, 0, 1, 48),
+                                (10, 10, 2, 2)]),
+        crop_resize_case("c3_upscale", 37, 1, 64, 48, 4, 224, 224, True, chains.normalize_ops(), lo=4, hi=24),
+        crop_resize_case("c3_pitched_src", 38, 2, 100, 60, 5, 48, 32, True, chains.normalize_ops(), src_pitch=333),
+        nv12_case("c4_exact3", 41, 3, 96, 54, 32, 18),
+        nv12_case("c4_fractional", 42, 2, 96, 54, 40, 22),
+        nv12_case("c4_pitched", 43, 2, 98, 54, 36, 20, pitch=128),
+        nv12_case("c4_odd_dst", 44, 2, 96, 54, 37, 21),
+        divergent_case("c5b_small", 51, 64, 36, 32, 18, 3),
+        divergent_case("c5b_odd", 52, 50, 30, 25, 15, 2),
+    ]
+    return cases
+
+
+def run_on_host(case: Case, port, host_branch=False):
+    """Runs the checker in place on the case's host arrays; returns the outputs dict."""
+    arrays = {**case.sources, **case.outputs}
+    for a in case.outputs.values():
+        a[...] = 0
+    plan = case.build(lambda name: arrays[name].ctypes.data)
+    port.run(plan, host_branch=host_branch)
+    return case.outputs
+
+
+def bits(a: np.ndarray) -> np.ndarray:
+    return a.view(np.uint32) if a.dtype == np.float32 else a

@@ -1,0 +1,95 @@
+"""Generates the golden vectors under tests/golden/ from the reference's own headers.
+
+Run where the reference tree is present, after `make -C oracle ref`:
+
+    python tests/golden/make_golden.py
+
+Every fixture stores the seeded inputs and the output of oracle/_ref/libfklref_device_branch.so
+(the reference's unmodified source with its device branch selected on the host, see
+oracle/ref/device_branch_prelude.h).  For chains that contain Resize the output of the literal
+CPU build is stored next to it under `literal_*`, to document where the two differ.
+The fixtures are what travels: tests never read the reference tree.
+"""
+import sys
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parents[2]
+sys.path.insert(0, str(ROOT))
+
+from fusedkernellibrary_b200 import chains  # noqa: E402
+from oracle import reference as ref  # noqa: E402
+
+OUT = Path(__file__).resolve().parent
+
+
+def u8(rng, *shape):
+    return rng.integers(0, 256, shape, dtype=np.uint8)
+
+
+def main():
+    rng = np.random.default_rng(20240607)
+
+    # --- element-wise chains on a 53x37 uchar3 image (configs 1, 5B groups 1-3) -----------
+    img = u8(rng, 37, 53, 3)
+    np.savez_compressed(
+        OUT / "elementwise_u8.npz", src=img,
+        cast_mul_sub_div=ref.cast_mul_sub_div(img, 1.4, 0.5, 255.0),
+        cast_mul_sub=ref.cast_mul_sub(img, 1.4, 0.5),
+        cast_add_div=ref.cast_add_div(img, 0.5, 255.0),
+        bgr_cast_mul_saturate=ref.bgr_cast_mul_saturate(img, 1.4),
+        cast_resize_30x20=ref.cast_resize(img, 30, 20),
+        literal_cast_resize_30x20=ref.cast_resize(img, 30, 20, flavour="literal"),
+    )
+
+    # --- long Add/Mul chains on a 31x20 float3 image (config 5A) ---------------------------
+    imgf = rng.random((20, 31, 3), dtype=np.float32)
+    np.savez_compressed(OUT / "addmul_chain.npz", src=imgf,
+                        **{f"n{n}": ref.addmul_chain(imgf, n, 0.001, 1.0001) for n in (1, 2, 3, 16, 64, 256)})
+
+    # --- README chain (config 2) on a 384x216 frame -----------------------------------------
+    frame = u8(rng, 216, 384, 3)
+    rects = chains.README_RECTS
+    np.savez_compressed(
+        OUT / "readme_crop_resize.npz", frame=frame, rects=rects,
+        out=ref.crop_resize_readme([frame], [0] * 5, rects, 60, 60, (0, 0, 0), 1.4, 0.5, 255.0),
+        out_ignore_ar=ref.crop_resize_readme([frame], [0] * 5, rects, 60, 60, (0, 0, 0), 1.4, 0.5, 255.0,
+                                             preserve_ar=False),
+        literal_out=ref.crop_resize_readme([frame], [0] * 5, rects, 60, 60, (0, 0, 0), 1.4, 0.5, 255.0,
+                                           flavour="literal"),
+    )
+
+    # --- batched crop -> resize -> normalise -> planar (config 3), 3 frames, 37 crops -------
+    frames = [u8(rng, 135, 240, 3) for _ in range(3)]
+    n = 37
+    rects3 = chains.random_rects(rng, n, 240, 135, lo=4, hi=120)
+    fi = [i % 3 for i in range(n)]
+    np.savez_compressed(
+        OUT / "batched_crop_resize_norm.npz", frames=np.stack(frames), rects=rects3, frame_index=np.array(fi),
+        out=ref.crop_resize_norm_planar(frames, fi, rects3, 48, 32, (0, 0, 0), 255.0, chains.IMAGENET_MEAN,
+                                        chains.IMAGENET_STD),
+    )
+
+    # --- NV12 -> RGB -> resize (config 4), 3 frames of 96x54 --------------------------------
+    nv = [u8(rng, 81, 96) for _ in range(3)]
+    np.savez_compressed(OUT / "nv12_resize.npz", frames=np.stack(nv),
+                        out_32x18=ref.nv12_resize(nv, 96, 54, 32, 18, 255.0),
+                        out_40x22=ref.nv12_resize(nv, 96, 54, 40, 22, 255.0))
+
+    # --- host-derived resize parameters (Resize::build) --------------------------------------
+    q = np.zeros((4000, 4), np.int32)
+    q[:, :] = rng.integers(1, 700, (4000, 4))
+    q[:100, 2:] = 224
+    q[100:200, 2:] = 60
+    res = np.zeros((4000, 2, 6), np.int64)
+    for i, (sw, sh, dw, dh) in enumerate(q):
+        for ar in (0, 1):
+            (fx, fy), roi = ref.resize_params(int(sw), int(sh), int(dw), int(dh), ar)
+            res[i, ar] = (np.float32(fx).view(np.uint32), np.float32(fy).view(np.uint32), *roi)
+    np.savez_compressed(OUT / "resize_params.npz", query=q, result=res)
+    print("golden vectors written to", OUT)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,147 @@
+"""Host-side checks of the C-ABI library that need no GPU: it loads, exports every symbol the
+header declares, derives the same host parameters as the checker and the golden table, rejects
+malformed plans with a status code, and refuses to run without a device (no fallback)."""
+import ctypes as C
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from fusedkernellibrary_b200 import abi, chains
+from fusedkernellibrary_b200.abi import op
+
+ROOT = Path(__file__).resolve().parent.parent
+GOLD = Path(__file__).resolve().parent / "golden"
+
+
+def test_every_declared_symbol_is_exported(fkb_lib):
+    header = (ROOT / "include" / "fkb200.h").read_text()
+    declared = sorted(set(re.findall(r"FKB_API\s+[\w\s\*]+?\b(fkb_\w+)\s*\(", header)))
+    assert len(declared) >= 16
+    for name in declared:
+        assert hasattr(fkb_lib, name), f"{name} declared in fkb200.h but not exported"
+    assert sorted(abi.EXPORTS) == declared
+    assert fkb_lib.fkb_version() >= 100
+
+
+def test_struct_sizes_match_header():
+    # sizes implied by the C declarations on LP64
+    assert C.sizeof(abi.Op) == 16
+    assert C.sizeof(abi.Sequence) == 40
+    assert C.sizeof(abi.Plane) == 72
+    assert C.sizeof(abi.PlanDesc) == 32
+    assert C.sizeof(abi.ResizeParams) == 32
+    assert C.sizeof(abi.PlanInfo) == 48
+
+
+def test_derive_resize_matches_golden_table(fkb_lib):
+    g = np.load(GOLD / "resize_params.npz")
+    rp = abi.ResizeParams()
+    for (sw, sh, dw, dh), res in zip(g["query"], g["result"]):
+        for ar, mode in ((0, abi.RESIZE_IGNORE_AR), (1, abi.RESIZE_PRESERVE_AR)):
+            assert fkb_lib.fkb_derive_resize(int(sw), int(sh), int(dw), int(dh), mode, C.byref(rp)) == abi.OK
+            got = [int(np.float32(rp.fx).view(np.uint32)), int(np.float32(rp.fy).view(np.uint32))]
+            assert got == list(res[ar][:2])
+            if ar:
+                assert [rp.x1, rp.y1, rp.x2, rp.y2] == list(res[ar][2:])
+
+
+def test_derive_resize_matches_checker_on_many_pairs(fkb_lib, oracle_port):
+    rng = np.random.default_rng(123)
+    rp = abi.ResizeParams()
+    q = rng.integers(1, 4000, (100000, 4))
+    for sw, sh, dw, dh in q:
+        fkb_lib.fkb_derive_resize(int(sw), int(sh), int(dw), int(dh), abi.RESIZE_PRESERVE_AR, C.byref(rp))
+        o = oracle_port.derive_resize(int(sw), int(sh), int(dw), int(dh), abi.RESIZE_PRESERVE_AR)
+        assert (rp.fx, rp.fy, rp.x1, rp.y1, rp.x2, rp.y2, rp.target_width, rp.target_height) == \
+               (o.fx, o.fy, o.x1, o.y1, o.x2, o.y2, o.target_width, o.target_height)
+
+
+def test_reference_block_size(fkb_lib, oracle_port):
+    """Block shapes the reference picks for the benchmark grids (executors.h:230-242)."""
+    want = {(1920, 1080): (32, 8), (224, 224): (32, 8), (1280, 720): (32, 8), (3840, 2160): (32, 8),
+            (60, 60): (32, 6), (960, 540): (32, 6)}
+    bx, by = C.c_uint32(), C.c_uint32()
+    for (w, h), blk in want.items():
+        assert fkb_lib.fkb_reference_block_size(w, h, C.byref(bx), C.byref(by)) == abi.OK
+        assert (bx.value, by.value) == blk
+        assert oracle_port.block_size(w, h) == blk
+    rng = np.random.default_rng(7)
+    for w, h in rng.integers(1, 5000, (5000, 2)):
+        fkb_lib.fkb_reference_block_size(int(w), int(h), C.byref(bx), C.byref(by))
+        assert (bx.value, by.value) == oracle_port.block_size(int(w), int(h))
+
+
+def _plan(**over):
+    src = np.zeros((16, 16, 3), np.uint8)
+    out = np.zeros((8, 8, 3), np.float32)
+    kw = dict(src=src.ctypes.data, src_width=16, src_height=16, src_pitch=48, dst=out.ctypes.data, dst_width=8,
+              dst_height=8, dst_pitch=96, crop=(0, 0, 16, 16))
+    seq = dict(src_format=abi.SRC_U8X3, dst_format=abi.DST_F32X3_PACKED, resize_mode=abi.RESIZE_IGNORE_AR,
+               ops=[op(abi.OP_MUL, 2.0)], n_pre_ops=0)
+    for k, v in over.items():
+        (seq if k in seq else kw)[k] = v
+    plan = abi.HostPlan()
+    plan.add_sequence(seq["src_format"], seq["dst_format"], seq["resize_mode"], seq["ops"], n_pre_ops=seq["n_pre_ops"])
+    plan.add_plane(**kw)
+    plan._keep = (src, out)
+    return plan
+
+
+BAD_PLANS = {
+    "null source": dict(src=None),
+    "null destination": dict(dst=None),
+    "pitch shorter than a row": dict(src_pitch=47),
+    "rect outside image": dict(crop=(10, 10, 8, 8)),
+    "negative rect origin": dict(crop=(-1, 0, 8, 8)),
+    "empty rect": dict(crop=(0, 0, 0, 8)),
+    "zero-sized output": dict(dst_width=0),
+    "misaligned float output": dict(dst_pitch=98),
+    "arithmetic on uchar without cast": dict(resize_mode=abi.RESIZE_NONE, dst_width=16, dst_height=16, dst_pitch=192),
+    "float chain into uchar receiver": dict(dst_format=abi.DST_U8X3_PACKED, dst_pitch=24),
+    "unknown opcode": dict(ops=[op(99)]),
+    "yuv conversion on rgb source": dict(ops=[op(abi.OP_YUV_TO_RGB_BT709_FULL)], n_pre_ops=1),
+    "size change without resize": dict(resize_mode=abi.RESIZE_NONE, ops=[op(abi.OP_CAST_F32)]),
+}
+
+
+@pytest.mark.parametrize("why", sorted(BAD_PLANS))
+def test_malformed_plans_are_rejected(fkb_lib, why):
+    plan = _plan(**BAD_PLANS[why])
+    handle = C.c_void_p()
+    d = plan.desc()
+    rc = fkb_lib.fkb_plan_create(C.byref(d), C.byref(handle))
+    assert rc == abi.ERR_INVALID_ARGUMENT, why
+    assert not handle.value
+    assert fkb_lib.fkb_last_error()
+
+
+def test_empty_batch_is_rejected(fkb_lib):
+    plan = abi.HostPlan()
+    plan.add_sequence(abi.SRC_U8X3, abi.DST_F32X3_PACKED, abi.RESIZE_NONE, [op(abi.OP_CAST_F32)])
+    handle = C.c_void_p()
+    d = plan.desc()
+    assert fkb_lib.fkb_plan_create(C.byref(d), C.byref(handle)) == abi.ERR_INVALID_ARGUMENT
+    assert fkb_lib.fkb_plan_create(None, C.byref(handle)) == abi.ERR_INVALID_ARGUMENT
+
+
+def test_no_device_means_error_not_fallback(fkb_lib):
+    """Without a GPU a valid plan must fail with FKB_ERR_NO_DEVICE; nothing computes on the CPU."""
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    plan = _plan()
+    handle = C.c_void_p()
+    d = plan.desc()
+    assert fkb_lib.fkb_plan_create(C.byref(d), C.byref(handle)) == abi.ERR_NO_DEVICE
+    assert b"no CPU fallback" in fkb_lib.fkb_last_error()
+    with pytest.raises(abi.FkbError):
+        abi.execute(plan)
+    with pytest.raises(abi.FkbError):
+        abi.execute_host(plan)
+
+
+def test_missing_library_is_an_error(tmp_path):
+    with pytest.raises(FileNotFoundError):
+        abi.load_library(tmp_path / "libfkb200.so")

@@ -1,0 +1,161 @@
+"""Pins the plain-C checker against golden vectors produced by the reference's own headers
+(tests/golden/make_golden.py) and, where oracle/_ref is present, against that build directly."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from fusedkernellibrary_b200 import abi, chains
+from fusedkernellibrary_b200.abi import op
+from oracle import reference as ref
+from tests import cases as tc
+
+GOLD = Path(__file__).resolve().parent / "golden"
+
+
+def _same(a, b):
+    return np.array_equal(tc.bits(np.ascontiguousarray(a)), tc.bits(np.ascontiguousarray(b)))
+
+
+def _elementwise(port, src, ops, dst_fmt=abi.DST_F32X3_PACKED, src_fmt=abi.SRC_U8X3):
+    h, w, _ = src.shape
+    src = np.ascontiguousarray(src)
+    out = np.zeros((h, w, 3), np.uint8 if dst_fmt == abi.DST_U8X3_PACKED else np.float32)
+    plan = chains.elementwise(ops, src=src.ctypes.data, dst=out.ctypes.data, width=w, height=h, src_format=src_fmt,
+                              dst_format=dst_fmt)
+    port.run(plan)
+    return out
+
+
+def test_elementwise_chains(oracle_port):
+    g = np.load(GOLD / "elementwise_u8.npz")
+    src = g["src"]
+    assert _same(_elementwise(oracle_port, src, chains.cast_mul_sub_div_ops()), g["cast_mul_sub_div"])
+    assert _same(_elementwise(oracle_port, src, [op(abi.OP_CAST_F32), op(abi.OP_MUL, 1.4), op(abi.OP_SUB, 0.5)]),
+                 g["cast_mul_sub"])
+    assert _same(_elementwise(oracle_port, src, [op(abi.OP_CAST_F32), op(abi.OP_ADD, 0.5), op(abi.OP_DIV, 255.0)]),
+                 g["cast_add_div"])
+    assert _same(_elementwise(oracle_port, src, [op(abi.OP_SWAP_RB), op(abi.OP_CAST_F32), op(abi.OP_MUL, 1.4),
+                                                 op(abi.OP_SATURATE_CAST_U8)], dst_fmt=abi.DST_U8X3_PACKED),
+                 g["bgr_cast_mul_saturate"])
+    # known answer stated by hand: (56*1.4 - 0.5)/255 in binary32
+    v = np.float32(np.float32(np.float32(56) * np.float32(1.4)) - np.float32(0.5)) / np.float32(255)
+    one = np.full((1, 1, 3), 56, np.uint8)
+    assert _elementwise(oracle_port, one, chains.cast_mul_sub_div_ops())[0, 0, 0] == v
+
+
+def _cast_resize(port, src, dw, dh, host_branch=False):
+    h, w, _ = src.shape
+    src = np.ascontiguousarray(src)
+    out = np.zeros((dh, dw, 3), np.float32)
+    plan = abi.HostPlan()
+    s = plan.add_sequence(abi.SRC_U8X3, abi.DST_F32X3_PACKED, abi.RESIZE_IGNORE_AR, [op(abi.OP_CAST_F32)], n_pre_ops=1)
+    plan.add_plane(src=src.ctypes.data, src_width=w, src_height=h, src_pitch=w * 3, dst=out.ctypes.data, dst_width=dw,
+                   dst_height=dh, dst_pitch=dw * 12, sequence=s)
+    port.run(plan, host_branch=host_branch)
+    return out
+
+
+def test_cast_then_resize(oracle_port):
+    g = np.load(GOLD / "elementwise_u8.npz")
+    assert _same(_cast_resize(oracle_port, g["src"], 30, 20), g["cast_resize_30x20"])
+
+
+def test_addmul_chains(oracle_port):
+    g = np.load(GOLD / "addmul_chain.npz")
+    for n in (1, 2, 3, 16, 64, 256):
+        got = _elementwise(oracle_port, g["src"], chains.addmul_ops(n), src_fmt=abi.SRC_F32X3)
+        assert _same(got, g[f"n{n}"]), n
+
+
+def _readme(port, frame, rects, mode=abi.RESIZE_PRESERVE_AR, host_branch=False):
+    frame = np.ascontiguousarray(frame)
+    h, w, _ = frame.shape
+    out = np.zeros((len(rects), 60, 60, 3), np.float32)
+    plan = chains.crop_resize_batch(frame_ptrs=[frame.ctypes.data], frame_index=[0] * len(rects), rects=rects,
+                                    src_width=w, src_height=h, src_pitch=w * 3, dst=out.ctypes.data, dst_width=60,
+                                    dst_height=60, post_ops=chains.readme_ops(), planar=False, mode=mode)
+    port.run(plan, host_branch=host_branch)
+    return out
+
+
+def test_readme_chain(oracle_port):
+    g = np.load(GOLD / "readme_crop_resize.npz")
+    assert _same(_readme(oracle_port, g["frame"], g["rects"]), g["out"])
+    assert _same(_readme(oracle_port, g["frame"], g["rects"], mode=abi.RESIZE_IGNORE_AR), g["out_ignore_ar"])
+
+
+def test_literal_host_branch_is_reproduced_and_differs(oracle_port):
+    """The reference's host branch takes the row tap from the column coordinate
+    (interpolation.h:70).  The checker can reproduce it, and it is NOT the parity target."""
+    g = np.load(GOLD / "readme_crop_resize.npz")
+    lit = _readme(oracle_port, g["frame"], g["rects"], host_branch=True)
+    assert _same(lit, g["literal_out"])
+    assert np.abs(g["literal_out"] - g["out"]).max() > 1e-2
+
+
+def test_batched_crop_resize_norm(oracle_port):
+    g = np.load(GOLD / "batched_crop_resize_norm.npz")
+    frames = [np.ascontiguousarray(f) for f in g["frames"]]
+    n = len(g["rects"])
+    out = np.zeros((n, 3, 32, 48), np.float32)
+    plan = chains.crop_resize_batch(frame_ptrs=[f.ctypes.data for f in frames], frame_index=list(g["frame_index"]),
+                                    rects=g["rects"], src_width=240, src_height=135, src_pitch=720,
+                                    dst=out.ctypes.data, dst_width=48, dst_height=32,
+                                    post_ops=chains.normalize_ops(), planar=True)
+    oracle_port.run(plan)
+    assert _same(out, g["out"])
+
+
+def test_nv12_resize(oracle_port):
+    g = np.load(GOLD / "nv12_resize.npz")
+    frames = [np.ascontiguousarray(f) for f in g["frames"]]
+    for (dw, dh) in ((32, 18), (40, 22)):
+        out = np.zeros((len(frames), dh, dw, 3), np.float32)
+        plan = chains.nv12_resize_batch(frame_ptrs=[f.ctypes.data for f in frames], width=96, height=54, pitch=96,
+                                        dst=out.ctypes.data, dst_width=dw, dst_height=dh)
+        oracle_port.run(plan)
+        assert _same(out, g[f"out_{dw}x{dh}"])
+    # no saturation on the float path: values leave [0, 1] (color_conversion.h:276-281)
+    assert g["out_32x18"].min() < 0 and g["out_32x18"].max() > 1
+
+
+def test_resize_params_table(oracle_port):
+    g = np.load(GOLD / "resize_params.npz")
+    for (sw, sh, dw, dh), res in zip(g["query"], g["result"]):
+        for ar, mode in ((0, abi.RESIZE_IGNORE_AR), (1, abi.RESIZE_PRESERVE_AR)):
+            rp = oracle_port.derive_resize(int(sw), int(sh), int(dw), int(dh), mode)
+            got = [int(np.float32(rp.fx).view(np.uint32)), int(np.float32(rp.fy).view(np.uint32))]
+            assert got == list(res[ar][:2])
+            if ar:
+                assert [rp.x1, rp.y1, rp.x2, rp.y2] == list(res[ar][2:])
+
+
+def test_survey_known_geometry(oracle_port):
+    """Crop 20x10 -> 8x8 PRESERVE_AR: target 8x4, factors 2.5, region [0,2]-[7,5]; 8x16 -> 8x8: target 4x8."""
+    a = oracle_port.derive_resize(20, 10, 8, 8, abi.RESIZE_PRESERVE_AR)
+    assert (a.target_width, a.target_height, a.fx, a.fy, a.x1, a.y1, a.x2, a.y2) == (8, 4, 2.5, 2.5, 0, 2, 7, 5)
+    b = oracle_port.derive_resize(8, 16, 8, 8, abi.RESIZE_PRESERVE_AR)
+    assert (b.target_width, b.target_height, b.fx, b.fy, b.x1, b.y1, b.x2, b.y2) == (4, 8, 2.0, 2.0, 2, 0, 5, 7)
+
+
+@pytest.mark.skipif(not ref.available(), reason="oracle/_ref not built (reference tree absent)")
+def test_port_matches_reference_build_on_shared_cases(oracle_port):
+    """Direct comparison with the compiled reference on fresh seeds (beyond the stored fixtures)."""
+    rng = np.random.default_rng(5)
+    for trial in range(4):
+        fw, fh = int(rng.integers(40, 300)), int(rng.integers(40, 200))
+        frames = [rng.integers(0, 256, (fh, fw, 3), dtype=np.uint8) for _ in range(2)]
+        n = int(rng.integers(1, 20))
+        rects = chains.random_rects(rng, n, fw, fh, lo=1, hi=min(fw, fh))
+        fi = [i % 2 for i in range(n)]
+        dw, dh = int(rng.integers(1, 80)), int(rng.integers(1, 80))
+        out = np.zeros((n, 3, dh, dw), np.float32)
+        plan = chains.crop_resize_batch(frame_ptrs=[f.ctypes.data for f in frames], frame_index=fi, rects=rects,
+                                        src_width=fw, src_height=fh, src_pitch=fw * 3, dst=out.ctypes.data,
+                                        dst_width=dw, dst_height=dh, post_ops=chains.normalize_ops(), planar=True,
+                                        background=(3.0, 5.0, 7.0))
+        oracle_port.run(plan)
+        expect = ref.crop_resize_norm_planar(frames, fi, rects, dw, dh, (3.0, 5.0, 7.0), 255.0, chains.IMAGENET_MEAN,
+                                             chains.IMAGENET_STD)
+        assert _same(out, expect), trial
