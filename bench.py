@@ -1,0 +1,577 @@
+#!/usr/bin/env python
+"""Benchmark of the fused-execution hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c3] [--impl ours|reference]
+
+A step is one pass of the hot path over one batch of synthetic input: one plan launch
+(one kernel).  The default workload is the batched crop -> resize -> normalise -> planar
+configuration (1024 crops from 8 4K frames per GPU); with N > 1 every rank owns its own
+frames, crops and output tensor (planes shard with no collective), so scaling is weak.
+
+One JSON line is printed by rank 0.  `value` is output Mpix/s with inputs resident in HBM;
+`e2e` is the same metric through the host-buffer C-ABI call (pinned host -> device copies,
+launch, device -> pinned host copy back, every step); `roofline` relates the kernel's
+algorithmic bytes to the measured HBM copy bandwidth; `cpu_baseline` is the reference's own
+CPU code for the same chain, compiled from its headers, timed on this box's host cores.
+
+`--impl reference` times that CPU implementation instead (all host threads, rank 0 only).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+from fusedkernellibrary_b200 import abi, chains  # noqa: E402
+
+L2_BYTES = 126 * 1024 * 1024
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the workload's kernel, from the ncu
+# capture summarised under profiles/ (None = not captured).
+TRAFFIC_BYTES_PER_LAUNCH = {"c3": None}
+
+
+# --------------------------------------------------------------------------------------
+# workloads
+# --------------------------------------------------------------------------------------
+class Workload:
+    """Host arrays + a plan builder.  `build(ptr)` lowers the chain given a name -> address map."""
+
+    name = ""
+    description = ""
+    sets = 1  # independent buffer sets rotated between steps (working sets smaller than L2)
+
+    def __init__(self, seed: int):
+        self.seed = seed
+        self.sources: list[dict] = []   # one dict of numpy arrays per buffer set
+        self.outputs: list[dict] = []
+
+    def build(self, ptr, s: int) -> abi.HostPlan:
+        raise NotImplementedError
+
+    def reference_run(self, threads: int, s: int = 0, planes=None) -> float | None:
+        """Runs the reference's CPU code on buffer set s; returns output pixels computed, or None."""
+        return None
+
+    out_pixels = 0
+
+
+def _u8(rng, *shape):
+    return rng.integers(0, 256, shape, dtype=np.uint8)
+
+
+def _parallel(fn, chunks, threads):
+    if threads <= 1 or len(chunks) <= 1:
+        for c in chunks:
+            fn(c)
+        return
+    it = iter(chunks)
+    lock = threading.Lock()
+
+    def worker():
+        while True:
+            with lock:
+                c = next(it, None)
+            if c is None:
+                return
+            fn(c)
+
+    ts = [threading.Thread(target=worker) for _ in range(min(threads, len(chunks)))]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+
+
+class CropResizeNorm(Workload):
+    """Config 3: PerThreadRead[B] -> Crop[B] -> Resize<INTER_LINEAR,PRESERVE_AR>(224x224, bg 0)
+    -> Div(255) -> Sub(mean) -> Div(std) -> TensorSplit (B x 3 x 224 x 224 float)."""
+    name = "c3"
+
+    def __init__(self, seed, n_frames=8, fw=3840, fh=2160, n_planes=1024, dw=224, dh=224, lo=16, hi=512):
+        super().__init__(seed)
+        rng = np.random.default_rng(seed)
+        self.fw, self.fh, self.dw, self.dh, self.n = fw, fh, dw, dh, n_planes
+        self.rects = chains.random_rects(rng, n_planes, fw, fh, lo=lo, hi=hi)
+        self.frame_index = [i % n_frames for i in range(n_planes)]
+        self.sources = [{f"frame{i}": _u8(rng, fh, fw * 3) for i in range(n_frames)}]
+        self.outputs = [{"out": ((n_planes, 3, dh, dw), np.float32)}]
+        self.n_frames = n_frames
+        self.out_pixels = n_planes * dw * dh
+        self.description = (f"C3 batched crop-resize-norm: {n_frames} frames {fw}x{fh} uchar3, {n_planes} crops "
+                            f"w,h~U[{lo},{hi}] -> PRESERVE_AR {dw}x{dh} -> /255 -mean /std -> planar f32")
+
+    def build(self, ptr, s=0, first=0, count=None):
+        count = self.n - first if count is None else count
+        sl = slice(first, first + count)
+        return chains.crop_resize_batch(
+            frame_ptrs=[ptr(f"frame{i}") for i in range(self.n_frames)], frame_index=self.frame_index[sl],
+            rects=self.rects[sl], src_width=self.fw, src_height=self.fh, src_pitch=self.fw * 3,
+            dst=ptr("out") + first * self.dw * self.dh * 12, dst_width=self.dw, dst_height=self.dh,
+            post_ops=chains.normalize_ops(), planar=True)
+
+    def reference_run(self, threads, s=0, planes=None, out=None):
+        from oracle import reference as ref
+        n = self.n if planes is None else planes
+        if out is None:
+            if getattr(self, "_ref_out", None) is None:
+                self._ref_out = np.zeros((self.n, 3, self.dh, self.dw), np.float32)
+            out = self._ref_out[:n]
+        frames = [self.sources[s][f"frame{i}"].reshape(self.fh, self.fw, 3) for i in range(self.n_frames)]
+        step = 16
+        chunks = [(a, min(a + step, n)) for a in range(0, n, step)]
+
+        def run(c):
+            a, b = c
+            ref.crop_resize_norm_planar(frames, self.frame_index[a:b], self.rects[a:b], self.dw, self.dh, (0, 0, 0),
+                                        255.0, chains.IMAGENET_MEAN, chains.IMAGENET_STD, out=out[a:b])
+
+        _parallel(run, chunks, threads)
+        return n * self.dw * self.dh
+
+
+class ReadmeCropResize(Workload):
+    """Config 2: the README chain, 5 crops of one 4K frame -> 60x60x5 packed float3.
+    `repeat` > 1 cycles the five rects over more planes and 8 frames (the scaled variant)."""
+    name = "c2"
+
+    def __init__(self, seed, repeat=1):
+        super().__init__(seed)
+        rng = np.random.default_rng(seed)
+        self.fw, self.fh = 3840, 2160
+        self.n = 5 * repeat
+        self.n_frames = 1 if repeat == 1 else 8
+        self.rects = np.tile(chains.README_RECTS, (repeat, 1))
+        self.frame_index = [(i // 5) % self.n_frames for i in range(self.n)]
+        self.sets = 1
+        self.sources = [{f"frame{i}": _u8(rng, self.fh, self.fw * 3) for i in range(self.n_frames)}]
+        self.outputs = [{"out": ((self.n, 60, 60, 3), np.float32)}]
+        self.out_pixels = self.n * 3600
+        self.name = "c2" if repeat == 1 else "c2s"
+        self.description = (f"C2 README crop-resize: {self.n_frames} frame(s) 3840x2160 uchar3, {self.n} crops "
+                            "(README rects) -> PRESERVE_AR 60x60 -> *1.4 -0.5 /255 -> RGB2BGR -> packed float3")
+
+    def build(self, ptr, s=0):
+        return chains.crop_resize_batch(
+            frame_ptrs=[ptr(f"frame{i}") for i in range(self.n_frames)], frame_index=self.frame_index, rects=self.rects,
+            src_width=self.fw, src_height=self.fh, src_pitch=self.fw * 3, dst=ptr("out"), dst_width=60, dst_height=60,
+            post_ops=chains.readme_ops(), planar=False)
+
+    def reference_run(self, threads, s=0, planes=None):
+        from oracle import reference as ref
+        frames = [self.sources[s][f"frame{i}"].reshape(self.fh, self.fw, 3) for i in range(self.n_frames)]
+        n = self.n
+        out = np.empty((n, 60, 60, 3), np.float32)
+        chunks = [(a, min(a + 80, n)) for a in range(0, n, 80)]
+
+        def run(c):
+            a, b = c
+            out[a:b] = ref.crop_resize_readme(frames, self.frame_index[a:b], self.rects[a:b], 60, 60, (0, 0, 0), 1.4,
+                                              0.5, 255.0)
+
+        _parallel(run, chunks, threads)
+        return n * 3600
+
+
+class VerticalFusion(Workload):
+    """Config 1: PerThreadRead<uchar3> -> Cast -> Mul(1.4) -> Sub(0.5) -> Div(255) -> PerThreadWrite<float3>."""
+    name = "c1"
+
+    def __init__(self, seed, w=1920, h=1080, sets=12):
+        super().__init__(seed)
+        rng = np.random.default_rng(seed)
+        self.w, self.h, self.sets = w, h, sets
+        self.sources = [{"src": _u8(rng, h, w * 3)} for _ in range(sets)]
+        self.outputs = [{"out": ((h, w, 3), np.float32)} for _ in range(sets)]
+        self.out_pixels = w * h
+        self.description = f"C1 vertical fusion: {w}x{h} uchar3 -> Cast, *1.4, -0.5, /255 -> float3 ({sets} buffer sets)"
+
+    def build(self, ptr, s=0):
+        return chains.elementwise(chains.cast_mul_sub_div_ops(), src=ptr("src"), dst=ptr("out"), width=self.w,
+                                  height=self.h)
+
+    def reference_run(self, threads, s=0, planes=None):
+        from oracle import reference as ref
+        ref.cast_mul_sub_div(self.sources[s]["src"].reshape(self.h, self.w, 3), 1.4, 0.5, 255.0)
+        return self.out_pixels
+
+
+class LongChain(Workload):
+    """Config 5A: N alternating Add(0.001)/Mul(1.0001) on a 3840x2160 float3 image."""
+    name = "c5a"
+
+    def __init__(self, seed, n_ops=16, w=3840, h=2160, sets=2):
+        super().__init__(seed)
+        rng = np.random.default_rng(seed)
+        self.w, self.h, self.sets, self.n_ops = w, h, sets, n_ops
+        self.sources = [{"src": rng.random((h, w * 3), dtype=np.float32)} for _ in range(sets)]
+        self.outputs = [{"out": ((h, w, 3), np.float32)} for _ in range(sets)]
+        self.out_pixels = w * h
+        self.name = f"c5a{n_ops}"
+        self.description = f"C5A long chain: {w}x{h} float3, {n_ops} alternating Add(0.001)/Mul(1.0001) ({sets} buffer sets)"
+
+    def build(self, ptr, s=0):
+        return chains.elementwise(chains.addmul_ops(self.n_ops), src=ptr("src"), dst=ptr("out"), width=self.w,
+                                  height=self.h, src_format=abi.SRC_F32X3)
+
+    def reference_run(self, threads, s=0, planes=None):
+        from oracle import reference as ref
+        ref.addmul_chain(self.sources[s]["src"].reshape(self.h, self.w, 3), self.n_ops, 0.001, 1.0001)
+        return self.out_pixels
+
+
+class Nv12Resize(Workload):
+    """Config 4: ReadYUV<NV12>[32] -> ConvertYUVToRGB<bt709,Full,float3> -> Resize 1280x720 -> Div(255)
+    -> TensorWrite<float3>."""
+    name = "c4"
+
+    def __init__(self, seed, n=32, w=3840, h=2160, dw=1280, dh=720):
+        super().__init__(seed)
+        rng = np.random.default_rng(seed)
+        self.n, self.w, self.h, self.dw, self.dh = n, w, h, dw, dh
+        self.sources = [{f"frame{i}": _u8(rng, h + h // 2, w) for i in range(n)}]
+        self.outputs = [{"out": ((n, dh, dw, 3), np.float32)}]
+        self.out_pixels = n * dw * dh
+        self.description = f"C4 NV12 BVF: {n} NV12 frames {w}x{h} -> BT.709 full RGB -> resize {dw}x{dh} -> /255 -> packed float3"
+
+    def build(self, ptr, s=0):
+        return chains.nv12_resize_batch(frame_ptrs=[ptr(f"frame{i}") for i in range(self.n)], width=self.w,
+                                        height=self.h, pitch=self.w, dst=ptr("out"), dst_width=self.dw,
+                                        dst_height=self.dh)
+
+    def reference_run(self, threads, s=0, planes=None):
+        from oracle import reference as ref
+        n = self.n if planes is None else planes
+        out = np.empty((n, self.dh, self.dw, 3), np.float32)
+        chunks = [(a, min(a + 2, n)) for a in range(0, n, 2)]
+
+        def run(c):
+            a, b = c
+            ref.nv12_resize([self.sources[s][f"frame{i}"] for i in range(a, b)], self.w, self.h, self.dw, self.dh,
+                            255.0, out=out[a:b])
+
+        _parallel(run, chunks, threads)
+        return n * self.dw * self.dh
+
+
+class Divergent(Workload):
+    """Config 5B: one launch, four different chains on four groups of 16 images 1920x1080 uchar3."""
+    name = "c5b"
+
+    def __init__(self, seed, per_group=16, w=1920, h=1080):
+        super().__init__(seed)
+        rng = np.random.default_rng(seed)
+        self.w, self.h, self.pg = w, h, per_group
+        self.sources = [{f"img{i}": _u8(rng, h, w * 3) for i in range(4 * per_group)}]
+        self.outputs = [{"g0": ((per_group, h, w, 3), np.float32), "g1": ((per_group, h, w, 3), np.float32),
+                         "g2": ((per_group, h, w, 3), np.uint8), "g3": ((per_group, h // 2, w // 2, 3), np.float32)}]
+        self.out_pixels = per_group * (3 * w * h + (w // 2) * (h // 2))
+        self.description = (f"C5B divergent horizontal fusion: 4 chains x {per_group} images {w}x{h} uchar3 in one launch "
+                            "(Cast-Mul-Sub | Cast-Add-Div | BGR-Cast-Mul-Saturate u8 | Cast-Resize 960x540)")
+
+    def build(self, ptr, s=0):
+        return chains.divergent_four_groups(src_ptrs=[ptr(f"img{i}") for i in range(4 * self.pg)], width=self.w,
+                                            height=self.h, dst_ptrs=[ptr(f"g{g}") for g in range(4)],
+                                            resize_to=(self.w // 2, self.h // 2), per_group=self.pg)
+
+
+def make_workload(name: str, seed: int) -> Workload:
+    if name == "c3":
+        return CropResizeNorm(seed)
+    if name == "c3small":
+        return CropResizeNorm(seed, n_frames=8, n_planes=256)
+    if name == "c2":
+        return ReadmeCropResize(seed)
+    if name == "c2s":
+        return ReadmeCropResize(seed, repeat=8192 // 5)
+    if name == "c1":
+        return VerticalFusion(seed)
+    if name.startswith("c5a"):
+        return LongChain(seed, n_ops=int(name[3:] or 16))
+    if name == "c4":
+        return Nv12Resize(seed)
+    if name == "c5b":
+        return Divergent(seed)
+    raise SystemExit(f"unknown workload {name}")
+
+
+# --------------------------------------------------------------------------------------
+# helpers
+# --------------------------------------------------------------------------------------
+def measured_peak_gbs() -> tuple[float, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi sampled every 200 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# --------------------------------------------------------------------------------------
+# reference arm (CPU)
+# --------------------------------------------------------------------------------------
+def run_reference_arm(args, rank: int):
+    if rank != 0:
+        return
+    from oracle import reference as ref
+    wl = make_workload(args.workload, 1000)
+    threads = os.cpu_count() or 1
+    if not ref.available() or wl.reference_run(1, 0, planes=1) is None:
+        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref was not built for this workload"}))
+        return
+    for _ in range(args.warmup):
+        wl.reference_run(threads)
+    t0 = time.perf_counter()
+    px = 0
+    for _ in range(args.steps):
+        px += wl.reference_run(threads)
+    dt = time.perf_counter() - t0
+    val = px / dt / 1e6
+    line = {
+        "impl": "reference", "metric": "output Mpix/s (crop-resize-norm)", "value": val, "unit": "Mpix/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": wl.description, "note": "reference CPU backend (TransformDPP<ParArch::CPU>) compiled from "
+                   "its own headers with the device branch of interpolation.h selected; plane chunks of 16 on all host threads"},
+        "cpu_baseline": {"value": val, "unit": "Mpix/s", "cores": threads, "kind": "reference",
+                         "sample": f"the whole workload ({wl.out_pixels} output px) per step"},
+        "e2e": {"value": val, "unit": "Mpix/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# --------------------------------------------------------------------------------------
+# our arm (GPU)
+# --------------------------------------------------------------------------------------
+def run_ours(args, rank: int, world: int, local_rank: int):
+    import torch
+    import torch.distributed as dist
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; this path has no CPU fallback")
+    abi.load_library()
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    wl = make_workload(args.workload, 1000 + 17 * rank)
+    stream = torch.cuda.Stream()
+    sh = stream.cuda_stream
+
+    # device-resident buffers and plans (one per buffer set)
+    dev_sets, plans = [], []
+    for s in range(wl.sets):
+        d = {k: torch.from_numpy(v).cuda() for k, v in wl.sources[s].items()}
+        for k, (shape, dt) in wl.outputs[s].items():
+            d[k] = torch.zeros(shape, dtype=torch.float32 if dt == np.float32 else torch.uint8, device="cuda")
+        dev_sets.append(d)
+        plans.append(abi.DevicePlan(wl.build(lambda n, d=d: d[n].data_ptr(), s)))
+    info = plans[0].info()
+    ws_bytes = sum(t.numel() * t.element_size() for d in dev_sets for t in d.values())
+    l2_note = ("inputs and outputs larger than L2" if ws_bytes > 2 * L2_BYTES
+               else "working set below 2x L2: numbers are L2-assisted")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def launch(i):
+        plans[i % wl.sets].launch(sh)
+
+    with torch.cuda.stream(stream):
+        for i in range(max(args.warmup, 3)):
+            launch(i)
+        barrier()
+        sampler = ClockSampler(local_rank)
+        if rank == 0:
+            sampler.start()
+        # --- timed region: exactly K steps, one kernel each, per-launch events inside ----
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+        barrier()
+        ev[0].record(stream)
+        for i in range(args.steps):
+            launch(i)
+            ev[i + 1].record(stream)
+        barrier()
+        total_ms = ev[0].elapsed_time(ev[-1])
+        per_launch_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
+        clocks = sampler.stop() if rank == 0 else None
+
+    t = torch.tensor([total_ms], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    max_ms = float(t.item())
+    value = wl.out_pixels * world * args.steps / (max_ms * 1e-3) / 1e6
+    kernel_ms = float(np.mean(per_launch_ms))
+
+    # --- end to end through the host-buffer C-ABI call (pinned host buffers) ---------------
+    e2e = None
+    if not args.no_e2e:
+        host = {k: torch.from_numpy(v).pin_memory() for k, v in wl.sources[0].items()}
+        for k, (shape, dt) in wl.outputs[0].items():
+            host[k] = torch.zeros(shape, dtype=torch.float32 if dt == np.float32 else torch.uint8).pin_memory()
+        sess = abi.HostSession(wl.build(lambda n: host[n].data_ptr(), 0))
+        h2d, d2h = sess.traffic()
+        e_steps = max(2, min(args.steps, 5))
+        sess.run(sh)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(e_steps):
+            sess.run(sh)   # returns after the stream has been synchronised
+        e1.record(stream)
+        torch.cuda.synchronize()
+        e_dt = e0.elapsed_time(e1) * 1e-3
+        te = torch.tensor([e_dt], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        e2e = {"value": wl.out_pixels * world * e_steps / float(te.item()) / 1e6, "unit": "Mpix/s",
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e_steps,
+               "ms_per_step": float(te.item()) / e_steps * 1e3,
+               "api": "fkb_host_session_run (pinned host buffers; H2D + kernel + D2H + sync per step)"}
+        sess.destroy()
+
+    # --- CPU baseline: the reference's own CPU code, one core, bounded sample -----------------
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu = cpu_baseline(wl)
+
+    if rank == 0:
+        peak, peak_kind = measured_peak_gbs()
+        achieved = info.algorithmic_bytes / (kernel_ms * 1e-3) / 1e9
+        line = {
+            "metric": "output Mpix/s (crop-resize-norm)", "value": value, "unit": "Mpix/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": max_ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": wl.description, "planes_per_gpu": info.n_planes, "l2": l2_note,
+                       "working_set_bytes_per_gpu": ws_bytes, "sharding": "independent planes per rank, no collective",
+                       "grid": info.grid_x, "block": info.block_x},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": TRAFFIC_BYTES_PER_LAUNCH.get(wl.name), "peak_kind": f"of {peak_kind}",
+                         "algorithmic_bytes_per_launch": info.algorithmic_bytes, "kernel_ms": kernel_ms,
+                         "frac_of_nominal_8TBs": achieved / 8000.0},
+            "cpu_baseline": cpu,
+            "e2e": e2e,
+            "gpu_launches": args.steps,
+            "clocks": clocks,
+        }
+        print(json.dumps(line))
+    for p in plans:
+        p.destroy()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_baseline(wl: Workload):
+    from oracle import reference as ref
+    if ref.available() and wl.reference_run(1, 0, planes=1) is not None:
+        sample_planes = None
+        if isinstance(wl, CropResizeNorm):
+            sample_planes = min(wl.n, 1024)
+        elif isinstance(wl, Nv12Resize):
+            sample_planes = 4
+        t0 = time.perf_counter()
+        px = wl.reference_run(1, 0, planes=sample_planes)
+        dt = time.perf_counter() - t0
+        reps = 1
+        while dt < 3.0 and reps < 50:   # small workloads: repeat up to a few seconds
+            px += wl.reference_run(1, 0, planes=sample_planes)
+            dt = time.perf_counter() - t0
+            reps += 1
+        return {"value": px / dt / 1e6, "unit": "Mpix/s", "cores": 1, "kind": "reference",
+                "host_cores_available": os.cpu_count(),
+                "sample": f"{px} output px of the same workload in {dt:.1f} s on one thread (the reference CPU "
+                          "backend is single-threaded)"}
+    # no compiled reference for this workload: time the plain-C restatement instead
+    from oracle import port
+    arrays = {**wl.sources[0]}
+    for k, (shape, dt_) in wl.outputs[0].items():
+        arrays[k] = np.zeros(shape, dt_)
+    plan = wl.build(lambda n: arrays[n].ctypes.data, 0)
+    t0 = time.perf_counter()
+    port.run(plan)
+    dt = time.perf_counter() - t0
+    return {"value": wl.out_pixels / dt / 1e6, "unit": "Mpix/s", "cores": 1, "kind": "port",
+            "host_cores_available": os.cpu_count(), "sample": f"the whole workload once ({dt:.1f} s, one thread)"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="c3")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        raise SystemExit("launch with: python -m torch.distributed.run --nnodes=1 --nproc-per-node N bench.py --gpus N ...")
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()
