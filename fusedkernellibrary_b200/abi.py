@@ -92,6 +92,8 @@ class PlanInfo(C.Structure):
         ("output_pixels", C.c_uint64),
         ("algorithmic_bytes", C.c_uint64),
         ("device_bytes", C.c_uint64),
+        ("n_constant_divisions", C.c_int32),
+        ("n_ieee_divisions", C.c_int32),
     ]
 
 
@@ -172,7 +174,7 @@ _lib = None
 
 EXPORTS = [
     "fkb_version", "fkb_status_string", "fkb_last_error", "fkb_derive_resize",
-    "fkb_reference_block_size", "fkb_plan_create", "fkb_plan_launch", "fkb_plan_get_info",
+    "fkb_reference_block_size", "fkb_plan_create", "fkb_plan_validate", "fkb_plan_launch", "fkb_plan_get_info",
     "fkb_plan_get_resize_params", "fkb_plan_destroy", "fkb_execute", "fkb_host_session_create",
     "fkb_host_session_run", "fkb_host_session_get_traffic", "fkb_host_session_destroy",
     "fkb_execute_host",
@@ -198,6 +200,7 @@ def load_library(path: os.PathLike | None = None) -> C.CDLL:
     lib.fkb_reference_block_size.argtypes = [C.c_uint32, C.c_uint32, C.POINTER(C.c_uint32),
                                              C.POINTER(C.c_uint32)]
     lib.fkb_plan_create.argtypes = [C.POINTER(PlanDesc), C.POINTER(C.c_void_p)]
+    lib.fkb_plan_validate.argtypes = [C.POINTER(PlanDesc), C.POINTER(PlanInfo)]
     lib.fkb_plan_launch.argtypes = [C.c_void_p, C.c_void_p]
     lib.fkb_plan_get_info.argtypes = [C.c_void_p, C.POINTER(PlanInfo)]
     lib.fkb_plan_get_resize_params.argtypes = [C.c_void_p, C.c_int32, C.POINTER(ResizeParams)]
@@ -253,6 +256,15 @@ class DevicePlan:
             self.destroy()
         except Exception:
             pass
+
+
+def validate(host_plan: HostPlan) -> PlanInfo:
+    """Host-only validation and lowering of a plan description (no device needed)."""
+    lib = load_library()
+    info = PlanInfo()
+    desc = host_plan.desc()
+    check(lib.fkb_plan_validate(C.byref(desc), C.byref(info)), "fkb_plan_validate")
+    return info
 
 
 def execute(host_plan: HostPlan, stream: int | None = None) -> None:

@@ -76,8 +76,37 @@ struct LaunchArgs {
 
 constexpr int BLOCK_THREADS = 256;
 constexpr int PX_PER_THREAD = 4;
-constexpr int ITEM_PIXELS_VEC = BLOCK_THREADS * PX_PER_THREAD; /* FLAT and RESIZE classes     */
+constexpr int ITEM_PIXELS_VEC = BLOCK_THREADS * PX_PER_THREAD; /* FLAT classes                */
 constexpr int ITEM_PIXELS_GENERIC = BLOCK_THREADS;
+
+/* Device-only opcode: division by a plan-time constant, lowered from FKB_OP_DIV when the host
+ * has proven the three-instruction form exact.  Takes two op slots: {-p}, then {1/p}. */
+constexpr int32_t DEV_OP_DIV_BY_CONSTANT = 16;
+
+/* RESIZE classes: a thread owns one group of four adjacent output columns and walks
+ * RESIZE_ROWS_PER_THREAD rows, so the horizontal taps and weights are computed once per
+ * thread.  A block covers `gw` groups x (`rs` row slots * RESIZE_ROWS_PER_THREAD) rows. */
+constexpr int RESIZE_ROWS_PER_THREAD = 8;
+
+struct ResizeTiling {
+    uint32_t gw;      /* column groups per block (<= BLOCK_THREADS)           */
+    uint32_t rs;      /* row slots per block: threads = gw * rs               */
+    uint32_t tiles_x; /* blocks across a row                                  */
+    uint32_t tiles_y; /* blocks down the plane                                */
+};
+#if defined(__CUDACC__)
+__host__ __device__
+#endif
+inline ResizeTiling resize_tiling(uint32_t dst_w, uint32_t dst_h) {
+    ResizeTiling t;
+    const uint32_t groups = dst_w / PX_PER_THREAD;
+    t.gw = groups < (uint32_t)BLOCK_THREADS ? groups : (uint32_t)BLOCK_THREADS;
+    t.rs = (uint32_t)BLOCK_THREADS / t.gw;
+    t.tiles_x = (groups + t.gw - 1) / t.gw;
+    const uint32_t rows = t.rs * RESIZE_ROWS_PER_THREAD;
+    t.tiles_y = (dst_h + rows - 1) / rows;
+    return t;
+}
 
 }  // namespace fkb
 

@@ -10,7 +10,9 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <cmath>
 #include <map>
+#include <mutex>
 #include <new>
 #include <string>
 #include <vector>
@@ -73,6 +75,7 @@ struct HostImage {
     uint32_t max_seq_ops = 0;
     uint64_t output_pixels = 0;
     uint64_t algorithmic_bytes = 0;
+    int n_constant_divisions = 0, n_ieee_divisions = 0;
 
     size_t off_planes() const { return 0; }
     size_t off_seqs() const { return planes.size() * sizeof(DevPlane); }
@@ -171,6 +174,182 @@ extern "C" FKB_API int fkb_reference_block_size(uint32_t ax, uint32_t ay, uint32
 }
 
 /* ------------------------------------------------------------------------------------ */
+/* division by a plan-time constant                                                     */
+/* ------------------------------------------------------------------------------------ */
+/* Div<float3> is a true IEEE division in the reference (basic_ops/arithmetic.h:84).  Its
+ * divisor is fixed when the plan is made, so the kernels may use
+ *     q0 = RN(x * r),  e = x - p*q0 (one FMA, exact),  q = RN(q0 + e*r),   r = RN(1/p)
+ * which costs three instructions, but only where it is PROVEN to return RN(x/p):
+ *  (1) per divisor: the sequence is compared with x/p for every one of the 2^23 significands
+ *      of x in [1, 2).  Multiplying x by a power of two multiplies every intermediate by the
+ *      same power exactly, so this covers every x for which nothing under- or overflows;
+ *  (2) per use: a range analysis of the sequence shows that the dividend is +0 or has
+ *      2^-100 <= |x| <= 2^100 (with 2^-20 <= |p| <= 2^20 every intermediate is then a normal
+ *      number or exactly representable), and that it cannot be -0 (the sequence would
+ *      return +0).
+ * Anything else keeps the IEEE division. */
+static inline uint32_t float_bits(float f) { uint32_t u; std::memcpy(&u, &f, 4); return u; }
+static inline float bits_float(uint32_t u) { float f; std::memcpy(&f, &u, 4); return f; }
+
+#if defined(__x86_64__)
+__attribute__((target("fma")))
+#endif
+static bool check_all_significands(float p) {
+    const float r = 1.0f / p, np = -p;
+    for (uint32_t m = 0; m < (1u << 23); ++m) {
+        const float x = bits_float(0x3F800000u | m);
+        const float q0 = x * r;
+        const float e = __builtin_fmaf(np, q0, x);
+        const float q = __builtin_fmaf(e, r, q0);
+        if (float_bits(q) != float_bits(x / p)) return false;
+    }
+    return true;
+}
+
+static bool constant_division_is_exact(float p) {
+    static std::mutex mu;
+    static std::map<uint32_t, bool> cache;
+#if defined(__x86_64__)
+    if (!__builtin_cpu_supports("fma")) return false;
+#endif
+    const float a = std::fabs(p);
+    if (!(a >= 0x1p-20f && a <= 0x1p20f)) return false; /* also rejects NaN, 0, inf */
+    std::lock_guard<std::mutex> lock(mu);
+    const auto it = cache.find(float_bits(p));
+    if (it != cache.end()) return it->second;
+    const bool ok = check_all_significands(p);
+    cache[float_bits(p)] = ok;
+    return ok;
+}
+
+/* What is known about the values flowing through a sequence (all three channels together). */
+struct ValueRange {
+    bool known = false;   /* false: anything, including NaN and infinities                    */
+    double absmax = 0;    /* |v| <= absmax                                                    */
+    int nz_exp = 0;       /* v != 0  =>  |v| >= 2^nz_exp                                      */
+    int grain = 0;        /* every v is an integer multiple of 2^grain                        */
+    bool nonneg = true;   /* v >= 0                                                           */
+    bool neg_zero = false;/* v may be -0                                                      */
+    void check() { if (!(absmax < 1e37) || nz_exp < -120 || grain < -140) known = false; }
+};
+
+static int exp_of(float f) { return std::ilogb(std::fabs(f)); }
+
+/* Applies one reference operation to the range; returns true when a division at this point
+   may use the constant form. */
+static bool advance_range(ValueRange& v, const fkb_op& op) {
+    const float* p = op.p;
+    bool fast = false;
+    switch (op.opcode) {
+        case FKB_OP_MUL: {
+            if (!v.known) break;
+            int emin = 1000; double amax = 0; bool neg = false;
+            for (int c = 0; c < 3; ++c) {
+                if (!std::isfinite(p[c]) || p[c] == 0.0f) { v.known = false; return false; }
+                emin = std::min(emin, exp_of(p[c])); amax = std::max(amax, (double)std::fabs(p[c])); neg |= p[c] < 0;
+            }
+            v.absmax *= amax * 1.000001; v.nz_exp += emin; v.grain = v.nz_exp - 23;
+            if (neg) { v.neg_zero = true; v.nonneg = false; }
+            break;
+        }
+        case FKB_OP_ADD: case FKB_OP_SUB: {
+            if (!v.known) break;
+            int nz = 1000, grain = v.grain; double amax = 0; bool any_zero = false;
+            for (int c = 0; c < 3; ++c) {
+                if (!std::isfinite(p[c])) { v.known = false; return false; }
+                if (p[c] == 0.0f) { any_zero = true; nz = std::min(nz, v.nz_exp); continue; }
+                const int ep = exp_of(p[c]);
+                /* RN(a +- p) != 0: either |a| < |p|/2 and the result is at least |p|/2, or a is a
+                   multiple of ulp(|p|/2) and so is the exact sum */
+                nz = std::min(nz, std::max(std::min(v.grain, ep - 23), ep - 24));
+                grain = std::min(grain, ep - 23);
+                amax = std::max(amax, (double)std::fabs(p[c]));
+            }
+            v.absmax += amax; v.nz_exp = nz; v.grain = grain; v.nonneg = false;
+            v.neg_zero = v.neg_zero && any_zero;
+            break;
+        }
+        case FKB_OP_DIV: {
+            bool exact = true; int emax = -1000; double amin = 1e300; bool neg = false;
+            for (int c = 0; c < 3; ++c) {
+                if (!std::isfinite(p[c]) || p[c] == 0.0f) { v.known = false; return false; }
+                exact = exact && constant_division_is_exact(p[c]);
+                emax = std::max(emax, exp_of(p[c])); amin = std::min(amin, (double)std::fabs(p[c])); neg |= p[c] < 0;
+            }
+            if (!v.known) break;
+            fast = exact && v.absmax <= 0x1p100 && v.nz_exp >= -100 && !v.neg_zero;
+            v.absmax = v.absmax / amin * 1.000001; v.nz_exp = v.nz_exp - emax - 1; v.grain = v.nz_exp - 23;
+            if (neg) { v.neg_zero = true; v.nonneg = false; }
+            break;
+        }
+        case FKB_OP_SATURATE_CAST_U8:
+            v = ValueRange{true, 255.0, 0, 0, true, false};
+            break;
+        case FKB_OP_YUV_TO_RGB_BT709_FULL:
+            /* integers times the matrix of color_conversion.h:143-146: the smallest non-zero
+               coefficient is 0.1873, so every product and sum is a multiple of 2^-26 */
+            if (v.known) v = ValueRange{true, 512.0, -26, -26, false, false};
+            break;
+        default: /* CAST_F32, SWAP_RB: values unchanged */
+            break;
+    }
+    v.check();
+    return fast;
+}
+
+/* Bilinear interpolation (interpolation.h:92-95) of values in range v.  step_exp_x/y: floor(log2)
+   of the smallest source step of any plane using the sequence, capped at 0: a non-zero weight is a
+   multiple of ulp(source coordinate) >= 2^(step_exp - 23). */
+static void advance_range_resize(ValueRange& v, int step_exp_x, int step_exp_y, bool preserve, const float* bg) {
+    if (v.known) {
+        const int gx = step_exp_x - 23, gy = step_exp_y - 23;
+        v.nz_exp = v.nz_exp + gx + gy;              /* one product value*weight, if not zero     */
+        if (!v.nonneg) v.nz_exp -= 23;              /* signed terms may cancel down to one grain */
+        v.grain = v.nz_exp - 23;
+        v.absmax *= 1.001;
+    }
+    if (preserve && v.known) {
+        for (int c = 0; c < 3; ++c) {
+            if (!std::isfinite(bg[c])) { v.known = false; break; }
+            v.absmax = std::max(v.absmax, (double)std::fabs(bg[c]));
+            if (bg[c] != 0.0f) { v.nz_exp = std::min(v.nz_exp, exp_of(bg[c])); v.grain = std::min(v.grain, exp_of(bg[c]) - 23); }
+            if (bg[c] < 0.0f) v.nonneg = false;
+            if (bg[c] == 0.0f && std::signbit(bg[c])) v.neg_zero = true;
+        }
+    }
+    v.check();
+}
+
+/* Device form of a sequence's operations. */
+static void lower_ops(const fkb_sequence& s, int n_pre, int step_exp_x, int step_exp_y, std::vector<DevOp>& out,
+                      int& dev_n_pre) {
+    ValueRange v;
+    if (s.src_format != FKB_SRC_F32X3) v = ValueRange{true, 255.0, 0, 0, true, false};
+    dev_n_pre = 0;
+    for (int k = 0; k <= s.n_ops; ++k) {
+        if (k == n_pre && s.resize_mode != FKB_RESIZE_NONE) {
+            advance_range_resize(v, step_exp_x, step_exp_y, s.resize_mode == FKB_RESIZE_PRESERVE_AR, s.background);
+            dev_n_pre = (int)out.size();
+        }
+        if (k == s.n_ops) break;
+        const fkb_op& op = s.ops[k];
+        const bool fast = advance_range(v, op);
+        DevOp o;
+        o.opcode = op.opcode; o.p[0] = op.p[0]; o.p[1] = op.p[1]; o.p[2] = op.p[2];
+        if (op.opcode == FKB_OP_DIV && fast) {
+            DevOp r;
+            o.opcode = DEV_OP_DIV_BY_CONSTANT;
+            r.opcode = 0;
+            for (int c = 0; c < 3; ++c) { o.p[c] = -op.p[c]; r.p[c] = 1.0f / op.p[c]; }
+            out.push_back(o);
+            out.push_back(r);
+        } else {
+            out.push_back(o);
+        }
+    }
+}
+
+/* ------------------------------------------------------------------------------------ */
 /* validation and lowering                                                              */
 /* ------------------------------------------------------------------------------------ */
 enum ValueType { VT_U8 = 0, VT_F32 = 1, VT_YUV8 = 2 };
@@ -247,15 +426,9 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
     for (int s = 0; s < d->n_sequences; ++s) {
         const int rc = check_sequence(d->sequences[s], s, img.seqs[s]);
         if (rc) return rc;
-        img.seqs[s].ops_begin = (int32_t)img.ops.size();
-        for (int k = 0; k < d->sequences[s].n_ops; ++k) {
-            DevOp o;
-            o.opcode = d->sequences[s].ops[k].opcode;
-            o.p[0] = d->sequences[s].ops[k].p[0]; o.p[1] = d->sequences[s].ops[k].p[1]; o.p[2] = d->sequences[s].ops[k].p[2];
-            img.ops.push_back(o);
-        }
-        img.max_seq_ops = std::max<uint32_t>(img.max_seq_ops, (uint32_t)d->sequences[s].n_ops);
     }
+    /* smallest source step of any plane of a sequence, as floor(log2), capped at 0 */
+    std::vector<int> step_exp_x(d->n_sequences, 0), step_exp_y(d->n_sequences, 0);
 
     img.planes.resize(d->n_planes);
     img.resize.assign(d->n_planes, fkb_resize_params{});
@@ -309,6 +482,8 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
             const int rc = fkb_derive_resize(p.crop_width, p.crop_height, (int32_t)p.dst_width, (int32_t)p.dst_height, s.resize_mode, &rp);
             if (rc) return rc;
             dp.fx = rp.fx; dp.fy = rp.fy; dp.x1 = rp.x1; dp.y1 = rp.y1; dp.x2 = rp.x2; dp.y2 = rp.y2;
+            step_exp_x[p.sequence] = std::min(step_exp_x[p.sequence], std::ilogb(rp.fx));
+            step_exp_y[p.sequence] = std::min(step_exp_y[p.sequence], std::ilogb(rp.fy));
         }
 
         /* choose the body */
@@ -334,7 +509,10 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
             if (s.src_format == FKB_SRC_U8X3 && s.dst_format == FKB_DST_F32_PLANAR3 && (p.dst_channel_stride % 16) == 0) cls = CLASS_RESIZE_U8_PLANAR;
             else if (s.src_format == FKB_SRC_U8X3 && s.dst_format == FKB_DST_F32X3_PACKED) cls = CLASS_RESIZE_U8_PACKED;
             else if (s.src_format == FKB_SRC_NV12 && s.dst_format == FKB_DST_F32X3_PACKED) cls = CLASS_RESIZE_NV12_PACKED;
-            if (cls != CLASS_GENERIC) items = ((out_px / PX_PER_THREAD) + BLOCK_THREADS - 1) / BLOCK_THREADS;
+            if (cls != CLASS_GENERIC) {
+                const ResizeTiling t = resize_tiling(p.dst_width, p.dst_height);
+                items = (uint64_t)t.tiles_x * t.tiles_y;
+            }
         }
         if (cls == CLASS_GENERIC) items = (out_px + ITEM_PIXELS_GENERIC - 1) / ITEM_PIXELS_GENERIC;
         dp.plane_class = cls;
@@ -350,6 +528,20 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
         img.output_pixels += out_px;
         const uint64_t crop_px = (uint64_t)p.crop_width * p.crop_height;
         img.algorithmic_bytes += (s.src_format == FKB_SRC_NV12 ? crop_px + crop_px / 2 : crop_px * spx) + out_px * (s.dst_format == FKB_DST_F32_PLANAR3 ? 12 : dpx);
+    }
+    for (int s = 0; s < d->n_sequences; ++s) {
+        DevSeq& ds = img.seqs[s];
+        const size_t begin = img.ops.size();
+        int dev_n_pre = 0;
+        lower_ops(d->sequences[s], ds.n_pre, step_exp_x[s], step_exp_y[s], img.ops, dev_n_pre);
+        ds.ops_begin = (int32_t)begin;
+        ds.n_ops = (int32_t)(img.ops.size() - begin);
+        ds.n_pre = dev_n_pre - (int32_t)begin;
+        img.max_seq_ops = std::max<uint32_t>(img.max_seq_ops, (uint32_t)ds.n_ops);
+        for (size_t k = begin; k < img.ops.size(); ++k) {
+            img.n_constant_divisions += img.ops[k].opcode == DEV_OP_DIV_BY_CONSTANT;
+            img.n_ieee_divisions += img.ops[k].opcode == FKB_OP_DIV;
+        }
     }
     img.item_start[d->n_planes] = (uint32_t)total;
     img.total_items = (uint32_t)total;
@@ -389,6 +581,29 @@ static int require_device(int* device) {
     return FKB_OK;
 }
 
+static fkb_plan_info info_of(const HostImage& img) {
+    fkb_plan_info info{};
+    info.n_planes = (int32_t)img.planes.size();
+    info.n_sequences = (int32_t)img.seqs.size();
+    info.n_launches = 1;
+    info.grid_x = img.total_items;
+    info.block_x = BLOCK_THREADS;
+    info.output_pixels = img.output_pixels;
+    info.algorithmic_bytes = img.algorithmic_bytes;
+    info.device_bytes = img.bytes();
+    info.n_constant_divisions = img.n_constant_divisions;
+    info.n_ieee_divisions = img.n_ieee_divisions;
+    return info;
+}
+
+extern "C" FKB_API int fkb_plan_validate(const fkb_plan_desc* desc, fkb_plan_info* out_info) {
+    HostImage img;
+    const int rc = lower(desc, img);
+    if (rc) return rc;
+    if (out_info) *out_info = info_of(img);
+    return FKB_OK;
+}
+
 extern "C" FKB_API int fkb_plan_create(const fkb_plan_desc* desc, fkb_plan** out_plan) {
     if (!out_plan) return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_plan_create: out_plan is NULL");
     *out_plan = nullptr;
@@ -415,14 +630,7 @@ extern "C" FKB_API int fkb_plan_create(const fkb_plan_desc* desc, fkb_plan** out
     plan->args = img.args_for(static_cast<const unsigned char*>(plan->d_block));
     plan->launch_class = img.launch_class;
     plan->resize = std::move(img.resize);
-    plan->info.n_planes = desc->n_planes;
-    plan->info.n_sequences = desc->n_sequences;
-    plan->info.n_launches = 1;
-    plan->info.grid_x = img.total_items;
-    plan->info.block_x = BLOCK_THREADS;
-    plan->info.output_pixels = img.output_pixels;
-    plan->info.algorithmic_bytes = img.algorithmic_bytes;
-    plan->info.device_bytes = plan->d_bytes;
+    plan->info = info_of(img);
     *out_plan = plan;
     return FKB_OK;
 }

@@ -32,6 +32,29 @@ __device__ __forceinline__ float saturate_round_u8(float f) {
     return (float)__float2int_rz(__fadd_rn(f, 0.5f));
 }
 
+/* Exact uchar -> float without the conversion unit: 2^23 + b has b in its low mantissa bits. */
+__device__ __forceinline__ float u8_to_float(uint32_t b) {
+    return __fsub_rn(__uint_as_float(b | 0x4B000000u), 8388608.0f);
+}
+
+/* Byte LANE of a packed word, as float: one byte permute builds 2^23 + b, one add removes 2^23. */
+template <int LANE>
+__device__ __forceinline__ float packed_u8_to_float(uint32_t w) {
+    return __fsub_rn(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7440 | LANE)), 8388608.0f);
+}
+
+/* x / p for a divisor known when the plan was made: with r = RN(1/p),
+ *     q0 = RN(x*r);  e = x - p*q0 (exact, one FMA);  q = RN(q0 + e*r)
+ * The host emits this form only for divisors for which it has checked the sequence against
+ * IEEE division on all 2^23 significands of x, and only where it has shown that x stays in
+ * the range in which scaling by powers of two is exact (see prove_fast_division in
+ * fkb_host.cu).  np is -p. */
+__device__ __forceinline__ float div_by_constant(float x, float np, float r) {
+    const float q0 = __fmul_rn(x, r);
+    const float e = __fmaf_rn(np, q0, x);
+    return __fmaf_rn(e, r, q0);
+}
+
 /* ConvertYUVToRGB<NV12, Full, bt709, false, float3> (color_conversion.h:265-308; matrix
  * :143-146; row reduction left to right, basic_ops/algebraic.h:58-64). */
 __device__ __forceinline__ void yuv_to_rgb_bt709_full(float& a, float& b, float& c) {
@@ -82,6 +105,17 @@ __device__ __forceinline__ void apply_ops(float (&v)[NPX * 3], const DevOp* __re
                     v[3 * i + 2] = __fadd_rn(v[3 * i + 2], o.w);
                 }
                 break;
+            case DEV_OP_DIV_BY_CONSTANT: { /* two slots: {-p}, {1/p} */
+                const float4 r = *reinterpret_cast<const float4*>(&sops[k + 1]);
+                ++k;
+#pragma unroll
+                for (int i = 0; i < NPX; ++i) {
+                    v[3 * i + 0] = div_by_constant(v[3 * i + 0], o.y, r.y);
+                    v[3 * i + 1] = div_by_constant(v[3 * i + 1], o.z, r.z);
+                    v[3 * i + 2] = div_by_constant(v[3 * i + 2], o.w, r.w);
+                }
+                break;
+            }
             case FKB_OP_SWAP_RB:
 #pragma unroll
                 for (int i = 0; i < NPX; ++i) {
@@ -118,7 +152,7 @@ __device__ __forceinline__ void read_tap(const DevPlane& P, int a, int b, float&
     const int x = a + P.crop_x, y = b + P.crop_y;
     if (SRC == FKB_SRC_U8X3) {
         const uint8_t* p = P.src + (size_t)y * P.src_pitch + (size_t)x * 3;
-        r0 = (float)__ldg(p); r1 = (float)__ldg(p + 1); r2 = (float)__ldg(p + 2);
+        r0 = u8_to_float(__ldg(p)); r1 = u8_to_float(__ldg(p + 1)); r2 = u8_to_float(__ldg(p + 2));
     } else if (SRC == FKB_SRC_F32X3) {
         const float* p = reinterpret_cast<const float*>(P.src + (size_t)y * P.src_pitch + (size_t)x * 12);
         r0 = __ldg(p); r1 = __ldg(p + 1); r2 = __ldg(p + 2);
@@ -126,7 +160,7 @@ __device__ __forceinline__ void read_tap(const DevPlane& P, int a, int b, float&
         const uint8_t* luma = P.src + (size_t)y * P.src_pitch + (size_t)x;
         const uint8_t* chroma = P.src + (size_t)P.src_pitch * P.src_height + (size_t)(y >> 1) * P.src_pitch +
                                 (size_t)(x >> 1) * 2;
-        r0 = (float)__ldg(luma); r1 = (float)__ldg(chroma); r2 = (float)__ldg(chroma + 1);
+        r0 = u8_to_float(__ldg(luma)); r1 = u8_to_float(__ldg(chroma)); r2 = u8_to_float(__ldg(chroma + 1));
     }
 }
 
@@ -234,10 +268,10 @@ __device__ __forceinline__ void body_flat(const DevPlane& P, const DevSeq& S, co
 #pragma unroll
             for (int k = 0; k < 3; ++k) {
                 const uint32_t w = __ldg(s4 + k);
-                v[4 * k + 0] = (float)(w & 0xFF);
-                v[4 * k + 1] = (float)((w >> 8) & 0xFF);
-                v[4 * k + 2] = (float)((w >> 16) & 0xFF);
-                v[4 * k + 3] = (float)(w >> 24);
+                v[4 * k + 0] = packed_u8_to_float<0>(w);
+                v[4 * k + 1] = packed_u8_to_float<1>(w);
+                v[4 * k + 2] = packed_u8_to_float<2>(w);
+                v[4 * k + 3] = packed_u8_to_float<3>(w);
             }
         } else {
             const float4* s4 = reinterpret_cast<const float4*>(src);
@@ -284,59 +318,99 @@ __device__ __forceinline__ void body_flat(const DevPlane& P, const DevSeq& S, co
 }
 
 /* ------------------------------------------------------------------------------------ */
-/* body: bilinear resize, four adjacent output pixels of one row per thread             */
+/* body: bilinear resize, a 4-column group walked down several rows per thread          */
 /* ------------------------------------------------------------------------------------ */
 template <int SRC, bool PLANAR>
 __device__ __forceinline__ void body_resize(const DevPlane& P, const DevSeq& S, const DevOp* sops, uint32_t local) {
-    const uint32_t groups_per_row = P.dst_w / PX_PER_THREAD;
-    const uint32_t g = local * BLOCK_THREADS + threadIdx.x;
-    if (g >= groups_per_row * P.dst_h) return;
-    const int y = g / groups_per_row;
-    const int x0 = (g - y * groups_per_row) * PX_PER_THREAD;
+    const ResizeTiling T = resize_tiling(P.dst_w, P.dst_h);
+    const uint32_t tile_y = local / T.tiles_x, tile_x = local - tile_y * T.tiles_x;
+    const uint32_t slot = threadIdx.x / T.gw, gi = threadIdx.x - slot * T.gw;
+    const uint32_t group = tile_x * T.gw + gi;
+    if (slot >= T.rs || group >= P.dst_w / PX_PER_THREAD) return;
+    const int x0 = group * PX_PER_THREAD;
     const bool preserve = S.resize_mode == FKB_RESIZE_PRESERVE_AR;
-    const bool row_inside = !preserve || (y >= P.y1 && y <= P.y2);
 
-    float v[12];
-    Axis ay;
-    if (row_inside) ay = make_axis(y - P.y1, P.fy, P.crop_h);
+    /* The value every output element outside the region of interest ends up with: the
+       default value run through the continuation (resize.h:84-86). */
+    float bgv[3] = {S.bg[0], S.bg[1], S.bg[2]};
+    if (preserve) apply_ops<1>(bgv, sops, S.n_pre, S.n_ops);
+
+    /* horizontal taps and weights of the four columns, once per thread */
+    int xa0[PX_PER_THREAD], xa1[PX_PER_THREAD];
+    float wx0[PX_PER_THREAD], wx1[PX_PER_THREAD];
+    uint32_t inside = 0;
 #pragma unroll
     for (int i = 0; i < PX_PER_THREAD; ++i) {
         const int x = x0 + i;
-        if (row_inside && (!preserve || (x >= P.x1 && x <= P.x2))) {
-            const Axis ax = make_axis(x - P.x1, P.fx, P.crop_w);
-            float t[4][3];
-            read_tap<SRC>(P, ax.i0, ay.i0, t[0][0], t[0][1], t[0][2]);
-            read_tap<SRC>(P, ax.i1, ay.i0, t[1][0], t[1][1], t[1][2]);
-            read_tap<SRC>(P, ax.i0, ay.i1, t[2][0], t[2][1], t[2][2]);
-            read_tap<SRC>(P, ax.i1, ay.i1, t[3][0], t[3][1], t[3][2]);
-            if (SRC == FKB_SRC_NV12) {
-                if (S.pre_kind == PRE_YUV_BT709) {
+        const bool in = !preserve || (x >= P.x1 && x <= P.x2);
+        const Axis ax = make_axis(in ? x - P.x1 : 0, P.fx, P.crop_w);
+        xa0[i] = ax.i0; xa1[i] = ax.i1; wx0[i] = ax.w0; wx1[i] = ax.w1;
+        inside |= (in ? 1u : 0u) << i;
+    }
+    const uint8_t* const src0 =
+        SRC == FKB_SRC_NV12 ? P.src : P.src + (size_t)P.crop_y * P.src_pitch + (size_t)P.crop_x * 3;
+
+    const int y_first = tile_y * (T.rs * RESIZE_ROWS_PER_THREAD) + slot;
+#pragma unroll 1
+    for (int j = 0; j < RESIZE_ROWS_PER_THREAD; ++j) {
+        const int y = y_first + j * (int)T.rs;
+        if (y >= (int)P.dst_h) break;
+        const bool row_inside = !preserve || (y >= P.y1 && y <= P.y2);
+        float v[12];
+        if (row_inside && inside != 0) {
+            const Axis ay = make_axis(y - P.y1, P.fy, P.crop_h);
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) yuv_to_rgb_bt709_full(t[k][0], t[k][1], t[k][2]);
+            for (int i = 0; i < PX_PER_THREAD; ++i) {
+                float t[4][3];
+                if (SRC == FKB_SRC_U8X3) {
+                    const uint8_t* r0 = src0 + (size_t)ay.i0 * P.src_pitch;
+                    const uint8_t* r1 = src0 + (size_t)ay.i1 * P.src_pitch;
+                    const uint8_t* p00 = r0 + xa0[i] * 3; const uint8_t* p10 = r0 + xa1[i] * 3;
+                    const uint8_t* p01 = r1 + xa0[i] * 3; const uint8_t* p11 = r1 + xa1[i] * 3;
+#pragma unroll
+                    for (int c = 0; c < 3; ++c) {
+                        t[0][c] = u8_to_float(__ldg(p00 + c)); t[1][c] = u8_to_float(__ldg(p10 + c));
+                        t[2][c] = u8_to_float(__ldg(p01 + c)); t[3][c] = u8_to_float(__ldg(p11 + c));
+                    }
+                } else {
+                    read_tap<SRC>(P, xa0[i], ay.i0, t[0][0], t[0][1], t[0][2]);
+                    read_tap<SRC>(P, xa1[i], ay.i0, t[1][0], t[1][1], t[1][2]);
+                    read_tap<SRC>(P, xa0[i], ay.i1, t[2][0], t[2][1], t[2][2]);
+                    read_tap<SRC>(P, xa1[i], ay.i1, t[3][0], t[3][1], t[3][2]);
+                    if (S.pre_kind == PRE_YUV_BT709) {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) yuv_to_rgb_bt709_full(t[k][0], t[k][1], t[k][2]);
+                    }
+                }
+                const float w00 = __fmul_rn(wx0[i], ay.w0), w10 = __fmul_rn(wx1[i], ay.w0);
+                const float w01 = __fmul_rn(wx0[i], ay.w1), w11 = __fmul_rn(wx1[i], ay.w1);
+#pragma unroll
+                for (int c = 0; c < 3; ++c) v[3 * i + c] = blend(t[0][c], t[1][c], t[2][c], t[3][c], w00, w10, w01, w11);
+            }
+            apply_ops<PX_PER_THREAD>(v, sops, S.n_pre, S.n_ops);
+            if (inside != 0xF) {
+#pragma unroll
+                for (int i = 0; i < PX_PER_THREAD; ++i) {
+                    if (!((inside >> i) & 1u)) { v[3 * i + 0] = bgv[0]; v[3 * i + 1] = bgv[1]; v[3 * i + 2] = bgv[2]; }
                 }
             }
-            const float w00 = __fmul_rn(ax.w0, ay.w0), w10 = __fmul_rn(ax.w1, ay.w0);
-            const float w01 = __fmul_rn(ax.w0, ay.w1), w11 = __fmul_rn(ax.w1, ay.w1);
-#pragma unroll
-            for (int c = 0; c < 3; ++c) v[3 * i + c] = blend(t[0][c], t[1][c], t[2][c], t[3][c], w00, w10, w01, w11);
         } else {
-            v[3 * i + 0] = S.bg[0]; v[3 * i + 1] = S.bg[1]; v[3 * i + 2] = S.bg[2];
-        }
-    }
-
-    apply_ops<PX_PER_THREAD>(v, sops, S.n_pre, S.n_ops);
-
-    if (PLANAR) {
 #pragma unroll
-        for (int c = 0; c < 3; ++c) {
-            float4* d = reinterpret_cast<float4*>(P.dst + (size_t)c * P.dst_cstride + (size_t)y * P.dst_pitch +
-                                                  (size_t)x0 * 4);
-            *d = make_float4(v[c], v[3 + c], v[6 + c], v[9 + c]);
+            for (int i = 0; i < PX_PER_THREAD; ++i) { v[3 * i + 0] = bgv[0]; v[3 * i + 1] = bgv[1]; v[3 * i + 2] = bgv[2]; }
         }
-    } else {
-        float4* d = reinterpret_cast<float4*>(P.dst + (size_t)y * P.dst_pitch + (size_t)x0 * 12);
+
+        if (PLANAR) {
 #pragma unroll
-        for (int k = 0; k < 3; ++k) d[k] = make_float4(v[4 * k + 0], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
+            for (int c = 0; c < 3; ++c) {
+                float4* d = reinterpret_cast<float4*>(P.dst + (size_t)c * P.dst_cstride + (size_t)y * P.dst_pitch +
+                                                      (size_t)x0 * 4);
+                *d = make_float4(v[c], v[3 + c], v[6 + c], v[9 + c]);
+            }
+        } else {
+            float4* d = reinterpret_cast<float4*>(P.dst + (size_t)y * P.dst_pitch + (size_t)x0 * 12);
+#pragma unroll
+            for (int k = 0; k < 3; ++k) d[k] = make_float4(v[4 * k + 0], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
+        }
     }
 }
 

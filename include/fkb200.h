@@ -151,6 +151,8 @@ typedef struct fkb_plan_info {
     uint64_t output_pixels;
     uint64_t algorithmic_bytes;  /* source bytes inside the crop rects + output bytes          */
     uint64_t device_bytes;       /* device memory held by the plan's descriptors               */
+    int32_t n_constant_divisions;/* Div operations lowered to the proven reciprocal form       */
+    int32_t n_ieee_divisions;    /* Div operations kept as IEEE division                       */
 } fkb_plan_info;
 
 typedef struct fkb_plan fkb_plan; /* opaque; owns only its own descriptor memory */
@@ -186,6 +188,11 @@ FKB_API int fkb_reference_block_size(uint32_t active_x, uint32_t active_y, uint3
  * points to may be released as soon as the call returns; image memory must stay valid
  * until the launches that use it have finished. */
 FKB_API int fkb_plan_create(const fkb_plan_desc* desc, fkb_plan** out_plan);
+
+/* The host half of fkb_plan_create alone: validates and lowers a description and reports what
+ * the plan would launch, without touching a device (pointers are checked for NULL and
+ * alignment only, never dereferenced). */
+FKB_API int fkb_plan_validate(const fkb_plan_desc* desc, fkb_plan_info* out_info);
 
 /* Replaces launchTransformDPP_Kernel<<<grid, block, 0, stream>>> (executors.h:267,270,284)
  * and, for plans with more than one sequence, launchDivergentBatchTransformDPP_Kernel

@@ -18,7 +18,7 @@ GOLD = Path(__file__).resolve().parent / "golden"
 def test_every_declared_symbol_is_exported(fkb_lib):
     header = (ROOT / "include" / "fkb200.h").read_text()
     declared = sorted(set(re.findall(r"FKB_API\s+[\w\s\*]+?\b(fkb_\w+)\s*\(", header)))
-    assert len(declared) >= 16
+    assert len(declared) >= 17
     for name in declared:
         assert hasattr(fkb_lib, name), f"{name} declared in fkb200.h but not exported"
     assert sorted(abi.EXPORTS) == declared
@@ -32,7 +32,7 @@ def test_struct_sizes_match_header():
     assert C.sizeof(abi.Plane) == 72
     assert C.sizeof(abi.PlanDesc) == 32
     assert C.sizeof(abi.ResizeParams) == 32
-    assert C.sizeof(abi.PlanInfo) == 48
+    assert C.sizeof(abi.PlanInfo) == 56
 
 
 def test_derive_resize_matches_golden_table(fkb_lib):
@@ -145,3 +145,40 @@ def test_no_device_means_error_not_fallback(fkb_lib):
 def test_missing_library_is_an_error(tmp_path):
     with pytest.raises(FileNotFoundError):
         abi.load_library(tmp_path / "libfkb200.so")
+
+
+def _c3_like_plan(src_format=abi.SRC_U8X3):
+    keep = np.zeros((64, 64 * 12), np.uint8)
+    out = np.zeros((2, 3, 224, 224), np.float32)
+    plan = chains.crop_resize_batch(frame_ptrs=[keep.ctypes.data], frame_index=[0, 0], rects=[(0, 0, 16, 16), (3, 5, 60, 40)],
+                                    src_width=64, src_height=64, src_pitch=64 * 3, dst=out.ctypes.data, dst_width=224,
+                                    dst_height=224, post_ops=chains.normalize_ops(), planar=True)
+    plan._keep = (keep, out)
+    return plan
+
+
+def test_divisions_by_plan_constants_are_lowered_only_when_proven(fkb_lib):
+    """Config 3's two divisions (255, then std) qualify for the reciprocal form; the same divisions on a
+    float source of unknown range, by a denormal, or after a multiplication by a negative number
+    (possible -0) must stay IEEE divisions."""
+    info = abi.validate(_c3_like_plan())
+    assert (info.n_constant_divisions, info.n_ieee_divisions) == (2, 0)
+    assert info.grid_x == 2 * 7  # 224x224 planes: 56 column groups x 4 row slots x 8 rows = 7 blocks each
+
+    src = np.zeros((8, 8, 3), np.float32)
+    out = np.zeros((8, 8, 3), np.float32)
+    unknown = chains.elementwise([op(abi.OP_DIV, 255.0)], src=src.ctypes.data, dst=out.ctypes.data, width=8, height=8,
+                                 src_format=abi.SRC_F32X3)
+    info = abi.validate(unknown)
+    assert (info.n_constant_divisions, info.n_ieee_divisions) == (0, 1)
+
+    u8 = np.zeros((8, 8, 3), np.uint8)
+    for ops, want in (([op(abi.OP_CAST_F32), op(abi.OP_DIV, 255.0)], (1, 0)),
+                      ([op(abi.OP_CAST_F32), op(abi.OP_DIV, 1e-39)], (0, 1)),
+                      ([op(abi.OP_CAST_F32), op(abi.OP_DIV, 3e7)], (0, 1)),
+                      ([op(abi.OP_CAST_F32), op(abi.OP_MUL, -2.0), op(abi.OP_DIV, 255.0)], (0, 1)),
+                      ([op(abi.OP_CAST_F32), op(abi.OP_DIV, -255.0), op(abi.OP_DIV, 3.0)], (1, 1)),
+                      ([op(abi.OP_CAST_F32), op(abi.OP_SUB, 1.0), op(abi.OP_DIV, (0.229, 0.224, 0.225))], (1, 0))):
+        plan = chains.elementwise(ops, src=u8.ctypes.data, dst=out.ctypes.data, width=8, height=8)
+        info = abi.validate(plan)
+        assert (info.n_constant_divisions, info.n_ieee_divisions) == want, ops
