@@ -94,6 +94,8 @@ class PlanInfo(C.Structure):
         ("device_bytes", C.c_uint64),
         ("n_constant_divisions", C.c_int32),
         ("n_ieee_divisions", C.c_int32),
+        ("compiled_chain", C.c_int32),
+        ("reserved", C.c_int32),
     ]
 
 
@@ -186,7 +188,7 @@ def load_library(path: os.PathLike | None = None) -> C.CDLL:
     global _lib
     if _lib is not None and path is None:
         return _lib
-    p = Path(path) if path else LIB_PATH
+    p = Path(path) if path else Path(os.environ.get("FKB200_LIBRARY", LIB_PATH))
     if not p.exists():
         raise FileNotFoundError(
             f"{p} not found: build it with `python -m fusedkernellibrary_b200.build` "

@@ -33,13 +33,19 @@ struct alignas(16) DevPlane {
     int32_t crop_x, crop_y, crop_w, crop_h;
     uint32_t dst_w, dst_h, dst_pitch, dst_cstride;
     float fx, fy;            /* resize.h:108-112: source step per output element              */
-    int32_t x1, y1, x2, y2;  /* PRESERVE_AR region of interest, inclusive (resize.h:150-158)  */
+    int32_t x1, y1, x2, y2;  /* region of interest, inclusive (resize.h:150-158); the whole   */
+                             /* output for IGNORE_AR                                          */
     uint32_t seq;
     uint32_t plane_class;
     uint32_t seg_pixels;     /* FLAT classes: pixels per contiguous segment                   */
     uint32_t n_segs;         /* FLAT classes: 1 (dense plane) or dst_h (one segment per row)  */
+    /* RESIZE classes: tiling of the region of interest (see ResizeTiling) */
+    uint32_t roi_items;      /* work items that interpolate; the rest fill background rows    */
+    uint32_t tiles_x;
+    uint32_t gw;
+    uint32_t rs;
 };
-static_assert(sizeof(DevPlane) == 96, "DevPlane layout");
+static_assert(sizeof(DevPlane) == 112, "DevPlane layout");
 
 struct alignas(16) DevOp {
     int32_t opcode;
@@ -62,7 +68,7 @@ enum PreKind : int32_t {
     PRE_GENERAL = 2   /* any other chain: interpreted per tap (generic class only)           */
 };
 
-/* Kernel argument block (passed by value; 64 bytes). */
+/* Kernel argument block (passed by value). */
 struct LaunchArgs {
     const DevPlane* planes;
     const DevSeq* seqs;
@@ -72,6 +78,8 @@ struct LaunchArgs {
     uint32_t uniform_items;     /* > 0: every plane has this many work items                  */
     uint32_t total_items;
     uint32_t max_seq_ops;       /* longest sequence: sizes the shared-memory op cache         */
+    uint32_t block_threads;     /* threads per block of this launch (multiple of 32, <= 256)  */
+    uint32_t pad[3];
 };
 
 constexpr int BLOCK_THREADS = 256;
@@ -83,29 +91,54 @@ constexpr int ITEM_PIXELS_GENERIC = BLOCK_THREADS;
  * has proven the three-instruction form exact.  Takes two op slots: {-p}, then {1/p}. */
 constexpr int32_t DEV_OP_DIV_BY_CONSTANT = 16;
 
-/* RESIZE classes: a thread owns one group of four adjacent output columns and walks
- * RESIZE_ROWS_PER_THREAD rows, so the horizontal taps and weights are computed once per
- * thread.  A block covers `gw` groups x (`rs` row slots * RESIZE_ROWS_PER_THREAD) rows. */
+/* RESIZE classes.  Only the region of interest [x1,x2] x [y1,y2] of a plane is interpolated;
+ * everything else receives one constant (the default value after the continuation).  Threads
+ * are therefore laid over the region of interest alone: a thread owns one group of four
+ * adjacent output columns and walks RESIZE_ROWS_PER_THREAD rows `rs` apart, so its horizontal
+ * taps and weights are computed once.  A block covers `gw` column groups x (rs *
+ * RESIZE_ROWS_PER_THREAD) rows and also fills the background to the left and right of its
+ * rows; rows above and below the region are filled by separate, store-only work items of
+ * BG_GROUPS_PER_ITEM column groups each. */
 constexpr int RESIZE_ROWS_PER_THREAD = 8;
+constexpr int BG_GROUPS_PER_THREAD = 8;
 
 struct ResizeTiling {
-    uint32_t gw;      /* column groups per block (<= BLOCK_THREADS)           */
-    uint32_t rs;      /* row slots per block: threads = gw * rs               */
-    uint32_t tiles_x; /* blocks across a row                                  */
-    uint32_t tiles_y; /* blocks down the plane                                */
+    uint32_t g_lo, n_groups; /* first column group touching the region, and how many do        */
+    uint32_t n_rows;         /* rows of the region                                             */
+    uint32_t gw;             /* column groups per block                                        */
+    uint32_t rs;             /* row slots per block: active threads = gw * rs                  */
+    uint32_t tiles_x, tiles_y;
+    uint32_t roi_items;      /* tiles_x * tiles_y                                              */
+    uint32_t bg_items;       /* store-only items for the rows outside the region               */
 };
 #if defined(__CUDACC__)
 __host__ __device__
 #endif
-inline ResizeTiling resize_tiling(uint32_t dst_w, uint32_t dst_h) {
+inline ResizeTiling resize_tiling(uint32_t dst_w, uint32_t dst_h, int x1, int y1, int x2, int y2,
+                                  uint32_t block_threads) {
     ResizeTiling t;
-    const uint32_t groups = dst_w / PX_PER_THREAD;
-    t.gw = groups < (uint32_t)BLOCK_THREADS ? groups : (uint32_t)BLOCK_THREADS;
-    t.rs = (uint32_t)BLOCK_THREADS / t.gw;
-    t.tiles_x = (groups + t.gw - 1) / t.gw;
+    t.g_lo = (uint32_t)x1 / PX_PER_THREAD;
+    t.n_groups = (uint32_t)x2 / PX_PER_THREAD - t.g_lo + 1;
+    t.n_rows = (uint32_t)(y2 - y1 + 1);
+    t.tiles_x = (t.n_groups + block_threads - 1) / block_threads;
+    t.gw = (t.n_groups + t.tiles_x - 1) / t.tiles_x;
+    t.rs = block_threads / t.gw;
     const uint32_t rows = t.rs * RESIZE_ROWS_PER_THREAD;
-    t.tiles_y = (dst_h + rows - 1) / rows;
+    t.tiles_y = (t.n_rows + rows - 1) / rows;
+    t.roi_items = t.tiles_x * t.tiles_y;
+    const uint64_t bg_groups = (uint64_t)(dst_h - t.n_rows) * (dst_w / PX_PER_THREAD);
+    const uint64_t per_item = (uint64_t)block_threads * BG_GROUPS_PER_THREAD;
+    t.bg_items = (uint32_t)((bg_groups + per_item - 1) / per_item);
     return t;
+}
+
+/* Compile-time operation chains.  A chain is a list of 4-bit operation codes, first operation
+ * in the lowest nibble, 0 terminates.  Kernels are instantiated for the chains in
+ * FKB_CHAIN_MENU; any other sequence runs through the interpreter (CHAIN_INTERPRET). */
+constexpr uint32_t CHAIN_INTERPRET = 0xFFFFFFFFu;
+constexpr uint32_t CH_MUL = 1, CH_SUB = 2, CH_DIV = 3, CH_ADD = 4, CH_SWAP = 6, CH_SAT = 7, CH_YUV = 8, CH_DIVC = 9;
+constexpr uint32_t chain_of(uint32_t a = 0, uint32_t b = 0, uint32_t c = 0, uint32_t d = 0, uint32_t e = 0) {
+    return a | (b << 4) | (c << 8) | (d << 12) | (e << 16);
 }
 
 }  // namespace fkb

@@ -21,7 +21,8 @@
 #include "fkb_device.h"
 
 namespace fkb {
-cudaError_t launch_plan_kernel(uint32_t launch_class, const LaunchArgs& a, cudaStream_t stream);
+cudaError_t launch_plan_kernel(uint32_t launch_class, uint32_t chain, const LaunchArgs& a, cudaStream_t stream);
+bool chain_is_compiled(uint32_t chain);
 }
 
 using namespace fkb;
@@ -58,6 +59,7 @@ struct fkb_plan {
     size_t d_bytes = 0;
     LaunchArgs args{};
     uint32_t launch_class = CLASS_GENERIC;
+    uint32_t chain = CHAIN_INTERPRET;
     std::vector<fkb_resize_params> resize;
     fkb_plan_info info{};
 };
@@ -70,6 +72,8 @@ struct HostImage {
     std::vector<uint32_t> item_start;
     std::vector<fkb_resize_params> resize;
     uint32_t launch_class = CLASS_GENERIC;
+    uint32_t chain = CHAIN_INTERPRET;   /* compiled chain shared by every sequence, or CHAIN_INTERPRET */
+    uint32_t block_threads = BLOCK_THREADS;
     uint32_t uniform_items = 0;
     uint32_t total_items = 0;
     uint32_t max_seq_ops = 0;
@@ -99,6 +103,7 @@ struct HostImage {
         a.uniform_items = uniform_items;
         a.total_items = total_items;
         a.max_seq_ops = max_seq_ops;
+        a.block_threads = block_threads;
         return a;
     }
 };
@@ -321,19 +326,45 @@ static void advance_range_resize(ValueRange& v, int step_exp_x, int step_exp_y, 
 }
 
 /* Device form of a sequence's operations. */
-static void lower_ops(const fkb_sequence& s, int n_pre, int step_exp_x, int step_exp_y, std::vector<DevOp>& out,
-                      int& dev_n_pre) {
+static uint32_t chain_code_of(int dev_opcode) {
+    switch (dev_opcode) {
+        case FKB_OP_MUL: return CH_MUL;
+        case FKB_OP_SUB: return CH_SUB;
+        case FKB_OP_DIV: return CH_DIV;
+        case FKB_OP_ADD: return CH_ADD;
+        case FKB_OP_SWAP_RB: return CH_SWAP;
+        case FKB_OP_SATURATE_CAST_U8: return CH_SAT;
+        case FKB_OP_YUV_TO_RGB_BT709_FULL: return CH_YUV;
+        case DEV_OP_DIV_BY_CONSTANT: return CH_DIVC;
+        default: return 0;
+    }
+}
+
+/* Lowers one sequence into `out`; Cast<uchar3,float3> is exact on values already held as float and
+   leaves no device operation.  Returns the chain code of the operations after the geometry stage
+   (CHAIN_INTERPRET when it does not fit eight nibbles). */
+static uint32_t lower_ops(const fkb_sequence& s, int n_pre, int step_exp_x, int step_exp_y, std::vector<DevOp>& out,
+                          int& dev_n_pre) {
     ValueRange v;
     if (s.src_format != FKB_SRC_F32X3) v = ValueRange{true, 255.0, 0, 0, true, false};
-    dev_n_pre = 0;
+    dev_n_pre = (int)out.size();
+    uint32_t chain = 0;
+    int chain_len = 0;
     for (int k = 0; k <= s.n_ops; ++k) {
         if (k == n_pre && s.resize_mode != FKB_RESIZE_NONE) {
             advance_range_resize(v, step_exp_x, step_exp_y, s.resize_mode == FKB_RESIZE_PRESERVE_AR, s.background);
             dev_n_pre = (int)out.size();
+            chain = 0; chain_len = 0;
         }
         if (k == s.n_ops) break;
         const fkb_op& op = s.ops[k];
         const bool fast = advance_range(v, op);
+        if (op.opcode == FKB_OP_CAST_F32) continue;
+        {
+            const uint32_t code = chain_code_of(op.opcode == FKB_OP_DIV && fast ? DEV_OP_DIV_BY_CONSTANT : op.opcode);
+            if (chain_len < 8 && chain != CHAIN_INTERPRET) chain |= code << (4 * chain_len++);
+            else chain = CHAIN_INTERPRET;
+        }
         DevOp o;
         o.opcode = op.opcode; o.p[0] = op.p[0]; o.p[1] = op.p[1]; o.p[2] = op.p[2];
         if (op.opcode == FKB_OP_DIV && fast) {
@@ -347,6 +378,7 @@ static void lower_ops(const fkb_sequence& s, int n_pre, int step_exp_x, int step
             out.push_back(o);
         }
     }
+    return chain;
 }
 
 /* ------------------------------------------------------------------------------------ */
@@ -434,8 +466,8 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
     img.resize.assign(d->n_planes, fkb_resize_params{});
     img.item_start.assign((size_t)d->n_planes + 1, 0);
     uint64_t total = 0;
-    bool uniform = true;
-    uint32_t first_items = 0;
+    bool uniform = true, same_groups = false;
+    uint32_t first_items = 0, first_groups = 0;
     uint32_t common_class = CLASS_MIXED;
     for (int i = 0; i < d->n_planes; ++i) {
         const fkb_plane& p = d->planes[i];
@@ -510,8 +542,11 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
             else if (s.src_format == FKB_SRC_U8X3 && s.dst_format == FKB_DST_F32X3_PACKED) cls = CLASS_RESIZE_U8_PACKED;
             else if (s.src_format == FKB_SRC_NV12 && s.dst_format == FKB_DST_F32X3_PACKED) cls = CLASS_RESIZE_NV12_PACKED;
             if (cls != CLASS_GENERIC) {
-                const ResizeTiling t = resize_tiling(p.dst_width, p.dst_height);
-                items = (uint64_t)t.tiles_x * t.tiles_y;
+                const ResizeTiling t = resize_tiling(p.dst_width, p.dst_height, dp.x1, dp.y1, dp.x2, dp.y2, BLOCK_THREADS);
+                items = (uint64_t)t.roi_items + t.bg_items;
+                dp.roi_items = t.roi_items; dp.tiles_x = t.tiles_x; dp.gw = t.gw; dp.rs = t.rs;
+                if (i == 0) { first_groups = t.n_groups; same_groups = true; }
+                else if (t.n_groups != first_groups) same_groups = false;
             }
         }
         if (cls == CLASS_GENERIC) items = (out_px + ITEM_PIXELS_GENERIC - 1) / ITEM_PIXELS_GENERIC;
@@ -529,11 +564,14 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
         const uint64_t crop_px = (uint64_t)p.crop_width * p.crop_height;
         img.algorithmic_bytes += (s.src_format == FKB_SRC_NV12 ? crop_px + crop_px / 2 : crop_px * spx) + out_px * (s.dst_format == FKB_DST_F32_PLANAR3 ? 12 : dpx);
     }
+    uint32_t common_chain = 0;
     for (int s = 0; s < d->n_sequences; ++s) {
         DevSeq& ds = img.seqs[s];
         const size_t begin = img.ops.size();
         int dev_n_pre = 0;
-        lower_ops(d->sequences[s], ds.n_pre, step_exp_x[s], step_exp_y[s], img.ops, dev_n_pre);
+        const uint32_t chain = lower_ops(d->sequences[s], ds.n_pre, step_exp_x[s], step_exp_y[s], img.ops, dev_n_pre);
+        if (s == 0) common_chain = chain;
+        else if (chain != common_chain) common_chain = CHAIN_INTERPRET;
         ds.ops_begin = (int32_t)begin;
         ds.n_ops = (int32_t)(img.ops.size() - begin);
         ds.n_pre = dev_n_pre - (int32_t)begin;
@@ -547,6 +585,33 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
     img.total_items = (uint32_t)total;
     img.uniform_items = uniform ? first_items : 0;
     img.launch_class = common_class;
+    img.chain = (common_class != CLASS_MIXED && common_class != CLASS_GENERIC && chain_is_compiled(common_chain))
+                    ? common_chain : CHAIN_INTERPRET;
+    /* A plan whose planes all have the same region width can run with exactly as many threads per
+       block as its tiling keeps busy. */
+    const bool resize_class = common_class == CLASS_RESIZE_U8_PLANAR || common_class == CLASS_RESIZE_U8_PACKED ||
+                              common_class == CLASS_RESIZE_NV12_PACKED;
+    if (resize_class && same_groups) {
+        const DevPlane& p0 = img.planes[0];
+        const uint32_t busy = p0.gw * p0.rs;
+        const uint32_t threads = (busy + 31) / 32 * 32;
+        if (threads < (uint32_t)BLOCK_THREADS) {
+            uint64_t t2 = 0;
+            for (size_t i = 0; i < img.planes.size(); ++i) {
+                DevPlane& dp = img.planes[i];
+                const ResizeTiling t = resize_tiling(dp.dst_w, dp.dst_h, dp.x1, dp.y1, dp.x2, dp.y2, threads);
+                dp.roi_items = t.roi_items; dp.tiles_x = t.tiles_x; dp.gw = t.gw; dp.rs = t.rs;
+                img.item_start[i] = (uint32_t)t2;
+                t2 += (uint64_t)t.roi_items + t.bg_items;
+                if (i == 0) first_items = t.roi_items + t.bg_items;
+                else if (t.roi_items + t.bg_items != first_items) uniform = false;
+            }
+            img.item_start[img.planes.size()] = (uint32_t)t2;
+            img.total_items = (uint32_t)t2;
+            img.uniform_items = uniform ? first_items : 0;
+            img.block_threads = threads;
+        }
+    }
     return FKB_OK;
 }
 
@@ -587,7 +652,8 @@ static fkb_plan_info info_of(const HostImage& img) {
     info.n_sequences = (int32_t)img.seqs.size();
     info.n_launches = 1;
     info.grid_x = img.total_items;
-    info.block_x = BLOCK_THREADS;
+    info.block_x = img.block_threads;
+    info.compiled_chain = img.chain != CHAIN_INTERPRET;
     info.output_pixels = img.output_pixels;
     info.algorithmic_bytes = img.algorithmic_bytes;
     info.device_bytes = img.bytes();
@@ -629,6 +695,7 @@ extern "C" FKB_API int fkb_plan_create(const fkb_plan_desc* desc, fkb_plan** out
     }
     plan->args = img.args_for(static_cast<const unsigned char*>(plan->d_block));
     plan->launch_class = img.launch_class;
+    plan->chain = img.chain;
     plan->resize = std::move(img.resize);
     plan->info = info_of(img);
     *out_plan = plan;
@@ -637,7 +704,7 @@ extern "C" FKB_API int fkb_plan_create(const fkb_plan_desc* desc, fkb_plan** out
 
 extern "C" FKB_API int fkb_plan_launch(const fkb_plan* plan, void* stream) {
     if (!plan) return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_plan_launch: plan is NULL");
-    const cudaError_t e = launch_plan_kernel(plan->launch_class, plan->args, static_cast<cudaStream_t>(stream));
+    const cudaError_t e = launch_plan_kernel(plan->launch_class, plan->chain, plan->args, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return fail_cuda(e, "kernel launch", __LINE__);
     return FKB_OK;
 }

@@ -7,10 +7,15 @@
  * horizontal fusion, data_parallel_patterns.h:315-323) is launched with a block-uniform
  * switch over the bodies.
  *
+ * The element-wise continuation of a chain is either one of a menu of chains compiled into
+ * the kernel (the reference compiles every chain, data_parallel_patterns.h:75-88) or, for
+ * any other sequence, interpreted from the operation table with a block-uniform switch.
+ *
  * Arithmetic follows the reference's per-thread function exactly (execute_thread,
  * data_parallel_patterns.h:153-181): IEEE binary32, round to nearest even, no fused
- * multiply-add, true division; every operation is spelled with the __f*_rn intrinsics so
- * that compiler flags cannot change the rounding.
+ * multiply-add except inside the proven constant division, true division otherwise; every
+ * operation is spelled with the __f*_rn intrinsics so that compiler flags cannot change the
+ * rounding.
  */
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -32,10 +37,9 @@ __device__ __forceinline__ float saturate_round_u8(float f) {
     return (float)__float2int_rz(__fadd_rn(f, 0.5f));
 }
 
-/* Exact uchar -> float without the conversion unit: 2^23 + b has b in its low mantissa bits. */
-__device__ __forceinline__ float u8_to_float(uint32_t b) {
-    return __fsub_rn(__uint_as_float(b | 0x4B000000u), 8388608.0f);
-}
+/* Exact uchar -> float.  Converting from a 32-bit integer (not from an 8-bit one) keeps the
+   conversion off the quarter-rate conversion unit. */
+__device__ __forceinline__ float u8_to_float(uint32_t b) { return __int2float_rn((int)b); }
 
 /* Byte LANE of a packed word, as float: one byte permute builds 2^23 + b, one add removes 2^23. */
 template <int LANE>
@@ -47,8 +51,8 @@ __device__ __forceinline__ float packed_u8_to_float(uint32_t w) {
  *     q0 = RN(x*r);  e = x - p*q0 (exact, one FMA);  q = RN(q0 + e*r)
  * The host emits this form only for divisors for which it has checked the sequence against
  * IEEE division on all 2^23 significands of x, and only where it has shown that x stays in
- * the range in which scaling by powers of two is exact (see prove_fast_division in
- * fkb_host.cu).  np is -p. */
+ * the range in which scaling by powers of two is exact (constant_division_is_exact and
+ * advance_range in fkb_host.cu).  np is -p. */
 __device__ __forceinline__ float div_by_constant(float x, float np, float r) {
     const float q0 = __fmul_rn(x, r);
     const float e = __fmaf_rn(np, q0, x);
@@ -64,78 +68,76 @@ __device__ __forceinline__ void yuv_to_rgb_bt709_full(float& a, float& b, float&
     c = __fmul_rn(__fadd_rn(__fadd_rn(__fmul_rn(y, 1.0f), __fmul_rn(u, 1.8556f)), __fmul_rn(v, 0.0f)), 1.0f);
 }
 
-/* Runs ops [begin, end) of a sequence (cached in shared memory) on NPX whole pixels held in
- * registers as v[3*i + channel].  The opcode is uniform across the block, so the switch
- * never diverges; its cost is shared by 3*NPX values. */
+/* One operation on NPX whole pixels held as v[3*i + channel]; o carries the per-channel
+   parameter in y, z, w; r is the second slot of a two-slot operation. */
+template <int CODE, int NPX>
+__device__ __forceinline__ void apply_one(float (&v)[NPX * 3], const float4 o, const float4 r) {
+#pragma unroll
+    for (int i = 0; i < NPX; ++i) {
+        float& a = v[3 * i + 0];
+        float& b = v[3 * i + 1];
+        float& c = v[3 * i + 2];
+        if (CODE == CH_MUL) { a = __fmul_rn(a, o.y); b = __fmul_rn(b, o.z); c = __fmul_rn(c, o.w); }
+        else if (CODE == CH_SUB) { a = __fsub_rn(a, o.y); b = __fsub_rn(b, o.z); c = __fsub_rn(c, o.w); }
+        else if (CODE == CH_DIV) { a = __fdiv_rn(a, o.y); b = __fdiv_rn(b, o.z); c = __fdiv_rn(c, o.w); }
+        else if (CODE == CH_ADD) { a = __fadd_rn(a, o.y); b = __fadd_rn(b, o.z); c = __fadd_rn(c, o.w); }
+        else if (CODE == CH_DIVC) {
+            a = div_by_constant(a, o.y, r.y); b = div_by_constant(b, o.z, r.z); c = div_by_constant(c, o.w, r.w);
+        } else if (CODE == CH_SWAP) { const float t = a; a = c; c = t; }
+        else if (CODE == CH_SAT) { a = saturate_round_u8(a); b = saturate_round_u8(b); c = saturate_round_u8(c); }
+        else if (CODE == CH_YUV) { yuv_to_rgb_bt709_full(a, b, c); }
+    }
+}
+
+/* Interpreter: runs ops [begin, end) of a sequence cached in shared memory.  The opcode is
+ * uniform across the block, so the switch never diverges. */
 template <int NPX>
-__device__ __forceinline__ void apply_ops(float (&v)[NPX * 3], const DevOp* __restrict__ sops, int begin, int end) {
+__device__ __forceinline__ void interpret_ops(float (&v)[NPX * 3], const DevOp* __restrict__ sops, int begin, int end) {
     for (int k = begin; k < end; ++k) {
         const float4 o = *reinterpret_cast<const float4*>(&sops[k]);
-        const int opcode = __float_as_int(o.x);
-        switch (opcode) {
-            case FKB_OP_MUL:
-#pragma unroll
-                for (int i = 0; i < NPX; ++i) {
-                    v[3 * i + 0] = __fmul_rn(v[3 * i + 0], o.y);
-                    v[3 * i + 1] = __fmul_rn(v[3 * i + 1], o.z);
-                    v[3 * i + 2] = __fmul_rn(v[3 * i + 2], o.w);
-                }
-                break;
-            case FKB_OP_SUB:
-#pragma unroll
-                for (int i = 0; i < NPX; ++i) {
-                    v[3 * i + 0] = __fsub_rn(v[3 * i + 0], o.y);
-                    v[3 * i + 1] = __fsub_rn(v[3 * i + 1], o.z);
-                    v[3 * i + 2] = __fsub_rn(v[3 * i + 2], o.w);
-                }
-                break;
-            case FKB_OP_DIV:
-#pragma unroll
-                for (int i = 0; i < NPX; ++i) {
-                    v[3 * i + 0] = __fdiv_rn(v[3 * i + 0], o.y);
-                    v[3 * i + 1] = __fdiv_rn(v[3 * i + 1], o.z);
-                    v[3 * i + 2] = __fdiv_rn(v[3 * i + 2], o.w);
-                }
-                break;
-            case FKB_OP_ADD:
-#pragma unroll
-                for (int i = 0; i < NPX; ++i) {
-                    v[3 * i + 0] = __fadd_rn(v[3 * i + 0], o.y);
-                    v[3 * i + 1] = __fadd_rn(v[3 * i + 1], o.z);
-                    v[3 * i + 2] = __fadd_rn(v[3 * i + 2], o.w);
-                }
-                break;
-            case DEV_OP_DIV_BY_CONSTANT: { /* two slots: {-p}, {1/p} */
-                const float4 r = *reinterpret_cast<const float4*>(&sops[k + 1]);
+        const float4 none = make_float4(0.f, 0.f, 0.f, 0.f);
+        switch (__float_as_int(o.x)) {
+            case FKB_OP_MUL: apply_one<CH_MUL, NPX>(v, o, none); break;
+            case FKB_OP_SUB: apply_one<CH_SUB, NPX>(v, o, none); break;
+            case FKB_OP_DIV: apply_one<CH_DIV, NPX>(v, o, none); break;
+            case FKB_OP_ADD: apply_one<CH_ADD, NPX>(v, o, none); break;
+            case DEV_OP_DIV_BY_CONSTANT: /* two slots: {-p}, {1/p} */
+                apply_one<CH_DIVC, NPX>(v, o, *reinterpret_cast<const float4*>(&sops[k + 1]));
                 ++k;
-#pragma unroll
-                for (int i = 0; i < NPX; ++i) {
-                    v[3 * i + 0] = div_by_constant(v[3 * i + 0], o.y, r.y);
-                    v[3 * i + 1] = div_by_constant(v[3 * i + 1], o.z, r.z);
-                    v[3 * i + 2] = div_by_constant(v[3 * i + 2], o.w, r.w);
-                }
                 break;
-            }
-            case FKB_OP_SWAP_RB:
-#pragma unroll
-                for (int i = 0; i < NPX; ++i) {
-                    const float t = v[3 * i + 0];
-                    v[3 * i + 0] = v[3 * i + 2];
-                    v[3 * i + 2] = t;
-                }
-                break;
-            case FKB_OP_SATURATE_CAST_U8:
-#pragma unroll
-                for (int i = 0; i < NPX * 3; ++i) v[i] = saturate_round_u8(v[i]);
-                break;
-            case FKB_OP_YUV_TO_RGB_BT709_FULL:
-#pragma unroll
-                for (int i = 0; i < NPX; ++i) yuv_to_rgb_bt709_full(v[3 * i + 0], v[3 * i + 1], v[3 * i + 2]);
-                break;
-            default: /* FKB_OP_CAST_F32: uchar -> float is exact, values are already float */
-                break;
+            case FKB_OP_SWAP_RB: apply_one<CH_SWAP, NPX>(v, o, none); break;
+            case FKB_OP_SATURATE_CAST_U8: apply_one<CH_SAT, NPX>(v, o, none); break;
+            case FKB_OP_YUV_TO_RGB_BT709_FULL: apply_one<CH_YUV, NPX>(v, o, none); break;
+            default: break;
         }
     }
+}
+
+/* A chain fixed at compile time: operation codes in the nibbles of CHAIN, parameters taken
+   from consecutive slots of the cached operation table starting at `slot`. */
+template <uint32_t CHAIN, int NPX>
+__device__ __forceinline__ void apply_chain(float (&v)[NPX * 3], const DevOp* __restrict__ sops, int slot) {
+    constexpr uint32_t CODE = CHAIN & 0xFu;
+    if constexpr (CODE != 0) {
+        const float4 none = make_float4(0.f, 0.f, 0.f, 0.f);
+        if constexpr (CODE == CH_SWAP || CODE == CH_SAT || CODE == CH_YUV) {
+            apply_one<CODE, NPX>(v, none, none);
+            apply_chain<(CHAIN >> 4), NPX>(v, sops, slot + 1);
+        } else if constexpr (CODE == CH_DIVC) {
+            apply_one<CODE, NPX>(v, *reinterpret_cast<const float4*>(&sops[slot]),
+                                 *reinterpret_cast<const float4*>(&sops[slot + 1]));
+            apply_chain<(CHAIN >> 4), NPX>(v, sops, slot + 2);
+        } else {
+            apply_one<CODE, NPX>(v, *reinterpret_cast<const float4*>(&sops[slot]), none);
+            apply_chain<(CHAIN >> 4), NPX>(v, sops, slot + 1);
+        }
+    }
+}
+
+template <uint32_t CHAIN, int NPX>
+__device__ __forceinline__ void run_ops(float (&v)[NPX * 3], const DevOp* __restrict__ sops, int begin, int end) {
+    if constexpr (CHAIN == CHAIN_INTERPRET) interpret_ops<NPX>(v, sops, begin, end);
+    else apply_chain<CHAIN, NPX>(v, sops, begin);
 }
 
 /* ------------------------------------------------------------------------------------ */
@@ -208,7 +210,7 @@ __device__ __forceinline__ void body_generic(const DevPlane& P, const DevSeq& S,
     } else {
         first_post = S.n_pre;
         /* Resize::exec (resize.h:75-87): outside the region of interest return the default */
-        if (S.resize_mode == FKB_RESIZE_PRESERVE_AR && !(x >= P.x1 && x <= P.x2 && y >= P.y1 && y <= P.y2)) {
+        if (!(x >= P.x1 && x <= P.x2 && y >= P.y1 && y <= P.y2)) {
             v[0] = S.bg[0]; v[1] = S.bg[1]; v[2] = S.bg[2];
         } else {
             const Axis ax = make_axis(x - P.x1, P.fx, P.crop_w);
@@ -220,7 +222,7 @@ __device__ __forceinline__ void body_generic(const DevPlane& P, const DevSeq& S,
             read_tap_any(S.src_format, P, ax.i1, ay.i1, t[3][0], t[3][1], t[3][2]);
             if (S.pre_kind != PRE_IDENTITY) {
 #pragma unroll
-                for (int k = 0; k < 4; ++k) apply_ops<1>(t[k], sops, 0, S.n_pre);
+                for (int k = 0; k < 4; ++k) interpret_ops<1>(t[k], sops, 0, S.n_pre);
             }
             const float w00 = __fmul_rn(ax.w0, ay.w0), w10 = __fmul_rn(ax.w1, ay.w0);
             const float w01 = __fmul_rn(ax.w0, ay.w1), w11 = __fmul_rn(ax.w1, ay.w1);
@@ -228,7 +230,7 @@ __device__ __forceinline__ void body_generic(const DevPlane& P, const DevSeq& S,
             for (int c = 0; c < 3; ++c) v[c] = blend(t[0][c], t[1][c], t[2][c], t[3][c], w00, w10, w01, w11);
         }
     }
-    apply_ops<1>(v, sops, first_post, S.n_ops);
+    interpret_ops<1>(v, sops, first_post, S.n_ops);
     /* receivers: memory_operations.h:122-127 (PerThreadWrite), :181-184 (TensorWrite),
        :203-219 (TensorSplit) */
     if (S.dst_format == FKB_DST_F32X3_PACKED) {
@@ -249,7 +251,7 @@ __device__ __forceinline__ void body_generic(const DevPlane& P, const DevSeq& S,
 /* ------------------------------------------------------------------------------------ */
 /* body: no geometry stage, four whole pixels per thread                                */
 /* ------------------------------------------------------------------------------------ */
-template <bool SRC_IS_U8, bool DST_IS_U8>
+template <uint32_t CHAIN, bool SRC_IS_U8, bool DST_IS_U8>
 __device__ __forceinline__ void body_flat(const DevPlane& P, const DevSeq& S, const DevOp* sops, uint32_t local) {
     constexpr int SPX = SRC_IS_U8 ? 3 : 12;
     constexpr int DPX = DST_IS_U8 ? 3 : 12;
@@ -286,12 +288,12 @@ __device__ __forceinline__ void body_flat(const DevPlane& P, const DevSeq& S, co
         for (int i = 0; i < 12; ++i) {
             v[i] = 0.0f;
             if (i < (int)n * 3) {
-                v[i] = SRC_IS_U8 ? (float)__ldg(src + i) : __ldg(reinterpret_cast<const float*>(src) + i);
+                v[i] = SRC_IS_U8 ? u8_to_float(__ldg(src + i)) : __ldg(reinterpret_cast<const float*>(src) + i);
             }
         }
     }
 
-    apply_ops<PX_PER_THREAD>(v, sops, 0, S.n_ops);
+    run_ops<CHAIN, PX_PER_THREAD>(v, sops, 0, S.n_ops);
 
     if (n == PX_PER_THREAD) {
         if (DST_IS_U8) {
@@ -318,98 +320,174 @@ __device__ __forceinline__ void body_flat(const DevPlane& P, const DevSeq& S, co
 }
 
 /* ------------------------------------------------------------------------------------ */
-/* body: bilinear resize, a 4-column group walked down several rows per thread          */
+/* body: bilinear resize                                                                */
 /* ------------------------------------------------------------------------------------ */
-template <int SRC, bool PLANAR>
+
+/* Stores one group of four output pixels (v[3*i + channel]) at column x0 of row y. */
+template <bool PLANAR>
+__device__ __forceinline__ void store_group(uint8_t* dst, uint32_t pitch, uint32_t cstride, int x0, int y,
+                                            const float (&v)[12]) {
+    if (PLANAR) {
+        uint8_t* d = dst + (size_t)y * pitch + (size_t)x0 * 4;
+#pragma unroll
+        for (int c = 0; c < 3; ++c) {
+            *reinterpret_cast<float4*>(d + (size_t)c * cstride) = make_float4(v[c], v[3 + c], v[6 + c], v[9 + c]);
+        }
+    } else {
+        float4* d = reinterpret_cast<float4*>(dst + (size_t)y * pitch + (size_t)x0 * 12);
+#pragma unroll
+        for (int k = 0; k < 3; ++k) d[k] = make_float4(v[4 * k + 0], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
+    }
+}
+
+template <uint32_t CHAIN, int SRC, bool PLANAR>
 __device__ __forceinline__ void body_resize(const DevPlane& P, const DevSeq& S, const DevOp* sops, uint32_t local) {
-    const ResizeTiling T = resize_tiling(P.dst_w, P.dst_h);
-    const uint32_t tile_y = local / T.tiles_x, tile_x = local - tile_y * T.tiles_x;
-    const uint32_t slot = threadIdx.x / T.gw, gi = threadIdx.x - slot * T.gw;
-    const uint32_t group = tile_x * T.gw + gi;
-    if (slot >= T.rs || group >= P.dst_w / PX_PER_THREAD) return;
-    const int x0 = group * PX_PER_THREAD;
-    const bool preserve = S.resize_mode == FKB_RESIZE_PRESERVE_AR;
+    /* plane fields used inside loops, copied out of shared memory once */
+    uint8_t* const dst = P.dst;
+    const uint32_t dst_pitch = P.dst_pitch, dst_cstride = P.dst_cstride, src_pitch = P.src_pitch;
+    const uint32_t groups_per_row = P.dst_w / PX_PER_THREAD;
+    const int x1 = P.x1, y1 = P.y1, x2 = P.x2, y2 = P.y2;
+    const uint32_t g_lo = (uint32_t)x1 / PX_PER_THREAD;
+    const uint32_t n_groups = (uint32_t)x2 / PX_PER_THREAD - g_lo + 1;
+    const uint32_t n_rows = (uint32_t)(y2 - y1 + 1);
+    const uint32_t nthreads = blockDim.x;
 
     /* The value every output element outside the region of interest ends up with: the
        default value run through the continuation (resize.h:84-86). */
     float bgv[3] = {S.bg[0], S.bg[1], S.bg[2]};
-    if (preserve) apply_ops<1>(bgv, sops, S.n_pre, S.n_ops);
-
-    /* horizontal taps and weights of the four columns, once per thread */
-    int xa0[PX_PER_THREAD], xa1[PX_PER_THREAD];
-    float wx0[PX_PER_THREAD], wx1[PX_PER_THREAD];
-    uint32_t inside = 0;
+    run_ops<CHAIN, 1>(bgv, sops, S.n_pre, S.n_ops);
+    float bg4[12];
 #pragma unroll
-    for (int i = 0; i < PX_PER_THREAD; ++i) {
-        const int x = x0 + i;
-        const bool in = !preserve || (x >= P.x1 && x <= P.x2);
-        const Axis ax = make_axis(in ? x - P.x1 : 0, P.fx, P.crop_w);
-        xa0[i] = ax.i0; xa1[i] = ax.i1; wx0[i] = ax.w0; wx1[i] = ax.w1;
-        inside |= (in ? 1u : 0u) << i;
-    }
-    const uint8_t* const src0 =
-        SRC == FKB_SRC_NV12 ? P.src : P.src + (size_t)P.crop_y * P.src_pitch + (size_t)P.crop_x * 3;
+    for (int i = 0; i < PX_PER_THREAD; ++i) { bg4[3 * i] = bgv[0]; bg4[3 * i + 1] = bgv[1]; bg4[3 * i + 2] = bgv[2]; }
 
-    const int y_first = tile_y * (T.rs * RESIZE_ROWS_PER_THREAD) + slot;
+    if (local >= P.roi_items) {
+        /* store-only item: rows above and below the region of interest */
+        const uint32_t total = (P.dst_h - n_rows) * groups_per_row;
+        uint32_t idx = (local - P.roi_items) * (nthreads * BG_GROUPS_PER_THREAD) + threadIdx.x;
 #pragma unroll 1
-    for (int j = 0; j < RESIZE_ROWS_PER_THREAD; ++j) {
-        const int y = y_first + j * (int)T.rs;
-        if (y >= (int)P.dst_h) break;
-        const bool row_inside = !preserve || (y >= P.y1 && y <= P.y2);
-        float v[12];
-        if (row_inside && inside != 0) {
-            const Axis ay = make_axis(y - P.y1, P.fy, P.crop_h);
+        for (int k = 0; k < BG_GROUPS_PER_THREAD; ++k, idx += nthreads) {
+            if (idx >= total) break;
+            const uint32_t r = idx / groups_per_row, g = idx - r * groups_per_row;
+            const int y = (int)r < y1 ? (int)r : (int)(r + n_rows);
+            store_group<PLANAR>(dst, dst_pitch, dst_cstride, (int)(g * PX_PER_THREAD), y, bg4);
+        }
+        return;
+    }
+
+    const uint32_t tiles_x = P.tiles_x, gw = P.gw, rs = P.rs;
+    const uint32_t tile_y = local / tiles_x, tile_x = local - tile_y * tiles_x;
+    const uint32_t slot = threadIdx.x / gw, gi = threadIdx.x - slot * gw;
+    const uint32_t g_in_roi = tile_x * gw + gi;
+    const int row0 = y1 + (int)(tile_y * rs * RESIZE_ROWS_PER_THREAD); /* first row of this tile */
+
+    if (slot < rs && g_in_roi < n_groups) {
+        const int x0 = (int)((g_lo + g_in_roi) * PX_PER_THREAD);
+        /* horizontal taps and weights of the four columns, once per thread */
+        uint32_t off0[PX_PER_THREAD], off1[PX_PER_THREAD]; /* U8X3: byte offsets in a source row; NV12: columns */
+        float wx0[PX_PER_THREAD], wx1[PX_PER_THREAD];
+        uint32_t inside = 0;
 #pragma unroll
-            for (int i = 0; i < PX_PER_THREAD; ++i) {
-                float t[4][3];
-                if (SRC == FKB_SRC_U8X3) {
-                    const uint8_t* r0 = src0 + (size_t)ay.i0 * P.src_pitch;
-                    const uint8_t* r1 = src0 + (size_t)ay.i1 * P.src_pitch;
-                    const uint8_t* p00 = r0 + xa0[i] * 3; const uint8_t* p10 = r0 + xa1[i] * 3;
-                    const uint8_t* p01 = r1 + xa0[i] * 3; const uint8_t* p11 = r1 + xa1[i] * 3;
-#pragma unroll
-                    for (int c = 0; c < 3; ++c) {
-                        t[0][c] = u8_to_float(__ldg(p00 + c)); t[1][c] = u8_to_float(__ldg(p10 + c));
-                        t[2][c] = u8_to_float(__ldg(p01 + c)); t[3][c] = u8_to_float(__ldg(p11 + c));
-                    }
-                } else {
-                    read_tap<SRC>(P, xa0[i], ay.i0, t[0][0], t[0][1], t[0][2]);
-                    read_tap<SRC>(P, xa1[i], ay.i0, t[1][0], t[1][1], t[1][2]);
-                    read_tap<SRC>(P, xa0[i], ay.i1, t[2][0], t[2][1], t[2][2]);
-                    read_tap<SRC>(P, xa1[i], ay.i1, t[3][0], t[3][1], t[3][2]);
-                    if (S.pre_kind == PRE_YUV_BT709) {
-#pragma unroll
-                        for (int k = 0; k < 4; ++k) yuv_to_rgb_bt709_full(t[k][0], t[k][1], t[k][2]);
-                    }
-                }
-                const float w00 = __fmul_rn(wx0[i], ay.w0), w10 = __fmul_rn(wx1[i], ay.w0);
-                const float w01 = __fmul_rn(wx0[i], ay.w1), w11 = __fmul_rn(wx1[i], ay.w1);
-#pragma unroll
-                for (int c = 0; c < 3; ++c) v[3 * i + c] = blend(t[0][c], t[1][c], t[2][c], t[3][c], w00, w10, w01, w11);
-            }
-            apply_ops<PX_PER_THREAD>(v, sops, S.n_pre, S.n_ops);
-            if (inside != 0xF) {
+        for (int i = 0; i < PX_PER_THREAD; ++i) {
+            const int x = x0 + i;
+            const bool in = (x >= x1 && x <= x2);
+            const Axis ax = make_axis(in ? x - x1 : 0, P.fx, P.crop_w);
+            if (SRC == FKB_SRC_NV12) { off0[i] = (uint32_t)(ax.i0 + P.crop_x); off1[i] = (uint32_t)(ax.i1 + P.crop_x); }
+            else { off0[i] = (uint32_t)ax.i0 * 3u; off1[i] = (uint32_t)ax.i1 * 3u; }
+            wx0[i] = ax.w0; wx1[i] = ax.w1;
+            inside |= (in ? 1u : 0u) << i;
+        }
+        const float fy = P.fy;
+        const int crop_h = P.crop_h, crop_y = P.crop_y;
+        const uint8_t* const src0 = SRC == FKB_SRC_NV12 ? P.src : P.src + (size_t)crop_y * src_pitch + (size_t)P.crop_x * 3;
+        const uint8_t* const chroma0 = P.src + (size_t)src_pitch * P.src_height;
+        const bool yuv = S.pre_kind == PRE_YUV_BT709;
+
+#pragma unroll 1
+        for (int j = 0; j < RESIZE_ROWS_PER_THREAD; ++j) {
+            const int y = row0 + (int)slot + j * (int)rs;
+            if (y > y2) break;
+            const Axis ay = make_axis(y - y1, fy, crop_h);
+            float v[12];
+            if (SRC == FKB_SRC_U8X3) {
+                const uint8_t* const r0 = src0 + (size_t)ay.i0 * src_pitch;
+                const uint8_t* const r1 = src0 + (size_t)ay.i1 * src_pitch;
 #pragma unroll
                 for (int i = 0; i < PX_PER_THREAD; ++i) {
-                    if (!((inside >> i) & 1u)) { v[3 * i + 0] = bgv[0]; v[3 * i + 1] = bgv[1]; v[3 * i + 2] = bgv[2]; }
+                    const uint8_t* p00 = r0 + off0[i]; const uint8_t* p10 = r0 + off1[i];
+                    const uint8_t* p01 = r1 + off0[i]; const uint8_t* p11 = r1 + off1[i];
+                    const float w00 = __fmul_rn(wx0[i], ay.w0), w10 = __fmul_rn(wx1[i], ay.w0);
+                    const float w01 = __fmul_rn(wx0[i], ay.w1), w11 = __fmul_rn(wx1[i], ay.w1);
+#pragma unroll
+                    for (int c = 0; c < 3; ++c) {
+                        v[3 * i + c] = blend(u8_to_float(__ldg(p00 + c)), u8_to_float(__ldg(p10 + c)),
+                                             u8_to_float(__ldg(p01 + c)), u8_to_float(__ldg(p11 + c)), w00, w10, w01, w11);
+                    }
+                }
+            } else {
+                /* NV12: luma at (x, y), chroma pair at (x>>1, y>>1) (color_conversion.h:329-346).  A tap
+                   whose weight is exactly zero contributes +-0 to the sum and is not fetched: the first
+                   term is never -0 here, so the sum is unchanged bit for bit. */
+                const int ya0 = ay.i0 + crop_y, ya1 = ay.i1 + crop_y;
+                const uint8_t* const l0 = src0 + (size_t)ya0 * src_pitch;
+                const uint8_t* const l1 = src0 + (size_t)ya1 * src_pitch;
+                const uint8_t* const c0 = chroma0 + (size_t)(ya0 >> 1) * src_pitch;
+                const uint8_t* const c1 = chroma0 + (size_t)(ya1 >> 1) * src_pitch;
+                const bool need_row1 = ay.w1 != 0.0f;
+#pragma unroll
+                for (int i = 0; i < PX_PER_THREAD; ++i) {
+                    const bool need_col1 = wx1[i] != 0.0f;
+                    const uint32_t xa = off0[i], xb = off1[i];
+                    const uint32_t ca = (xa >> 1) * 2u, cb = (xb >> 1) * 2u;
+                    float t[3];
+                    t[0] = u8_to_float(__ldg(l0 + xa)); t[1] = u8_to_float(__ldg(c0 + ca)); t[2] = u8_to_float(__ldg(c0 + ca + 1));
+                    if (yuv) yuv_to_rgb_bt709_full(t[0], t[1], t[2]);
+                    const float w00 = __fmul_rn(wx0[i], ay.w0);
+                    float acc[3] = {__fmul_rn(t[0], w00), __fmul_rn(t[1], w00), __fmul_rn(t[2], w00)};
+                    if (need_col1) {
+                        t[0] = u8_to_float(__ldg(l0 + xb)); t[1] = u8_to_float(__ldg(c0 + cb)); t[2] = u8_to_float(__ldg(c0 + cb + 1));
+                        if (yuv) yuv_to_rgb_bt709_full(t[0], t[1], t[2]);
+                        const float w10 = __fmul_rn(wx1[i], ay.w0);
+#pragma unroll
+                        for (int c = 0; c < 3; ++c) acc[c] = __fadd_rn(acc[c], __fmul_rn(t[c], w10));
+                    }
+                    if (need_row1) {
+                        t[0] = u8_to_float(__ldg(l1 + xa)); t[1] = u8_to_float(__ldg(c1 + ca)); t[2] = u8_to_float(__ldg(c1 + ca + 1));
+                        if (yuv) yuv_to_rgb_bt709_full(t[0], t[1], t[2]);
+                        const float w01 = __fmul_rn(wx0[i], ay.w1);
+#pragma unroll
+                        for (int c = 0; c < 3; ++c) acc[c] = __fadd_rn(acc[c], __fmul_rn(t[c], w01));
+                        if (need_col1) {
+                            t[0] = u8_to_float(__ldg(l1 + xb)); t[1] = u8_to_float(__ldg(c1 + cb)); t[2] = u8_to_float(__ldg(c1 + cb + 1));
+                            if (yuv) yuv_to_rgb_bt709_full(t[0], t[1], t[2]);
+                            const float w11 = __fmul_rn(wx1[i], ay.w1);
+#pragma unroll
+                            for (int c = 0; c < 3; ++c) acc[c] = __fadd_rn(acc[c], __fmul_rn(t[c], w11));
+                        }
+                    }
+                    v[3 * i] = acc[0]; v[3 * i + 1] = acc[1]; v[3 * i + 2] = acc[2];
                 }
             }
-        } else {
+            run_ops<CHAIN, PX_PER_THREAD>(v, sops, S.n_pre, S.n_ops);
+            if (inside != 0xFu) { /* a group straddling the edge of the region */
 #pragma unroll
-            for (int i = 0; i < PX_PER_THREAD; ++i) { v[3 * i + 0] = bgv[0]; v[3 * i + 1] = bgv[1]; v[3 * i + 2] = bgv[2]; }
-        }
-
-        if (PLANAR) {
-#pragma unroll
-            for (int c = 0; c < 3; ++c) {
-                float4* d = reinterpret_cast<float4*>(P.dst + (size_t)c * P.dst_cstride + (size_t)y * P.dst_pitch +
-                                                      (size_t)x0 * 4);
-                *d = make_float4(v[c], v[3 + c], v[6 + c], v[9 + c]);
+                for (int i = 0; i < PX_PER_THREAD; ++i) {
+                    if (!((inside >> i) & 1u)) { v[3 * i] = bgv[0]; v[3 * i + 1] = bgv[1]; v[3 * i + 2] = bgv[2]; }
+                }
             }
-        } else {
-            float4* d = reinterpret_cast<float4*>(P.dst + (size_t)y * P.dst_pitch + (size_t)x0 * 12);
-#pragma unroll
-            for (int k = 0; k < 3; ++k) d[k] = make_float4(v[4 * k + 0], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
+            store_group<PLANAR>(dst, dst_pitch, dst_cstride, x0, y, v);
+        }
+    }
+
+    /* background to the left and right of this tile's rows (first tile of a row band only) */
+    const uint32_t n_band = groups_per_row - n_groups;
+    if (tile_x == 0 && n_band != 0) {
+        const uint32_t rows_here = min(rs * RESIZE_ROWS_PER_THREAD, (uint32_t)(y2 - row0 + 1));
+        const uint32_t total = rows_here * n_band;
+#pragma unroll 1
+        for (uint32_t idx = threadIdx.x; idx < total; idx += nthreads) {
+            const uint32_t r = idx / n_band, b = idx - r * n_band;
+            const uint32_t g = b < g_lo ? b : b + n_groups;
+            store_group<PLANAR>(dst, dst_pitch, dst_cstride, (int)(g * PX_PER_THREAD), row0 + (int)r, bg4);
         }
     }
 }
@@ -417,22 +495,22 @@ __device__ __forceinline__ void body_resize(const DevPlane& P, const DevSeq& S, 
 /* ------------------------------------------------------------------------------------ */
 /* the kernel                                                                           */
 /* ------------------------------------------------------------------------------------ */
-template <uint32_t CLASS>
+template <uint32_t CLASS, uint32_t CHAIN>
 __device__ __forceinline__ void run_body(uint32_t cls, const DevPlane& P, const DevSeq& S, const DevOp* sops,
                                          uint32_t local) {
     if (CLASS != CLASS_MIXED) cls = CLASS;
     switch (cls) {
-        case CLASS_FLAT_U8_F32: body_flat<true, false>(P, S, sops, local); break;
-        case CLASS_FLAT_F32_F32: body_flat<false, false>(P, S, sops, local); break;
-        case CLASS_FLAT_U8_U8: body_flat<true, true>(P, S, sops, local); break;
-        case CLASS_RESIZE_U8_PLANAR: body_resize<FKB_SRC_U8X3, true>(P, S, sops, local); break;
-        case CLASS_RESIZE_U8_PACKED: body_resize<FKB_SRC_U8X3, false>(P, S, sops, local); break;
-        case CLASS_RESIZE_NV12_PACKED: body_resize<FKB_SRC_NV12, false>(P, S, sops, local); break;
+        case CLASS_FLAT_U8_F32: body_flat<CHAIN, true, false>(P, S, sops, local); break;
+        case CLASS_FLAT_F32_F32: body_flat<CHAIN, false, false>(P, S, sops, local); break;
+        case CLASS_FLAT_U8_U8: body_flat<CHAIN, true, true>(P, S, sops, local); break;
+        case CLASS_RESIZE_U8_PLANAR: body_resize<CHAIN, FKB_SRC_U8X3, true>(P, S, sops, local); break;
+        case CLASS_RESIZE_U8_PACKED: body_resize<CHAIN, FKB_SRC_U8X3, false>(P, S, sops, local); break;
+        case CLASS_RESIZE_NV12_PACKED: body_resize<CHAIN, FKB_SRC_NV12, false>(P, S, sops, local); break;
         default: body_generic(P, S, sops, local); break;
     }
 }
 
-template <uint32_t CLASS>
+template <uint32_t CLASS, uint32_t CHAIN>
 __global__ void __launch_bounds__(BLOCK_THREADS) fused_plan_kernel(const __grid_constant__ LaunchArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     DevOp* sops = reinterpret_cast<DevOp*>(smem_raw);
@@ -466,34 +544,66 @@ __global__ void __launch_bounds__(BLOCK_THREADS) fused_plan_kernel(const __grid_
     {
         const DevSeq* gs = a.seqs + seq;
         const int n_ops = __ldg(&gs->n_ops), begin = __ldg(&gs->ops_begin);
-        for (int k = threadIdx.x; k < n_ops; k += BLOCK_THREADS) {
+        for (int k = threadIdx.x; k < n_ops; k += blockDim.x) {
             reinterpret_cast<uint4*>(sops)[k] = __ldg(reinterpret_cast<const uint4*>(a.ops + begin + k));
         }
     }
     __syncthreads();
-    run_body<CLASS>(s_plane.plane_class, s_plane, s_seq, sops, local);
+    run_body<CLASS, CHAIN>(s_plane.plane_class, s_plane, s_seq, sops, local);
 }
 
 /* ------------------------------------------------------------------------------------ */
 /* launcher                                                                             */
 /* ------------------------------------------------------------------------------------ */
+
+/* Chains compiled into the kernels (codes of the operations after the geometry stage, in
+ * order).  Casts never reach the device table.  Anything else is interpreted. */
+#define FKB_CHAIN_MENU(X)                                                                                         \
+    X(chain_of())                                 /* no continuation (copy, Cast -> Resize)                    */ \
+    X(chain_of(CH_DIVC))                          /* Div                                                       */ \
+    X(chain_of(CH_DIVC, CH_SUB, CH_DIVC))         /* Div, Sub, Div: normalise with mean and std                */ \
+    X(chain_of(CH_MUL, CH_SUB, CH_DIVC, CH_SWAP)) /* Mul, Sub, Div, RGB2BGR                                    */ \
+    X(chain_of(CH_MUL, CH_SUB, CH_DIVC))          /* Mul, Sub, Div                                             */ \
+    X(chain_of(CH_MUL, CH_SUB))                   /* Mul, Sub                                                  */ \
+    X(chain_of(CH_ADD, CH_DIVC))                  /* Add, Div                                                  */ \
+    X(chain_of(CH_SWAP, CH_MUL, CH_SAT))          /* RGB2BGR, Mul, SaturateCast                                */
+
 template <uint32_t CLASS>
-static cudaError_t launch_one(const LaunchArgs& a, size_t smem, cudaStream_t stream) {
-    fused_plan_kernel<CLASS><<<a.total_items, BLOCK_THREADS, smem, stream>>>(a);
+static cudaError_t launch_class(uint32_t chain, const LaunchArgs& a, size_t smem, cudaStream_t stream) {
+#define FKB_LAUNCH_CASE(CH)                                                                  \
+    if (chain == (CH)) {                                                                     \
+        fused_plan_kernel<CLASS, (CH)><<<a.total_items, a.block_threads, smem, stream>>>(a); \
+        return cudaGetLastError();                                                           \
+    }
+    FKB_CHAIN_MENU(FKB_LAUNCH_CASE)
+#undef FKB_LAUNCH_CASE
+    fused_plan_kernel<CLASS, CHAIN_INTERPRET><<<a.total_items, a.block_threads, smem, stream>>>(a);
     return cudaGetLastError();
 }
 
-cudaError_t launch_plan_kernel(uint32_t launch_class, const LaunchArgs& a, cudaStream_t stream) {
+bool chain_is_compiled(uint32_t chain) {
+#define FKB_CHAIN_TEST(CH) if (chain == (CH)) return true;
+    FKB_CHAIN_MENU(FKB_CHAIN_TEST)
+#undef FKB_CHAIN_TEST
+    return false;
+}
+
+/* launch_class: one of CLASS_* or CLASS_MIXED; chain: a menu chain or CHAIN_INTERPRET. */
+cudaError_t launch_plan_kernel(uint32_t launch_cls, uint32_t chain, const LaunchArgs& a, cudaStream_t stream) {
     const size_t smem = (size_t)(a.max_seq_ops > 0 ? a.max_seq_ops : 1) * sizeof(DevOp);
-    switch (launch_class) {
-        case CLASS_GENERIC: return launch_one<CLASS_GENERIC>(a, smem, stream);
-        case CLASS_FLAT_U8_F32: return launch_one<CLASS_FLAT_U8_F32>(a, smem, stream);
-        case CLASS_FLAT_F32_F32: return launch_one<CLASS_FLAT_F32_F32>(a, smem, stream);
-        case CLASS_FLAT_U8_U8: return launch_one<CLASS_FLAT_U8_U8>(a, smem, stream);
-        case CLASS_RESIZE_U8_PLANAR: return launch_one<CLASS_RESIZE_U8_PLANAR>(a, smem, stream);
-        case CLASS_RESIZE_U8_PACKED: return launch_one<CLASS_RESIZE_U8_PACKED>(a, smem, stream);
-        case CLASS_RESIZE_NV12_PACKED: return launch_one<CLASS_RESIZE_NV12_PACKED>(a, smem, stream);
-        default: return launch_one<CLASS_MIXED>(a, smem, stream);
+    switch (launch_cls) {
+        case CLASS_FLAT_U8_F32: return launch_class<CLASS_FLAT_U8_F32>(chain, a, smem, stream);
+        case CLASS_FLAT_F32_F32: return launch_class<CLASS_FLAT_F32_F32>(chain, a, smem, stream);
+        case CLASS_FLAT_U8_U8: return launch_class<CLASS_FLAT_U8_U8>(chain, a, smem, stream);
+        case CLASS_RESIZE_U8_PLANAR: return launch_class<CLASS_RESIZE_U8_PLANAR>(chain, a, smem, stream);
+        case CLASS_RESIZE_U8_PACKED: return launch_class<CLASS_RESIZE_U8_PACKED>(chain, a, smem, stream);
+        case CLASS_RESIZE_NV12_PACKED: return launch_class<CLASS_RESIZE_NV12_PACKED>(chain, a, smem, stream);
+        case CLASS_GENERIC:
+            fused_plan_kernel<CLASS_GENERIC, CHAIN_INTERPRET><<<a.total_items, a.block_threads, smem, stream>>>(a);
+            return cudaGetLastError();
+        default:
+            fused_plan_kernel<CLASS_MIXED, CHAIN_INTERPRET><<<a.total_items, a.block_threads, smem, stream>>>(a);
+            return cudaGetLastError();
     }
 }
 

@@ -153,6 +153,9 @@ typedef struct fkb_plan_info {
     uint64_t device_bytes;       /* device memory held by the plan's descriptors               */
     int32_t n_constant_divisions;/* Div operations lowered to the proven reciprocal form       */
     int32_t n_ieee_divisions;    /* Div operations kept as IEEE division                       */
+    int32_t compiled_chain;      /* 1: the continuation is one of the chains compiled into the  */
+                                 /* kernels; 0: it is interpreted from the operation table      */
+    int32_t reserved;
 } fkb_plan_info;
 
 typedef struct fkb_plan fkb_plan; /* opaque; owns only its own descriptor memory */
