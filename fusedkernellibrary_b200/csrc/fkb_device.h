@@ -99,13 +99,20 @@ constexpr int32_t DEV_OP_DIV_BY_CONSTANT = 16;
  * RESIZE_ROWS_PER_THREAD) rows and also fills the background to the left and right of its
  * rows; rows above and below the region are filled by separate, store-only work items of
  * BG_GROUPS_PER_ITEM column groups each. */
-constexpr int RESIZE_ROWS_PER_THREAD = 8;
+#ifndef FKB_ROWS
+#define FKB_ROWS 8
+#endif
+constexpr int RESIZE_ROWS_PER_THREAD = FKB_ROWS;
+#ifndef FKB_RPX
+#define FKB_RPX 4
+#endif
+constexpr int RESIZE_PX = FKB_RPX; /* output columns per thread in the interpolating items */
 constexpr int BG_GROUPS_PER_THREAD = 8;
 
 struct ResizeTiling {
     uint32_t g_lo, n_groups; /* first column group touching the region, and how many do        */
     uint32_t n_rows;         /* rows of the region                                             */
-    uint32_t gw;             /* column groups per block                                        */
+    uint32_t gw;             /* threads across a block: each owns RESIZE_PX columns gw apart   */
     uint32_t rs;             /* row slots per block: active threads = gw * rs                  */
     uint32_t tiles_x, tiles_y;
     uint32_t roi_items;      /* tiles_x * tiles_y                                              */
@@ -120,8 +127,9 @@ inline ResizeTiling resize_tiling(uint32_t dst_w, uint32_t dst_h, int x1, int y1
     t.g_lo = (uint32_t)x1 / PX_PER_THREAD;
     t.n_groups = (uint32_t)x2 / PX_PER_THREAD - t.g_lo + 1;
     t.n_rows = (uint32_t)(y2 - y1 + 1);
-    t.tiles_x = (t.n_groups + block_threads - 1) / block_threads;
-    t.gw = (t.n_groups + t.tiles_x - 1) / t.tiles_x;
+    const uint32_t col_threads = (t.n_groups * PX_PER_THREAD + RESIZE_PX - 1) / RESIZE_PX;
+    t.tiles_x = (col_threads + block_threads - 1) / block_threads;
+    t.gw = (col_threads + t.tiles_x - 1) / t.tiles_x;
     t.rs = block_threads / t.gw;
     const uint32_t rows = t.rs * RESIZE_ROWS_PER_THREAD;
     t.tiles_y = (t.n_rows + rows - 1) / rows;

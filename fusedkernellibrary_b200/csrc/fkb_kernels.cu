@@ -340,6 +340,21 @@ __device__ __forceinline__ void store_group(uint8_t* dst, uint32_t pitch, uint32
     }
 }
 
+/* Stores one output pixel (three channels) at column x of row y. */
+template <bool PLANAR>
+__device__ __forceinline__ void store_pixel(uint8_t* dst, uint32_t pitch, uint32_t cstride, int x, int y, float a,
+                                            float b, float c) {
+    if (PLANAR) {
+        uint8_t* d = dst + (size_t)y * pitch + (size_t)x * 4;
+        *reinterpret_cast<float*>(d) = a;
+        *reinterpret_cast<float*>(d + (size_t)cstride) = b;
+        *reinterpret_cast<float*>(d + 2 * (size_t)cstride) = c;
+    } else {
+        float* d = reinterpret_cast<float*>(dst + (size_t)y * pitch + (size_t)x * 12);
+        d[0] = a; d[1] = b; d[2] = c;
+    }
+}
+
 template <uint32_t CHAIN, int SRC, bool PLANAR>
 __device__ __forceinline__ void body_resize(const DevPlane& P, const DevSeq& S, const DevOp* sops, uint32_t local) {
     /* plane fields used inside loops, copied out of shared memory once */
@@ -377,19 +392,23 @@ __device__ __forceinline__ void body_resize(const DevPlane& P, const DevSeq& S, 
     const uint32_t tiles_x = P.tiles_x, gw = P.gw, rs = P.rs;
     const uint32_t tile_y = local / tiles_x, tile_x = local - tile_y * tiles_x;
     const uint32_t slot = threadIdx.x / gw, gi = threadIdx.x - slot * gw;
-    const uint32_t g_in_roi = tile_x * gw + gi;
     const int row0 = y1 + (int)(tile_y * rs * RESIZE_ROWS_PER_THREAD); /* first row of this tile */
 
-    if (slot < rs && g_in_roi < n_groups) {
-        const int x0 = (int)((g_lo + g_in_roi) * PX_PER_THREAD);
+    if (slot < rs) {
+        /* The thread's four columns are gw apart, so that neighbouring lanes read neighbouring
+           source pixels and write neighbouring output elements: a warp-wide byte load then touches
+           a few hundred contiguous bytes instead of a span four times as wide. */
+        const int x0 = (int)(g_lo * PX_PER_THREAD + tile_x * gw * RESIZE_PX + gi);
+        const int x_end = (int)(g_lo * PX_PER_THREAD + min(n_groups * PX_PER_THREAD, (tile_x + 1) * gw * RESIZE_PX));
         /* horizontal taps and weights of the four columns, once per thread */
-        uint32_t off0[PX_PER_THREAD], off1[PX_PER_THREAD]; /* U8X3: byte offsets in a source row; NV12: columns */
-        float wx0[PX_PER_THREAD], wx1[PX_PER_THREAD];
-        uint32_t inside = 0;
+        uint32_t off0[RESIZE_PX], off1[RESIZE_PX]; /* U8X3: byte offsets in a source row; NV12: columns */
+        float wx0[RESIZE_PX], wx1[RESIZE_PX];
+        uint32_t inside = 0, valid = 0;
 #pragma unroll
-        for (int i = 0; i < PX_PER_THREAD; ++i) {
-            const int x = x0 + i;
+        for (int i = 0; i < RESIZE_PX; ++i) {
+            const int x = x0 + i * (int)gw;
             const bool in = (x >= x1 && x <= x2);
+            valid |= (x < x_end ? 1u : 0u) << i;
             const Axis ax = make_axis(in ? x - x1 : 0, P.fx, P.crop_w);
             if (SRC == FKB_SRC_NV12) { off0[i] = (uint32_t)(ax.i0 + P.crop_x); off1[i] = (uint32_t)(ax.i1 + P.crop_x); }
             else { off0[i] = (uint32_t)ax.i0 * 3u; off1[i] = (uint32_t)ax.i1 * 3u; }
@@ -402,17 +421,49 @@ __device__ __forceinline__ void body_resize(const DevPlane& P, const DevSeq& S, 
         const uint8_t* const chroma0 = P.src + (size_t)src_pitch * P.src_height;
         const bool yuv = S.pre_kind == PRE_YUV_BT709;
 
+#ifdef FKB_EXP_PREFETCH_TILE
+        if (SRC == FKB_SRC_U8X3) {
+            /* pull the tile's whole source footprint towards L2: one line per thread per step */
+            const int y_last = min(y2, row0 + (int)(rs * RESIZE_ROWS_PER_THREAD) - 1);
+            const int ia = make_axis(row0 - y1, fy, crop_h).i0, ib = make_axis(y_last - y1, fy, crop_h).i1;
+            const uint32_t row_bytes = (uint32_t)P.crop_w * 3u;
+            const uint32_t lines = (row_bytes + 127u) / 128u + 1u;
+            const uint32_t total = (uint32_t)(ib - ia + 1) * lines;
+            for (uint32_t k = threadIdx.x; k < total; k += nthreads) {
+                const uint32_t r = k / lines, l = k - r * lines;
+                const uint32_t o = min(l * 128u, row_bytes - 1u);
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(src0 + (size_t)(ia + (int)r) * src_pitch + o));
+            }
+        }
+#endif
 #pragma unroll 1
         for (int j = 0; j < RESIZE_ROWS_PER_THREAD; ++j) {
             const int y = row0 + (int)slot + j * (int)rs;
             if (y > y2) break;
             const Axis ay = make_axis(y - y1, fy, crop_h);
-            float v[12];
+            float v[3 * RESIZE_PX];
             if (SRC == FKB_SRC_U8X3) {
+#ifdef FKB_EXP_HOT
+                const uint8_t* const r0 = src0 + (size_t)(ay.i0 & 3) * src_pitch;
+                const uint8_t* const r1 = src0 + (size_t)(ay.i1 & 3) * src_pitch;
+#else
                 const uint8_t* const r0 = src0 + (size_t)ay.i0 * src_pitch;
                 const uint8_t* const r1 = src0 + (size_t)ay.i1 * src_pitch;
+#endif
+#ifdef FKB_EXP_PREFETCH
+                if (j + 1 < RESIZE_ROWS_PER_THREAD && y + (int)rs <= y2) {
+                    const Axis an = make_axis(y + (int)rs - y1, fy, crop_h);
+                    const uint8_t* const n0 = src0 + (size_t)an.i0 * src_pitch;
+                    const uint8_t* const n1 = src0 + (size_t)an.i1 * src_pitch;
 #pragma unroll
-                for (int i = 0; i < PX_PER_THREAD; ++i) {
+                    for (int i = 0; i < RESIZE_PX; ++i) {
+                        asm volatile("prefetch.global.L1 [%0];" ::"l"(n0 + off0[i]));
+                        asm volatile("prefetch.global.L1 [%0];" ::"l"(n1 + off0[i]));
+                    }
+                }
+#endif
+#pragma unroll
+                for (int i = 0; i < RESIZE_PX; ++i) {
                     const uint8_t* p00 = r0 + off0[i]; const uint8_t* p10 = r0 + off1[i];
                     const uint8_t* p01 = r1 + off0[i]; const uint8_t* p11 = r1 + off1[i];
                     const float w00 = __fmul_rn(wx0[i], ay.w0), w10 = __fmul_rn(wx1[i], ay.w0);
@@ -434,7 +485,7 @@ __device__ __forceinline__ void body_resize(const DevPlane& P, const DevSeq& S, 
                 const uint8_t* const c1 = chroma0 + (size_t)(ya1 >> 1) * src_pitch;
                 const bool need_row1 = ay.w1 != 0.0f;
 #pragma unroll
-                for (int i = 0; i < PX_PER_THREAD; ++i) {
+                for (int i = 0; i < RESIZE_PX; ++i) {
                     const bool need_col1 = wx1[i] != 0.0f;
                     const uint32_t xa = off0[i], xb = off1[i];
                     const uint32_t ca = (xa >> 1) * 2u, cb = (xb >> 1) * 2u;
@@ -467,14 +518,18 @@ __device__ __forceinline__ void body_resize(const DevPlane& P, const DevSeq& S, 
                     v[3 * i] = acc[0]; v[3 * i + 1] = acc[1]; v[3 * i + 2] = acc[2];
                 }
             }
-            run_ops<CHAIN, PX_PER_THREAD>(v, sops, S.n_pre, S.n_ops);
-            if (inside != 0xFu) { /* a group straddling the edge of the region */
+            run_ops<CHAIN, RESIZE_PX>(v, sops, S.n_pre, S.n_ops);
+            if (inside != (1u << RESIZE_PX) - 1u) { /* a group straddling the edge of the region */
 #pragma unroll
-                for (int i = 0; i < PX_PER_THREAD; ++i) {
+                for (int i = 0; i < RESIZE_PX; ++i) {
                     if (!((inside >> i) & 1u)) { v[3 * i] = bgv[0]; v[3 * i + 1] = bgv[1]; v[3 * i + 2] = bgv[2]; }
                 }
             }
-            store_group<PLANAR>(dst, dst_pitch, dst_cstride, x0, y, v);
+#pragma unroll
+            for (int i = 0; i < RESIZE_PX; ++i) {
+                if ((valid >> i) & 1u)
+                    store_pixel<PLANAR>(dst, dst_pitch, dst_cstride, x0 + i * (int)gw, y, v[3 * i], v[3 * i + 1], v[3 * i + 2]);
+            }
         }
     }
 
@@ -510,8 +565,11 @@ __device__ __forceinline__ void run_body(uint32_t cls, const DevPlane& P, const 
     }
 }
 
+#ifndef FKB_MIN_BLOCKS
+#define FKB_MIN_BLOCKS 1
+#endif
 template <uint32_t CLASS, uint32_t CHAIN>
-__global__ void __launch_bounds__(BLOCK_THREADS) fused_plan_kernel(const __grid_constant__ LaunchArgs a) {
+__global__ void __launch_bounds__(BLOCK_THREADS, FKB_MIN_BLOCKS) fused_plan_kernel(const __grid_constant__ LaunchArgs a) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     DevOp* sops = reinterpret_cast<DevOp*>(smem_raw);
     __shared__ DevPlane s_plane;
