@@ -9,7 +9,7 @@
  *
  * Parity status: PINNED.  Every function below is checked bit-for-bit against the
  * reference's own headers compiled here (oracle/ref/, built into oracle/_ref/) by
- * tests/test_oracle_vs_reference.py, and against the golden vectors under tests/golden/
+ * tests/test_oracle_golden.py, and against the golden vectors under tests/golden/
  * that were generated from that build.
  *
  * All arithmetic is IEEE-754 binary32, round-to-nearest-even, without contraction: build
