@@ -179,7 +179,7 @@ EXPORTS = [
     "fkb_reference_block_size", "fkb_plan_create", "fkb_plan_validate", "fkb_plan_launch", "fkb_plan_get_info",
     "fkb_plan_get_resize_params", "fkb_plan_destroy", "fkb_execute", "fkb_host_session_create",
     "fkb_host_session_run", "fkb_host_session_get_traffic", "fkb_host_session_destroy",
-    "fkb_execute_host",
+    "fkb_execute_host", "fkb_execute_static",
 ]
 
 
@@ -209,6 +209,7 @@ def load_library(path: os.PathLike | None = None) -> C.CDLL:
     lib.fkb_plan_destroy.argtypes = [C.c_void_p]
     lib.fkb_execute.argtypes = [C.POINTER(PlanDesc), C.c_void_p]
     lib.fkb_execute_host.argtypes = [C.POINTER(PlanDesc), C.c_void_p]
+    lib.fkb_execute_static.argtypes = [C.POINTER(PlanDesc), C.c_void_p]
     lib.fkb_host_session_create.argtypes = [C.POINTER(PlanDesc), C.POINTER(C.c_void_p)]
     lib.fkb_host_session_run.argtypes = [C.c_void_p, C.c_void_p]
     lib.fkb_host_session_get_traffic.argtypes = [C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
@@ -279,6 +280,17 @@ def execute_host(host_plan: HostPlan, stream: int | None = None) -> None:
     lib = load_library()
     desc = host_plan.desc()
     check(lib.fkb_execute_host(C.byref(desc), C.c_void_p(stream or 0)), "fkb_execute_host")
+
+
+STATIC_TABLE_BYTES = 512 * 1024
+
+
+def execute_static(host_plan: HostPlan, stream: int | None = None) -> None:
+    """fkb_execute_static: the one-shot run that allocates no device memory (descriptor table in
+    the library's fixed array; plans beyond STATIC_TABLE_BYTES raise FkbError with ERR_TOO_LARGE)."""
+    lib = load_library()
+    desc = host_plan.desc()
+    check(lib.fkb_execute_static(C.byref(desc), C.c_void_p(stream or 0)), "fkb_execute_static")
 
 
 class HostSession:

@@ -890,3 +890,69 @@ extern "C" FKB_API int fkb_execute_host(const fkb_plan_desc* desc, void* stream)
     fkb_host_session_destroy(s);
     return rc;
 }
+
+/* ------------------------------------------------------------------------------------ */
+/* allocation-free variant                                                              */
+/* ------------------------------------------------------------------------------------ */
+/* fkb_execute_static runs a plan like fkb_execute, but its descriptor table - the only device
+ * memory the kernels use beyond the caller's images - lives in the fixed array below instead
+ * of a cudaMalloc'ed block.  It is for hosts that must not allocate device memory while they
+ * run: a server whose framework reserved the whole of HBM for its own pool at start-up (a
+ * cudaMalloc from a plug-in then fails or fragments that pool), and a frame loop with a
+ * latency bound, where cudaMalloc and cudaFree stall the host against everything in flight on
+ * the device.
+ *
+ * Every GPU that loads the library holds FKB_STATIC_TABLE_BYTES for this array until the
+ * process exits.  All calls on a device share it; it keeps what the last call wrote.  A call
+ * rewrites the whole prefix that its kernel reads (planes, sequences, operations, work-item
+ * prefix sums) before the launch, in stream order, and the kernel reads nothing beyond that
+ * prefix, so nothing has to start at zero. */
+static __device__ __align__(256) unsigned char g_static_table[FKB_STATIC_TABLE_BYTES];
+
+/* In host code `g_static_table` is only a handle for the runtime, not a device address; the
+ * address on the current device is looked up once per device and cached here. */
+static std::mutex g_static_mu;
+static unsigned char* g_static_addr[64] = {};
+
+static int static_table_address(int device, unsigned char** out) {
+    if (device < 0 || device >= 64) return fail(FKB_ERR_UNSUPPORTED, "fkb_execute_static: device ordinal %d beyond 63", device);
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (!g_static_addr[device]) {
+        void* p = nullptr;
+        FKB_CUDA(cudaGetSymbolAddress(&p, g_static_table)); /* resolves on the CURRENT device */
+        if (!p) return fail(FKB_ERR_CUDA, "fkb_execute_static: the descriptor table has no address on device %d", device);
+        g_static_addr[device] = static_cast<unsigned char*>(p);
+    }
+    *out = g_static_addr[device];
+    return FKB_OK;
+}
+
+extern "C" FKB_API int fkb_execute_static(const fkb_plan_desc* desc, void* stream_) {
+    HostImage img;
+    int rc = lower(desc, img);
+    if (rc) return rc;
+    const size_t bytes = img.bytes();
+    if (bytes > (size_t)FKB_STATIC_TABLE_BYTES)
+        return fail(FKB_ERR_TOO_LARGE,
+                    "fkb_execute_static: the plan needs a descriptor table of %zu bytes (%zu planes, %zu sequences, %zu operations) "
+                    "but the fixed table holds %d; split the batch or use fkb_plan_create",
+                    bytes, img.planes.size(), img.seqs.size(), img.ops.size(), (int)FKB_STATIC_TABLE_BYTES);
+    int device = -1;
+    rc = require_device(&device);
+    if (rc) return rc;
+    unsigned char* table = nullptr;
+    rc = static_table_address(device, &table);
+    if (rc) return rc;
+
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    std::vector<unsigned char> staging(bytes); /* host memory only */
+    img.serialize(staging.data());
+    /* From pageable memory this returns once `staging` has been read, and is ordered on the
+       stream before the launch and after any earlier kernel that still reads the table. */
+    FKB_CUDA(cudaMemcpyAsync(table, staging.data(), bytes, cudaMemcpyHostToDevice, stream));
+    const cudaError_t le = launch_plan_kernel(img.launch_class, img.chain, img.args_for(table), stream);
+    const cudaError_t se = cudaStreamSynchronize(stream);
+    if (le != cudaSuccess) return fail_cuda(le, "kernel launch", __LINE__);
+    if (se != cudaSuccess) return fail_cuda(se, "cudaStreamSynchronize", __LINE__);
+    return FKB_OK;
+}

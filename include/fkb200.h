@@ -233,6 +233,25 @@ FKB_API int fkb_host_session_destroy(fkb_host_session* session);
 /* One-shot fkb_host_session_create + run + destroy. */
 FKB_API int fkb_execute_host(const fkb_plan_desc* desc, void* stream);
 
+/* fkb_execute without any device allocation.  No counterpart in the reference (its launch
+ * passes all parameters as kernel arguments and never allocates).  Meant for hosts that cannot
+ * call cudaMalloc while running: plug-ins inside a server whose framework has taken all of HBM
+ * for its own pool, and latency-bound frame loops that cannot afford the device-wide stall of
+ * cudaMalloc / cudaFree.  The plan's descriptor table goes into a fixed array of
+ * FKB_STATIC_TABLE_BYTES that every GPU loading the library holds until the process exits;
+ * image pointers are the caller's, as everywhere else.  Behaviour:
+ *  - validates and lowers `desc` exactly like fkb_plan_create, copies the table into the fixed
+ *    array on `stream`, launches, and synchronises `stream` before returning;
+ *  - a plan whose table (112 B per plane + 48 B per sequence + 16 B per operation + 4 B per
+ *    plane) exceeds FKB_STATIC_TABLE_BYTES is refused with FKB_ERR_TOO_LARGE, nothing runs;
+ *  - calls cudaMalloc, cudaFree or an allocating library routine never; host memory only;
+ *  - the first call on a device looks up the array's device address (with that device
+ *    current); make that first call before starting any stream capture on the device;
+ *  - all calls on one device share the array: two calls that overlap on the GPU (different
+ *    host threads on different streams) race on it and must be serialised by the caller. */
+#define FKB_STATIC_TABLE_BYTES (512 * 1024)
+FKB_API int fkb_execute_static(const fkb_plan_desc* desc, void* stream);
+
 #ifdef __cplusplus
 } /* extern "C" */
 #endif
