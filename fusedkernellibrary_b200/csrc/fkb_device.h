@@ -21,7 +21,9 @@ enum PlaneClass : uint32_t {
     CLASS_RESIZE_U8_PLANAR = 4, /* bilinear, 4 adjacent output pixels per thread             */
     CLASS_RESIZE_U8_PACKED = 5,
     CLASS_RESIZE_NV12_PACKED = 6,
-    CLASS_COUNT = 7,
+    CLASS_RESIZE_U8_PLANAR_STAGED = 7, /* bilinear from a source footprint staged in shared memory */
+    CLASS_RESIZE_U8_PACKED_STAGED = 8,
+    CLASS_COUNT = 9,
     CLASS_MIXED = 0xFF       /* launch-level only: planes of several classes in one grid     */
 };
 
@@ -41,7 +43,7 @@ struct alignas(16) DevPlane {
     uint32_t n_segs;         /* FLAT classes: 1 (dense plane) or dst_h (one segment per row)  */
     /* RESIZE classes: tiling of the region of interest (see ResizeTiling) */
     uint32_t roi_items;      /* work items that interpolate; the rest fill background rows    */
-    uint32_t tiles_x;
+    uint32_t tiles_x;        /* STAGED classes: output rows per work item (band)               */
     uint32_t gw;
     uint32_t rs;
 };
@@ -58,7 +60,8 @@ struct alignas(16) DevSeq {
     int32_t n_ops, n_pre, ops_begin; /* ops_begin: index of the first op in the op table      */
     int32_t pre_kind;                /* PRE_* below                                           */
     int32_t pad;
-    float bg[4];
+    float bg[3];
+    float one;                       /* 1.0f, read at run time by the packed additions         */
 };
 static_assert(sizeof(DevSeq) == 48, "DevSeq layout");
 
@@ -79,7 +82,9 @@ struct LaunchArgs {
     uint32_t total_items;
     uint32_t max_seq_ops;       /* longest sequence: sizes the shared-memory op cache         */
     uint32_t block_threads;     /* threads per block of this launch (multiple of 32, <= 256)  */
-    uint32_t pad[3];
+    uint32_t staged_bytes;      /* STAGED classes: shared memory behind the operation cache    */
+    uint32_t pad[2];
+    uint32_t* status;           /* one word in the plan's device block: 0, or a STATUS_* code  */
 };
 
 constexpr int BLOCK_THREADS = 256;
@@ -139,6 +144,18 @@ inline ResizeTiling resize_tiling(uint32_t dst_w, uint32_t dst_h, int x1, int y1
     t.bg_items = (uint32_t)((bg_groups + per_item - 1) / per_item);
     return t;
 }
+
+/* STAGED classes: a work item is a band of `band_rows` output rows of the region of interest,
+ * all columns; its source footprint (whole crop rows, widened to 16-byte boundaries) sits in
+ * shared memory behind a 16-byte mbarrier slot and a table of per-row vertical taps. */
+constexpr uint32_t STAGED_MAX_ROWS = 64;          /* output rows per band                        */
+#ifndef FKB_STAGE_KB
+#define FKB_STAGE_KB 40
+#endif
+constexpr uint32_t STAGED_MAX_STAGE_BYTES = FKB_STAGE_KB * 1024u;
+constexpr uint32_t STAGED_HEADER_BYTES = 16 + STAGED_MAX_ROWS * 16;
+constexpr uint32_t STAGED_WAIT_LIMIT = 1u << 22;  /* try_wait rounds before a block gives up     */
+constexpr uint32_t STATUS_STAGED_WAIT_TIMEOUT = 1; /* a bulk copy did not complete in time        */
 
 /* Compile-time operation chains.  A chain is a list of 4-bit operation codes, first operation
  * in the lowest nibble, 0 terminates.  Kernels are instantiated for the chains in

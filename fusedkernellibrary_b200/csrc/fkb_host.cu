@@ -77,6 +77,7 @@ struct HostImage {
     uint32_t uniform_items = 0;
     uint32_t total_items = 0;
     uint32_t max_seq_ops = 0;
+    uint32_t staged_bytes = 0;          /* > 0: a STAGED class, this much shared memory per block */
     uint64_t output_pixels = 0;
     uint64_t algorithmic_bytes = 0;
     int n_constant_divisions = 0, n_ieee_divisions = 0;
@@ -85,13 +86,15 @@ struct HostImage {
     size_t off_seqs() const { return planes.size() * sizeof(DevPlane); }
     size_t off_ops() const { return off_seqs() + seqs.size() * sizeof(DevSeq); }
     size_t off_items() const { return off_ops() + std::max<size_t>(ops.size(), 1) * sizeof(DevOp); }
-    size_t bytes() const { return off_items() + item_start.size() * sizeof(uint32_t); }
+    size_t off_status() const { return (off_items() + item_start.size() * sizeof(uint32_t) + 15) & ~(size_t)15; }
+    size_t bytes() const { return off_status() + 16; }
 
     void serialize(unsigned char* dst) const {
         std::memcpy(dst + off_planes(), planes.data(), planes.size() * sizeof(DevPlane));
         std::memcpy(dst + off_seqs(), seqs.data(), seqs.size() * sizeof(DevSeq));
         if (!ops.empty()) std::memcpy(dst + off_ops(), ops.data(), ops.size() * sizeof(DevOp));
         std::memcpy(dst + off_items(), item_start.data(), item_start.size() * sizeof(uint32_t));
+        std::memset(dst + off_status(), 0, 16);
     }
     LaunchArgs args_for(const unsigned char* d_base) const {
         LaunchArgs a{};
@@ -104,6 +107,8 @@ struct HostImage {
         a.total_items = total_items;
         a.max_seq_ops = max_seq_ops;
         a.block_threads = block_threads;
+        a.staged_bytes = staged_bytes;
+        a.status = reinterpret_cast<uint32_t*>(const_cast<unsigned char*>(d_base) + off_status());
         return a;
     }
 };
@@ -443,8 +448,58 @@ static int check_sequence(const fkb_sequence& s, int index, DevSeq& ds) {
     ds.src_format = s.src_format; ds.dst_format = s.dst_format; ds.resize_mode = s.resize_mode;
     ds.n_ops = s.n_ops; ds.n_pre = n_pre; ds.ops_begin = 0; ds.pad = 0;
     ds.pre_kind = (n_pre == 0 || pre_only_casts) ? PRE_IDENTITY : pre_is_yuv ? PRE_YUV_BT709 : PRE_GENERAL;
-    ds.bg[0] = s.background[0]; ds.bg[1] = s.background[1]; ds.bg[2] = s.background[2]; ds.bg[3] = 0.0f;
+    ds.bg[0] = s.background[0]; ds.bg[1] = s.background[1]; ds.bg[2] = s.background[2]; ds.one = 1.0f;
     return FKB_OK;
+}
+
+/* STAGED classes: how a plane's region of interest is cut into bands whose source footprint
+ * fits the shared-memory stage.  Source rows are found with the arithmetic the kernel uses
+ * (binary32 product of the row index and fy, floor: resize.h:183-194, interpolation.h:66-67). */
+struct StagedTiling {
+    bool ok = false;
+    uint32_t band_rows = 0, gw = 0, rs = 0, n_bands = 0, stage_bytes = 0;
+};
+static int staged_src_row(int r, float fy) { return (int)std::floor((float)r * fy); }
+
+static StagedTiling staged_tiling(const DevPlane& dp, uint32_t block_threads) {
+    StagedTiling t;
+    const uint32_t g_lo = (uint32_t)dp.x1 / PX_PER_THREAD;
+    const uint32_t n_groups = (uint32_t)dp.x2 / PX_PER_THREAD - g_lo + 1;
+    const uint32_t n_rows = (uint32_t)(dp.y2 - dp.y1 + 1);
+    const uint32_t pairs = n_groups * (PX_PER_THREAD / 2); /* threads across: each owns two columns */
+    if (pairs > block_threads) return t;
+    if ((reinterpret_cast<uintptr_t>(dp.src) % 16) != 0 || (dp.src_pitch % 16) != 0) return t;
+    const uint32_t row_first = ((uint32_t)dp.crop_x * 3u) & ~15u;
+    const uint32_t phase = (uint32_t)dp.crop_x * 3u - row_first;
+    const uint32_t row_len = (phase + (uint32_t)dp.crop_w * 3u + 15u) & ~15u;
+    if (row_first + row_len > dp.src_pitch) return t; /* never reads past the end of a row */
+    const uint32_t max_src_rows = STAGED_MAX_STAGE_BYTES / row_len;
+    if (max_src_rows < 2) return t;
+    t.gw = pairs;
+    t.rs = block_threads / pairs;
+    auto worst_rows = [&](uint32_t band) {
+        uint32_t worst = 0;
+        for (uint32_t a = 0; a < n_rows; a += band) {
+            const uint32_t b = std::min(a + band, n_rows) - 1;
+            const int first = staged_src_row((int)a, dp.fy);
+            const int last = std::min(staged_src_row((int)b, dp.fy) + 1, dp.crop_h - 1);
+            worst = std::max(worst, (uint32_t)(last - first + 1));
+        }
+        return worst;
+    };
+    uint32_t band = std::min<uint32_t>(STAGED_MAX_ROWS, n_rows);
+    {   /* first guess from the step, then exact */
+        const double guess = ((double)max_src_rows - 2.0) / std::max((double)dp.fy, 1e-6) + 1.0;
+        if (guess < (double)band) band = (uint32_t)std::max(1.0, guess);
+    }
+    while (band > 1 && worst_rows(band) > max_src_rows) --band;
+    if (worst_rows(band) > max_src_rows) return t;
+    if (band > t.rs) band -= band % t.rs; /* whole rounds of the row slots */
+    t.band_rows = band;
+    t.n_bands = (n_rows + band - 1) / band;
+    t.stage_bytes = worst_rows(band) * row_len;
+    t.ok = true;
+    return t;
 }
 
 static bool aligned(const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
@@ -587,6 +642,42 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
     img.launch_class = common_class;
     img.chain = (common_class != CLASS_MIXED && common_class != CLASS_GENERIC && chain_is_compiled(common_chain))
                     ? common_chain : CHAIN_INTERPRET;
+#ifndef FKB_DISABLE_STAGED
+    /* uchar3 resize plans whose every plane can stage its bands' source rows in shared memory */
+    if (common_class == CLASS_RESIZE_U8_PLANAR || common_class == CLASS_RESIZE_U8_PACKED) {
+        std::vector<StagedTiling> st(img.planes.size());
+        bool all = true;
+        uint32_t stage = 0;
+        for (size_t i = 0; i < img.planes.size() && all; ++i) {
+            st[i] = staged_tiling(img.planes[i], BLOCK_THREADS);
+            all = st[i].ok;
+            stage = std::max(stage, st[i].stage_bytes);
+        }
+        if (all) {
+            const uint32_t cls = common_class == CLASS_RESIZE_U8_PLANAR ? CLASS_RESIZE_U8_PLANAR_STAGED : CLASS_RESIZE_U8_PACKED_STAGED;
+            uint64_t t2 = 0;
+            uniform = true;
+            for (size_t i = 0; i < img.planes.size(); ++i) {
+                DevPlane& dp = img.planes[i];
+                const ResizeTiling rt = resize_tiling(dp.dst_w, dp.dst_h, dp.x1, dp.y1, dp.x2, dp.y2, BLOCK_THREADS);
+                const uint32_t items = st[i].n_bands + rt.bg_items;
+                dp.plane_class = cls;
+                dp.roi_items = st[i].n_bands; dp.tiles_x = st[i].band_rows; dp.gw = st[i].gw; dp.rs = st[i].rs;
+                img.item_start[i] = (uint32_t)t2;
+                t2 += items;
+                if (i == 0) first_items = items;
+                else if (items != first_items) uniform = false;
+            }
+            if (t2 > 0x7FFFFFFFull) return fail(FKB_ERR_INVALID_ARGUMENT, "plan needs more than 2^31 thread blocks");
+            img.item_start[img.planes.size()] = (uint32_t)t2;
+            img.total_items = (uint32_t)t2;
+            img.uniform_items = uniform ? first_items : 0;
+            img.block_threads = BLOCK_THREADS;
+            img.staged_bytes = STAGED_HEADER_BYTES + stage;
+            img.launch_class = common_class = cls;
+        }
+    }
+#endif
     /* A plan whose planes all have the same region width can run with exactly as many threads per
        block as its tiling keeps busy. */
     const bool resize_class = common_class == CLASS_RESIZE_U8_PLANAR || common_class == CLASS_RESIZE_U8_PACKED ||

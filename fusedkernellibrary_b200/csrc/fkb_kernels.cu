@@ -68,46 +68,80 @@ __device__ __forceinline__ void yuv_to_rgb_bt709_full(float& a, float& b, float&
     c = __fmul_rn(__fadd_rn(__fadd_rn(__fmul_rn(y, 1.0f), __fmul_rn(u, 1.8556f)), __fmul_rn(v, 0.0f)), 1.0f);
 }
 
-/* One operation on NPX whole pixels held as v[3*i + channel]; o carries the per-channel
-   parameter in y, z, w; r is the second slot of a two-slot operation. */
-template <int CODE, int NPX>
-__device__ __forceinline__ void apply_one(float (&v)[NPX * 3], const float4 o, const float4 r) {
+/* Packed binary32 arithmetic (sm_100): one instruction rounds two independent products, sums
+ * or fused multiply-adds, each to nearest even exactly like the scalar instruction.  Values
+ * travel as pairs of horizontally adjacent pixels, one pair per channel. */
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 dup2(float a) { return make_float2(a, a); }
+/* a + b as RN(a*1 + b), which is the same value for every input including signed zeros.  The
+ * packed add itself cannot be used after a packed multiply: the assembler contracts
+ * mul.rn.f32x2 + add.rn.f32x2 into one fused multiply-add even with contraction disabled
+ * (measured on this toolchain: the fused result differs from the separately rounded one on
+ * 15 % of random inputs), and a literal 1.0 is folded back into an add and contracted too.
+ * `one` is therefore (1, 1) read from the plan's descriptor at run time. */
+__device__ __forceinline__ float2 add2(float2 a, float2 b, float2 one) { return __ffma2_rn(a, one, b); }
+
+/* One operation on NPAIR pixel pairs held as v[3*j + channel] = (pixel 2j, pixel 2j+1); o carries
+   the per-channel parameter in y, z, w; r is the second slot of a two-slot operation. */
+template <int CODE, int NPAIR>
+__device__ __forceinline__ void apply_one(float2 (&v)[NPAIR * 3], const float4 o, const float4 r, const float2 one) {
+    if (CODE == CH_SUB) { /* x - p == x + (-p), negated once per parameter */
+        const float2 n0 = dup2(-o.y), n1 = dup2(-o.z), n2 = dup2(-o.w);
 #pragma unroll
-    for (int i = 0; i < NPX; ++i) {
-        float& a = v[3 * i + 0];
-        float& b = v[3 * i + 1];
-        float& c = v[3 * i + 2];
-        if (CODE == CH_MUL) { a = __fmul_rn(a, o.y); b = __fmul_rn(b, o.z); c = __fmul_rn(c, o.w); }
-        else if (CODE == CH_SUB) { a = __fsub_rn(a, o.y); b = __fsub_rn(b, o.z); c = __fsub_rn(c, o.w); }
-        else if (CODE == CH_DIV) { a = __fdiv_rn(a, o.y); b = __fdiv_rn(b, o.z); c = __fdiv_rn(c, o.w); }
-        else if (CODE == CH_ADD) { a = __fadd_rn(a, o.y); b = __fadd_rn(b, o.z); c = __fadd_rn(c, o.w); }
-        else if (CODE == CH_DIVC) {
-            a = div_by_constant(a, o.y, r.y); b = div_by_constant(b, o.z, r.z); c = div_by_constant(c, o.w, r.w);
-        } else if (CODE == CH_SWAP) { const float t = a; a = c; c = t; }
-        else if (CODE == CH_SAT) { a = saturate_round_u8(a); b = saturate_round_u8(b); c = saturate_round_u8(c); }
-        else if (CODE == CH_YUV) { yuv_to_rgb_bt709_full(a, b, c); }
+        for (int j = 0; j < NPAIR; ++j) {
+            v[3 * j] = add2(v[3 * j], n0, one); v[3 * j + 1] = add2(v[3 * j + 1], n1, one); v[3 * j + 2] = add2(v[3 * j + 2], n2, one);
+        }
+        return;
+    }
+    const float2 p0 = dup2(o.y), p1 = dup2(o.z), p2 = dup2(o.w);
+    const float2 r0 = dup2(r.y), r1 = dup2(r.z), r2 = dup2(r.w);
+#pragma unroll
+    for (int j = 0; j < NPAIR; ++j) {
+        float2& a = v[3 * j + 0];
+        float2& b = v[3 * j + 1];
+        float2& c = v[3 * j + 2];
+        if (CODE == CH_MUL) { a = mul2(a, p0); b = mul2(b, p1); c = mul2(c, p2); }
+        else if (CODE == CH_DIV) {
+            a = make_float2(__fdiv_rn(a.x, o.y), __fdiv_rn(a.y, o.y));
+            b = make_float2(__fdiv_rn(b.x, o.z), __fdiv_rn(b.y, o.z));
+            c = make_float2(__fdiv_rn(c.x, o.w), __fdiv_rn(c.y, o.w));
+        } else if (CODE == CH_ADD) { a = add2(a, p0, one); b = add2(b, p1, one); c = add2(c, p2, one); }
+        else if (CODE == CH_DIVC) { /* div_by_constant on both halves: p holds -divisor, r its reciprocal */
+            const float2 qa = mul2(a, r0), qb = mul2(b, r1), qc = mul2(c, r2);
+            a = fma2(fma2(p0, qa, a), r0, qa); b = fma2(fma2(p1, qb, b), r1, qb); c = fma2(fma2(p2, qc, c), r2, qc);
+        } else if (CODE == CH_SWAP) { const float2 t = a; a = c; c = t; }
+        else if (CODE == CH_SAT) {
+            a = make_float2(saturate_round_u8(a.x), saturate_round_u8(a.y));
+            b = make_float2(saturate_round_u8(b.x), saturate_round_u8(b.y));
+            c = make_float2(saturate_round_u8(c.x), saturate_round_u8(c.y));
+        } else if (CODE == CH_YUV) {
+            yuv_to_rgb_bt709_full(a.x, b.x, c.x);
+            yuv_to_rgb_bt709_full(a.y, b.y, c.y);
+        }
     }
 }
 
 /* Interpreter: runs ops [begin, end) of a sequence cached in shared memory.  The opcode is
  * uniform across the block, so the switch never diverges. */
-template <int NPX>
-__device__ __forceinline__ void interpret_ops(float (&v)[NPX * 3], const DevOp* __restrict__ sops, int begin, int end) {
+template <int NPAIR>
+__device__ __forceinline__ void interpret_ops(float2 (&v)[NPAIR * 3], const DevOp* __restrict__ sops, int begin, int end,
+                                              const float2 one) {
     for (int k = begin; k < end; ++k) {
         const float4 o = *reinterpret_cast<const float4*>(&sops[k]);
         const float4 none = make_float4(0.f, 0.f, 0.f, 0.f);
         switch (__float_as_int(o.x)) {
-            case FKB_OP_MUL: apply_one<CH_MUL, NPX>(v, o, none); break;
-            case FKB_OP_SUB: apply_one<CH_SUB, NPX>(v, o, none); break;
-            case FKB_OP_DIV: apply_one<CH_DIV, NPX>(v, o, none); break;
-            case FKB_OP_ADD: apply_one<CH_ADD, NPX>(v, o, none); break;
+            case FKB_OP_MUL: apply_one<CH_MUL, NPAIR>(v, o, none, one); break;
+            case FKB_OP_SUB: apply_one<CH_SUB, NPAIR>(v, o, none, one); break;
+            case FKB_OP_DIV: apply_one<CH_DIV, NPAIR>(v, o, none, one); break;
+            case FKB_OP_ADD: apply_one<CH_ADD, NPAIR>(v, o, none, one); break;
             case DEV_OP_DIV_BY_CONSTANT: /* two slots: {-p}, {1/p} */
-                apply_one<CH_DIVC, NPX>(v, o, *reinterpret_cast<const float4*>(&sops[k + 1]));
+                apply_one<CH_DIVC, NPAIR>(v, o, *reinterpret_cast<const float4*>(&sops[k + 1]), one);
                 ++k;
                 break;
-            case FKB_OP_SWAP_RB: apply_one<CH_SWAP, NPX>(v, o, none); break;
-            case FKB_OP_SATURATE_CAST_U8: apply_one<CH_SAT, NPX>(v, o, none); break;
-            case FKB_OP_YUV_TO_RGB_BT709_FULL: apply_one<CH_YUV, NPX>(v, o, none); break;
+            case FKB_OP_SWAP_RB: apply_one<CH_SWAP, NPAIR>(v, o, none, one); break;
+            case FKB_OP_SATURATE_CAST_U8: apply_one<CH_SAT, NPAIR>(v, o, none, one); break;
+            case FKB_OP_YUV_TO_RGB_BT709_FULL: apply_one<CH_YUV, NPAIR>(v, o, none, one); break;
             default: break;
         }
     }
@@ -115,29 +149,38 @@ __device__ __forceinline__ void interpret_ops(float (&v)[NPX * 3], const DevOp* 
 
 /* A chain fixed at compile time: operation codes in the nibbles of CHAIN, parameters taken
    from consecutive slots of the cached operation table starting at `slot`. */
-template <uint32_t CHAIN, int NPX>
-__device__ __forceinline__ void apply_chain(float (&v)[NPX * 3], const DevOp* __restrict__ sops, int slot) {
+template <uint32_t CHAIN, int NPAIR>
+__device__ __forceinline__ void apply_chain(float2 (&v)[NPAIR * 3], const DevOp* __restrict__ sops, int slot, const float2 one) {
     constexpr uint32_t CODE = CHAIN & 0xFu;
     if constexpr (CODE != 0) {
         const float4 none = make_float4(0.f, 0.f, 0.f, 0.f);
         if constexpr (CODE == CH_SWAP || CODE == CH_SAT || CODE == CH_YUV) {
-            apply_one<CODE, NPX>(v, none, none);
-            apply_chain<(CHAIN >> 4), NPX>(v, sops, slot + 1);
+            apply_one<CODE, NPAIR>(v, none, none, one);
+            apply_chain<(CHAIN >> 4), NPAIR>(v, sops, slot + 1, one);
         } else if constexpr (CODE == CH_DIVC) {
-            apply_one<CODE, NPX>(v, *reinterpret_cast<const float4*>(&sops[slot]),
-                                 *reinterpret_cast<const float4*>(&sops[slot + 1]));
-            apply_chain<(CHAIN >> 4), NPX>(v, sops, slot + 2);
+            apply_one<CODE, NPAIR>(v, *reinterpret_cast<const float4*>(&sops[slot]),
+                                   *reinterpret_cast<const float4*>(&sops[slot + 1]), one);
+            apply_chain<(CHAIN >> 4), NPAIR>(v, sops, slot + 2, one);
         } else {
-            apply_one<CODE, NPX>(v, *reinterpret_cast<const float4*>(&sops[slot]), none);
-            apply_chain<(CHAIN >> 4), NPX>(v, sops, slot + 1);
+            apply_one<CODE, NPAIR>(v, *reinterpret_cast<const float4*>(&sops[slot]), none, one);
+            apply_chain<(CHAIN >> 4), NPAIR>(v, sops, slot + 1, one);
         }
     }
 }
 
-template <uint32_t CHAIN, int NPX>
-__device__ __forceinline__ void run_ops(float (&v)[NPX * 3], const DevOp* __restrict__ sops, int begin, int end) {
-    if constexpr (CHAIN == CHAIN_INTERPRET) interpret_ops<NPX>(v, sops, begin, end);
-    else apply_chain<CHAIN, NPX>(v, sops, begin);
+template <uint32_t CHAIN, int NPAIR>
+__device__ __forceinline__ void run_ops(float2 (&v)[NPAIR * 3], const DevOp* __restrict__ sops, int begin, int end,
+                                        const float2 one) {
+    if constexpr (CHAIN == CHAIN_INTERPRET) interpret_ops<NPAIR>(v, sops, begin, end, one);
+    else apply_chain<CHAIN, NPAIR>(v, sops, begin, one);
+}
+
+/* The same on one pixel (both halves of a pair carry it). */
+template <uint32_t CHAIN>
+__device__ __forceinline__ void run_ops_1(float (&v)[3], const DevOp* __restrict__ sops, int begin, int end, const float2 one) {
+    float2 p[3] = {dup2(v[0]), dup2(v[1]), dup2(v[2])};
+    run_ops<CHAIN, 1>(p, sops, begin, end, one);
+    v[0] = p[0].x; v[1] = p[1].x; v[2] = p[2].x;
 }
 
 /* ------------------------------------------------------------------------------------ */
@@ -203,6 +246,7 @@ __device__ __forceinline__ void body_generic(const DevPlane& P, const DevSeq& S,
     const uint32_t idx = local * ITEM_PIXELS_GENERIC + threadIdx.x;
     if (idx >= P.dst_w * P.dst_h) return;
     const int y = idx / P.dst_w, x = idx - y * P.dst_w;
+    const float2 one = dup2(S.one);
     float v[3];
     int first_post = 0;
     if (S.resize_mode == FKB_RESIZE_NONE) {
@@ -222,7 +266,7 @@ __device__ __forceinline__ void body_generic(const DevPlane& P, const DevSeq& S,
             read_tap_any(S.src_format, P, ax.i1, ay.i1, t[3][0], t[3][1], t[3][2]);
             if (S.pre_kind != PRE_IDENTITY) {
 #pragma unroll
-                for (int k = 0; k < 4; ++k) interpret_ops<1>(t[k], sops, 0, S.n_pre);
+                for (int k = 0; k < 4; ++k) run_ops_1<CHAIN_INTERPRET>(t[k], sops, 0, S.n_pre, one);
             }
             const float w00 = __fmul_rn(ax.w0, ay.w0), w10 = __fmul_rn(ax.w1, ay.w0);
             const float w01 = __fmul_rn(ax.w0, ay.w1), w11 = __fmul_rn(ax.w1, ay.w1);
@@ -230,7 +274,7 @@ __device__ __forceinline__ void body_generic(const DevPlane& P, const DevSeq& S,
             for (int c = 0; c < 3; ++c) v[c] = blend(t[0][c], t[1][c], t[2][c], t[3][c], w00, w10, w01, w11);
         }
     }
-    interpret_ops<1>(v, sops, first_post, S.n_ops);
+    run_ops_1<CHAIN_INTERPRET>(v, sops, first_post, S.n_ops, one);
     /* receivers: memory_operations.h:122-127 (PerThreadWrite), :181-184 (TensorWrite),
        :203-219 (TensorSplit) */
     if (S.dst_format == FKB_DST_F32X3_PACKED) {
@@ -293,7 +337,19 @@ __device__ __forceinline__ void body_flat(const DevPlane& P, const DevSeq& S, co
         }
     }
 
-    run_ops<CHAIN, PX_PER_THREAD>(v, sops, 0, S.n_ops);
+    {
+        /* pair pixels (0,1) and (2,3) channel by channel */
+        float2 q[6];
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int c = 0; c < 3; ++c) q[3 * j + c] = make_float2(v[6 * j + c], v[6 * j + 3 + c]);
+        run_ops<CHAIN, 2>(q, sops, 0, S.n_ops, dup2(S.one));
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int c = 0; c < 3; ++c) { v[6 * j + c] = q[3 * j + c].x; v[6 * j + 3 + c] = q[3 * j + c].y; }
+    }
 
     if (n == PX_PER_THREAD) {
         if (DST_IS_U8) {
@@ -370,7 +426,8 @@ __device__ __forceinline__ void body_resize(const DevPlane& P, const DevSeq& S, 
     /* The value every output element outside the region of interest ends up with: the
        default value run through the continuation (resize.h:84-86). */
     float bgv[3] = {S.bg[0], S.bg[1], S.bg[2]};
-    run_ops<CHAIN, 1>(bgv, sops, S.n_pre, S.n_ops);
+    const float2 one = dup2(S.one);
+    run_ops_1<CHAIN>(bgv, sops, S.n_pre, S.n_ops, one);
     float bg4[12];
 #pragma unroll
     for (int i = 0; i < PX_PER_THREAD; ++i) { bg4[3 * i] = bgv[0]; bg4[3 * i + 1] = bgv[1]; bg4[3 * i + 2] = bgv[2]; }
@@ -400,9 +457,11 @@ __device__ __forceinline__ void body_resize(const DevPlane& P, const DevSeq& S, 
            a few hundred contiguous bytes instead of a span four times as wide. */
         const int x0 = (int)(g_lo * PX_PER_THREAD + tile_x * gw * RESIZE_PX + gi);
         const int x_end = (int)(g_lo * PX_PER_THREAD + min(n_groups * PX_PER_THREAD, (tile_x + 1) * gw * RESIZE_PX));
-        /* horizontal taps and weights of the four columns, once per thread */
+        /* horizontal taps and weights of the thread's columns, once per thread; columns 2j and
+           2j+1 travel as one pair */
+        constexpr int NPAIR = RESIZE_PX / 2;
         uint32_t off0[RESIZE_PX], off1[RESIZE_PX]; /* U8X3: byte offsets in a source row; NV12: columns */
-        float wx0[RESIZE_PX], wx1[RESIZE_PX];
+        float2 wx0[NPAIR], wx1[NPAIR];
         uint32_t inside = 0, valid = 0;
 #pragma unroll
         for (int i = 0; i < RESIZE_PX; ++i) {
@@ -412,7 +471,8 @@ __device__ __forceinline__ void body_resize(const DevPlane& P, const DevSeq& S, 
             const Axis ax = make_axis(in ? x - x1 : 0, P.fx, P.crop_w);
             if (SRC == FKB_SRC_NV12) { off0[i] = (uint32_t)(ax.i0 + P.crop_x); off1[i] = (uint32_t)(ax.i1 + P.crop_x); }
             else { off0[i] = (uint32_t)ax.i0 * 3u; off1[i] = (uint32_t)ax.i1 * 3u; }
-            wx0[i] = ax.w0; wx1[i] = ax.w1;
+            if (i & 1) { wx0[i / 2].y = ax.w0; wx1[i / 2].y = ax.w1; }
+            else { wx0[i / 2].x = ax.w0; wx1[i / 2].x = ax.w1; }
             inside |= (in ? 1u : 0u) << i;
         }
         const float fy = P.fy;
@@ -421,57 +481,32 @@ __device__ __forceinline__ void body_resize(const DevPlane& P, const DevSeq& S, 
         const uint8_t* const chroma0 = P.src + (size_t)src_pitch * P.src_height;
         const bool yuv = S.pre_kind == PRE_YUV_BT709;
 
-#ifdef FKB_EXP_PREFETCH_TILE
-        if (SRC == FKB_SRC_U8X3) {
-            /* pull the tile's whole source footprint towards L2: one line per thread per step */
-            const int y_last = min(y2, row0 + (int)(rs * RESIZE_ROWS_PER_THREAD) - 1);
-            const int ia = make_axis(row0 - y1, fy, crop_h).i0, ib = make_axis(y_last - y1, fy, crop_h).i1;
-            const uint32_t row_bytes = (uint32_t)P.crop_w * 3u;
-            const uint32_t lines = (row_bytes + 127u) / 128u + 1u;
-            const uint32_t total = (uint32_t)(ib - ia + 1) * lines;
-            for (uint32_t k = threadIdx.x; k < total; k += nthreads) {
-                const uint32_t r = k / lines, l = k - r * lines;
-                const uint32_t o = min(l * 128u, row_bytes - 1u);
-                asm volatile("prefetch.global.L2 [%0];" ::"l"(src0 + (size_t)(ia + (int)r) * src_pitch + o));
-            }
-        }
-#endif
 #pragma unroll 1
         for (int j = 0; j < RESIZE_ROWS_PER_THREAD; ++j) {
             const int y = row0 + (int)slot + j * (int)rs;
             if (y > y2) break;
             const Axis ay = make_axis(y - y1, fy, crop_h);
-            float v[3 * RESIZE_PX];
+            float2 v[3 * NPAIR];
             if (SRC == FKB_SRC_U8X3) {
-#ifdef FKB_EXP_HOT
-                const uint8_t* const r0 = src0 + (size_t)(ay.i0 & 3) * src_pitch;
-                const uint8_t* const r1 = src0 + (size_t)(ay.i1 & 3) * src_pitch;
-#else
                 const uint8_t* const r0 = src0 + (size_t)ay.i0 * src_pitch;
                 const uint8_t* const r1 = src0 + (size_t)ay.i1 * src_pitch;
-#endif
-#ifdef FKB_EXP_PREFETCH
-                if (j + 1 < RESIZE_ROWS_PER_THREAD && y + (int)rs <= y2) {
-                    const Axis an = make_axis(y + (int)rs - y1, fy, crop_h);
-                    const uint8_t* const n0 = src0 + (size_t)an.i0 * src_pitch;
-                    const uint8_t* const n1 = src0 + (size_t)an.i1 * src_pitch;
+                const float2 wy0 = dup2(ay.w0), wy1 = dup2(ay.w1);
 #pragma unroll
-                    for (int i = 0; i < RESIZE_PX; ++i) {
-                        asm volatile("prefetch.global.L1 [%0];" ::"l"(n0 + off0[i]));
-                        asm volatile("prefetch.global.L1 [%0];" ::"l"(n1 + off0[i]));
-                    }
-                }
-#endif
-#pragma unroll
-                for (int i = 0; i < RESIZE_PX; ++i) {
-                    const uint8_t* p00 = r0 + off0[i]; const uint8_t* p10 = r0 + off1[i];
-                    const uint8_t* p01 = r1 + off0[i]; const uint8_t* p11 = r1 + off1[i];
-                    const float w00 = __fmul_rn(wx0[i], ay.w0), w10 = __fmul_rn(wx1[i], ay.w0);
-                    const float w01 = __fmul_rn(wx0[i], ay.w1), w11 = __fmul_rn(wx1[i], ay.w1);
+                for (int k = 0; k < NPAIR; ++k) {
+                    const uint8_t* a00 = r0 + off0[2 * k]; const uint8_t* a10 = r0 + off1[2 * k];
+                    const uint8_t* a01 = r1 + off0[2 * k]; const uint8_t* a11 = r1 + off1[2 * k];
+                    const uint8_t* b00 = r0 + off0[2 * k + 1]; const uint8_t* b10 = r0 + off1[2 * k + 1];
+                    const uint8_t* b01 = r1 + off0[2 * k + 1]; const uint8_t* b11 = r1 + off1[2 * k + 1];
+                    const float2 w00 = mul2(wx0[k], wy0), w10 = mul2(wx1[k], wy0);
+                    const float2 w01 = mul2(wx0[k], wy1), w11 = mul2(wx1[k], wy1);
 #pragma unroll
                     for (int c = 0; c < 3; ++c) {
-                        v[3 * i + c] = blend(u8_to_float(__ldg(p00 + c)), u8_to_float(__ldg(p10 + c)),
-                                             u8_to_float(__ldg(p01 + c)), u8_to_float(__ldg(p11 + c)), w00, w10, w01, w11);
+                        const float2 p00 = make_float2(u8_to_float(__ldg(a00 + c)), u8_to_float(__ldg(b00 + c)));
+                        const float2 p10 = make_float2(u8_to_float(__ldg(a10 + c)), u8_to_float(__ldg(b10 + c)));
+                        const float2 p01 = make_float2(u8_to_float(__ldg(a01 + c)), u8_to_float(__ldg(b01 + c)));
+                        const float2 p11 = make_float2(u8_to_float(__ldg(a11 + c)), u8_to_float(__ldg(b11 + c)));
+                        /* ((p00*w00 + p10*w10) + p01*w01) + p11*w11, every product and sum rounded */
+                        v[3 * k + c] = add2(add2(add2(mul2(p00, w00), mul2(p10, w10), one), mul2(p01, w01), one), mul2(p11, w11), one);
                     }
                 }
             } else {
@@ -486,49 +521,50 @@ __device__ __forceinline__ void body_resize(const DevPlane& P, const DevSeq& S, 
                 const bool need_row1 = ay.w1 != 0.0f;
 #pragma unroll
                 for (int i = 0; i < RESIZE_PX; ++i) {
-                    const bool need_col1 = wx1[i] != 0.0f;
+                    const float wxa = (i & 1) ? wx0[i / 2].y : wx0[i / 2].x;
+                    const float wxb = (i & 1) ? wx1[i / 2].y : wx1[i / 2].x;
+                    const bool need_col1 = wxb != 0.0f;
                     const uint32_t xa = off0[i], xb = off1[i];
                     const uint32_t ca = (xa >> 1) * 2u, cb = (xb >> 1) * 2u;
                     float t[3];
                     t[0] = u8_to_float(__ldg(l0 + xa)); t[1] = u8_to_float(__ldg(c0 + ca)); t[2] = u8_to_float(__ldg(c0 + ca + 1));
                     if (yuv) yuv_to_rgb_bt709_full(t[0], t[1], t[2]);
-                    const float w00 = __fmul_rn(wx0[i], ay.w0);
+                    const float w00 = __fmul_rn(wxa, ay.w0);
                     float acc[3] = {__fmul_rn(t[0], w00), __fmul_rn(t[1], w00), __fmul_rn(t[2], w00)};
                     if (need_col1) {
                         t[0] = u8_to_float(__ldg(l0 + xb)); t[1] = u8_to_float(__ldg(c0 + cb)); t[2] = u8_to_float(__ldg(c0 + cb + 1));
                         if (yuv) yuv_to_rgb_bt709_full(t[0], t[1], t[2]);
-                        const float w10 = __fmul_rn(wx1[i], ay.w0);
+                        const float w10 = __fmul_rn(wxb, ay.w0);
 #pragma unroll
                         for (int c = 0; c < 3; ++c) acc[c] = __fadd_rn(acc[c], __fmul_rn(t[c], w10));
                     }
                     if (need_row1) {
                         t[0] = u8_to_float(__ldg(l1 + xa)); t[1] = u8_to_float(__ldg(c1 + ca)); t[2] = u8_to_float(__ldg(c1 + ca + 1));
                         if (yuv) yuv_to_rgb_bt709_full(t[0], t[1], t[2]);
-                        const float w01 = __fmul_rn(wx0[i], ay.w1);
+                        const float w01 = __fmul_rn(wxa, ay.w1);
 #pragma unroll
                         for (int c = 0; c < 3; ++c) acc[c] = __fadd_rn(acc[c], __fmul_rn(t[c], w01));
                         if (need_col1) {
                             t[0] = u8_to_float(__ldg(l1 + xb)); t[1] = u8_to_float(__ldg(c1 + cb)); t[2] = u8_to_float(__ldg(c1 + cb + 1));
                             if (yuv) yuv_to_rgb_bt709_full(t[0], t[1], t[2]);
-                            const float w11 = __fmul_rn(wx1[i], ay.w1);
+                            const float w11 = __fmul_rn(wxb, ay.w1);
 #pragma unroll
                             for (int c = 0; c < 3; ++c) acc[c] = __fadd_rn(acc[c], __fmul_rn(t[c], w11));
                         }
                     }
-                    v[3 * i] = acc[0]; v[3 * i + 1] = acc[1]; v[3 * i + 2] = acc[2];
-                }
-            }
-            run_ops<CHAIN, RESIZE_PX>(v, sops, S.n_pre, S.n_ops);
-            if (inside != (1u << RESIZE_PX) - 1u) { /* a group straddling the edge of the region */
 #pragma unroll
-                for (int i = 0; i < RESIZE_PX; ++i) {
-                    if (!((inside >> i) & 1u)) { v[3 * i] = bgv[0]; v[3 * i + 1] = bgv[1]; v[3 * i + 2] = bgv[2]; }
+                    for (int c = 0; c < 3; ++c) { if (i & 1) v[3 * (i / 2) + c].y = acc[c]; else v[3 * (i / 2) + c].x = acc[c]; }
                 }
             }
+            run_ops<CHAIN, NPAIR>(v, sops, S.n_pre, S.n_ops, one);
 #pragma unroll
             for (int i = 0; i < RESIZE_PX; ++i) {
-                if ((valid >> i) & 1u)
-                    store_pixel<PLANAR>(dst, dst_pitch, dst_cstride, x0 + i * (int)gw, y, v[3 * i], v[3 * i + 1], v[3 * i + 2]);
+                if ((valid >> i) & 1u) {
+                    const bool in = (inside >> i) & 1u; /* false: a column group straddling the edge of the region */
+                    const float2 a = v[3 * (i / 2)], b = v[3 * (i / 2) + 1], c = v[3 * (i / 2) + 2];
+                    store_pixel<PLANAR>(dst, dst_pitch, dst_cstride, x0 + i * (int)gw, y, in ? ((i & 1) ? a.y : a.x) : bgv[0],
+                                        in ? ((i & 1) ? b.y : b.x) : bgv[1], in ? ((i & 1) ? c.y : c.x) : bgv[2]);
+                }
             }
         }
     }
@@ -548,11 +584,182 @@ __device__ __forceinline__ void body_resize(const DevPlane& P, const DevSeq& S, 
 }
 
 /* ------------------------------------------------------------------------------------ */
+/* body: bilinear resize of uchar3 from a source footprint staged in shared memory      */
+/* ------------------------------------------------------------------------------------ */
+
+/* Asynchronous bulk copies (the copy engine that also serves tensor-map TMA) and the mbarrier
+ * that counts their bytes.  No cluster launch and no multicast: every copy lands in the shared
+ * memory of the block that issued it. */
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t mbar, uint32_t arrivals) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(mbar), "r"(arrivals) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t mbar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mbar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t mbar) {
+    asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+                 "r"(bytes), "r"(mbar)
+                 : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t mbar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(mbar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+/* Waits for phase `parity` with an iteration limit (each try_wait itself blocks for a
+   hardware-defined time slice); false when the limit ran out. */
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t mbar, uint32_t parity) {
+    for (uint32_t i = 0; i < STAGED_WAIT_LIMIT; ++i)
+        if (mbar_try_wait(mbar, parity)) return true;
+    return false;
+}
+
+/* A work item is a band of STAGED rows of one plane's region of interest, all columns.  The rows
+ * of the crop that the band's taps touch are copied into shared memory by bulk copies (one per
+ * source row, started and sized on 16-byte boundaries), then every thread interpolates a pair
+ * of columns `gw` apart down its row slots, reading its twelve tap bytes per pixel from shared
+ * memory.  Vertical tap positions and weights are computed once per row of the band. */
+template <uint32_t CHAIN, bool PLANAR>
+__device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevSeq& S, const DevOp* sops, uint32_t local,
+                                                   unsigned char* staged_mem, uint32_t* status) {
+    uint8_t* const dst = P.dst;
+    const uint32_t dst_pitch = P.dst_pitch, dst_cstride = P.dst_cstride;
+    const uint32_t groups_per_row = P.dst_w / PX_PER_THREAD;
+    const int x1 = P.x1, y1 = P.y1, x2 = P.x2, y2 = P.y2;
+    const uint32_t g_lo = (uint32_t)x1 / PX_PER_THREAD;
+    const uint32_t n_groups = (uint32_t)x2 / PX_PER_THREAD - g_lo + 1;
+    const uint32_t n_rows = (uint32_t)(y2 - y1 + 1);
+    const uint32_t nthreads = blockDim.x;
+
+    float bgv[3] = {S.bg[0], S.bg[1], S.bg[2]};
+    const float2 one = dup2(S.one);
+    run_ops_1<CHAIN>(bgv, sops, S.n_pre, S.n_ops, one);
+    float bg4[12];
+#pragma unroll
+    for (int i = 0; i < PX_PER_THREAD; ++i) { bg4[3 * i] = bgv[0]; bg4[3 * i + 1] = bgv[1]; bg4[3 * i + 2] = bgv[2]; }
+
+    if (local >= P.roi_items) {
+        /* store-only item: rows above and below the region of interest */
+        const uint32_t total = (P.dst_h - n_rows) * groups_per_row;
+        uint32_t idx = (local - P.roi_items) * (nthreads * BG_GROUPS_PER_THREAD) + threadIdx.x;
+#pragma unroll 1
+        for (int k = 0; k < BG_GROUPS_PER_THREAD; ++k, idx += nthreads) {
+            if (idx >= total) break;
+            const uint32_t r = idx / groups_per_row, g = idx - r * groups_per_row;
+            const int y = (int)r < y1 ? (int)r : (int)(r + n_rows);
+            store_group<PLANAR>(dst, dst_pitch, dst_cstride, (int)(g * PX_PER_THREAD), y, bg4);
+        }
+        return;
+    }
+
+    /* shared memory: | mbarrier (16 B) | row table | staged source rows | */
+    uint64_t* const mbar_ptr = reinterpret_cast<uint64_t*>(staged_mem);
+    float4* const row_tab = reinterpret_cast<float4*>(staged_mem + 16);
+    unsigned char* const stage = staged_mem + 16 + STAGED_MAX_ROWS * sizeof(float4);
+    const uint32_t mbar = smem_addr(mbar_ptr);
+
+    const uint32_t band_rows = P.tiles_x, gw = P.gw, rs = P.rs; /* rows per band, threads across, row slots */
+    const int ya = y1 + (int)(local * band_rows);
+    const int yb = min(ya + (int)band_rows - 1, y2);
+    const int crop_h = P.crop_h;
+    const float fy = P.fy;
+
+    /* source bytes of one crop row, widened to 16-byte boundaries */
+    const uint32_t row_first = ((uint32_t)P.crop_x * 3u) & ~15u;
+    const uint32_t phase = (uint32_t)P.crop_x * 3u - row_first;
+    const uint32_t row_len = (phase + (uint32_t)P.crop_w * 3u + 15u) & ~15u;
+
+    const int src_first = make_axis(ya - y1, fy, crop_h).i0;
+    const int src_last = make_axis(yb - y1, fy, crop_h).i1;
+    const uint32_t n_src = (uint32_t)(src_last - src_first + 1);
+    if (threadIdx.x == 0) {
+        mbar_init(mbar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_expect_tx(mbar, n_src * row_len);
+    }
+    if (threadIdx.x <= (uint32_t)(yb - ya)) {
+        const Axis ay = make_axis(ya + (int)threadIdx.x - y1, fy, crop_h);
+        row_tab[threadIdx.x] = make_float4(__int_as_float(ay.i0), __int_as_float(ay.i1), ay.w0, ay.w1);
+    }
+    __syncthreads(); /* barrier initialised and armed, row table written */
+    {
+        const uint8_t* g = P.src + (size_t)(P.crop_y + src_first) * P.src_pitch + row_first;
+        for (uint32_t r = threadIdx.x; r < n_src; r += nthreads)
+            bulk_copy_g2s(smem_addr(stage + r * row_len), g + (size_t)r * P.src_pitch, row_len, mbar);
+    }
+
+    /* the thread's two columns and their horizontal taps, while the copies are in flight */
+    const uint32_t slot = threadIdx.x / gw, gi = threadIdx.x - slot * gw;
+    const int xa = (int)(g_lo * PX_PER_THREAD + gi), xb = xa + (int)gw;
+    const int x_end = (int)((g_lo + n_groups) * PX_PER_THREAD);
+    const bool in_a = xa >= x1 && xa <= x2, in_b = xb >= x1 && xb <= x2;
+    const bool valid_b = xb < x_end;
+    const Axis axa = make_axis(in_a ? xa - x1 : 0, P.fx, P.crop_w);
+    const Axis axb = make_axis(in_b ? xb - x1 : 0, P.fx, P.crop_w);
+    const uint32_t oa0 = phase + (uint32_t)axa.i0 * 3u, oa1 = phase + (uint32_t)axa.i1 * 3u;
+    const uint32_t ob0 = phase + (uint32_t)axb.i0 * 3u, ob1 = phase + (uint32_t)axb.i1 * 3u;
+    const float2 wx0 = make_float2(axa.w0, axb.w0), wx1 = make_float2(axa.w1, axb.w1);
+
+    const bool arrived = mbar_wait_bounded(mbar, 0);
+    if (!arrived) {
+        /* never expected: record it and give the copies one more bounded chance to land before
+           this block's shared memory is released */
+        atomicExch(status, STATUS_STAGED_WAIT_TIMEOUT);
+        (void)mbar_wait_bounded(mbar, 0);
+        return;
+    }
+
+    if (slot < rs) {
+#pragma unroll 1
+        for (int y = ya + (int)slot; y <= yb; y += (int)rs) {
+            const float4 rt = row_tab[y - ya];
+            const unsigned char* const r0 = stage + (uint32_t)(__float_as_int(rt.x) - src_first) * row_len;
+            const unsigned char* const r1 = stage + (uint32_t)(__float_as_int(rt.y) - src_first) * row_len;
+            const float2 wy0 = dup2(rt.z), wy1 = dup2(rt.w);
+            const float2 w00 = mul2(wx0, wy0), w10 = mul2(wx1, wy0), w01 = mul2(wx0, wy1), w11 = mul2(wx1, wy1);
+            float2 v[3];
+#pragma unroll
+            for (int c = 0; c < 3; ++c) {
+                const float2 p00 = make_float2(u8_to_float(r0[oa0 + c]), u8_to_float(r0[ob0 + c]));
+                const float2 p10 = make_float2(u8_to_float(r0[oa1 + c]), u8_to_float(r0[ob1 + c]));
+                const float2 p01 = make_float2(u8_to_float(r1[oa0 + c]), u8_to_float(r1[ob0 + c]));
+                const float2 p11 = make_float2(u8_to_float(r1[oa1 + c]), u8_to_float(r1[ob1 + c]));
+                /* ((p00*w00 + p10*w10) + p01*w01) + p11*w11, every product and sum rounded */
+                v[c] = add2(add2(add2(mul2(p00, w00), mul2(p10, w10), one), mul2(p01, w01), one), mul2(p11, w11), one);
+            }
+            run_ops<CHAIN, 1>(v, sops, S.n_pre, S.n_ops, one);
+            store_pixel<PLANAR>(dst, dst_pitch, dst_cstride, xa, y, in_a ? v[0].x : bgv[0], in_a ? v[1].x : bgv[1],
+                                in_a ? v[2].x : bgv[2]);
+            if (valid_b)
+                store_pixel<PLANAR>(dst, dst_pitch, dst_cstride, xb, y, in_b ? v[0].y : bgv[0], in_b ? v[1].y : bgv[1],
+                                    in_b ? v[2].y : bgv[2]);
+        }
+    }
+
+    /* background to the left and right of this band's rows */
+    const uint32_t n_side = groups_per_row - n_groups;
+    if (n_side != 0) {
+        const uint32_t total = (uint32_t)(yb - ya + 1) * n_side;
+#pragma unroll 1
+        for (uint32_t idx = threadIdx.x; idx < total; idx += nthreads) {
+            const uint32_t r = idx / n_side, b = idx - r * n_side;
+            const uint32_t g = b < g_lo ? b : b + n_groups;
+            store_group<PLANAR>(dst, dst_pitch, dst_cstride, (int)(g * PX_PER_THREAD), ya + (int)r, bg4);
+        }
+    }
+}
+
+/* ------------------------------------------------------------------------------------ */
 /* the kernel                                                                           */
 /* ------------------------------------------------------------------------------------ */
 template <uint32_t CLASS, uint32_t CHAIN>
 __device__ __forceinline__ void run_body(uint32_t cls, const DevPlane& P, const DevSeq& S, const DevOp* sops,
-                                         uint32_t local) {
+                                         uint32_t local, unsigned char* staged_mem, uint32_t* status) {
     if (CLASS != CLASS_MIXED) cls = CLASS;
     switch (cls) {
         case CLASS_FLAT_U8_F32: body_flat<CHAIN, true, false>(P, S, sops, local); break;
@@ -561,16 +768,25 @@ __device__ __forceinline__ void run_body(uint32_t cls, const DevPlane& P, const 
         case CLASS_RESIZE_U8_PLANAR: body_resize<CHAIN, FKB_SRC_U8X3, true>(P, S, sops, local); break;
         case CLASS_RESIZE_U8_PACKED: body_resize<CHAIN, FKB_SRC_U8X3, false>(P, S, sops, local); break;
         case CLASS_RESIZE_NV12_PACKED: body_resize<CHAIN, FKB_SRC_NV12, false>(P, S, sops, local); break;
+        case CLASS_RESIZE_U8_PLANAR_STAGED: body_resize_staged<CHAIN, true>(P, S, sops, local, staged_mem, status); break;
+        case CLASS_RESIZE_U8_PACKED_STAGED: body_resize_staged<CHAIN, false>(P, S, sops, local, staged_mem, status); break;
         default: body_generic(P, S, sops, local); break;
     }
 }
 
-#ifndef FKB_MIN_BLOCKS
-#define FKB_MIN_BLOCKS 1
+/* Resident blocks per SM the compiler must leave room for.  The staged bodies hide the latency
+   of their shared-memory reads and of the next blocks' bulk copies with four blocks (64
+   registers per thread); the bodies that read taps straight from global memory keep all their
+   loads in flight in registers instead. */
+#ifndef FKB_STAGED_MIN_BLOCKS
+#define FKB_STAGED_MIN_BLOCKS 4
 #endif
+constexpr int min_blocks_of(uint32_t cls) {
+    return (cls == CLASS_RESIZE_U8_PLANAR_STAGED || cls == CLASS_RESIZE_U8_PACKED_STAGED) ? FKB_STAGED_MIN_BLOCKS : 1;
+}
 template <uint32_t CLASS, uint32_t CHAIN>
-__global__ void __launch_bounds__(BLOCK_THREADS, FKB_MIN_BLOCKS) fused_plan_kernel(const __grid_constant__ LaunchArgs a) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
+__global__ void __launch_bounds__(BLOCK_THREADS, min_blocks_of(CLASS)) fused_plan_kernel(const __grid_constant__ LaunchArgs a) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
     DevOp* sops = reinterpret_cast<DevOp*>(smem_raw);
     __shared__ DevPlane s_plane;
     __shared__ DevSeq s_seq;
@@ -607,7 +823,9 @@ __global__ void __launch_bounds__(BLOCK_THREADS, FKB_MIN_BLOCKS) fused_plan_kern
         }
     }
     __syncthreads();
-    run_body<CLASS, CHAIN>(s_plane.plane_class, s_plane, s_seq, sops, local);
+    /* staged classes: the region after the operation cache, on a 128-byte boundary */
+    unsigned char* staged_mem = smem_raw + (((a.max_seq_ops > 0 ? a.max_seq_ops : 1u) * (uint32_t)sizeof(DevOp) + 127u) & ~127u);
+    run_body<CLASS, CHAIN>(s_plane.plane_class, s_plane, s_seq, sops, local, staged_mem, a.status);
 }
 
 /* ------------------------------------------------------------------------------------ */
@@ -626,17 +844,32 @@ __global__ void __launch_bounds__(BLOCK_THREADS, FKB_MIN_BLOCKS) fused_plan_kern
     X(chain_of(CH_ADD, CH_DIVC))                  /* Add, Div                                                  */ \
     X(chain_of(CH_SWAP, CH_MUL, CH_SAT))          /* RGB2BGR, Mul, SaturateCast                                */
 
+/* Launches one instantiation; the first launch that needs more than the default 48 KB of
+   dynamic shared memory raises the kernel's limit (once per instantiation and device). */
+template <uint32_t CLASS, uint32_t CHAIN>
+static cudaError_t launch_one(const LaunchArgs& a, size_t smem, cudaStream_t stream) {
+    if (smem > 48 * 1024) {
+        static size_t raised[64] = {};
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return e;
+        if (dev < 0 || dev >= 64 || raised[dev] < smem) {
+            e = cudaFuncSetAttribute(fused_plan_kernel<CLASS, CHAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return e;
+            if (dev >= 0 && dev < 64) raised[dev] = smem;
+        }
+    }
+    fused_plan_kernel<CLASS, CHAIN><<<a.total_items, a.block_threads, smem, stream>>>(a);
+    return cudaGetLastError();
+}
+
 template <uint32_t CLASS>
 static cudaError_t launch_class(uint32_t chain, const LaunchArgs& a, size_t smem, cudaStream_t stream) {
-#define FKB_LAUNCH_CASE(CH)                                                                  \
-    if (chain == (CH)) {                                                                     \
-        fused_plan_kernel<CLASS, (CH)><<<a.total_items, a.block_threads, smem, stream>>>(a); \
-        return cudaGetLastError();                                                           \
-    }
+#define FKB_LAUNCH_CASE(CH) \
+    if (chain == (CH)) return launch_one<CLASS, (CH)>(a, smem, stream);
     FKB_CHAIN_MENU(FKB_LAUNCH_CASE)
 #undef FKB_LAUNCH_CASE
-    fused_plan_kernel<CLASS, CHAIN_INTERPRET><<<a.total_items, a.block_threads, smem, stream>>>(a);
-    return cudaGetLastError();
+    return launch_one<CLASS, CHAIN_INTERPRET>(a, smem, stream);
 }
 
 bool chain_is_compiled(uint32_t chain) {
@@ -648,7 +881,8 @@ bool chain_is_compiled(uint32_t chain) {
 
 /* launch_class: one of CLASS_* or CLASS_MIXED; chain: a menu chain or CHAIN_INTERPRET. */
 cudaError_t launch_plan_kernel(uint32_t launch_cls, uint32_t chain, const LaunchArgs& a, cudaStream_t stream) {
-    const size_t smem = (size_t)(a.max_seq_ops > 0 ? a.max_seq_ops : 1) * sizeof(DevOp);
+    const size_t ops_bytes = (size_t)(a.max_seq_ops > 0 ? a.max_seq_ops : 1) * sizeof(DevOp);
+    const size_t smem = a.staged_bytes ? ((ops_bytes + 127) & ~(size_t)127) + a.staged_bytes : ops_bytes;
     switch (launch_cls) {
         case CLASS_FLAT_U8_F32: return launch_class<CLASS_FLAT_U8_F32>(chain, a, smem, stream);
         case CLASS_FLAT_F32_F32: return launch_class<CLASS_FLAT_F32_F32>(chain, a, smem, stream);
@@ -656,12 +890,10 @@ cudaError_t launch_plan_kernel(uint32_t launch_cls, uint32_t chain, const Launch
         case CLASS_RESIZE_U8_PLANAR: return launch_class<CLASS_RESIZE_U8_PLANAR>(chain, a, smem, stream);
         case CLASS_RESIZE_U8_PACKED: return launch_class<CLASS_RESIZE_U8_PACKED>(chain, a, smem, stream);
         case CLASS_RESIZE_NV12_PACKED: return launch_class<CLASS_RESIZE_NV12_PACKED>(chain, a, smem, stream);
-        case CLASS_GENERIC:
-            fused_plan_kernel<CLASS_GENERIC, CHAIN_INTERPRET><<<a.total_items, a.block_threads, smem, stream>>>(a);
-            return cudaGetLastError();
-        default:
-            fused_plan_kernel<CLASS_MIXED, CHAIN_INTERPRET><<<a.total_items, a.block_threads, smem, stream>>>(a);
-            return cudaGetLastError();
+        case CLASS_RESIZE_U8_PLANAR_STAGED: return launch_class<CLASS_RESIZE_U8_PLANAR_STAGED>(chain, a, smem, stream);
+        case CLASS_RESIZE_U8_PACKED_STAGED: return launch_class<CLASS_RESIZE_U8_PACKED_STAGED>(chain, a, smem, stream);
+        case CLASS_GENERIC: return launch_one<CLASS_GENERIC, CHAIN_INTERPRET>(a, smem, stream);
+        default: return launch_one<CLASS_MIXED, CHAIN_INTERPRET>(a, smem, stream);
     }
 }
 
