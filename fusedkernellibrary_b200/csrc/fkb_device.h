@@ -76,9 +76,10 @@ struct LaunchArgs {
     const DevPlane* planes;
     const DevSeq* seqs;
     const DevOp* ops;
-    const uint32_t* item_start; /* n_planes + 1 prefix sums of work items per plane          */
+    const uint4* items;         /* one entry per thread block: plane, tile within the plane,  */
+                                /* sequence | operations << 16, first operation                */
     uint32_t n_planes;
-    uint32_t uniform_items;     /* > 0: every plane has this many work items                  */
+    uint32_t reserved;
     uint32_t total_items;
     uint32_t max_seq_ops;       /* longest sequence: sizes the shared-memory op cache         */
     uint32_t block_threads;     /* threads per block of this launch (multiple of 32, <= 256)  */

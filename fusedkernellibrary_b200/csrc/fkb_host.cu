@@ -55,7 +55,7 @@ static int fail_cuda(cudaError_t e, const char* what, int line) {
 /* ------------------------------------------------------------------------------------ */
 struct fkb_plan {
     int device = -1;
-    void* d_block = nullptr; /* one allocation: planes | seqs | ops | item_start */
+    void* d_block = nullptr; /* one allocation: planes | seqs | ops | work-item table | status word */
     size_t d_bytes = 0;
     LaunchArgs args{};
     uint32_t launch_class = CLASS_GENERIC;
@@ -86,14 +86,21 @@ struct HostImage {
     size_t off_seqs() const { return planes.size() * sizeof(DevPlane); }
     size_t off_ops() const { return off_seqs() + seqs.size() * sizeof(DevSeq); }
     size_t off_items() const { return off_ops() + std::max<size_t>(ops.size(), 1) * sizeof(DevOp); }
-    size_t off_status() const { return (off_items() + item_start.size() * sizeof(uint32_t) + 15) & ~(size_t)15; }
+    size_t off_status() const { return off_items() + (size_t)total_items * 16; }
     size_t bytes() const { return off_status() + 16; }
 
     void serialize(unsigned char* dst) const {
         std::memcpy(dst + off_planes(), planes.data(), planes.size() * sizeof(DevPlane));
         std::memcpy(dst + off_seqs(), seqs.data(), seqs.size() * sizeof(DevSeq));
         if (!ops.empty()) std::memcpy(dst + off_ops(), ops.data(), ops.size() * sizeof(DevOp));
-        std::memcpy(dst + off_items(), item_start.data(), item_start.size() * sizeof(uint32_t));
+        /* work-item table: item_start holds the prefix sums of the items per plane */
+        uint32_t* e = reinterpret_cast<uint32_t*>(dst + off_items());
+        for (size_t i = 0; i < planes.size(); ++i) {
+            const DevSeq& q = seqs[planes[i].seq];
+            for (uint32_t l = 0, n = item_start[i + 1] - item_start[i]; l < n; ++l, e += 4) {
+                e[0] = (uint32_t)i; e[1] = l; e[2] = planes[i].seq | ((uint32_t)q.n_ops << 16); e[3] = (uint32_t)q.ops_begin;
+            }
+        }
         std::memset(dst + off_status(), 0, 16);
     }
     LaunchArgs args_for(const unsigned char* d_base) const {
@@ -101,9 +108,8 @@ struct HostImage {
         a.planes = reinterpret_cast<const DevPlane*>(d_base + off_planes());
         a.seqs = reinterpret_cast<const DevSeq*>(d_base + off_seqs());
         a.ops = reinterpret_cast<const DevOp*>(d_base + off_ops());
-        a.item_start = reinterpret_cast<const uint32_t*>(d_base + off_items());
+        a.items = reinterpret_cast<const uint4*>(d_base + off_items());
         a.n_planes = (uint32_t)planes.size();
-        a.uniform_items = uniform_items;
         a.total_items = total_items;
         a.max_seq_ops = max_seq_ops;
         a.block_threads = block_threads;
@@ -473,7 +479,8 @@ static StagedTiling staged_tiling(const DevPlane& dp, uint32_t block_threads) {
     const uint32_t phase = (uint32_t)dp.crop_x * 3u - row_first;
     const uint32_t row_len = (phase + (uint32_t)dp.crop_w * 3u + 15u) & ~15u;
     if (row_first + row_len > dp.src_pitch) return t; /* never reads past the end of a row */
-    const uint32_t max_src_rows = STAGED_MAX_STAGE_BYTES / row_len;
+    /* the kernel reads whole words around the last tap: 16 spare bytes behind the last row */
+    const uint32_t max_src_rows = (STAGED_MAX_STAGE_BYTES - 16) / row_len;
     if (max_src_rows < 2) return t;
     t.gw = pairs;
     t.rs = block_threads / pairs;
@@ -497,7 +504,7 @@ static StagedTiling staged_tiling(const DevPlane& dp, uint32_t block_threads) {
     if (band > t.rs) band -= band % t.rs; /* whole rounds of the row slots */
     t.band_rows = band;
     t.n_bands = (n_rows + band - 1) / band;
-    t.stage_bytes = worst_rows(band) * row_len;
+    t.stage_bytes = worst_rows(band) * row_len + 16;
     t.ok = true;
     return t;
 }
@@ -507,6 +514,7 @@ static bool aligned(const void* p, uintptr_t a) { return (reinterpret_cast<uintp
 static int lower(const fkb_plan_desc* d, HostImage& img) {
     if (!d) return fail(FKB_ERR_INVALID_ARGUMENT, "plan description is NULL");
     if (!d->sequences || d->n_sequences <= 0) return fail(FKB_ERR_INVALID_ARGUMENT, "plan has no sequences");
+    if (d->n_sequences > 65535) return fail(FKB_ERR_INVALID_ARGUMENT, "plan has more than 65535 sequences");
     if (!d->planes || d->n_planes <= 0) return fail(FKB_ERR_INVALID_ARGUMENT, "plan has no planes (batch of 0)");
 
     img.seqs.resize(d->n_sequences);

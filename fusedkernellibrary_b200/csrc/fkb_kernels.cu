@@ -591,6 +591,12 @@ __device__ __forceinline__ void body_resize(const DevPlane& P, const DevSeq& S, 
  * that counts their bytes.  No cluster launch and no multicast: every copy lands in the shared
  * memory of the block that issued it. */
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+/* Three consecutive aligned words of shared memory at a 32-bit shared-window address. */
+__device__ __forceinline__ void lds32x3(uint32_t addr, uint32_t& w0, uint32_t& w1, uint32_t& w2) {
+    asm volatile("ld.shared.b32 %0, [%3];\n\tld.shared.b32 %1, [%3+4];\n\tld.shared.b32 %2, [%3+8];"
+                 : "=r"(w0), "=r"(w1), "=r"(w2)
+                 : "r"(addr));
+}
 __device__ __forceinline__ void mbar_init(uint32_t mbar, uint32_t arrivals) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(mbar), "r"(arrivals) : "memory");
 }
@@ -693,7 +699,11 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
             bulk_copy_g2s(smem_addr(stage + r * row_len), g + (size_t)r * P.src_pitch, row_len, mbar);
     }
 
-    /* the thread's two columns and their horizontal taps, while the copies are in flight */
+    /* The thread's two columns and their horizontal taps, while the copies are in flight.  The two
+       taps of a column are six consecutive bytes of a staged row (three when the second tap is
+       clamped onto the first, interpolation.h:76): they are fetched as the three aligned words
+       that hold them, shifted down to byte 0, and each byte is turned into a float by one byte
+       permute (2^23 + b) and half of a packed subtraction. */
     const uint32_t slot = threadIdx.x / gw, gi = threadIdx.x - slot * gw;
     const int xa = (int)(g_lo * PX_PER_THREAD + gi), xb = xa + (int)gw;
     const int x_end = (int)((g_lo + n_groups) * PX_PER_THREAD);
@@ -701,9 +711,14 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
     const bool valid_b = xb < x_end;
     const Axis axa = make_axis(in_a ? xa - x1 : 0, P.fx, P.crop_w);
     const Axis axb = make_axis(in_b ? xb - x1 : 0, P.fx, P.crop_w);
-    const uint32_t oa0 = phase + (uint32_t)axa.i0 * 3u, oa1 = phase + (uint32_t)axa.i1 * 3u;
-    const uint32_t ob0 = phase + (uint32_t)axb.i0 * 3u, ob1 = phase + (uint32_t)axb.i1 * 3u;
+    const uint32_t oa = phase + (uint32_t)axa.i0 * 3u, ob = phase + (uint32_t)axb.i0 * 3u;
+    const uint32_t word_a = oa & ~3u, word_b = ob & ~3u;
+    const uint32_t shift_a = (oa & 3u) * 8u, shift_b = (ob & 3u) * 8u;
+    const uint32_t second_a = axa.i1 == axa.i0 ? 0x3210u : 0x3543u; /* bytes of the second tap in (u0, u1) */
+    const uint32_t second_b = axb.i1 == axb.i0 ? 0x3210u : 0x3543u;
     const float2 wx0 = make_float2(axa.w0, axb.w0), wx1 = make_float2(axa.w1, axb.w1);
+    const uint32_t stage_addr = smem_addr(stage);
+    const float2 minus_2p23 = make_float2(-8388608.0f, -8388608.0f);
 
     const bool arrived = mbar_wait_bounded(mbar, 0);
     if (!arrived) {
@@ -715,29 +730,49 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
     }
 
     if (slot < rs) {
+        const bool plain = in_a && in_b && valid_b;
 #pragma unroll 1
         for (int y = ya + (int)slot; y <= yb; y += (int)rs) {
             const float4 rt = row_tab[y - ya];
-            const unsigned char* const r0 = stage + (uint32_t)(__float_as_int(rt.x) - src_first) * row_len;
-            const unsigned char* const r1 = stage + (uint32_t)(__float_as_int(rt.y) - src_first) * row_len;
+            const uint32_t row_addr[2] = {stage_addr + (uint32_t)(__float_as_int(rt.x) - src_first) * row_len,
+                                          stage_addr + (uint32_t)(__float_as_int(rt.y) - src_first) * row_len};
+            float2 tap[2][2][3]; /* [source row][first / second tap][channel] = (column a, column b) */
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                uint32_t wa0, wa1, wa2, wb0, wb1, wb2;
+                lds32x3(row_addr[r] + word_a, wa0, wa1, wa2);
+                lds32x3(row_addr[r] + word_b, wb0, wb1, wb2);
+                const uint32_t ua0 = __funnelshift_r(wa0, wa1, shift_a), ua1 = __funnelshift_r(wa1, wa2, shift_a);
+                const uint32_t ub0 = __funnelshift_r(wb0, wb1, shift_b), ub1 = __funnelshift_r(wb1, wb2, shift_b);
+                const uint32_t ta = __byte_perm(ua0, ua1, second_a), tb = __byte_perm(ub0, ub1, second_b);
+#pragma unroll
+                for (int c = 0; c < 3; ++c) {
+                    tap[r][0][c] = __fadd2_rn(make_float2(__uint_as_float(__byte_perm(ua0, 0x4B000000u, 0x7440 | c)),
+                                                          __uint_as_float(__byte_perm(ub0, 0x4B000000u, 0x7440 | c))), minus_2p23);
+                    tap[r][1][c] = __fadd2_rn(make_float2(__uint_as_float(__byte_perm(ta, 0x4B000000u, 0x7440 | c)),
+                                                          __uint_as_float(__byte_perm(tb, 0x4B000000u, 0x7440 | c))), minus_2p23);
+                }
+            }
             const float2 wy0 = dup2(rt.z), wy1 = dup2(rt.w);
             const float2 w00 = mul2(wx0, wy0), w10 = mul2(wx1, wy0), w01 = mul2(wx0, wy1), w11 = mul2(wx1, wy1);
             float2 v[3];
 #pragma unroll
             for (int c = 0; c < 3; ++c) {
-                const float2 p00 = make_float2(u8_to_float(r0[oa0 + c]), u8_to_float(r0[ob0 + c]));
-                const float2 p10 = make_float2(u8_to_float(r0[oa1 + c]), u8_to_float(r0[ob1 + c]));
-                const float2 p01 = make_float2(u8_to_float(r1[oa0 + c]), u8_to_float(r1[ob0 + c]));
-                const float2 p11 = make_float2(u8_to_float(r1[oa1 + c]), u8_to_float(r1[ob1 + c]));
                 /* ((p00*w00 + p10*w10) + p01*w01) + p11*w11, every product and sum rounded */
-                v[c] = add2(add2(add2(mul2(p00, w00), mul2(p10, w10), one), mul2(p01, w01), one), mul2(p11, w11), one);
+                v[c] = add2(add2(add2(mul2(tap[0][0][c], w00), mul2(tap[0][1][c], w10), one), mul2(tap[1][0][c], w01), one),
+                            mul2(tap[1][1][c], w11), one);
             }
             run_ops<CHAIN, 1>(v, sops, S.n_pre, S.n_ops, one);
-            store_pixel<PLANAR>(dst, dst_pitch, dst_cstride, xa, y, in_a ? v[0].x : bgv[0], in_a ? v[1].x : bgv[1],
-                                in_a ? v[2].x : bgv[2]);
-            if (valid_b)
-                store_pixel<PLANAR>(dst, dst_pitch, dst_cstride, xb, y, in_b ? v[0].y : bgv[0], in_b ? v[1].y : bgv[1],
-                                    in_b ? v[2].y : bgv[2]);
+            if (plain) {
+                store_pixel<PLANAR>(dst, dst_pitch, dst_cstride, xa, y, v[0].x, v[1].x, v[2].x);
+                store_pixel<PLANAR>(dst, dst_pitch, dst_cstride, xb, y, v[0].y, v[1].y, v[2].y);
+            } else { /* a column group straddling the edge of the region, or the last odd column */
+                store_pixel<PLANAR>(dst, dst_pitch, dst_cstride, xa, y, in_a ? v[0].x : bgv[0], in_a ? v[1].x : bgv[1],
+                                    in_a ? v[2].x : bgv[2]);
+                if (valid_b)
+                    store_pixel<PLANAR>(dst, dst_pitch, dst_cstride, xb, y, in_b ? v[0].y : bgv[0], in_b ? v[1].y : bgv[1],
+                                        in_b ? v[2].y : bgv[2]);
+            }
         }
     }
 
@@ -791,36 +826,18 @@ __global__ void __launch_bounds__(BLOCK_THREADS, min_blocks_of(CLASS)) fused_pla
     __shared__ DevPlane s_plane;
     __shared__ DevSeq s_seq;
 
-    const uint32_t item = blockIdx.x;
-    uint32_t plane_idx, local;
-    if (a.uniform_items) {
-        plane_idx = item / a.uniform_items;
-        local = item - plane_idx * a.uniform_items;
-    } else {
-        /* largest p with item_start[p] <= item */
-        uint32_t lo = 0, hi = a.n_planes;
-        while (hi - lo > 1) {
-            const uint32_t mid = (lo + hi) >> 1;
-            if (__ldg(a.item_start + mid) <= item) lo = mid; else hi = mid;
-        }
-        plane_idx = lo;
-        local = item - __ldg(a.item_start + lo);
-    }
+    /* One 16-byte table entry tells the block its plane, its tile within the plane and where the
+       plane's sequence and operations are, so that the three descriptors arrive in one round trip. */
+    const uint4 entry = __ldg(a.items + blockIdx.x);
+    const uint32_t plane_idx = entry.x, local = entry.y, seq = entry.z & 0xFFFFu, n_ops = entry.z >> 16, ops_begin = entry.w;
     if (threadIdx.x < sizeof(DevPlane) / 16) {
         reinterpret_cast<uint4*>(&s_plane)[threadIdx.x] =
             __ldg(reinterpret_cast<const uint4*>(a.planes + plane_idx) + threadIdx.x);
-    }
-    __syncthreads();
-    const uint32_t seq = s_plane.seq;
-    if (threadIdx.x < sizeof(DevSeq) / 16) {
-        reinterpret_cast<uint4*>(&s_seq)[threadIdx.x] = __ldg(reinterpret_cast<const uint4*>(a.seqs + seq) + threadIdx.x);
-    }
-    {
-        const DevSeq* gs = a.seqs + seq;
-        const int n_ops = __ldg(&gs->n_ops), begin = __ldg(&gs->ops_begin);
-        for (int k = threadIdx.x; k < n_ops; k += blockDim.x) {
-            reinterpret_cast<uint4*>(sops)[k] = __ldg(reinterpret_cast<const uint4*>(a.ops + begin + k));
-        }
+    } else if (threadIdx.x >= 32 && threadIdx.x < 32 + sizeof(DevSeq) / 16) {
+        reinterpret_cast<uint4*>(&s_seq)[threadIdx.x - 32] = __ldg(reinterpret_cast<const uint4*>(a.seqs + seq) + (threadIdx.x - 32));
+    } else if (threadIdx.x >= 64) {
+        for (uint32_t k = threadIdx.x - 64; k < n_ops; k += blockDim.x - 64)
+            reinterpret_cast<uint4*>(sops)[k] = __ldg(reinterpret_cast<const uint4*>(a.ops + ops_begin + k));
     }
     __syncthreads();
     /* staged classes: the region after the operation cache, on a 128-byte boundary */
