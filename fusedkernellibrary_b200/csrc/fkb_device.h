@@ -154,7 +154,7 @@ constexpr uint32_t STAGED_MAX_ROWS = 64;          /* output rows per band       
 #define FKB_STAGE_KB 40
 #endif
 constexpr uint32_t STAGED_MAX_STAGE_BYTES = FKB_STAGE_KB * 1024u;
-constexpr uint32_t STAGED_HEADER_BYTES = 16 + STAGED_MAX_ROWS * 16;
+constexpr uint32_t STAGED_HEADER_BYTES = 16 + STAGED_MAX_ROWS * 32;
 constexpr uint32_t STAGED_WAIT_LIMIT = 1u << 22;  /* try_wait rounds before a block gives up     */
 constexpr uint32_t STATUS_STAGED_WAIT_TIMEOUT = 1; /* a bulk copy did not complete in time        */
 

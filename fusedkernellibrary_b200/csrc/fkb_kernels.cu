@@ -41,6 +41,13 @@ __device__ __forceinline__ float saturate_round_u8(float f) {
    conversion off the quarter-rate conversion unit. */
 __device__ __forceinline__ float u8_to_float(uint32_t b) { return __int2float_rn((int)b); }
 
+#ifndef FKB_CVT_MODE
+#define FKB_CVT_MODE 1
+#endif
+/* Lowest byte of w, as float, by the integer-to-float conversion with a byte source. */
+template <int UNUSED>
+__device__ __forceinline__ float byte_to_float(uint32_t w) { return __int2float_rn((int)(w & 0xFFu)); }
+
 /* Byte LANE of a packed word, as float: one byte permute builds 2^23 + b, one add removes 2^23. */
 template <int LANE>
 __device__ __forceinline__ float packed_u8_to_float(uint32_t w) {
@@ -82,20 +89,48 @@ __device__ __forceinline__ float2 dup2(float a) { return make_float2(a, a); }
  * `one` is therefore (1, 1) read from the plan's descriptor at run time. */
 __device__ __forceinline__ float2 add2(float2 a, float2 b, float2 one) { return __ffma2_rn(a, one, b); }
 
-/* One operation on NPAIR pixel pairs held as v[3*j + channel] = (pixel 2j, pixel 2j+1); o carries
-   the per-channel parameter in y, z, w; r is the second slot of a two-slot operation. */
+/* The block's copy of its sequence's operation table, laid out for packed arithmetic: slot k
+ * holds four pairs, (p0,p0) (p1,p1) (p2,p2) (opcode bits, 0), so that a per-channel parameter
+ * arrives as a register pair with one 8-byte shared-memory load.  Sub is stored negated
+ * (x - p == x + (-p) exactly); a division by a plan-time constant takes two slots: -p, then 1/p. */
+struct OpSlot {
+    float2 p[3];
+    int32_t opcode;
+    int32_t pad;
+};
+static_assert(sizeof(OpSlot) == 32, "OpSlot layout");
+
+__device__ __forceinline__ void expand_op(const uint4 g, OpSlot* slot) {
+    const int32_t opcode = (int32_t)g.x;
+    float p0 = __uint_as_float(g.y), p1 = __uint_as_float(g.z), p2 = __uint_as_float(g.w);
+    if (opcode == FKB_OP_SUB) { p0 = -p0; p1 = -p1; p2 = -p2; }
+    reinterpret_cast<float4*>(slot)[0] = make_float4(p0, p0, p1, p1);
+    reinterpret_cast<float4*>(slot)[1] = make_float4(p2, p2, __int_as_float(opcode), 0.0f);
+}
+
+/* One operation on NPAIR pixel pairs held as v[3*j + channel] = (pixel 2j, pixel 2j+1); `s` is the
+   operation's slot (and s[1] the second slot of a two-slot operation). */
 template <int CODE, int NPAIR>
-__device__ __forceinline__ void apply_one(float2 (&v)[NPAIR * 3], const float4 o, const float4 r, const float2 one) {
-    if (CODE == CH_SUB) { /* x - p == x + (-p), negated once per parameter */
-        const float2 n0 = dup2(-o.y), n1 = dup2(-o.z), n2 = dup2(-o.w);
+__device__ __forceinline__ void apply_one(float2 (&v)[NPAIR * 3], const OpSlot* __restrict__ s, const float2 one) {
+    if (CODE == CH_SWAP || CODE == CH_SAT || CODE == CH_YUV) {
 #pragma unroll
         for (int j = 0; j < NPAIR; ++j) {
-            v[3 * j] = add2(v[3 * j], n0, one); v[3 * j + 1] = add2(v[3 * j + 1], n1, one); v[3 * j + 2] = add2(v[3 * j + 2], n2, one);
+            float2& a = v[3 * j + 0];
+            float2& b = v[3 * j + 1];
+            float2& c = v[3 * j + 2];
+            if (CODE == CH_SWAP) { const float2 t = a; a = c; c = t; }
+            else if (CODE == CH_SAT) {
+                a = make_float2(saturate_round_u8(a.x), saturate_round_u8(a.y));
+                b = make_float2(saturate_round_u8(b.x), saturate_round_u8(b.y));
+                c = make_float2(saturate_round_u8(c.x), saturate_round_u8(c.y));
+            } else {
+                yuv_to_rgb_bt709_full(a.x, b.x, c.x);
+                yuv_to_rgb_bt709_full(a.y, b.y, c.y);
+            }
         }
         return;
     }
-    const float2 p0 = dup2(o.y), p1 = dup2(o.z), p2 = dup2(o.w);
-    const float2 r0 = dup2(r.y), r1 = dup2(r.z), r2 = dup2(r.w);
+    const float2 p0 = s[0].p[0], p1 = s[0].p[1], p2 = s[0].p[2];
 #pragma unroll
     for (int j = 0; j < NPAIR; ++j) {
         float2& a = v[3 * j + 0];
@@ -103,21 +138,14 @@ __device__ __forceinline__ void apply_one(float2 (&v)[NPAIR * 3], const float4 o
         float2& c = v[3 * j + 2];
         if (CODE == CH_MUL) { a = mul2(a, p0); b = mul2(b, p1); c = mul2(c, p2); }
         else if (CODE == CH_DIV) {
-            a = make_float2(__fdiv_rn(a.x, o.y), __fdiv_rn(a.y, o.y));
-            b = make_float2(__fdiv_rn(b.x, o.z), __fdiv_rn(b.y, o.z));
-            c = make_float2(__fdiv_rn(c.x, o.w), __fdiv_rn(c.y, o.w));
-        } else if (CODE == CH_ADD) { a = add2(a, p0, one); b = add2(b, p1, one); c = add2(c, p2, one); }
+            a = make_float2(__fdiv_rn(a.x, p0.x), __fdiv_rn(a.y, p0.x));
+            b = make_float2(__fdiv_rn(b.x, p1.x), __fdiv_rn(b.y, p1.x));
+            c = make_float2(__fdiv_rn(c.x, p2.x), __fdiv_rn(c.y, p2.x));
+        } else if (CODE == CH_ADD || CODE == CH_SUB) { a = add2(a, p0, one); b = add2(b, p1, one); c = add2(c, p2, one); }
         else if (CODE == CH_DIVC) { /* div_by_constant on both halves: p holds -divisor, r its reciprocal */
+            const float2 r0 = s[1].p[0], r1 = s[1].p[1], r2 = s[1].p[2];
             const float2 qa = mul2(a, r0), qb = mul2(b, r1), qc = mul2(c, r2);
             a = fma2(fma2(p0, qa, a), r0, qa); b = fma2(fma2(p1, qb, b), r1, qb); c = fma2(fma2(p2, qc, c), r2, qc);
-        } else if (CODE == CH_SWAP) { const float2 t = a; a = c; c = t; }
-        else if (CODE == CH_SAT) {
-            a = make_float2(saturate_round_u8(a.x), saturate_round_u8(a.y));
-            b = make_float2(saturate_round_u8(b.x), saturate_round_u8(b.y));
-            c = make_float2(saturate_round_u8(c.x), saturate_round_u8(c.y));
-        } else if (CODE == CH_YUV) {
-            yuv_to_rgb_bt709_full(a.x, b.x, c.x);
-            yuv_to_rgb_bt709_full(a.y, b.y, c.y);
         }
     }
 }
@@ -125,23 +153,21 @@ __device__ __forceinline__ void apply_one(float2 (&v)[NPAIR * 3], const float4 o
 /* Interpreter: runs ops [begin, end) of a sequence cached in shared memory.  The opcode is
  * uniform across the block, so the switch never diverges. */
 template <int NPAIR>
-__device__ __forceinline__ void interpret_ops(float2 (&v)[NPAIR * 3], const DevOp* __restrict__ sops, int begin, int end,
+__device__ __forceinline__ void interpret_ops(float2 (&v)[NPAIR * 3], const OpSlot* __restrict__ sops, int begin, int end,
                                               const float2 one) {
     for (int k = begin; k < end; ++k) {
-        const float4 o = *reinterpret_cast<const float4*>(&sops[k]);
-        const float4 none = make_float4(0.f, 0.f, 0.f, 0.f);
-        switch (__float_as_int(o.x)) {
-            case FKB_OP_MUL: apply_one<CH_MUL, NPAIR>(v, o, none, one); break;
-            case FKB_OP_SUB: apply_one<CH_SUB, NPAIR>(v, o, none, one); break;
-            case FKB_OP_DIV: apply_one<CH_DIV, NPAIR>(v, o, none, one); break;
-            case FKB_OP_ADD: apply_one<CH_ADD, NPAIR>(v, o, none, one); break;
+        switch (sops[k].opcode) {
+            case FKB_OP_MUL: apply_one<CH_MUL, NPAIR>(v, sops + k, one); break;
+            case FKB_OP_SUB: apply_one<CH_SUB, NPAIR>(v, sops + k, one); break;
+            case FKB_OP_DIV: apply_one<CH_DIV, NPAIR>(v, sops + k, one); break;
+            case FKB_OP_ADD: apply_one<CH_ADD, NPAIR>(v, sops + k, one); break;
             case DEV_OP_DIV_BY_CONSTANT: /* two slots: {-p}, {1/p} */
-                apply_one<CH_DIVC, NPAIR>(v, o, *reinterpret_cast<const float4*>(&sops[k + 1]), one);
+                apply_one<CH_DIVC, NPAIR>(v, sops + k, one);
                 ++k;
                 break;
-            case FKB_OP_SWAP_RB: apply_one<CH_SWAP, NPAIR>(v, o, none, one); break;
-            case FKB_OP_SATURATE_CAST_U8: apply_one<CH_SAT, NPAIR>(v, o, none, one); break;
-            case FKB_OP_YUV_TO_RGB_BT709_FULL: apply_one<CH_YUV, NPAIR>(v, o, none, one); break;
+            case FKB_OP_SWAP_RB: apply_one<CH_SWAP, NPAIR>(v, sops + k, one); break;
+            case FKB_OP_SATURATE_CAST_U8: apply_one<CH_SAT, NPAIR>(v, sops + k, one); break;
+            case FKB_OP_YUV_TO_RGB_BT709_FULL: apply_one<CH_YUV, NPAIR>(v, sops + k, one); break;
             default: break;
         }
     }
@@ -150,26 +176,16 @@ __device__ __forceinline__ void interpret_ops(float2 (&v)[NPAIR * 3], const DevO
 /* A chain fixed at compile time: operation codes in the nibbles of CHAIN, parameters taken
    from consecutive slots of the cached operation table starting at `slot`. */
 template <uint32_t CHAIN, int NPAIR>
-__device__ __forceinline__ void apply_chain(float2 (&v)[NPAIR * 3], const DevOp* __restrict__ sops, int slot, const float2 one) {
+__device__ __forceinline__ void apply_chain(float2 (&v)[NPAIR * 3], const OpSlot* __restrict__ sops, int slot, const float2 one) {
     constexpr uint32_t CODE = CHAIN & 0xFu;
     if constexpr (CODE != 0) {
-        const float4 none = make_float4(0.f, 0.f, 0.f, 0.f);
-        if constexpr (CODE == CH_SWAP || CODE == CH_SAT || CODE == CH_YUV) {
-            apply_one<CODE, NPAIR>(v, none, none, one);
-            apply_chain<(CHAIN >> 4), NPAIR>(v, sops, slot + 1, one);
-        } else if constexpr (CODE == CH_DIVC) {
-            apply_one<CODE, NPAIR>(v, *reinterpret_cast<const float4*>(&sops[slot]),
-                                   *reinterpret_cast<const float4*>(&sops[slot + 1]), one);
-            apply_chain<(CHAIN >> 4), NPAIR>(v, sops, slot + 2, one);
-        } else {
-            apply_one<CODE, NPAIR>(v, *reinterpret_cast<const float4*>(&sops[slot]), none, one);
-            apply_chain<(CHAIN >> 4), NPAIR>(v, sops, slot + 1, one);
-        }
+        apply_one<CODE, NPAIR>(v, sops + slot, one);
+        apply_chain<(CHAIN >> 4), NPAIR>(v, sops, slot + (CODE == CH_DIVC ? 2 : 1), one);
     }
 }
 
 template <uint32_t CHAIN, int NPAIR>
-__device__ __forceinline__ void run_ops(float2 (&v)[NPAIR * 3], const DevOp* __restrict__ sops, int begin, int end,
+__device__ __forceinline__ void run_ops(float2 (&v)[NPAIR * 3], const OpSlot* __restrict__ sops, int begin, int end,
                                         const float2 one) {
     if constexpr (CHAIN == CHAIN_INTERPRET) interpret_ops<NPAIR>(v, sops, begin, end, one);
     else apply_chain<CHAIN, NPAIR>(v, sops, begin, one);
@@ -177,7 +193,7 @@ __device__ __forceinline__ void run_ops(float2 (&v)[NPAIR * 3], const DevOp* __r
 
 /* The same on one pixel (both halves of a pair carry it). */
 template <uint32_t CHAIN>
-__device__ __forceinline__ void run_ops_1(float (&v)[3], const DevOp* __restrict__ sops, int begin, int end, const float2 one) {
+__device__ __forceinline__ void run_ops_1(float (&v)[3], const OpSlot* __restrict__ sops, int begin, int end, const float2 one) {
     float2 p[3] = {dup2(v[0]), dup2(v[1]), dup2(v[2])};
     run_ops<CHAIN, 1>(p, sops, begin, end, one);
     v[0] = p[0].x; v[1] = p[1].x; v[2] = p[2].x;
@@ -242,7 +258,7 @@ __device__ __forceinline__ float blend(float p00, float p10, float p01, float p1
 /* ------------------------------------------------------------------------------------ */
 /* body: generic, one output pixel per thread                                           */
 /* ------------------------------------------------------------------------------------ */
-__device__ __forceinline__ void body_generic(const DevPlane& P, const DevSeq& S, const DevOp* sops, uint32_t local) {
+__device__ __forceinline__ void body_generic(const DevPlane& P, const DevSeq& S, const OpSlot* sops, uint32_t local) {
     const uint32_t idx = local * ITEM_PIXELS_GENERIC + threadIdx.x;
     if (idx >= P.dst_w * P.dst_h) return;
     const int y = idx / P.dst_w, x = idx - y * P.dst_w;
@@ -296,7 +312,7 @@ __device__ __forceinline__ void body_generic(const DevPlane& P, const DevSeq& S,
 /* body: no geometry stage, four whole pixels per thread                                */
 /* ------------------------------------------------------------------------------------ */
 template <uint32_t CHAIN, bool SRC_IS_U8, bool DST_IS_U8>
-__device__ __forceinline__ void body_flat(const DevPlane& P, const DevSeq& S, const DevOp* sops, uint32_t local) {
+__device__ __forceinline__ void body_flat(const DevPlane& P, const DevSeq& S, const OpSlot* sops, uint32_t local) {
     constexpr int SPX = SRC_IS_U8 ? 3 : 12;
     constexpr int DPX = DST_IS_U8 ? 3 : 12;
     const uint32_t items_per_seg = (P.seg_pixels + ITEM_PIXELS_VEC - 1) / ITEM_PIXELS_VEC;
@@ -411,8 +427,21 @@ __device__ __forceinline__ void store_pixel(uint8_t* dst, uint32_t pitch, uint32
     }
 }
 
+/* The same at an address already computed. */
+template <bool PLANAR>
+__device__ __forceinline__ void store_pixel_at(uint8_t* d, uint32_t cstride, float a, float b, float c) {
+    if (PLANAR) {
+        *reinterpret_cast<float*>(d) = a;
+        *reinterpret_cast<float*>(d + (size_t)cstride) = b;
+        *reinterpret_cast<float*>(d + 2 * (size_t)cstride) = c;
+    } else {
+        float* f = reinterpret_cast<float*>(d);
+        f[0] = a; f[1] = b; f[2] = c;
+    }
+}
+
 template <uint32_t CHAIN, int SRC, bool PLANAR>
-__device__ __forceinline__ void body_resize(const DevPlane& P, const DevSeq& S, const DevOp* sops, uint32_t local) {
+__device__ __forceinline__ void body_resize(const DevPlane& P, const DevSeq& S, const OpSlot* sops, uint32_t local) {
     /* plane fields used inside loops, copied out of shared memory once */
     uint8_t* const dst = P.dst;
     const uint32_t dst_pitch = P.dst_pitch, dst_cstride = P.dst_cstride, src_pitch = P.src_pitch;
@@ -631,7 +660,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t mbar, uint32_t parity
  * of columns `gw` apart down its row slots, reading its twelve tap bytes per pixel from shared
  * memory.  Vertical tap positions and weights are computed once per row of the band. */
 template <uint32_t CHAIN, bool PLANAR>
-__device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevSeq& S, const DevOp* sops, uint32_t local,
+__device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevSeq& S, const OpSlot* sops, uint32_t local,
                                                    unsigned char* staged_mem, uint32_t* status) {
     uint8_t* const dst = P.dst;
     const uint32_t dst_pitch = P.dst_pitch, dst_cstride = P.dst_cstride;
@@ -663,10 +692,11 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
         return;
     }
 
-    /* shared memory: | mbarrier (16 B) | row table | staged source rows | */
+    /* shared memory: | mbarrier (16 B) | row table (32 B per row of the band) | staged source rows | */
     uint64_t* const mbar_ptr = reinterpret_cast<uint64_t*>(staged_mem);
     float4* const row_tab = reinterpret_cast<float4*>(staged_mem + 16);
-    unsigned char* const stage = staged_mem + 16 + STAGED_MAX_ROWS * sizeof(float4);
+    unsigned char* const stage = staged_mem + STAGED_HEADER_BYTES;
+    const uint32_t stage_addr = smem_addr(stage);
     const uint32_t mbar = smem_addr(mbar_ptr);
 
     const uint32_t band_rows = P.tiles_x, gw = P.gw, rs = P.rs; /* rows per band, threads across, row slots */
@@ -689,8 +719,12 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
         mbar_expect_tx(mbar, n_src * row_len);
     }
     if (threadIdx.x <= (uint32_t)(yb - ya)) {
+        /* vertical taps of one row of the band: shared-memory addresses of its two source rows, and
+           its two weights already duplicated into pairs */
         const Axis ay = make_axis(ya + (int)threadIdx.x - y1, fy, crop_h);
-        row_tab[threadIdx.x] = make_float4(__int_as_float(ay.i0), __int_as_float(ay.i1), ay.w0, ay.w1);
+        row_tab[2 * threadIdx.x] = make_float4(__uint_as_float(stage_addr + (uint32_t)(ay.i0 - src_first) * row_len),
+                                               __uint_as_float(stage_addr + (uint32_t)(ay.i1 - src_first) * row_len), 0.0f, 0.0f);
+        row_tab[2 * threadIdx.x + 1] = make_float4(ay.w0, ay.w0, ay.w1, ay.w1);
     }
     __syncthreads(); /* barrier initialised and armed, row table written */
     {
@@ -717,7 +751,6 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
     const uint32_t second_a = axa.i1 == axa.i0 ? 0x3210u : 0x3543u; /* bytes of the second tap in (u0, u1) */
     const uint32_t second_b = axb.i1 == axb.i0 ? 0x3210u : 0x3543u;
     const float2 wx0 = make_float2(axa.w0, axb.w0), wx1 = make_float2(axa.w1, axb.w1);
-    const uint32_t stage_addr = smem_addr(stage);
     const float2 minus_2p23 = make_float2(-8388608.0f, -8388608.0f);
 
     const bool arrived = mbar_wait_bounded(mbar, 0);
@@ -731,11 +764,15 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
 
     if (slot < rs) {
         const bool plain = in_a && in_b && valid_b;
+        /* running output pointers of the two columns (channel 0), advanced one row slot round at a time */
+        const size_t px_bytes = PLANAR ? 4 : 12;
+        uint8_t* out_a = dst + (size_t)(ya + (int)slot) * dst_pitch + (size_t)xa * px_bytes;
+        const size_t b_off = (size_t)gw * px_bytes, row_step = (size_t)rs * dst_pitch;
+        const float4* rt = row_tab + 2 * slot;
 #pragma unroll 1
-        for (int y = ya + (int)slot; y <= yb; y += (int)rs) {
-            const float4 rt = row_tab[y - ya];
-            const uint32_t row_addr[2] = {stage_addr + (uint32_t)(__float_as_int(rt.x) - src_first) * row_len,
-                                          stage_addr + (uint32_t)(__float_as_int(rt.y) - src_first) * row_len};
+        for (int y = ya + (int)slot; y <= yb; y += (int)rs, rt += 2 * rs, out_a += row_step) {
+            const float4 rows = rt[0], wy = rt[1];
+            const uint32_t row_addr[2] = {__float_as_uint(rows.x), __float_as_uint(rows.y)};
             float2 tap[2][2][3]; /* [source row][first / second tap][channel] = (column a, column b) */
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
@@ -747,13 +784,22 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
                 const uint32_t ta = __byte_perm(ua0, ua1, second_a), tb = __byte_perm(ub0, ub1, second_b);
 #pragma unroll
                 for (int c = 0; c < 3; ++c) {
+#if FKB_CVT_MODE == 0
                     tap[r][0][c] = __fadd2_rn(make_float2(__uint_as_float(__byte_perm(ua0, 0x4B000000u, 0x7440 | c)),
                                                           __uint_as_float(__byte_perm(ub0, 0x4B000000u, 0x7440 | c))), minus_2p23);
                     tap[r][1][c] = __fadd2_rn(make_float2(__uint_as_float(__byte_perm(ta, 0x4B000000u, 0x7440 | c)),
                                                           __uint_as_float(__byte_perm(tb, 0x4B000000u, 0x7440 | c))), minus_2p23);
+#elif FKB_CVT_MODE == 1
+                    tap[r][0][c] = make_float2(byte_to_float<0>(ua0 >> (8 * c)), byte_to_float<0>(ub0 >> (8 * c)));
+                    tap[r][1][c] = make_float2(byte_to_float<0>(ta >> (8 * c)), byte_to_float<0>(tb >> (8 * c)));
+#else
+                    tap[r][0][c] = make_float2(byte_to_float<0>(ua0 >> (8 * c)), byte_to_float<0>(ub0 >> (8 * c)));
+                    tap[r][1][c] = __fadd2_rn(make_float2(__uint_as_float(__byte_perm(ta, 0x4B000000u, 0x7440 | c)),
+                                                          __uint_as_float(__byte_perm(tb, 0x4B000000u, 0x7440 | c))), minus_2p23);
+#endif
                 }
             }
-            const float2 wy0 = dup2(rt.z), wy1 = dup2(rt.w);
+            const float2 wy0 = make_float2(wy.x, wy.y), wy1 = make_float2(wy.z, wy.w);
             const float2 w00 = mul2(wx0, wy0), w10 = mul2(wx1, wy0), w01 = mul2(wx0, wy1), w11 = mul2(wx1, wy1);
             float2 v[3];
 #pragma unroll
@@ -763,15 +809,14 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
                             mul2(tap[1][1][c], w11), one);
             }
             run_ops<CHAIN, 1>(v, sops, S.n_pre, S.n_ops, one);
+            uint8_t* const out_b = out_a + b_off;
             if (plain) {
-                store_pixel<PLANAR>(dst, dst_pitch, dst_cstride, xa, y, v[0].x, v[1].x, v[2].x);
-                store_pixel<PLANAR>(dst, dst_pitch, dst_cstride, xb, y, v[0].y, v[1].y, v[2].y);
+                store_pixel_at<PLANAR>(out_a, dst_cstride, v[0].x, v[1].x, v[2].x);
+                store_pixel_at<PLANAR>(out_b, dst_cstride, v[0].y, v[1].y, v[2].y);
             } else { /* a column group straddling the edge of the region, or the last odd column */
-                store_pixel<PLANAR>(dst, dst_pitch, dst_cstride, xa, y, in_a ? v[0].x : bgv[0], in_a ? v[1].x : bgv[1],
-                                    in_a ? v[2].x : bgv[2]);
+                store_pixel_at<PLANAR>(out_a, dst_cstride, in_a ? v[0].x : bgv[0], in_a ? v[1].x : bgv[1], in_a ? v[2].x : bgv[2]);
                 if (valid_b)
-                    store_pixel<PLANAR>(dst, dst_pitch, dst_cstride, xb, y, in_b ? v[0].y : bgv[0], in_b ? v[1].y : bgv[1],
-                                        in_b ? v[2].y : bgv[2]);
+                    store_pixel_at<PLANAR>(out_b, dst_cstride, in_b ? v[0].y : bgv[0], in_b ? v[1].y : bgv[1], in_b ? v[2].y : bgv[2]);
             }
         }
     }
@@ -793,7 +838,7 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
 /* the kernel                                                                           */
 /* ------------------------------------------------------------------------------------ */
 template <uint32_t CLASS, uint32_t CHAIN>
-__device__ __forceinline__ void run_body(uint32_t cls, const DevPlane& P, const DevSeq& S, const DevOp* sops,
+__device__ __forceinline__ void run_body(uint32_t cls, const DevPlane& P, const DevSeq& S, const OpSlot* sops,
                                          uint32_t local, unsigned char* staged_mem, uint32_t* status) {
     if (CLASS != CLASS_MIXED) cls = CLASS;
     switch (cls) {
@@ -822,7 +867,7 @@ constexpr int min_blocks_of(uint32_t cls) {
 template <uint32_t CLASS, uint32_t CHAIN>
 __global__ void __launch_bounds__(BLOCK_THREADS, min_blocks_of(CLASS)) fused_plan_kernel(const __grid_constant__ LaunchArgs a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    DevOp* sops = reinterpret_cast<DevOp*>(smem_raw);
+    OpSlot* sops = reinterpret_cast<OpSlot*>(smem_raw);
     __shared__ DevPlane s_plane;
     __shared__ DevSeq s_seq;
 
@@ -837,11 +882,11 @@ __global__ void __launch_bounds__(BLOCK_THREADS, min_blocks_of(CLASS)) fused_pla
         reinterpret_cast<uint4*>(&s_seq)[threadIdx.x - 32] = __ldg(reinterpret_cast<const uint4*>(a.seqs + seq) + (threadIdx.x - 32));
     } else if (threadIdx.x >= 64) {
         for (uint32_t k = threadIdx.x - 64; k < n_ops; k += blockDim.x - 64)
-            reinterpret_cast<uint4*>(sops)[k] = __ldg(reinterpret_cast<const uint4*>(a.ops + ops_begin + k));
+            expand_op(__ldg(reinterpret_cast<const uint4*>(a.ops + ops_begin + k)), sops + k);
     }
     __syncthreads();
     /* staged classes: the region after the operation cache, on a 128-byte boundary */
-    unsigned char* staged_mem = smem_raw + (((a.max_seq_ops > 0 ? a.max_seq_ops : 1u) * (uint32_t)sizeof(DevOp) + 127u) & ~127u);
+    unsigned char* staged_mem = smem_raw + (((a.max_seq_ops > 0 ? a.max_seq_ops : 1u) * (uint32_t)sizeof(OpSlot) + 127u) & ~127u);
     run_body<CLASS, CHAIN>(s_plane.plane_class, s_plane, s_seq, sops, local, staged_mem, a.status);
 }
 
@@ -898,7 +943,7 @@ bool chain_is_compiled(uint32_t chain) {
 
 /* launch_class: one of CLASS_* or CLASS_MIXED; chain: a menu chain or CHAIN_INTERPRET. */
 cudaError_t launch_plan_kernel(uint32_t launch_cls, uint32_t chain, const LaunchArgs& a, cudaStream_t stream) {
-    const size_t ops_bytes = (size_t)(a.max_seq_ops > 0 ? a.max_seq_ops : 1) * sizeof(DevOp);
+    const size_t ops_bytes = (size_t)(a.max_seq_ops > 0 ? a.max_seq_ops : 1) * sizeof(OpSlot);
     const size_t smem = a.staged_bytes ? ((ops_bytes + 127) & ~(size_t)127) + a.staged_bytes : ops_bytes;
     switch (launch_cls) {
         case CLASS_FLAT_U8_F32: return launch_class<CLASS_FLAT_U8_F32>(chain, a, smem, stream);
