@@ -77,16 +77,14 @@ struct LaunchArgs {
     const DevSeq* seqs;
     const DevOp* ops;
     const uint4* items;         /* one entry per thread block: plane, tile within the plane,  */
-                                /* sequence | operations << 16, first operation; STAGED        */
-                                /* classes: StagedItem entries (two uint4 each) instead        */
+                                /* sequence | operations << 16, first operation                */
     uint32_t n_planes;
     uint32_t reserved;
     uint32_t total_items;
     uint32_t max_seq_ops;       /* longest sequence: sizes the shared-memory op cache         */
     uint32_t block_threads;     /* threads per block of this launch (multiple of 32, <= 256)  */
-    uint32_t staged_bytes;      /* STAGED classes: bytes of one shared-memory stage (x128)     */
-    uint32_t grid_blocks;       /* STAGED classes: persistent blocks launched                  */
-    uint32_t pad;
+    uint32_t staged_bytes;      /* STAGED classes: shared memory behind the operation cache    */
+    uint32_t pad[2];
     uint32_t* status;           /* one word in the plan's device block: 0, or a STATUS_* code  */
 };
 
@@ -150,24 +148,13 @@ inline ResizeTiling resize_tiling(uint32_t dst_w, uint32_t dst_h, int x1, int y1
 
 /* STAGED classes: a work item is a band of `band_rows` output rows of the region of interest,
  * all columns; its source footprint (whole crop rows, widened to 16-byte boundaries) sits in
- * one of two shared-memory stages. */
+ * shared memory behind a 16-byte mbarrier slot and a table of per-row vertical taps. */
 constexpr uint32_t STAGED_MAX_ROWS = 64;          /* output rows per band                        */
 #ifndef FKB_STAGE_KB
-#define FKB_STAGE_KB 32
+#define FKB_STAGE_KB 40
 #endif
 constexpr uint32_t STAGED_MAX_STAGE_BYTES = FKB_STAGE_KB * 1024u;
-
-/* One work item of the staged kernel (32 bytes, read as two uint4). */
-struct alignas(16) StagedItem {
-    uint32_t plane;
-    uint32_t local;        /* band index, or roi_items + index of a run of background rows       */
-    const uint8_t* src;    /* first byte to copy of the band's first source row (16-byte aligned) */
-    uint32_t n_src;        /* source rows to copy; 0 for a run of background rows                 */
-    uint32_t row_len;      /* bytes copied per source row (a multiple of 16)                      */
-    int32_t src_first;     /* index, within the crop, of the first source row copied              */
-    uint32_t cost;         /* what the host ordered the table by                                  */
-};
-static_assert(sizeof(StagedItem) == 32, "StagedItem layout");
+constexpr uint32_t STAGED_HEADER_BYTES = 16 + STAGED_MAX_ROWS * 32;
 constexpr uint32_t STAGED_WAIT_LIMIT = 1u << 22;  /* try_wait rounds before a block gives up     */
 constexpr uint32_t STATUS_STAGED_WAIT_TIMEOUT = 1; /* a bulk copy did not complete in time        */
 

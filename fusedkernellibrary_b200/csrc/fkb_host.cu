@@ -23,7 +23,6 @@
 namespace fkb {
 cudaError_t launch_plan_kernel(uint32_t launch_class, uint32_t chain, const LaunchArgs& a, cudaStream_t stream);
 bool chain_is_compiled(uint32_t chain);
-int staged_blocks_per_sm();
 }
 
 using namespace fkb;
@@ -78,9 +77,7 @@ struct HostImage {
     uint32_t uniform_items = 0;
     uint32_t total_items = 0;
     uint32_t max_seq_ops = 0;
-    uint32_t grid_blocks = 0;           /* STAGED classes: persistent blocks (set when a device is known) */
-    uint32_t staged_bytes = 0;          /* > 0: a STAGED class, bytes of one shared-memory stage  */
-    std::vector<StagedItem> staged_items; /* STAGED classes: the work-item table, in launch order  */
+    uint32_t staged_bytes = 0;          /* > 0: a STAGED class, this much shared memory per block */
     uint64_t output_pixels = 0;
     uint64_t algorithmic_bytes = 0;
     int n_constant_divisions = 0, n_ieee_divisions = 0;
@@ -89,7 +86,7 @@ struct HostImage {
     size_t off_seqs() const { return planes.size() * sizeof(DevPlane); }
     size_t off_ops() const { return off_seqs() + seqs.size() * sizeof(DevSeq); }
     size_t off_items() const { return off_ops() + std::max<size_t>(ops.size(), 1) * sizeof(DevOp); }
-    size_t off_status() const { return off_items() + (size_t)total_items * (staged_items.empty() ? 16 : sizeof(StagedItem)); }
+    size_t off_status() const { return off_items() + (size_t)total_items * 16; }
     size_t bytes() const { return off_status() + 16; }
 
     void serialize(unsigned char* dst) const {
@@ -98,8 +95,7 @@ struct HostImage {
         if (!ops.empty()) std::memcpy(dst + off_ops(), ops.data(), ops.size() * sizeof(DevOp));
         /* work-item table: item_start holds the prefix sums of the items per plane */
         uint32_t* e = reinterpret_cast<uint32_t*>(dst + off_items());
-        if (!staged_items.empty()) std::memcpy(e, staged_items.data(), staged_items.size() * sizeof(StagedItem));
-        else for (size_t i = 0; i < planes.size(); ++i) {
+        for (size_t i = 0; i < planes.size(); ++i) {
             const DevSeq& q = seqs[planes[i].seq];
             for (uint32_t l = 0, n = item_start[i + 1] - item_start[i]; l < n; ++l, e += 4) {
                 e[0] = (uint32_t)i; e[1] = l; e[2] = planes[i].seq | ((uint32_t)q.n_ops << 16); e[3] = (uint32_t)q.ops_begin;
@@ -118,7 +114,6 @@ struct HostImage {
         a.max_seq_ops = max_seq_ops;
         a.block_threads = block_threads;
         a.staged_bytes = staged_bytes;
-        a.grid_blocks = grid_blocks;
         a.status = reinterpret_cast<uint32_t*>(const_cast<unsigned char*>(d_base) + off_status());
         return a;
     }
@@ -657,7 +652,7 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
                     ? common_chain : CHAIN_INTERPRET;
 #ifndef FKB_DISABLE_STAGED
     /* uchar3 resize plans whose every plane can stage its bands' source rows in shared memory */
-    if ((common_class == CLASS_RESIZE_U8_PLANAR || common_class == CLASS_RESIZE_U8_PACKED) && d->n_sequences == 1) {
+    if (common_class == CLASS_RESIZE_U8_PLANAR || common_class == CLASS_RESIZE_U8_PACKED) {
         std::vector<StagedTiling> st(img.planes.size());
         bool all = true;
         uint32_t stage = 0;
@@ -669,45 +664,24 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
         if (all) {
             const uint32_t cls = common_class == CLASS_RESIZE_U8_PLANAR ? CLASS_RESIZE_U8_PLANAR_STAGED : CLASS_RESIZE_U8_PACKED_STAGED;
             uint64_t t2 = 0;
+            uniform = true;
             for (size_t i = 0; i < img.planes.size(); ++i) {
                 DevPlane& dp = img.planes[i];
                 const ResizeTiling rt = resize_tiling(dp.dst_w, dp.dst_h, dp.x1, dp.y1, dp.x2, dp.y2, BLOCK_THREADS);
+                const uint32_t items = st[i].n_bands + rt.bg_items;
                 dp.plane_class = cls;
                 dp.roi_items = st[i].n_bands; dp.tiles_x = st[i].band_rows; dp.gw = st[i].gw; dp.rs = st[i].rs;
                 img.item_start[i] = (uint32_t)t2;
-                t2 += st[i].n_bands + rt.bg_items;
-                if (t2 > 0x7FFFFFFFull) return fail(FKB_ERR_INVALID_ARGUMENT, "plan needs more than 2^31 work items");
-                /* the items of this plane: bands with their copy parameters, then runs of background rows */
-                const uint32_t row_first = ((uint32_t)dp.crop_x * 3u) & ~15u;
-                const uint32_t row_len = (((uint32_t)dp.crop_x * 3u - row_first) + (uint32_t)dp.crop_w * 3u + 15u) & ~15u;
-                const uint32_t n_rows = (uint32_t)(dp.y2 - dp.y1 + 1);
-                const uint32_t cols = ((uint32_t)dp.x2 / PX_PER_THREAD - (uint32_t)dp.x1 / PX_PER_THREAD + 1) * PX_PER_THREAD;
-                for (uint32_t b = 0; b < st[i].n_bands; ++b) {
-                    const uint32_t ra = b * st[i].band_rows, rb = std::min(ra + st[i].band_rows, n_rows) - 1;
-                    StagedItem it{};
-                    it.plane = (uint32_t)i; it.local = b;
-                    it.src_first = staged_src_row((int)ra, dp.fy);
-                    const int last = std::min(staged_src_row((int)rb, dp.fy) + 1, dp.crop_h - 1);
-                    it.n_src = (uint32_t)(last - it.src_first + 1);
-                    it.row_len = row_len;
-                    it.src = dp.src + (size_t)(dp.crop_y + it.src_first) * dp.src_pitch + row_first;
-                    it.cost = 64 + (rb - ra + 1) * (cols + (dp.dst_w - cols) / 8) + it.n_src * row_len / 64;
-                    img.staged_items.push_back(it);
-                }
-                for (uint32_t b = 0; b < rt.bg_items; ++b) {
-                    StagedItem it{};
-                    it.plane = (uint32_t)i; it.local = st[i].n_bands + b; it.cost = 64 + BLOCK_THREADS * BG_GROUPS_PER_THREAD / 4;
-                    img.staged_items.push_back(it);
-                }
+                t2 += items;
+                if (i == 0) first_items = items;
+                else if (items != first_items) uniform = false;
             }
-            /* most expensive first: block b of G persistent blocks takes items b, b+G, ... */
-            std::stable_sort(img.staged_items.begin(), img.staged_items.end(),
-                             [](const StagedItem& x, const StagedItem& y) { return x.cost > y.cost; });
+            if (t2 > 0x7FFFFFFFull) return fail(FKB_ERR_INVALID_ARGUMENT, "plan needs more than 2^31 thread blocks");
             img.item_start[img.planes.size()] = (uint32_t)t2;
             img.total_items = (uint32_t)t2;
-            img.uniform_items = 0;
+            img.uniform_items = uniform ? first_items : 0;
             img.block_threads = BLOCK_THREADS;
-            img.staged_bytes = (stage + 127u) & ~127u;
+            img.staged_bytes = STAGED_HEADER_BYTES + stage;
             img.launch_class = common_class = cls;
         }
     }
@@ -771,21 +745,12 @@ static int require_device(int* device) {
     return FKB_OK;
 }
 
-/* Persistent kernels: as many blocks as stay resident on the current device. */
-static int size_grid(HostImage& img, int device) {
-    if (img.staged_bytes == 0) return FKB_OK;
-    int sms = 0;
-    FKB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device));
-    img.grid_blocks = std::min<uint32_t>(img.total_items, (uint32_t)std::max(sms, 1) * (uint32_t)staged_blocks_per_sm());
-    return FKB_OK;
-}
-
 static fkb_plan_info info_of(const HostImage& img) {
     fkb_plan_info info{};
     info.n_planes = (int32_t)img.planes.size();
     info.n_sequences = (int32_t)img.seqs.size();
     info.n_launches = 1;
-    info.grid_x = img.grid_blocks ? img.grid_blocks : img.total_items;
+    info.grid_x = img.total_items;
     info.block_x = img.block_threads;
     info.compiled_chain = img.chain != CHAIN_INTERPRET;
     info.output_pixels = img.output_pixels;
@@ -812,8 +777,6 @@ extern "C" FKB_API int fkb_plan_create(const fkb_plan_desc* desc, fkb_plan** out
     if (rc) return rc;
     int device = -1;
     rc = require_device(&device);
-    if (rc) return rc;
-    rc = size_grid(img, device);
     if (rc) return rc;
 
     fkb_plan* plan = new (std::nothrow) fkb_plan();
@@ -1075,8 +1038,6 @@ extern "C" FKB_API int fkb_execute_static(const fkb_plan_desc* desc, void* strea
                     bytes, img.planes.size(), img.seqs.size(), img.ops.size(), (int)FKB_STATIC_TABLE_BYTES);
     int device = -1;
     rc = require_device(&device);
-    if (rc) return rc;
-    rc = size_grid(img, device);
     if (rc) return rc;
     unsigned char* table = nullptr;
     rc = static_table_address(device, &table);

@@ -41,11 +41,8 @@ __device__ __forceinline__ float saturate_round_u8(float f) {
    conversion off the quarter-rate conversion unit. */
 __device__ __forceinline__ float u8_to_float(uint32_t b) { return __int2float_rn((int)b); }
 
-#ifndef FKB_CVT_MODE
-#define FKB_CVT_MODE 1
-#endif
-/* Lowest byte of w, as float, by the integer-to-float conversion with a byte source. */
-template <int UNUSED>
+/* Lowest byte of w, as float.  Written as shift-and-mask at the call site so that the compiler
+   can use the integer-to-float conversion that takes a byte of its source register directly. */
 __device__ __forceinline__ float byte_to_float(uint32_t w) { return __int2float_rn((int)(w & 0xFFu)); }
 
 /* Byte LANE of a packed word, as float: one byte permute builds 2^23 + b, one add removes 2^23. */
@@ -654,237 +651,191 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t mbar, uint32_t parity
     return false;
 }
 
-/* The staged kernel.  A work item is a band of rows of one plane's region of interest, all
- * columns (or a run of background rows above and below it).  Thread blocks are persistent: block
- * b works through items b, b + gridDim.x, ... of a table that the host ordered by decreasing
- * cost.  For every item the rows of the crop that the band's taps touch are copied into shared
- * memory by bulk copies (one per source row, started and sized on 16-byte boundaries) that
- * complete on an mbarrier; there are two stages, and the copies of item k+1 are in flight while
- * item k is computed, as are the global loads of the descriptors of item k+2.  In the compute
- * phase a thread interpolates a pair of columns `gw` apart down its row slots; vertical tap
- * addresses and weights come from a per-band table that is filled when the copies are issued. */
-#ifndef FKB_STAGED_MIN_BLOCKS
-#define FKB_STAGED_MIN_BLOCKS 3
-#endif
-struct StagedSmem {
-    uint64_t mbar[2];
-    StagedItem item[3];
-    DevPlane plane[3];
-    float4 row_tab[2][2 * STAGED_MAX_ROWS];
-};
-
+/* A work item is a band of STAGED rows of one plane's region of interest, all columns.  The rows
+ * of the crop that the band's taps touch are copied into shared memory by bulk copies (one per
+ * source row, started and sized on 16-byte boundaries), then every thread interpolates a pair
+ * of columns `gw` apart down its row slots, reading its twelve tap bytes per pixel from shared
+ * memory.  Vertical tap positions and weights are computed once per row of the band. */
 template <uint32_t CHAIN, bool PLANAR>
-__global__ void __launch_bounds__(BLOCK_THREADS, FKB_STAGED_MIN_BLOCKS) staged_resize_kernel(const __grid_constant__ LaunchArgs a) {
-    extern __shared__ __align__(128) unsigned char smem_raw[];
-    OpSlot* const sops = reinterpret_cast<OpSlot*>(smem_raw);
-    const uint32_t ops_bytes = ((a.max_seq_ops > 0 ? a.max_seq_ops : 1u) * (uint32_t)sizeof(OpSlot) + 127u) & ~127u;
-    StagedSmem& sm = *reinterpret_cast<StagedSmem*>(smem_raw + ops_bytes);
-    unsigned char* const stage0 = smem_raw + ops_bytes + ((sizeof(StagedSmem) + 127u) & ~127u);
-    const uint32_t stage_bytes = a.staged_bytes; /* one stage, a multiple of 128 */
-    __shared__ DevSeq s_seq;
+__device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevSeq& S, const OpSlot* sops, uint32_t local,
+                                                   unsigned char* staged_mem, uint32_t* status) {
+    uint8_t* const dst = P.dst;
+    const uint32_t dst_pitch = P.dst_pitch, dst_cstride = P.dst_cstride;
+    const uint32_t groups_per_row = P.dst_w / PX_PER_THREAD;
+    const int x1 = P.x1, y1 = P.y1, x2 = P.x2, y2 = P.y2;
+    const uint32_t g_lo = (uint32_t)x1 / PX_PER_THREAD;
+    const uint32_t n_groups = (uint32_t)x2 / PX_PER_THREAD - g_lo + 1;
+    const uint32_t n_rows = (uint32_t)(y2 - y1 + 1);
+    const uint32_t nthreads = blockDim.x;
 
-    const StagedItem* const items = reinterpret_cast<const StagedItem*>(a.items);
-    const uint32_t nthreads = blockDim.x, tid = threadIdx.x;
-    const uint32_t first = blockIdx.x, stride = gridDim.x;
-    if (first >= a.total_items) return;
-    const uint32_t n_mine = (a.total_items - first + stride - 1) / stride;
-
-    /* global loads of an item's descriptors: lanes 0..6 of warp 0 fetch the plane, lanes 8, 9 the item */
-    auto fetch = [&](uint32_t k, uint4& reg) {
-        if (k < n_mine && tid < 10 && tid != 7) {
-            const StagedItem* it = items + (first + k * stride);
-            if (tid < 7) reg = __ldg(reinterpret_cast<const uint4*>(a.planes + __ldg(&it->plane)) + tid);
-            else reg = __ldg(reinterpret_cast<const uint4*>(it) + (tid - 8));
-        }
-    };
-    auto deposit = [&](uint32_t k, const uint4& reg) {
-        if (k < n_mine && tid < 10 && tid != 7) {
-            if (tid < 7) reinterpret_cast<uint4*>(&sm.plane[k % 3])[tid] = reg;
-            else reinterpret_cast<uint4*>(&sm.item[k % 3])[tid - 8] = reg;
-        }
-    };
-    /* starts the copies of item k into stage k & 1 and fills that stage's row table */
-    auto issue = [&](uint32_t k) {
-        if (k >= n_mine) return;
-        const StagedItem& it = sm.item[k % 3];
-        if (it.n_src == 0) return; /* background rows: nothing to read */
-        const DevPlane& P = sm.plane[k % 3];
-        const uint32_t slot = k & 1u;
-        const uint32_t stage_addr = smem_addr(stage0 + slot * stage_bytes);
-        const uint32_t mbar = smem_addr(&sm.mbar[slot]);
-        const uint32_t row_len = it.row_len, n_src = it.n_src;
-        if (tid == 0) mbar_expect_tx(mbar, n_src * row_len);
-        const int ya = P.y1 + (int)(it.local * P.tiles_x);
-        const int yb = min(ya + (int)P.tiles_x - 1, P.y2);
-        if (tid <= (uint32_t)(yb - ya)) {
-            const Axis ay = make_axis(ya + (int)tid - P.y1, P.fy, P.crop_h);
-            sm.row_tab[slot][2 * tid] = make_float4(__uint_as_float(stage_addr + (uint32_t)(ay.i0 - it.src_first) * row_len),
-                                                    __uint_as_float(stage_addr + (uint32_t)(ay.i1 - it.src_first) * row_len), 0.0f, 0.0f);
-            sm.row_tab[slot][2 * tid + 1] = make_float4(ay.w0, ay.w0, ay.w1, ay.w1);
-        }
-        const uint8_t* g = it.src;
-        const uint32_t pitch = P.src_pitch;
-        for (uint32_t r = tid; r < n_src; r += nthreads)
-            bulk_copy_g2s(stage_addr + r * row_len, g + (size_t)r * pitch, row_len, mbar);
-    };
-
-    /* ---- prologue: operation table, sequence, barriers, descriptors of the first two items ---- */
-    {
-        const DevSeq* gs = a.seqs; /* staged plans have one sequence */
-        if (tid < sizeof(DevSeq) / 16) reinterpret_cast<uint4*>(&s_seq)[tid] = __ldg(reinterpret_cast<const uint4*>(gs) + tid);
-        const uint32_t n_ops = (uint32_t)__ldg(&gs->n_ops), ops_begin = (uint32_t)__ldg(&gs->ops_begin);
-        for (uint32_t k = tid; k < n_ops; k += nthreads) expand_op(__ldg(reinterpret_cast<const uint4*>(a.ops + ops_begin + k)), sops + k);
-        if (tid == 0) {
-            mbar_init(smem_addr(&sm.mbar[0]), 1);
-            mbar_init(smem_addr(&sm.mbar[1]), 1);
-            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        }
-        uint4 r0 = make_uint4(0, 0, 0, 0), r1 = make_uint4(0, 0, 0, 0);
-        fetch(0, r0);
-        fetch(1, r1);
-        deposit(0, r0);
-        deposit(1, r1);
-    }
-    __syncthreads();
-    const DevSeq& S = s_seq;
-    const float2 one = dup2(S.one);
     float bgv[3] = {S.bg[0], S.bg[1], S.bg[2]};
+    const float2 one = dup2(S.one);
     run_ops_1<CHAIN>(bgv, sops, S.n_pre, S.n_ops, one);
-    const float2 minus_2p23 = make_float2(-8388608.0f, -8388608.0f);
-    (void)minus_2p23;
-    issue(0);
-    __syncthreads(); /* row table of item 0 */
-    uint32_t parity_bits = 0; /* bit s: the phase of barrier s that the next waiter on stage s waits for */
-
-    for (uint32_t k = 0; k < n_mine; ++k) {
-        uint4 ahead = make_uint4(0, 0, 0, 0);
-        fetch(k + 2, ahead); /* consumed at the end of this round */
-        issue(k + 1);
-
-        const StagedItem& it = sm.item[k % 3];
-        const DevPlane& P = sm.plane[k % 3];
-        uint8_t* const dst = P.dst;
-        const uint32_t dst_pitch = P.dst_pitch, dst_cstride = P.dst_cstride;
-        const uint32_t groups_per_row = P.dst_w / PX_PER_THREAD;
-        const int x1 = P.x1, y1 = P.y1, x2 = P.x2, y2 = P.y2;
-        const uint32_t g_lo = (uint32_t)x1 / PX_PER_THREAD;
-        const uint32_t n_groups = (uint32_t)x2 / PX_PER_THREAD - g_lo + 1;
-        const uint32_t n_rows = (uint32_t)(y2 - y1 + 1);
-        float bg4[12];
+    float bg4[12];
 #pragma unroll
-        for (int i = 0; i < PX_PER_THREAD; ++i) { bg4[3 * i] = bgv[0]; bg4[3 * i + 1] = bgv[1]; bg4[3 * i + 2] = bgv[2]; }
+    for (int i = 0; i < PX_PER_THREAD; ++i) { bg4[3 * i] = bgv[0]; bg4[3 * i + 1] = bgv[1]; bg4[3 * i + 2] = bgv[2]; }
 
-        if (it.n_src == 0) {
-            /* store-only item: rows above and below the region of interest */
-            const uint32_t total = (P.dst_h - n_rows) * groups_per_row;
-            uint32_t idx = (it.local - P.roi_items) * (nthreads * BG_GROUPS_PER_THREAD) + tid;
+    if (local >= P.roi_items) {
+        /* store-only item: rows above and below the region of interest */
+        const uint32_t total = (P.dst_h - n_rows) * groups_per_row;
+        uint32_t idx = (local - P.roi_items) * (nthreads * BG_GROUPS_PER_THREAD) + threadIdx.x;
 #pragma unroll 1
-            for (int q = 0; q < BG_GROUPS_PER_THREAD; ++q, idx += nthreads) {
-                if (idx >= total) break;
-                const uint32_t r = idx / groups_per_row, g = idx - r * groups_per_row;
-                const int y = (int)r < y1 ? (int)r : (int)(r + n_rows);
-                store_group<PLANAR>(dst, dst_pitch, dst_cstride, (int)(g * PX_PER_THREAD), y, bg4);
-            }
-        } else {
-            const uint32_t slot_k = k & 1u;
-            const uint32_t band_rows = P.tiles_x, gw = P.gw, rs = P.rs; /* rows per band, threads across, row slots */
-            const int ya = y1 + (int)(it.local * band_rows);
-            const int yb = min(ya + (int)band_rows - 1, y2);
-            const uint32_t phase = ((uint32_t)P.crop_x * 3u) & 15u;
-
-            /* The thread's two columns and their horizontal taps, while the copies are in flight.  The
-               two taps of a column are six consecutive bytes of a staged row (three when the second tap
-               is clamped onto the first, interpolation.h:76): they are fetched as the three aligned
-               words that hold them and shifted down to byte 0. */
-            const uint32_t slot = tid / gw, gi = tid - slot * gw;
-            const int xa = (int)(g_lo * PX_PER_THREAD + gi), xb = xa + (int)gw;
-            const int x_end = (int)((g_lo + n_groups) * PX_PER_THREAD);
-            const bool in_a = xa >= x1 && xa <= x2, in_b = xb >= x1 && xb <= x2;
-            const bool valid_b = xb < x_end;
-            const Axis axa = make_axis(in_a ? xa - x1 : 0, P.fx, P.crop_w);
-            const Axis axb = make_axis(in_b ? xb - x1 : 0, P.fx, P.crop_w);
-            const uint32_t oa = phase + (uint32_t)axa.i0 * 3u, ob = phase + (uint32_t)axb.i0 * 3u;
-            const uint32_t word_a = oa & ~3u, word_b = ob & ~3u;
-            const uint32_t shift_a = (oa & 3u) * 8u, shift_b = (ob & 3u) * 8u;
-            const uint32_t second_a = axa.i1 == axa.i0 ? 0x3210u : 0x3543u; /* bytes of the second tap in (u0, u1) */
-            const uint32_t second_b = axb.i1 == axb.i0 ? 0x3210u : 0x3543u;
-            const float2 wx0 = make_float2(axa.w0, axb.w0), wx1 = make_float2(axa.w1, axb.w1);
-
-            const uint32_t mbar = smem_addr(&sm.mbar[slot_k]);
-            const uint32_t parity = (parity_bits >> slot_k) & 1u;
-            parity_bits ^= 1u << slot_k;
-            if (!mbar_wait_bounded(mbar, parity)) {
-                /* never expected: record it and give the copies in flight (this item's and the next
-                   one's) one more bounded chance to land before the block's shared memory is released */
-                atomicExch(a.status, STATUS_STAGED_WAIT_TIMEOUT);
-                (void)mbar_wait_bounded(mbar, parity);
-                if (k + 1 < n_mine && sm.item[(k + 1) % 3].n_src != 0)
-                    (void)mbar_wait_bounded(smem_addr(&sm.mbar[slot_k ^ 1u]), (parity_bits >> (slot_k ^ 1u)) & 1u);
-                return;
-            }
-
-            if (slot < rs) {
-                const bool plain = in_a && in_b && valid_b;
-                /* running output pointer of column a (channel 0), advanced one round of row slots at a time */
-                const size_t px_bytes = PLANAR ? 4 : 12;
-                uint8_t* out_a = dst + (size_t)(ya + (int)slot) * dst_pitch + (size_t)xa * px_bytes;
-                const size_t b_off = (size_t)gw * px_bytes, row_step = (size_t)rs * dst_pitch;
-                const float4* rt = sm.row_tab[slot_k] + 2 * slot;
-#pragma unroll 1
-                for (int y = ya + (int)slot; y <= yb; y += (int)rs, rt += 2 * rs, out_a += row_step) {
-                    const float4 rows = rt[0], wy = rt[1];
-                    const uint32_t row_addr[2] = {__float_as_uint(rows.x), __float_as_uint(rows.y)};
-                    float2 tap[2][2][3]; /* [source row][first / second tap][channel] = (column a, column b) */
-#pragma unroll
-                    for (int r = 0; r < 2; ++r) {
-                        uint32_t wa0, wa1, wa2, wb0, wb1, wb2;
-                        lds32x3(row_addr[r] + word_a, wa0, wa1, wa2);
-                        lds32x3(row_addr[r] + word_b, wb0, wb1, wb2);
-                        const uint32_t ua0 = __funnelshift_r(wa0, wa1, shift_a), ua1 = __funnelshift_r(wa1, wa2, shift_a);
-                        const uint32_t ub0 = __funnelshift_r(wb0, wb1, shift_b), ub1 = __funnelshift_r(wb1, wb2, shift_b);
-                        const uint32_t ta = __byte_perm(ua0, ua1, second_a), tb = __byte_perm(ub0, ub1, second_b);
-#pragma unroll
-                        for (int c = 0; c < 3; ++c) {
-                            tap[r][0][c] = make_float2(byte_to_float<0>(ua0 >> (8 * c)), byte_to_float<0>(ub0 >> (8 * c)));
-                            tap[r][1][c] = make_float2(byte_to_float<0>(ta >> (8 * c)), byte_to_float<0>(tb >> (8 * c)));
-                        }
-                    }
-                    const float2 wy0 = make_float2(wy.x, wy.y), wy1 = make_float2(wy.z, wy.w);
-                    const float2 w00 = mul2(wx0, wy0), w10 = mul2(wx1, wy0), w01 = mul2(wx0, wy1), w11 = mul2(wx1, wy1);
-                    float2 v[3];
-#pragma unroll
-                    for (int c = 0; c < 3; ++c) {
-                        /* ((p00*w00 + p10*w10) + p01*w01) + p11*w11, every product and sum rounded */
-                        v[c] = add2(add2(add2(mul2(tap[0][0][c], w00), mul2(tap[0][1][c], w10), one), mul2(tap[1][0][c], w01), one),
-                                    mul2(tap[1][1][c], w11), one);
-                    }
-                    run_ops<CHAIN, 1>(v, sops, S.n_pre, S.n_ops, one);
-                    uint8_t* const out_b = out_a + b_off;
-                    if (plain) {
-                        store_pixel_at<PLANAR>(out_a, dst_cstride, v[0].x, v[1].x, v[2].x);
-                        store_pixel_at<PLANAR>(out_b, dst_cstride, v[0].y, v[1].y, v[2].y);
-                    } else { /* a column group straddling the edge of the region, or the last odd column */
-                        store_pixel_at<PLANAR>(out_a, dst_cstride, in_a ? v[0].x : bgv[0], in_a ? v[1].x : bgv[1], in_a ? v[2].x : bgv[2]);
-                        if (valid_b)
-                            store_pixel_at<PLANAR>(out_b, dst_cstride, in_b ? v[0].y : bgv[0], in_b ? v[1].y : bgv[1], in_b ? v[2].y : bgv[2]);
-                    }
-                }
-            }
-
-            /* background to the left and right of this band's rows */
-            const uint32_t n_side = groups_per_row - n_groups;
-            if (n_side != 0) {
-                const uint32_t total = (uint32_t)(yb - ya + 1) * n_side;
-#pragma unroll 1
-                for (uint32_t idx = tid; idx < total; idx += nthreads) {
-                    const uint32_t r = idx / n_side, bnd = idx - r * n_side;
-                    const uint32_t g = bnd < g_lo ? bnd : bnd + n_groups;
-                    store_group<PLANAR>(dst, dst_pitch, dst_cstride, (int)(g * PX_PER_THREAD), ya + (int)r, bg4);
-                }
-            }
+        for (int k = 0; k < BG_GROUPS_PER_THREAD; ++k, idx += nthreads) {
+            if (idx >= total) break;
+            const uint32_t r = idx / groups_per_row, g = idx - r * groups_per_row;
+            const int y = (int)r < y1 ? (int)r : (int)(r + n_rows);
+            store_group<PLANAR>(dst, dst_pitch, dst_cstride, (int)(g * PX_PER_THREAD), y, bg4);
         }
-        deposit(k + 2, ahead);
-        __syncthreads(); /* stage k & 1 and descriptor slot k % 3 may be reused from here on */
+        return;
+    }
+
+    /* shared memory: | mbarrier (16 B) | row table (32 B per row of the band) | staged source rows | */
+    uint64_t* const mbar_ptr = reinterpret_cast<uint64_t*>(staged_mem);
+    float4* const row_tab = reinterpret_cast<float4*>(staged_mem + 16);
+    unsigned char* const stage = staged_mem + STAGED_HEADER_BYTES;
+    const uint32_t stage_addr = smem_addr(stage);
+    const uint32_t mbar = smem_addr(mbar_ptr);
+
+    const uint32_t band_rows = P.tiles_x, gw = P.gw, rs = P.rs; /* rows per band, threads across, row slots */
+    const int ya = y1 + (int)(local * band_rows);
+    const int yb = min(ya + (int)band_rows - 1, y2);
+    const int crop_h = P.crop_h;
+    const float fy = P.fy;
+
+    /* source bytes of one crop row, widened to 16-byte boundaries */
+    const uint32_t row_first = ((uint32_t)P.crop_x * 3u) & ~15u;
+    const uint32_t phase = (uint32_t)P.crop_x * 3u - row_first;
+    const uint32_t row_len = (phase + (uint32_t)P.crop_w * 3u + 15u) & ~15u;
+
+    const int src_first = make_axis(ya - y1, fy, crop_h).i0;
+    const int src_last = make_axis(yb - y1, fy, crop_h).i1;
+    const uint32_t n_src = (uint32_t)(src_last - src_first + 1);
+    if (threadIdx.x == 0) {
+        mbar_init(mbar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_expect_tx(mbar, n_src * row_len);
+    }
+    if (threadIdx.x <= (uint32_t)(yb - ya)) {
+        /* vertical taps of one row of the band: shared-memory addresses of its two source rows, and
+           its two weights already duplicated into pairs */
+        const Axis ay = make_axis(ya + (int)threadIdx.x - y1, fy, crop_h);
+        row_tab[2 * threadIdx.x] = make_float4(__uint_as_float(stage_addr + (uint32_t)(ay.i0 - src_first) * row_len),
+                                               __uint_as_float(stage_addr + (uint32_t)(ay.i1 - src_first) * row_len), 0.0f, 0.0f);
+        row_tab[2 * threadIdx.x + 1] = make_float4(ay.w0, ay.w0, ay.w1, ay.w1);
+    }
+    __syncthreads(); /* barrier initialised and armed, row table written */
+    {
+        const uint8_t* g = P.src + (size_t)(P.crop_y + src_first) * P.src_pitch + row_first;
+        for (uint32_t r = threadIdx.x; r < n_src; r += nthreads)
+            bulk_copy_g2s(smem_addr(stage + r * row_len), g + (size_t)r * P.src_pitch, row_len, mbar);
+    }
+
+    /* The thread's two columns and their horizontal taps, while the copies are in flight.  The two
+       taps of a column are six consecutive bytes of a staged row (three when the second tap is
+       clamped onto the first, interpolation.h:76): they are fetched as the three aligned words
+       that hold them, shifted down to byte 0, and each byte is turned into a float by one byte
+       permute (2^23 + b) and half of a packed subtraction. */
+    const uint32_t slot = threadIdx.x / gw, gi = threadIdx.x - slot * gw;
+    const int xa = (int)(g_lo * PX_PER_THREAD + gi), xb = xa + (int)gw;
+    const int x_end = (int)((g_lo + n_groups) * PX_PER_THREAD);
+    const bool in_a = xa >= x1 && xa <= x2, in_b = xb >= x1 && xb <= x2;
+    const bool valid_b = xb < x_end;
+    const Axis axa = make_axis(in_a ? xa - x1 : 0, P.fx, P.crop_w);
+    const Axis axb = make_axis(in_b ? xb - x1 : 0, P.fx, P.crop_w);
+    const uint32_t oa = phase + (uint32_t)axa.i0 * 3u, ob = phase + (uint32_t)axb.i0 * 3u;
+    const uint32_t word_a = oa & ~3u, word_b = ob & ~3u;
+    const uint32_t shift_a = (oa & 3u) * 8u, shift_b = (ob & 3u) * 8u;
+    const uint32_t second_a = axa.i1 == axa.i0 ? 0x3210u : 0x3543u; /* bytes of the second tap in (u0, u1) */
+    const uint32_t second_b = axb.i1 == axb.i0 ? 0x3210u : 0x3543u;
+    const float2 wx0 = make_float2(axa.w0, axb.w0), wx1 = make_float2(axa.w1, axb.w1);
+
+    const bool arrived = mbar_wait_bounded(mbar, 0);
+    if (!arrived) {
+        /* never expected: record it and give the copies one more bounded chance to land before
+           this block's shared memory is released */
+        atomicExch(status, STATUS_STAGED_WAIT_TIMEOUT);
+        (void)mbar_wait_bounded(mbar, 0);
+        return;
+    }
+
+    if (slot < rs) {
+        const bool plain = in_a && in_b && valid_b;
+        /* running output pointer of column a (channel 0), advanced one round of row slots at a time */
+        const size_t px_bytes = PLANAR ? 4 : 12;
+        uint8_t* out_a = dst + (size_t)(ya + (int)slot) * dst_pitch + (size_t)xa * px_bytes;
+        const size_t b_off = (size_t)gw * px_bytes, row_step = (size_t)rs * dst_pitch;
+        const float4* rt = row_tab + 2 * slot;
+
+        /* interpolated value of the thread's two columns in the row described by t[0], t[1] */
+        auto interpolate = [&](const float4* t, float2 (&v)[3]) {
+            const float4 rows = t[0], wy = t[1];
+            const uint32_t row_addr[2] = {__float_as_uint(rows.x), __float_as_uint(rows.y)};
+            float2 tap[2][2][3]; /* [source row][first / second tap][channel] = (column a, column b) */
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                uint32_t wa0, wa1, wa2, wb0, wb1, wb2;
+                lds32x3(row_addr[r] + word_a, wa0, wa1, wa2);
+                lds32x3(row_addr[r] + word_b, wb0, wb1, wb2);
+                const uint32_t ua0 = __funnelshift_r(wa0, wa1, shift_a), ua1 = __funnelshift_r(wa1, wa2, shift_a);
+                const uint32_t ub0 = __funnelshift_r(wb0, wb1, shift_b), ub1 = __funnelshift_r(wb1, wb2, shift_b);
+                const uint32_t ta = __byte_perm(ua0, ua1, second_a), tb = __byte_perm(ub0, ub1, second_b);
+#pragma unroll
+                for (int c = 0; c < 3; ++c) {
+                    tap[r][0][c] = make_float2(byte_to_float(ua0 >> (8 * c)), byte_to_float(ub0 >> (8 * c)));
+                    tap[r][1][c] = make_float2(byte_to_float(ta >> (8 * c)), byte_to_float(tb >> (8 * c)));
+                }
+            }
+            const float2 wy0 = make_float2(wy.x, wy.y), wy1 = make_float2(wy.z, wy.w);
+            const float2 w00 = mul2(wx0, wy0), w10 = mul2(wx1, wy0), w01 = mul2(wx0, wy1), w11 = mul2(wx1, wy1);
+#pragma unroll
+            for (int c = 0; c < 3; ++c) {
+                /* ((p00*w00 + p10*w10) + p01*w01) + p11*w11, every product and sum rounded */
+                v[c] = add2(add2(add2(mul2(tap[0][0][c], w00), mul2(tap[0][1][c], w10), one), mul2(tap[1][0][c], w01), one),
+                            mul2(tap[1][1][c], w11), one);
+            }
+        };
+        auto store_row = [&](uint8_t* oa, const float2& r, const float2& g, const float2& bl) {
+            uint8_t* const ob = oa + b_off;
+            if (plain) {
+                store_pixel_at<PLANAR>(oa, dst_cstride, r.x, g.x, bl.x);
+                store_pixel_at<PLANAR>(ob, dst_cstride, r.y, g.y, bl.y);
+            } else { /* a column group straddling the edge of the region, or the last odd column */
+                store_pixel_at<PLANAR>(oa, dst_cstride, in_a ? r.x : bgv[0], in_a ? g.x : bgv[1], in_a ? bl.x : bgv[2]);
+                if (valid_b) store_pixel_at<PLANAR>(ob, dst_cstride, in_b ? r.y : bgv[0], in_b ? g.y : bgv[1], in_b ? bl.y : bgv[2]);
+            }
+        };
+
+        int y = ya + (int)slot;
+        /* two rows of the thread per round: the continuation's parameters are fetched once for both */
+#pragma unroll 1
+        for (; y + (int)rs <= yb; y += 2 * (int)rs, rt += 4 * rs, out_a += 2 * row_step) {
+            float2 v[6], lo[3], hi[3];
+            interpolate(rt, lo);
+            interpolate(rt + 2 * rs, hi);
+#pragma unroll
+            for (int c = 0; c < 3; ++c) { v[c] = lo[c]; v[3 + c] = hi[c]; }
+            run_ops<CHAIN, 2>(v, sops, S.n_pre, S.n_ops, one);
+            store_row(out_a, v[0], v[1], v[2]);
+            store_row(out_a + row_step, v[3], v[4], v[5]);
+        }
+        if (y <= yb) {
+            float2 v[3];
+            interpolate(rt, v);
+            run_ops<CHAIN, 1>(v, sops, S.n_pre, S.n_ops, one);
+            store_row(out_a, v[0], v[1], v[2]);
+        }
+    }
+
+    /* background to the left and right of this band's rows */
+    const uint32_t n_side = groups_per_row - n_groups;
+    if (n_side != 0) {
+        const uint32_t total = (uint32_t)(yb - ya + 1) * n_side;
+#pragma unroll 1
+        for (uint32_t idx = threadIdx.x; idx < total; idx += nthreads) {
+            const uint32_t r = idx / n_side, b = idx - r * n_side;
+            const uint32_t g = b < g_lo ? b : b + n_groups;
+            store_group<PLANAR>(dst, dst_pitch, dst_cstride, (int)(g * PX_PER_THREAD), ya + (int)r, bg4);
+        }
     }
 }
 
@@ -893,7 +844,7 @@ __global__ void __launch_bounds__(BLOCK_THREADS, FKB_STAGED_MIN_BLOCKS) staged_r
 /* ------------------------------------------------------------------------------------ */
 template <uint32_t CLASS, uint32_t CHAIN>
 __device__ __forceinline__ void run_body(uint32_t cls, const DevPlane& P, const DevSeq& S, const OpSlot* sops,
-                                         uint32_t local) {
+                                         uint32_t local, unsigned char* staged_mem, uint32_t* status) {
     if (CLASS != CLASS_MIXED) cls = CLASS;
     switch (cls) {
         case CLASS_FLAT_U8_F32: body_flat<CHAIN, true, false>(P, S, sops, local); break;
@@ -902,12 +853,24 @@ __device__ __forceinline__ void run_body(uint32_t cls, const DevPlane& P, const 
         case CLASS_RESIZE_U8_PLANAR: body_resize<CHAIN, FKB_SRC_U8X3, true>(P, S, sops, local); break;
         case CLASS_RESIZE_U8_PACKED: body_resize<CHAIN, FKB_SRC_U8X3, false>(P, S, sops, local); break;
         case CLASS_RESIZE_NV12_PACKED: body_resize<CHAIN, FKB_SRC_NV12, false>(P, S, sops, local); break;
+        case CLASS_RESIZE_U8_PLANAR_STAGED: body_resize_staged<CHAIN, true>(P, S, sops, local, staged_mem, status); break;
+        case CLASS_RESIZE_U8_PACKED_STAGED: body_resize_staged<CHAIN, false>(P, S, sops, local, staged_mem, status); break;
         default: body_generic(P, S, sops, local); break;
     }
 }
 
+/* Resident blocks per SM the compiler must leave room for.  The staged bodies hide the latency
+   of their shared-memory reads and of the next blocks' bulk copies with four blocks (64
+   registers per thread); the bodies that read taps straight from global memory keep all their
+   loads in flight in registers instead. */
+#ifndef FKB_STAGED_MIN_BLOCKS
+#define FKB_STAGED_MIN_BLOCKS 4
+#endif
+constexpr int min_blocks_of(uint32_t cls) {
+    return (cls == CLASS_RESIZE_U8_PLANAR_STAGED || cls == CLASS_RESIZE_U8_PACKED_STAGED) ? FKB_STAGED_MIN_BLOCKS : 1;
+}
 template <uint32_t CLASS, uint32_t CHAIN>
-__global__ void __launch_bounds__(BLOCK_THREADS) fused_plan_kernel(const __grid_constant__ LaunchArgs a) {
+__global__ void __launch_bounds__(BLOCK_THREADS, min_blocks_of(CLASS)) fused_plan_kernel(const __grid_constant__ LaunchArgs a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     OpSlot* sops = reinterpret_cast<OpSlot*>(smem_raw);
     __shared__ DevPlane s_plane;
@@ -927,7 +890,9 @@ __global__ void __launch_bounds__(BLOCK_THREADS) fused_plan_kernel(const __grid_
             expand_op(__ldg(reinterpret_cast<const uint4*>(a.ops + ops_begin + k)), sops + k);
     }
     __syncthreads();
-    run_body<CLASS, CHAIN>(s_plane.plane_class, s_plane, s_seq, sops, local);
+    /* staged classes: the region after the operation cache, on a 128-byte boundary */
+    unsigned char* staged_mem = smem_raw + (((a.max_seq_ops > 0 ? a.max_seq_ops : 1u) * (uint32_t)sizeof(OpSlot) + 127u) & ~127u);
+    run_body<CLASS, CHAIN>(s_plane.plane_class, s_plane, s_seq, sops, local, staged_mem, a.status);
 }
 
 /* ------------------------------------------------------------------------------------ */
@@ -974,34 +939,6 @@ static cudaError_t launch_class(uint32_t chain, const LaunchArgs& a, size_t smem
     return launch_one<CLASS, CHAIN_INTERPRET>(a, smem, stream);
 }
 
-/* The persistent staged kernel: a.grid_blocks blocks, each with two stages of a.staged_bytes. */
-template <bool PLANAR, uint32_t CHAIN>
-static cudaError_t launch_staged_one(const LaunchArgs& a, size_t smem, cudaStream_t stream) {
-    static size_t raised[64] = {};
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return e;
-    if (dev < 0 || dev >= 64 || raised[dev] < smem) {
-        e = cudaFuncSetAttribute(staged_resize_kernel<CHAIN, PLANAR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return e;
-        if (dev >= 0 && dev < 64) raised[dev] = smem;
-    }
-    staged_resize_kernel<CHAIN, PLANAR><<<a.grid_blocks, a.block_threads, smem, stream>>>(a);
-    return cudaGetLastError();
-}
-template <bool PLANAR>
-static cudaError_t launch_staged(uint32_t chain, const LaunchArgs& a, cudaStream_t stream) {
-    const size_t ops_bytes = ((size_t)(a.max_seq_ops > 0 ? a.max_seq_ops : 1) * sizeof(OpSlot) + 127) & ~(size_t)127;
-    const size_t smem = ops_bytes + ((sizeof(StagedSmem) + 127) & ~(size_t)127) + 2 * (size_t)a.staged_bytes;
-#define FKB_LAUNCH_CASE(CH) \
-    if (chain == (CH)) return launch_staged_one<PLANAR, (CH)>(a, smem, stream);
-    FKB_CHAIN_MENU(FKB_LAUNCH_CASE)
-#undef FKB_LAUNCH_CASE
-    return launch_staged_one<PLANAR, CHAIN_INTERPRET>(a, smem, stream);
-}
-size_t staged_fixed_smem_bytes() { return ((sizeof(StagedSmem) + 127) & ~(size_t)127) + sizeof(DevSeq); }
-int staged_blocks_per_sm() { return FKB_STAGED_MIN_BLOCKS; }
-
 bool chain_is_compiled(uint32_t chain) {
 #define FKB_CHAIN_TEST(CH) if (chain == (CH)) return true;
     FKB_CHAIN_MENU(FKB_CHAIN_TEST)
@@ -1011,7 +948,8 @@ bool chain_is_compiled(uint32_t chain) {
 
 /* launch_class: one of CLASS_* or CLASS_MIXED; chain: a menu chain or CHAIN_INTERPRET. */
 cudaError_t launch_plan_kernel(uint32_t launch_cls, uint32_t chain, const LaunchArgs& a, cudaStream_t stream) {
-    const size_t smem = (size_t)(a.max_seq_ops > 0 ? a.max_seq_ops : 1) * sizeof(OpSlot);
+    const size_t ops_bytes = (size_t)(a.max_seq_ops > 0 ? a.max_seq_ops : 1) * sizeof(OpSlot);
+    const size_t smem = a.staged_bytes ? ((ops_bytes + 127) & ~(size_t)127) + a.staged_bytes : ops_bytes;
     switch (launch_cls) {
         case CLASS_FLAT_U8_F32: return launch_class<CLASS_FLAT_U8_F32>(chain, a, smem, stream);
         case CLASS_FLAT_F32_F32: return launch_class<CLASS_FLAT_F32_F32>(chain, a, smem, stream);
@@ -1019,8 +957,8 @@ cudaError_t launch_plan_kernel(uint32_t launch_cls, uint32_t chain, const Launch
         case CLASS_RESIZE_U8_PLANAR: return launch_class<CLASS_RESIZE_U8_PLANAR>(chain, a, smem, stream);
         case CLASS_RESIZE_U8_PACKED: return launch_class<CLASS_RESIZE_U8_PACKED>(chain, a, smem, stream);
         case CLASS_RESIZE_NV12_PACKED: return launch_class<CLASS_RESIZE_NV12_PACKED>(chain, a, smem, stream);
-        case CLASS_RESIZE_U8_PLANAR_STAGED: return launch_staged<true>(chain, a, stream);
-        case CLASS_RESIZE_U8_PACKED_STAGED: return launch_staged<false>(chain, a, stream);
+        case CLASS_RESIZE_U8_PLANAR_STAGED: return launch_class<CLASS_RESIZE_U8_PLANAR_STAGED>(chain, a, smem, stream);
+        case CLASS_RESIZE_U8_PACKED_STAGED: return launch_class<CLASS_RESIZE_U8_PACKED_STAGED>(chain, a, smem, stream);
         case CLASS_GENERIC: return launch_one<CLASS_GENERIC, CHAIN_INTERPRET>(a, smem, stream);
         default: return launch_one<CLASS_MIXED, CHAIN_INTERPRET>(a, smem, stream);
     }
