@@ -849,22 +849,40 @@ extern "C" FKB_API int fkb_execute(const fkb_plan_desc* desc, void* stream) {
 /* The reference's counterpart is a Ptr allocated as MemType::DeviceAndPinned with
  * upload(stream) before and download(stream) after executeOperations
  * (core/data/ptr_nd.h:252-268,519-530): device mirrors are allocated once and every step
- * copies in, launches and copies out. */
+ * copies in, launches and copies out.
+ *
+ * A session splits the batch by source image: group g holds the planes that read image g and
+ * has its own plan.  A step uploads image g, launches group g, and hands the group's outputs
+ * to a second stream for the copy back, so that the upload of image g+1 (host to device) runs
+ * while the outputs of group g travel the other way. */
 struct fkb_host_session {
-    struct Source { const void* host; void* dev; size_t bytes; };
-    struct Download { void* host; const void* dev; size_t pitch, row_bytes, rows; };
-    std::vector<Source> sources;
+    struct Copy { void* host; const void* dev; size_t pitch, row_bytes, rows; }; /* rows == 1: plain copy */
+    struct Group {
+        const void* host_src = nullptr;
+        void* dev_src = nullptr;
+        size_t src_bytes = 0;
+        fkb_plan* plan = nullptr;
+        std::vector<Copy> downloads;
+        cudaEvent_t computed = nullptr;
+    };
+    std::vector<Group> groups;
     std::vector<void*> dev_outputs;
-    std::vector<Download> downloads;
-    fkb_plan* plan = nullptr;
+    cudaStream_t out_stream = nullptr;
+    cudaEvent_t start = nullptr, downloaded = nullptr;
     uint64_t h2d_bytes = 0, d2h_bytes = 0;
 };
 
 extern "C" FKB_API int fkb_host_session_destroy(fkb_host_session* s) {
     if (!s) return FKB_OK;
-    if (s->plan) fkb_plan_destroy(s->plan);
-    for (auto& src : s->sources) if (src.dev) cudaFree(src.dev);
+    for (auto& g : s->groups) {
+        if (g.plan) fkb_plan_destroy(g.plan);
+        if (g.dev_src) cudaFree(g.dev_src);
+        if (g.computed) cudaEventDestroy(g.computed);
+    }
     for (void* p : s->dev_outputs) if (p) cudaFree(p);
+    if (s->start) cudaEventDestroy(s->start);
+    if (s->downloaded) cudaEventDestroy(s->downloaded);
+    if (s->out_stream) cudaStreamDestroy(s->out_stream);
     delete s;
     return FKB_OK;
 }
@@ -882,13 +900,13 @@ extern "C" FKB_API int fkb_host_session_create(const fkb_plan_desc* desc, fkb_ho
     if (rc) return rc;
     fkb_host_session* s = new (std::nothrow) fkb_host_session();
     if (!s) return fail(FKB_ERR_INVALID_ARGUMENT, "out of host memory");
+    auto bail = [&](int code) { fkb_host_session_destroy(s); return code; };
 
     const int n = desc->n_planes;
     std::vector<fkb_plane> planes(desc->planes, desc->planes + n);
-    std::map<const void*, size_t> src_index;
 
     /* extent of every plane's output in host memory */
-    std::vector<size_t> out_bytes(n);
+    std::vector<size_t> out_bytes(n), out_payload(n);
     uintptr_t lo = UINTPTR_MAX, hi = 0;
     size_t sum = 0;
     for (int i = 0; i < n; ++i) {
@@ -897,65 +915,109 @@ extern "C" FKB_API int fkb_host_session_create(const fkb_plan_desc* desc, fkb_ho
         const size_t row = (size_t)p.dst_width * dst_pixel_bytes(q.dst_format);
         out_bytes[i] = (q.dst_format == FKB_DST_F32_PLANAR3 ? 2 * (size_t)p.dst_channel_stride : 0) +
                        (size_t)p.dst_pitch * (p.dst_height - 1) + row;
+        out_payload[i] = (q.dst_format == FKB_DST_F32_PLANAR3 ? 3 : 1) * row * p.dst_height;
         lo = std::min(lo, reinterpret_cast<uintptr_t>(p.dst));
         hi = std::max(hi, reinterpret_cast<uintptr_t>(p.dst) + out_bytes[i]);
-        sum += (q.dst_format == FKB_DST_F32_PLANAR3 ? 3 : 1) * row * p.dst_height;
+        sum += out_payload[i];
     }
-    /* Outputs that tile one host range without gaps (a dense tensor) get one device mirror
-       and one copy back; anything else is mirrored and copied plane by plane, row-exact. */
+    /* Outputs that tile one host range without gaps (a dense tensor) get one device mirror;
+       anything else is mirrored and copied plane by plane, row-exact. */
     const bool one_block = (hi - lo) == sum;
+    unsigned char* block = nullptr;
+    if (one_block) {
+        void* b = nullptr;
+        const cudaError_t e = cudaMalloc(&b, hi - lo);
+        if (e != cudaSuccess) return bail(fail_cuda(e, "output mirror allocation", __LINE__));
+        s->dev_outputs.push_back(b);
+        block = static_cast<unsigned char*>(b);
+    }
 
-    auto bail = [&](int code) { fkb_host_session_destroy(s); return code; };
+    /* groups: planes by source image, in order of first use */
+    std::map<const void*, size_t> group_of;
+    std::vector<std::vector<int>> members;
     for (int i = 0; i < n; ++i) {
         const fkb_plane& p = desc->planes[i];
         const fkb_sequence& q = desc->sequences[p.sequence];
         const size_t rows = q.src_format == FKB_SRC_NV12 ? (size_t)p.src_height + (p.src_height + 1) / 2 : p.src_height;
         const size_t bytes = (size_t)p.src_pitch * rows;
-        auto it = src_index.find(p.src);
-        if (it == src_index.end()) {
-            fkb_host_session::Source sd{p.src, nullptr, bytes};
-            const cudaError_t e = cudaMalloc(&sd.dev, bytes);
+        auto it = group_of.find(p.src);
+        if (it == group_of.end()) {
+            fkb_host_session::Group g;
+            g.host_src = p.src;
+            g.src_bytes = bytes;
+            const cudaError_t e = cudaMalloc(&g.dev_src, bytes);
             if (e != cudaSuccess) return bail(fail_cuda(e, "source mirror allocation", __LINE__));
-            s->sources.push_back(sd);
+            s->groups.push_back(g);
+            members.emplace_back();
             s->h2d_bytes += bytes;
-            it = src_index.emplace(p.src, s->sources.size() - 1).first;
-        } else if (s->sources[it->second].bytes != bytes) {
+            it = group_of.emplace(p.src, s->groups.size() - 1).first;
+        } else if (s->groups[it->second].src_bytes != bytes) {
             return bail(fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: one source pointer is described with two sizes", i));
         }
-        planes[i].src = s->sources[it->second].dev;
+        members[it->second].push_back(i);
+        planes[i].src = s->groups[it->second].dev_src;
     }
-    if (one_block) {
-        void* block = nullptr;
-        const cudaError_t e = cudaMalloc(&block, hi - lo);
-        if (e != cudaSuccess) return bail(fail_cuda(e, "output mirror allocation", __LINE__));
-        s->dev_outputs.push_back(block);
-        for (int i = 0; i < n; ++i)
-            planes[i].dst = static_cast<unsigned char*>(block) + (reinterpret_cast<uintptr_t>(desc->planes[i].dst) - lo);
-        s->downloads.push_back({reinterpret_cast<void*>(lo), block, hi - lo, hi - lo, 1});
-        s->d2h_bytes = hi - lo;
-    } else {
-        for (int i = 0; i < n; ++i) {
+
+    for (size_t g = 0; g < s->groups.size(); ++g) {
+        fkb_host_session::Group& grp = s->groups[g];
+        std::vector<fkb_plane> sub;
+        for (int i : members[g]) {
             const fkb_plane& p = desc->planes[i];
             const fkb_sequence& q = desc->sequences[p.sequence];
-            void* mirror = nullptr;
-            const cudaError_t e = cudaMalloc(&mirror, out_bytes[i]);
-            if (e != cudaSuccess) return bail(fail_cuda(e, "output mirror allocation", __LINE__));
-            s->dev_outputs.push_back(mirror);
-            planes[i].dst = mirror;
-            const size_t row = (size_t)p.dst_width * dst_pixel_bytes(q.dst_format);
-            const int channels = q.dst_format == FKB_DST_F32_PLANAR3 ? 3 : 1;
-            for (int c = 0; c < channels; ++c) {
-                const size_t off = (size_t)c * p.dst_channel_stride;
-                s->downloads.push_back({static_cast<unsigned char*>(p.dst) + off, static_cast<unsigned char*>(mirror) + off,
-                                        p.dst_pitch, row, p.dst_height});
-                s->d2h_bytes += row * p.dst_height;
+            if (one_block) {
+                planes[i].dst = block + (reinterpret_cast<uintptr_t>(p.dst) - lo);
+            } else {
+                void* mirror = nullptr;
+                const cudaError_t e = cudaMalloc(&mirror, out_bytes[i]);
+                if (e != cudaSuccess) return bail(fail_cuda(e, "output mirror allocation", __LINE__));
+                s->dev_outputs.push_back(mirror);
+                planes[i].dst = mirror;
+            }
+            sub.push_back(planes[i]);
+            const bool dense = out_bytes[i] == out_payload[i]; /* no padding inside this plane's output */
+            if (dense) {
+                grp.downloads.push_back({p.dst, planes[i].dst, out_bytes[i], out_bytes[i], 1});
+            } else {
+                const size_t row = (size_t)p.dst_width * dst_pixel_bytes(q.dst_format);
+                const int channels = q.dst_format == FKB_DST_F32_PLANAR3 ? 3 : 1;
+                for (int c = 0; c < channels; ++c) {
+                    const size_t off = (size_t)c * p.dst_channel_stride;
+                    grp.downloads.push_back({static_cast<unsigned char*>(p.dst) + off, static_cast<unsigned char*>(planes[i].dst) + off,
+                                             p.dst_pitch, row, p.dst_height});
+                }
+            }
+            s->d2h_bytes += out_payload[i];
+        }
+        /* dense planes of equal size at a constant distance (a batch dealt round-robin over the
+           images) come back as one strided copy; neighbours as one plain copy */
+        if (one_block && grp.downloads.size() == members[g].size() && grp.downloads.size() > 1) {
+            const auto& d0 = grp.downloads[0];
+            const ptrdiff_t step = static_cast<const unsigned char*>(grp.downloads[1].host) - static_cast<const unsigned char*>(d0.host);
+            bool regular = step >= (ptrdiff_t)d0.row_bytes;
+            for (size_t k = 1; k < grp.downloads.size() && regular; ++k) {
+                const auto& d = grp.downloads[k];
+                regular = d.rows == 1 && d.row_bytes == d0.row_bytes &&
+                          static_cast<const unsigned char*>(d.host) - static_cast<const unsigned char*>(d0.host) == step * (ptrdiff_t)k;
+            }
+            if (regular && d0.rows == 1) {
+                fkb_host_session::Copy c = d0;
+                if ((size_t)step == d0.row_bytes) { c.row_bytes = c.pitch = d0.row_bytes * grp.downloads.size(); c.rows = 1; }
+                else { c.pitch = (size_t)step; c.rows = grp.downloads.size(); }
+                grp.downloads.assign(1, c);
             }
         }
+        fkb_plan_desc dd = *desc;
+        dd.planes = sub.data();
+        dd.n_planes = (int32_t)sub.size();
+        rc = fkb_plan_create(&dd, &grp.plan);
+        if (rc) return bail(rc);
+        const cudaError_t e = cudaEventCreateWithFlags(&grp.computed, cudaEventDisableTiming);
+        if (e != cudaSuccess) return bail(fail_cuda(e, "cudaEventCreate", __LINE__));
     }
-    fkb_plan_desc dd = *desc;
-    dd.planes = planes.data();
-    rc = fkb_plan_create(&dd, &s->plan);
-    if (rc) return bail(rc);
+    cudaError_t e = cudaStreamCreateWithFlags(&s->out_stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&s->start, cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&s->downloaded, cudaEventDisableTiming);
+    if (e != cudaSuccess) return bail(fail_cuda(e, "stream / event creation", __LINE__));
     *out = s;
     return FKB_OK;
 }
@@ -963,13 +1025,22 @@ extern "C" FKB_API int fkb_host_session_create(const fkb_plan_desc* desc, fkb_ho
 extern "C" FKB_API int fkb_host_session_run(fkb_host_session* s, void* stream_) {
     if (!s) return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_host_session_run: session is NULL");
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-    for (const auto& src : s->sources) FKB_CUDA(cudaMemcpyAsync(src.dev, src.host, src.bytes, cudaMemcpyHostToDevice, stream));
-    const int rc = fkb_plan_launch(s->plan, stream);
-    if (rc) return rc;
-    for (const auto& d : s->downloads) {
-        if (d.rows == 1) FKB_CUDA(cudaMemcpyAsync(d.host, d.dev, d.row_bytes, cudaMemcpyDeviceToHost, stream));
-        else FKB_CUDA(cudaMemcpy2DAsync(d.host, d.pitch, d.dev, d.pitch, d.row_bytes, d.rows, cudaMemcpyDeviceToHost, stream));
+    /* the copy-back stream starts after whatever the caller already queued on `stream` */
+    FKB_CUDA(cudaEventRecord(s->start, stream));
+    FKB_CUDA(cudaStreamWaitEvent(s->out_stream, s->start, 0));
+    for (auto& g : s->groups) {
+        FKB_CUDA(cudaMemcpyAsync(g.dev_src, g.host_src, g.src_bytes, cudaMemcpyHostToDevice, stream));
+        const int rc = fkb_plan_launch(g.plan, stream);
+        if (rc) return rc;
+        FKB_CUDA(cudaEventRecord(g.computed, stream));
+        FKB_CUDA(cudaStreamWaitEvent(s->out_stream, g.computed, 0));
+        for (const auto& d : g.downloads) {
+            if (d.rows == 1) FKB_CUDA(cudaMemcpyAsync(d.host, d.dev, d.row_bytes, cudaMemcpyDeviceToHost, s->out_stream));
+            else FKB_CUDA(cudaMemcpy2DAsync(d.host, d.pitch, d.dev, d.pitch, d.row_bytes, d.rows, cudaMemcpyDeviceToHost, s->out_stream));
+        }
     }
+    FKB_CUDA(cudaEventRecord(s->downloaded, s->out_stream));
+    FKB_CUDA(cudaStreamWaitEvent(stream, s->downloaded, 0));
     FKB_CUDA(cudaStreamSynchronize(stream));
     return FKB_OK;
 }
