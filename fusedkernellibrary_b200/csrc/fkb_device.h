@@ -12,6 +12,8 @@
 
 namespace fkb {
 
+constexpr uint32_t CHAIN_INTERPRET = 0xFFFFFFFFu; /* see the end of this file */
+
 /* How a plane is processed (chosen on the host from formats, sizes and alignment). */
 enum PlaneClass : uint32_t {
     CLASS_GENERIC = 0,       /* one thread per output pixel, scalar accesses; always valid   */
@@ -59,7 +61,7 @@ struct alignas(16) DevSeq {
     int32_t src_format, dst_format, resize_mode;
     int32_t n_ops, n_pre, ops_begin; /* ops_begin: index of the first op in the op table      */
     int32_t pre_kind;                /* PRE_* below                                           */
-    int32_t pad;
+    uint32_t chain;                  /* the continuation as a compiled chain, or CHAIN_INTERPRET */
     float bg[3];
     float one;                       /* 1.0f, read at run time by the packed additions         */
 };
@@ -161,8 +163,11 @@ constexpr uint32_t STATUS_STAGED_WAIT_TIMEOUT = 1; /* a bulk copy did not comple
 /* Compile-time operation chains.  A chain is a list of 4-bit operation codes, first operation
  * in the lowest nibble, 0 terminates.  Kernels are instantiated for the chains in
  * FKB_CHAIN_MENU; any other sequence runs through the interpreter (CHAIN_INTERPRET). */
-constexpr uint32_t CHAIN_INTERPRET = 0xFFFFFFFFu;
+
 constexpr uint32_t CH_MUL = 1, CH_SUB = 2, CH_DIV = 3, CH_ADD = 4, CH_SWAP = 6, CH_SAT = 7, CH_YUV = 8, CH_DIVC = 9;
+#if defined(__CUDACC__)
+__host__ __device__
+#endif
 constexpr uint32_t chain_of(uint32_t a = 0, uint32_t b = 0, uint32_t c = 0, uint32_t d = 0, uint32_t e = 0) {
     return a | (b << 4) | (c << 8) | (d << 12) | (e << 16);
 }

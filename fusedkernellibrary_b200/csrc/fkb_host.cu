@@ -452,7 +452,7 @@ static int check_sequence(const fkb_sequence& s, int index, DevSeq& ds) {
                     t == VT_F32 ? "float" : "uchar", dst_u8 ? "uchar3" : "float");
 
     ds.src_format = s.src_format; ds.dst_format = s.dst_format; ds.resize_mode = s.resize_mode;
-    ds.n_ops = s.n_ops; ds.n_pre = n_pre; ds.ops_begin = 0; ds.pad = 0;
+    ds.n_ops = s.n_ops; ds.n_pre = n_pre; ds.ops_begin = 0; ds.chain = CHAIN_INTERPRET;
     ds.pre_kind = (n_pre == 0 || pre_only_casts) ? PRE_IDENTITY : pre_is_yuv ? PRE_YUV_BT709 : PRE_GENERAL;
     ds.bg[0] = s.background[0]; ds.bg[1] = s.background[1]; ds.bg[2] = s.background[2]; ds.one = 1.0f;
     return FKB_OK;
@@ -635,6 +635,7 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
         const uint32_t chain = lower_ops(d->sequences[s], ds.n_pre, step_exp_x[s], step_exp_y[s], img.ops, dev_n_pre);
         if (s == 0) common_chain = chain;
         else if (chain != common_chain) common_chain = CHAIN_INTERPRET;
+        ds.chain = chain_is_compiled(chain) ? chain : CHAIN_INTERPRET;
         ds.ops_begin = (int32_t)begin;
         ds.n_ops = (int32_t)(img.ops.size() - begin);
         ds.n_pre = dev_n_pre - (int32_t)begin;

@@ -842,9 +842,22 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
 /* ------------------------------------------------------------------------------------ */
 /* the kernel                                                                           */
 /* ------------------------------------------------------------------------------------ */
+/* Chains compiled into the kernels (codes of the operations after the geometry stage, in
+ * order).  Casts never reach the device table.  Anything else is interpreted. */
+#define FKB_CHAIN_MENU(X)                                                                                         \
+    X(chain_of())                                 /* no continuation (copy, Cast -> Resize)                    */ \
+    X(chain_of(CH_DIVC))                          /* Div                                                       */ \
+    X(chain_of(CH_DIVC, CH_SUB, CH_DIVC))         /* Div, Sub, Div: normalise with mean and std                */ \
+    X(chain_of(CH_MUL, CH_SUB, CH_DIVC, CH_SWAP)) /* Mul, Sub, Div, RGB2BGR                                    */ \
+    X(chain_of(CH_MUL, CH_SUB, CH_DIVC))          /* Mul, Sub, Div                                             */ \
+    X(chain_of(CH_MUL, CH_SUB))                   /* Mul, Sub                                                  */ \
+    X(chain_of(CH_ADD, CH_DIVC))                  /* Add, Div                                                  */ \
+    X(chain_of(CH_SWAP, CH_MUL, CH_SAT))          /* RGB2BGR, Mul, SaturateCast                                */
+
+/* The bodies of one continuation (compiled chain or interpreter), selected by the plane's class. */
 template <uint32_t CLASS, uint32_t CHAIN>
-__device__ __forceinline__ void run_body(uint32_t cls, const DevPlane& P, const DevSeq& S, const OpSlot* sops,
-                                         uint32_t local, unsigned char* staged_mem, uint32_t* status) {
+__device__ __forceinline__ void run_class(uint32_t cls, const DevPlane& P, const DevSeq& S, const OpSlot* sops,
+                                          uint32_t local, unsigned char* staged_mem, uint32_t* status) {
     if (CLASS != CLASS_MIXED) cls = CLASS;
     switch (cls) {
         case CLASS_FLAT_U8_F32: body_flat<CHAIN, true, false>(P, S, sops, local); break;
@@ -853,21 +866,43 @@ __device__ __forceinline__ void run_body(uint32_t cls, const DevPlane& P, const 
         case CLASS_RESIZE_U8_PLANAR: body_resize<CHAIN, FKB_SRC_U8X3, true>(P, S, sops, local); break;
         case CLASS_RESIZE_U8_PACKED: body_resize<CHAIN, FKB_SRC_U8X3, false>(P, S, sops, local); break;
         case CLASS_RESIZE_NV12_PACKED: body_resize<CHAIN, FKB_SRC_NV12, false>(P, S, sops, local); break;
-        case CLASS_RESIZE_U8_PLANAR_STAGED: body_resize_staged<CHAIN, true>(P, S, sops, local, staged_mem, status); break;
-        case CLASS_RESIZE_U8_PACKED_STAGED: body_resize_staged<CHAIN, false>(P, S, sops, local, staged_mem, status); break;
+        case CLASS_RESIZE_U8_PLANAR_STAGED:
+            if constexpr (CLASS != CLASS_MIXED) body_resize_staged<CHAIN, true>(P, S, sops, local, staged_mem, status);
+            break;
+        case CLASS_RESIZE_U8_PACKED_STAGED:
+            if constexpr (CLASS != CLASS_MIXED) body_resize_staged<CHAIN, false>(P, S, sops, local, staged_mem, status);
+            break;
         default: body_generic(P, S, sops, local); break;
     }
 }
 
-/* Resident blocks per SM the compiler must leave room for.  The staged bodies hide the latency
-   of their shared-memory reads and of the next blocks' bulk copies with four blocks (64
-   registers per thread); the bodies that read taps straight from global memory keep all their
-   loads in flight in registers instead. */
+/* A plan of one class runs the body of that class with the plan's continuation.  A plan of several
+ * classes (divergent horizontal fusion, data_parallel_patterns.h:315-323) selects per block: first
+ * the continuation of the plane's sequence, if it is one of the compiled chains, then the class. */
+template <uint32_t CLASS, uint32_t CHAIN>
+__device__ __forceinline__ void run_body(uint32_t cls, const DevPlane& P, const DevSeq& S, const OpSlot* sops,
+                                         uint32_t local, unsigned char* staged_mem, uint32_t* status) {
+    if constexpr (CLASS != CLASS_MIXED) {
+        run_class<CLASS, CHAIN>(cls, P, S, sops, local, staged_mem, status);
+    } else {
+        const uint32_t chain = S.chain;
+#define FKB_MIXED_CASE(CH) \
+    if (chain == (CH)) { run_class<CLASS_MIXED, (CH)>(cls, P, S, sops, local, staged_mem, status); return; }
+        FKB_CHAIN_MENU(FKB_MIXED_CASE)
+#undef FKB_MIXED_CASE
+        run_class<CLASS_MIXED, CHAIN_INTERPRET>(cls, P, S, sops, local, staged_mem, status);
+    }
+}
+
 #ifndef FKB_STAGED_MIN_BLOCKS
 #define FKB_STAGED_MIN_BLOCKS 4
 #endif
+#ifndef FKB_MIXED_MIN_BLOCKS
+#define FKB_MIXED_MIN_BLOCKS 6
+#endif
 constexpr int min_blocks_of(uint32_t cls) {
-    return (cls == CLASS_RESIZE_U8_PLANAR_STAGED || cls == CLASS_RESIZE_U8_PACKED_STAGED) ? FKB_STAGED_MIN_BLOCKS : 1;
+    return (cls == CLASS_RESIZE_U8_PLANAR_STAGED || cls == CLASS_RESIZE_U8_PACKED_STAGED) ? FKB_STAGED_MIN_BLOCKS
+           : cls == CLASS_MIXED ? FKB_MIXED_MIN_BLOCKS : 1;
 }
 template <uint32_t CLASS, uint32_t CHAIN>
 __global__ void __launch_bounds__(BLOCK_THREADS, min_blocks_of(CLASS)) fused_plan_kernel(const __grid_constant__ LaunchArgs a) {
@@ -898,18 +933,6 @@ __global__ void __launch_bounds__(BLOCK_THREADS, min_blocks_of(CLASS)) fused_pla
 /* ------------------------------------------------------------------------------------ */
 /* launcher                                                                             */
 /* ------------------------------------------------------------------------------------ */
-
-/* Chains compiled into the kernels (codes of the operations after the geometry stage, in
- * order).  Casts never reach the device table.  Anything else is interpreted. */
-#define FKB_CHAIN_MENU(X)                                                                                         \
-    X(chain_of())                                 /* no continuation (copy, Cast -> Resize)                    */ \
-    X(chain_of(CH_DIVC))                          /* Div                                                       */ \
-    X(chain_of(CH_DIVC, CH_SUB, CH_DIVC))         /* Div, Sub, Div: normalise with mean and std                */ \
-    X(chain_of(CH_MUL, CH_SUB, CH_DIVC, CH_SWAP)) /* Mul, Sub, Div, RGB2BGR                                    */ \
-    X(chain_of(CH_MUL, CH_SUB, CH_DIVC))          /* Mul, Sub, Div                                             */ \
-    X(chain_of(CH_MUL, CH_SUB))                   /* Mul, Sub                                                  */ \
-    X(chain_of(CH_ADD, CH_DIVC))                  /* Add, Div                                                  */ \
-    X(chain_of(CH_SWAP, CH_MUL, CH_SAT))          /* RGB2BGR, Mul, SaturateCast                                */
 
 /* Launches one instantiation; the first launch that needs more than the default 48 KB of
    dynamic shared memory raises the kernel's limit (once per instantiation and device). */
