@@ -900,9 +900,13 @@ __device__ __forceinline__ void run_body(uint32_t cls, const DevPlane& P, const 
 #ifndef FKB_MIXED_MIN_BLOCKS
 #define FKB_MIXED_MIN_BLOCKS 6
 #endif
+#ifndef FKB_DIRECT_MIN_BLOCKS
+#define FKB_DIRECT_MIN_BLOCKS 1
+#endif
 constexpr int min_blocks_of(uint32_t cls) {
     return (cls == CLASS_RESIZE_U8_PLANAR_STAGED || cls == CLASS_RESIZE_U8_PACKED_STAGED) ? FKB_STAGED_MIN_BLOCKS
-           : cls == CLASS_MIXED ? FKB_MIXED_MIN_BLOCKS : 1;
+           : cls == CLASS_MIXED ? FKB_MIXED_MIN_BLOCKS
+           : (cls == CLASS_RESIZE_NV12_PACKED || cls == CLASS_RESIZE_U8_PLANAR || cls == CLASS_RESIZE_U8_PACKED) ? FKB_DIRECT_MIN_BLOCKS : 1;
 }
 template <uint32_t CLASS, uint32_t CHAIN>
 __global__ void __launch_bounds__(BLOCK_THREADS, min_blocks_of(CLASS)) fused_plan_kernel(const __grid_constant__ LaunchArgs a) {

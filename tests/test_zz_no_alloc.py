@@ -19,8 +19,8 @@ from tests import cases as tc
 
 
 def test_plans_beyond_the_fixed_table_are_refused(fkb_lib):
-    """Capacity is checked on the host, before any device is touched: 112 B per plane alone put
-    a 5000-plane batch over the 512 KiB table."""
+    """Capacity is checked on the host, before any device is touched: 112 B per plane and 16 B per
+    thread block put a 5000-plane batch over the 512 KiB table."""
     src = np.zeros((8, 8 * 3), np.uint8)
     out = np.zeros((5000, 8, 8, 3), np.float32)
     plan = abi.HostPlan()
