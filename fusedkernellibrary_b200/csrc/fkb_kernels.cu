@@ -614,8 +614,8 @@ __device__ __forceinline__ void body_resize(const DevPlane& P, const DevSeq& S, 
 /* ------------------------------------------------------------------------------------ */
 
 /* Asynchronous bulk copies (the copy engine that also serves tensor-map TMA) and the mbarrier
- * that counts their bytes.  No cluster launch and no multicast: every copy lands in the shared
- * memory of the block that issued it. */
+ * that counts their bytes.  Kernels are launched without clusters: every copy lands in the shared
+ * memory of the block that issued it and nowhere else. */
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 /* Three consecutive aligned words of shared memory at a 32-bit shared-window address. */
 __device__ __forceinline__ void lds32x3(uint32_t addr, uint32_t& w0, uint32_t& w1, uint32_t& w2) {
