@@ -20,6 +20,7 @@ ERR_UNSUPPORTED = 2
 ERR_CUDA = 3
 ERR_TOO_LARGE = 4
 ERR_NO_DEVICE = 5
+ERR_DEVICE_WAIT = 6
 
 # vocabulary ---------------------------------------------------------------------------
 SRC_U8X3, SRC_F32X3, SRC_NV12 = 1, 2, 3
@@ -179,7 +180,7 @@ EXPORTS = [
     "fkb_reference_block_size", "fkb_plan_create", "fkb_plan_validate", "fkb_plan_launch", "fkb_plan_get_info",
     "fkb_plan_get_resize_params", "fkb_plan_destroy", "fkb_execute", "fkb_host_session_create",
     "fkb_host_session_run", "fkb_host_session_get_traffic", "fkb_host_session_destroy",
-    "fkb_execute_host", "fkb_execute_static",
+    "fkb_execute_host", "fkb_execute_static", "fkb_plan_check",
 ]
 
 
@@ -207,6 +208,7 @@ def load_library(path: os.PathLike | None = None) -> C.CDLL:
     lib.fkb_plan_get_info.argtypes = [C.c_void_p, C.POINTER(PlanInfo)]
     lib.fkb_plan_get_resize_params.argtypes = [C.c_void_p, C.c_int32, C.POINTER(ResizeParams)]
     lib.fkb_plan_destroy.argtypes = [C.c_void_p]
+    lib.fkb_plan_check.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_uint32)]
     lib.fkb_execute.argtypes = [C.POINTER(PlanDesc), C.c_void_p]
     lib.fkb_execute_host.argtypes = [C.POINTER(PlanDesc), C.c_void_p]
     lib.fkb_execute_static.argtypes = [C.POINTER(PlanDesc), C.c_void_p]
@@ -237,6 +239,13 @@ class DevicePlan:
 
     def launch(self, stream: int | None = None) -> None:
         check(self._lib.fkb_plan_launch(self._h, C.c_void_p(stream or 0)), "fkb_plan_launch")
+
+    def check(self, stream: int | None = None) -> int:
+        """Synchronises `stream` and returns the device status word (0 = every block completed);
+        raises FkbError(ERR_DEVICE_WAIT) otherwise."""
+        st = C.c_uint32()
+        check(self._lib.fkb_plan_check(self._h, C.c_void_p(stream or 0), C.byref(st)), "fkb_plan_check")
+        return st.value
 
     def info(self) -> PlanInfo:
         info = PlanInfo()

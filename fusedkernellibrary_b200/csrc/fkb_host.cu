@@ -728,6 +728,7 @@ extern "C" FKB_API const char* fkb_status_string(int status) {
         case FKB_ERR_CUDA: return "CUDA error";
         case FKB_ERR_TOO_LARGE: return "too large";
         case FKB_ERR_NO_DEVICE: return "no CUDA device";
+        case FKB_ERR_DEVICE_WAIT: return "a device-side wait ran out";
         default: return "unknown status";
     }
 }
@@ -823,6 +824,20 @@ extern "C" FKB_API int fkb_plan_get_resize_params(const fkb_plan* plan, int32_t 
     return FKB_OK;
 }
 
+static int read_status(const uint32_t* d_status, cudaStream_t stream, uint32_t* out) {
+    uint32_t st = 0;
+    FKB_CUDA(cudaMemcpyAsync(&st, d_status, sizeof st, cudaMemcpyDeviceToHost, stream));
+    FKB_CUDA(cudaStreamSynchronize(stream));
+    if (out) *out = st;
+    if (st != 0) return fail(FKB_ERR_DEVICE_WAIT, "a thread block gave up waiting for its asynchronous copies (status %u); outputs are incomplete", st);
+    return FKB_OK;
+}
+
+extern "C" FKB_API int fkb_plan_check(const fkb_plan* plan, void* stream, uint32_t* device_status) {
+    if (!plan) return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_plan_check: plan is NULL");
+    return read_status(plan->args.status, static_cast<cudaStream_t>(stream), device_status);
+}
+
 extern "C" FKB_API int fkb_plan_destroy(fkb_plan* plan) {
     if (!plan) return FKB_OK;
     cudaError_t e = cudaSuccess;
@@ -838,10 +853,12 @@ extern "C" FKB_API int fkb_execute(const fkb_plan_desc* desc, void* stream) {
     if (rc) return rc;
     rc = fkb_plan_launch(plan, stream);
     const cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+    int rs = FKB_OK;
+    if (rc == FKB_OK && e == cudaSuccess) rs = fkb_plan_check(plan, stream, nullptr);
     fkb_plan_destroy(plan);
     if (rc) return rc;
     if (e != cudaSuccess) return fail_cuda(e, "cudaStreamSynchronize", __LINE__);
-    return FKB_OK;
+    return rs;
 }
 
 /* ------------------------------------------------------------------------------------ */
@@ -1043,6 +1060,10 @@ extern "C" FKB_API int fkb_host_session_run(fkb_host_session* s, void* stream_) 
     FKB_CUDA(cudaEventRecord(s->downloaded, s->out_stream));
     FKB_CUDA(cudaStreamWaitEvent(stream, s->downloaded, 0));
     FKB_CUDA(cudaStreamSynchronize(stream));
+    for (auto& g : s->groups) {
+        const int rc = fkb_plan_check(g.plan, stream, nullptr);
+        if (rc) return rc;
+    }
     return FKB_OK;
 }
 
@@ -1125,5 +1146,5 @@ extern "C" FKB_API int fkb_execute_static(const fkb_plan_desc* desc, void* strea
     const cudaError_t se = cudaStreamSynchronize(stream);
     if (le != cudaSuccess) return fail_cuda(le, "kernel launch", __LINE__);
     if (se != cudaSuccess) return fail_cuda(se, "cudaStreamSynchronize", __LINE__);
-    return FKB_OK;
+    return read_status(img.args_for(table).status, stream, nullptr);
 }

@@ -41,7 +41,8 @@ typedef enum fkb_status {
     FKB_ERR_UNSUPPORTED = 2,      /* a chain shape the kernels do not implement               */
     FKB_ERR_CUDA = 3,             /* a CUDA runtime call failed; see fkb_last_error()         */
     FKB_ERR_TOO_LARGE = 4,        /* beyond a stated capacity (fixed-scratch entry point)     */
-    FKB_ERR_NO_DEVICE = 5         /* no usable CUDA device: there is no CPU fallback          */
+    FKB_ERR_NO_DEVICE = 5,        /* no usable CUDA device: there is no CPU fallback          */
+    FKB_ERR_DEVICE_WAIT = 6       /* a kernel gave up a bounded wait; outputs are incomplete  */
 } fkb_status;
 
 /* ------------------------------------------------------------------------------------ */
@@ -207,6 +208,14 @@ FKB_API int fkb_plan_get_info(const fkb_plan* plan, fkb_plan_info* out_info);
 
 /* Copies the derived resize parameters of plane `index` out of a plan (for parity checks). */
 FKB_API int fkb_plan_get_resize_params(const fkb_plan* plan, int32_t index, fkb_resize_params* out);
+
+/* Reads the plan's device status word after synchronising `stream` (the stream of the last
+ * launch).  Kernels never trap and never wait without a limit: a thread block whose wait for an
+ * asynchronous copy ran out records it there and returns.  *device_status is 0 when every block
+ * completed; the call then returns FKB_OK, otherwise FKB_ERR_DEVICE_WAIT.  The reference has no
+ * counterpart (its kernel has no waits); its launch-site check is cudaGetLastError alone
+ * (executors.h:285), which fkb_plan_launch keeps. */
+FKB_API int fkb_plan_check(const fkb_plan* plan, void* stream, uint32_t* device_status);
 
 /* Frees the plan's descriptor memory.  Call after the launches that use it have finished. */
 FKB_API int fkb_plan_destroy(fkb_plan* plan);

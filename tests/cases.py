@@ -154,6 +154,18 @@ def small_cases():
                                 (10, 10, 2, 2)]),
         crop_resize_case("c3_upscale", 37, 1, 64, 48, 4, 224, 224, True, chains.normalize_ops(), lo=4, hi=24),
         crop_resize_case("c3_pitched_src", 38, 2, 100, 60, 5, 48, 32, True, chains.normalize_ops(), src_pitch=333),
+        # frames whose pitch and base are 16-byte aligned take the shared-memory staged path
+        crop_resize_case("c3_staged_borders", 61, 1, 512, 300, 6, 224, 224, True, chains.normalize_ops(),
+                         rects=[(0, 0, 512, 300), (511, 299, 1, 1), (500, 0, 12, 300), (0, 290, 512, 10), (3, 5, 509, 295),
+                                (255, 100, 2, 200)]),
+        crop_resize_case("c3_staged_steep", 62, 2, 1024, 600, 5, 64, 64, True, chains.normalize_ops(),
+                         rects=[(0, 0, 1024, 600), (1, 1, 1023, 599), (17, 33, 1000, 64), (100, 0, 64, 600), (0, 0, 1024, 8)]),
+        crop_resize_case("c3_staged_upscale", 63, 1, 64, 64, 5, 224, 224, True, chains.normalize_ops(),
+                         rects=[(0, 0, 3, 3), (61, 61, 3, 3), (5, 0, 7, 64), (0, 5, 64, 7), (31, 31, 2, 2)]),
+        crop_resize_case("c2_staged_packed_bg", 64, 2, 208, 120, 9, 60, 44, False, chains.readme_ops(),
+                         background=(10.0, 20.0, 30.0)),
+        crop_resize_case("c2_staged_ignore_ar_odd_groups", 65, 1, 208, 120, 4, 36, 20, False, chains.readme_ops(),
+                         mode=abi.RESIZE_IGNORE_AR),
         nv12_case("c4_exact3", 41, 3, 96, 54, 32, 18),
         nv12_case("c4_fractional", 42, 2, 96, 54, 40, 22),
         nv12_case("c4_pitched", 43, 2, 98, 54, 36, 20, pitch=128),
