@@ -64,8 +64,10 @@ struct alignas(16) DevSeq {
     uint32_t chain;                  /* the continuation as a compiled chain, or CHAIN_INTERPRET */
     float bg[3];
     float one;                       /* 1.0f, read at run time by the packed additions         */
+    float bg_out[3];                 /* bg after the operations that follow the geometry stage  */
+    float pad;
 };
-static_assert(sizeof(DevSeq) == 48, "DevSeq layout");
+static_assert(sizeof(DevSeq) == 64, "DevSeq layout");
 
 enum PreKind : int32_t {
     PRE_IDENTITY = 0, /* nothing, or only exact uchar->float casts, before interpolation      */

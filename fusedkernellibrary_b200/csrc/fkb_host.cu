@@ -336,6 +336,31 @@ static void advance_range_resize(ValueRange& v, int step_exp_x, int step_exp_y, 
     v.check();
 }
 
+/* The default value of a PRESERVE_AR resize after the operations that follow the geometry stage
+ * (resize.h:84-86), in the reference's arithmetic: binary32, every operation rounded, true
+ * division (this file is compiled without contraction). */
+static float saturate_round_u8_host(float f) {
+    if (f > 255.0f) return 255.0f;
+    if (f < 0.0f) return 0.0f;
+    return (float)(int)(f + 0.5f);
+}
+static void background_after_ops(const fkb_sequence& s, int n_pre, float out[3]) {
+    volatile float v[3] = {s.background[0], s.background[1], s.background[2]};
+    for (int k = n_pre; k < s.n_ops; ++k) {
+        const fkb_op& op = s.ops[k];
+        switch (op.opcode) {
+            case FKB_OP_MUL: for (int c = 0; c < 3; ++c) v[c] = v[c] * op.p[c]; break;
+            case FKB_OP_SUB: for (int c = 0; c < 3; ++c) v[c] = v[c] - op.p[c]; break;
+            case FKB_OP_DIV: for (int c = 0; c < 3; ++c) v[c] = v[c] / op.p[c]; break;
+            case FKB_OP_ADD: for (int c = 0; c < 3; ++c) v[c] = v[c] + op.p[c]; break;
+            case FKB_OP_SWAP_RB: { const float t = v[0]; v[0] = v[2]; v[2] = t; break; }
+            case FKB_OP_SATURATE_CAST_U8: for (int c = 0; c < 3; ++c) v[c] = saturate_round_u8_host(v[c]); break;
+            default: break; /* casts leave a float value unchanged; YUV conversion never follows a resize */
+        }
+    }
+    out[0] = v[0]; out[1] = v[1]; out[2] = v[2];
+}
+
 /* Device form of a sequence's operations. */
 static uint32_t chain_code_of(int dev_opcode) {
     switch (dev_opcode) {
@@ -455,6 +480,7 @@ static int check_sequence(const fkb_sequence& s, int index, DevSeq& ds) {
     ds.n_ops = s.n_ops; ds.n_pre = n_pre; ds.ops_begin = 0; ds.chain = CHAIN_INTERPRET;
     ds.pre_kind = (n_pre == 0 || pre_only_casts) ? PRE_IDENTITY : pre_is_yuv ? PRE_YUV_BT709 : PRE_GENERAL;
     ds.bg[0] = s.background[0]; ds.bg[1] = s.background[1]; ds.bg[2] = s.background[2]; ds.one = 1.0f;
+    background_after_ops(s, n_pre, ds.bg_out); ds.pad = 0.0f;
     return FKB_OK;
 }
 

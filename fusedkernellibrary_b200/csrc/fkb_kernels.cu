@@ -392,6 +392,20 @@ __device__ __forceinline__ void body_flat(const DevPlane& P, const DevSeq& S, co
 /* body: bilinear resize                                                                */
 /* ------------------------------------------------------------------------------------ */
 
+/* Position idx of a row-major walk over rows of `per_row` cells, advanced `step` cells at a time
+   with one division at the start instead of one per step. */
+struct CellWalk {
+    uint32_t r, c, dr, dc, per_row;
+    __device__ __forceinline__ CellWalk(uint32_t idx, uint32_t step, uint32_t per_row_) : per_row(per_row_) {
+        r = idx / per_row; c = idx - r * per_row;
+        dr = step / per_row; dc = step - dr * per_row;
+    }
+    __device__ __forceinline__ void advance() {
+        r += dr; c += dc;
+        if (c >= per_row) { c -= per_row; ++r; }
+    }
+};
+
 /* Stores one group of four output pixels (v[3*i + channel]) at column x0 of row y. */
 template <bool PLANAR>
 __device__ __forceinline__ void store_group(uint8_t* dst, uint32_t pitch, uint32_t cstride, int x0, int y,
@@ -451,9 +465,10 @@ __device__ __forceinline__ void body_resize(const DevPlane& P, const DevSeq& S, 
 
     /* The value every output element outside the region of interest ends up with: the
        default value run through the continuation (resize.h:84-86). */
-    float bgv[3] = {S.bg[0], S.bg[1], S.bg[2]};
+    /* what every output element outside the region of interest ends up with: the default value
+       after the continuation (resize.h:84-86), evaluated once when the plan was made */
+    const float bgv[3] = {S.bg_out[0], S.bg_out[1], S.bg_out[2]};
     const float2 one = dup2(S.one);
-    run_ops_1<CHAIN>(bgv, sops, S.n_pre, S.n_ops, one);
     float bg4[12];
 #pragma unroll
     for (int i = 0; i < PX_PER_THREAD; ++i) { bg4[3 * i] = bgv[0]; bg4[3 * i + 1] = bgv[1]; bg4[3 * i + 2] = bgv[2]; }
@@ -462,12 +477,11 @@ __device__ __forceinline__ void body_resize(const DevPlane& P, const DevSeq& S, 
         /* store-only item: rows above and below the region of interest */
         const uint32_t total = (P.dst_h - n_rows) * groups_per_row;
         uint32_t idx = (local - P.roi_items) * (nthreads * BG_GROUPS_PER_THREAD) + threadIdx.x;
+        CellWalk w(idx, nthreads, groups_per_row);
 #pragma unroll 1
-        for (int k = 0; k < BG_GROUPS_PER_THREAD; ++k, idx += nthreads) {
-            if (idx >= total) break;
-            const uint32_t r = idx / groups_per_row, g = idx - r * groups_per_row;
-            const int y = (int)r < y1 ? (int)r : (int)(r + n_rows);
-            store_group<PLANAR>(dst, dst_pitch, dst_cstride, (int)(g * PX_PER_THREAD), y, bg4);
+        for (int k = 0; k < BG_GROUPS_PER_THREAD && idx < total; ++k, idx += nthreads, w.advance()) {
+            const int y = (int)w.r < y1 ? (int)w.r : (int)(w.r + n_rows);
+            store_group<PLANAR>(dst, dst_pitch, dst_cstride, (int)(w.c * PX_PER_THREAD), y, bg4);
         }
         return;
     }
@@ -668,9 +682,10 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
     const uint32_t n_rows = (uint32_t)(y2 - y1 + 1);
     const uint32_t nthreads = blockDim.x;
 
-    float bgv[3] = {S.bg[0], S.bg[1], S.bg[2]};
+    /* what every output element outside the region of interest ends up with: the default value
+       after the continuation (resize.h:84-86), evaluated once when the plan was made */
+    const float bgv[3] = {S.bg_out[0], S.bg_out[1], S.bg_out[2]};
     const float2 one = dup2(S.one);
-    run_ops_1<CHAIN>(bgv, sops, S.n_pre, S.n_ops, one);
     float bg4[12];
 #pragma unroll
     for (int i = 0; i < PX_PER_THREAD; ++i) { bg4[3 * i] = bgv[0]; bg4[3 * i + 1] = bgv[1]; bg4[3 * i + 2] = bgv[2]; }
@@ -679,12 +694,11 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
         /* store-only item: rows above and below the region of interest */
         const uint32_t total = (P.dst_h - n_rows) * groups_per_row;
         uint32_t idx = (local - P.roi_items) * (nthreads * BG_GROUPS_PER_THREAD) + threadIdx.x;
+        CellWalk w(idx, nthreads, groups_per_row);
 #pragma unroll 1
-        for (int k = 0; k < BG_GROUPS_PER_THREAD; ++k, idx += nthreads) {
-            if (idx >= total) break;
-            const uint32_t r = idx / groups_per_row, g = idx - r * groups_per_row;
-            const int y = (int)r < y1 ? (int)r : (int)(r + n_rows);
-            store_group<PLANAR>(dst, dst_pitch, dst_cstride, (int)(g * PX_PER_THREAD), y, bg4);
+        for (int k = 0; k < BG_GROUPS_PER_THREAD && idx < total; ++k, idx += nthreads, w.advance()) {
+            const int y = (int)w.r < y1 ? (int)w.r : (int)(w.r + n_rows);
+            store_group<PLANAR>(dst, dst_pitch, dst_cstride, (int)(w.c * PX_PER_THREAD), y, bg4);
         }
         return;
     }
@@ -830,11 +844,11 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
     const uint32_t n_side = groups_per_row - n_groups;
     if (n_side != 0) {
         const uint32_t total = (uint32_t)(yb - ya + 1) * n_side;
+        CellWalk w(threadIdx.x, nthreads, n_side);
 #pragma unroll 1
-        for (uint32_t idx = threadIdx.x; idx < total; idx += nthreads) {
-            const uint32_t r = idx / n_side, b = idx - r * n_side;
-            const uint32_t g = b < g_lo ? b : b + n_groups;
-            store_group<PLANAR>(dst, dst_pitch, dst_cstride, (int)(g * PX_PER_THREAD), ya + (int)r, bg4);
+        for (uint32_t idx = threadIdx.x; idx < total; idx += nthreads, w.advance()) {
+            const uint32_t g = w.c < g_lo ? w.c : w.c + n_groups;
+            store_group<PLANAR>(dst, dst_pitch, dst_cstride, (int)(g * PX_PER_THREAD), ya + (int)w.r, bg4);
         }
     }
 }
