@@ -299,6 +299,8 @@ def make_workload(name: str, seed: int) -> Workload:
         return LongChain(seed, n_ops=int(name[3:] or 16))
     if name == "c4":
         return Nv12Resize(seed)
+    if name == "c4small":
+        return Nv12Resize(seed, n=8)
     if name == "c5b":
         return Divergent(seed)
     raise SystemExit(f"unknown workload {name}")

@@ -25,7 +25,8 @@ enum PlaneClass : uint32_t {
     CLASS_RESIZE_NV12_PACKED = 6,
     CLASS_RESIZE_U8_PLANAR_STAGED = 7, /* bilinear from a source footprint staged in shared memory */
     CLASS_RESIZE_U8_PACKED_STAGED = 8,
-    CLASS_COUNT = 9,
+    CLASS_RESIZE_NV12_PACKED_STAGED = 9, /* NV12 taps from luma and chroma rows staged in shared memory */
+    CLASS_COUNT = 10,
     CLASS_MIXED = 0xFF       /* launch-level only: planes of several classes in one grid     */
 };
 
@@ -41,7 +42,8 @@ struct alignas(16) DevPlane {
                              /* output for IGNORE_AR                                          */
     uint32_t seq;
     uint32_t plane_class;
-    uint32_t seg_pixels;     /* FLAT classes: pixels per contiguous segment                   */
+    uint32_t seg_pixels;     /* FLAT classes: pixels per contiguous segment; staged NV12:     */
+                             /* output rows per work item (band)                              */
     uint32_t n_segs;         /* FLAT classes: 1 (dense plane) or dst_h (one segment per row)  */
     /* RESIZE classes: tiling of the region of interest (see ResizeTiling) */
     uint32_t roi_items;      /* work items that interpolate; the rest fill background rows    */
@@ -159,6 +161,11 @@ constexpr uint32_t STAGED_MAX_ROWS = 64;          /* output rows per band       
 #endif
 constexpr uint32_t STAGED_MAX_STAGE_BYTES = FKB_STAGE_KB * 1024u;
 constexpr uint32_t STAGED_HEADER_BYTES = 16 + STAGED_MAX_ROWS * 32;
+#ifndef FKB_NV12_STAGE_KB
+#define FKB_NV12_STAGE_KB 64
+#endif
+constexpr uint32_t NV12_MAX_STAGE_BYTES = FKB_NV12_STAGE_KB * 1024u; /* luma and chroma rows of a band tile */
+constexpr uint32_t NV12_MAX_SPAN = 256;           /* source rows between a band's first and last tap */
 constexpr uint32_t STAGED_WAIT_LIMIT = 1u << 22;  /* try_wait rounds before a block gives up     */
 constexpr uint32_t STATUS_STAGED_WAIT_TIMEOUT = 1; /* a bulk copy did not complete in time        */
 

@@ -535,6 +535,58 @@ static StagedTiling staged_tiling(const DevPlane& dp, uint32_t block_threads) {
     return t;
 }
 
+/* Staged NV12: bands of rows times tiles of columns; the luma and chroma rows between a band's
+ * first and last tap, over the tile's byte range, must fit the stage. */
+struct Nv12Tiling {
+    bool ok = false;
+    uint32_t band_rows = 0, gw = 0, rs = 0, tiles_x = 0, n_bands = 0, stage_bytes = 0;
+};
+static Nv12Tiling nv12_staged_tiling(const DevPlane& dp, uint32_t block_threads) {
+    Nv12Tiling t;
+    if ((reinterpret_cast<uintptr_t>(dp.src) % 16) != 0 || (dp.src_pitch % 16) != 0) return t;
+    const uint32_t g_lo = (uint32_t)dp.x1 / PX_PER_THREAD;
+    const uint32_t n_groups = (uint32_t)dp.x2 / PX_PER_THREAD - g_lo + 1;
+    const uint32_t n_rows = (uint32_t)(dp.y2 - dp.y1 + 1);
+    const uint32_t pairs = n_groups * (PX_PER_THREAD / 2);
+    t.tiles_x = (pairs + block_threads - 1) / block_threads;
+    t.gw = (pairs + t.tiles_x - 1) / t.tiles_x;
+    t.rs = block_threads / t.gw;
+    /* widest byte range of any column tile */
+    uint32_t row_len = 0;
+    for (uint32_t tx = 0; tx < t.tiles_x; ++tx) {
+        const int c_base = (int)(g_lo * PX_PER_THREAD + tx * 2 * t.gw);
+        const int x_end = (int)std::min((g_lo + n_groups) * PX_PER_THREAD, (uint32_t)c_base + 2 * t.gw);
+        const int rc0 = std::min(std::max(c_base, dp.x1), dp.x2), rc1 = std::max(std::min(x_end - 1, dp.x2), rc0);
+        const int sx_first = dp.crop_x + staged_src_row(rc0 - dp.x1, dp.fx);
+        const int sx_last = dp.crop_x + std::min(staged_src_row(rc1 - dp.x1, dp.fx) + 1, dp.crop_w - 1);
+        const uint32_t byte0 = (uint32_t)sx_first & ~15u;
+        row_len = std::max(row_len, std::min(((uint32_t)sx_last + 2u + 15u) & ~15u, dp.src_pitch) - byte0);
+    }
+    auto worst = [&](uint32_t band, uint32_t& span) {
+        uint32_t rows = 0;
+        span = 0;
+        for (uint32_t a = 0; a < n_rows; a += band) {
+            const uint32_t b = std::min(a + band, n_rows) - 1;
+            const int first = dp.crop_y + staged_src_row((int)a, dp.fy);
+            const int last = dp.crop_y + std::min(staged_src_row((int)b, dp.fy) + 1, dp.crop_h - 1);
+            const uint32_t l_span = (uint32_t)(last - first + 1), c_span = (uint32_t)((last >> 1) - (first >> 1) + 1);
+            rows = std::max(rows, l_span + c_span);
+            span = std::max(span, l_span);
+        }
+        return rows;
+    };
+    uint32_t band = std::min<uint32_t>(STAGED_MAX_ROWS, n_rows), span = 0;
+    while (band > 1 && (worst(band, span) * row_len > NV12_MAX_STAGE_BYTES || span > NV12_MAX_SPAN)) --band;
+    const uint32_t rows = worst(band, span);
+    if (rows * row_len > NV12_MAX_STAGE_BYTES || span > NV12_MAX_SPAN) return t;
+    if (band > t.rs) band -= band % t.rs;
+    t.band_rows = band;
+    t.n_bands = (n_rows + band - 1) / band;
+    t.stage_bytes = worst(band, span) * row_len;
+    t.ok = true;
+    return t;
+}
+
 static bool aligned(const void* p, uintptr_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 
 static int lower(const fkb_plan_desc* d, HostImage& img) {
@@ -710,6 +762,38 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
             img.block_threads = BLOCK_THREADS;
             img.staged_bytes = STAGED_HEADER_BYTES + stage;
             img.launch_class = common_class = cls;
+        }
+    }
+    /* NV12 resize plans whose every plane can stage the luma and chroma rows of its band tiles */
+    if (common_class == CLASS_RESIZE_NV12_PACKED) {
+        std::vector<Nv12Tiling> st(img.planes.size());
+        bool all = true;
+        uint32_t stage = 0;
+        for (size_t i = 0; i < img.planes.size() && all; ++i) {
+            st[i] = nv12_staged_tiling(img.planes[i], BLOCK_THREADS);
+            all = st[i].ok;
+            stage = std::max(stage, st[i].stage_bytes);
+        }
+        if (all) {
+            uint64_t t2 = 0;
+            uniform = true;
+            for (size_t i = 0; i < img.planes.size(); ++i) {
+                DevPlane& dp = img.planes[i];
+                const ResizeTiling rt = resize_tiling(dp.dst_w, dp.dst_h, dp.x1, dp.y1, dp.x2, dp.y2, BLOCK_THREADS);
+                const uint32_t items = st[i].n_bands * st[i].tiles_x + rt.bg_items;
+                dp.plane_class = CLASS_RESIZE_NV12_PACKED_STAGED;
+                dp.roi_items = st[i].n_bands * st[i].tiles_x; dp.tiles_x = st[i].tiles_x; dp.seg_pixels = st[i].band_rows;
+                dp.gw = st[i].gw; dp.rs = st[i].rs;
+                img.item_start[i] = (uint32_t)t2;
+                t2 += items;
+            }
+            if (t2 > 0x7FFFFFFFull) return fail(FKB_ERR_INVALID_ARGUMENT, "plan needs more than 2^31 thread blocks");
+            img.item_start[img.planes.size()] = (uint32_t)t2;
+            img.total_items = (uint32_t)t2;
+            img.uniform_items = 0;
+            img.block_threads = BLOCK_THREADS;
+            img.staged_bytes = STAGED_HEADER_BYTES + 2 * NV12_MAX_SPAN + stage;
+            img.launch_class = common_class = CLASS_RESIZE_NV12_PACKED_STAGED;
         }
     }
 #endif

@@ -854,6 +854,229 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
 }
 
 /* ------------------------------------------------------------------------------------ */
+/* body: bilinear resize of NV12 from source rows staged in shared memory               */
+/* ------------------------------------------------------------------------------------ */
+__device__ __forceinline__ void mbar_expect_tx_only(uint32_t mbar, uint32_t bytes) {
+    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(mbar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t mbar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(mbar) : "memory");
+}
+__device__ __forceinline__ uint32_t lds_u8(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(addr));
+    return v;
+}
+
+/* A work item is a band of rows of one plane's region of interest times a tile of its columns.
+ * Only the luma and chroma rows that some tap of the band reads with a non-zero weight are
+ * copied (an exact 3:1 reduction touches one luma row in three), each as one bulk copy of the
+ * tile's byte range widened to 16-byte boundaries.  ReadYUV<NV12> takes Y at (x, y) and the U,V
+ * pair at (x>>1, y>>1) (color_conversion.h:329-346); the conversion runs on every tap before
+ * the interpolation, as in the reference's chain.  A tap whose weight is exactly zero adds +-0
+ * to a sum whose first term is never -0, so it is skipped without changing a bit. */
+template <uint32_t CHAIN>
+__device__ __forceinline__ void body_nv12_staged(const DevPlane& P, const DevSeq& S, const OpSlot* sops, uint32_t local,
+                                                 unsigned char* staged_mem, uint32_t* status) {
+    constexpr bool PLANAR = false;
+    uint8_t* const dst = P.dst;
+    const uint32_t dst_pitch = P.dst_pitch, dst_cstride = P.dst_cstride;
+    const uint32_t groups_per_row = P.dst_w / PX_PER_THREAD;
+    const int x1 = P.x1, y1 = P.y1, x2 = P.x2, y2 = P.y2;
+    const uint32_t g_lo = (uint32_t)x1 / PX_PER_THREAD;
+    const uint32_t n_groups = (uint32_t)x2 / PX_PER_THREAD - g_lo + 1;
+    const uint32_t n_rows = (uint32_t)(y2 - y1 + 1);
+    const uint32_t nthreads = blockDim.x, tid = threadIdx.x;
+    const float bgv[3] = {S.bg_out[0], S.bg_out[1], S.bg_out[2]};
+    const float2 one = dup2(S.one);
+    float bg4[12];
+#pragma unroll
+    for (int i = 0; i < PX_PER_THREAD; ++i) { bg4[3 * i] = bgv[0]; bg4[3 * i + 1] = bgv[1]; bg4[3 * i + 2] = bgv[2]; }
+
+    if (local >= P.roi_items) {
+        /* store-only item: rows above and below the region of interest */
+        const uint32_t total = (P.dst_h - n_rows) * groups_per_row;
+        uint32_t idx = (local - P.roi_items) * (nthreads * BG_GROUPS_PER_THREAD) + tid;
+        CellWalk w(idx, nthreads, groups_per_row);
+#pragma unroll 1
+        for (int k = 0; k < BG_GROUPS_PER_THREAD && idx < total; ++k, idx += nthreads, w.advance()) {
+            const int y = (int)w.r < y1 ? (int)w.r : (int)(w.r + n_rows);
+            store_group<PLANAR>(dst, dst_pitch, dst_cstride, (int)(w.c * PX_PER_THREAD), y, bg4);
+        }
+        return;
+    }
+
+    /* shared memory: | mbarrier (16 B) | row table (32 B per row of the band) | luma flags | chroma
+       flags | luma rows | chroma rows | */
+    uint64_t* const mbar_ptr = reinterpret_cast<uint64_t*>(staged_mem);
+    float4* const row_tab = reinterpret_cast<float4*>(staged_mem + 16);
+    unsigned char* const need_l = staged_mem + STAGED_HEADER_BYTES;
+    unsigned char* const need_c = need_l + NV12_MAX_SPAN;
+    unsigned char* const stage = need_c + NV12_MAX_SPAN;
+    const uint32_t stage_addr = smem_addr(stage);
+    const uint32_t mbar = smem_addr(mbar_ptr);
+
+    const uint32_t tiles_x = P.tiles_x, band_rows = P.seg_pixels, gw = P.gw, rs = P.rs;
+    const uint32_t band = local / tiles_x, tile_x = local - band * tiles_x;
+    const int ya = y1 + (int)(band * band_rows);
+    const int yb = min(ya + (int)band_rows - 1, y2);
+    const int crop_h = P.crop_h, crop_w = P.crop_w, crop_x = P.crop_x, crop_y = P.crop_y;
+    const float fx = P.fx, fy = P.fy;
+
+    /* columns of this tile and the byte range of a source row that their taps touch */
+    const int c_base = (int)(g_lo * PX_PER_THREAD + tile_x * 2 * gw);
+    const int x_end = (int)min((g_lo + n_groups) * PX_PER_THREAD, (uint32_t)c_base + 2 * gw);
+    const int rc0 = min(max(c_base, x1), x2), rc1 = max(min(x_end - 1, x2), rc0); /* region columns inside the tile */
+    const int sx_first = crop_x + make_axis(max(rc0, x1) - x1, fx, crop_w).i0;
+    const int sx_last = crop_x + make_axis(max(rc1, x1) - x1, fx, crop_w).i1;
+    const uint32_t byte0 = (uint32_t)sx_first & ~15u;
+    const uint32_t row_len = min(((uint32_t)sx_last + 2u + 15u) & ~15u, P.src_pitch) - byte0;
+
+    /* source rows of the band */
+    const int l_first = crop_y + make_axis(ya - y1, fy, crop_h).i0;
+    const int l_last = crop_y + make_axis(yb - y1, fy, crop_h).i1;
+    const uint32_t l_span = (uint32_t)(l_last - l_first + 1);
+    const int c_first = l_first >> 1;
+    const uint32_t c_span = (uint32_t)((l_last >> 1) - c_first + 1);
+    const uint32_t chroma_addr = stage_addr + l_span * row_len;
+
+    if (tid == 0) {
+        mbar_init(mbar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (tid < l_span) need_l[tid] = 0;
+    if (tid < c_span) need_c[tid] = 0;
+    __syncthreads();
+    if (tid <= (uint32_t)(yb - ya)) {
+        const Axis ay = make_axis(ya + (int)tid - y1, fy, crop_h);
+        const int r0 = crop_y + ay.i0, r1 = crop_y + ay.i1;
+        need_l[r0 - l_first] = 1;
+        need_c[(r0 >> 1) - c_first] = 1;
+        if (ay.w1 != 0.0f) { need_l[r1 - l_first] = 1; need_c[(r1 >> 1) - c_first] = 1; }
+        /* luma and chroma row addresses of the two vertical taps (16-bit offsets from the stage) */
+        const uint32_t a0 = (uint32_t)(r0 - l_first) * row_len, a1 = (uint32_t)(r1 - l_first) * row_len;
+        const uint32_t b0 = l_span * row_len + (uint32_t)((r0 >> 1) - c_first) * row_len;
+        const uint32_t b1 = l_span * row_len + (uint32_t)((r1 >> 1) - c_first) * row_len;
+        row_tab[2 * tid] = make_float4(__uint_as_float(stage_addr + a0), __uint_as_float(stage_addr + a1),
+                                       __uint_as_float(stage_addr + b0), __uint_as_float(stage_addr + b1));
+        row_tab[2 * tid + 1] = make_float4(ay.w0, ay.w0, ay.w1, ay.w1);
+    }
+    __syncthreads();
+    {
+        const uint8_t* luma = P.src + (size_t)l_first * P.src_pitch + byte0;
+        const uint8_t* chroma = P.src + (size_t)P.src_pitch * P.src_height + (size_t)c_first * P.src_pitch + byte0;
+        for (uint32_t r = tid; r < l_span; r += nthreads) {
+            if (need_l[r]) {
+                mbar_expect_tx_only(mbar, row_len);
+                bulk_copy_g2s(stage_addr + r * row_len, luma + (size_t)r * P.src_pitch, row_len, mbar);
+            }
+        }
+        for (uint32_t r = tid; r < c_span; r += nthreads) {
+            if (need_c[r]) {
+                mbar_expect_tx_only(mbar, row_len);
+                bulk_copy_g2s(chroma_addr + r * row_len, chroma + (size_t)r * P.src_pitch, row_len, mbar);
+            }
+        }
+    }
+    __syncthreads(); /* every copy's bytes are expected before the one arrival */
+    if (tid == 0) mbar_arrive(mbar);
+
+    /* the thread's two columns */
+    const uint32_t slot = tid / gw, gi = tid - slot * gw;
+    const int xa = c_base + (int)gi, xb = xa + (int)gw;
+    const bool in_a = xa >= x1 && xa <= x2, in_b = xb >= x1 && xb <= x2;
+    const bool valid_a = xa < x_end, valid_b = xb < x_end;
+    const Axis axa = make_axis(in_a ? xa - x1 : rc0 - x1, fx, crop_w);
+    const Axis axb = make_axis(in_b ? xb - x1 : rc0 - x1, fx, crop_w);
+    /* byte offsets of the taps in a staged luma row, and of their U,V pairs in a staged chroma row */
+    const uint32_t la0 = (uint32_t)(crop_x + axa.i0) - byte0, la1 = (uint32_t)(crop_x + axa.i1) - byte0;
+    const uint32_t lb0 = (uint32_t)(crop_x + axb.i0) - byte0, lb1 = (uint32_t)(crop_x + axb.i1) - byte0;
+    const uint32_t ca0 = (((uint32_t)(crop_x + axa.i0) >> 1) << 1) - byte0, ca1 = (((uint32_t)(crop_x + axa.i1) >> 1) << 1) - byte0;
+    const uint32_t cb0 = (((uint32_t)(crop_x + axb.i0) >> 1) << 1) - byte0, cb1 = (((uint32_t)(crop_x + axb.i1) >> 1) << 1) - byte0;
+    const bool col1_a = axa.w1 != 0.0f, col1_b = axb.w1 != 0.0f;
+    const bool yuv = S.pre_kind == PRE_YUV_BT709;
+
+    if (!mbar_wait_bounded(mbar, 0)) {
+        atomicExch(status, STATUS_STAGED_WAIT_TIMEOUT);
+        (void)mbar_wait_bounded(mbar, 0);
+        return;
+    }
+
+    /* one tap: Y, U, V as floats, converted when the chain says so */
+    auto tap = [&](uint32_t l_addr, uint32_t c_addr, float (&t)[3]) {
+        const uint32_t uv = lds_u16(c_addr);
+        t[0] = byte_to_float(lds_u8(l_addr));
+        t[1] = byte_to_float(uv);
+        t[2] = byte_to_float(uv >> 8);
+        if (yuv) yuv_to_rgb_bt709_full(t[0], t[1], t[2]);
+    };
+    /* interpolated value of one column in the row described by rows / wy */
+    auto column = [&](const float4& rows, const float4& wy, uint32_t l0, uint32_t l1, uint32_t c0, uint32_t c1, float w0x,
+                      float w1x, bool col1, float (&acc)[3]) {
+        const uint32_t lr0 = __float_as_uint(rows.x), lr1 = __float_as_uint(rows.y);
+        const uint32_t cr0 = __float_as_uint(rows.z), cr1 = __float_as_uint(rows.w);
+        float t[3];
+        tap(lr0 + l0, cr0 + c0, t);
+        const float w00 = __fmul_rn(w0x, wy.x);
+#pragma unroll
+        for (int c = 0; c < 3; ++c) acc[c] = __fmul_rn(t[c], w00);
+        if (col1) {
+            tap(lr0 + l1, cr0 + c1, t);
+            const float w10 = __fmul_rn(w1x, wy.x);
+#pragma unroll
+            for (int c = 0; c < 3; ++c) acc[c] = __fadd_rn(acc[c], __fmul_rn(t[c], w10));
+        }
+        if (wy.z != 0.0f) {
+            tap(lr1 + l0, cr1 + c0, t);
+            const float w01 = __fmul_rn(w0x, wy.z);
+#pragma unroll
+            for (int c = 0; c < 3; ++c) acc[c] = __fadd_rn(acc[c], __fmul_rn(t[c], w01));
+            if (col1) {
+                tap(lr1 + l1, cr1 + c1, t);
+                const float w11 = __fmul_rn(w1x, wy.z);
+#pragma unroll
+                for (int c = 0; c < 3; ++c) acc[c] = __fadd_rn(acc[c], __fmul_rn(t[c], w11));
+            }
+        }
+    };
+
+    if (slot < rs && valid_a) {
+        uint8_t* out_a = dst + (size_t)(ya + (int)slot) * dst_pitch + (size_t)xa * 12;
+        const size_t b_off = (size_t)gw * 12, row_step = (size_t)rs * dst_pitch;
+        const float4* rt = row_tab + 2 * slot;
+#pragma unroll 1
+        for (int y = ya + (int)slot; y <= yb; y += (int)rs, rt += 2 * rs, out_a += row_step) {
+            const float4 rows = rt[0], wy = rt[1];
+            float va[3], vb[3] = {0.0f, 0.0f, 0.0f};
+            column(rows, wy, la0, la1, ca0, ca1, axa.w0, axa.w1, col1_a, va);
+            if (valid_b) column(rows, wy, lb0, lb1, cb0, cb1, axb.w0, axb.w1, col1_b, vb);
+            float2 v[3] = {make_float2(va[0], vb[0]), make_float2(va[1], vb[1]), make_float2(va[2], vb[2])};
+            run_ops<CHAIN, 1>(v, sops, S.n_pre, S.n_ops, one);
+            store_pixel_at<PLANAR>(out_a, dst_cstride, in_a ? v[0].x : bgv[0], in_a ? v[1].x : bgv[1], in_a ? v[2].x : bgv[2]);
+            if (valid_b)
+                store_pixel_at<PLANAR>(out_a + b_off, dst_cstride, in_b ? v[0].y : bgv[0], in_b ? v[1].y : bgv[1], in_b ? v[2].y : bgv[2]);
+        }
+    }
+
+    /* background to the left and right of this band's rows (first column tile only) */
+    const uint32_t n_side = groups_per_row - n_groups;
+    if (tile_x == 0 && n_side != 0) {
+        const uint32_t total = (uint32_t)(yb - ya + 1) * n_side;
+        CellWalk w(tid, nthreads, n_side);
+#pragma unroll 1
+        for (uint32_t idx = tid; idx < total; idx += nthreads, w.advance()) {
+            const uint32_t g = w.c < g_lo ? w.c : w.c + n_groups;
+            store_group<PLANAR>(dst, dst_pitch, dst_cstride, (int)(g * PX_PER_THREAD), ya + (int)w.r, bg4);
+        }
+    }
+}
+
+/* ------------------------------------------------------------------------------------ */
 /* the kernel                                                                           */
 /* ------------------------------------------------------------------------------------ */
 /* Chains compiled into the kernels (codes of the operations after the geometry stage, in
@@ -886,6 +1109,9 @@ __device__ __forceinline__ void run_class(uint32_t cls, const DevPlane& P, const
         case CLASS_RESIZE_U8_PACKED_STAGED:
             if constexpr (CLASS != CLASS_MIXED) body_resize_staged<CHAIN, false>(P, S, sops, local, staged_mem, status);
             break;
+        case CLASS_RESIZE_NV12_PACKED_STAGED:
+            if constexpr (CLASS != CLASS_MIXED) body_nv12_staged<CHAIN>(P, S, sops, local, staged_mem, status);
+            break;
         default: body_generic(P, S, sops, local); break;
     }
 }
@@ -914,11 +1140,15 @@ __device__ __forceinline__ void run_body(uint32_t cls, const DevPlane& P, const 
 #ifndef FKB_MIXED_MIN_BLOCKS
 #define FKB_MIXED_MIN_BLOCKS 6
 #endif
+#ifndef FKB_NV12_MIN_BLOCKS
+#define FKB_NV12_MIN_BLOCKS 3
+#endif
 #ifndef FKB_DIRECT_MIN_BLOCKS
 #define FKB_DIRECT_MIN_BLOCKS 1
 #endif
 constexpr int min_blocks_of(uint32_t cls) {
     return (cls == CLASS_RESIZE_U8_PLANAR_STAGED || cls == CLASS_RESIZE_U8_PACKED_STAGED) ? FKB_STAGED_MIN_BLOCKS
+           : cls == CLASS_RESIZE_NV12_PACKED_STAGED ? FKB_NV12_MIN_BLOCKS
            : cls == CLASS_MIXED ? FKB_MIXED_MIN_BLOCKS
            : (cls == CLASS_RESIZE_NV12_PACKED || cls == CLASS_RESIZE_U8_PLANAR || cls == CLASS_RESIZE_U8_PACKED) ? FKB_DIRECT_MIN_BLOCKS : 1;
 }
@@ -1000,6 +1230,7 @@ cudaError_t launch_plan_kernel(uint32_t launch_cls, uint32_t chain, const Launch
         case CLASS_RESIZE_NV12_PACKED: return launch_class<CLASS_RESIZE_NV12_PACKED>(chain, a, smem, stream);
         case CLASS_RESIZE_U8_PLANAR_STAGED: return launch_class<CLASS_RESIZE_U8_PLANAR_STAGED>(chain, a, smem, stream);
         case CLASS_RESIZE_U8_PACKED_STAGED: return launch_class<CLASS_RESIZE_U8_PACKED_STAGED>(chain, a, smem, stream);
+        case CLASS_RESIZE_NV12_PACKED_STAGED: return launch_class<CLASS_RESIZE_NV12_PACKED_STAGED>(chain, a, smem, stream);
         case CLASS_GENERIC: return launch_one<CLASS_GENERIC, CHAIN_INTERPRET>(a, smem, stream);
         default: return launch_one<CLASS_MIXED, CHAIN_INTERPRET>(a, smem, stream);
     }
