@@ -111,14 +111,8 @@ constexpr int32_t DEV_OP_DIV_BY_CONSTANT = 16;
  * RESIZE_ROWS_PER_THREAD) rows and also fills the background to the left and right of its
  * rows; rows above and below the region are filled by separate, store-only work items of
  * BG_GROUPS_PER_ITEM column groups each. */
-#ifndef FKB_ROWS
-#define FKB_ROWS 8
-#endif
-constexpr int RESIZE_ROWS_PER_THREAD = FKB_ROWS;
-#ifndef FKB_RPX
-#define FKB_RPX 4
-#endif
-constexpr int RESIZE_PX = FKB_RPX; /* output columns per thread in the interpolating items */
+constexpr int RESIZE_ROWS_PER_THREAD = 8;
+constexpr int RESIZE_PX = 4; /* output columns per thread in the interpolating items */
 constexpr int BG_GROUPS_PER_THREAD = 8;
 
 struct ResizeTiling {
@@ -156,15 +150,9 @@ inline ResizeTiling resize_tiling(uint32_t dst_w, uint32_t dst_h, int x1, int y1
  * all columns; its source footprint (whole crop rows, widened to 16-byte boundaries) sits in
  * shared memory behind a 16-byte mbarrier slot and a table of per-row vertical taps. */
 constexpr uint32_t STAGED_MAX_ROWS = 64;          /* output rows per band                        */
-#ifndef FKB_STAGE_KB
-#define FKB_STAGE_KB 40
-#endif
-constexpr uint32_t STAGED_MAX_STAGE_BYTES = FKB_STAGE_KB * 1024u;
+constexpr uint32_t STAGED_MAX_STAGE_BYTES = 40 * 1024u; /* four blocks of it fit one SM */
 constexpr uint32_t STAGED_HEADER_BYTES = 16 + STAGED_MAX_ROWS * 32;
-#ifndef FKB_NV12_STAGE_KB
-#define FKB_NV12_STAGE_KB 64
-#endif
-constexpr uint32_t NV12_MAX_STAGE_BYTES = FKB_NV12_STAGE_KB * 1024u; /* luma and chroma rows of a band tile */
+constexpr uint32_t NV12_MAX_STAGE_BYTES = 40 * 1024u; /* luma and chroma rows of a band tile; five blocks per SM */
 constexpr uint32_t NV12_MAX_SPAN = 256;           /* source rows between a band's first and last tap */
 constexpr uint32_t STAGED_WAIT_LIMIT = 1u << 22;  /* try_wait rounds before a block gives up     */
 constexpr uint32_t STATUS_STAGED_WAIT_TIMEOUT = 1; /* a bulk copy did not complete in time        */

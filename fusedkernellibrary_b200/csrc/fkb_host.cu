@@ -74,7 +74,6 @@ struct HostImage {
     uint32_t launch_class = CLASS_GENERIC;
     uint32_t chain = CHAIN_INTERPRET;   /* compiled chain shared by every sequence, or CHAIN_INTERPRET */
     uint32_t block_threads = BLOCK_THREADS;
-    uint32_t uniform_items = 0;
     uint32_t total_items = 0;
     uint32_t max_seq_ops = 0;
     uint32_t staged_bytes = 0;          /* > 0: a STAGED class, this much shared memory per block */
@@ -607,8 +606,8 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
     img.resize.assign(d->n_planes, fkb_resize_params{});
     img.item_start.assign((size_t)d->n_planes + 1, 0);
     uint64_t total = 0;
-    bool uniform = true, same_groups = false;
-    uint32_t first_items = 0, first_groups = 0;
+    bool same_groups = false;
+    uint32_t first_groups = 0;
     uint32_t common_class = CLASS_MIXED;
     for (int i = 0; i < d->n_planes; ++i) {
         const fkb_plane& p = d->planes[i];
@@ -692,10 +691,9 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
         }
         if (cls == CLASS_GENERIC) items = (out_px + ITEM_PIXELS_GENERIC - 1) / ITEM_PIXELS_GENERIC;
         dp.plane_class = cls;
-        if (i == 0) { common_class = cls; first_items = (uint32_t)items; }
+        if (i == 0) common_class = cls;
         else {
             if (cls != common_class) common_class = CLASS_MIXED;
-            if (items != first_items) uniform = false;
         }
         img.item_start[i] = (uint32_t)total;
         total += items;
@@ -725,11 +723,9 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
     }
     img.item_start[d->n_planes] = (uint32_t)total;
     img.total_items = (uint32_t)total;
-    img.uniform_items = uniform ? first_items : 0;
     img.launch_class = common_class;
     img.chain = (common_class != CLASS_MIXED && common_class != CLASS_GENERIC && chain_is_compiled(common_chain))
                     ? common_chain : CHAIN_INTERPRET;
-#ifndef FKB_DISABLE_STAGED
     /* uchar3 resize plans whose every plane can stage its bands' source rows in shared memory */
     if (common_class == CLASS_RESIZE_U8_PLANAR || common_class == CLASS_RESIZE_U8_PACKED) {
         std::vector<StagedTiling> st(img.planes.size());
@@ -743,7 +739,6 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
         if (all) {
             const uint32_t cls = common_class == CLASS_RESIZE_U8_PLANAR ? CLASS_RESIZE_U8_PLANAR_STAGED : CLASS_RESIZE_U8_PACKED_STAGED;
             uint64_t t2 = 0;
-            uniform = true;
             for (size_t i = 0; i < img.planes.size(); ++i) {
                 DevPlane& dp = img.planes[i];
                 const ResizeTiling rt = resize_tiling(dp.dst_w, dp.dst_h, dp.x1, dp.y1, dp.x2, dp.y2, BLOCK_THREADS);
@@ -752,13 +747,10 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
                 dp.roi_items = st[i].n_bands; dp.tiles_x = st[i].band_rows; dp.gw = st[i].gw; dp.rs = st[i].rs;
                 img.item_start[i] = (uint32_t)t2;
                 t2 += items;
-                if (i == 0) first_items = items;
-                else if (items != first_items) uniform = false;
             }
             if (t2 > 0x7FFFFFFFull) return fail(FKB_ERR_INVALID_ARGUMENT, "plan needs more than 2^31 thread blocks");
             img.item_start[img.planes.size()] = (uint32_t)t2;
             img.total_items = (uint32_t)t2;
-            img.uniform_items = uniform ? first_items : 0;
             img.block_threads = BLOCK_THREADS;
             img.staged_bytes = STAGED_HEADER_BYTES + stage;
             img.launch_class = common_class = cls;
@@ -776,7 +768,6 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
         }
         if (all) {
             uint64_t t2 = 0;
-            uniform = true;
             for (size_t i = 0; i < img.planes.size(); ++i) {
                 DevPlane& dp = img.planes[i];
                 const ResizeTiling rt = resize_tiling(dp.dst_w, dp.dst_h, dp.x1, dp.y1, dp.x2, dp.y2, BLOCK_THREADS);
@@ -790,13 +781,11 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
             if (t2 > 0x7FFFFFFFull) return fail(FKB_ERR_INVALID_ARGUMENT, "plan needs more than 2^31 thread blocks");
             img.item_start[img.planes.size()] = (uint32_t)t2;
             img.total_items = (uint32_t)t2;
-            img.uniform_items = 0;
             img.block_threads = BLOCK_THREADS;
             img.staged_bytes = STAGED_HEADER_BYTES + 2 * NV12_MAX_SPAN + stage;
             img.launch_class = common_class = CLASS_RESIZE_NV12_PACKED_STAGED;
         }
     }
-#endif
     /* A plan whose planes all have the same region width can run with exactly as many threads per
        block as its tiling keeps busy. */
     const bool resize_class = common_class == CLASS_RESIZE_U8_PLANAR || common_class == CLASS_RESIZE_U8_PACKED ||
@@ -813,12 +802,9 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
                 dp.roi_items = t.roi_items; dp.tiles_x = t.tiles_x; dp.gw = t.gw; dp.rs = t.rs;
                 img.item_start[i] = (uint32_t)t2;
                 t2 += (uint64_t)t.roi_items + t.bg_items;
-                if (i == 0) first_items = t.roi_items + t.bg_items;
-                else if (t.roi_items + t.bg_items != first_items) uniform = false;
             }
             img.item_start[img.planes.size()] = (uint32_t)t2;
             img.total_items = (uint32_t)t2;
-            img.uniform_items = uniform ? first_items : 0;
             img.block_threads = threads;
         }
     }
