@@ -65,6 +65,8 @@ class Workload:
         return None
 
     out_pixels = 0
+    algorithmic_bytes = None   # None: what fkb_plan_get_info reports (source bytes inside the crops + output bytes)
+    algorithmic_note = "source bytes inside the crop rects + output bytes"
 
 
 def _u8(rng, *shape):
@@ -241,6 +243,10 @@ class Nv12Resize(Workload):
         self.sources = [{f"frame{i}": _u8(rng, h + h // 2, w) for i in range(n)}]
         self.outputs = [{"out": ((n, dh, dw, 3), np.float32)}]
         self.out_pixels = n * dw * dh
+        # tap samples + output per output pixel: 4 luma bytes, 4.5 chroma bytes, 12 output bytes; the whole
+        # frames (what the plan reports) would be (w*h*1.5*n + output) = 752 MB at the full size
+        self.algorithmic_bytes = int(self.out_pixels * 20.5)
+        self.algorithmic_note = "tap samples + output: (4 Y + 4.5 UV + 12) B per output pixel"
         self.description = f"C4 NV12 BVF: {n} NV12 frames {w}x{h} -> BT.709 full RGB -> resize {dw}x{dh} -> /255 -> packed float3"
 
     def build(self, ptr, s=0):
@@ -497,7 +503,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
     if rank == 0:
         peak, peak_kind = measured_peak_gbs()
-        achieved = info.algorithmic_bytes / (kernel_ms * 1e-3) / 1e9
+        alg_bytes = wl.algorithmic_bytes or info.algorithmic_bytes
+        achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9
         line = {
             "metric": "output Mpix/s (crop-resize-norm)", "value": value, "unit": "Mpix/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": max_ms / args.steps,
@@ -507,7 +514,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                        "grid": info.grid_x, "block": info.block_x},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "traffic": TRAFFIC_BYTES_PER_LAUNCH.get(wl.name), "peak_kind": f"of {peak_kind}",
-                         "algorithmic_bytes_per_launch": info.algorithmic_bytes, "kernel_ms": kernel_ms,
+                         "algorithmic_bytes_per_launch": alg_bytes, "algorithmic_bytes_are": wl.algorithmic_note,
+                         "kernel_ms": kernel_ms,
                          "frac_of_nominal_8TBs": achieved / 8000.0},
             "cpu_baseline": cpu,
             "e2e": e2e,

@@ -77,6 +77,8 @@ enum PreKind : int32_t {
     PRE_GENERAL = 2   /* any other chain: interpreted per tap (generic class only)           */
 };
 
+constexpr int INLINE_MAX_OPS = 16;
+
 /* Kernel argument block (passed by value). */
 struct LaunchArgs {
     const DevPlane* planes;
@@ -90,8 +92,13 @@ struct LaunchArgs {
     uint32_t max_seq_ops;       /* longest sequence: sizes the shared-memory op cache         */
     uint32_t block_threads;     /* threads per block of this launch (multiple of 32, <= 256)  */
     uint32_t staged_bytes;      /* STAGED classes: shared memory behind the operation cache    */
-    uint32_t pad[2];
+    uint32_t inline_plane;      /* 1: a plan of one plane whose descriptors travel in the      */
+                                /* kernel arguments below; block b is tile b of that plane     */
+    uint32_t pad;
     uint32_t* status;           /* one word in the plan's device block: 0, or a STATUS_* code  */
+    DevPlane plane0;            /* inline_plane: the plane, its sequence and its operations    */
+    DevSeq seq0;
+    DevOp ops0[INLINE_MAX_OPS];
 };
 
 constexpr int BLOCK_THREADS = 256;

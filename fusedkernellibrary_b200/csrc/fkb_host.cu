@@ -114,6 +114,14 @@ struct HostImage {
         a.block_threads = block_threads;
         a.staged_bytes = staged_bytes;
         a.status = reinterpret_cast<uint32_t*>(const_cast<unsigned char*>(d_base) + off_status());
+        /* a single image: its descriptors ride in the kernel arguments, so that a block starts
+           without a round trip to global memory */
+        if (planes.size() == 1 && seqs.size() == 1 && ops.size() <= (size_t)INLINE_MAX_OPS && staged_bytes == 0) {
+            a.inline_plane = 1;
+            a.plane0 = planes[0];
+            a.seq0 = seqs[0];
+            for (size_t k = 0; k < ops.size(); ++k) a.ops0[k] = ops[k];
+        }
         return a;
     }
 };

@@ -1150,6 +1150,14 @@ __global__ void __launch_bounds__(BLOCK_THREADS, min_blocks_of(CLASS)) fused_pla
     __shared__ DevPlane s_plane;
     __shared__ DevSeq s_seq;
 
+    if (a.inline_plane) {
+        /* one plane: everything is in the kernel arguments; only the operation table is expanded */
+        const uint32_t n_ops = (uint32_t)a.seq0.n_ops;
+        if (threadIdx.x < n_ops) expand_op(*reinterpret_cast<const uint4*>(&a.ops0[threadIdx.x]), sops + threadIdx.x);
+        __syncthreads();
+        run_body<CLASS, CHAIN>(a.plane0.plane_class, a.plane0, a.seq0, sops, blockIdx.x, nullptr, a.status);
+        return;
+    }
     /* One 16-byte table entry tells the block its plane, its tile within the plane and where the
        plane's sequence and operations are, so that the three descriptors arrive in one round trip. */
     const uint4 entry = __ldg(a.items + blockIdx.x);
