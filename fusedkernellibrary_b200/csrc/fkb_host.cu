@@ -1110,23 +1110,34 @@ extern "C" FKB_API int fkb_host_session_create(const fkb_plan_desc* desc, fkb_ho
             }
             s->d2h_bytes += out_payload[i];
         }
-        /* dense planes of equal size at a constant distance (a batch dealt round-robin over the
-           images) come back as one strided copy; neighbours as one plain copy */
+        /* Outputs of one dense tensor: neighbouring planes merge into runs, and runs of equal size
+           at a constant distance (a batch dealt round-robin over the images) come back as one
+           strided copy. */
         if (one_block && grp.downloads.size() == members[g].size() && grp.downloads.size() > 1) {
-            const auto& d0 = grp.downloads[0];
-            const ptrdiff_t step = static_cast<const unsigned char*>(grp.downloads[1].host) - static_cast<const unsigned char*>(d0.host);
-            bool regular = step >= (ptrdiff_t)d0.row_bytes;
-            for (size_t k = 1; k < grp.downloads.size() && regular; ++k) {
-                const auto& d = grp.downloads[k];
-                regular = d.rows == 1 && d.row_bytes == d0.row_bytes &&
-                          static_cast<const unsigned char*>(d.host) - static_cast<const unsigned char*>(d0.host) == step * (ptrdiff_t)k;
+            auto& dl = grp.downloads;
+            std::sort(dl.begin(), dl.end(), [](const fkb_host_session::Copy& x, const fkb_host_session::Copy& y) { return x.host < y.host; });
+            std::vector<fkb_host_session::Copy> runs;
+            for (const auto& d : dl) {
+                if (!runs.empty() && d.rows == 1 && runs.back().rows == 1 &&
+                    static_cast<unsigned char*>(runs.back().host) + runs.back().row_bytes == d.host) {
+                    runs.back().row_bytes += d.row_bytes;
+                    runs.back().pitch = runs.back().row_bytes;
+                } else {
+                    runs.push_back(d);
+                }
             }
-            if (regular && d0.rows == 1) {
-                fkb_host_session::Copy c = d0;
-                if ((size_t)step == d0.row_bytes) { c.row_bytes = c.pitch = d0.row_bytes * grp.downloads.size(); c.rows = 1; }
-                else { c.pitch = (size_t)step; c.rows = grp.downloads.size(); }
-                grp.downloads.assign(1, c);
+            bool regular = runs.size() > 1 && runs[0].rows == 1;
+            const ptrdiff_t step = regular ? static_cast<unsigned char*>(runs[1].host) - static_cast<unsigned char*>(runs[0].host) : 0;
+            for (size_t k = 1; k < runs.size() && regular; ++k)
+                regular = runs[k].rows == 1 && runs[k].row_bytes == runs[0].row_bytes &&
+                          static_cast<unsigned char*>(runs[k].host) - static_cast<unsigned char*>(runs[0].host) == step * (ptrdiff_t)k;
+            if (regular) {
+                fkb_host_session::Copy c = runs[0];
+                c.pitch = (size_t)step;
+                c.rows = runs.size();
+                runs.assign(1, c);
             }
+            dl.swap(runs);
         }
         fkb_plan_desc dd = *desc;
         dd.planes = sub.data();

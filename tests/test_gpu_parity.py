@@ -97,3 +97,36 @@ def test_execute_one_shot_and_host_session(fkb_lib, oracle_port):
     sess.run()
     assert np.array_equal(tc.bits(case.outputs["out"]), tc.bits(expected["out"]))
     sess.destroy()
+
+
+def test_host_session_groups_and_copy_patterns(fkb_lib, oracle_port):
+    """Planes dealt to three source images in runs of uneven length, and outputs with padded rows:
+    the session's per-image groups must bring every byte back (runs, strided and row-exact copies)."""
+    rng = np.random.default_rng(79)
+    fw, fh, n, dw, dh = 160, 96, 23, 32, 24
+    frames = [rng.integers(0, 256, (fh, fw * 3), dtype=np.uint8) for _ in range(3)]
+    rects = tc.chains.random_rects(rng, n, fw, fh, lo=4, hi=90)
+    fi = [(i // 4) % 3 if i < 20 else 2 - (i % 3) for i in range(n)]
+    for planar, pad in ((True, 0), (False, 0), (False, 16)):
+        pitch = dw * (4 if planar else 12) + pad
+        out = np.zeros((n, 3 * dh, pitch) if planar else (n, dh, pitch), np.uint8)
+        want = np.zeros_like(out)
+
+        def plan_for(ptrs, dst):
+            plan = abi.HostPlan()
+            seq = plan.add_sequence(abi.SRC_U8X3, abi.DST_F32_PLANAR3 if planar else abi.DST_F32X3_PACKED, abi.RESIZE_PRESERVE_AR,
+                                    tc.chains.normalize_ops())
+            for i in range(n):
+                plan.add_plane(src=ptrs[fi[i]], src_width=fw, src_height=fh, src_pitch=fw * 3, crop=tuple(int(v) for v in rects[i]),
+                               dst=dst + i * out[0].nbytes, dst_width=dw, dst_height=dh, dst_pitch=pitch,
+                               dst_channel_stride=dh * pitch if planar else 0, sequence=seq)
+            return plan
+
+        oracle_port.run(plan_for([f.ctypes.data for f in frames], want.ctypes.data))
+        sess = abi.HostSession(plan_for([f.ctypes.data for f in frames], out.ctypes.data))
+        sess.run()
+        h2d, d2h = sess.traffic()
+        assert h2d == sum(f.nbytes for f in frames)
+        assert d2h == n * 3 * dh * dw * 4
+        sess.destroy()
+        assert np.array_equal(out, want), f"planar={planar} pad={pad}"
