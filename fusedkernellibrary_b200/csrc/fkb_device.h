@@ -44,7 +44,9 @@ struct alignas(16) DevPlane {
     uint32_t plane_class;
     uint32_t seg_pixels;     /* FLAT classes: pixels per contiguous segment; staged NV12:     */
                              /* output rows per work item (band)                              */
-    uint32_t n_segs;         /* FLAT classes: 1 (dense plane) or dst_h (one segment per row)  */
+    uint32_t n_segs;         /* FLAT classes: 1 (dense plane) or dst_h (one segment per row); */
+                             /* staged uchar3 resize: 1 when the last band also fills the     */
+                             /* rows outside the region (no store-only items)                 */
     /* RESIZE classes: tiling of the region of interest (see ResizeTiling) */
     uint32_t roi_items;      /* work items that interpolate; the rest fill background rows    */
     uint32_t tiles_x;        /* STAGED classes: output rows per work item (band)               */
@@ -109,6 +111,9 @@ constexpr int ITEM_PIXELS_GENERIC = BLOCK_THREADS;
 /* Device-only opcode: division by a plan-time constant, lowered from FKB_OP_DIV when the host
  * has proven the three-instruction form exact.  Takes two op slots: {-p}, then {1/p}. */
 constexpr int32_t DEV_OP_DIV_BY_CONSTANT = 16;
+/* Device-only opcode: the next p[1] slots (1 or 2 of Mul, Sub, Add) run p[0] times; both counts are
+ * stored as integer bit patterns. */
+constexpr int32_t DEV_OP_REPEAT = 17;
 
 /* RESIZE classes.  Only the region of interest [x1,x2] x [y1,y2] of a plane is interpolated;
  * everything else receives one constant (the default value after the continuation).  Threads
@@ -161,6 +166,7 @@ constexpr uint32_t STAGED_MAX_STAGE_BYTES = 40 * 1024u; /* four blocks of it fit
 constexpr uint32_t STAGED_HEADER_BYTES = 16 + STAGED_MAX_ROWS * 32;
 constexpr uint32_t NV12_MAX_STAGE_BYTES = 40 * 1024u; /* luma and chroma rows of a band tile; five blocks per SM */
 constexpr uint32_t NV12_MAX_SPAN = 256;           /* source rows between a band's first and last tap */
+constexpr uint32_t STAGED_FOLD_BG_GROUPS = 1024;  /* at most this many outside groups: no store-only items */
 constexpr uint32_t STAGED_WAIT_LIMIT = 1u << 22;  /* try_wait rounds before a block gives up     */
 constexpr uint32_t STATUS_STAGED_WAIT_TIMEOUT = 1; /* a bulk copy did not complete in time        */
 

@@ -421,6 +421,48 @@ static uint32_t lower_ops(const fkb_sequence& s, int n_pre, int step_exp_x, int 
             out.push_back(o);
         }
     }
+    /* A long continuation that repeats one operation or a pair of them (the reference spells this
+       StaticLoop, basic_ops/static_loop.h:22-44) runs as a counted loop on the device: the
+       repeated part is stored once behind a header slot. */
+    if (chain == CHAIN_INTERPRET) {
+        const size_t begin = (size_t)dev_n_pre;
+        std::vector<DevOp> packed(out.begin() + begin, out.end());
+        std::vector<DevOp> res;
+        auto simple = [](const DevOp& o) { return o.opcode == FKB_OP_MUL || o.opcode == FKB_OP_SUB || o.opcode == FKB_OP_ADD; };
+        auto same = [](const DevOp& x, const DevOp& y) { return std::memcmp(&x, &y, sizeof(DevOp)) == 0; };
+        size_t i = 0;
+        while (i < packed.size()) {
+            size_t best_period = 0, best_count = 0;
+            for (size_t period = 1; period <= 2; ++period) {
+                if (i + period > packed.size()) break;
+                bool ok = true;
+                for (size_t q = 0; q < period; ++q) ok = ok && simple(packed[i + q]);
+                if (!ok) continue;
+                size_t count = 1;
+                while (i + (count + 1) * period <= packed.size()) {
+                    bool eq = true;
+                    for (size_t q = 0; q < period; ++q) eq = eq && same(packed[i + q], packed[i + count * period + q]);
+                    if (!eq) break;
+                    ++count;
+                }
+                if (count * period >= 6 && count * period > best_count * best_period) { best_period = period; best_count = count; }
+            }
+            if (best_period) {
+                DevOp head;
+                head.opcode = DEV_OP_REPEAT;
+                head.p[0] = bits_float((uint32_t)best_count); head.p[1] = bits_float((uint32_t)best_period); head.p[2] = 0.0f;
+                res.push_back(head);
+                for (size_t q = 0; q < best_period; ++q) res.push_back(packed[i + q]);
+                i += best_count * best_period;
+            } else {
+                res.push_back(packed[i++]);
+            }
+        }
+        if (res.size() < packed.size()) {
+            out.resize(begin);
+            out.insert(out.end(), res.begin(), res.end());
+        }
+    }
     return chain;
 }
 
@@ -750,7 +792,10 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
             for (size_t i = 0; i < img.planes.size(); ++i) {
                 DevPlane& dp = img.planes[i];
                 const ResizeTiling rt = resize_tiling(dp.dst_w, dp.dst_h, dp.x1, dp.y1, dp.x2, dp.y2, BLOCK_THREADS);
-                const uint32_t items = st[i].n_bands + rt.bg_items;
+                const uint64_t outside_groups = (uint64_t)(dp.dst_h - (uint32_t)(dp.y2 - dp.y1 + 1)) * (dp.dst_w / PX_PER_THREAD);
+                const bool fold = outside_groups <= STAGED_FOLD_BG_GROUPS;
+                dp.n_segs = fold ? 1u : 0u;
+                const uint32_t items = st[i].n_bands + (fold ? 0u : rt.bg_items);
                 dp.plane_class = cls;
                 dp.roi_items = st[i].n_bands; dp.tiles_x = st[i].band_rows; dp.gw = st[i].gw; dp.rs = st[i].rs;
                 img.item_start[i] = (uint32_t)t2;

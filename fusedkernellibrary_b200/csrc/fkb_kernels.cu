@@ -64,12 +64,17 @@ __device__ __forceinline__ float div_by_constant(float x, float np, float r) {
 }
 
 /* ConvertYUVToRGB<NV12, Full, bt709, false, float3> (color_conversion.h:265-308; matrix
- * :143-146; row reduction left to right, basic_ops/algebraic.h:58-64). */
+ * :143-146; row reduction left to right, basic_ops/algebraic.h:58-64).  The reference computes
+ *     R = ((y*1 + u*0) + v*1.5748) * 1,  G = ((y*1 + u*-0.1873) + v*-0.4681) * 1,  B = ((y*1 + u*1.8556) + v*0) * 1
+ * with u, v already reduced by 128.  The operations dropped below cannot change a bit: x*1 is x;
+ * y is a converted byte, so it is +0 or positive and y + (+-0) is y; and y + u*1.8556 is never -0
+ * (a sum of a non-negative and a product rounds to +0 when it cancels), so adding v*0 = +-0 leaves
+ * it as it is. */
 __device__ __forceinline__ void yuv_to_rgb_bt709_full(float& a, float& b, float& c) {
     const float y = a, u = __fsub_rn(b, 128.0f), v = __fsub_rn(c, 128.0f);
-    a = __fmul_rn(__fadd_rn(__fadd_rn(__fmul_rn(y, 1.0f), __fmul_rn(u, 0.0f)), __fmul_rn(v, 1.5748f)), 1.0f);
-    b = __fmul_rn(__fadd_rn(__fadd_rn(__fmul_rn(y, 1.0f), __fmul_rn(u, -0.1873f)), __fmul_rn(v, -0.4681f)), 1.0f);
-    c = __fmul_rn(__fadd_rn(__fadd_rn(__fmul_rn(y, 1.0f), __fmul_rn(u, 1.8556f)), __fmul_rn(v, 0.0f)), 1.0f);
+    a = __fadd_rn(y, __fmul_rn(v, 1.5748f));
+    b = __fadd_rn(__fadd_rn(y, __fmul_rn(u, -0.1873f)), __fmul_rn(v, -0.4681f));
+    c = __fadd_rn(y, __fmul_rn(u, 1.8556f));
 }
 
 /* Packed binary32 arithmetic (sm_100): one instruction rounds two independent products, sums
@@ -147,6 +152,45 @@ __device__ __forceinline__ void apply_one(float2 (&v)[NPAIR * 3], const OpSlot* 
     }
 }
 
+/* `count` rounds of one or two operations out of Mul and Add (Sub is stored as an addition of the
+ * negated parameter), with the parameters held in registers across the loop. */
+template <int NPAIR>
+__device__ __forceinline__ void repeat_ops(float2 (&v)[NPAIR * 3], const OpSlot* __restrict__ body, int count, int period,
+                                           const float2 one) {
+    const bool mul0 = body[0].opcode == FKB_OP_MUL;
+    const float2 a0 = body[0].p[0], a1 = body[0].p[1], a2 = body[0].p[2];
+    if (period == 1) {
+        if (mul0) {
+#pragma unroll 1
+            for (int r = 0; r < count; ++r)
+#pragma unroll
+                for (int j = 0; j < NPAIR; ++j) { v[3 * j] = mul2(v[3 * j], a0); v[3 * j + 1] = mul2(v[3 * j + 1], a1); v[3 * j + 2] = mul2(v[3 * j + 2], a2); }
+        } else {
+#pragma unroll 1
+            for (int r = 0; r < count; ++r)
+#pragma unroll
+                for (int j = 0; j < NPAIR; ++j) { v[3 * j] = add2(v[3 * j], a0, one); v[3 * j + 1] = add2(v[3 * j + 1], a1, one); v[3 * j + 2] = add2(v[3 * j + 2], a2, one); }
+        }
+        return;
+    }
+    const bool mul1 = body[1].opcode == FKB_OP_MUL;
+    const float2 b0 = body[1].p[0], b1 = body[1].p[1], b2 = body[1].p[2];
+#define FKB_REPEAT_PAIR(OP0, OP1)                                                                      \
+    _Pragma("unroll 1") for (int r = 0; r < count; ++r) {                                              \
+        _Pragma("unroll") for (int j = 0; j < NPAIR; ++j) {                                            \
+            v[3 * j] = OP0(v[3 * j], a0); v[3 * j + 1] = OP0(v[3 * j + 1], a1); v[3 * j + 2] = OP0(v[3 * j + 2], a2); \
+            v[3 * j] = OP1(v[3 * j], b0); v[3 * j + 1] = OP1(v[3 * j + 1], b1); v[3 * j + 2] = OP1(v[3 * j + 2], b2); \
+        }                                                                                              \
+    }
+    auto MUL = [&](float2 x, float2 p) { return mul2(x, p); };
+    auto ADD = [&](float2 x, float2 p) { return add2(x, p, one); };
+    if (mul0 && mul1) { FKB_REPEAT_PAIR(MUL, MUL) }
+    else if (mul0) { FKB_REPEAT_PAIR(MUL, ADD) }
+    else if (mul1) { FKB_REPEAT_PAIR(ADD, MUL) }
+    else { FKB_REPEAT_PAIR(ADD, ADD) }
+#undef FKB_REPEAT_PAIR
+}
+
 /* Interpreter: runs ops [begin, end) of a sequence cached in shared memory.  The opcode is
  * uniform across the block, so the switch never diverges. */
 template <int NPAIR>
@@ -162,6 +206,14 @@ __device__ __forceinline__ void interpret_ops(float2 (&v)[NPAIR * 3], const OpSl
                 apply_one<CH_DIVC, NPAIR>(v, sops + k, one);
                 ++k;
                 break;
+            case DEV_OP_REPEAT: {
+                /* header: p[0] = (count, count), p[1] = (period, period) as integer bit patterns; the
+                   body's opcodes are dispatched once, outside the counted loop */
+                const int count = __float_as_int(sops[k].p[0].x), period = __float_as_int(sops[k].p[1].x);
+                repeat_ops<NPAIR>(v, sops + k + 1, count, period, one);
+                k += period;
+                break;
+            }
             case FKB_OP_SWAP_RB: apply_one<CH_SWAP, NPAIR>(v, sops + k, one); break;
             case FKB_OP_SATURATE_CAST_U8: apply_one<CH_SAT, NPAIR>(v, sops + k, one); break;
             case FKB_OP_YUV_TO_RGB_BT709_FULL: apply_one<CH_YUV, NPAIR>(v, sops + k, one); break;
@@ -849,6 +901,16 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
         for (uint32_t idx = threadIdx.x; idx < total; idx += nthreads, w.advance()) {
             const uint32_t g = w.c < g_lo ? w.c : w.c + n_groups;
             store_group<PLANAR>(dst, dst_pitch, dst_cstride, (int)(g * PX_PER_THREAD), ya + (int)w.r, bg4);
+        }
+    }
+    /* a plane with few rows outside its region has no store-only items: its last band fills them */
+    if (P.n_segs != 0 && local == P.roi_items - 1) {
+        const uint32_t total = (P.dst_h - n_rows) * groups_per_row;
+        CellWalk w(threadIdx.x, nthreads, groups_per_row);
+#pragma unroll 1
+        for (uint32_t idx = threadIdx.x; idx < total; idx += nthreads, w.advance()) {
+            const int y = (int)w.r < y1 ? (int)w.r : (int)(w.r + n_rows);
+            store_group<PLANAR>(dst, dst_pitch, dst_cstride, (int)(w.c * PX_PER_THREAD), y, bg4);
         }
     }
 }

@@ -138,6 +138,13 @@ def small_cases():
         elementwise_case("c5a_n16", 22, 40, 30, chains.addmul_ops(16), src_fmt=abi.SRC_F32X3),
         elementwise_case("c5a_n64", 23, 40, 30, chains.addmul_ops(64), src_fmt=abi.SRC_F32X3),
         elementwise_case("c5a_n256", 24, 41, 31, chains.addmul_ops(256), src_fmt=abi.SRC_F32X3),
+        # repeated operations run as counted loops on the device (the reference's StaticLoop benchmark shape)
+        elementwise_case("repeat_mul_then_sub", 29, 40, 30,
+                         [op(abi.OP_MUL, (1.01, 0.99, 1.002))] * 21 + [op(abi.OP_SUB, (0.1, 0.2, 0.3))] * 7 +
+                         [op(abi.OP_ADD, 0.001), op(abi.OP_MUL, 1.0001)] * 5 + [op(abi.OP_DIV, 3.0), op(abi.OP_MUL, 2.0)],
+                         src_fmt=abi.SRC_F32X3),
+        elementwise_case("repeat_after_cast_u8", 30, 53, 37,
+                         [op(abi.OP_CAST_F32)] + [op(abi.OP_SUB, 1.5), op(abi.OP_ADD, 0.25)] * 9 + [op(abi.OP_MUL, 0.5)] * 6),
         elementwise_case("g3_saturate_u8", 25, 64, 32, g3, dst_fmt=abi.DST_U8X3_PACKED),
         elementwise_case("g3_saturate_u8_odd", 26, 53, 37, g3, dst_fmt=abi.DST_U8X3_PACKED),
         elementwise_case("copy_u8", 27, 300, 20, [], dst_fmt=abi.DST_U8X3_PACKED),
