@@ -954,6 +954,10 @@ extern "C" FKB_API int fkb_plan_create(const fkb_plan_desc* desc, fkb_plan** out
 
 extern "C" FKB_API int fkb_plan_launch(const fkb_plan* plan, void* stream) {
     if (!plan) return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_plan_launch: plan is NULL");
+    int device = -1;
+    FKB_CUDA(cudaGetDevice(&device));
+    if (device != plan->device)
+        return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_plan_launch: the plan lives on device %d but device %d is current", plan->device, device);
     const cudaError_t e = launch_plan_kernel(plan->launch_class, plan->chain, plan->args, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return fail_cuda(e, "kernel launch", __LINE__);
     return FKB_OK;
