@@ -297,6 +297,9 @@ __device__ __forceinline__ Axis make_axis(int r, float f, int src_extent) {
     return ax;
 }
 
+/* The first tap index alone: floor of the binary32 product (resize.h:183-194, interpolation.h:66-67). */
+__device__ __forceinline__ int axis_first(int r, float f) { return __float2int_rd(__fmul_rn((float)r, f)); }
+
 /* ((p00*w00 + p10*w10) + p01*w01) + p11*w11, products and sums rounded separately. */
 __device__ __forceinline__ float blend(float p00, float p10, float p01, float p11, float w00, float w10, float w01,
                                        float w11) {
@@ -448,9 +451,11 @@ __device__ __forceinline__ void body_flat(const DevPlane& P, const DevSeq& S, co
    with one division at the start instead of one per step. */
 struct CellWalk {
     uint32_t r, c, dr, dc, per_row;
-    __device__ __forceinline__ CellWalk(uint32_t idx, uint32_t step, uint32_t per_row_) : per_row(per_row_) {
+    /* `more`: whether any walker will advance at all (uniform); the step's division is skipped if not */
+    __device__ __forceinline__ CellWalk(uint32_t idx, uint32_t step, uint32_t per_row_, bool more = true) : per_row(per_row_) {
         r = idx / per_row; c = idx - r * per_row;
-        dr = step / per_row; dc = step - dr * per_row;
+        dr = 0; dc = 0;
+        if (more) { dr = step / per_row; dc = step - dr * per_row; }
     }
     __device__ __forceinline__ void advance() {
         r += dr; c += dc;
@@ -773,8 +778,8 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
     const uint32_t phase = (uint32_t)P.crop_x * 3u - row_first;
     const uint32_t row_len = (phase + (uint32_t)P.crop_w * 3u + 15u) & ~15u;
 
-    const int src_first = make_axis(ya - y1, fy, crop_h).i0;
-    const int src_last = make_axis(yb - y1, fy, crop_h).i1;
+    const int src_first = axis_first(ya - y1, fy);
+    const int src_last = min(axis_first(yb - y1, fy) + 1, crop_h - 1);
     const uint32_t n_src = (uint32_t)(src_last - src_first + 1);
     if (threadIdx.x == 0) {
         mbar_init(mbar, 1);
@@ -896,7 +901,7 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
     const uint32_t n_side = groups_per_row - n_groups;
     if (n_side != 0) {
         const uint32_t total = (uint32_t)(yb - ya + 1) * n_side;
-        CellWalk w(threadIdx.x, nthreads, n_side);
+        CellWalk w(threadIdx.x, nthreads, n_side, total > nthreads);
 #pragma unroll 1
         for (uint32_t idx = threadIdx.x; idx < total; idx += nthreads, w.advance()) {
             const uint32_t g = w.c < g_lo ? w.c : w.c + n_groups;
@@ -906,7 +911,7 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
     /* a plane with few rows outside its region has no store-only items: its last band fills them */
     if (P.n_segs != 0 && local == P.roi_items - 1) {
         const uint32_t total = (P.dst_h - n_rows) * groups_per_row;
-        CellWalk w(threadIdx.x, nthreads, groups_per_row);
+        CellWalk w(threadIdx.x, nthreads, groups_per_row, total > nthreads);
 #pragma unroll 1
         for (uint32_t idx = threadIdx.x; idx < total; idx += nthreads, w.advance()) {
             const int y = (int)w.r < y1 ? (int)w.r : (int)(w.r + n_rows);
@@ -1129,7 +1134,7 @@ __device__ __forceinline__ void body_nv12_staged(const DevPlane& P, const DevSeq
     const uint32_t n_side = groups_per_row - n_groups;
     if (tile_x == 0 && n_side != 0) {
         const uint32_t total = (uint32_t)(yb - ya + 1) * n_side;
-        CellWalk w(tid, nthreads, n_side);
+        CellWalk w(tid, nthreads, n_side, total > nthreads);
 #pragma unroll 1
         for (uint32_t idx = tid; idx < total; idx += nthreads, w.advance()) {
             const uint32_t g = w.c < g_lo ? w.c : w.c + n_groups;
