@@ -87,7 +87,9 @@ struct LaunchArgs {
     const DevSeq* seqs;
     const DevOp* ops;
     const uint4* items;         /* one entry per thread block: plane, tile within the plane,  */
-                                /* sequence | operations << 16, first operation                */
+                                /* sequence | operations << 16, first operation; the staged    */
+                                /* uchar3 classes have two per block, the second being the     */
+                                /* first byte to copy, rows | row bytes << 16, source pitch    */
     uint32_t n_planes;
     uint32_t reserved;
     uint32_t total_items;

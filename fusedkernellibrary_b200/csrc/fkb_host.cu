@@ -77,6 +77,7 @@ struct HostImage {
     uint32_t total_items = 0;
     uint32_t max_seq_ops = 0;
     uint32_t staged_bytes = 0;          /* > 0: a STAGED class, this much shared memory per block */
+    bool early_copies = false;          /* staged uchar3 classes: two table entries per block     */
     uint64_t output_pixels = 0;
     uint64_t algorithmic_bytes = 0;
     int n_constant_divisions = 0, n_ieee_divisions = 0;
@@ -85,7 +86,7 @@ struct HostImage {
     size_t off_seqs() const { return planes.size() * sizeof(DevPlane); }
     size_t off_ops() const { return off_seqs() + seqs.size() * sizeof(DevSeq); }
     size_t off_items() const { return off_ops() + std::max<size_t>(ops.size(), 1) * sizeof(DevOp); }
-    size_t off_status() const { return off_items() + (size_t)total_items * 16; }
+    size_t off_status() const { return off_items() + (size_t)total_items * (early_copies ? 32 : 16); }
     size_t bytes() const { return off_status() + 16; }
 
     void serialize(unsigned char* dst) const {
@@ -96,8 +97,23 @@ struct HostImage {
         uint32_t* e = reinterpret_cast<uint32_t*>(dst + off_items());
         for (size_t i = 0; i < planes.size(); ++i) {
             const DevSeq& q = seqs[planes[i].seq];
+            const DevPlane& dp = planes[i];
             for (uint32_t l = 0, n = item_start[i + 1] - item_start[i]; l < n; ++l, e += 4) {
-                e[0] = (uint32_t)i; e[1] = l; e[2] = planes[i].seq | ((uint32_t)q.n_ops << 16); e[3] = (uint32_t)q.ops_begin;
+                e[0] = (uint32_t)i; e[1] = l; e[2] = dp.seq | ((uint32_t)q.n_ops << 16); e[3] = (uint32_t)q.ops_begin;
+                if (!early_copies) continue;
+                /* second entry: what the band's bulk copies need (nothing for a store-only item) */
+                e += 4;
+                e[0] = e[1] = e[2] = e[3] = 0;
+                if (l >= dp.roi_items) continue;
+                const uint32_t n_rows = (uint32_t)(dp.y2 - dp.y1 + 1);
+                const uint32_t ra = l * dp.tiles_x, rb = std::min(ra + dp.tiles_x, n_rows) - 1;
+                const int first = (int)std::floor((float)ra * dp.fy);
+                const int last = std::min((int)std::floor((float)rb * dp.fy) + 1, dp.crop_h - 1);
+                const uint32_t row_first = ((uint32_t)dp.crop_x * 3u) & ~15u;
+                const uint32_t row_len = (((uint32_t)dp.crop_x * 3u - row_first) + (uint32_t)dp.crop_w * 3u + 15u) & ~15u;
+                const uintptr_t src = reinterpret_cast<uintptr_t>(dp.src) + (size_t)(dp.crop_y + first) * dp.src_pitch + row_first;
+                e[0] = (uint32_t)(src & 0xFFFFFFFFu); e[1] = (uint32_t)((uint64_t)src >> 32);
+                e[2] = (uint32_t)(last - first + 1) | (row_len << 16); e[3] = dp.src_pitch;
             }
         }
         std::memset(dst + off_status(), 0, 16);
@@ -806,6 +822,7 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
             img.total_items = (uint32_t)t2;
             img.block_threads = BLOCK_THREADS;
             img.staged_bytes = STAGED_HEADER_BYTES + stage;
+            img.early_copies = true;
             img.launch_class = common_class = cls;
         }
     }

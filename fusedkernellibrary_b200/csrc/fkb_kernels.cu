@@ -781,11 +781,6 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
     const int src_first = axis_first(ya - y1, fy);
     const int src_last = min(axis_first(yb - y1, fy) + 1, crop_h - 1);
     const uint32_t n_src = (uint32_t)(src_last - src_first + 1);
-    if (threadIdx.x == 0) {
-        mbar_init(mbar, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        mbar_expect_tx(mbar, n_src * row_len);
-    }
     if (threadIdx.x <= (uint32_t)(yb - ya)) {
         /* vertical taps of one row of the band: shared-memory addresses of its two source rows, and
            its two weights already duplicated into pairs */
@@ -794,12 +789,7 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
                                                __uint_as_float(stage_addr + (uint32_t)(ay.i1 - src_first) * row_len), 0.0f, 0.0f);
         row_tab[2 * threadIdx.x + 1] = make_float4(ay.w0, ay.w0, ay.w1, ay.w1);
     }
-    __syncthreads(); /* barrier initialised and armed, row table written */
-    {
-        const uint8_t* g = P.src + (size_t)(P.crop_y + src_first) * P.src_pitch + row_first;
-        for (uint32_t r = threadIdx.x; r < n_src; r += nthreads)
-            bulk_copy_g2s(smem_addr(stage + r * row_len), g + (size_t)r * P.src_pitch, row_len, mbar);
-    }
+    __syncthreads(); /* row table written (the band's copies were started when the block began) */
 
     /* The thread's two columns and their horizontal taps, while the copies are in flight.  The two
        taps of a column are six consecutive bytes of a staged row (three when the second tap is
@@ -1226,8 +1216,27 @@ __global__ void __launch_bounds__(BLOCK_THREADS, min_blocks_of(CLASS)) fused_pla
         return;
     }
     /* One 16-byte table entry tells the block its plane, its tile within the plane and where the
-       plane's sequence and operations are, so that the three descriptors arrive in one round trip. */
-    const uint4 entry = __ldg(a.items + blockIdx.x);
+       plane's sequence and operations are, so that the three descriptors arrive in one round trip.
+       The staged uchar3 classes have a second entry with the band's copy parameters: warp 0 starts
+       the bulk copies of the source rows from it at once, before the plane's descriptor is known. */
+    constexpr bool EARLY_COPIES = CLASS == CLASS_RESIZE_U8_PLANAR_STAGED || CLASS == CLASS_RESIZE_U8_PACKED_STAGED;
+    const uint4 entry = __ldg(a.items + (EARLY_COPIES ? 2u * blockIdx.x : blockIdx.x));
+    if (EARLY_COPIES && threadIdx.x < 32) {
+        const uint4 cp = __ldg(a.items + 2u * blockIdx.x + 1u); /* source pointer, rows | row bytes << 16, pitch */
+        const uint32_t n_src = cp.z & 0xFFFFu, row_len = cp.z >> 16;
+        if (n_src != 0) {
+            unsigned char* const staged = smem_raw + (((a.max_seq_ops > 0 ? a.max_seq_ops : 1u) * (uint32_t)sizeof(OpSlot) + 127u) & ~127u);
+            const uint32_t mbar = smem_addr(staged), stage_addr = smem_addr(staged + STAGED_HEADER_BYTES);
+            if (threadIdx.x == 0) {
+                mbar_init(mbar, 1);
+                asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+                mbar_expect_tx(mbar, n_src * row_len);
+            }
+            __syncwarp();
+            const uint8_t* g = reinterpret_cast<const uint8_t*>((size_t)cp.x | ((size_t)cp.y << 32));
+            for (uint32_t r = threadIdx.x; r < n_src; r += 32) bulk_copy_g2s(stage_addr + r * row_len, g + (size_t)r * cp.w, row_len, mbar);
+        }
+    }
     const uint32_t plane_idx = entry.x, local = entry.y, seq = entry.z & 0xFFFFu, n_ops = entry.z >> 16, ops_begin = entry.w;
     if (threadIdx.x < sizeof(DevPlane) / 16) {
         reinterpret_cast<uint4*>(&s_plane)[threadIdx.x] =
