@@ -779,8 +779,6 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
     const uint32_t row_len = (phase + (uint32_t)P.crop_w * 3u + 15u) & ~15u;
 
     const int src_first = axis_first(ya - y1, fy);
-    const int src_last = min(axis_first(yb - y1, fy) + 1, crop_h - 1);
-    const uint32_t n_src = (uint32_t)(src_last - src_first + 1);
     if (threadIdx.x <= (uint32_t)(yb - ya)) {
         /* vertical taps of one row of the band: shared-memory addresses of its two source rows, and
            its two weights already duplicated into pairs */

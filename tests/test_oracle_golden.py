@@ -131,7 +131,7 @@ def test_resize_params_table(oracle_port):
                 assert [rp.x1, rp.y1, rp.x2, rp.y2] == list(res[ar][2:])
 
 
-def test_survey_known_geometry(oracle_port):
+def test_preserve_ar_geometry_worked_examples(oracle_port):
     """Crop 20x10 -> 8x8 PRESERVE_AR: target 8x4, factors 2.5, region [0,2]-[7,5]; 8x16 -> 8x8: target 4x8."""
     a = oracle_port.derive_resize(20, 10, 8, 8, abi.RESIZE_PRESERVE_AR)
     assert (a.target_width, a.target_height, a.fx, a.fy, a.x1, a.y1, a.x2, a.y2) == (8, 4, 2.5, 2.5, 0, 2, 7, 5)
