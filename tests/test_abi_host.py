@@ -182,3 +182,32 @@ def test_divisions_by_plan_constants_are_lowered_only_when_proven(fkb_lib):
         plan = chains.elementwise(ops, src=u8.ctypes.data, dst=out.ctypes.data, width=8, height=8)
         info = abi.validate(plan)
         assert (info.n_constant_divisions, info.n_ieee_divisions) == want, ops
+
+
+def test_repeated_operations_are_stored_once(fkb_lib):
+    """A long continuation that repeats a pair of operations is lowered to a counted loop: the plan's
+    device table holds the pair once (plus a header), not every repetition."""
+    def table_bytes(ops):
+        plan = chains.elementwise(ops, src=1 << 20, dst=1 << 24, width=64, height=8, src_format=abi.SRC_F32X3)
+        return abi.validate(plan).device_bytes
+    long_chain = table_bytes(chains.addmul_ops(256))
+    short_chain = table_bytes(chains.addmul_ops(2))
+    assert long_chain - short_chain == 16          # one header slot
+    irregular = [op(abi.OP_ADD, 0.001 * (i + 1)) for i in range(256)]   # nothing repeats: every op is stored
+    assert table_bytes(irregular) - short_chain == 254 * 16
+
+
+def test_staged_plans_have_two_table_entries_per_block(fkb_lib):
+    """uchar3 resize plans on 16-byte aligned frames run the shared-memory staged body: 32 bytes of
+    work-item table per thread block (the second entry starts the block's bulk copies); frames with
+    an unaligned pitch fall back to 16."""
+    def info(pitch):
+        rects = np.array([(0, 0, 100, 80), (20, 10, 60, 90)], np.int32)
+        plan = chains.crop_resize_batch(frame_ptrs=[1 << 28], frame_index=[0, 0], rects=rects, src_width=200, src_height=120,
+                                        src_pitch=pitch, dst=1 << 30, dst_width=64, dst_height=64,
+                                        post_ops=chains.normalize_ops(), planar=True)
+        return abi.validate(plan)
+    fixed = 2 * 112 + 64 + 5 * 16 + 16              # planes, sequence, operations (two divisions take two slots), status
+    staged, direct = info(608), info(600)
+    assert staged.device_bytes == fixed + 32 * staged.grid_x
+    assert direct.device_bytes == fixed + 16 * direct.grid_x
