@@ -251,9 +251,9 @@ FKB_API int fkb_execute_host(const fkb_plan_desc* desc, void* stream);
  * image pointers are the caller's, as everywhere else.  Behaviour:
  *  - validates and lowers `desc` exactly like fkb_plan_create, copies the table into the fixed
  *    array on `stream`, launches, and synchronises `stream` before returning;
- *  - a plan whose table (112 B per plane + 48 B per sequence + 16 B per operation + 16 B per
- *    thread block of its launch; fkb_plan_validate reports it as device_bytes) exceeds
- *    FKB_STATIC_TABLE_BYTES is refused with FKB_ERR_TOO_LARGE, nothing runs;
+ *  - a plan whose table (112 B per plane + 64 B per sequence + 16 B per operation + 16 or 32 B
+ *    per thread block of its launch) exceeds FKB_STATIC_TABLE_BYTES is refused with
+ *    FKB_ERR_TOO_LARGE, nothing runs;
  *  - calls cudaMalloc, cudaFree or an allocating library routine never; host memory only;
  *  - the first call on a device looks up the array's device address (with that device
  *    current); make that first call before starting any stream capture on the device;
