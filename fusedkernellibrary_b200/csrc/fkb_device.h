@@ -80,7 +80,6 @@ enum PreKind : int32_t {
 };
 
 constexpr int INLINE_MAX_OPS = 16;
-constexpr uint32_t WIDE_ITEM_STRIDE = 2 + 112 / 16; /* two entries and a DevPlane, in 16-byte units */
 
 /* Kernel argument block (passed by value). */
 struct LaunchArgs {
@@ -92,15 +91,14 @@ struct LaunchArgs {
                                 /* uchar3 classes have two per block, the second being the     */
                                 /* first byte to copy, rows | row bytes << 16, source pitch    */
     uint32_t n_planes;
-    uint32_t item_stride;       /* table entries (16 B) per thread block: 1, 2, or               */
-                                /* WIDE_ITEM_STRIDE = the two entries + a copy of the plane      */
+    uint32_t reserved;
     uint32_t total_items;
     uint32_t max_seq_ops;       /* longest sequence: sizes the shared-memory op cache         */
     uint32_t block_threads;     /* threads per block of this launch (multiple of 32, <= 256)  */
     uint32_t staged_bytes;      /* STAGED classes: shared memory behind the operation cache    */
     uint32_t inline_plane;      /* 1: a plan of one plane whose descriptors travel in the      */
                                 /* kernel arguments below; block b is tile b of that plane     */
-    uint32_t single_seq;        /* 1: the plan has one sequence (its operations start at 0)    */
+    uint32_t pad;
     uint32_t* status;           /* one word in the plan's device block: 0, or a STATUS_* code  */
     DevPlane plane0;            /* inline_plane: the plane, its sequence and its operations    */
     DevSeq seq0;

@@ -77,8 +77,7 @@ struct HostImage {
     uint32_t total_items = 0;
     uint32_t max_seq_ops = 0;
     uint32_t staged_bytes = 0;          /* > 0: a STAGED class, this much shared memory per block */
-    bool early_copies = false;          /* staged uchar3 classes: two table entries per block ...  */
-    bool compact = false;               /* ... followed by a copy of the plane unless this is set  */
+    bool early_copies = false;          /* staged uchar3 classes: two table entries per block     */
     uint64_t output_pixels = 0;
     uint64_t algorithmic_bytes = 0;
     int n_constant_divisions = 0, n_ieee_divisions = 0;
@@ -87,8 +86,7 @@ struct HostImage {
     size_t off_seqs() const { return planes.size() * sizeof(DevPlane); }
     size_t off_ops() const { return off_seqs() + seqs.size() * sizeof(DevSeq); }
     size_t off_items() const { return off_ops() + std::max<size_t>(ops.size(), 1) * sizeof(DevOp); }
-    uint32_t item_stride() const { return !early_copies ? 1u : compact ? 2u : WIDE_ITEM_STRIDE; }
-    size_t off_status() const { return off_items() + (size_t)total_items * item_stride() * 16; }
+    size_t off_status() const { return off_items() + (size_t)total_items * (early_copies ? 32 : 16); }
     size_t bytes() const { return off_status() + 16; }
 
     void serialize(unsigned char* dst) const {
@@ -96,20 +94,16 @@ struct HostImage {
         std::memcpy(dst + off_seqs(), seqs.data(), seqs.size() * sizeof(DevSeq));
         if (!ops.empty()) std::memcpy(dst + off_ops(), ops.data(), ops.size() * sizeof(DevOp));
         /* work-item table: item_start holds the prefix sums of the items per plane */
-        const size_t stride_words = (size_t)item_stride() * 4;
-        uint32_t* const table = reinterpret_cast<uint32_t*>(dst + off_items());
+        uint32_t* e = reinterpret_cast<uint32_t*>(dst + off_items());
         for (size_t i = 0; i < planes.size(); ++i) {
             const DevSeq& q = seqs[planes[i].seq];
             const DevPlane& dp = planes[i];
-            for (uint32_t l = 0, n = item_start[i + 1] - item_start[i]; l < n; ++l) {
-                uint32_t* const e = table + (size_t)(item_start[i] + l) * stride_words;
+            for (uint32_t l = 0, n = item_start[i + 1] - item_start[i]; l < n; ++l, e += 4) {
                 e[0] = (uint32_t)i; e[1] = l; e[2] = dp.seq | ((uint32_t)q.n_ops << 16); e[3] = (uint32_t)q.ops_begin;
                 if (!early_copies) continue;
-                /* second entry: what the band's bulk copies need (zeros for a store-only item); in the
-                   wide form a copy of the plane's descriptor follows it */
-                uint32_t* const cp = e + 4;
-                cp[0] = cp[1] = cp[2] = cp[3] = 0;
-                if (!compact) std::memcpy(e + 8, &dp, sizeof(DevPlane));
+                /* second entry: what the band's bulk copies need (nothing for a store-only item) */
+                e += 4;
+                e[0] = e[1] = e[2] = e[3] = 0;
                 if (l >= dp.roi_items) continue;
                 const uint32_t n_rows = (uint32_t)(dp.y2 - dp.y1 + 1);
                 const uint32_t ra = l * dp.tiles_x, rb = std::min(ra + dp.tiles_x, n_rows) - 1;
@@ -118,8 +112,8 @@ struct HostImage {
                 const uint32_t row_first = ((uint32_t)dp.crop_x * 3u) & ~15u;
                 const uint32_t row_len = (((uint32_t)dp.crop_x * 3u - row_first) + (uint32_t)dp.crop_w * 3u + 15u) & ~15u;
                 const uintptr_t src = reinterpret_cast<uintptr_t>(dp.src) + (size_t)(dp.crop_y + first) * dp.src_pitch + row_first;
-                cp[0] = (uint32_t)(src & 0xFFFFFFFFu); cp[1] = (uint32_t)((uint64_t)src >> 32);
-                cp[2] = (uint32_t)(last - first + 1) | (row_len << 16); cp[3] = dp.src_pitch;
+                e[0] = (uint32_t)(src & 0xFFFFFFFFu); e[1] = (uint32_t)((uint64_t)src >> 32);
+                e[2] = (uint32_t)(last - first + 1) | (row_len << 16); e[3] = dp.src_pitch;
             }
         }
         std::memset(dst + off_status(), 0, 16);
@@ -131,8 +125,6 @@ struct HostImage {
         a.ops = reinterpret_cast<const DevOp*>(d_base + off_ops());
         a.items = reinterpret_cast<const uint4*>(d_base + off_items());
         a.n_planes = (uint32_t)planes.size();
-        a.item_stride = item_stride();
-        a.single_seq = seqs.size() == 1 ? 1u : 0u;
         a.total_items = total_items;
         a.max_seq_ops = max_seq_ops;
         a.block_threads = block_threads;
@@ -1312,7 +1304,6 @@ extern "C" FKB_API int fkb_execute_static(const fkb_plan_desc* desc, void* strea
     HostImage img;
     int rc = lower(desc, img);
     if (rc) return rc;
-    img.compact = true; /* the fixed table holds the short form of the work-item entries */
     const size_t bytes = img.bytes();
     if (bytes > (size_t)FKB_STATIC_TABLE_BYTES)
         return fail(FKB_ERR_TOO_LARGE,

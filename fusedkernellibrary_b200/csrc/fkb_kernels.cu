@@ -1216,14 +1216,11 @@ __global__ void __launch_bounds__(BLOCK_THREADS, min_blocks_of(CLASS)) fused_pla
     /* One 16-byte table entry tells the block its plane, its tile within the plane and where the
        plane's sequence and operations are, so that the three descriptors arrive in one round trip.
        The staged uchar3 classes have a second entry with the band's copy parameters: warp 0 starts
-       the bulk copies of the source rows from it at once, before the plane's descriptor is known.
-       In their wide table form a copy of the plane's descriptor follows the two entries, and with a
-       single sequence in the plan nothing has to wait for the first entry: one round trip in all. */
+       the bulk copies of the source rows from it at once, before the plane's descriptor is known. */
     constexpr bool EARLY_COPIES = CLASS == CLASS_RESIZE_U8_PLANAR_STAGED || CLASS == CLASS_RESIZE_U8_PACKED_STAGED;
-    const uint4* const mine = a.items + (size_t)a.item_stride * blockIdx.x;
-    const uint4 entry = __ldg(mine);
+    const uint4 entry = __ldg(a.items + (EARLY_COPIES ? 2u * blockIdx.x : blockIdx.x));
     if (EARLY_COPIES && threadIdx.x < 32) {
-        const uint4 cp = __ldg(mine + 1); /* source pointer, rows | row bytes << 16, pitch */
+        const uint4 cp = __ldg(a.items + 2u * blockIdx.x + 1u); /* source pointer, rows | row bytes << 16, pitch */
         const uint32_t n_src = cp.z & 0xFFFFu, row_len = cp.z >> 16;
         if (n_src != 0) {
             unsigned char* const staged = smem_raw + (((a.max_seq_ops > 0 ? a.max_seq_ops : 1u) * (uint32_t)sizeof(OpSlot) + 127u) & ~127u);
@@ -1238,12 +1235,10 @@ __global__ void __launch_bounds__(BLOCK_THREADS, min_blocks_of(CLASS)) fused_pla
             for (uint32_t r = threadIdx.x; r < n_src; r += 32) bulk_copy_g2s(stage_addr + r * row_len, g + (size_t)r * cp.w, row_len, mbar);
         }
     }
-    const bool one_trip = EARLY_COPIES && a.item_stride == WIDE_ITEM_STRIDE && a.single_seq != 0;
-    const uint4* const plane_src = (EARLY_COPIES && a.item_stride == WIDE_ITEM_STRIDE) ? mine + 2 : reinterpret_cast<const uint4*>(a.planes + entry.x);
-    const uint32_t local = entry.y;
-    const uint32_t seq = one_trip ? 0u : entry.z & 0xFFFFu, n_ops = one_trip ? a.max_seq_ops : entry.z >> 16, ops_begin = one_trip ? 0u : entry.w;
+    const uint32_t plane_idx = entry.x, local = entry.y, seq = entry.z & 0xFFFFu, n_ops = entry.z >> 16, ops_begin = entry.w;
     if (threadIdx.x < sizeof(DevPlane) / 16) {
-        reinterpret_cast<uint4*>(&s_plane)[threadIdx.x] = __ldg(plane_src + threadIdx.x);
+        reinterpret_cast<uint4*>(&s_plane)[threadIdx.x] =
+            __ldg(reinterpret_cast<const uint4*>(a.planes + plane_idx) + threadIdx.x);
     } else if (threadIdx.x >= 32 && threadIdx.x < 32 + sizeof(DevSeq) / 16) {
         reinterpret_cast<uint4*>(&s_seq)[threadIdx.x - 32] = __ldg(reinterpret_cast<const uint4*>(a.seqs + seq) + (threadIdx.x - 32));
     } else if (threadIdx.x >= 64) {

@@ -197,10 +197,10 @@ def test_repeated_operations_are_stored_once(fkb_lib):
     assert table_bytes(irregular) - short_chain == 254 * 16
 
 
-def test_staged_plans_have_wide_table_entries(fkb_lib):
-    """uchar3 resize plans on 16-byte aligned frames run the shared-memory staged body: 144 bytes of
-    work-item table per thread block (the block's entry, the parameters of its bulk copies and a copy of
-    its plane's descriptor); frames with an unaligned pitch fall back to 16."""
+def test_staged_plans_have_two_table_entries_per_block(fkb_lib):
+    """uchar3 resize plans on 16-byte aligned frames run the shared-memory staged body: 32 bytes of
+    work-item table per thread block (the second entry starts the block's bulk copies); frames with
+    an unaligned pitch fall back to 16."""
     def info(pitch):
         rects = np.array([(0, 0, 100, 80), (20, 10, 60, 90)], np.int32)
         plan = chains.crop_resize_batch(frame_ptrs=[1 << 28], frame_index=[0, 0], rects=rects, src_width=200, src_height=120,
@@ -209,5 +209,5 @@ def test_staged_plans_have_wide_table_entries(fkb_lib):
         return abi.validate(plan)
     fixed = 2 * 112 + 64 + 5 * 16 + 16              # planes, sequence, operations (two divisions take two slots), status
     staged, direct = info(608), info(600)
-    assert staged.device_bytes == fixed + 144 * staged.grid_x
+    assert staged.device_bytes == fixed + 32 * staged.grid_x
     assert direct.device_bytes == fixed + 16 * direct.grid_x
