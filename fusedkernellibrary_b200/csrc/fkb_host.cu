@@ -94,8 +94,17 @@ struct HostImage {
         std::memcpy(dst + off_seqs(), seqs.data(), seqs.size() * sizeof(DevSeq));
         if (!ops.empty()) std::memcpy(dst + off_ops(), ops.data(), ops.size() * sizeof(DevOp));
         /* work-item table: item_start holds the prefix sums of the items per plane */
+        /* Blocks start in table order.  In a plan of several classes the planes that interpolate
+           go first: their blocks take longest, and started last they would run alone at the end. */
+        std::vector<size_t> order(planes.size());
+        for (size_t i = 0; i < order.size(); ++i) order[i] = i;
+        if (launch_class == CLASS_MIXED)
+            std::stable_partition(order.begin(), order.end(), [&](size_t i) {
+                const uint32_t c = planes[i].plane_class;
+                return c == CLASS_RESIZE_U8_PLANAR || c == CLASS_RESIZE_U8_PACKED || c == CLASS_RESIZE_NV12_PACKED || c == CLASS_GENERIC;
+            });
         uint32_t* e = reinterpret_cast<uint32_t*>(dst + off_items());
-        for (size_t i = 0; i < planes.size(); ++i) {
+        for (size_t i : order) {
             const DevSeq& q = seqs[planes[i].seq];
             const DevPlane& dp = planes[i];
             for (uint32_t l = 0, n = item_start[i + 1] - item_start[i]; l < n; ++l, e += 4) {
