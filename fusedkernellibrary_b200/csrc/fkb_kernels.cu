@@ -367,77 +367,94 @@ template <uint32_t CHAIN, bool SRC_IS_U8, bool DST_IS_U8>
 __device__ __forceinline__ void body_flat(const DevPlane& P, const DevSeq& S, const OpSlot* sops, uint32_t local) {
     constexpr int SPX = SRC_IS_U8 ? 3 : 12;
     constexpr int DPX = DST_IS_U8 ? 3 : 12;
+    constexpr int Q = FLAT_QUADS;
+    /* A work item is FLAT_QUADS runs of 4 * blockDim pixels of one segment; a thread owns four
+       consecutive pixels of each run, so that a warp reads and writes whole 128-byte lines, and has
+       the loads of all its runs in flight before it computes. */
     const uint32_t items_per_seg = (P.seg_pixels + ITEM_PIXELS_VEC - 1) / ITEM_PIXELS_VEC;
     const uint32_t seg = local / items_per_seg;
-    const uint32_t px0 = (local - seg * items_per_seg) * ITEM_PIXELS_VEC + threadIdx.x * PX_PER_THREAD;
-    if (px0 >= P.seg_pixels) return;
-    const uint32_t n = min((uint32_t)PX_PER_THREAD, P.seg_pixels - px0);
-    const uint8_t* src = P.src + (size_t)(P.crop_y + seg) * P.src_pitch + (size_t)P.crop_x * SPX + (size_t)px0 * SPX;
-    uint8_t* dst = P.dst + (size_t)seg * P.dst_pitch + (size_t)px0 * DPX;
+    const uint32_t base = (local - seg * items_per_seg) * ITEM_PIXELS_VEC + threadIdx.x * PX_PER_THREAD;
+    const uint8_t* const src_seg = P.src + (size_t)(P.crop_y + seg) * P.src_pitch + (size_t)P.crop_x * SPX;
+    uint8_t* const dst_seg = P.dst + (size_t)seg * P.dst_pitch;
 
-    float v[12];
-    if (n == PX_PER_THREAD) {
-        if (SRC_IS_U8) {
-            const uint32_t* s4 = reinterpret_cast<const uint32_t*>(src);
+    float v[Q][12];
+    uint32_t n[Q];
 #pragma unroll
-            for (int k = 0; k < 3; ++k) {
-                const uint32_t w = __ldg(s4 + k);
-                v[4 * k + 0] = packed_u8_to_float<0>(w);
-                v[4 * k + 1] = packed_u8_to_float<1>(w);
-                v[4 * k + 2] = packed_u8_to_float<2>(w);
-                v[4 * k + 3] = packed_u8_to_float<3>(w);
+    for (int r = 0; r < Q; ++r) {
+        const uint32_t px0 = base + r * (BLOCK_THREADS * PX_PER_THREAD);
+        n[r] = px0 < P.seg_pixels ? min((uint32_t)PX_PER_THREAD, P.seg_pixels - px0) : 0u;
+        const uint8_t* src = src_seg + (size_t)px0 * SPX;
+        if (n[r] == PX_PER_THREAD) {
+            if (SRC_IS_U8) {
+                const uint32_t* s4 = reinterpret_cast<const uint32_t*>(src);
+#pragma unroll
+                for (int k = 0; k < 3; ++k) {
+                    const uint32_t w = __ldg(s4 + k);
+                    v[r][4 * k + 0] = packed_u8_to_float<0>(w);
+                    v[r][4 * k + 1] = packed_u8_to_float<1>(w);
+                    v[r][4 * k + 2] = packed_u8_to_float<2>(w);
+                    v[r][4 * k + 3] = packed_u8_to_float<3>(w);
+                }
+            } else {
+                const float4* s4 = reinterpret_cast<const float4*>(src);
+#pragma unroll
+                for (int k = 0; k < 3; ++k) {
+                    const float4 w = __ldg(s4 + k);
+                    v[r][4 * k + 0] = w.x; v[r][4 * k + 1] = w.y; v[r][4 * k + 2] = w.z; v[r][4 * k + 3] = w.w;
+                }
             }
         } else {
-            const float4* s4 = reinterpret_cast<const float4*>(src);
 #pragma unroll
-            for (int k = 0; k < 3; ++k) {
-                const float4 w = __ldg(s4 + k);
-                v[4 * k + 0] = w.x; v[4 * k + 1] = w.y; v[4 * k + 2] = w.z; v[4 * k + 3] = w.w;
-            }
-        }
-    } else {
-#pragma unroll
-        for (int i = 0; i < 12; ++i) {
-            v[i] = 0.0f;
-            if (i < (int)n * 3) {
-                v[i] = SRC_IS_U8 ? u8_to_float(__ldg(src + i)) : __ldg(reinterpret_cast<const float*>(src) + i);
+            for (int i = 0; i < 12; ++i) {
+                v[r][i] = 0.0f;
+                if (i < (int)n[r] * 3) v[r][i] = SRC_IS_U8 ? u8_to_float(__ldg(src + i)) : __ldg(reinterpret_cast<const float*>(src) + i);
             }
         }
     }
+    if (n[0] == 0) return;
 
     {
-        /* pair pixels (0,1) and (2,3) channel by channel */
-        float2 q[6];
+        /* pair pixels (0,1) and (2,3) of every run channel by channel */
+        float2 q[6 * Q];
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
+        for (int r = 0; r < Q; ++r)
 #pragma unroll
-            for (int c = 0; c < 3; ++c) q[3 * j + c] = make_float2(v[6 * j + c], v[6 * j + 3 + c]);
-        run_ops<CHAIN, 2>(q, sops, 0, S.n_ops, dup2(S.one));
+            for (int j = 0; j < 2; ++j)
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
+                for (int c = 0; c < 3; ++c) q[6 * r + 3 * j + c] = make_float2(v[r][6 * j + c], v[r][6 * j + 3 + c]);
+        run_ops<CHAIN, 2 * Q>(q, sops, 0, S.n_ops, dup2(S.one));
 #pragma unroll
-            for (int c = 0; c < 3; ++c) { v[6 * j + c] = q[3 * j + c].x; v[6 * j + 3 + c] = q[3 * j + c].y; }
+        for (int r = 0; r < Q; ++r)
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int c = 0; c < 3; ++c) { v[r][6 * j + c] = q[6 * r + 3 * j + c].x; v[r][6 * j + 3 + c] = q[6 * r + 3 * j + c].y; }
     }
 
-    if (n == PX_PER_THREAD) {
-        if (DST_IS_U8) {
-            uint32_t* d4 = reinterpret_cast<uint32_t*>(dst);
 #pragma unroll
-            for (int k = 0; k < 3; ++k) {
-                d4[k] = (uint32_t)(uint8_t)v[4 * k + 0] | ((uint32_t)(uint8_t)v[4 * k + 1] << 8) |
-                        ((uint32_t)(uint8_t)v[4 * k + 2] << 16) | ((uint32_t)(uint8_t)v[4 * k + 3] << 24);
+    for (int r = 0; r < Q; ++r) {
+        const uint32_t px0 = base + r * (BLOCK_THREADS * PX_PER_THREAD);
+        uint8_t* dst = dst_seg + (size_t)px0 * DPX;
+        if (n[r] == PX_PER_THREAD) {
+            if (DST_IS_U8) {
+                uint32_t* d4 = reinterpret_cast<uint32_t*>(dst);
+#pragma unroll
+                for (int k = 0; k < 3; ++k) {
+                    d4[k] = (uint32_t)(uint8_t)v[r][4 * k + 0] | ((uint32_t)(uint8_t)v[r][4 * k + 1] << 8) |
+                            ((uint32_t)(uint8_t)v[r][4 * k + 2] << 16) | ((uint32_t)(uint8_t)v[r][4 * k + 3] << 24);
+                }
+            } else {
+                float4* d4 = reinterpret_cast<float4*>(dst);
+#pragma unroll
+                for (int k = 0; k < 3; ++k) d4[k] = make_float4(v[r][4 * k + 0], v[r][4 * k + 1], v[r][4 * k + 2], v[r][4 * k + 3]);
             }
         } else {
-            float4* d4 = reinterpret_cast<float4*>(dst);
 #pragma unroll
-            for (int k = 0; k < 3; ++k) d4[k] = make_float4(v[4 * k + 0], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
-        }
-    } else {
-#pragma unroll
-        for (int i = 0; i < 12; ++i) {
-            if (i < (int)n * 3) {
-                if (DST_IS_U8) dst[i] = (uint8_t)v[i];
-                else reinterpret_cast<float*>(dst)[i] = v[i];
+            for (int i = 0; i < 12; ++i) {
+                if (i < (int)n[r] * 3) {
+                    if (DST_IS_U8) dst[i] = (uint8_t)v[r][i];
+                    else reinterpret_cast<float*>(dst)[i] = v[r][i];
+                }
             }
         }
     }
