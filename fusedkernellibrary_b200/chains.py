@@ -71,16 +71,18 @@ def normalize_ops(mean=IMAGENET_MEAN, std=IMAGENET_STD):
     return [op(OP_DIV, 255.0), op(OP_SUB, mean), op(OP_DIV, std)]
 
 
-def nv12_resize_batch(*, frame_ptrs, width, height, pitch, dst, dst_width, dst_height, div=255.0, plan=None):
+def nv12_resize_batch(*, frame_ptrs, width, height, pitch, dst, dst_width, dst_height, div=255.0, plan=None,
+                      mode=RESIZE_IGNORE_AR, background=(0.0, 0.0, 0.0), crops=None):
     """Config 4: ReadYUV<NV12>[B] -> ConvertYUVToRGB<bt709, Full, float3> -> Resize(IGNORE_AR) -> Div
-    -> TensorWrite<float3>."""
+    -> TensorWrite<float3>.  `crops` (one rect per frame) and PRESERVE_AR are variations for tests."""
     plan = plan or abi.HostPlan()
-    seq = plan.add_sequence(SRC_NV12, DST_F32X3_PACKED, RESIZE_IGNORE_AR,
-                            [op(OP_YUV_TO_RGB_BT709_FULL), op(OP_DIV, div)], n_pre_ops=1)
+    seq = plan.add_sequence(SRC_NV12, DST_F32X3_PACKED, mode,
+                            [op(OP_YUV_TO_RGB_BT709_FULL), op(OP_DIV, div)], n_pre_ops=1, background=background)
     plane_bytes = dst_width * dst_height * 12
     for i, p in enumerate(frame_ptrs):
         plan.add_plane(src=p, src_width=width, src_height=height, src_pitch=pitch, dst=dst + i * plane_bytes,
-                       dst_width=dst_width, dst_height=dst_height, dst_pitch=dst_width * 12, sequence=seq)
+                       dst_width=dst_width, dst_height=dst_height, dst_pitch=dst_width * 12, sequence=seq,
+                       crop=None if crops is None else tuple(int(v) for v in crops[i]))
     return plan
 
 

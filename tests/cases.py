@@ -84,7 +84,8 @@ def crop_resize_case(name, seed, n_frames, fw, fh, n_planes, dw, dh, planar, pos
     return Case(name, sources, {"out": out}, build, meta=dict(rects=rects, frame_index=frame_index))
 
 
-def nv12_case(name, seed, n_frames, w, h, dw, dh, pitch=None):
+def nv12_case(name, seed, n_frames, w, h, dw, dh, pitch=None, mode=abi.RESIZE_IGNORE_AR, background=(0.0, 0.0, 0.0),
+              crops=None):
     rng = np.random.default_rng(seed)
     pitch = pitch or w
     sources = {}
@@ -96,9 +97,33 @@ def nv12_case(name, seed, n_frames, w, h, dw, dh, pitch=None):
 
     def build(ptr):
         return chains.nv12_resize_batch(frame_ptrs=[ptr(f"frame{i}") for i in range(n_frames)], width=w, height=h,
-                                        pitch=pitch, dst=ptr("out"), dst_width=dw, dst_height=dh)
+                                        pitch=pitch, dst=ptr("out"), dst_width=dw, dst_height=dh, mode=mode,
+                                        background=background, crops=crops)
 
     return Case(name, sources, {"out": out}, build)
+
+
+def resize_any_case(name, seed, src_fmt, dst_fmt, w, h, dw, dh, pre_ops, post_ops, mode=abi.RESIZE_IGNORE_AR):
+    """One image -> pre_ops on every tap -> Resize -> post_ops -> receiver, any source / destination format."""
+    rng = np.random.default_rng(seed)
+    if src_fmt == abi.SRC_U8X3:
+        src = _u8(rng, h, w * 3)
+        sp = w * 3
+    else:
+        src = (rng.random((h, w * 3), dtype=np.float32) * 255).astype(np.float32)
+        sp = w * 12
+    planar = dst_fmt == abi.DST_F32_PLANAR3
+    dpx = {abi.DST_F32X3_PACKED: 12, abi.DST_U8X3_PACKED: 3, abi.DST_F32_PLANAR3: 4}[dst_fmt]
+    out = np.zeros((3 * dh if planar else dh, dw * dpx), np.uint8)
+
+    def build(ptr):
+        plan = abi.HostPlan()
+        seq = plan.add_sequence(src_fmt, dst_fmt, mode, list(pre_ops) + list(post_ops), n_pre_ops=len(pre_ops))
+        plan.add_plane(src=ptr("src"), src_width=w, src_height=h, src_pitch=sp, dst=ptr("out"), dst_width=dw, dst_height=dh,
+                       dst_pitch=dw * dpx, dst_channel_stride=dh * dw * 4 if planar else 0, sequence=seq)
+        return plan
+
+    return Case(name, {"src": src}, {"out": out}, build, float_outputs=dst_fmt != abi.DST_U8X3_PACKED)
 
 
 def divergent_case(name, seed, w, h, rw, rh, per_group):
@@ -177,6 +202,15 @@ def small_cases():
         nv12_case("c4_fractional", 42, 2, 96, 54, 40, 22),
         nv12_case("c4_pitched", 43, 2, 98, 54, 36, 20, pitch=128),
         nv12_case("c4_odd_dst", 44, 2, 96, 54, 37, 21),
+        nv12_case("c4_preserve_ar_bg", 45, 2, 96, 54, 48, 48, mode=abi.RESIZE_PRESERVE_AR, background=(16.0, 128.0, 240.0)),
+        nv12_case("c4_crops", 46, 3, 128, 64, 40, 24, crops=[(1, 1, 101, 33), (64, 31, 64, 33), (0, 0, 2, 2)]),
+        nv12_case("c4_upscale_tiles", 47, 1, 32, 16, 1280, 40),                 # three column tiles, every tap fractional
+        # chains that only the one-pixel-per-thread body takes
+        resize_any_case("float_source_resize", 71, abi.SRC_F32X3, abi.DST_F32X3_PACKED, 40, 30, 24, 18,
+                        [op(abi.OP_MUL, 2.0)], [op(abi.OP_ADD, 0.5)]),
+        resize_any_case("resize_then_saturate_u8", 72, abi.SRC_U8X3, abi.DST_U8X3_PACKED, 64, 48, 32, 20,
+                        [op(abi.OP_CAST_F32)], [op(abi.OP_MUL, 1.1), op(abi.OP_SATURATE_CAST_U8)]),
+        resize_any_case("planar_ignore_ar", 73, abi.SRC_U8X3, abi.DST_F32_PLANAR3, 64, 48, 40, 28, [], chains.normalize_ops()),
         divergent_case("c5b_small", 51, 64, 36, 32, 18, 3),
         divergent_case("c5b_odd", 52, 50, 30, 25, 15, 2),
     ]
