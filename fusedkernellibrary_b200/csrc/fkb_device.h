@@ -107,8 +107,15 @@ struct LaunchArgs {
 
 constexpr int BLOCK_THREADS = 256;
 constexpr int PX_PER_THREAD = 4;
-constexpr int FLAT_QUADS = 1; /* FLAT classes: runs of four pixels per thread (2 measured slower: 36.9 -> 42.8 us on C5A N=1) */
-constexpr int ITEM_PIXELS_VEC = BLOCK_THREADS * PX_PER_THREAD * FLAT_QUADS; /* FLAT classes: pixels per work item */
+#ifndef FKB_FLAT_QUADS_U8
+#define FKB_FLAT_QUADS_U8 4
+#endif
+/* FLAT classes: runs of four pixels per thread.  A thread has the raw words of all its runs in
+ * flight before it computes the first; a uchar3 run is three words, so four runs are cheap to hold,
+ * a float3 run is twelve (two runs measured slower than one: 36.9 -> 42.8 us on one 4K float3 Add). */
+__host__ __device__ constexpr int flat_quads(bool src_is_u8) { return src_is_u8 ? FKB_FLAT_QUADS_U8 : 1; }
+/* FLAT classes: pixels per work item */
+__host__ __device__ constexpr int flat_item_pixels(bool src_is_u8) { return BLOCK_THREADS * PX_PER_THREAD * flat_quads(src_is_u8); }
 constexpr int ITEM_PIXELS_GENERIC = BLOCK_THREADS;
 
 /* Device-only opcode: division by a plan-time constant, lowered from FKB_OP_DIV when the host

@@ -749,7 +749,8 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
                 dp.n_segs = dense ? 1 : p.dst_height;
                 dp.seg_pixels = dense ? (uint32_t)out_px : p.dst_width;
                 if (dense && out_px > 0xFFFFFFFFull) return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: too many pixels", i);
-                items = (uint64_t)dp.n_segs * ((dp.seg_pixels + ITEM_PIXELS_VEC - 1) / ITEM_PIXELS_VEC);
+                const uint32_t item_px = (uint32_t)flat_item_pixels(src_u8);
+                items = (uint64_t)dp.n_segs * ((dp.seg_pixels + item_px - 1) / item_px);
             }
         } else if (s.resize_mode != FKB_RESIZE_NONE && (p.dst_width % PX_PER_THREAD) == 0 && aligned(dp.dst, 16) && (p.dst_pitch % 16) == 0 &&
                    s.pre_kind != PRE_GENERAL) {
@@ -798,6 +799,15 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
     }
     img.item_start[d->n_planes] = (uint32_t)total;
     img.total_items = (uint32_t)total;
+    /* Planes of one flat class whose sequences differ, some of them compiled chains: the kernel
+       that selects per block (first the chain, then the class) runs each plane's compiled chain,
+       where the kernel of the class would interpret them all. */
+    if ((common_class == CLASS_FLAT_U8_F32 || common_class == CLASS_FLAT_F32_F32 || common_class == CLASS_FLAT_U8_U8) &&
+        !chain_is_compiled(common_chain)) {
+        bool any_compiled = false;
+        for (const DevSeq& ds : img.seqs) any_compiled = any_compiled || ds.chain != CHAIN_INTERPRET;
+        if (any_compiled) common_class = CLASS_MIXED;
+    }
     img.launch_class = common_class;
     img.chain = (common_class != CLASS_MIXED && common_class != CLASS_GENERIC && chain_is_compiled(common_chain))
                     ? common_chain : CHAIN_INTERPRET;

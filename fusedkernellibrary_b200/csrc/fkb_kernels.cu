@@ -21,6 +21,7 @@
 #include <stdint.h>
 
 #include "fkb200.h"
+#include <type_traits>
 #include "fkb_device.h"
 
 namespace fkb {
@@ -32,9 +33,12 @@ namespace fkb {
 /* SaturateCast<float, uchar>: clamp, then cxp::round = (int)(x + 0.5f) for x > 0
  * (image_processing/saturate.h:27-50, constexpr_libs/constexpr_cmath.h:119-130). */
 __device__ __forceinline__ float saturate_round_u8(float f) {
-    if (f > 255.0f) return 255.0f;
-    if (f < 0.0f) return 0.0f;
-    return (float)__float2int_rz(__fadd_rn(f, 0.5f));
+    /* (int)(t) of t = f + 0.5f in [0.5, 255.5] is floor(t): adding 2^23 rounded down leaves
+       2^23 + floor(t), and taking 2^23 off again is exact.  Same values as a float -> int -> float
+       round trip, without two trips through the quarter-rate conversion unit.  fmaxf maps NaN to
+       0 as the comparisons of the reference's clamp followed by the conversion do. */
+    const float t = __fadd_rn(fminf(fmaxf(f, 0.0f), 255.0f), 0.5f);
+    return __fadd_rn(__fadd_rd(t, 8388608.0f), -8388608.0f);
 }
 
 /* Exact uchar -> float.  Converting from a 32-bit integer (not from an 8-bit one) keeps the
@@ -371,96 +375,128 @@ __device__ __forceinline__ void body_generic(const DevPlane& P, const DevSeq& S,
 /* body: no geometry stage, four whole pixels per thread                                */
 /* ------------------------------------------------------------------------------------ */
 template <uint32_t CHAIN, bool SRC_IS_U8, bool DST_IS_U8>
-__device__ __forceinline__ void body_flat(const DevPlane& P, const DevSeq& S, const OpSlot* sops, uint32_t local) {
+__device__ __forceinline__ void body_flat(const DevPlane& P, const DevSeq& S, const OpSlot* sops, uint32_t local,
+                                          unsigned char* turn_mem) {
     constexpr int SPX = SRC_IS_U8 ? 3 : 12;
     constexpr int DPX = DST_IS_U8 ? 3 : 12;
-    constexpr int Q = FLAT_QUADS;
-    /* A work item is FLAT_QUADS runs of 4 * blockDim pixels of one segment; a thread owns four
-       consecutive pixels of each run, so that a warp reads and writes whole 128-byte lines, and has
-       the loads of all its runs in flight before it computes. */
-    const uint32_t items_per_seg = (P.seg_pixels + ITEM_PIXELS_VEC - 1) / ITEM_PIXELS_VEC;
+    constexpr int Q = flat_quads(SRC_IS_U8);
+    constexpr int RAW = SRC_IS_U8 ? 3 : 12; /* words of a run of four pixels as it lies in memory */
+    constexpr uint32_t ITEM = (uint32_t)flat_item_pixels(SRC_IS_U8);
+    /* A work item is Q runs of 4 * blockDim pixels of one segment; a thread owns four consecutive
+       pixels of each run, so that a warp reads and writes whole 128-byte lines.  The raw words of
+       all runs are loaded before the first run is computed: the block's start-up (two dependent
+       descriptor reads) is paid once for Q times the data, with Q loads in flight per thread. */
+    const uint32_t items_per_seg = (P.seg_pixels + ITEM - 1) / ITEM;
     const uint32_t seg = local / items_per_seg;
-    const uint32_t base = (local - seg * items_per_seg) * ITEM_PIXELS_VEC + threadIdx.x * PX_PER_THREAD;
+    const uint32_t base = (local - seg * items_per_seg) * ITEM + threadIdx.x * PX_PER_THREAD;
     const uint8_t* const src_seg = P.src + (size_t)(P.crop_y + seg) * P.src_pitch + (size_t)P.crop_x * SPX;
     uint8_t* const dst_seg = P.dst + (size_t)seg * P.dst_pitch;
 
-    float v[Q][12];
+    /* Output of one run, warp by warp: a thread's four pixels are 48 (12) bytes, so stores straight
+       from the registers would write a third of every sector per instruction, and that pattern was
+       measured at 5.0 TB/s against 6.4 TB/s for whole lines.  The warp therefore turns its 128
+       pixels around in shared memory and every store instruction writes consecutive bytes. */
+    using OutWord = typename std::conditional<DST_IS_U8, uint32_t, float4>::type;
+    const uint32_t lane = threadIdx.x & 31u;
+    OutWord* const my_turn = reinterpret_cast<OutWord*>(turn_mem) + (threadIdx.x >> 5) * 96u;
+
+    uint32_t raw[Q][RAW];
     uint32_t n[Q];
+    bool whole_warp[Q]; /* every thread of the warp has a full run: uniform across the warp */
 #pragma unroll
     for (int r = 0; r < Q; ++r) {
         const uint32_t px0 = base + r * (BLOCK_THREADS * PX_PER_THREAD);
         n[r] = px0 < P.seg_pixels ? min((uint32_t)PX_PER_THREAD, P.seg_pixels - px0) : 0u;
+        whole_warp[r] = px0 - lane * PX_PER_THREAD + 32u * PX_PER_THREAD <= P.seg_pixels;
         const uint8_t* src = src_seg + (size_t)px0 * SPX;
         if (n[r] == PX_PER_THREAD) {
-            if (SRC_IS_U8) {
+            if constexpr (SRC_IS_U8) {
                 const uint32_t* s4 = reinterpret_cast<const uint32_t*>(src);
 #pragma unroll
-                for (int k = 0; k < 3; ++k) {
-                    const uint32_t w = __ldg(s4 + k);
-                    v[r][4 * k + 0] = packed_u8_to_float<0>(w);
-                    v[r][4 * k + 1] = packed_u8_to_float<1>(w);
-                    v[r][4 * k + 2] = packed_u8_to_float<2>(w);
-                    v[r][4 * k + 3] = packed_u8_to_float<3>(w);
-                }
+                for (int k = 0; k < 3; ++k) raw[r][k] = __ldg(s4 + k);
             } else {
-                const float4* s4 = reinterpret_cast<const float4*>(src);
+                const uint4* s4 = reinterpret_cast<const uint4*>(src);
 #pragma unroll
                 for (int k = 0; k < 3; ++k) {
-                    const float4 w = __ldg(s4 + k);
-                    v[r][4 * k + 0] = w.x; v[r][4 * k + 1] = w.y; v[r][4 * k + 2] = w.z; v[r][4 * k + 3] = w.w;
+                    const uint4 w = __ldg(s4 + k);
+                    raw[r][4 * k + 0] = w.x; raw[r][4 * k + 1] = w.y; raw[r][4 * k + 2] = w.z; raw[r][4 * k + 3] = w.w;
                 }
             }
         } else {
+            /* the ragged end of a segment, element by element into the same layout */
+#pragma unroll
+            for (int k = 0; k < RAW; ++k) raw[r][k] = 0u;
 #pragma unroll
             for (int i = 0; i < 12; ++i) {
-                v[r][i] = 0.0f;
-                if (i < (int)n[r] * 3) v[r][i] = SRC_IS_U8 ? u8_to_float(__ldg(src + i)) : __ldg(reinterpret_cast<const float*>(src) + i);
+                if (i < (int)n[r] * 3) {
+                    if constexpr (SRC_IS_U8) raw[r][i / 4] |= (uint32_t)__ldg(src + i) << (8 * (i % 4));
+                    else raw[r][i] = __ldg(reinterpret_cast<const uint32_t*>(src) + i);
+                }
             }
         }
     }
-    if (n[0] == 0) return;
 
-    {
-        /* pair pixels (0,1) and (2,3) of every run channel by channel */
-        float2 q[6 * Q];
-#pragma unroll
-        for (int r = 0; r < Q; ++r)
-#pragma unroll
-            for (int j = 0; j < 2; ++j)
-#pragma unroll
-                for (int c = 0; c < 3; ++c) q[6 * r + 3 * j + c] = make_float2(v[r][6 * j + c], v[r][6 * j + 3 + c]);
-        run_ops<CHAIN, 2 * Q>(q, sops, 0, S.n_ops, dup2(S.one));
-#pragma unroll
-        for (int r = 0; r < Q; ++r)
-#pragma unroll
-            for (int j = 0; j < 2; ++j)
-#pragma unroll
-                for (int c = 0; c < 3; ++c) { v[r][6 * j + c] = q[6 * r + 3 * j + c].x; v[r][6 * j + 3 + c] = q[6 * r + 3 * j + c].y; }
-    }
-
+    const float2 one2 = dup2(S.one);
 #pragma unroll
     for (int r = 0; r < Q; ++r) {
+        if (n[r] == 0) break;
+        float v[12];
+#pragma unroll
+        for (int k = 0; k < 3; ++k) {
+            if constexpr (SRC_IS_U8) {
+                v[4 * k + 0] = packed_u8_to_float<0>(raw[r][k]);
+                v[4 * k + 1] = packed_u8_to_float<1>(raw[r][k]);
+                v[4 * k + 2] = packed_u8_to_float<2>(raw[r][k]);
+                v[4 * k + 3] = packed_u8_to_float<3>(raw[r][k]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) v[4 * k + j] = __uint_as_float(raw[r][4 * k + j]);
+            }
+        }
+        /* pair pixels (0,1) and (2,3) channel by channel */
+        float2 q[6];
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int c = 0; c < 3; ++c) q[3 * j + c] = make_float2(v[6 * j + c], v[6 * j + 3 + c]);
+        run_ops<CHAIN, 2>(q, sops, 0, S.n_ops, one2);
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int c = 0; c < 3; ++c) { v[6 * j + c] = q[3 * j + c].x; v[6 * j + 3 + c] = q[3 * j + c].y; }
+
         const uint32_t px0 = base + r * (BLOCK_THREADS * PX_PER_THREAD);
         uint8_t* dst = dst_seg + (size_t)px0 * DPX;
         if (n[r] == PX_PER_THREAD) {
-            if (DST_IS_U8) {
-                uint32_t* d4 = reinterpret_cast<uint32_t*>(dst);
+            OutWord w[3];
 #pragma unroll
-                for (int k = 0; k < 3; ++k) {
-                    d4[k] = (uint32_t)(uint8_t)v[r][4 * k + 0] | ((uint32_t)(uint8_t)v[r][4 * k + 1] << 8) |
-                            ((uint32_t)(uint8_t)v[r][4 * k + 2] << 16) | ((uint32_t)(uint8_t)v[r][4 * k + 3] << 24);
+            for (int k = 0; k < 3; ++k) {
+                if constexpr (DST_IS_U8) {
+                    w[k] = (uint32_t)(uint8_t)v[4 * k + 0] | ((uint32_t)(uint8_t)v[4 * k + 1] << 8) |
+                           ((uint32_t)(uint8_t)v[4 * k + 2] << 16) | ((uint32_t)(uint8_t)v[4 * k + 3] << 24);
+                } else {
+                    w[k] = make_float4(v[4 * k + 0], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
                 }
-            } else {
-                float4* d4 = reinterpret_cast<float4*>(dst);
+            }
+            if (whole_warp[r]) {
 #pragma unroll
-                for (int k = 0; k < 3; ++k) d4[k] = make_float4(v[r][4 * k + 0], v[r][4 * k + 1], v[r][4 * k + 2], v[r][4 * k + 3]);
+                for (int k = 0; k < 3; ++k) my_turn[lane * 3 + k] = w[k];
+                __syncwarp();
+                OutWord* const warp_dst = reinterpret_cast<OutWord*>(dst) - lane * 3;
+#pragma unroll
+                for (int k = 0; k < 3; ++k) warp_dst[k * 32 + lane] = my_turn[k * 32 + lane];
+                __syncwarp();
+            } else {
+                OutWord* d4 = reinterpret_cast<OutWord*>(dst);
+#pragma unroll
+                for (int k = 0; k < 3; ++k) d4[k] = w[k];
             }
         } else {
 #pragma unroll
             for (int i = 0; i < 12; ++i) {
                 if (i < (int)n[r] * 3) {
-                    if (DST_IS_U8) dst[i] = (uint8_t)v[r][i];
-                    else reinterpret_cast<float*>(dst)[i] = v[r][i];
+                    if (DST_IS_U8) dst[i] = (uint8_t)v[i];
+                    else reinterpret_cast<float*>(dst)[i] = v[i];
                 }
             }
         }
@@ -1184,12 +1220,12 @@ __device__ __forceinline__ void body_nv12_staged(const DevPlane& P, const DevSeq
 /* The bodies of one continuation (compiled chain or interpreter), selected by the plane's class. */
 template <uint32_t CLASS, uint32_t CHAIN>
 __device__ __forceinline__ void run_class(uint32_t cls, const DevPlane& P, const DevSeq& S, const OpSlot* sops,
-                                          uint32_t local, unsigned char* staged_mem, uint32_t* status) {
+                                          uint32_t local, unsigned char* staged_mem, unsigned char* turn_mem, uint32_t* status) {
     if (CLASS != CLASS_MIXED) cls = CLASS;
     switch (cls) {
-        case CLASS_FLAT_U8_F32: body_flat<CHAIN, true, false>(P, S, sops, local); break;
-        case CLASS_FLAT_F32_F32: body_flat<CHAIN, false, false>(P, S, sops, local); break;
-        case CLASS_FLAT_U8_U8: body_flat<CHAIN, true, true>(P, S, sops, local); break;
+        case CLASS_FLAT_U8_F32: body_flat<CHAIN, true, false>(P, S, sops, local, turn_mem); break;
+        case CLASS_FLAT_F32_F32: body_flat<CHAIN, false, false>(P, S, sops, local, turn_mem); break;
+        case CLASS_FLAT_U8_U8: body_flat<CHAIN, true, true>(P, S, sops, local, turn_mem); break;
         case CLASS_RESIZE_U8_PLANAR: body_resize<CHAIN, FKB_SRC_U8X3, true>(P, S, sops, local); break;
         case CLASS_RESIZE_U8_PACKED: body_resize<CHAIN, FKB_SRC_U8X3, false>(P, S, sops, local); break;
         case CLASS_RESIZE_NV12_PACKED: body_resize<CHAIN, FKB_SRC_NV12, false>(P, S, sops, local); break;
@@ -1211,16 +1247,16 @@ __device__ __forceinline__ void run_class(uint32_t cls, const DevPlane& P, const
  * the continuation of the plane's sequence, if it is one of the compiled chains, then the class. */
 template <uint32_t CLASS, uint32_t CHAIN>
 __device__ __forceinline__ void run_body(uint32_t cls, const DevPlane& P, const DevSeq& S, const OpSlot* sops,
-                                         uint32_t local, unsigned char* staged_mem, uint32_t* status) {
+                                         uint32_t local, unsigned char* staged_mem, unsigned char* turn_mem, uint32_t* status) {
     if constexpr (CLASS != CLASS_MIXED) {
-        run_class<CLASS, CHAIN>(cls, P, S, sops, local, staged_mem, status);
+        run_class<CLASS, CHAIN>(cls, P, S, sops, local, staged_mem, turn_mem, status);
     } else {
         const uint32_t chain = S.chain;
 #define FKB_MIXED_CASE(CH) \
-    if (chain == (CH)) { run_class<CLASS_MIXED, (CH)>(cls, P, S, sops, local, staged_mem, status); return; }
+    if (chain == (CH)) { run_class<CLASS_MIXED, (CH)>(cls, P, S, sops, local, staged_mem, turn_mem, status); return; }
         FKB_CHAIN_MENU(FKB_MIXED_CASE)
 #undef FKB_MIXED_CASE
-        run_class<CLASS_MIXED, CHAIN_INTERPRET>(cls, P, S, sops, local, staged_mem, status);
+        run_class<CLASS_MIXED, CHAIN_INTERPRET>(cls, P, S, sops, local, staged_mem, turn_mem, status);
     }
 }
 
@@ -1239,13 +1275,16 @@ __global__ void __launch_bounds__(BLOCK_THREADS, min_blocks_of(CLASS)) fused_pla
     OpSlot* sops = reinterpret_cast<OpSlot*>(smem_raw);
     __shared__ DevPlane s_plane;
     __shared__ DevSeq s_seq;
+    /* flat bodies: 96 sixteen-byte words per warp in which a run of output is turned around */
+    constexpr bool HAS_FLAT = CLASS == CLASS_FLAT_U8_F32 || CLASS == CLASS_FLAT_F32_F32 || CLASS == CLASS_FLAT_U8_U8 || CLASS == CLASS_MIXED;
+    __shared__ __align__(16) unsigned char s_turn[HAS_FLAT ? (BLOCK_THREADS / 32) * 96 * 16 : 16];
 
     if (a.inline_plane) {
         /* one plane: everything is in the kernel arguments; only the operation table is expanded */
         const uint32_t n_ops = (uint32_t)a.seq0.n_ops;
         if (threadIdx.x < n_ops) expand_op(*reinterpret_cast<const uint4*>(&a.ops0[threadIdx.x]), sops + threadIdx.x);
         __syncthreads();
-        run_body<CLASS, CHAIN>(a.plane0.plane_class, a.plane0, a.seq0, sops, blockIdx.x, nullptr, a.status);
+        run_body<CLASS, CHAIN>(a.plane0.plane_class, a.plane0, a.seq0, sops, blockIdx.x, nullptr, s_turn, a.status);
         return;
     }
     /* One 16-byte table entry tells the block its plane, its tile within the plane and where the
@@ -1283,7 +1322,7 @@ __global__ void __launch_bounds__(BLOCK_THREADS, min_blocks_of(CLASS)) fused_pla
     __syncthreads();
     /* staged classes: the region after the operation cache, on a 128-byte boundary */
     unsigned char* staged_mem = smem_raw + (((a.max_seq_ops > 0 ? a.max_seq_ops : 1u) * (uint32_t)sizeof(OpSlot) + 127u) & ~127u);
-    run_body<CLASS, CHAIN>(s_plane.plane_class, s_plane, s_seq, sops, local, staged_mem, a.status);
+    run_body<CLASS, CHAIN>(s_plane.plane_class, s_plane, s_seq, sops, local, staged_mem, s_turn, a.status);
 }
 
 /* ------------------------------------------------------------------------------------ */
