@@ -1265,11 +1265,14 @@ __device__ __forceinline__ void run_body(uint32_t cls, const DevPlane& P, const 
  * of several classes with four as well (the flat bodies hold four runs per thread and the
  * interpolating body its taps: at six blocks and 40 registers both spilled; four groups of 16 images
  * 1920x1080 took 0.319 ms at six, 0.294 at five, 0.285 at four); the bodies that read taps straight
- * from global memory keep all their loads in flight in registers instead. */
+ * from global memory keep all their loads in flight in registers instead.  The flat bodies run
+ * five blocks (48 registers, no spills in the compiled chains): a 4K float3 Add took 37.6 us
+ * unconstrained (three to four blocks) and 35.9 us at five, 64 alternating Add/Mul 76.6 and 65.7. */
 constexpr int min_blocks_of(uint32_t cls) {
     return (cls == CLASS_RESIZE_U8_PLANAR_STAGED || cls == CLASS_RESIZE_U8_PACKED_STAGED) ? 4
            : cls == CLASS_RESIZE_NV12_PACKED_STAGED ? 5
-           : cls == CLASS_MIXED ? 4 : 1;
+           : cls == CLASS_MIXED ? 4
+           : (cls == CLASS_FLAT_U8_F32 || cls == CLASS_FLAT_U8_U8 || cls == CLASS_FLAT_F32_F32) ? 5 : 1;
 }
 template <uint32_t CLASS, uint32_t CHAIN>
 __global__ void __launch_bounds__(BLOCK_THREADS, min_blocks_of(CLASS)) fused_plan_kernel(const __grid_constant__ LaunchArgs a) {
