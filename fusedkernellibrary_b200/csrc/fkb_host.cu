@@ -601,7 +601,15 @@ static StagedTiling staged_tiling(const DevPlane& dp, uint32_t block_threads) {
     }
     while (band > 1 && worst_rows(band) > max_src_rows) --band;
     if (worst_rows(band) > max_src_rows) return t;
-    if (band > t.rs) band -= band % t.rs; /* whole rounds of the row slots */
+    /* Bands of equal height, in whole rounds of the row slots: 44 rows that fit one band are one
+       band (not 40 + 4, each paying a block's start-up), 224 rows under a limit of 64 are 4 x 56. */
+    {
+        const uint32_t n_bands = (n_rows + band - 1) / band;
+        uint32_t even = (n_rows + n_bands - 1) / n_bands;
+        even = (even + t.rs - 1) / t.rs * t.rs;
+        if (even <= STAGED_MAX_ROWS && worst_rows(even) <= max_src_rows) band = even;
+        else if (band > t.rs) band -= band % t.rs;
+    }
     t.band_rows = band;
     t.n_bands = (n_rows + band - 1) / band;
     t.stage_bytes = worst_rows(band) * row_len + 16;
