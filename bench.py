@@ -39,7 +39,7 @@ L2_BYTES = 126 * 1024 * 1024
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the workload's kernel, from the ncu
 # capture summarised under profiles/ (None = not captured).
-TRAFFIC_BYTES_PER_LAUNCH = {"c3": 778.5e6, "c4": 472.9e6}
+TRAFFIC_BYTES_PER_LAUNCH = {"c3": 774.0e6, "c4": 472.9e6}
 
 
 # --------------------------------------------------------------------------------------
@@ -207,6 +207,37 @@ class VerticalFusion(Workload):
         return self.out_pixels
 
 
+class VerticalFusionBatch(Workload):
+    """Config 1's chain on a batch of images in one launch (BatchRead of the same sequence): the
+    single 31 MB image of config 1 is too small to show what the element-wise body sustains."""
+    name = "c1b"
+
+    def __init__(self, seed, n=16, w=1920, h=1080, sets=2):
+        super().__init__(seed)
+        rng = np.random.default_rng(seed)
+        self.w, self.h, self.n, self.sets = w, h, n, sets
+        self.sources = [{f"src{i}": _u8(rng, h, w * 3) for i in range(n)} for _ in range(sets)]
+        self.outputs = [{"out": ((n, h, w, 3), np.float32)} for _ in range(sets)]
+        self.out_pixels = n * w * h
+        self.description = (f"C1 chain on a batch: {n} x {w}x{h} uchar3 -> Cast, *1.4, -0.5, /255 -> float3, one launch "
+                            f"({sets} buffer sets)")
+
+    def build(self, ptr, s=0):
+        plan = abi.HostPlan()
+        seq = plan.add_sequence(abi.SRC_U8X3, abi.DST_F32X3_PACKED, abi.RESIZE_NONE, chains.cast_mul_sub_div_ops())
+        for i in range(self.n):
+            plan.add_plane(src=ptr(f"src{i}"), src_width=self.w, src_height=self.h, src_pitch=self.w * 3,
+                           dst=ptr("out") + i * self.w * self.h * 12, dst_width=self.w, dst_height=self.h,
+                           dst_pitch=self.w * 12, sequence=seq)
+        return plan
+
+    def reference_run(self, threads, s=0, planes=None):
+        from oracle import reference as ref
+        for i in range(self.n):
+            ref.cast_mul_sub_div(self.sources[s][f"src{i}"].reshape(self.h, self.w, 3), 1.4, 0.5, 255.0)
+        return self.out_pixels
+
+
 class LongChain(Workload):
     """Config 5A: N alternating Add(0.001)/Mul(1.0001) on a 3840x2160 float3 image."""
     name = "c5a"
@@ -301,6 +332,8 @@ def make_workload(name: str, seed: int) -> Workload:
         return ReadmeCropResize(seed, repeat=8192 // 5)
     if name == "c1":
         return VerticalFusion(seed)
+    if name == "c1b":
+        return VerticalFusionBatch(seed)
     if name.startswith("c5a"):
         return LongChain(seed, n_ops=int(name[3:] or 16))
     if name == "c4":
