@@ -8,6 +8,7 @@
 #ifndef FKB_DEVICE_H
 #define FKB_DEVICE_H
 
+#include <math.h>
 #include <stdint.h>
 
 namespace fkb {
@@ -43,7 +44,10 @@ struct alignas(16) DevPlane {
     uint32_t seq;
     uint32_t plane_class;
     uint32_t seg_pixels;     /* FLAT classes: pixels per contiguous segment; staged NV12:     */
-                             /* output rows per work item (band)                              */
+                             /* output rows per work item (band); staged uchar3: index, within */
+                             /* the whole region of interest, of this column tile's first     */
+                             /* region column (a region wider than a block's columns is cut   */
+                             /* into tiles, each a DevPlane of its own over the same source)  */
     uint32_t n_segs;         /* FLAT classes: 1 (dense plane) or dst_h (one segment per row); */
                              /* staged uchar3 resize: 1 when the last band also fills the     */
                              /* rows outside the region (no store-only items)                 */
@@ -146,6 +150,37 @@ struct ResizeTiling {
     uint32_t roi_items;      /* tiles_x * tiles_y                                              */
     uint32_t bg_items;       /* store-only items for the rows outside the region               */
 };
+/* Staged uchar3 resize: the bytes of a crop row that the taps of region columns
+ * [col0, col0 + n_cols) touch, widened to 16-byte boundaries (what one bulk copy fetches per
+ * source row).  First taps are floor(column * fx) in binary32 (resize.h:183-194,
+ * interpolation.h:66-67); host and device evaluate the same expression. */
+struct StagedSpan {
+    int sx0;            /* first source column staged, relative to the crop            */
+    uint32_t row_first; /* byte offset of the copy within a source row                 */
+    uint32_t phase;     /* byte of column sx0 within the copy                          */
+    uint32_t row_len;   /* bytes per copied row, a multiple of 16                      */
+};
+#if defined(__CUDACC__)
+__host__ __device__
+#endif
+inline StagedSpan staged_span(int crop_x, int crop_w, uint32_t col0, uint32_t n_cols, float fx) {
+    StagedSpan s;
+#if defined(__CUDA_ARCH__)
+    s.sx0 = __float2int_rd(__fmul_rn((float)col0, fx));
+    int sx1 = __float2int_rd(__fmul_rn((float)(col0 + n_cols - 1u), fx)) + 1;
+#else
+    s.sx0 = (int)floorf((float)col0 * fx);
+    int sx1 = (int)floorf((float)(col0 + n_cols - 1u) * fx) + 1;
+#endif
+    if (sx1 > crop_w - 1) sx1 = crop_w - 1;
+    if (sx1 < s.sx0) sx1 = s.sx0;
+    const uint32_t b0 = (uint32_t)(crop_x + s.sx0) * 3u;
+    s.row_first = b0 & ~15u;
+    s.phase = b0 - s.row_first;
+    s.row_len = (s.phase + (uint32_t)(sx1 - s.sx0 + 1) * 3u + 15u) & ~15u;
+    return s;
+}
+
 #if defined(__CUDACC__)
 __host__ __device__
 #endif

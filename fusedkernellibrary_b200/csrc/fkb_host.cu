@@ -72,6 +72,7 @@ struct HostImage {
     std::vector<uint32_t> item_start;
     std::vector<fkb_resize_params> resize;
     uint32_t launch_class = CLASS_GENERIC;
+    uint32_t n_user_planes = 0;         /* planes of the description (a wide staged plane is several DevPlanes) */
     uint32_t chain = CHAIN_INTERPRET;   /* compiled chain shared by every sequence, or CHAIN_INTERPRET */
     uint32_t block_threads = BLOCK_THREADS;
     uint32_t total_items = 0;
@@ -118,9 +119,9 @@ struct HostImage {
                 const uint32_t ra = l * dp.tiles_x, rb = std::min(ra + dp.tiles_x, n_rows) - 1;
                 const int first = (int)std::floor((float)ra * dp.fy);
                 const int last = std::min((int)std::floor((float)rb * dp.fy) + 1, dp.crop_h - 1);
-                const uint32_t row_first = ((uint32_t)dp.crop_x * 3u) & ~15u;
-                const uint32_t row_len = (((uint32_t)dp.crop_x * 3u - row_first) + (uint32_t)dp.crop_w * 3u + 15u) & ~15u;
-                const uintptr_t src = reinterpret_cast<uintptr_t>(dp.src) + (size_t)(dp.crop_y + first) * dp.src_pitch + row_first;
+                const StagedSpan span = staged_span(dp.crop_x, dp.crop_w, dp.seg_pixels, (uint32_t)(dp.x2 - dp.x1 + 1), dp.fx);
+                const uint32_t row_len = span.row_len;
+                const uintptr_t src = reinterpret_cast<uintptr_t>(dp.src) + (size_t)(dp.crop_y + first) * dp.src_pitch + span.row_first;
                 e[0] = (uint32_t)(src & 0xFFFFFFFFu); e[1] = (uint32_t)((uint64_t)src >> 32);
                 e[2] = (uint32_t)(last - first + 1) | (row_len << 16); e[3] = dp.src_pitch;
             }
@@ -575,10 +576,9 @@ static StagedTiling staged_tiling(const DevPlane& dp, uint32_t block_threads) {
     const uint32_t pairs = n_groups * (PX_PER_THREAD / 2); /* threads across: each owns two columns */
     if (pairs > block_threads) return t;
     if ((reinterpret_cast<uintptr_t>(dp.src) % 16) != 0 || (dp.src_pitch % 16) != 0) return t;
-    const uint32_t row_first = ((uint32_t)dp.crop_x * 3u) & ~15u;
-    const uint32_t phase = (uint32_t)dp.crop_x * 3u - row_first;
-    const uint32_t row_len = (phase + (uint32_t)dp.crop_w * 3u + 15u) & ~15u;
-    if (row_first + row_len > dp.src_pitch) return t; /* never reads past the end of a row */
+    const StagedSpan span = staged_span(dp.crop_x, dp.crop_w, dp.seg_pixels, (uint32_t)(dp.x2 - dp.x1 + 1), dp.fx);
+    const uint32_t row_len = span.row_len;
+    if (span.row_first + row_len > dp.src_pitch) return t; /* never reads past the end of a row */
     /* the kernel reads whole words around the last tap: 16 spare bytes behind the last row */
     const uint32_t max_src_rows = (STAGED_MAX_STAGE_BYTES - 16) / row_len;
     if (max_src_rows < 2) return t;
@@ -686,6 +686,7 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
     std::vector<int> step_exp_x(d->n_sequences, 0), step_exp_y(d->n_sequences, 0);
 
     img.planes.resize(d->n_planes);
+    img.n_user_planes = (uint32_t)d->n_planes;
     img.resize.assign(d->n_planes, fkb_resize_params{});
     img.item_start.assign((size_t)d->n_planes + 1, 0);
     uint64_t total = 0;
@@ -821,6 +822,35 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
                     ? common_chain : CHAIN_INTERPRET;
     /* uchar3 resize plans whose every plane can stage its bands' source rows in shared memory */
     if (common_class == CLASS_RESIZE_U8_PLANAR || common_class == CLASS_RESIZE_U8_PACKED) {
+        /* A region wider than the columns one block covers (two per thread) is cut into column
+           tiles of whole four-pixel groups, each a plane of its own over the same source: its
+           destination starts at the tile, its region is the part of the region inside the tile, and
+           seg_pixels tells the kernel where in the whole region its first column lies.  The first
+           and last tile also take the columns left and right of the region. */
+        const std::vector<DevPlane> user_planes = img.planes;
+        {
+            std::vector<DevPlane> cut;
+            const uint32_t px_bytes = common_class == CLASS_RESIZE_U8_PLANAR ? 4u : 12u;
+            const uint32_t max_groups = (uint32_t)BLOCK_THREADS * 2u / PX_PER_THREAD;
+            for (const DevPlane& up : user_planes) {
+                const uint32_t g_lo = (uint32_t)up.x1 / PX_PER_THREAD;
+                const uint32_t n_groups = (uint32_t)up.x2 / PX_PER_THREAD - g_lo + 1;
+                const uint32_t n_tiles = (n_groups + max_groups - 1) / max_groups;
+                const uint32_t per_tile = (n_groups + n_tiles - 1) / n_tiles;
+                for (uint32_t k = 0; k < n_tiles; ++k) {
+                    DevPlane dp = up;
+                    const uint32_t c0 = k == 0 ? 0u : (g_lo + k * per_tile) * PX_PER_THREAD;
+                    const uint32_t c1 = k == n_tiles - 1 ? up.dst_w : (g_lo + (k + 1) * per_tile) * PX_PER_THREAD;
+                    const int r0 = std::max(up.x1, (int)c0), r1 = std::min(up.x2, (int)c1 - 1);
+                    dp.dst = up.dst + (size_t)c0 * px_bytes;
+                    dp.dst_w = c1 - c0;
+                    dp.x1 = r0 - (int)c0; dp.x2 = r1 - (int)c0;
+                    dp.seg_pixels = (uint32_t)(r0 - up.x1);
+                    cut.push_back(dp);
+                }
+            }
+            img.planes = std::move(cut);
+        }
         std::vector<StagedTiling> st(img.planes.size());
         bool all = true;
         uint32_t stage = 0;
@@ -829,8 +859,10 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
             all = st[i].ok;
             stage = std::max(stage, st[i].stage_bytes);
         }
+        if (!all) img.planes = user_planes; /* the body that reads taps from global memory takes whole planes */
         if (all) {
             const uint32_t cls = common_class == CLASS_RESIZE_U8_PLANAR ? CLASS_RESIZE_U8_PLANAR_STAGED : CLASS_RESIZE_U8_PACKED_STAGED;
+            img.item_start.assign(img.planes.size() + 1, 0);
             uint64_t t2 = 0;
             for (size_t i = 0; i < img.planes.size(); ++i) {
                 DevPlane& dp = img.planes[i];
@@ -942,7 +974,7 @@ static int require_device(int* device) {
 
 static fkb_plan_info info_of(const HostImage& img) {
     fkb_plan_info info{};
-    info.n_planes = (int32_t)img.planes.size();
+    info.n_planes = (int32_t)img.n_user_planes;
     info.n_sequences = (int32_t)img.seqs.size();
     info.n_launches = 1;
     info.grid_x = img.total_items;

@@ -833,10 +833,11 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
     const int crop_h = P.crop_h;
     const float fy = P.fy;
 
-    /* source bytes of one crop row, widened to 16-byte boundaries */
-    const uint32_t row_first = ((uint32_t)P.crop_x * 3u) & ~15u;
-    const uint32_t phase = (uint32_t)P.crop_x * 3u - row_first;
-    const uint32_t row_len = (phase + (uint32_t)P.crop_w * 3u + 15u) & ~15u;
+    /* source bytes of one crop row that this plane's region columns touch, widened to 16-byte
+       boundaries; col0 > 0 when the plane is a column tile of a wider region */
+    const uint32_t col0 = P.seg_pixels;
+    const StagedSpan span = staged_span(P.crop_x, P.crop_w, col0, (uint32_t)(x2 - x1 + 1), P.fx);
+    const uint32_t phase = span.phase, row_len = span.row_len;
 
     const int src_first = axis_first(ya - y1, fy);
     if (threadIdx.x <= (uint32_t)(yb - ya)) {
@@ -859,9 +860,9 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
     const int x_end = (int)((g_lo + n_groups) * PX_PER_THREAD);
     const bool in_a = xa >= x1 && xa <= x2, in_b = xb >= x1 && xb <= x2;
     const bool valid_b = xb < x_end;
-    const Axis axa = make_axis(in_a ? xa - x1 : 0, P.fx, P.crop_w);
-    const Axis axb = make_axis(in_b ? xb - x1 : 0, P.fx, P.crop_w);
-    const uint32_t oa = phase + (uint32_t)axa.i0 * 3u, ob = phase + (uint32_t)axb.i0 * 3u;
+    const Axis axa = make_axis((in_a ? xa - x1 : 0) + (int)col0, P.fx, P.crop_w);
+    const Axis axb = make_axis((in_b ? xb - x1 : 0) + (int)col0, P.fx, P.crop_w);
+    const uint32_t oa = phase + (uint32_t)(axa.i0 - span.sx0) * 3u, ob = phase + (uint32_t)(axb.i0 - span.sx0) * 3u;
     const uint32_t word_a = oa & ~3u, word_b = ob & ~3u;
     const uint32_t shift_a = (oa & 3u) * 8u, shift_b = (ob & 3u) * 8u;
     const uint32_t second_a = axa.i1 == axa.i0 ? 0x3210u : 0x3543u; /* bytes of the second tap in (u0, u1) */

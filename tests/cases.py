@@ -198,6 +198,14 @@ def small_cases():
                          background=(10.0, 20.0, 30.0)),
         crop_resize_case("c2_staged_ignore_ar_odd_groups", 65, 1, 208, 120, 4, 36, 20, False, chains.readme_ops(),
                          mode=abi.RESIZE_IGNORE_AR),
+        # regions wider than 512 columns: the staged body cuts them into column tiles
+        crop_resize_case("wide_planar_preserve_ar_bg", 66, 1, 1600, 96, 4, 1320, 40, True, chains.normalize_ops(),
+                         rects=[(0, 0, 1600, 40), (3, 1, 1597, 95), (37, 8, 901, 20), (800, 0, 640, 33)],
+                         background=(7.0, 9.0, 11.0)),
+        crop_resize_case("wide_packed_ignore_ar", 67, 2, 2048, 64, 3, 1024, 24, False, chains.readme_ops(),
+                         rects=[(0, 0, 2048, 48), (5, 3, 2043, 61), (16, 0, 520, 10)], mode=abi.RESIZE_IGNORE_AR),
+        crop_resize_case("wide_packed_upscale", 68, 1, 208, 32, 2, 2052, 12, False, chains.readme_ops(),
+                         rects=[(1, 1, 203, 9), (0, 0, 208, 32)], mode=abi.RESIZE_IGNORE_AR),
         nv12_case("c4_exact3", 41, 3, 96, 54, 32, 18),
         nv12_case("c4_fractional", 42, 2, 96, 54, 40, 22),
         nv12_case("c4_pitched", 43, 2, 98, 54, 36, 20, pitch=128),

@@ -211,3 +211,17 @@ def test_staged_plans_have_two_table_entries_per_block(fkb_lib):
     staged, direct = info(608), info(600)
     assert staged.device_bytes == fixed + 32 * staged.grid_x
     assert direct.device_bytes == fixed + 16 * direct.grid_x
+
+
+def test_wide_regions_are_cut_into_column_tiles_for_the_staged_body(fkb_lib):
+    """A region of 960 columns is more than the 512 a block of the staged body covers (two columns per
+    thread): the plane is lowered to two column tiles, each with a plane descriptor of its own, and the
+    plan still reports one plane."""
+    plan = abi.HostPlan()
+    seq = plan.add_sequence(abi.SRC_U8X3, abi.DST_F32X3_PACKED, abi.RESIZE_IGNORE_AR, [abi.op(abi.OP_CAST_F32)], n_pre_ops=1)
+    plan.add_plane(src=1 << 28, src_width=1920, src_height=1080, src_pitch=5760, dst=1 << 30, dst_width=960,
+                   dst_height=540, dst_pitch=960 * 12, sequence=seq)
+    info = abi.validate(plan)
+    assert info.n_planes == 1
+    fixed = 2 * 112 + 64 + 16 + 16                   # two tiles, sequence, empty operation table, status
+    assert info.device_bytes == fixed + 32 * info.grid_x
