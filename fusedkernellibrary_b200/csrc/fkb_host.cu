@@ -102,7 +102,8 @@ struct HostImage {
         if (launch_class == CLASS_MIXED)
             std::stable_partition(order.begin(), order.end(), [&](size_t i) {
                 const uint32_t c = planes[i].plane_class;
-                return c == CLASS_RESIZE_U8_PLANAR || c == CLASS_RESIZE_U8_PACKED || c == CLASS_RESIZE_NV12_PACKED || c == CLASS_GENERIC;
+                return c == CLASS_RESIZE_U8_PLANAR || c == CLASS_RESIZE_U8_PACKED || c == CLASS_RESIZE_NV12_PACKED || c == CLASS_GENERIC ||
+                       c == CLASS_RESIZE_U8_PLANAR_STAGED || c == CLASS_RESIZE_U8_PACKED_STAGED;
             });
         uint32_t* e = reinterpret_cast<uint32_t*>(dst + off_items());
         for (size_t i : order) {
@@ -114,6 +115,7 @@ struct HostImage {
                 /* second entry: what the band's bulk copies need (nothing for a store-only item) */
                 e += 4;
                 e[0] = e[1] = e[2] = e[3] = 0;
+                if (dp.plane_class != CLASS_RESIZE_U8_PLANAR_STAGED && dp.plane_class != CLASS_RESIZE_U8_PACKED_STAGED) continue;
                 if (l >= dp.roi_items) continue;
                 const uint32_t n_rows = (uint32_t)(dp.y2 - dp.y1 + 1);
                 const uint32_t ra = l * dp.tiles_x, rb = std::min(ra + dp.tiles_x, n_rows) - 1;
@@ -821,18 +823,29 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
     img.chain = (common_class != CLASS_MIXED && common_class != CLASS_GENERIC && chain_is_compiled(common_chain))
                     ? common_chain : CHAIN_INTERPRET;
     /* uchar3 resize plans whose every plane can stage its bands' source rows in shared memory */
-    if (common_class == CLASS_RESIZE_U8_PLANAR || common_class == CLASS_RESIZE_U8_PACKED) {
-        /* A region wider than the columns one block covers (two per thread) is cut into column
+    if (common_class == CLASS_RESIZE_U8_PLANAR || common_class == CLASS_RESIZE_U8_PACKED || common_class == CLASS_MIXED) {
+        /* In a plan of several classes the same holds for its uchar3 resize planes, if all of them
+           can be staged; planes of other classes keep their items.
+           A region wider than the columns one block covers (two per thread) is cut into column
            tiles of whole four-pixel groups, each a plane of its own over the same source: its
            destination starts at the tile, its region is the part of the region inside the tile, and
            seg_pixels tells the kernel where in the whole region its first column lies.  The first
            and last tile also take the columns left and right of the region. */
         const std::vector<DevPlane> user_planes = img.planes;
+        std::vector<uint32_t> kept_items; /* per lowered plane: its item count if it is not staged, else 0 */
+        bool any_resize = false;
         {
             std::vector<DevPlane> cut;
-            const uint32_t px_bytes = common_class == CLASS_RESIZE_U8_PLANAR ? 4u : 12u;
             const uint32_t max_groups = (uint32_t)BLOCK_THREADS * 2u / PX_PER_THREAD;
-            for (const DevPlane& up : user_planes) {
+            for (size_t u = 0; u < user_planes.size(); ++u) {
+                const DevPlane& up = user_planes[u];
+                if (up.plane_class != CLASS_RESIZE_U8_PLANAR && up.plane_class != CLASS_RESIZE_U8_PACKED) {
+                    cut.push_back(up);
+                    kept_items.push_back(img.item_start[u + 1] - img.item_start[u]);
+                    continue;
+                }
+                any_resize = true;
+                const uint32_t px_bytes = up.plane_class == CLASS_RESIZE_U8_PLANAR ? 4u : 12u;
                 const uint32_t g_lo = (uint32_t)up.x1 / PX_PER_THREAD;
                 const uint32_t n_groups = (uint32_t)up.x2 / PX_PER_THREAD - g_lo + 1;
                 const uint32_t n_tiles = (n_groups + max_groups - 1) / max_groups;
@@ -847,25 +860,32 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
                     dp.x1 = r0 - (int)c0; dp.x2 = r1 - (int)c0;
                     dp.seg_pixels = (uint32_t)(r0 - up.x1);
                     cut.push_back(dp);
+                    kept_items.push_back(0);
                 }
             }
             img.planes = std::move(cut);
         }
         std::vector<StagedTiling> st(img.planes.size());
-        bool all = true;
+        bool all = any_resize;
         uint32_t stage = 0;
         for (size_t i = 0; i < img.planes.size() && all; ++i) {
+            if (kept_items[i] != 0) continue;
             st[i] = staged_tiling(img.planes[i], BLOCK_THREADS);
             all = st[i].ok;
             stage = std::max(stage, st[i].stage_bytes);
         }
         if (!all) img.planes = user_planes; /* the body that reads taps from global memory takes whole planes */
         if (all) {
-            const uint32_t cls = common_class == CLASS_RESIZE_U8_PLANAR ? CLASS_RESIZE_U8_PLANAR_STAGED : CLASS_RESIZE_U8_PACKED_STAGED;
             img.item_start.assign(img.planes.size() + 1, 0);
             uint64_t t2 = 0;
             for (size_t i = 0; i < img.planes.size(); ++i) {
                 DevPlane& dp = img.planes[i];
+                if (kept_items[i] != 0) {
+                    img.item_start[i] = (uint32_t)t2;
+                    t2 += kept_items[i];
+                    continue;
+                }
+                const uint32_t cls = dp.plane_class == CLASS_RESIZE_U8_PLANAR ? CLASS_RESIZE_U8_PLANAR_STAGED : CLASS_RESIZE_U8_PACKED_STAGED;
                 const ResizeTiling rt = resize_tiling(dp.dst_w, dp.dst_h, dp.x1, dp.y1, dp.x2, dp.y2, BLOCK_THREADS);
                 const uint64_t outside_groups = (uint64_t)(dp.dst_h - (uint32_t)(dp.y2 - dp.y1 + 1)) * (dp.dst_w / PX_PER_THREAD);
                 const bool fold = outside_groups <= STAGED_FOLD_BG_GROUPS;
@@ -882,7 +902,7 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
             img.block_threads = BLOCK_THREADS;
             img.staged_bytes = STAGED_HEADER_BYTES + stage;
             img.early_copies = true;
-            img.launch_class = common_class = cls;
+            if (common_class != CLASS_MIXED) img.launch_class = common_class = img.planes[0].plane_class;
         }
     }
     /* NV12 resize plans whose every plane can stage the luma and chroma rows of its band tiles */

@@ -1231,10 +1231,10 @@ __device__ __forceinline__ void run_class(uint32_t cls, const DevPlane& P, const
         case CLASS_RESIZE_U8_PACKED: body_resize<CHAIN, FKB_SRC_U8X3, false>(P, S, sops, local); break;
         case CLASS_RESIZE_NV12_PACKED: body_resize<CHAIN, FKB_SRC_NV12, false>(P, S, sops, local); break;
         case CLASS_RESIZE_U8_PLANAR_STAGED:
-            if constexpr (CLASS != CLASS_MIXED) body_resize_staged<CHAIN, true>(P, S, sops, local, staged_mem, status);
+            body_resize_staged<CHAIN, true>(P, S, sops, local, staged_mem, status);
             break;
         case CLASS_RESIZE_U8_PACKED_STAGED:
-            if constexpr (CLASS != CLASS_MIXED) body_resize_staged<CHAIN, false>(P, S, sops, local, staged_mem, status);
+            body_resize_staged<CHAIN, false>(P, S, sops, local, staged_mem, status);
             break;
         case CLASS_RESIZE_NV12_PACKED_STAGED:
             if constexpr (CLASS != CLASS_MIXED) body_nv12_staged<CHAIN>(P, S, sops, local, staged_mem, status);
@@ -1297,7 +1297,8 @@ __global__ void __launch_bounds__(BLOCK_THREADS, min_blocks_of(CLASS)) fused_pla
        plane's sequence and operations are, so that the three descriptors arrive in one round trip.
        The staged uchar3 classes have a second entry with the band's copy parameters: warp 0 starts
        the bulk copies of the source rows from it at once, before the plane's descriptor is known. */
-    constexpr bool EARLY_COPIES = CLASS == CLASS_RESIZE_U8_PLANAR_STAGED || CLASS == CLASS_RESIZE_U8_PACKED_STAGED;
+    const bool EARLY_COPIES = CLASS == CLASS_RESIZE_U8_PLANAR_STAGED || CLASS == CLASS_RESIZE_U8_PACKED_STAGED ||
+                              (CLASS == CLASS_MIXED && a.staged_bytes != 0); /* a plan of several classes with staged planes */
     const uint4 entry = __ldg(a.items + (EARLY_COPIES ? 2u * blockIdx.x : blockIdx.x));
     if (EARLY_COPIES && threadIdx.x < 32) {
         const uint4 cp = __ldg(a.items + 2u * blockIdx.x + 1u); /* source pointer, rows | row bytes << 16, pitch */
@@ -1336,10 +1337,12 @@ __global__ void __launch_bounds__(BLOCK_THREADS, min_blocks_of(CLASS)) fused_pla
 /* ------------------------------------------------------------------------------------ */
 
 /* Launches one instantiation; the first launch that needs more than the default 48 KB of
-   dynamic shared memory raises the kernel's limit (once per instantiation and device). */
+   shared memory raises the kernel's limit (once per instantiation and device). */
 template <uint32_t CLASS, uint32_t CHAIN>
 static cudaError_t launch_one(const LaunchArgs& a, size_t smem, cudaStream_t stream) {
-    if (smem > 48 * 1024) {
+    /* the kernel's static shared memory (descriptors, the flat bodies' turn-around buffer: under
+       13 KB) counts against the same 48 KB */
+    if (smem + 13 * 1024 > 48 * 1024) {
         static size_t raised[64] = {};
         int dev = 0;
         cudaError_t e = cudaGetDevice(&dev);

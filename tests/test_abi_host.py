@@ -225,3 +225,16 @@ def test_wide_regions_are_cut_into_column_tiles_for_the_staged_body(fkb_lib):
     assert info.n_planes == 1
     fixed = 2 * 112 + 64 + 16 + 16                   # two tiles, sequence, empty operation table, status
     assert info.device_bytes == fixed + 32 * info.grid_x
+
+
+def test_plans_of_several_classes_stage_their_uchar3_resize_planes(fkb_lib):
+    """The four-chain divergent plan: 48 element-wise planes keep their items, the 16 planes of the
+    Cast -> Resize group become two staged column tiles each, and every block has two table entries
+    (the second one is empty for blocks that copy nothing)."""
+    w, h = 1920, 1080
+    plan = chains.divergent_four_groups(src_ptrs=[(1 << 28) + i * w * h * 3 for i in range(64)], width=w, height=h,
+                                        dst_ptrs=[(1 << 32) + g * (1 << 30) for g in range(4)], per_group=16)
+    info = abi.validate(plan)
+    assert info.n_planes == 64 and info.n_sequences == 4 and info.n_launches == 1
+    fixed = (48 + 2 * 16) * 112 + 4 * 64 + 8 * 16 + 16    # planes, sequences, operations, status
+    assert info.device_bytes == fixed + 32 * info.grid_x
