@@ -206,6 +206,10 @@ inline ResizeTiling resize_tiling(uint32_t dst_w, uint32_t dst_h, int x1, int y1
 /* STAGED classes: a work item is a band of `band_rows` output rows of the region of interest,
  * all columns; its source footprint (whole crop rows, widened to 16-byte boundaries) sits in
  * shared memory behind a 16-byte mbarrier slot and a table of per-row vertical taps. */
+#ifndef FKB_BAND_PIXELS
+#define FKB_BAND_PIXELS 7168
+#endif
+constexpr uint32_t STAGED_BAND_PIXELS = FKB_BAND_PIXELS; /* output pixels per band, about         */
 constexpr uint32_t STAGED_MAX_ROWS = 64;          /* output rows per band                        */
 constexpr uint32_t STAGED_MAX_STAGE_BYTES = 40 * 1024u; /* four blocks of it fit one SM */
 constexpr uint32_t STAGED_HEADER_BYTES = 16 + STAGED_MAX_ROWS * 32;

@@ -596,7 +596,11 @@ static StagedTiling staged_tiling(const DevPlane& dp, uint32_t block_threads) {
         }
         return worst;
     };
-    uint32_t band = std::min<uint32_t>(STAGED_MAX_ROWS, n_rows);
+    /* Height limit: STAGED_MAX_ROWS rows, and about STAGED_BAND_PIXELS output pixels, so that a wide
+       region is cut into more, shorter bands (their copies and arithmetic overlap across the blocks
+       of an SM) while a narrow one stays in one block. */
+    const uint32_t by_pixels = std::max<uint32_t>(t.rs, (STAGED_BAND_PIXELS / (2u * pairs) + t.rs - 1) / t.rs * t.rs);
+    uint32_t band = std::min<uint32_t>(std::min<uint32_t>(STAGED_MAX_ROWS, by_pixels), n_rows);
     {   /* first guess from the step, then exact */
         const double guess = ((double)max_src_rows - 2.0) / std::max((double)dp.fy, 1e-6) + 1.0;
         if (guess < (double)band) band = (uint32_t)std::max(1.0, guess);
