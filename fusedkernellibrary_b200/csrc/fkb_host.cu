@@ -869,12 +869,22 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
             }
             img.planes = std::move(cut);
         }
+        /* A batch of narrow regions only (at most 128 columns, 64 threads across) runs blocks of
+           128 threads: the same registers hold twice as many blocks per SM, and a batch of small
+           planes is bound by how many block start-ups are in flight. */
+        uint32_t staged_threads = common_class == CLASS_MIXED ? (uint32_t)BLOCK_THREADS : 128u;
+        for (size_t i = 0; i < img.planes.size(); ++i) {
+            if (kept_items[i] != 0) continue;
+            const DevPlane& dp = img.planes[i];
+            const uint32_t n_groups = (uint32_t)dp.x2 / PX_PER_THREAD - (uint32_t)dp.x1 / PX_PER_THREAD + 1;
+            if (n_groups * (PX_PER_THREAD / 2) > 64u) staged_threads = BLOCK_THREADS;
+        }
         std::vector<StagedTiling> st(img.planes.size());
         bool all = any_resize;
         uint32_t stage = 0;
         for (size_t i = 0; i < img.planes.size() && all; ++i) {
             if (kept_items[i] != 0) continue;
-            st[i] = staged_tiling(img.planes[i], BLOCK_THREADS);
+            st[i] = staged_tiling(img.planes[i], staged_threads);
             all = st[i].ok;
             stage = std::max(stage, st[i].stage_bytes);
         }
@@ -890,7 +900,7 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
                     continue;
                 }
                 const uint32_t cls = dp.plane_class == CLASS_RESIZE_U8_PLANAR ? CLASS_RESIZE_U8_PLANAR_STAGED : CLASS_RESIZE_U8_PACKED_STAGED;
-                const ResizeTiling rt = resize_tiling(dp.dst_w, dp.dst_h, dp.x1, dp.y1, dp.x2, dp.y2, BLOCK_THREADS);
+                const ResizeTiling rt = resize_tiling(dp.dst_w, dp.dst_h, dp.x1, dp.y1, dp.x2, dp.y2, staged_threads);
                 const uint64_t outside_groups = (uint64_t)(dp.dst_h - (uint32_t)(dp.y2 - dp.y1 + 1)) * (dp.dst_w / PX_PER_THREAD);
                 const bool fold = outside_groups <= STAGED_FOLD_BG_GROUPS;
                 dp.n_segs = fold ? 1u : 0u;
@@ -903,7 +913,7 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
             if (t2 > 0x7FFFFFFFull) return fail(FKB_ERR_INVALID_ARGUMENT, "plan needs more than 2^31 thread blocks");
             img.item_start[img.planes.size()] = (uint32_t)t2;
             img.total_items = (uint32_t)t2;
-            img.block_threads = BLOCK_THREADS;
+            img.block_threads = staged_threads;
             img.staged_bytes = STAGED_HEADER_BYTES + stage;
             img.early_copies = true;
             if (common_class != CLASS_MIXED) img.launch_class = common_class = img.planes[0].plane_class;
