@@ -111,13 +111,11 @@ struct LaunchArgs {
 
 constexpr int BLOCK_THREADS = 256;
 constexpr int PX_PER_THREAD = 4;
-#ifndef FKB_FLAT_QUADS_U8
-#define FKB_FLAT_QUADS_U8 4
-#endif
+constexpr int FLAT_QUADS_U8 = 4;
 /* FLAT classes: runs of four pixels per thread.  A thread has the raw words of all its runs in
  * flight before it computes the first; a uchar3 run is three words, so four runs are cheap to hold,
  * a float3 run is twelve (two runs measured slower than one: 36.9 -> 42.8 us on one 4K float3 Add). */
-__host__ __device__ constexpr int flat_quads(bool src_is_u8) { return src_is_u8 ? FKB_FLAT_QUADS_U8 : 1; }
+__host__ __device__ constexpr int flat_quads(bool src_is_u8) { return src_is_u8 ? FLAT_QUADS_U8 : 1; }
 /* FLAT classes: pixels per work item */
 __host__ __device__ constexpr int flat_item_pixels(bool src_is_u8) { return BLOCK_THREADS * PX_PER_THREAD * flat_quads(src_is_u8); }
 constexpr int ITEM_PIXELS_GENERIC = BLOCK_THREADS;
@@ -187,6 +185,15 @@ __host__ __device__
 inline ResizeTiling resize_tiling(uint32_t dst_w, uint32_t dst_h, int x1, int y1, int x2, int y2,
                                   uint32_t block_threads) {
     ResizeTiling t;
+    const uint64_t per_item = (uint64_t)block_threads * BG_GROUPS_PER_THREAD;
+    if (x2 < x1 || y2 < y1) {
+        /* An empty region (a PRESERVE_AR target that rounds to zero columns or rows, resize.h:196-221):
+           no interpolating items, every row is filled by store-only items. */
+        t.g_lo = 0; t.n_groups = 0; t.n_rows = 0; t.gw = block_threads; t.rs = 1; t.tiles_x = 1; t.tiles_y = 0;
+        t.roi_items = 0;
+        t.bg_items = (uint32_t)(((uint64_t)dst_h * (dst_w / PX_PER_THREAD) + per_item - 1) / per_item);
+        return t;
+    }
     t.g_lo = (uint32_t)x1 / PX_PER_THREAD;
     t.n_groups = (uint32_t)x2 / PX_PER_THREAD - t.g_lo + 1;
     t.n_rows = (uint32_t)(y2 - y1 + 1);
@@ -198,7 +205,6 @@ inline ResizeTiling resize_tiling(uint32_t dst_w, uint32_t dst_h, int x1, int y1
     t.tiles_y = (t.n_rows + rows - 1) / rows;
     t.roi_items = t.tiles_x * t.tiles_y;
     const uint64_t bg_groups = (uint64_t)(dst_h - t.n_rows) * (dst_w / PX_PER_THREAD);
-    const uint64_t per_item = (uint64_t)block_threads * BG_GROUPS_PER_THREAD;
     t.bg_items = (uint32_t)((bg_groups + per_item - 1) / per_item);
     return t;
 }
@@ -206,10 +212,7 @@ inline ResizeTiling resize_tiling(uint32_t dst_w, uint32_t dst_h, int x1, int y1
 /* STAGED classes: a work item is a band of `band_rows` output rows of the region of interest,
  * all columns; its source footprint (whole crop rows, widened to 16-byte boundaries) sits in
  * shared memory behind a 16-byte mbarrier slot and a table of per-row vertical taps. */
-#ifndef FKB_BAND_PIXELS
-#define FKB_BAND_PIXELS 7168
-#endif
-constexpr uint32_t STAGED_BAND_PIXELS = FKB_BAND_PIXELS; /* output pixels per band, about         */
+constexpr uint32_t STAGED_BAND_PIXELS = 7168; /* output pixels per band, about         */
 constexpr uint32_t STAGED_MAX_ROWS = 64;          /* output rows per band                        */
 constexpr uint32_t STAGED_MAX_STAGE_BYTES = 40 * 1024u; /* four blocks of it fit one SM */
 constexpr uint32_t STAGED_HEADER_BYTES = 16 + STAGED_MAX_ROWS * 32;

@@ -570,8 +570,14 @@ struct StagedTiling {
 };
 static int staged_src_row(int r, float fy) { return (int)std::floor((float)r * fy); }
 
+static bool region_empty(const DevPlane& dp) { return dp.x2 < dp.x1 || dp.y2 < dp.y1; }
+
 static StagedTiling staged_tiling(const DevPlane& dp, uint32_t block_threads) {
     StagedTiling t;
+    if (region_empty(dp)) { /* nothing to interpolate: store-only items alone */
+        t.ok = true; t.gw = block_threads; t.rs = 1;
+        return t;
+    }
     const uint32_t g_lo = (uint32_t)dp.x1 / PX_PER_THREAD;
     const uint32_t n_groups = (uint32_t)dp.x2 / PX_PER_THREAD - g_lo + 1;
     const uint32_t n_rows = (uint32_t)(dp.y2 - dp.y1 + 1);
@@ -631,6 +637,10 @@ struct Nv12Tiling {
 };
 static Nv12Tiling nv12_staged_tiling(const DevPlane& dp, uint32_t block_threads) {
     Nv12Tiling t;
+    if (region_empty(dp)) { /* nothing to interpolate: store-only items alone */
+        t.ok = true; t.gw = block_threads; t.rs = 1; t.tiles_x = 1;
+        return t;
+    }
     if ((reinterpret_cast<uintptr_t>(dp.src) % 16) != 0 || (dp.src_pitch % 16) != 0) return t;
     const uint32_t g_lo = (uint32_t)dp.x1 / PX_PER_THREAD;
     const uint32_t n_groups = (uint32_t)dp.x2 / PX_PER_THREAD - g_lo + 1;
@@ -744,8 +754,17 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
             const int rc = fkb_derive_resize(p.crop_width, p.crop_height, (int32_t)p.dst_width, (int32_t)p.dst_height, s.resize_mode, &rp);
             if (rc) return rc;
             dp.fx = rp.fx; dp.fy = rp.fy; dp.x1 = rp.x1; dp.y1 = rp.y1; dp.x2 = rp.x2; dp.y2 = rp.y2;
-            step_exp_x[p.sequence] = std::min(step_exp_x[p.sequence], std::ilogb(rp.fx));
-            step_exp_y[p.sequence] = std::min(step_exp_y[p.sequence], std::ilogb(rp.fy));
+            if (rp.target_width <= 0 || rp.target_height <= 0) {
+                /* A PRESERVE_AR target that rounds to zero columns or rows (a crop more than about
+                   2 * dst : 1 off the destination's aspect ratio): the reference's factors become
+                   infinite and its region of interest empty (resize.h:127-158), so every output
+                   element takes the default value.  The plane is lowered to store-only work; the
+                   infinite step is never used. */
+                dp.fx = dp.fy = 1.0f; dp.x1 = 0; dp.y1 = 0; dp.x2 = -1; dp.y2 = -1;
+            } else {
+                step_exp_x[p.sequence] = std::min(step_exp_x[p.sequence], std::ilogb(rp.fx));
+                step_exp_y[p.sequence] = std::min(step_exp_y[p.sequence], std::ilogb(rp.fy));
+            }
         }
 
         /* choose the body */
@@ -849,6 +868,11 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
                     continue;
                 }
                 any_resize = true;
+                if (region_empty(up)) { /* store-only plane: one "tile", never cut */
+                    cut.push_back(up);
+                    kept_items.push_back(0);
+                    continue;
+                }
                 const uint32_t px_bytes = up.plane_class == CLASS_RESIZE_U8_PLANAR ? 4u : 12u;
                 const uint32_t g_lo = (uint32_t)up.x1 / PX_PER_THREAD;
                 const uint32_t n_groups = (uint32_t)up.x2 / PX_PER_THREAD - g_lo + 1;
@@ -876,6 +900,7 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
         for (size_t i = 0; i < img.planes.size(); ++i) {
             if (kept_items[i] != 0) continue;
             const DevPlane& dp = img.planes[i];
+            if (region_empty(dp)) continue;
             const uint32_t n_groups = (uint32_t)dp.x2 / PX_PER_THREAD - (uint32_t)dp.x1 / PX_PER_THREAD + 1;
             if (n_groups * (PX_PER_THREAD / 2) > 64u) staged_threads = BLOCK_THREADS;
         }
@@ -902,7 +927,7 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
                 const uint32_t cls = dp.plane_class == CLASS_RESIZE_U8_PLANAR ? CLASS_RESIZE_U8_PLANAR_STAGED : CLASS_RESIZE_U8_PACKED_STAGED;
                 const ResizeTiling rt = resize_tiling(dp.dst_w, dp.dst_h, dp.x1, dp.y1, dp.x2, dp.y2, staged_threads);
                 const uint64_t outside_groups = (uint64_t)(dp.dst_h - (uint32_t)(dp.y2 - dp.y1 + 1)) * (dp.dst_w / PX_PER_THREAD);
-                const bool fold = outside_groups <= STAGED_FOLD_BG_GROUPS;
+                const bool fold = outside_groups <= STAGED_FOLD_BG_GROUPS && st[i].n_bands != 0;
                 dp.n_segs = fold ? 1u : 0u;
                 const uint32_t items = st[i].n_bands + (fold ? 0u : rt.bg_items);
                 dp.plane_class = cls;

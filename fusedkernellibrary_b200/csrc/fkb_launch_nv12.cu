@@ -1,0 +1,10 @@
+/* Instantiations of fused_plan_kernel for one group of plane classes (see fkb_bodies.cuh). */
+#include "fkb_bodies.cuh"
+
+namespace fkb {
+
+cudaError_t launch_nv12_staged(uint32_t chain, const LaunchArgs& a, size_t smem, cudaStream_t stream) {
+    return launch_class<CLASS_RESIZE_NV12_PACKED_STAGED>(chain, a, smem, stream);
+}
+
+}  // namespace fkb

@@ -206,6 +206,18 @@ def small_cases():
                          rects=[(0, 0, 2048, 48), (5, 3, 2043, 61), (16, 0, 520, 10)], mode=abi.RESIZE_IGNORE_AR),
         crop_resize_case("wide_packed_upscale", 68, 1, 208, 32, 2, 2052, 12, False, chains.readme_ops(),
                          rects=[(1, 1, 203, 9), (0, 0, 208, 32)], mode=abi.RESIZE_IGNORE_AR),
+        # PRESERVE_AR targets that round to zero columns or rows: the whole plane is background
+        crop_resize_case("c3_empty_regions", 69, 1, 1024, 1024, 5, 32, 32, True, chains.normalize_ops(),
+                         rects=[(0, 0, 2, 130), (0, 0, 1, 1000), (0, 0, 1000, 1), (10, 10, 100, 80), (5, 7, 3, 900)],
+                         background=(3.0, 7.0, 11.0)),
+        crop_resize_case("c3_all_empty_regions", 70, 1, 1024, 1024, 2, 224, 224, True, chains.normalize_ops(),
+                         rects=[(0, 0, 2, 1000), (0, 0, 1000, 2)], background=(3.0, 7.0, 11.0)),
+        crop_resize_case("c2_empty_regions_packed", 74, 2, 1024, 1024, 4, 60, 60, False, chains.readme_ops(),
+                         rects=[(0, 0, 1, 1024), (0, 0, 34, 25), (0, 0, 1024, 1), (40, 40, 12, 11)], background=(1.0, 2.0, 3.0)),
+        crop_resize_case("c3_empty_regions_odd_dst", 75, 1, 300, 700, 3, 45, 31, True, chains.normalize_ops(),
+                         rects=[(0, 0, 1, 700), (0, 0, 300, 2), (3, 3, 100, 100)], background=(3.0, 7.0, 11.0)),
+        nv12_case("c4_empty_regions", 48, 3, 1024, 256, 32, 32, mode=abi.RESIZE_PRESERVE_AR, background=(16.0, 128.0, 240.0),
+                  crops=[(0, 0, 2, 130), (0, 0, 1000, 2), (0, 0, 64, 64)]),
         nv12_case("c4_exact3", 41, 3, 96, 54, 32, 18),
         nv12_case("c4_fractional", 42, 2, 96, 54, 40, 22),
         nv12_case("c4_pitched", 43, 2, 98, 54, 36, 20, pitch=128),

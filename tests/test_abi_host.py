@@ -10,6 +10,7 @@ import pytest
 
 from fusedkernellibrary_b200 import abi, chains
 from fusedkernellibrary_b200.abi import op
+from tests import cases as tc
 
 ROOT = Path(__file__).resolve().parent.parent
 GOLD = Path(__file__).resolve().parent / "golden"
@@ -238,3 +239,15 @@ def test_plans_of_several_classes_stage_their_uchar3_resize_planes(fkb_lib):
     assert info.n_planes == 64 and info.n_sequences == 4 and info.n_launches == 1
     fixed = (48 + 2 * 16) * 112 + 4 * 64 + 8 * 16 + 16    # planes, sequences, operations, status
     assert info.device_bytes == fixed + 32 * info.grid_x
+
+
+def test_empty_regions_of_interest_lower_to_store_only_work(fkb_lib):
+    """Crops far off the destination's aspect ratio give PRESERVE_AR a target of zero columns or rows;
+    lowering them must neither divide by zero nor use the infinite source step."""
+    for case in (c for c in tc.small_cases() if "empty_regions" in c.name):
+        arrays = {**case.sources, **case.outputs}
+        info = abi.validate(case.build(lambda n: arrays[n].ctypes.data))
+        assert info.grid_x >= 1 and info.n_planes >= 2
+    rp = abi.ResizeParams()
+    assert fkb_lib.fkb_derive_resize(2, 130, 32, 32, abi.RESIZE_PRESERVE_AR, rp) == 0
+    assert rp.target_width == 0 and rp.x2 == rp.x1 - 1 and np.isinf(rp.fx)

@@ -159,3 +159,31 @@ def test_port_matches_reference_build_on_shared_cases(oracle_port):
         expect = ref.crop_resize_norm_planar(frames, fi, rects, dw, dh, (3.0, 5.0, 7.0), 255.0, chains.IMAGENET_MEAN,
                                              chains.IMAGENET_STD)
         assert _same(out, expect), trial
+
+
+@pytest.mark.skipif(not ref.available(), reason="oracle/_ref not built (reference tree absent)")
+def test_port_matches_reference_build_on_empty_regions(oracle_port):
+    """A PRESERVE_AR target of zero columns or rows (resize.h:196-221 rounds it down): the reference's
+    factors are infinite, its region of interest is empty, every element is the default value after
+    the continuation."""
+    rng = np.random.default_rng(6)
+    frame = rng.integers(0, 256, (1024, 1024, 3), dtype=np.uint8)
+    rects = np.array([(0, 0, 2, 130), (0, 0, 1, 1000), (0, 0, 1000, 1), (5, 7, 3, 900), (10, 10, 100, 80)], np.int32)
+    fi = [0] * len(rects)
+    for dw, dh in ((32, 32), (224, 224), (45, 31)):
+        out = np.zeros((len(rects), 3, dh, dw), np.float32)
+        plan = chains.crop_resize_batch(frame_ptrs=[frame.ctypes.data], frame_index=fi, rects=rects, src_width=1024,
+                                        src_height=1024, src_pitch=3072, dst=out.ctypes.data, dst_width=dw, dst_height=dh,
+                                        post_ops=chains.normalize_ops(), planar=True, background=(3.0, 7.0, 11.0))
+        oracle_port.run(plan)
+        expect = ref.crop_resize_norm_planar([frame], fi, rects, dw, dh, (3.0, 7.0, 11.0), 255.0, chains.IMAGENET_MEAN,
+                                             chains.IMAGENET_STD)
+        assert _same(out, expect)
+        n_empty = 0
+        for i, r in enumerate(rects):
+            rp = oracle_port.derive_resize(int(r[2]), int(r[3]), dw, dh, abi.RESIZE_PRESERVE_AR)
+            if rp.target_width == 0 or rp.target_height == 0:   # background only
+                n_empty += 1
+                for c in range(3):
+                    assert np.unique(expect[i, c]).size == 1
+        assert n_empty >= 2
