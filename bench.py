@@ -64,6 +64,11 @@ class Workload:
         """Runs the reference's CPU code on buffer set s; returns output pixels computed, or None."""
         return None
 
+    def reference_gpu(self, ptr, s: int = 0) -> bool:
+        """Enqueues the reference's own CUDA kernel(s) for buffer set s (device pointers from `ptr`) on the
+        stream given to oracle.reference_gpu.set_stream; False when the chain is not built for it."""
+        return False
+
     out_pixels = 0
     algorithmic_bytes = None   # None: what fkb_plan_get_info reports (source bytes inside the crops + output bytes)
     algorithmic_note = "source bytes inside the crop rects + output bytes"
@@ -140,6 +145,13 @@ class CropResizeNorm(Workload):
         _parallel(run, chunks, threads)
         return n * self.dw * self.dh
 
+    def reference_gpu(self, ptr, s=0):
+        from oracle import reference_gpu as rg
+        rg.crop_resize_norm_planar([ptr(f"frame{i}") for i in range(self.n_frames)], self.frame_index, self.fw, self.fh,
+                                   self.fw * 3, self.rects, self.dw, self.dh, (0, 0, 0), 255.0, chains.IMAGENET_MEAN,
+                                   chains.IMAGENET_STD, ptr("out"))
+        return True
+
 
 class ReadmeCropResize(Workload):
     """Config 2: the README chain, 5 crops of one 4K frame -> 60x60x5 packed float3.
@@ -183,6 +195,12 @@ class ReadmeCropResize(Workload):
         _parallel(run, chunks, threads)
         return n * 3600
 
+    def reference_gpu(self, ptr, s=0):
+        from oracle import reference_gpu as rg
+        rg.crop_resize_readme([ptr(f"frame{i}") for i in range(self.n_frames)], self.frame_index, self.fw, self.fh,
+                              self.fw * 3, self.rects, 60, 60, (0, 0, 0), 1.4, 0.5, 255.0, ptr("out"))
+        return True
+
 
 class VerticalFusion(Workload):
     """Config 1: PerThreadRead<uchar3> -> Cast -> Mul(1.4) -> Sub(0.5) -> Div(255) -> PerThreadWrite<float3>."""
@@ -205,6 +223,11 @@ class VerticalFusion(Workload):
         from oracle import reference as ref
         ref.cast_mul_sub_div(self.sources[s]["src"].reshape(self.h, self.w, 3), 1.4, 0.5, 255.0)
         return self.out_pixels
+
+    def reference_gpu(self, ptr, s=0):
+        from oracle import reference_gpu as rg
+        rg.cast_mul_sub_div(ptr("src"), self.w, self.h, self.w * 3, 1.4, 0.5, 255.0, ptr("out"), self.w * 12)
+        return True
 
 
 class VerticalFusionBatch(Workload):
@@ -237,6 +260,15 @@ class VerticalFusionBatch(Workload):
             ref.cast_mul_sub_div(self.sources[s][f"src{i}"].reshape(self.h, self.w, 3), 1.4, 0.5, 255.0)
         return self.out_pixels
 
+    def reference_gpu(self, ptr, s=0):
+        from oracle import reference_gpu as rg
+        if self.n % 16:
+            return False
+        for a in range(0, self.n, 16):
+            rg.cast_mul_sub_div_batch16([ptr(f"src{i}") for i in range(a, a + 16)], self.w, self.h, self.w * 3, 1.4, 0.5,
+                                        255.0, ptr("out") + a * self.w * self.h * 12)
+        return True
+
 
 class LongChain(Workload):
     """Config 5A: N alternating Add(0.001)/Mul(1.0001) on a 3840x2160 float3 image."""
@@ -260,6 +292,10 @@ class LongChain(Workload):
         from oracle import reference as ref
         ref.addmul_chain(self.sources[s]["src"].reshape(self.h, self.w, 3), self.n_ops, 0.001, 1.0001)
         return self.out_pixels
+
+    def reference_gpu(self, ptr, s=0):
+        from oracle import reference_gpu as rg
+        return rg.addmul_chain(ptr("src"), self.w, self.h, self.w * 12, self.n_ops, 0.001, 1.0001, ptr("out"), self.w * 12)
 
 
 class Nv12Resize(Workload):
@@ -299,6 +335,11 @@ class Nv12Resize(Workload):
         _parallel(run, chunks, threads)
         return n * self.dw * self.dh
 
+    def reference_gpu(self, ptr, s=0):
+        from oracle import reference_gpu as rg
+        rg.nv12_resize([ptr(f"frame{i}") for i in range(self.n)], self.w, self.h, self.w, self.dw, self.dh, 255.0, ptr("out"))
+        return True
+
 
 class Divergent(Workload):
     """Config 5B: one launch, four different chains on four groups of 16 images 1920x1080 uchar3."""
@@ -319,6 +360,19 @@ class Divergent(Workload):
         return chains.divergent_four_groups(src_ptrs=[ptr(f"img{i}") for i in range(4 * self.pg)], width=self.w,
                                             height=self.h, dst_ptrs=[ptr(f"g{g}") for g in range(4)],
                                             resize_to=(self.w // 2, self.h // 2), per_group=self.pg)
+
+    def reference_gpu(self, ptr, s=0):
+        """Four launches: the reference has no host launcher for its divergent kernel (executors.h:129-145)."""
+        from oracle import reference_gpu as rg
+        if self.pg != 16:
+            return False
+        p = [ptr(f"img{i}") for i in range(64)]
+        w, h = self.w, self.h
+        rg.cast_mul_sub_batch16(p[0:16], w, h, w * 3, 1.4, 0.5, ptr("g0"))
+        rg.cast_add_div_batch16(p[16:32], w, h, w * 3, 0.5, 255.0, ptr("g1"))
+        rg.bgr_cast_mul_saturate_batch16(p[32:48], w, h, w * 3, 1.4, ptr("g2"))
+        rg.cast_resize_batch16(p[48:64], w, h, w * 3, w // 2, h // 2, ptr("g3"))
+        return True
 
 
 def make_workload(name: str, seed: int) -> Workload:
@@ -348,6 +402,38 @@ def make_workload(name: str, seed: int) -> Workload:
 # --------------------------------------------------------------------------------------
 # helpers
 # --------------------------------------------------------------------------------------
+METRIC_NAMES = {"c3": "crop-resize-norm", "c3small": "crop-resize-norm, 256 crops", "c2": "README crop-resize",
+                "c2s": "README crop-resize, 8190 crops", "c1": "vertical fusion", "c1b": "vertical fusion, 16 images",
+                "c4": "NV12 resize", "c4small": "NV12 resize, 8 frames", "c5b": "divergent horizontal fusion"}
+
+# bytes that one launch really moves where that differs from the canonical algorithmic figure: the staged NV12
+# kernel copies only the luma and chroma rows with a non-zero tap weight (profiles/nv12_staged_c4.md)
+MOVED_BYTES_PER_OUTPUT_PIXEL = {"c4": 6.0 + 12.0, "c4small": 6.0 + 12.0}
+
+
+def metric_of(wl) -> str:
+    return f"output Mpix/s ({METRIC_NAMES.get(wl.name, 'long chain, ' + wl.name[3:] + ' ops' if wl.name.startswith('c5a') else wl.name)})"
+
+
+def working_set_bytes(wl) -> int:
+    n = 0
+    for srcs, outs in zip(wl.sources, wl.outputs):
+        n += sum(a.nbytes for a in srcs.values())
+        n += sum(int(np.prod(shape)) * np.dtype(dt).itemsize for shape, dt in outs.values())
+    return n
+
+
+def base_config(wl, world: int) -> dict:
+    """The `config` object of the JSON line: the same keys and values in both arms."""
+    ws = working_set_bytes(wl)
+    return {"workload": wl.description, "name": wl.name, "output_pixels_per_gpu_per_step": wl.out_pixels,
+            "working_set_bytes_per_gpu": ws,
+            "l2": ("inputs and outputs larger than L2" if ws > 2 * L2_BYTES
+                   else "working set below 2x L2: buffer sets rotate, numbers are L2-assisted"),
+            "sharding": "independent planes per rank, no collective",
+            "seeds": "numpy default_rng(1000 + 17 * rank)"}
+
+
 def measured_peak_gbs() -> tuple[float, str]:
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -359,47 +445,49 @@ def measured_peak_gbs() -> tuple[float, str]:
 
 
 class ClockSampler:
-    """nvidia-smi sampled every 200 ms while the timed region runs."""
+    """nvidia-smi sampled every `interval_ms` while a timed region runs."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, gpu_index: int):
+    def __init__(self, gpu_index: int, interval_ms: int = 200):
         self.gpu = gpu_index
+        self.interval_ms = interval_ms
         self.proc = None
 
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.gpu)], stdout=subprocess.PIPE,
+                                          "-lms", str(self.interval_ms), "-i", str(self.gpu)], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
 
-    def stop(self) -> dict:
+    def stop(self, settle: float = 0.25) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.25)
+        time.sleep(settle)
         self.proc.terminate()
         try:
             out, _ = self.proc.communicate(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        sm, mx, reasons = [], [], set()
+        sm, mx, pw, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in out.strip().splitlines():
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
                 continue
             try:
-                sm.append(float(f[1])); mx.append(float(f[2]))
+                sm.append(float(f[1])); mx.append(float(f[2])); pw.append(float(f[3]))
             except ValueError:
                 continue
             for nm, v in zip(names, f[5:9]):
                 if v.lower().startswith("active"):
                     reasons.add(nm)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w": float(np.median(pw)) if pw else None, "power_w_max": max(pw) if pw else None,
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
@@ -424,11 +512,12 @@ def run_reference_arm(args, rank: int):
     dt = time.perf_counter() - t0
     val = px / dt / 1e6
     line = {
-        "impl": "reference", "metric": "output Mpix/s (crop-resize-norm)", "value": val, "unit": "Mpix/s",
+        "impl": "reference", "metric": metric_of(wl), "value": val, "unit": "Mpix/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": wl.description, "note": "reference CPU backend (TransformDPP<ParArch::CPU>) compiled from "
-                   "its own headers with the device branch of interpolation.h selected; plane chunks of 16 on all host threads"},
+        "config": base_config(wl, args.gpus),
+        "note": "reference CPU backend (TransformDPP<ParArch::CPU>) compiled from its own headers with the device "
+                "branch of interpolation.h selected; plane chunks of 16 on all host threads",
         "cpu_baseline": {"value": val, "unit": "Mpix/s", "cores": threads, "kind": "reference",
                          "sample": f"the whole workload ({wl.out_pixels} output px) per step"},
         "e2e": {"value": val, "unit": "Mpix/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -440,6 +529,94 @@ def run_reference_arm(args, rank: int):
 # --------------------------------------------------------------------------------------
 # our arm (GPU)
 # --------------------------------------------------------------------------------------
+class DeviceWorkload:
+    """A workload's buffers resident on the current device, one plan per buffer set."""
+
+    def __init__(self, wl, torch):
+        self.wl = wl
+        self.sets, self.plans = [], []
+        for s in range(wl.sets):
+            d = {k: torch.from_numpy(v).cuda() for k, v in wl.sources[s].items()}
+            for k, (shape, dt) in wl.outputs[s].items():
+                d[k] = torch.zeros(shape, dtype=torch.float32 if dt == np.float32 else torch.uint8, device="cuda")
+            self.sets.append(d)
+            self.plans.append(abi.DevicePlan(wl.build(lambda n, d=d: d[n].data_ptr(), s)))
+        self.info = self.plans[0].info()
+
+    def launch(self, i, sh):
+        self.plans[i % self.wl.sets].launch(sh)
+
+    def reference_gpu(self, i):
+        d = self.sets[i % self.wl.sets]
+        return self.wl.reference_gpu(lambda n: d[n].data_ptr(), i % self.wl.sets)
+
+    def check(self, sh):
+        for p in self.plans:
+            p.check(sh)   # raises when a block gave up a bounded wait: the number would be invalid
+
+    def destroy(self):
+        for p in self.plans:
+            p.destroy()
+        self.sets = []
+
+
+def time_launches(torch, stream, fn, steps, warmup):
+    """CUDA events on `stream` around each of `steps` calls of fn(i) after `warmup` untimed ones; ms per call."""
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    ev[0].record(stream)
+    for i in range(steps):
+        fn(i)
+        ev[i + 1].record(stream)
+    torch.cuda.synchronize()
+    return [ev[i].elapsed_time(ev[i + 1]) for i in range(steps)], ev[0].elapsed_time(ev[-1])
+
+
+def reference_gpu_record(torch, stream, dw: DeviceWorkload, steps, warmup):
+    """The reference's own kernel (its headers compiled for sm_100a with nvcc's defaults) on the same device
+    buffers, same event protocol."""
+    from oracle import reference_gpu as rg
+    if not rg.available():
+        return {"unavailable": "oracle/_ref/libfklref_gpu.so was not built (reference tree absent at build time)"}
+    rg.set_stream(stream.cuda_stream)
+    if not dw.reference_gpu(0):
+        return {"unavailable": "this chain is not instantiated in the reference wrapper (nvcc cannot compile a "
+                               "256-operation chain: operate() recursion, data_parallel_patterns.h:86)"}
+    n0 = rg.launches()
+    per, total = time_launches(torch, stream, dw.reference_gpu, steps, warmup)
+    launches = (rg.launches() - n0) / (steps + warmup)
+    ms = total / steps
+    return {"ms_per_step": ms, "value": dw.wl.out_pixels / (ms * 1e-3) / 1e6, "unit": "Mpix/s",
+            "launches_per_step": launches,
+            "what": "launchTransformDPP_Kernel from the reference's headers, nvcc -O3 sm_100a, default flags; batches in "
+                    "chunks of at most 128 planes per launch (its per-plane parameters are kernel arguments)"}
+
+
+def side_workload(torch, stream, name, steps, warmup, peak):
+    """One more configuration, timed the same way (a few ms): kernel time, roofline fraction, reference kernel."""
+    wl = make_workload(name, 1000)
+    dw = DeviceWorkload(wl, torch)
+    sh = stream.cuda_stream
+    per, total = time_launches(torch, stream, lambda i: dw.launch(i, sh), steps, warmup)
+    dw.check(sh)
+    ms = float(np.mean(per))
+    alg = wl.algorithmic_bytes or dw.info.algorithmic_bytes
+    rec = {"name": wl.name, "workload": wl.description, "kernel_ms": ms, "value": wl.out_pixels / (ms * 1e-3) / 1e6,
+           "unit": "Mpix/s", "algorithmic_bytes": alg, "achieved_gbs": alg / (ms * 1e-3) / 1e9,
+           "frac": alg / (ms * 1e-3) / 1e9 / peak, "grid": dw.info.grid_x, "block": dw.info.block_x}
+    if wl.name in MOVED_BYTES_PER_OUTPUT_PIXEL:
+        moved = MOVED_BYTES_PER_OUTPUT_PIXEL[wl.name] * wl.out_pixels
+        rec["moved_bytes"] = moved
+        rec["frac_of_moved_bytes"] = moved / (ms * 1e-3) / 1e9 / peak
+    rec["reference_gpu"] = reference_gpu_record(torch, stream, dw, steps, warmup)
+    dw.destroy()
+    del dw, wl
+    torch.cuda.empty_cache()
+    return rec
+
+
 def run_ours(args, rank: int, world: int, local_rank: int):
     import torch
     import torch.distributed as dist
@@ -454,31 +631,24 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     wl = make_workload(args.workload, 1000 + 17 * rank)
     stream = torch.cuda.Stream()
     sh = stream.cuda_stream
-
-    # device-resident buffers and plans (one per buffer set)
-    dev_sets, plans = [], []
-    for s in range(wl.sets):
-        d = {k: torch.from_numpy(v).cuda() for k, v in wl.sources[s].items()}
-        for k, (shape, dt) in wl.outputs[s].items():
-            d[k] = torch.zeros(shape, dtype=torch.float32 if dt == np.float32 else torch.uint8, device="cuda")
-        dev_sets.append(d)
-        plans.append(abi.DevicePlan(wl.build(lambda n, d=d: d[n].data_ptr(), s)))
-    info = plans[0].info()
-    ws_bytes = sum(t.numel() * t.element_size() for d in dev_sets for t in d.values())
-    l2_note = ("inputs and outputs larger than L2" if ws_bytes > 2 * L2_BYTES
-               else "working set below 2x L2: numbers are L2-assisted")
+    dw = DeviceWorkload(wl, torch)
+    info = dw.info
+    warmup = max(args.warmup, 3)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def launch(i):
-        plans[i % wl.sets].launch(sh)
+    def max_over_ranks(x: float) -> float:
+        t = torch.tensor([x], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
 
     with torch.cuda.stream(stream):
-        for i in range(max(args.warmup, 3)):
-            launch(i)
+        for i in range(warmup):
+            dw.launch(i, sh)
         barrier()
         sampler = ClockSampler(local_rank)
         if rank == 0:
@@ -488,19 +658,43 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         barrier()
         ev[0].record(stream)
         for i in range(args.steps):
-            launch(i)
+            dw.launch(i, sh)
             ev[i + 1].record(stream)
         barrier()
         total_ms = ev[0].elapsed_time(ev[-1])
         per_launch_ms = [ev[i].elapsed_time(ev[i + 1]) for i in range(args.steps)]
         clocks = sampler.stop() if rank == 0 else None
+        dw.check(sh)
 
-    t = torch.tensor([total_ms], dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    max_ms = float(t.item())
+        # --- sustained: launches back to back for at least a second, clocks and power sampled inside -------
+        sustained = None
+        if not args.no_sustained:
+            n = max(args.steps, int(1.2e3 / max(float(np.mean(per_launch_ms)), 1e-3)) + 1)
+            barrier()
+            s2 = ClockSampler(local_rank, interval_ms=100)
+            if rank == 0:
+                s2.start()
+                time.sleep(0.15)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            for i in range(n):
+                dw.launch(i, sh)
+            b.record(stream)
+            torch.cuda.synchronize()
+            c2 = s2.stop(settle=0.0) if rank == 0 else None
+            sus_ms = max_over_ranks(a.elapsed_time(b)) / n
+            dw.check(sh)
+            if rank == 0:
+                sustained = {"launches": n, "seconds": sus_ms * n * 1e-3, "ms_per_launch": sus_ms,
+                             "value": wl.out_pixels * world / (sus_ms * 1e-3) / 1e6, "unit": "Mpix/s",
+                             "sm_mhz_median": c2["sm_mhz"], "power_w_median": c2["power_w"], "power_w_max": c2["power_w_max"],
+                             "clock_samples": c2["samples"], "reasons": c2["reasons"],
+                             "ms_x_mhz": sus_ms * c2["sm_mhz"] if c2["sm_mhz"] else None}
+
+    max_ms = max_over_ranks(total_ms)
     value = wl.out_pixels * world * args.steps / (max_ms * 1e-3) / 1e6
     kernel_ms = float(np.mean(per_launch_ms))
+    peak, peak_kind = measured_peak_gbs()
 
     # --- end to end through the host-buffer C-ABI call (pinned host buffers) ---------------
     e2e = None
@@ -510,56 +704,144 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             host[k] = torch.zeros(shape, dtype=torch.float32 if dt == np.float32 else torch.uint8).pin_memory()
         sess = abi.HostSession(wl.build(lambda n: host[n].data_ptr(), 0))
         h2d, d2h = sess.traffic()
-        e_steps = max(2, min(args.steps, 5))
-        sess.run(sh)
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(e_steps):
-            sess.run(sh)   # returns after the stream has been synchronised
-        e1.record(stream)
-        torch.cuda.synchronize()
-        e_dt = e0.elapsed_time(e1) * 1e-3
-        te = torch.tensor([e_dt], dtype=torch.float64, device="cuda")
-        if world > 1:
-            dist.all_reduce(te, op=dist.ReduceOp.MAX)
-        e2e = {"value": wl.out_pixels * world * e_steps / float(te.item()) / 1e6, "unit": "Mpix/s",
+        e_steps = max(20, args.steps)
+        with torch.cuda.stream(stream):
+            for _ in range(2):
+                sess.run(sh)
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(e_steps):
+                sess.run(sh)   # returns after the stream has been synchronised
+            e1.record(stream)
+            torch.cuda.synchronize()
+        e_dt = max_over_ranks(e0.elapsed_time(e1) * 1e-3)
+        e2e = {"value": wl.out_pixels * world * e_steps / e_dt / 1e6, "unit": "Mpix/s",
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e_steps,
-               "ms_per_step": float(te.item()) / e_steps * 1e3,
+               "ms_per_step": e_dt / e_steps * 1e3,
                "api": "fkb_host_session_run (pinned host buffers; H2D + kernel + D2H + sync per step)"}
         sess.destroy()
+        # the ceiling of that call on this box: the same bytes as plain pinned copies, both directions at
+        # once on two streams, by the same ranks at the same time, no kernel
+        d_in = torch.empty(h2d, dtype=torch.uint8, device="cuda")
+        d_out = torch.empty(d2h, dtype=torch.uint8, device="cuda")
+        h_in = torch.empty(h2d, dtype=torch.uint8).pin_memory()
+        h_out = torch.empty(d2h, dtype=torch.uint8).pin_memory()
+        s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
 
-    # --- CPU baseline: the reference's own CPU code, one core, bounded sample -----------------
-    cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu:
-        cpu = cpu_baseline(wl)
+        def copies():
+            with torch.cuda.stream(s_in):
+                d_in.copy_(h_in, non_blocking=True)
+            with torch.cuda.stream(s_out):
+                h_out.copy_(d_out, non_blocking=True)
+            s_in.synchronize(); s_out.synchronize()
+
+        copies()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(e_steps):
+            copies()
+        c_dt = max_over_ranks(time.perf_counter() - t0)
+        e2e["copy_ceiling"] = {"ms_per_step": c_dt / e_steps * 1e3,
+                               "value": wl.out_pixels * world * e_steps / c_dt / 1e6, "unit": "Mpix/s",
+                               "gbs_all_ranks": (h2d + d2h) * world * e_steps / c_dt / 1e9,
+                               "what": "cudaMemcpyAsync of the same h2d and d2h bytes from and to pinned memory on two "
+                                       "streams, every rank at once, no kernel"}
+        del d_in, d_out, h_in, h_out, host
+
+    # --- strong scaling of ONE fixed batch split over the ranks, and the consolidated output -------------
+    strong = None
+    if world > 1 and isinstance(wl, CropResizeNorm) and not args.no_strong:
+        strong = strong_scaling(torch, dist, stream, rank, world, args.steps, warmup, max_over_ranks, barrier)
+
+    # --- the reference's own kernel on this GPU, the other configurations, the CPU baseline ----------------
+    ref_gpu = others = cpu = None
+    if rank == 0 and world == 1:
+        with torch.cuda.stream(stream):
+            if not args.no_reference_gpu:
+                ref_gpu = reference_gpu_record(torch, stream, dw, args.steps, warmup)
+            if not args.no_others and args.workload == "c3":
+                dw.destroy()
+                others = [side_workload(torch, stream, n, 20, 3, peak) for n in ("c2s", "c2", "c4", "c5b", "c1b", "c1", "c5a16")]
+        if not args.no_cpu:
+            cpu = cpu_baseline(wl)
 
     if rank == 0:
-        peak, peak_kind = measured_peak_gbs()
         alg_bytes = wl.algorithmic_bytes or info.algorithmic_bytes
         achieved = alg_bytes / (kernel_ms * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                    "traffic": TRAFFIC_BYTES_PER_LAUNCH.get(wl.name), "peak_kind": f"of {peak_kind}",
+                    "algorithmic_bytes_per_launch": alg_bytes, "algorithmic_bytes_are": wl.algorithmic_note,
+                    "kernel_ms": kernel_ms, "frac_of_nominal_8TBs": achieved / 8000.0}
+        if wl.name in MOVED_BYTES_PER_OUTPUT_PIXEL:
+            moved = MOVED_BYTES_PER_OUTPUT_PIXEL[wl.name] * wl.out_pixels
+            roofline["moved_bytes_per_launch"] = moved
+            roofline["frac_of_moved_bytes"] = moved / (kernel_ms * 1e-3) / 1e9 / peak
         line = {
-            "metric": "output Mpix/s (crop-resize-norm)", "value": value, "unit": "Mpix/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": max_ms / args.steps,
+            "metric": metric_of(wl), "value": value, "unit": "Mpix/s", "n_gpus": world,
+            "steps": args.steps, "warmup": warmup, "ms_per_step": max_ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": wl.description, "planes_per_gpu": info.n_planes, "l2": l2_note,
-                       "working_set_bytes_per_gpu": ws_bytes, "sharding": "independent planes per rank, no collective",
-                       "grid": info.grid_x, "block": info.block_x},
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": TRAFFIC_BYTES_PER_LAUNCH.get(wl.name), "peak_kind": f"of {peak_kind}",
-                         "algorithmic_bytes_per_launch": alg_bytes, "algorithmic_bytes_are": wl.algorithmic_note,
-                         "kernel_ms": kernel_ms,
-                         "frac_of_nominal_8TBs": achieved / 8000.0},
+            "config": base_config(wl, world),
+            "launch": {"planes_per_gpu": info.n_planes, "grid": info.grid_x, "block": info.block_x},
+            "roofline": roofline,
+            "sustained": sustained,
             "cpu_baseline": cpu,
+            "reference_gpu": ref_gpu,
             "e2e": e2e,
+            "strong": strong,
+            "other_workloads": others,
             "gpu_launches": args.steps,
             "clocks": clocks,
         }
         print(json.dumps(line))
-    for p in plans:
-        p.destroy()
+    dw.destroy()
     if world > 1:
         dist.destroy_process_group()
+
+
+def strong_scaling(torch, dist, stream, rank, world, steps, warmup, max_over_ranks, barrier):
+    """The fixed 1024-crop batch (the same on every rank: seed 1000) split by contiguous plane ranges: each
+    rank computes its planes straight into its slab of a whole-batch tensor; with `gather` the slabs are
+    then exchanged by one NCCL all-gather so that every GPU holds the consolidated tensor."""
+    from fusedkernellibrary_b200 import sharding
+    wl = CropResizeNorm(1000)
+    first, count = sharding.plane_range(wl.n, world, rank)
+    d = {k: torch.from_numpy(v).cuda() for k, v in wl.sources[0].items()}
+    out = torch.zeros((wl.n, 3, wl.dh, wl.dw), dtype=torch.float32, device="cuda")
+    d["out"] = out
+    plan = abi.DevicePlan(wl.build(lambda n: d[n].data_ptr(), 0, first=first, count=count))
+    sh = stream.cuda_stream
+    equal = wl.n % world == 0
+    slab = out[first:first + count]
+    rec = {}
+    with torch.cuda.stream(stream):
+        for gather in (False, True):
+            if gather and not equal:
+                break
+
+            def step():
+                plan.launch(sh)
+                if gather:
+                    dist.all_gather_into_tensor(out, slab)
+
+            for _ in range(warmup):
+                step()
+            barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            for _ in range(steps):
+                step()
+            b.record(stream)
+            barrier()
+            ms = max_over_ranks(a.elapsed_time(b)) / steps
+            plan.check(sh)
+            rec["gather" if gather else "compute"] = {"ms_per_step": ms, "value": wl.out_pixels / (ms * 1e-3) / 1e6, "unit": "Mpix/s"}
+    plan.destroy()
+    rec["what"] = (f"one batch of {wl.n} crops split over {world} GPUs by contiguous plane ranges ({count} planes on this "
+                   "rank), device-timed first launch to last completion, max over ranks; gather = the same plus one "
+                   "ncclAllGather of the slabs into a consolidated tensor on every GPU")
+    rec["scaling"] = "strong"
+    return rec
 
 
 def cpu_baseline(wl: Workload):
@@ -604,7 +886,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-sustained", action="store_true")
+    ap.add_argument("--no-reference-gpu", action="store_true")
+    ap.add_argument("--no-others", action="store_true")
+    ap.add_argument("--no-strong", action="store_true")
+    ap.add_argument("--kernel-only", action="store_true", help="the timed region alone (for profiler runs)")
     args = ap.parse_args()
+    if args.kernel_only:
+        args.no_e2e = args.no_cpu = args.no_sustained = args.no_reference_gpu = args.no_others = args.no_strong = True
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

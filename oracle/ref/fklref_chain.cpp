@@ -1,4 +1,4 @@
-/* extern "C" entry points around the UNMODIFIED reference headers (CPU backend).
+/* extern "C" entry points around the UNMODIFIED reference headers (CPU backend; CUDA backend with -DFKLREF_GPU).
  *
  * TEST INFRASTRUCTURE ONLY.  Compiled by oracle/Makefile against the reference's include
  * tree where it lies (never copied); the shared objects go to oracle/_ref/.  Only tests,
@@ -25,7 +25,7 @@ namespace {
 template <size_t... I>
 void addmul_pairs(std::index_sequence<I...>, bool trailing_add, const float* src, int w, int h, int spitch,
                   const float* addv, const float* mulv, float* dst, int dpitch) {
-    CpuStream stream;
+    RefStream stream = make_stream();
     const auto read = PerThreadRead<ND::_2D, float3>::build(raw_f32x3(src, w, h, spitch));
     const auto add = Add<float3>::build(f3(addv));
     const auto mul = Mul<float3>::build(f3(mulv));
@@ -33,13 +33,13 @@ void addmul_pairs(std::index_sequence<I...>, bool trailing_add, const float* src
     if (trailing_add) {
         const auto all = std::tuple_cat(std::make_tuple(read), ((void)I, std::make_tuple(add, mul))...,
                                         std::make_tuple(add, write));
-        std::apply([&](const auto&... iops) { executeOperations<CpuDPP>(stream, iops...); }, all);
+        std::apply([&](const auto&... iops) { executeOperations<RefDPP>(stream, iops...); }, all);
     } else {
         const auto all = std::tuple_cat(std::make_tuple(read), ((void)I, std::make_tuple(add, mul))...,
                                         std::make_tuple(write));
-        std::apply([&](const auto&... iops) { executeOperations<CpuDPP>(stream, iops...); }, all);
+        std::apply([&](const auto&... iops) { executeOperations<RefDPP>(stream, iops...); }, all);
     }
-    stream.sync();
+    finish(stream);
 }
 
 template <int N>
@@ -53,8 +53,8 @@ void addmul_chain(const float* src, int w, int h, int spitch, const float* addv,
 extern "C" {
 
 /* PerThreadRead<float3> -> n alternating Add(add)/Mul(mul) (Add first) -> PerThreadWrite<float3>.
-   n must be one of 1, 2, 3, 16, 64, 256; returns 0 on success, -1 for another n. */
-int fklref_addmul_chain(const float* src, int w, int h, int spitch, int n, const float* addv, const float* mulv,
+   n must be one of 1, 2, 3, 16, 64, 256 (256: CPU build only); returns 0 on success, -1 for another n. */
+int FKLREF_FN(addmul_chain)(const float* src, int w, int h, int spitch, int n, const float* addv, const float* mulv,
                         float* dst, int dpitch) {
     switch (n) {
         case 1: addmul_chain<1>(src, w, h, spitch, addv, mulv, dst, dpitch); return 0;
@@ -62,7 +62,9 @@ int fklref_addmul_chain(const float* src, int w, int h, int spitch, int n, const
         case 3: addmul_chain<3>(src, w, h, spitch, addv, mulv, dst, dpitch); return 0;
         case 16: addmul_chain<16>(src, w, h, spitch, addv, mulv, dst, dpitch); return 0;
         case 64: addmul_chain<64>(src, w, h, spitch, addv, mulv, dst, dpitch); return 0;
+#ifndef FKLREF_GPU /* nvcc cannot deduce operate()'s return type at this recursion depth (data_parallel_patterns.h:86) */
         case 256: addmul_chain<256>(src, w, h, spitch, addv, mulv, dst, dpitch); return 0;
+#endif
         default: return -1;
     }
 }

@@ -1,4 +1,4 @@
-/* extern "C" entry points around the UNMODIFIED reference headers (CPU backend).
+/* extern "C" entry points around the UNMODIFIED reference headers.
  *
  * TEST INFRASTRUCTURE ONLY.  Compiled by oracle/Makefile against the reference's include
  * tree where it lies (never copied); the shared objects go to oracle/_ref/.  Only tests,
@@ -9,6 +9,13 @@
  * (Op::build(...).then(...)), closes it with a receiver and runs it with
  * fk::executeOperations<TransformDPP<ParArch::CPU>> (fused_kernel.h:22-25,
  * core/execution_model/executors.h:147-173, data_parallel_patterns.h:272-299).
+ *
+ * The same sources are also compiled by nvcc with -DFKLREF_GPU: the chains then run on the
+ * reference's own CUDA backend (TransformDPP<ParArch::GPU_NVIDIA>, executors.h:252-287,
+ * executor_details/executor_kernels.h:25-29), every pointer is a device pointer, the entry points
+ * are named fklref_gpu_* and return after the launch without synchronising, on the stream given
+ * to fklref_gpu_set_stream.  That build is the reference's kernel on this GPU: a second checker
+ * and the GPU baseline the benchmark reports.
  */
 #ifndef FKLREF_COMMON_H
 #define FKLREF_COMMON_H
@@ -24,8 +31,30 @@ using namespace fk;
 
 namespace fklref {
 
-using CpuDPP = TransformDPP<ParArch::CPU>;
-using CpuStream = Stream_<ParArch::CPU>;
+#ifdef FKLREF_GPU
+using RefDPP = TransformDPP<ParArch::GPU_NVIDIA>;
+using RefStream = Stream_<ParArch::GPU_NVIDIA>;
+constexpr MemType REF_MEM = MemType::Device;
+/* the stream and the launch counter of the calling thread (fklref_elementwise.cpp) */
+cudaStream_t& current_stream();
+long& launch_counter();
+inline RefStream make_stream() { ++launch_counter(); return RefStream(current_stream()); }
+inline void finish(RefStream&) {} /* asynchronous: the caller times and synchronises */
+#define FKLREF_FN(name) fklref_gpu_##name
+/* planes per launch: the per-plane parameters travel in the kernel arguments (batch_operations.h:98-102),
+   and about 136 bytes per plane fit the 32764-byte argument space 128 at a time */
+#ifndef FKLREF_BIG_CHUNK
+#define FKLREF_BIG_CHUNK 128
+#endif
+#else
+using RefDPP = TransformDPP<ParArch::CPU>;
+using RefStream = Stream_<ParArch::CPU>;
+constexpr MemType REF_MEM = MemType::Host;
+inline RefStream make_stream() { return RefStream(); }
+inline void finish(RefStream& s) { s.sync(); }
+#define FKLREF_FN(name) fklref_##name
+#define FKLREF_BIG_CHUNK 16
+#endif
 
 constexpr auto LINEAR = InterpolationType::INTER_LINEAR;
 

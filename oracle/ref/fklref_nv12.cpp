@@ -1,4 +1,4 @@
-/* extern "C" entry points around the UNMODIFIED reference headers (CPU backend).
+/* extern "C" entry points around the UNMODIFIED reference headers (CPU backend; CUDA backend with -DFKLREF_GPU).
  *
  * TEST INFRASTRUCTURE ONLY.  Compiled by oracle/Makefile against the reference's include
  * tree where it lies (never copied); the shared objects go to oracle/_ref/.  Only tests,
@@ -19,13 +19,13 @@ namespace {
 template <size_t B>
 void nv12_chunk(const uint8_t* const* frames, int w, int h, int pitch, int dw, int dh, const float* div,
                 float* out) {
-    CpuStream stream;
+    RefStream stream = make_stream();
     using Img = Image<PixelFormat::NV12>;
     /* Wrap each frame as a view whose data height equals the image height so that the chroma
        plane is addressed at data + pitch*h (color_conversion.h:336-341, image.h:35-38). */
     auto make = [&](size_t i) {
         Ptr<ND::_2D, uchar> view(const_cast<uint8_t*>(frames[i]), PtrDims<ND::_2D>((uint)w, (uint)h, (uint)pitch),
-                                 MemType::Host, 0);
+                                 REF_MEM, 0);
         return Img(view, (uint)w, (uint)h);
     };
     std::array<Img, B> imgs = [&]<size_t... I>(std::index_sequence<I...>) {
@@ -37,8 +37,8 @@ void nv12_chunk(const uint8_t* const* frames, int w, int h, int pitch, int dw, i
             .then(Resize<LINEAR>::build(Size(dw, dh)))
             .then(Div<float3>::build(f3(div)));
     const auto receiver = TensorWrite<float3>::build(raw_tensor<float3>(out, dw, dh, (int)B, 1));
-    executeOperations<CpuDPP>(stream, sender, receiver);
-    stream.sync();
+    executeOperations<RefDPP>(stream, sender, receiver);
+    finish(stream);
 }
 
 }  // namespace
@@ -47,21 +47,26 @@ extern "C" {
 
 /* ReadYUV<NV12>[B] -> ConvertYUVToRGB<NV12,Full,bt709,false,float3> -> Resize<INTER_LINEAR>(dw,dh) -> Div
    -> TensorWrite<float3> (dw x dh x B).  Each frame: h rows of luma then h/2 rows of interleaved chroma, one pitch. */
-void fklref_nv12_resize(const uint8_t* const* frames, int w, int h, int pitch, int batch, int dw, int dh,
+void FKLREF_FN(nv12_resize)(const uint8_t* const* frames, int w, int h, int pitch, int batch, int dw, int dh,
                         const float* div, float* out) {
     const size_t plane_floats = (size_t)dw * dh * 3;
     int i = 0;
+#ifdef FKLREF_GPU
+    for (; i + 32 <= batch; i += 32) nv12_chunk<32>(frames + i, w, h, pitch, dw, dh, div, out + plane_floats * i);
+#endif
     for (; i + 4 <= batch; i += 4) nv12_chunk<4>(frames + i, w, h, pitch, dw, dh, div, out + plane_floats * i);
     for (; i + 2 <= batch; i += 2) nv12_chunk<2>(frames + i, w, h, pitch, dw, dh, div, out + plane_floats * i);
     if (i < batch) {
         if (batch >= 2) {
             nv12_chunk<2>(frames + batch - 2, w, h, pitch, dw, dh, div, out + plane_floats * (batch - 2));
         } else {
+#ifndef FKLREF_GPU
             const uint8_t* two[2] = {frames[0], frames[0]};
             float* scratch = new float[plane_floats * 2];
             nv12_chunk<2>(two, w, h, pitch, dw, dh, div, scratch);
             std::memcpy(out, scratch, plane_floats * sizeof(float));
             delete[] scratch;
+#endif
         }
     }
 }
