@@ -24,10 +24,13 @@ ERR_DEVICE_WAIT = 6
 
 # vocabulary ---------------------------------------------------------------------------
 SRC_U8X3, SRC_F32X3, SRC_NV12 = 1, 2, 3
-DST_F32X3_PACKED, DST_F32_PLANAR3, DST_U8X3_PACKED = 1, 2, 3
+DST_F32X3_PACKED, DST_F32_PLANAR3, DST_U8X3_PACKED, DST_I32X3_PACKED, DST_U32X3_PACKED = 1, 2, 3, 4, 5
 RESIZE_NONE, RESIZE_IGNORE_AR, RESIZE_PRESERVE_AR = 0, 1, 2
 (OP_MUL, OP_SUB, OP_DIV, OP_ADD, OP_CAST_F32, OP_SWAP_RB, OP_SATURATE_CAST_U8,
- OP_YUV_TO_RGB_BT709_FULL) = range(1, 9)
+ OP_YUV_TO_RGB_BT709_FULL, OP_CAST_I32, OP_CAST_U32) = range(1, 11)
+PLAN_WAIT_LIMIT_US, PLAN_TEST_EXPECT_EXTRA_BYTES = 1, 2
+DEFAULT_WAIT_LIMIT_US = 100000
+ASYNC_ARENA_BYTES = 8 * 1024 * 1024
 
 
 class Op(C.Structure):
@@ -98,6 +101,11 @@ class PlanInfo(C.Structure):
         ("compiled_chain", C.c_int32),
         ("reserved", C.c_int32),
     ]
+
+
+class DebugCounters(C.Structure):
+    _fields_ = [("device_allocations", C.c_uint64), ("device_frees", C.c_uint64), ("host_pinned_allocations", C.c_uint64),
+                ("plans_lowered", C.c_uint64), ("plans_reused", C.c_uint64)]
 
 
 def op(opcode: int, p=(0.0, 0.0, 0.0)) -> Op:
@@ -180,7 +188,8 @@ EXPORTS = [
     "fkb_reference_block_size", "fkb_plan_create", "fkb_plan_validate", "fkb_plan_launch", "fkb_plan_get_info",
     "fkb_plan_get_resize_params", "fkb_plan_destroy", "fkb_execute", "fkb_host_session_create",
     "fkb_host_session_run", "fkb_host_session_get_traffic", "fkb_host_session_destroy",
-    "fkb_execute_host", "fkb_execute_static", "fkb_plan_check",
+    "fkb_execute_host", "fkb_execute_static", "fkb_plan_check", "fkb_plan_set_option", "fkb_execute_async",
+    "fkb_async_check", "fkb_debug_get_counters",
 ]
 
 
@@ -209,6 +218,10 @@ def load_library(path: os.PathLike | None = None) -> C.CDLL:
     lib.fkb_plan_get_resize_params.argtypes = [C.c_void_p, C.c_int32, C.POINTER(ResizeParams)]
     lib.fkb_plan_destroy.argtypes = [C.c_void_p]
     lib.fkb_plan_check.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_uint32)]
+    lib.fkb_plan_set_option.argtypes = [C.c_void_p, C.c_int, C.c_uint32]
+    lib.fkb_execute_async.argtypes = [C.POINTER(PlanDesc), C.c_void_p]
+    lib.fkb_async_check.argtypes = [C.c_void_p, C.POINTER(C.c_uint32)]
+    lib.fkb_debug_get_counters.argtypes = [C.POINTER(DebugCounters)]
     lib.fkb_execute.argtypes = [C.POINTER(PlanDesc), C.c_void_p]
     lib.fkb_execute_host.argtypes = [C.POINTER(PlanDesc), C.c_void_p]
     lib.fkb_execute_static.argtypes = [C.POINTER(PlanDesc), C.c_void_p]
@@ -246,6 +259,9 @@ class DevicePlan:
         st = C.c_uint32()
         check(self._lib.fkb_plan_check(self._h, C.c_void_p(stream or 0), C.byref(st)), "fkb_plan_check")
         return st.value
+
+    def set_option(self, option: int, value: int) -> None:
+        check(self._lib.fkb_plan_set_option(self._h, option, value), "fkb_plan_set_option")
 
     def info(self) -> PlanInfo:
         info = PlanInfo()
@@ -289,6 +305,28 @@ def execute_host(host_plan: HostPlan, stream: int | None = None) -> None:
     lib = load_library()
     desc = host_plan.desc()
     check(lib.fkb_execute_host(C.byref(desc), C.c_void_p(stream or 0)), "fkb_execute_host")
+
+
+def execute_async(host_plan: HostPlan, stream: int | None = None) -> None:
+    """fkb_execute_async: lower, one stream-ordered table copy from the library's pinned arena, launch; returns
+    without synchronising."""
+    lib = load_library()
+    desc = host_plan.desc()
+    check(lib.fkb_execute_async(C.byref(desc), C.c_void_p(stream or 0)), "fkb_execute_async")
+
+
+def async_check(stream: int | None = None) -> int:
+    """Synchronises `stream`; raises FkbError(ERR_DEVICE_WAIT) if an asynchronous launch gave up a wait."""
+    lib = load_library()
+    st = C.c_uint32()
+    check(lib.fkb_async_check(C.c_void_p(stream or 0), C.byref(st)), "fkb_async_check")
+    return st.value
+
+
+def debug_counters() -> DebugCounters:
+    c = DebugCounters()
+    load_library().fkb_debug_get_counters(C.byref(c))
+    return c
 
 
 STATIC_TABLE_BYTES = 512 * 1024

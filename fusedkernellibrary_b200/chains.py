@@ -23,7 +23,7 @@ def elementwise(ops, *, src, dst, width, height, src_format=SRC_U8X3, dst_format
                 src_pitch=None, dst_pitch=None, plan=None, crop=None):
     """Read -> ops -> PerThreadWrite on one image (no geometry stage)."""
     spx = {SRC_U8X3: 3, SRC_F32X3: 12}[src_format]
-    dpx = {DST_F32X3_PACKED: 12, DST_U8X3_PACKED: 3}[dst_format]
+    dpx = 3 if dst_format == DST_U8X3_PACKED else 12   # float3, int3 and uint3 pixels are twelve bytes
     plan = plan or abi.HostPlan()
     seq = plan.add_sequence(src_format, dst_format, RESIZE_NONE, list(ops))
     cw, ch = (crop[2], crop[3]) if crop is not None else (width, height)

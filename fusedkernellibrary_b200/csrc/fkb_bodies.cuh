@@ -130,6 +130,16 @@ __device__ __forceinline__ void expand_op(const uint4 g, OpSlot* slot) {
    operation's slot (and s[1] the second slot of a two-slot operation). */
 template <int CODE, int NPAIR>
 __device__ __forceinline__ void apply_one(float2 (&v)[NPAIR * 3], const OpSlot* __restrict__ s, const float2 one) {
+    if (CODE == CH_CASTI || CODE == CH_CASTU) {
+        /* Cast<float3,int3> / Cast<float3,uint3>: static_cast truncates toward zero (cast_base.h:20-30); the
+           integer travels on as a bit pattern in the same registers and is stored as it is */
+#pragma unroll
+        for (int k = 0; k < NPAIR * 3; ++k) {
+            if (CODE == CH_CASTI) v[k] = make_float2(__int_as_float(__float2int_rz(v[k].x)), __int_as_float(__float2int_rz(v[k].y)));
+            else v[k] = make_float2(__uint_as_float(__float2uint_rz(v[k].x)), __uint_as_float(__float2uint_rz(v[k].y)));
+        }
+        return;
+    }
     if (CODE == CH_SWAP || CODE == CH_SAT || CODE == CH_YUV) {
 #pragma unroll
         for (int j = 0; j < NPAIR; ++j) {
@@ -233,6 +243,8 @@ __device__ __forceinline__ void interpret_ops(float2 (&v)[NPAIR * 3], const OpSl
             case FKB_OP_SWAP_RB: apply_one<CH_SWAP, NPAIR>(v, sops + k, one); break;
             case FKB_OP_SATURATE_CAST_U8: apply_one<CH_SAT, NPAIR>(v, sops + k, one); break;
             case FKB_OP_YUV_TO_RGB_BT709_FULL: apply_one<CH_YUV, NPAIR>(v, sops + k, one); break;
+            case FKB_OP_CAST_I32: apply_one<CH_CASTI, NPAIR>(v, sops + k, one); break;
+            case FKB_OP_CAST_U32: apply_one<CH_CASTU, NPAIR>(v, sops + k, one); break;
             default: break;
         }
     }
@@ -779,13 +791,31 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t mbar, uint32_t parity) {
         : "memory");
     return done != 0;
 }
-/* Waits for phase `parity` with an iteration limit (each try_wait itself blocks for a
-   hardware-defined time slice); false when the limit ran out. */
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t mbar, uint32_t parity) {
-    for (uint32_t i = 0; i < STAGED_WAIT_LIMIT; ++i)
-        if (mbar_try_wait(mbar, parity)) return true;
-    return false;
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
 }
+/* Waits for phase `parity` for at most `limit_us` microseconds of the GPU's global timer (each
+   try_wait itself suspends the warp for a hardware-defined slice, far below a microsecond
+   limit's resolution); false when the time ran out.  The clock is read only once a first
+   attempt has failed. */
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t mbar, uint32_t parity, uint32_t limit_us) {
+    if (mbar_try_wait(mbar, parity)) return true;
+    const uint64_t t0 = global_timer_ns(), limit = (uint64_t)limit_us * 1000ull;
+    do {
+        if (mbar_try_wait(mbar, parity)) return true;
+    } while (global_timer_ns() - t0 < limit);
+    return mbar_try_wait(mbar, parity);
+}
+
+/* What a body needs to bound its wait: the plan's status word, the limit, and the test-only
+   surplus of expected bytes. */
+struct WaitCtl {
+    uint32_t* status;
+    uint32_t limit_us;
+    uint32_t test_extra_bytes;
+};
 
 /* A work item is a band of STAGED rows of one plane's region of interest, all columns.  The rows
  * of the crop that the band's taps touch are copied into shared memory by bulk copies (one per
@@ -794,7 +824,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t mbar, uint32_t parity
  * memory.  Vertical tap positions and weights are computed once per row of the band. */
 template <uint32_t CHAIN, bool PLANAR>
 __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevSeq& S, const OpSlot* sops, uint32_t local,
-                                                   unsigned char* staged_mem, uint32_t* status) {
+                                                   unsigned char* staged_mem, const WaitCtl wc) {
     uint8_t* const dst = P.dst;
     const uint32_t dst_pitch = P.dst_pitch, dst_cstride = P.dst_cstride;
     const uint32_t groups_per_row = P.dst_w / PX_PER_THREAD;
@@ -874,12 +904,12 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
     const uint32_t second_b = axb.i1 == axb.i0 ? 0x3210u : 0x3543u;
     const float2 wx0 = make_float2(axa.w0, axb.w0), wx1 = make_float2(axa.w1, axb.w1);
 
-    const bool arrived = mbar_wait_bounded(mbar, 0);
+    const bool arrived = mbar_wait_bounded(mbar, 0, wc.limit_us);
     if (!arrived) {
         /* never expected: record it and give the copies one more bounded chance to land before
            this block's shared memory is released */
-        atomicExch(status, STATUS_STAGED_WAIT_TIMEOUT);
-        (void)mbar_wait_bounded(mbar, 0);
+        atomicExch(wc.status, STATUS_STAGED_WAIT_TIMEOUT);
+        (void)mbar_wait_bounded(mbar, 0, wc.limit_us);
         return;
     }
 
@@ -1014,7 +1044,7 @@ __device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
  * to a sum whose first term is never -0, so it is skipped without changing a bit. */
 template <uint32_t CHAIN>
 __device__ __forceinline__ void body_nv12_staged(const DevPlane& P, const DevSeq& S, const OpSlot* sops, uint32_t local,
-                                                 unsigned char* staged_mem, uint32_t* status) {
+                                                 unsigned char* staged_mem, const WaitCtl wc) {
     constexpr bool PLANAR = false;
     uint8_t* const dst = P.dst;
     const uint32_t dst_pitch = P.dst_pitch, dst_cstride = P.dst_cstride;
@@ -1116,7 +1146,10 @@ __device__ __forceinline__ void body_nv12_staged(const DevPlane& P, const DevSeq
         }
     }
     __syncthreads(); /* every copy's bytes are expected before the one arrival */
-    if (tid == 0) mbar_arrive(mbar);
+    if (tid == 0) {
+        if (wc.test_extra_bytes) mbar_expect_tx_only(mbar, wc.test_extra_bytes);
+        mbar_arrive(mbar);
+    }
 
     /* the thread's two columns */
     const uint32_t slot = tid / gw, gi = tid - slot * gw;
@@ -1133,9 +1166,9 @@ __device__ __forceinline__ void body_nv12_staged(const DevPlane& P, const DevSeq
     const bool col1_a = axa.w1 != 0.0f, col1_b = axb.w1 != 0.0f;
     const bool yuv = S.pre_kind == PRE_YUV_BT709;
 
-    if (!mbar_wait_bounded(mbar, 0)) {
-        atomicExch(status, STATUS_STAGED_WAIT_TIMEOUT);
-        (void)mbar_wait_bounded(mbar, 0);
+    if (!mbar_wait_bounded(mbar, 0, wc.limit_us)) {
+        atomicExch(wc.status, STATUS_STAGED_WAIT_TIMEOUT);
+        (void)mbar_wait_bounded(mbar, 0, wc.limit_us);
         return;
     }
 
@@ -1226,7 +1259,7 @@ __device__ __forceinline__ void body_nv12_staged(const DevPlane& P, const DevSeq
 /* The bodies of one continuation (compiled chain or interpreter), selected by the plane's class. */
 template <uint32_t CLASS, uint32_t CHAIN>
 __device__ __forceinline__ void run_class(uint32_t cls, const DevPlane& P, const DevSeq& S, const OpSlot* sops,
-                                          uint32_t local, unsigned char* staged_mem, unsigned char* turn_mem, uint32_t* status) {
+                                          uint32_t local, unsigned char* staged_mem, unsigned char* turn_mem, const WaitCtl status) {
     if (CLASS != CLASS_MIXED) cls = CLASS;
     switch (cls) {
         case CLASS_FLAT_U8_F32: body_flat<CHAIN, true, false>(P, S, sops, local, turn_mem); break;
@@ -1256,12 +1289,12 @@ __device__ __forceinline__ void run_class(uint32_t cls, const DevPlane& P, const
  * spill when all of them were inlined into one function. */
 template <uint32_t CLS, uint32_t CHAIN>
 __device__ __noinline__ void mixed_body(const DevPlane* P, const DevSeq* S, const OpSlot* sops, uint32_t local,
-                                        unsigned char* staged_mem, unsigned char* turn_mem, uint32_t* status) {
+                                        unsigned char* staged_mem, unsigned char* turn_mem, const WaitCtl status) {
     run_class<CLS, CHAIN>(CLS, *P, *S, sops, local, staged_mem, turn_mem, status);
 }
 template <uint32_t CHAIN>
 __device__ __forceinline__ void run_mixed_chain(uint32_t cls, const DevPlane* P, const DevSeq* S, const OpSlot* sops,
-                                                uint32_t local, unsigned char* staged_mem, unsigned char* turn_mem, uint32_t* status) {
+                                                uint32_t local, unsigned char* staged_mem, unsigned char* turn_mem, const WaitCtl status) {
     switch (cls) {
 #define FKB_MIXED_BODY(C) case C: mixed_body<C, CHAIN>(P, S, sops, local, staged_mem, turn_mem, status); break;
         FKB_MIXED_BODY(CLASS_FLAT_U8_F32) FKB_MIXED_BODY(CLASS_FLAT_F32_F32) FKB_MIXED_BODY(CLASS_FLAT_U8_U8)
@@ -1274,7 +1307,7 @@ __device__ __forceinline__ void run_mixed_chain(uint32_t cls, const DevPlane* P,
 
 template <uint32_t CLASS, uint32_t CHAIN>
 __device__ __forceinline__ void run_body(uint32_t cls, const DevPlane& P, const DevSeq& S, const OpSlot* sops,
-                                         uint32_t local, unsigned char* staged_mem, unsigned char* turn_mem, uint32_t* status) {
+                                         uint32_t local, unsigned char* staged_mem, unsigned char* turn_mem, const WaitCtl status) {
     if constexpr (CLASS != CLASS_MIXED) {
         run_class<CLASS, CHAIN>(cls, P, S, sops, local, staged_mem, turn_mem, status);
     } else {
@@ -1316,7 +1349,8 @@ __global__ void __launch_bounds__(BLOCK_THREADS, min_blocks_of(CLASS)) fused_pla
         const uint32_t n_ops = (uint32_t)a.seq0.n_ops;
         if (threadIdx.x < n_ops) expand_op(*reinterpret_cast<const uint4*>(&a.ops0[threadIdx.x]), sops + threadIdx.x);
         __syncthreads();
-        run_body<CLASS, CHAIN>(a.plane0.plane_class, a.plane0, a.seq0, sops, blockIdx.x, nullptr, s_turn, a.status);
+        run_body<CLASS, CHAIN>(a.plane0.plane_class, a.plane0, a.seq0, sops, blockIdx.x, nullptr, s_turn,
+                               WaitCtl{a.status, a.wait_limit_us, a.test_extra_bytes});
         return;
     }
     /* One 16-byte table entry tells the block its plane, its tile within the plane and where the
@@ -1335,7 +1369,7 @@ __global__ void __launch_bounds__(BLOCK_THREADS, min_blocks_of(CLASS)) fused_pla
             if (threadIdx.x == 0) {
                 mbar_init(mbar, 1);
                 asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-                mbar_expect_tx(mbar, n_src * row_len);
+                mbar_expect_tx(mbar, n_src * row_len + a.test_extra_bytes);
             }
             __syncwarp();
             const uint8_t* g = reinterpret_cast<const uint8_t*>((size_t)cp.x | ((size_t)cp.y << 32));
@@ -1355,7 +1389,8 @@ __global__ void __launch_bounds__(BLOCK_THREADS, min_blocks_of(CLASS)) fused_pla
     __syncthreads();
     /* staged classes: the region after the operation cache, on a 128-byte boundary */
     unsigned char* staged_mem = smem_raw + (((a.max_seq_ops > 0 ? a.max_seq_ops : 1u) * (uint32_t)sizeof(OpSlot) + 127u) & ~127u);
-    run_body<CLASS, CHAIN>(s_plane.plane_class, s_plane, s_seq, sops, local, staged_mem, s_turn, a.status);
+    run_body<CLASS, CHAIN>(s_plane.plane_class, s_plane, s_seq, sops, local, staged_mem, s_turn,
+                           WaitCtl{a.status, a.wait_limit_us, a.test_extra_bytes});
 }
 
 /* ------------------------------------------------------------------------------------ */

@@ -95,14 +95,14 @@ struct LaunchArgs {
                                 /* uchar3 classes have two per block, the second being the     */
                                 /* first byte to copy, rows | row bytes << 16, source pitch    */
     uint32_t n_planes;
-    uint32_t reserved;
+    uint32_t wait_limit_us;     /* longest wait of a block for its asynchronous copies (global timer) */
     uint32_t total_items;
     uint32_t max_seq_ops;       /* longest sequence: sizes the shared-memory op cache         */
     uint32_t block_threads;     /* threads per block of this launch (multiple of 32, <= 256)  */
     uint32_t staged_bytes;      /* STAGED classes: shared memory behind the operation cache    */
     uint32_t inline_plane;      /* 1: a plan of one plane whose descriptors travel in the      */
                                 /* kernel arguments below; block b is tile b of that plane     */
-    uint32_t pad;
+    uint32_t test_extra_bytes;  /* TEST ONLY: bytes a block expects beyond what its copies deliver   */
     uint32_t* status;           /* one word in the plan's device block: 0, or a STATUS_* code  */
     DevPlane plane0;            /* inline_plane: the plane, its sequence and its operations    */
     DevSeq seq0;
@@ -219,14 +219,14 @@ constexpr uint32_t STAGED_HEADER_BYTES = 16 + STAGED_MAX_ROWS * 32;
 constexpr uint32_t NV12_MAX_STAGE_BYTES = 40 * 1024u; /* luma and chroma rows of a band tile; five blocks per SM */
 constexpr uint32_t NV12_MAX_SPAN = 256;           /* source rows between a band's first and last tap */
 constexpr uint32_t STAGED_FOLD_BG_GROUPS = 1024;  /* at most this many outside groups: no store-only items */
-constexpr uint32_t STAGED_WAIT_LIMIT = 1u << 22;  /* try_wait rounds before a block gives up     */
 constexpr uint32_t STATUS_STAGED_WAIT_TIMEOUT = 1; /* a bulk copy did not complete in time        */
 
 /* Compile-time operation chains.  A chain is a list of 4-bit operation codes, first operation
  * in the lowest nibble, 0 terminates.  Kernels are instantiated for the chains in
  * FKB_CHAIN_MENU; any other sequence runs through the interpreter (CHAIN_INTERPRET). */
 
-constexpr uint32_t CH_MUL = 1, CH_SUB = 2, CH_DIV = 3, CH_ADD = 4, CH_SWAP = 6, CH_SAT = 7, CH_YUV = 8, CH_DIVC = 9;
+constexpr uint32_t CH_MUL = 1, CH_SUB = 2, CH_DIV = 3, CH_ADD = 4, CH_SWAP = 6, CH_SAT = 7, CH_YUV = 8, CH_DIVC = 9,
+                   CH_CASTI = 10, CH_CASTU = 11;
 #if defined(__CUDACC__)
 __host__ __device__
 #endif

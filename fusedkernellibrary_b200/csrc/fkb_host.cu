@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
+#include <deque>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -49,6 +51,34 @@ static int fail_cuda(cudaError_t e, const char* what, int line) {
         const cudaError_t e__ = (call);                                  \
         if (e__ != cudaSuccess) return fail_cuda(e__, #call, __LINE__);  \
     } while (0)
+
+/* ------------------------------------------------------------------------------------ */
+/* device memory: every allocation of the library goes through these, and is counted     */
+/* ------------------------------------------------------------------------------------ */
+static std::atomic<uint64_t> g_n_device_alloc{0}, g_n_device_free{0}, g_n_pinned_alloc{0}, g_n_lowered{0}, g_n_reused{0};
+
+static cudaError_t device_alloc(void** p, size_t bytes) {
+    g_n_device_alloc.fetch_add(1, std::memory_order_relaxed);
+    return cudaMalloc(p, bytes);
+}
+static cudaError_t device_free(void* p) {
+    g_n_device_free.fetch_add(1, std::memory_order_relaxed);
+    return cudaFree(p);
+}
+static cudaError_t pinned_alloc(void** p, size_t bytes) {
+    g_n_pinned_alloc.fetch_add(1, std::memory_order_relaxed);
+    return cudaHostAlloc(p, bytes, cudaHostAllocDefault);
+}
+
+extern "C" FKB_API int fkb_debug_get_counters(fkb_debug_counters* out) {
+    if (!out) return FKB_ERR_INVALID_ARGUMENT;
+    out->device_allocations = g_n_device_alloc.load();
+    out->device_frees = g_n_device_free.load();
+    out->host_pinned_allocations = g_n_pinned_alloc.load();
+    out->plans_lowered = g_n_lowered.load();
+    out->plans_reused = g_n_reused.load();
+    return FKB_OK;
+}
 
 /* ------------------------------------------------------------------------------------ */
 /* plan object                                                                          */
@@ -141,6 +171,7 @@ struct HostImage {
         a.max_seq_ops = max_seq_ops;
         a.block_threads = block_threads;
         a.staged_bytes = staged_bytes;
+        a.wait_limit_us = FKB_DEFAULT_WAIT_LIMIT_US;
         a.status = reinterpret_cast<uint32_t*>(const_cast<unsigned char*>(d_base) + off_status());
         /* a single image: its descriptors ride in the kernel arguments, so that a block starts
            without a round trip to global memory */
@@ -268,7 +299,8 @@ static bool constant_division_is_exact(float p) {
     std::lock_guard<std::mutex> lock(mu);
     const auto it = cache.find(float_bits(p));
     if (it != cache.end()) return it->second;
-    const bool ok = check_all_significands(p);
+    const bool ok = check_all_significands(p); /* about 10 ms, once per divisor value */
+    if (cache.size() >= 4096) cache.clear();
     cache[float_bits(p)] = ok;
     return ok;
 }
@@ -336,6 +368,9 @@ static bool advance_range(ValueRange& v, const fkb_op& op) {
         case FKB_OP_SATURATE_CAST_U8:
             v = ValueRange{true, 255.0, 0, 0, true, false};
             break;
+        case FKB_OP_CAST_I32: case FKB_OP_CAST_U32: /* bit patterns from here on; nothing follows */
+            v.known = false;
+            break;
         case FKB_OP_YUV_TO_RGB_BT709_FULL:
             /* integers times the matrix of color_conversion.h:143-146: the smallest non-zero
                coefficient is 0.1873, so every product and sum is a multiple of 2^-26 */
@@ -379,6 +414,18 @@ static float saturate_round_u8_host(float f) {
     if (f < 0.0f) return 0.0f;
     return (float)(int)(f + 0.5f);
 }
+/* What cvt.rzi.s32.f32 / cvt.rzi.u32.f32 return (truncation; out-of-range values saturate, NaN gives 0). */
+static int32_t cast_to_i32(float f) {
+    if (!(f == f)) return 0;
+    if (f >= 2147483648.0f) return INT32_MAX;
+    if (f <= -2147483648.0f) return INT32_MIN;
+    return (int32_t)f;
+}
+static uint32_t cast_to_u32(float f) {
+    if (!(f > 0.0f)) return 0u;
+    if (f >= 4294967296.0f) return UINT32_MAX;
+    return (uint32_t)f;
+}
 static void background_after_ops(const fkb_sequence& s, int n_pre, float out[3]) {
     volatile float v[3] = {s.background[0], s.background[1], s.background[2]};
     for (int k = n_pre; k < s.n_ops; ++k) {
@@ -390,6 +437,8 @@ static void background_after_ops(const fkb_sequence& s, int n_pre, float out[3])
             case FKB_OP_ADD: for (int c = 0; c < 3; ++c) v[c] = v[c] + op.p[c]; break;
             case FKB_OP_SWAP_RB: { const float t = v[0]; v[0] = v[2]; v[2] = t; break; }
             case FKB_OP_SATURATE_CAST_U8: for (int c = 0; c < 3; ++c) v[c] = saturate_round_u8_host(v[c]); break;
+            case FKB_OP_CAST_I32: for (int c = 0; c < 3; ++c) v[c] = bits_float((uint32_t)cast_to_i32(v[c])); break;
+            case FKB_OP_CAST_U32: for (int c = 0; c < 3; ++c) v[c] = bits_float(cast_to_u32(v[c])); break;
             default: break; /* casts leave a float value unchanged; YUV conversion never follows a resize */
         }
     }
@@ -407,6 +456,8 @@ static uint32_t chain_code_of(int dev_opcode) {
         case FKB_OP_SATURATE_CAST_U8: return CH_SAT;
         case FKB_OP_YUV_TO_RGB_BT709_FULL: return CH_YUV;
         case DEV_OP_DIV_BY_CONSTANT: return CH_DIVC;
+        case FKB_OP_CAST_I32: return CH_CASTI;
+        case FKB_OP_CAST_U32: return CH_CASTU;
         default: return 0;
     }
 }
@@ -497,17 +548,17 @@ static uint32_t lower_ops(const fkb_sequence& s, int n_pre, int step_exp_x, int 
 /* ------------------------------------------------------------------------------------ */
 /* validation and lowering                                                              */
 /* ------------------------------------------------------------------------------------ */
-enum ValueType { VT_U8 = 0, VT_F32 = 1, VT_YUV8 = 2 };
+enum ValueType { VT_U8 = 0, VT_F32 = 1, VT_YUV8 = 2, VT_I32 = 3, VT_U32 = 4 };
 
 static uint32_t src_pixel_bytes(int f) { return f == FKB_SRC_U8X3 ? 3u : f == FKB_SRC_F32X3 ? 12u : 1u; }
-static uint32_t dst_pixel_bytes(int f) { return f == FKB_DST_U8X3_PACKED ? 3u : f == FKB_DST_F32X3_PACKED ? 12u : 4u; }
+static uint32_t dst_pixel_bytes(int f) { return f == FKB_DST_U8X3_PACKED ? 3u : f == FKB_DST_F32_PLANAR3 ? 4u : 12u; }
 
 /* Walks a sequence's operations with the value type the reference's templates would have
    (a mismatch there is a compile error; here it is FKB_ERR_INVALID_ARGUMENT). */
 static int check_sequence(const fkb_sequence& s, int index, DevSeq& ds) {
     if (s.src_format < FKB_SRC_U8X3 || s.src_format > FKB_SRC_NV12)
         return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d: unknown source format %d", index, s.src_format);
-    if (s.dst_format < FKB_DST_F32X3_PACKED || s.dst_format > FKB_DST_U8X3_PACKED)
+    if (s.dst_format < FKB_DST_F32X3_PACKED || s.dst_format > FKB_DST_U32X3_PACKED)
         return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d: unknown destination format %d", index, s.dst_format);
     if (s.resize_mode < FKB_RESIZE_NONE || s.resize_mode > FKB_RESIZE_PRESERVE_AR)
         return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d: unknown resize mode %d", index, s.resize_mode);
@@ -527,7 +578,14 @@ static int check_sequence(const fkb_sequence& s, int index, DevSeq& ds) {
             if (oc != FKB_OP_CAST_F32) pre_only_casts = false;
             if (oc != FKB_OP_YUV_TO_RGB_BT709_FULL) pre_is_yuv = false;
         }
+        if (t == VT_I32 || t == VT_U32)
+            return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d op %d: nothing but the receiver may follow a cast to int3 / uint3", index, k);
         switch (oc) {
+            case FKB_OP_CAST_I32: case FKB_OP_CAST_U32:
+                if (t != VT_F32) return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d op %d: Cast<float3,int3|uint3> needs a float value", index, k);
+                if (k < n_pre) return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d op %d: an integer cast cannot precede the interpolation", index, k);
+                t = oc == FKB_OP_CAST_I32 ? VT_I32 : VT_U32;
+                break;
             case FKB_OP_MUL: case FKB_OP_SUB: case FKB_OP_DIV: case FKB_OP_ADD:
                 if (t != VT_F32) return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d op %d: arithmetic on a non-float value (add a Cast first)", index, k);
                 break;
@@ -549,11 +607,17 @@ static int check_sequence(const fkb_sequence& s, int index, DevSeq& ds) {
         }
     }
     const bool dst_u8 = s.dst_format == FKB_DST_U8X3_PACKED;
-    if (dst_u8 != (t == VT_U8 || t == VT_YUV8))
+    const ValueType want = dst_u8 ? VT_U8 : s.dst_format == FKB_DST_I32X3_PACKED ? VT_I32 : s.dst_format == FKB_DST_U32X3_PACKED ? VT_U32 : VT_F32;
+    if (want != (t == VT_YUV8 ? VT_U8 : t)) {
+        static const char* const names[] = {"uchar", "float", "uchar", "int", "uint"};
         return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d: chain ends in a %s value but the receiver writes %s", index,
-                    t == VT_F32 ? "float" : "uchar", dst_u8 ? "uchar3" : "float");
+                    names[t], names[want]);
+    }
 
     ds.src_format = s.src_format; ds.dst_format = s.dst_format; ds.resize_mode = s.resize_mode;
+    /* int3 / uint3 pixels are twelve bytes like float3 and their values travel as bit patterns: the
+       kernels store them through the float3 receiver */
+    if (want == VT_I32 || want == VT_U32) ds.dst_format = FKB_DST_F32X3_PACKED;
     ds.n_ops = s.n_ops; ds.n_pre = n_pre; ds.ops_begin = 0; ds.chain = CHAIN_INTERPRET;
     ds.pre_kind = (n_pre == 0 || pre_only_casts) ? PRE_IDENTITY : pre_is_yuv ? PRE_YUV_BT709 : PRE_GENERAL;
     ds.bg[0] = s.background[0]; ds.bg[1] = s.background[1]; ds.bg[2] = s.background[2]; ds.one = 1.0f;
@@ -1071,10 +1135,10 @@ extern "C" FKB_API int fkb_plan_create(const fkb_plan_desc* desc, fkb_plan** out
     plan->d_bytes = img.bytes();
     std::vector<unsigned char> staging(plan->d_bytes);
     img.serialize(staging.data());
-    cudaError_t e = cudaMalloc(&plan->d_block, plan->d_bytes);
+    cudaError_t e = device_alloc(&plan->d_block, plan->d_bytes);
     if (e == cudaSuccess) e = cudaMemcpy(plan->d_block, staging.data(), plan->d_bytes, cudaMemcpyHostToDevice);
     if (e != cudaSuccess) {
-        if (plan->d_block) cudaFree(plan->d_block);
+        if (plan->d_block) device_free(plan->d_block);
         delete plan;
         return fail_cuda(e, "plan upload", __LINE__);
     }
@@ -1117,6 +1181,7 @@ static int read_status(const uint32_t* d_status, cudaStream_t stream, uint32_t* 
     FKB_CUDA(cudaMemcpyAsync(&st, d_status, sizeof st, cudaMemcpyDeviceToHost, stream));
     FKB_CUDA(cudaStreamSynchronize(stream));
     if (out) *out = st;
+    if (st != 0) (void)cudaMemsetAsync(const_cast<uint32_t*>(d_status), 0, sizeof st, stream); /* reported once */
     if (st != 0) return fail(FKB_ERR_DEVICE_WAIT, "a thread block gave up waiting for its asynchronous copies (status %u); outputs are incomplete", st);
     return FKB_OK;
 }
@@ -1126,10 +1191,26 @@ extern "C" FKB_API int fkb_plan_check(const fkb_plan* plan, void* stream, uint32
     return read_status(plan->args.status, static_cast<cudaStream_t>(stream), device_status);
 }
 
+extern "C" FKB_API int fkb_plan_set_option(fkb_plan* plan, int option, uint32_t value) {
+    if (!plan) return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_plan_set_option: plan is NULL");
+    switch (option) {
+        case FKB_PLAN_WAIT_LIMIT_US:
+            if (value == 0 || value > 4000000u) return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_plan_set_option: wait limit %u us outside [1, 4000000]", value);
+            plan->args.wait_limit_us = value;
+            return FKB_OK;
+        case FKB_PLAN_TEST_EXPECT_EXTRA_BYTES:
+            if (value % 16 != 0 || value > 1024u) return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_plan_set_option: surplus of %u bytes is not a multiple of 16 up to 1024", value);
+            plan->args.test_extra_bytes = value;
+            return FKB_OK;
+        default:
+            return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_plan_set_option: unknown option %d", option);
+    }
+}
+
 extern "C" FKB_API int fkb_plan_destroy(fkb_plan* plan) {
     if (!plan) return FKB_OK;
     cudaError_t e = cudaSuccess;
-    if (plan->d_block) e = cudaFree(plan->d_block);
+    if (plan->d_block) e = device_free(plan->d_block);
     delete plan;
     if (e != cudaSuccess) return fail_cuda(e, "cudaFree", __LINE__);
     return FKB_OK;
@@ -1147,6 +1228,174 @@ extern "C" FKB_API int fkb_execute(const fkb_plan_desc* desc, void* stream) {
     if (rc) return rc;
     if (e != cudaSuccess) return fail_cuda(e, "cudaStreamSynchronize", __LINE__);
     return rs;
+}
+
+/* ------------------------------------------------------------------------------------ */
+/* asynchronous, allocation-free variant                                                */
+/* ------------------------------------------------------------------------------------ */
+/* fkb_execute_async is the launch of executors.h:284-285 as this library can make it: lowering on
+ * the host, one stream-ordered copy of the descriptor table, the kernel, cudaGetLastError.  Device
+ * and pinned memory come from one arena per device that is allocated by the first call and kept
+ * until the process ends; tables are placed in it as in a ring, and a table whose range is needed
+ * again is released only after the launches that used it have finished (one event per table). */
+namespace {
+
+struct AsyncTable {
+    size_t off = 0, bytes = 0;          /* range in the arena (0 bytes: a plan that travels in the kernel arguments) */
+    cudaEvent_t last_use = nullptr;     /* recorded behind the latest launch that reads the table */
+    cudaEvent_t uploaded = nullptr;     /* recorded behind the copy, for launches on another stream */
+    cudaStream_t upload_stream = nullptr;
+    uint64_t hash = 0;
+    std::vector<unsigned char> key;     /* the description, byte for byte */
+    LaunchArgs args{};
+    uint32_t launch_class = 0, chain = 0;
+};
+
+struct AsyncArena {
+    std::mutex mu;
+    unsigned char* dev = nullptr;       /* | status word (256 B) | ring of FKB_ASYNC_ARENA_BYTES | */
+    unsigned char* pinned = nullptr;    /* the ring's staging copy in page-locked host memory */
+    size_t head = 0;
+    std::deque<AsyncTable> tables;      /* resident tables, oldest first */
+    std::vector<cudaEvent_t> spare_events;
+};
+constexpr size_t ASYNC_HEADER = 256;
+constexpr size_t ASYNC_MAX_CACHED = 16; /* descriptions remembered per device */
+AsyncArena g_async[64];
+
+cudaError_t arena_event(AsyncArena& ar, cudaEvent_t* ev) {
+    if (!ar.spare_events.empty()) { *ev = ar.spare_events.back(); ar.spare_events.pop_back(); return cudaSuccess; }
+    return cudaEventCreateWithFlags(ev, cudaEventDisableTiming);
+}
+
+/* Releases the oldest table: waits for its launches, keeps its events for reuse. */
+cudaError_t arena_release_oldest(AsyncArena& ar) {
+    AsyncTable& t = ar.tables.front();
+    cudaError_t e = cudaSuccess;
+    if (t.last_use) { e = cudaEventSynchronize(t.last_use); ar.spare_events.push_back(t.last_use); }
+    if (t.uploaded) ar.spare_events.push_back(t.uploaded);
+    ar.tables.pop_front();
+    return e;
+}
+
+bool ranges_overlap(size_t a, size_t an, size_t b, size_t bn) { return a < b + bn && b < a + an; }
+
+/* The description as one byte string (pointers included: the same chain over other buffers is another plan). */
+void description_key(const fkb_plan_desc* d, std::vector<unsigned char>& key) {
+    size_t n = 2 * sizeof(int32_t) + (size_t)d->n_planes * sizeof(fkb_plane);
+    for (int s = 0; s < d->n_sequences; ++s) n += 8 * sizeof(int32_t) + (size_t)std::max(d->sequences[s].n_ops, 0) * sizeof(fkb_op);
+    key.resize(n);
+    unsigned char* o = key.data();
+    auto put = [&](const void* p, size_t bytes) { std::memcpy(o, p, bytes); o += bytes; };
+    put(&d->n_sequences, 4); put(&d->n_planes, 4);
+    for (int s = 0; s < d->n_sequences; ++s) {
+        const fkb_sequence& q = d->sequences[s];
+        put(&q.src_format, 4); put(&q.dst_format, 4); put(&q.resize_mode, 4); put(&q.n_ops, 4); put(&q.n_pre_ops, 4);
+        put(q.background, 12);
+        if (q.n_ops > 0) put(q.ops, (size_t)q.n_ops * sizeof(fkb_op));
+    }
+    put(d->planes, (size_t)d->n_planes * sizeof(fkb_plane));
+}
+uint64_t fnv1a(const std::vector<unsigned char>& v) {
+    uint64_t h = 1469598103934665603ull;
+    const size_t words = v.size() / 8;
+    const uint64_t* w = reinterpret_cast<const uint64_t*>(v.data());
+    for (size_t i = 0; i < words; ++i) { uint64_t x; std::memcpy(&x, w + i, 8); h = (h ^ x) * 1099511628211ull; }
+    for (size_t i = words * 8; i < v.size(); ++i) h = (h ^ v[i]) * 1099511628211ull;
+    return h;
+}
+
+}  // namespace
+
+extern "C" FKB_API int fkb_execute_async(const fkb_plan_desc* desc, void* stream_) {
+    if (!desc || !desc->sequences || !desc->planes || desc->n_sequences <= 0 || desc->n_planes <= 0) {
+        HostImage probe;
+        return lower(desc, probe); /* reports what is wrong */
+    }
+    for (int s = 0; s < desc->n_sequences; ++s)
+        if (desc->sequences[s].n_ops > 0 && !desc->sequences[s].ops) { HostImage probe; return lower(desc, probe); }
+    int device = -1;
+    int rc = require_device(&device);
+    if (rc) return rc;
+    if (device < 0 || device >= 64) return fail(FKB_ERR_UNSUPPORTED, "fkb_execute_async: device ordinal %d beyond 63", device);
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    AsyncArena& ar = g_async[device];
+    std::lock_guard<std::mutex> lock(ar.mu);
+    if (!ar.dev) { /* first call on this device: the only allocations this entry point ever makes */
+        void* d = nullptr; void* h = nullptr;
+        cudaError_t e = device_alloc(&d, ASYNC_HEADER + FKB_ASYNC_ARENA_BYTES);
+        if (e == cudaSuccess) e = pinned_alloc(&h, FKB_ASYNC_ARENA_BYTES);
+        if (e == cudaSuccess) e = cudaMemset(d, 0, ASYNC_HEADER);
+        if (e != cudaSuccess) { if (d) device_free(d); if (h) cudaFreeHost(h); return fail_cuda(e, "arena allocation", __LINE__); }
+        ar.dev = static_cast<unsigned char*>(d);
+        ar.pinned = static_cast<unsigned char*>(h);
+    }
+    uint32_t* const status = reinterpret_cast<uint32_t*>(ar.dev);
+
+    std::vector<unsigned char> key;
+    description_key(desc, key);
+    const uint64_t hash = fnv1a(key);
+    AsyncTable* t = nullptr;
+    for (AsyncTable& c : ar.tables)
+        if (c.hash == hash && c.key == key) { t = &c; break; }
+    if (t) {
+        g_n_reused.fetch_add(1, std::memory_order_relaxed);
+        if (t->bytes != 0 && t->upload_stream != stream) FKB_CUDA(cudaStreamWaitEvent(stream, t->uploaded, 0));
+    } else {
+        HostImage img;
+        rc = lower(desc, img);
+        if (rc) return rc;
+        g_n_lowered.fetch_add(1, std::memory_order_relaxed);
+        const bool in_arguments = img.args_for(nullptr).inline_plane != 0;
+        const size_t bytes = in_arguments ? 0 : (img.bytes() + 255) & ~(size_t)255;
+        if (bytes > FKB_ASYNC_ARENA_BYTES)
+            return fail(FKB_ERR_TOO_LARGE, "fkb_execute_async: the plan's descriptor table (%zu bytes) exceeds the arena of %u; use fkb_plan_create", bytes, FKB_ASYNC_ARENA_BYTES);
+        while (ar.tables.size() >= ASYNC_MAX_CACHED) FKB_CUDA(arena_release_oldest(ar));
+        size_t off = ar.head;
+        if (bytes != 0) {
+            if (off + bytes > FKB_ASYNC_ARENA_BYTES) off = 0;
+            /* tables lie in ring order, so whatever overlaps the new range is at the front */
+            for (;;) {
+                bool clash = false;
+                for (const AsyncTable& c : ar.tables) clash = clash || (c.bytes != 0 && ranges_overlap(off, bytes, c.off, c.bytes));
+                if (!clash) break;
+                FKB_CUDA(arena_release_oldest(ar));
+            }
+            ar.head = off + bytes;
+        }
+        ar.tables.emplace_back();
+        t = &ar.tables.back();
+        t->off = off; t->bytes = bytes; t->hash = hash; t->key.swap(key);
+        t->launch_class = img.launch_class; t->chain = img.chain;
+        t->args = img.args_for(ar.dev + ASYNC_HEADER + off);
+        t->args.status = status;
+        cudaError_t e = arena_event(ar, &t->last_use);
+        if (e == cudaSuccess && bytes != 0) e = arena_event(ar, &t->uploaded);
+        if (e == cudaSuccess && bytes != 0) {
+            img.serialize(ar.pinned + off);
+            e = cudaMemcpyAsync(ar.dev + ASYNC_HEADER + off, ar.pinned + off, img.bytes(), cudaMemcpyHostToDevice, stream);
+            if (e == cudaSuccess) e = cudaEventRecord(t->uploaded, stream);
+            t->upload_stream = stream;
+        }
+        if (e != cudaSuccess) { ar.tables.pop_back(); return fail_cuda(e, "descriptor upload", __LINE__); }
+    }
+    const cudaError_t le = launch_plan_kernel(t->launch_class, t->chain, t->args, stream);
+    if (le != cudaSuccess) return fail_cuda(le, "kernel launch", __LINE__);
+    FKB_CUDA(cudaEventRecord(t->last_use, stream));
+    return FKB_OK;
+}
+
+extern "C" FKB_API int fkb_async_check(void* stream_, uint32_t* device_status) {
+    int device = -1;
+    const int rc = require_device(&device);
+    if (rc) return rc;
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    if (device < 0 || device >= 64 || !g_async[device].dev) { /* nothing was launched here: only the synchronisation */
+        FKB_CUDA(cudaStreamSynchronize(stream));
+        if (device_status) *device_status = 0;
+        return FKB_OK;
+    }
+    return read_status(reinterpret_cast<uint32_t*>(g_async[device].dev), stream, device_status);
 }
 
 /* ------------------------------------------------------------------------------------ */
@@ -1182,10 +1431,10 @@ extern "C" FKB_API int fkb_host_session_destroy(fkb_host_session* s) {
     if (!s) return FKB_OK;
     for (auto& g : s->groups) {
         if (g.plan) fkb_plan_destroy(g.plan);
-        if (g.dev_src) cudaFree(g.dev_src);
+        if (g.dev_src) device_free(g.dev_src);
         if (g.computed) cudaEventDestroy(g.computed);
     }
-    for (void* p : s->dev_outputs) if (p) cudaFree(p);
+    for (void* p : s->dev_outputs) if (p) device_free(p);
     if (s->start) cudaEventDestroy(s->start);
     if (s->downloaded) cudaEventDestroy(s->downloaded);
     if (s->out_stream) cudaStreamDestroy(s->out_stream);
@@ -1232,7 +1481,7 @@ extern "C" FKB_API int fkb_host_session_create(const fkb_plan_desc* desc, fkb_ho
     unsigned char* block = nullptr;
     if (one_block) {
         void* b = nullptr;
-        const cudaError_t e = cudaMalloc(&b, hi - lo);
+        const cudaError_t e = device_alloc(&b, hi - lo);
         if (e != cudaSuccess) return bail(fail_cuda(e, "output mirror allocation", __LINE__));
         s->dev_outputs.push_back(b);
         block = static_cast<unsigned char*>(b);
@@ -1251,7 +1500,7 @@ extern "C" FKB_API int fkb_host_session_create(const fkb_plan_desc* desc, fkb_ho
             fkb_host_session::Group g;
             g.host_src = p.src;
             g.src_bytes = bytes;
-            const cudaError_t e = cudaMalloc(&g.dev_src, bytes);
+            const cudaError_t e = device_alloc(&g.dev_src, bytes);
             if (e != cudaSuccess) return bail(fail_cuda(e, "source mirror allocation", __LINE__));
             s->groups.push_back(g);
             members.emplace_back();
@@ -1274,7 +1523,7 @@ extern "C" FKB_API int fkb_host_session_create(const fkb_plan_desc* desc, fkb_ho
                 planes[i].dst = block + (reinterpret_cast<uintptr_t>(p.dst) - lo);
             } else {
                 void* mirror = nullptr;
-                const cudaError_t e = cudaMalloc(&mirror, out_bytes[i]);
+                const cudaError_t e = device_alloc(&mirror, out_bytes[i]);
                 if (e != cudaSuccess) return bail(fail_cuda(e, "output mirror allocation", __LINE__));
                 s->dev_outputs.push_back(mirror);
                 planes[i].dst = mirror;
@@ -1441,9 +1690,16 @@ extern "C" FKB_API int fkb_execute_static(const fkb_plan_desc* desc, void* strea
     /* From pageable memory this returns once `staging` has been read, and is ordered on the
        stream before the launch and after any earlier kernel that still reads the table. */
     FKB_CUDA(cudaMemcpyAsync(table, staging.data(), bytes, cudaMemcpyHostToDevice, stream));
-    const cudaError_t le = launch_plan_kernel(img.launch_class, img.chain, img.args_for(table), stream);
+    const LaunchArgs args = img.args_for(table);
+    const cudaError_t le = launch_plan_kernel(img.launch_class, img.chain, args, stream);
+    /* the status word is read back in stream order, right behind the kernel: a later call on the same
+       stream cannot rewrite the table between the kernel and this read */
+    uint32_t st = 0;
+    const cudaError_t ce = le == cudaSuccess ? cudaMemcpyAsync(&st, args.status, sizeof st, cudaMemcpyDeviceToHost, stream) : cudaSuccess;
     const cudaError_t se = cudaStreamSynchronize(stream);
     if (le != cudaSuccess) return fail_cuda(le, "kernel launch", __LINE__);
+    if (ce != cudaSuccess) return fail_cuda(ce, "status read-back", __LINE__);
     if (se != cudaSuccess) return fail_cuda(se, "cudaStreamSynchronize", __LINE__);
-    return read_status(img.args_for(table).status, stream, nullptr);
+    if (st != 0) return fail(FKB_ERR_DEVICE_WAIT, "a thread block gave up waiting for its asynchronous copies (status %u); outputs are incomplete", st);
+    return FKB_OK;
 }

@@ -63,7 +63,9 @@ typedef enum fkb_dst_format {
                               /* (memory_operations.h:114-137,173-193)                        */
     FKB_DST_F32_PLANAR3 = 2,  /* TensorSplit<float3> (memory_operations.h:195-226): channel c */
                               /* of a plane at byte offset c * channel_stride                 */
-    FKB_DST_U8X3_PACKED = 3   /* PerThreadWrite<_2D,uchar3> / TensorWrite<uchar3>             */
+    FKB_DST_U8X3_PACKED = 3,  /* PerThreadWrite<_2D,uchar3> / TensorWrite<uchar3>             */
+    FKB_DST_I32X3_PACKED = 4, /* PerThreadWrite<_2D,int3> / TensorWrite<int3>: 12 bytes a pixel */
+    FKB_DST_U32X3_PACKED = 5  /* PerThreadWrite<_2D,uint3> / TensorWrite<uint3>                 */
 } fkb_dst_format;
 
 /* Geometry stage between the read and the element-wise continuation. */
@@ -83,8 +85,15 @@ typedef enum fkb_opcode {
     FKB_OP_SWAP_RB = 6,         /* ColorConversion<COLOR_RGB2BGR|COLOR_BGR2RGB> =               */
                                 /* VectorReorder<T,2,1,0> (basic_ops/cuda_vector.h:50-62)       */
     FKB_OP_SATURATE_CAST_U8 = 7,/* SaturateCast<float3,uchar3> (image_processing/saturate.h)    */
-    FKB_OP_YUV_TO_RGB_BT709_FULL = 8 /* ConvertYUVToRGB<NV12,Full,bt709,false,float3>           */
+    FKB_OP_YUV_TO_RGB_BT709_FULL = 8, /* ConvertYUVToRGB<NV12,Full,bt709,false,float3>          */
                                 /* (color_conversion.h:250-309, matrix :143-146)                */
+    FKB_OP_CAST_I32 = 9,        /* Cast<float3,int3>: per-channel static_cast, truncation toward  */
+                                /* zero (basic_ops/cast_base.h:20-30, cast.h:23-33).  Last        */
+                                /* operation of a sequence only; the receiver is an I32X3 format. */
+    FKB_OP_CAST_U32 = 10        /* Cast<float3,uint3> (the ending of the reference's run-time test,*/
+                                /* tests/operation/test_instantiable_operations.h:241-264).  C++   */
+                                /* leaves static_cast of a negative or too large float undefined;  */
+                                /* here such values saturate (cvt.rzi.u32.f32).  U32X3 receiver.   */
 } fkb_opcode;
 
 typedef struct fkb_op {
@@ -212,10 +221,26 @@ FKB_API int fkb_plan_get_resize_params(const fkb_plan* plan, int32_t index, fkb_
 /* Reads the plan's device status word after synchronising `stream` (the stream of the last
  * launch).  Kernels never trap and never wait without a limit: a thread block whose wait for an
  * asynchronous copy ran out records it there and returns.  *device_status is 0 when every block
- * completed; the call then returns FKB_OK, otherwise FKB_ERR_DEVICE_WAIT.  The reference has no
- * counterpart (its kernel has no waits); its launch-site check is cudaGetLastError alone
- * (executors.h:285), which fkb_plan_launch keeps. */
+ * completed; the call then returns FKB_OK, otherwise FKB_ERR_DEVICE_WAIT and the word is cleared
+ * (in stream order), so that one incomplete launch is reported once and later launches of the
+ * plan are judged on their own.  The reference has no counterpart (its kernel has no waits); its
+ * launch-site check is cudaGetLastError alone (executors.h:285), which fkb_plan_launch keeps. */
 FKB_API int fkb_plan_check(const fkb_plan* plan, void* stream, uint32_t* device_status);
+
+/* Run-time options of a plan (fkb_plan_set_option). */
+typedef enum fkb_plan_option {
+    FKB_PLAN_WAIT_LIMIT_US = 1,       /* longest a thread block waits for its asynchronous copies before it   */
+                                      /* records FKB_ERR_DEVICE_WAIT and returns; wall-clock microseconds of  */
+                                      /* the GPU's global timer, 1 .. 4,000,000; default FKB_DEFAULT_WAIT_LIMIT_US. */
+                                      /* A block that gives up waits once more, as long, for copies still in   */
+                                      /* flight towards its shared memory, so it holds an SM for at most twice */
+                                      /* the limit.                                                            */
+    FKB_PLAN_TEST_EXPECT_EXTRA_BYTES = 2 /* TEST ONLY: every block expects this many bytes more than its copies */
+                                      /* deliver (a multiple of 16), so that its wait runs out although every  */
+                                      /* copy completed; exercises the give-up path without a fault or a hang. */
+} fkb_plan_option;
+#define FKB_DEFAULT_WAIT_LIMIT_US 100000u
+FKB_API int fkb_plan_set_option(fkb_plan* plan, int option, uint32_t value);
 
 /* Frees the plan's descriptor memory.  Call after the launches that use it have finished. */
 FKB_API int fkb_plan_destroy(fkb_plan* plan);
@@ -223,6 +248,34 @@ FKB_API int fkb_plan_destroy(fkb_plan* plan);
 /* One-shot equivalent of fk::executeOperations(stream, sender, receiver) followed by
  * stream.sync(): create, launch, synchronise the stream, destroy. */
 FKB_API int fkb_execute(const fkb_plan_desc* desc, void* stream);
+
+/* Asynchronous, allocation-free form of fk::executeOperations(stream, sender, receiver)
+ * (fused_kernel.h:22-54 -> executors.h:252-287: one launch, cudaGetLastError, nothing else):
+ * validates and lowers `desc`, places the descriptor table in a per-device arena that the
+ * library allocates once (device ring + pinned host ring, FKB_ASYNC_ARENA_BYTES each, on the
+ * first call on a device), copies it with one stream-ordered cudaMemcpyAsync from pinned memory
+ * and launches.  Returns after the launch: it does not synchronise, and after the first call on
+ * a device it calls neither cudaMalloc nor cudaFree.  A plan of one plane with up to 16
+ * operations travels in the kernel arguments and is not copied at all.  A description equal to
+ * one of the last few on the same device (same sequences, planes and pointers: a frame loop over
+ * fixed buffers) reuses its lowered table, still resident in the arena, without lowering or
+ * copying again.  When the ring is full the call waits for the oldest launch that still holds a
+ * slot.  A table larger than the arena is refused with FKB_ERR_TOO_LARGE (use fkb_plan_create).
+ * `desc` and what it points to may be released when the call returns. */
+#define FKB_ASYNC_ARENA_BYTES (8u * 1024u * 1024u)
+FKB_API int fkb_execute_async(const fkb_plan_desc* desc, void* stream);
+
+/* Synchronises `stream` and reports whether any fkb_execute_async launch on the current device
+ * since the last check gave up a bounded wait (FKB_ERR_DEVICE_WAIT, cleared by the call); the
+ * counterpart of stream.sync() after executeOperations. */
+FKB_API int fkb_async_check(void* stream, uint32_t* device_status);
+
+/* Counters for tests: device allocations (cudaMalloc, cudaHostAlloc) and frees made by this
+ * library in this process, lowerings skipped because a description was found in the cache. */
+typedef struct fkb_debug_counters {
+    uint64_t device_allocations, device_frees, host_pinned_allocations, plans_lowered, plans_reused;
+} fkb_debug_counters;
+FKB_API int fkb_debug_get_counters(fkb_debug_counters* out);
 
 /* Host-buffer sessions: for callers whose images live in HOST memory (preferably pinned).
  * Every pointer in desc->planes (src and dst) is a host pointer.  The reference's
@@ -256,9 +309,14 @@ FKB_API int fkb_execute_host(const fkb_plan_desc* desc, void* stream);
  *    FKB_ERR_TOO_LARGE, nothing runs;
  *  - calls cudaMalloc, cudaFree or an allocating library routine never; host memory only;
  *  - the first call on a device looks up the array's device address (with that device
- *    current); make that first call before starting any stream capture on the device;
- *  - all calls on one device share the array: two calls that overlap on the GPU (different
- *    host threads on different streams) race on it and must be serialised by the caller. */
+ *    current), which is also when the CUDA runtime loads this library's module on that device
+ *    and reserves the array there; make that first call before the embedding framework takes
+ *    the rest of HBM and before starting any stream capture on the device;
+ *  - all calls on one device share the array: serialise them per device, whatever their
+ *    streams and host threads (two calls that overlap on the GPU race on the array, and two
+ *    host threads on one stream would overwrite each other's table before it has been used);
+ *  - proving a new Div constant exact costs about 10 ms of host time once per divisor value
+ *    and process (see fkb_plan_validate, which can be called at start-up to pay it early). */
 #define FKB_STATIC_TABLE_BYTES (512 * 1024)
 FKB_API int fkb_execute_static(const fkb_plan_desc* desc, void* stream);
 

@@ -95,21 +95,10 @@ public:
     Stream& operator=(const Stream&) = delete;
     ~Stream() { try { sync(); } catch (...) {} }
     void* getCUDAStream() const { return stream_; }
-    /* Waits for the launches made through this object and releases their plans. */
-    void sync() {
-        int first_error = FKB_OK;
-        for (fkb_plan* p : pending_) {
-            const int rc = fkb_plan_check(p, stream_, nullptr); /* synchronises the stream */
-            if (rc != FKB_OK && first_error == FKB_OK) first_error = rc;
-            fkb_plan_destroy(p);
-        }
-        pending_.clear();
-        check(first_error);
-    }
-    void keep(fkb_plan* p) { pending_.push_back(p); }
+    /* Waits for the launches made on the stream; throws if a kernel gave up a bounded wait. */
+    void sync() { check(fkb_async_check(stream_, nullptr)); }
 private:
     void* stream_;
-    std::vector<fkb_plan*> pending_;
 };
 
 /* ---- the chain as a value ---- */
@@ -260,11 +249,9 @@ inline void lower_into(const Sender& s, const Receiver& r, Lowered& out, std::ve
 inline void launch(Stream& stream, Lowered& low, std::vector<std::vector<fkb_op>>& op_store) {
     for (size_t k = 0; k < low.seqs.size(); ++k) low.seqs[k].ops = op_store[k].empty() ? nullptr : op_store[k].data();
     fkb_plan_desc d{low.seqs.data(), (int32_t)low.seqs.size(), low.planes.data(), (int32_t)low.planes.size()};
-    fkb_plan* plan = nullptr;
-    check(fkb_plan_create(&d, &plan));
-    const int rc = fkb_plan_launch(plan, stream.getCUDAStream());
-    if (rc != FKB_OK) { fkb_plan_destroy(plan); check(rc); }
-    stream.keep(plan); /* released by stream.sync(), after the launch has finished */
+    /* lowering, one stream-ordered copy of the descriptor table from pinned memory, the launch: no
+       allocation and no synchronisation, like the reference's launch site */
+    check(fkb_execute_async(&d, stream.getCUDAStream()));
 }
 }  // namespace detail
 

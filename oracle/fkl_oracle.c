@@ -105,6 +105,12 @@ static px3 apply_op(px3 in, const fkb_op* op) {
                 else o.v[c] = (float)(uint8_t)cxp_roundf(f);
             }
             break;
+        case FKB_OP_CAST_I32:                            /* Cast<float3,int3>: static_cast per channel, cast_base.h:20-30 */
+            for (c = 0; c < 3; ++c) { const int32_t i = (int32_t)in.v[c]; memcpy(&o.v[c], &i, 4); }  /* kept as bits */
+            break;
+        case FKB_OP_CAST_U32:                            /* Cast<float3,uint3> */
+            for (c = 0; c < 3; ++c) { const uint32_t u = (uint32_t)in.v[c]; memcpy(&o.v[c], &u, 4); }
+            break;
         case FKB_OP_YUV_TO_RGB_BT709_FULL: {             /* color_conversion.h:265-308, :143-146 */
             /* (Y, U-128, V-128) times the matrix rows, each row reduced left to right
                (algebraic.h:58-64, cuda_vector.h:113-126), then scaled by 1.0f (:241-243). */
@@ -158,7 +164,8 @@ static px3 interpolate(const fkb_plane* pl, const fkb_sequence* sq, int n_pre, f
  * (memory_operations.h:203-219). */
 static void write_px(const fkb_plane* pl, int dst_format, int x, int y, px3 v) {
     uint8_t* base = (uint8_t*)pl->dst;
-    if (dst_format == FKB_DST_F32X3_PACKED) {
+    if (dst_format == FKB_DST_F32X3_PACKED || dst_format == FKB_DST_I32X3_PACKED || dst_format == FKB_DST_U32X3_PACKED) {
+        /* int3 / uint3 values are carried as bit patterns (see FKB_OP_CAST_I32) */
         float* p = (float*)(base + (size_t)y * pl->dst_pitch + (size_t)x * 12);
         p[0] = v.v[0]; p[1] = v.v[1]; p[2] = v.v[2];
     } else if (dst_format == FKB_DST_F32_PLANAR3) {

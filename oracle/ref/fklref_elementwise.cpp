@@ -164,6 +164,37 @@ void FKLREF_FN(bgr_cast_mul_saturate)(const uint8_t* src, int w, int h, int spit
     finish(stream);
 }
 
+/* PerThreadRead<uchar3> -> Cast<uchar3,float3> -> Mul -> Sub -> Cast<float3,int3> -> PerThreadWrite<int3> */
+void FKLREF_FN(cast_mul_sub_cast_int3)(const uint8_t* src, int w, int h, int spitch, const float* mul, const float* sub,
+                                       int32_t* dst, int dpitch) {
+    RefStream stream = make_stream();
+    const auto sender = PerThreadRead<ND::_2D, uchar3>::build(raw_u8x3(src, w, h, spitch))
+                            .then(Cast<uchar3, float3>::build())
+                            .then(Mul<float3>::build(f3(mul)))
+                            .then(Sub<float3>::build(f3(sub)))
+                            .then(Cast<float3, int3>::build());
+    const auto receiver = PerThreadWrite<ND::_2D, int3>::build(
+        RawPtr<ND::_2D, int3>{reinterpret_cast<int3*>(dst), PtrDims<ND::_2D>((uint)w, (uint)h, (uint)dpitch)});
+    executeOperations<RefDPP>(stream, sender, receiver);
+    finish(stream);
+}
+
+/* PerThreadRead<uchar3> -> Cast<uchar3,float3> -> Resize<INTER_LINEAR>(dw,dh) -> Mul -> Cast<float3,uint3>
+   -> PerThreadWrite<uint3> (the shape of tests/operation/test_instantiable_operations.h:236-264) */
+void FKLREF_FN(cast_resize_mul_cast_uint3)(const uint8_t* src, int w, int h, int spitch, int dw, int dh, const float* mul,
+                                           uint32_t* dst, int dpitch) {
+    RefStream stream = make_stream();
+    const auto sender = PerThreadRead<ND::_2D, uchar3>::build(raw_u8x3(src, w, h, spitch))
+                            .then(Cast<uchar3, float3>::build())
+                            .then(Resize<LINEAR>::build(Size(dw, dh)))
+                            .then(Mul<float3>::build(f3(mul)))
+                            .then(Cast<float3, uint3>::build());
+    const auto receiver = PerThreadWrite<ND::_2D, uint3>::build(
+        RawPtr<ND::_2D, uint3>{reinterpret_cast<uint3*>(dst), PtrDims<ND::_2D>((uint)dw, (uint)dh, (uint)dpitch)});
+    executeOperations<RefDPP>(stream, sender, receiver);
+    finish(stream);
+}
+
 /* PerThreadRead<uchar3> -> Cast<uchar3,float3> -> Resize<INTER_LINEAR, IGNORE_AR>(dw,dh) -> PerThreadWrite<float3> */
 void FKLREF_FN(cast_resize)(const uint8_t* src, int w, int h, int spitch, int dw, int dh, float* dst, int dpitch) {
     RefStream stream = make_stream();

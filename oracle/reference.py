@@ -82,6 +82,22 @@ def bgr_cast_mul_saturate(src, mul, flavour="device_branch"):
     return out
 
 
+def cast_mul_sub_cast_int3(src, mul, sub, flavour="device_branch"):
+    h, w, _ = src.shape
+    out = np.empty((h, w, 3), np.int32)
+    lib(flavour).fklref_cast_mul_sub_cast_int3(_u8(src), w, h, src.strides[0], _f3(mul), _f3(sub),
+                                              out.ctypes.data_as(C.POINTER(C.c_int32)), out.strides[0])
+    return out
+
+
+def cast_resize_mul_cast_uint3(src, dw, dh, mul, flavour="device_branch"):
+    h, w, _ = src.shape
+    out = np.empty((dh, dw, 3), np.uint32)
+    lib(flavour).fklref_cast_resize_mul_cast_uint3(_u8(src), w, h, src.strides[0], dw, dh, _f3(mul),
+                                                  out.ctypes.data_as(C.POINTER(C.c_uint32)), out.strides[0])
+    return out
+
+
 def cast_resize(src, dw, dh, flavour="device_branch"):
     h, w, _ = src.shape
     out = np.empty((dh, dw, 3), np.float32)

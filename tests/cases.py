@@ -41,7 +41,7 @@ def elementwise_case(name, seed, w, h, ops, src_fmt=abi.SRC_U8X3, dst_fmt=abi.DS
                      dst_pitch=None, crop=None):
     rng = np.random.default_rng(seed)
     spx = 3 if src_fmt == abi.SRC_U8X3 else 12
-    dpx = 3 if dst_fmt == abi.DST_U8X3_PACKED else 12
+    dpx = 3 if dst_fmt == abi.DST_U8X3_PACKED else 12   # float3, int3 and uint3 are twelve bytes
     sp = src_pitch or w * spx
     ow, oh = (crop[2], crop[3]) if crop else (w, h)
     dp = dst_pitch or ow * dpx
@@ -113,7 +113,8 @@ def resize_any_case(name, seed, src_fmt, dst_fmt, w, h, dw, dh, pre_ops, post_op
         src = (rng.random((h, w * 3), dtype=np.float32) * 255).astype(np.float32)
         sp = w * 12
     planar = dst_fmt == abi.DST_F32_PLANAR3
-    dpx = {abi.DST_F32X3_PACKED: 12, abi.DST_U8X3_PACKED: 3, abi.DST_F32_PLANAR3: 4}[dst_fmt]
+    dpx = {abi.DST_F32X3_PACKED: 12, abi.DST_U8X3_PACKED: 3, abi.DST_F32_PLANAR3: 4, abi.DST_I32X3_PACKED: 12,
+           abi.DST_U32X3_PACKED: 12}[dst_fmt]
     out = np.zeros((3 * dh if planar else dh, dw * dpx), np.uint8)
 
     def build(ptr):
@@ -231,6 +232,14 @@ def small_cases():
         resize_any_case("resize_then_saturate_u8", 72, abi.SRC_U8X3, abi.DST_U8X3_PACKED, 64, 48, 32, 20,
                         [op(abi.OP_CAST_F32)], [op(abi.OP_MUL, 1.1), op(abi.OP_SATURATE_CAST_U8)]),
         resize_any_case("planar_ignore_ar", 73, abi.SRC_U8X3, abi.DST_F32_PLANAR3, 64, 48, 40, 28, [], chains.normalize_ops()),
+        # Cast<float3,int3> / Cast<float3,uint3> closing a chain (truncation toward zero)
+        elementwise_case("cast_int3_after_arithmetic", 81, 64, 33, [op(abi.OP_CAST_F32), op(abi.OP_MUL, (1.37, 0.5, 2.25)),
+                                                                    op(abi.OP_SUB, (100.5, 3.25, 7.0)), op(abi.OP_CAST_I32)],
+                         dst_fmt=abi.DST_I32X3_PACKED),
+        elementwise_case("cast_uint3_odd_width", 82, 53, 37, [op(abi.OP_CAST_F32), op(abi.OP_MUL, (1.37, 300.5, 2.25)),
+                                                              op(abi.OP_CAST_U32)], dst_fmt=abi.DST_U32X3_PACKED),
+        resize_any_case("resize_then_cast_uint3", 83, abi.SRC_U8X3, abi.DST_U32X3_PACKED, 64, 48, 32, 20,
+                        [op(abi.OP_CAST_F32)], [op(abi.OP_MUL, 3.7), op(abi.OP_CAST_U32)]),
         divergent_case("c5b_small", 51, 64, 36, 32, 18, 3),
         divergent_case("c5b_odd", 52, 50, 30, 25, 15, 2),
     ]

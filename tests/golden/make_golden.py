@@ -88,6 +88,13 @@ def main():
             (fx, fy), roi = ref.resize_params(int(sw), int(sh), int(dw), int(dh), ar)
             res[i, ar] = (np.float32(fx).view(np.uint32), np.float32(fy).view(np.uint32), *roi)
     np.savez_compressed(OUT / "resize_params.npz", query=q, result=res)
+
+    # --- Cast<float3,int3> / Cast<float3,uint3> closing a chain (own seed: added after the fixtures above) ---
+    rng2 = np.random.default_rng(20240608)
+    img2 = u8(rng2, 37, 53, 3)
+    np.savez_compressed(OUT / "int_casts.npz", src=img2,
+                        cast_mul_sub_cast_int3=ref.cast_mul_sub_cast_int3(img2, (1.37, 0.5, 2.25), (100.5, 3.25, 7.0)),
+                        cast_resize_mul_cast_uint3_30x20=ref.cast_resize_mul_cast_uint3(img2, 30, 20, (3.7, 1.0, 0.01)))
     print("golden vectors written to", OUT)
 
 

@@ -1,8 +1,9 @@
 """Known-answer cases taken from the reference's tests for this path (values read from the test
 sources; nothing is executed from the reference tree).
 
-* constant image -> Resize 32x32 -> Add(3,1,32): every pixel equals the constant plus (3,1,32)
-  (tests/operation/test_instantiable_operations.h:241-264; the constant there is 0).
+* constant image (128x128 of 0) -> Cast<uchar3,float3> -> Resize 32x32 -> Add(3,1,32) -> Cast<float3,uint3>
+  -> PerThreadWrite<uint3>: every pixel equals (3,1,32) as unsigned integers
+  (tests/operation/test_instantiable_operations.h:236-264).
 * constant 2 copied through PerThreadRead -> PerThreadWrite, full 1920x1080 image and a 300x200
   crop, for uchar3 and float3 (tests/data/basic_test.h:32-84).
 * COLOR_BGR2RGB on uchar3 {100,150,200} -> {200,150,100} and {50,75,125} -> {125,75,50}
@@ -31,22 +32,22 @@ class KnownAnswer:
 
 def _resize_constant():
     def make():
-        return {"src": np.zeros((48, 64, 3), np.uint8), "out": np.zeros((32, 32, 3), np.float32)}
+        return {"src": np.zeros((128, 128, 3), np.uint8), "out": np.zeros((32, 32, 3), np.uint32)}
 
     def build(ptr):
         plan = abi.HostPlan()
-        s = plan.add_sequence(abi.SRC_U8X3, abi.DST_F32X3_PACKED, abi.RESIZE_IGNORE_AR,
-                              [op(abi.OP_CAST_F32), op(abi.OP_ADD, (3.0, 1.0, 32.0))], n_pre_ops=1)
-        plan.add_plane(src=ptr("src"), src_width=64, src_height=48, src_pitch=192, dst=ptr("out"), dst_width=32,
+        s = plan.add_sequence(abi.SRC_U8X3, abi.DST_U32X3_PACKED, abi.RESIZE_IGNORE_AR,
+                              [op(abi.OP_CAST_F32), op(abi.OP_ADD, (3.0, 1.0, 32.0)), op(abi.OP_CAST_U32)], n_pre_ops=1)
+        plan.add_plane(src=ptr("src"), src_width=128, src_height=128, src_pitch=384, dst=ptr("out"), dst_width=32,
                        dst_height=32, dst_pitch=384, sequence=s)
         return plan
 
     def expect(a):
-        want = np.empty((32, 32, 3), np.float32)
-        want[...] = (3.0, 1.0, 32.0)
+        want = np.empty((32, 32, 3), np.uint32)
+        want[...] = (3, 1, 32)
         return a["out"], want
 
-    return KnownAnswer("resize_constant_then_add", make, build, expect)
+    return KnownAnswer("resize_constant_then_add_then_cast_uint3", make, build, expect)
 
 
 def _copy(fmt, crop):

@@ -20,7 +20,7 @@ def _same(a, b):
 def _elementwise(port, src, ops, dst_fmt=abi.DST_F32X3_PACKED, src_fmt=abi.SRC_U8X3):
     h, w, _ = src.shape
     src = np.ascontiguousarray(src)
-    out = np.zeros((h, w, 3), np.uint8 if dst_fmt == abi.DST_U8X3_PACKED else np.float32)
+    out = np.zeros((h, w, 3), np.uint8 if dst_fmt == abi.DST_U8X3_PACKED else np.float32)   # int3 / uint3: same 12 bytes
     plan = chains.elementwise(ops, src=src.ctypes.data, dst=out.ctypes.data, width=w, height=h, src_format=src_fmt,
                               dst_format=dst_fmt)
     port.run(plan)
@@ -42,6 +42,26 @@ def test_elementwise_chains(oracle_port):
     v = np.float32(np.float32(np.float32(56) * np.float32(1.4)) - np.float32(0.5)) / np.float32(255)
     one = np.full((1, 1, 3), 56, np.uint8)
     assert _elementwise(oracle_port, one, chains.cast_mul_sub_div_ops())[0, 0, 0] == v
+
+
+def test_integer_casts_close_a_chain(oracle_port):
+    """Cast<float3,int3> and Cast<float3,uint3> (cast_base.h:20-30): truncation toward zero, values stored as
+    12-byte integer pixels."""
+    g = np.load(GOLD / "int_casts.npz")
+    src = np.ascontiguousarray(g["src"])
+    got = _elementwise(oracle_port, src, [op(abi.OP_CAST_F32), op(abi.OP_MUL, (1.37, 0.5, 2.25)), op(abi.OP_SUB, (100.5, 3.25, 7.0)),
+                                          op(abi.OP_CAST_I32)], dst_fmt=abi.DST_I32X3_PACKED)
+    assert np.array_equal(got.view(np.int32), g["cast_mul_sub_cast_int3"])
+    assert (g["cast_mul_sub_cast_int3"] < 0).any() and (g["cast_mul_sub_cast_int3"] > 0).any()
+    h, w, _ = src.shape
+    out = np.zeros((20, 30, 3), np.uint32)
+    plan = abi.HostPlan()
+    s = plan.add_sequence(abi.SRC_U8X3, abi.DST_U32X3_PACKED, abi.RESIZE_IGNORE_AR,
+                          [op(abi.OP_CAST_F32), op(abi.OP_MUL, (3.7, 1.0, 0.01)), op(abi.OP_CAST_U32)], n_pre_ops=1)
+    plan.add_plane(src=src.ctypes.data, src_width=w, src_height=h, src_pitch=w * 3, dst=out.ctypes.data, dst_width=30,
+                   dst_height=20, dst_pitch=360, sequence=s)
+    oracle_port.run(plan)
+    assert np.array_equal(out, g["cast_resize_mul_cast_uint3_30x20"])
 
 
 def _cast_resize(port, src, dw, dh, host_branch=False):

@@ -8,7 +8,11 @@ For them the library keeps the plan's descriptor table in a fixed array inside t
 
 The array is shared by every call on a device and keeps what the previous call wrote, so the
 GPU test runs two different plans back to back through the C ABI and compares each, bit for bit,
-with the ordinary entry point (fkb_plan_create + fkb_plan_launch) on the same device buffers.
+with the ordinary entry point (fkb_plan_create + fkb_plan_launch) on the same device buffers
+(both run the same kernels, so this compares two entry points of this library; the kernels
+themselves are compared with the reference in the parity tests).  It also checks the property
+the entry point exists for: after a first call, the library's allocation counters and the
+device's free memory do not move, on the default stream and on a stream of the caller's.
 This file sorts last so that a stop-at-first-failure run has already run everything else.
 """
 import numpy as np
@@ -63,12 +67,24 @@ def test_static_table_run_equals_allocating_run_twice_in_a_row(fkb_lib):
 
     for case, dev, _, _ in prepared:
         clear(dev, case)
-    # calls in a row: A, B, then A again over B's leftovers
+    # a first call loads the module's array on this device; from then on nothing may be allocated
+    abi.execute_static(prepared[0][2])
+    clear(prepared[0][1], prepared[0][0])
+    own_stream = torch.cuda.Stream()
+    torch.cuda.synchronize()
+    counters_before = abi.debug_counters()
+    free_before, _ = torch.cuda.mem_get_info()
+    # calls in a row: A, B, then A again over B's leftovers, the last one on a stream of the caller's
     order = [prepared[0], prepared[1], prepared[0]]
     for n, (case, dev, plan_desc, want) in enumerate(order):
         if n == 2:
             clear(dev, case)
-        abi.execute_static(plan_desc)          # returns after its stream has been synchronised
+        abi.execute_static(plan_desc, own_stream.cuda_stream if n == 2 else None)   # returns after its stream has been synchronised
         for k, v in case.outputs.items():
             got = dev.download(k, v)
             assert np.array_equal(tc.bits(got), tc.bits(want[k])), f"call {n} ({case.name}/{k}) differs from fkb_plan_launch"
+    counters_after = abi.debug_counters()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert (counters_after.device_allocations, counters_after.device_frees, counters_after.host_pinned_allocations) == \
+           (counters_before.device_allocations, counters_before.device_frees, counters_before.host_pinned_allocations)
+    assert free_after == free_before, "device memory was allocated or freed during fkb_execute_static"
