@@ -594,6 +594,39 @@ def reference_gpu_record(torch, stream, dw: DeviceWorkload, steps, warmup):
                     "chunks of at most 128 planes per launch (its per-plane parameters are kernel arguments)"}
 
 
+def call_overhead(torch, stream, dw: DeviceWorkload, calls: int = 200):
+    """Host time of one call, launches queued back to back on a stream and synchronised once at the end:
+    this package's asynchronous call on a repeated description (fkb_execute_async), its one-shot call that
+    allocates and synchronises (fkb_execute), and the reference's executeOperations on its CUDA backend.
+    All three through ctypes from Python, so each carries the same few microseconds of binding overhead."""
+    from oracle import reference_gpu as rg
+    sh = stream.cuda_stream
+    d = dw.sets[0]
+    desc = dw.wl.build(lambda n: d[n].data_ptr(), 0)
+    out = {}
+    abi.execute_async(desc, sh)
+    abi.async_check(sh)
+    t0 = time.perf_counter()
+    for _ in range(calls):
+        abi.execute_async(desc, sh)
+    out["fkb_execute_async"] = (time.perf_counter() - t0) / calls * 1e6
+    abi.async_check(sh)
+    t0 = time.perf_counter()
+    for _ in range(20):
+        abi.execute(desc, sh)
+    out["fkb_execute (allocates, synchronises)"] = (time.perf_counter() - t0) / 20 * 1e6
+    if rg.available():
+        rg.set_stream(sh)
+        dw.reference_gpu(0)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(calls):
+            dw.reference_gpu(0)
+        out["reference executeOperations (CUDA backend)"] = (time.perf_counter() - t0) / calls * 1e6
+        torch.cuda.synchronize()
+    return out
+
+
 def side_workload(torch, stream, name, steps, warmup, peak):
     """One more configuration, timed the same way (a few ms): kernel time, roofline fraction, reference kernel."""
     wl = make_workload(name, 1000)
@@ -611,6 +644,8 @@ def side_workload(torch, stream, name, steps, warmup, peak):
         rec["moved_bytes"] = moved
         rec["frac_of_moved_bytes"] = moved / (ms * 1e-3) / 1e9 / peak
     rec["reference_gpu"] = reference_gpu_record(torch, stream, dw, steps, warmup)
+    if wl.name in ("c2", "c1", "c2s"):
+        rec["host_us_per_call"] = call_overhead(torch, stream, dw)
     dw.destroy()
     del dw, wl
     torch.cuda.empty_cache()

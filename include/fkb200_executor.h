@@ -1,0 +1,392 @@
+/* fkb200_executor.h - the reference-side binding of libfkb200: a drop-in at the reference's own
+ * extension point.
+ *
+ * The reference dispatches fk::executeOperations<DPPType>(stream, iops...) (fused_kernel.h:22-54) to
+ * fk::Executor<DPPType> (core/execution_model/executors.h:129-145 is the primary template, :245-293
+ * the CUDA specialisation whose executeOperations_helper holds the one launch site, :252-287).  This
+ * header adds one more data-parallel-pattern tag, fkb200::TransformDPP, and specialises fk::Executor
+ * for it: its executeOperations_helper walks the instantiable operations the caller built with the
+ * reference's own Op::build(...).then(...) - the values they already carry in OperationData::params /
+ * ::backIOp (operation_model/operation_data.h:79-159) - fills a plain-old-data plan and hands it to
+ * fkb_execute_async (include/fkb200.h), where the reference would have launched
+ * launchTransformDPP_Kernel.  User code changes one template argument:
+ *
+ *     fk::executeOperations<fk::TransformDPP<>>(stream, sender, receiver);     // the reference's kernel
+ *     fk::executeOperations<fkb200::TransformDPP>(stream, sender, receiver);   // this library's kernels
+ *
+ * All seven overloads of fk::executeOperations work, since they reach the executor through
+ * BaseExecutor (executors.h:44-94).  Like the reference's launch it is asynchronous on the stream
+ * and allocates nothing (after the library's first call on a device); a chain with an operation
+ * outside the path fails to compile with a static_assert naming it, as an unsupported chain does
+ * in the reference.  Errors of the library are rethrown as std::runtime_error with the wording of
+ * the reference's gpuErrchk (core/utils/utils.h:95-109).
+ *
+ * Include after <fused_kernel/fused_kernel.h> and <fused_kernel/algorithms/algorithms.h>, in a
+ * translation unit compiled by nvcc (the reference defines Stream_<ParArch::GPU_NVIDIA> only there,
+ * core/execution_model/stream.h:50).  Needs only include/fkb200.h beside the reference's headers.
+ *
+ * Operations understood (anything else: static_assert):
+ *   reads      PerThreadRead<_2D, uchar3|float3>, ReadYUV<NV12>, Crop<Back>, Resize<INTER_LINEAR,
+ *              IGNORE_AR|PRESERVE_AR, Back>, BatchRead<B, PROCESS_ALL, ...>, FusedOperation_<...>
+ *   compute    Mul / Sub / Div / Add <float3>, Cast<uchar3,float3>, Cast<float3,int3|uint3>,
+ *              SaturateCast<float3,uchar3>, VectorReorder<T,2,1,0> (COLOR_RGB2BGR / COLOR_BGR2RGB),
+ *              ConvertYUVToRGB<NV12, Full, bt709, false, float3>
+ *   receivers  PerThreadWrite<_2D|_3D, T>, TensorWrite<T>, TensorSplit<float3>
+ */
+#ifndef FKB200_EXECUTOR_H
+#define FKB200_EXECUTOR_H
+
+#include <cstring>
+#include <stdexcept>
+#include <string>
+#include <type_traits>
+#include <vector>
+
+#include <fkb200.h>
+
+namespace fkb200 {
+
+/* The tag to pass as DPPType.  PAR_ARCH selects the stream type of fk::executeOperations' signature. */
+struct TransformDPP {
+    static constexpr fk::ParArch PAR_ARCH = fk::ParArch::GPU_NVIDIA;
+};
+
+namespace binding {
+
+template <typename T> struct dependent_false : std::false_type {};
+
+/* What is known about one batch plane while its read chain is walked from the outside in. */
+struct PlaneState {
+    fkb_plane plane{};
+    int src_format = 0;
+    int resize_mode = FKB_RESIZE_NONE;
+    float background[3] = {0.f, 0.f, 0.f};
+    std::vector<fkb_op> ops;
+    int n_pre_ops = 0;
+    bool has_crop = false;
+    /* what the reference's Resize::build derived on the host (resize.h:105-166), kept so that a caller
+       can compare it with what the library derives (fkb_derive_resize) */
+    fkb_resize_params reference_resize{};
+    bool has_reference_resize = false;
+};
+
+inline fkb_op make_op(int opcode, float a = 0.f, float b = 0.f, float c = 0.f) {
+    fkb_op o{};
+    o.opcode = opcode; o.p[0] = a; o.p[1] = b; o.p[2] = c;
+    return o;
+}
+
+/* ---- compute operations: LowerCompute<Op>::apply(state[, data]) appends to the plane's operation list ---- */
+template <typename Op, typename Enable = void>
+struct LowerCompute {
+    static_assert(dependent_false<Op>::value, "fkb200: this compute operation is not on the accelerated path");
+};
+template <typename P> struct LowerCompute<fk::Mul<float3, P, float3>> {
+    template <typename D> static void apply(PlaneState& st, const D& d) { st.ops.push_back(make_op(FKB_OP_MUL, d.params.x, d.params.y, d.params.z)); }
+};
+template <typename P> struct LowerCompute<fk::Sub<float3, P, float3>> {
+    template <typename D> static void apply(PlaneState& st, const D& d) { st.ops.push_back(make_op(FKB_OP_SUB, d.params.x, d.params.y, d.params.z)); }
+};
+template <typename P> struct LowerCompute<fk::Div<float3, P, float3>> {
+    template <typename D> static void apply(PlaneState& st, const D& d) { st.ops.push_back(make_op(FKB_OP_DIV, d.params.x, d.params.y, d.params.z)); }
+};
+template <typename P> struct LowerCompute<fk::Add<float3, P, float3, fk::BinaryType>> {
+    template <typename D> static void apply(PlaneState& st, const D& d) { st.ops.push_back(make_op(FKB_OP_ADD, d.params.x, d.params.y, d.params.z)); }
+};
+template <> struct LowerCompute<fk::Cast<uchar3, float3>> { static void apply(PlaneState& st) { st.ops.push_back(make_op(FKB_OP_CAST_F32)); } };
+template <> struct LowerCompute<fk::Cast<float3, int3>> { static void apply(PlaneState& st) { st.ops.push_back(make_op(FKB_OP_CAST_I32)); } };
+template <> struct LowerCompute<fk::Cast<float3, uint3>> { static void apply(PlaneState& st) { st.ops.push_back(make_op(FKB_OP_CAST_U32)); } };
+template <> struct LowerCompute<fk::SaturateCast<float3, uchar3>> { static void apply(PlaneState& st) { st.ops.push_back(make_op(FKB_OP_SATURATE_CAST_U8)); } };
+template <typename T> struct LowerCompute<fk::VectorReorder<T, 2, 1, 0>> { static void apply(PlaneState& st) { st.ops.push_back(make_op(FKB_OP_SWAP_RB)); } };
+template <> struct LowerCompute<fk::ConvertYUVToRGB<fk::PixelFormat::NV12, fk::ColorRange::Full, fk::ColorPrimitives::bt709, false, float3>> {
+    static void apply(PlaneState& st) { st.ops.push_back(make_op(FKB_OP_YUV_TO_RGB_BT709_FULL)); }
+};
+
+template <typename Op, typename Data>
+inline void lower_compute(PlaneState& st, const Data& d) {
+    if constexpr (fk::isUnaryType<Op>) LowerCompute<Op>::apply(st);
+    else LowerCompute<Op>::apply(st, d);
+}
+
+/* ---- read chains ---- */
+template <typename Op, typename Enable = void>
+struct LowerRead {
+    static_assert(dependent_false<Op>::value, "fkb200: this read operation is not on the accelerated path");
+};
+
+template <typename T> inline int source_format_of() {
+    if constexpr (std::is_same_v<T, uchar3>) return FKB_SRC_U8X3;
+    else if constexpr (std::is_same_v<T, float3>) return FKB_SRC_F32X3;
+    else { static_assert(dependent_false<T>::value, "fkb200: PerThreadRead of this element type is not on the accelerated path"); return 0; }
+}
+
+/* PerThreadRead<_2D, T> (memory_operations.h:71-112): params is the RawPtr of the image */
+template <typename T> struct LowerRead<fk::PerThreadRead<fk::ND::_2D, T>> {
+    template <typename D> static void apply(PlaneState& st, const D& d) {
+        st.src_format = source_format_of<T>();
+        st.plane.src = d.params.data;
+        st.plane.src_width = d.params.dims.width; st.plane.src_height = d.params.dims.height; st.plane.src_pitch = d.params.dims.pitch;
+        st.plane.crop_x = 0; st.plane.crop_y = 0;
+        st.plane.crop_width = (int32_t)d.params.dims.width; st.plane.crop_height = (int32_t)d.params.dims.height;
+    }
+};
+/* ReadYUV<NV12> (color_conversion.h:314-400): params is a RawImage whose luma RawPtr has dims.height rows and
+   whose chroma plane lies at data + pitch * dims.height (:336-341) */
+template <> struct LowerRead<fk::ReadYUV<fk::PixelFormat::NV12>> {
+    template <typename D> static void apply(PlaneState& st, const D& d) {
+        st.src_format = FKB_SRC_NV12;
+        st.plane.src = d.params.data.data;
+        st.plane.src_width = d.params.width; st.plane.src_height = d.params.data.dims.height; st.plane.src_pitch = d.params.data.dims.pitch;
+        st.plane.crop_x = 0; st.plane.crop_y = 0;
+        st.plane.crop_width = (int32_t)d.params.width; st.plane.crop_height = (int32_t)d.params.height;
+    }
+};
+/* Crop<Back> (crop.h:23-59): params is the Rect, backIOp the read below it */
+template <typename Back> struct LowerRead<fk::Crop<Back>> {
+    template <typename D> static void apply(PlaneState& st, const D& d) {
+        LowerRead<typename Back::Operation>::apply(st, d.backIOp);
+        if (st.resize_mode != FKB_RESIZE_NONE || !st.ops.empty())
+            throw std::runtime_error("fkb200: a Crop above a Resize or above compute operations is not on the accelerated path");
+        /* crops nest: a rect is relative to the crop below it (crop.h:35-38) */
+        st.plane.crop_x += (int32_t)d.params.x; st.plane.crop_y += (int32_t)d.params.y;
+        st.plane.crop_width = d.params.width; st.plane.crop_height = d.params.height;
+        st.has_crop = true;
+    }
+};
+/* Resize<INTER_LINEAR, AR, Back> (resize.h:61-222): params holds dstSize, the factors and - for PRESERVE_AR - the
+   region of interest and the default value that Resize::build computed on the host */
+template <fk::AspectRatio AR, typename Back> struct LowerRead<fk::Resize<fk::InterpolationType::INTER_LINEAR, AR, Back>> {
+    static_assert(AR == fk::AspectRatio::IGNORE_AR || AR == fk::AspectRatio::PRESERVE_AR,
+                  "fkb200: only IGNORE_AR and PRESERVE_AR resizes are on the accelerated path");
+    template <typename D> static void apply(PlaneState& st, const D& d) {
+        LowerRead<typename Back::Operation>::apply(st, d.backIOp);
+        if (st.resize_mode != FKB_RESIZE_NONE) throw std::runtime_error("fkb200: two Resize operations in one chain are not on the accelerated path");
+        st.n_pre_ops = (int)st.ops.size(); /* what the back operation computes runs on every tap, before the interpolation */
+        st.plane.dst_width = (uint32_t)d.params.dstSize.width; st.plane.dst_height = (uint32_t)d.params.dstSize.height;
+        st.reference_resize.fx = d.params.src_conv_factors.x; st.reference_resize.fy = d.params.src_conv_factors.y;
+        st.reference_resize.x1 = 0; st.reference_resize.y1 = 0;
+        st.reference_resize.x2 = d.params.dstSize.width - 1; st.reference_resize.y2 = d.params.dstSize.height - 1;
+        if constexpr (AR == fk::AspectRatio::PRESERVE_AR) {
+            st.resize_mode = FKB_RESIZE_PRESERVE_AR;
+            st.background[0] = d.params.defaultValue.x; st.background[1] = d.params.defaultValue.y; st.background[2] = d.params.defaultValue.z;
+            st.reference_resize.x1 = d.params.x1; st.reference_resize.y1 = d.params.y1;
+            st.reference_resize.x2 = d.params.x2; st.reference_resize.y2 = d.params.y2;
+        } else {
+            st.resize_mode = FKB_RESIZE_IGNORE_AR;
+        }
+        st.reference_resize.target_width = st.reference_resize.x2 - st.reference_resize.x1 + 1;
+        st.reference_resize.target_height = st.reference_resize.y2 - st.reference_resize.y1 + 1;
+        st.has_reference_resize = true;
+    }
+};
+
+/* OperationTuple<Ops...> (operation_tuple.h:22-67): `instance` exists for operations with parameters, `next`
+   unless everything from here on is unary, in which case only the types remain */
+template <typename Tuple> inline void walk_types_only(PlaneState& st) {
+    LowerCompute<typename Tuple::Operation>::apply(st);
+    if constexpr (Tuple::size > 1) walk_types_only<typename Tuple::Next>(st);
+}
+template <typename Tuple> inline void walk_compute_tuple(PlaneState& st, const Tuple& t) {
+    using Op = typename Tuple::Operation;
+    if constexpr (fk::isUnaryType<Op>) {
+        LowerCompute<Op>::apply(st);
+        if constexpr (Tuple::size > 1) {
+            if constexpr (std::is_empty_v<Tuple>) walk_types_only<typename Tuple::Next>(st);
+            else walk_compute_tuple(st, t.next);
+        }
+    } else {
+        LowerCompute<Op>::apply(st, t.instance);
+        if constexpr (Tuple::size > 1) walk_compute_tuple(st, t.next);
+    }
+}
+/* FusedOperation_<E, Read, Compute...> (fused_operation.h:136-329): a read followed by the continuation that .then()
+   fused onto it; params is the OperationTuple */
+template <typename E, typename First, typename... Rest> struct LowerRead<fk::FusedOperation_<E, First, Rest...>, std::enable_if_t<fk::isAnyReadType<First>>> {
+    template <typename D> static void apply(PlaneState& st, const D& d) {
+        LowerRead<First>::apply(st, d.params.instance);
+        if constexpr (sizeof...(Rest) > 0) {
+            using Tuple = std::decay_t<decltype(d.params)>;
+            if constexpr (std::is_empty_v<typename Tuple::Next>) walk_types_only<typename Tuple::Next>(st);
+            else walk_compute_tuple(st, d.params.next);
+        }
+    }
+};
+/* a fused continuation handed to executeOperations as one compute operation */
+template <typename E, typename First, typename... Rest> struct LowerCompute<fk::FusedOperation_<E, First, Rest...>, std::enable_if_t<fk::isComputeType<First>>> {
+    static void apply(PlaneState& st) { walk_types_only<fk::OperationTuple<First, Rest...>>(st); }
+    template <typename D> static void apply(PlaneState& st, const D& d) { walk_compute_tuple(st, d.params); }
+};
+
+/* ---- receivers ---- */
+struct Receiver {
+    void* data = nullptr;
+    uint32_t width = 0, height = 0, pitch = 0, planes = 1;
+    size_t plane_bytes = 0;        /* distance between the outputs of consecutive batch planes */
+    uint32_t channel_stride = 0;   /* TensorSplit: bytes between the channel planes of one output */
+    int dst_format = 0;
+};
+template <typename T> inline int packed_format_of() {
+    if constexpr (std::is_same_v<T, float3>) return FKB_DST_F32X3_PACKED;
+    else if constexpr (std::is_same_v<T, uchar3>) return FKB_DST_U8X3_PACKED;
+    else if constexpr (std::is_same_v<T, int3>) return FKB_DST_I32X3_PACKED;
+    else if constexpr (std::is_same_v<T, uint3>) return FKB_DST_U32X3_PACKED;
+    else { static_assert(dependent_false<T>::value, "fkb200: a receiver of this element type is not on the accelerated path"); return 0; }
+}
+template <typename Op, typename Enable = void>
+struct LowerWrite {
+    static_assert(dependent_false<Op>::value, "fkb200: this receiver is not on the accelerated path");
+};
+template <typename T> struct LowerWrite<fk::PerThreadWrite<fk::ND::_2D, T>> {
+    template <typename D> static Receiver apply(const D& d) {
+        Receiver r;
+        r.data = d.params.data; r.width = d.params.dims.width; r.height = d.params.dims.height; r.pitch = d.params.dims.pitch;
+        r.planes = 1; r.plane_bytes = (size_t)r.pitch * r.height; r.dst_format = packed_format_of<T>();
+        return r;
+    }
+};
+template <typename D> inline Receiver tensor_receiver(const D& d, int fmt) {
+    Receiver r;
+    r.data = d.params.data; r.width = d.params.dims.width; r.height = d.params.dims.height; r.pitch = d.params.dims.pitch;
+    r.planes = d.params.dims.planes;
+    /* plane z starts plane_pitch * color_planes * z bytes in (core/data/rawptr.h:222-225) */
+    r.plane_bytes = (size_t)d.params.dims.plane_pitch * d.params.dims.color_planes;
+    r.dst_format = fmt;
+    return r;
+}
+template <typename T> struct LowerWrite<fk::PerThreadWrite<fk::ND::_3D, T>> {
+    template <typename D> static Receiver apply(const D& d) { return tensor_receiver(d, packed_format_of<T>()); }
+};
+template <typename T> struct LowerWrite<fk::TensorWrite<T>> {
+    template <typename D> static Receiver apply(const D& d) { return tensor_receiver(d, packed_format_of<T>()); }
+};
+/* TensorSplit<float3> (memory_operations.h:195-226): channel c of a plane lies width*height elements further */
+template <> struct LowerWrite<fk::TensorSplit<float3>> {
+    template <typename D> static Receiver apply(const D& d) {
+        Receiver r = tensor_receiver(d, FKB_DST_F32_PLANAR3);
+        r.channel_stride = d.params.dims.width * d.params.dims.height * (uint32_t)sizeof(float);
+        return r;
+    }
+};
+
+/* ---- the whole call ---- */
+struct LoweredPlan {
+    std::vector<PlaneState> states;
+    std::vector<fkb_sequence> sequences;
+    std::vector<std::vector<fkb_op>> sequence_ops;
+    std::vector<fkb_plane> planes;
+
+    fkb_plan_desc desc() {
+        for (size_t s = 0; s < sequences.size(); ++s) sequences[s].ops = sequence_ops[s].empty() ? nullptr : sequence_ops[s].data();
+        return fkb_plan_desc{sequences.data(), (int32_t)sequences.size(), planes.data(), (int32_t)planes.size()};
+    }
+};
+
+/* the first operation: one plane, or BatchRead<B, PROCESS_ALL, Op> (batch_operations.h:135-210) whose params hold
+   one OperationData per plane (:98-102) */
+template <typename Op> struct LowerFirst {
+    template <typename D> static void apply(std::vector<PlaneState>& states, const D& d) {
+        states.emplace_back();
+        LowerRead<Op>::apply(states.back(), d);
+    }
+};
+template <size_t B, typename Op, typename Out> struct LowerFirst<fk::BatchRead<B, fk::PlanePolicy::PROCESS_ALL, Op, Out>> {
+    template <typename D> static void apply(std::vector<PlaneState>& states, const D& d) {
+        states.reserve(B);
+        for (size_t z = 0; z < B; ++z) {
+            states.emplace_back();
+            LowerRead<Op>::apply(states.back(), d.params.opData[z]);
+        }
+    }
+};
+
+template <typename IOp> inline void lower_middle(std::vector<PlaneState>& states, const IOp& iop) {
+    for (PlaneState& st : states) lower_compute<typename IOp::Operation>(st, iop);
+}
+
+inline bool same_sequence(const PlaneState& a, const fkb_sequence& q, const std::vector<fkb_op>& ops, int dst_format) {
+    if (a.src_format != q.src_format || dst_format != q.dst_format || a.resize_mode != q.resize_mode) return false;
+    if ((int)a.ops.size() != q.n_ops || (a.resize_mode == FKB_RESIZE_NONE ? 0 : a.n_pre_ops) != q.n_pre_ops) return false;
+    if (std::memcmp(a.background, q.background, sizeof a.background) != 0) return false;
+    for (size_t k = 0; k < ops.size(); ++k)
+        if (a.ops[k].opcode != ops[k].opcode || std::memcmp(a.ops[k].p, ops[k].p, sizeof ops[k].p) != 0) return false;
+    return true;
+}
+
+template <typename First, typename... Rest>
+inline LoweredPlan lower(const First& first, const Rest&... rest) {
+    static_assert(sizeof...(Rest) >= 1, "fkb200: a sender chain must be closed by a receiver");
+    LoweredPlan plan;
+    LowerFirst<typename First::Operation>::apply(plan.states, first);
+    /* everything between the read and the receiver continues every plane; the last one is the receiver */
+    Receiver recv;
+    size_t index = 0;
+    auto visit = [&](const auto& iop) {
+        using IOp = std::decay_t<decltype(iop)>;
+        if (++index == sizeof...(Rest)) {
+            if constexpr (fk::isWriteType<typename IOp::Operation>) recv = LowerWrite<typename IOp::Operation>::apply(iop);
+            else throw std::runtime_error("fkb200: the last operation must be a receiver");
+        } else {
+            if constexpr (fk::isWriteType<typename IOp::Operation>) throw std::runtime_error("fkb200: mid-chain writes are not on the accelerated path");
+            else lower_middle(plan.states, iop);
+        }
+    };
+    (visit(rest), ...);
+    if (recv.planes < plan.states.size()) throw std::runtime_error("fkb200: the receiver has fewer planes than the batch");
+    for (size_t z = 0; z < plan.states.size(); ++z) {
+        PlaneState& st = plan.states[z];
+        if (st.resize_mode == FKB_RESIZE_NONE) { st.plane.dst_width = (uint32_t)st.plane.crop_width; st.plane.dst_height = (uint32_t)st.plane.crop_height; }
+        if (st.plane.dst_width > recv.width || st.plane.dst_height > recv.height)
+            throw std::runtime_error("fkb200: the sender's output is larger than the receiver");
+        st.plane.dst = static_cast<unsigned char*>(recv.data) + z * recv.plane_bytes;
+        st.plane.dst_pitch = recv.pitch;
+        st.plane.dst_channel_stride = recv.channel_stride;
+        size_t s = 0;
+        for (; s < plan.sequences.size(); ++s)
+            if (same_sequence(st, plan.sequences[s], plan.sequence_ops[s], recv.dst_format)) break;
+        if (s == plan.sequences.size()) {
+            fkb_sequence q{};
+            q.src_format = st.src_format; q.dst_format = recv.dst_format; q.resize_mode = st.resize_mode;
+            q.n_ops = (int32_t)st.ops.size(); q.n_pre_ops = st.resize_mode == FKB_RESIZE_NONE ? 0 : st.n_pre_ops;
+            std::memcpy(q.background, st.background, sizeof q.background);
+            plan.sequences.push_back(q);
+            plan.sequence_ops.push_back(st.ops);
+        }
+        st.plane.sequence = (int32_t)s;
+        plan.planes.push_back(st.plane);
+    }
+    return plan;
+}
+
+inline void check(int status) {
+    if (status != FKB_OK)
+        throw std::runtime_error(std::string("GPU Error: ") + (fkb_last_error()[0] ? fkb_last_error() : fkb_status_string(status)));
+}
+
+}  // namespace binding
+}  // namespace fkb200
+
+namespace fk {
+
+/* The executor of the fkb200::TransformDPP tag: same shape as Executor<TransformDPP<ParArch::GPU_NVIDIA, TFEN>>
+   (executors.h:245-293), with the launch replaced by a call into libfkb200. */
+template <>
+struct Executor<fkb200::TransformDPP> {
+    FK_STATIC_STRUCT(Executor, Executor)
+private:
+    using Child = Executor<fkb200::TransformDPP>;
+    using Parent = BaseExecutor<Child>;
+
+    template <typename... IOps>
+    FK_HOST_FUSE void executeOperations_helper(Stream_<ParArch::GPU_NVIDIA>& stream_, const IOps&... iOps) {
+        fkb200::binding::LoweredPlan plan = fkb200::binding::lower(iOps...);
+        const fkb_plan_desc desc = plan.desc();
+        fkb200::binding::check(fkb_execute_async(&desc, stream_.getCUDAStream()));
+    }
+public:
+    FK_HOST_FUSE ParArch parArch() { return ParArch::GPU_NVIDIA; }
+    DECLARE_EXECUTOR_PARENT_IMPL
+};
+
+}  // namespace fk
+
+#endif /* FKB200_EXECUTOR_H */

@@ -1,0 +1,182 @@
+/* The reference-side binding (include/fkb200_executor.h) compiled against the UNMODIFIED reference headers.
+ *
+ * TEST INFRASTRUCTURE ONLY.  Compiled by oracle/Makefile with nvcc (the reference defines
+ * Stream_<ParArch::GPU_NVIDIA> only there) into oracle/_ref/libfklref_binding.so, which links
+ * libfkb200.so.  Every entry point builds a sender chain with the reference's REAL types, exactly as
+ * a user of the reference writes it - PerThreadRead<_2D, uchar3>::build(...).then(Crop<>::build(...))
+ * .then(Resize<...>::build(...))... - and then either
+ *   mode 0: runs it with fk::executeOperations<fkb200::TransformDPP>(stream, sender, receiver), i.e.
+ *           through the Executor specialisation of fkb200_executor.h and libfkb200's kernels, or
+ *   mode 1: only lowers it (no device is touched) and keeps the plan for inspection, so that a CPU
+ *           test can compare it with the plan the Python harness builds for the same chain.
+ * All image pointers are DEVICE pointers in mode 0; in mode 1 they are never dereferenced.
+ */
+#include <array>
+#include <cstdint>
+#include <cstring>
+#include <string>
+
+#include <fused_kernel/fused_kernel.h>
+#include <fused_kernel/algorithms/algorithms.h>
+#include <fused_kernel/algorithms/image_processing/image.h>
+
+#include <fkb200_executor.h>
+
+using namespace fk;
+
+namespace {
+
+thread_local fkb200::binding::LoweredPlan g_last;
+thread_local std::string g_error;
+
+constexpr auto LINEAR = InterpolationType::INTER_LINEAR;
+
+RawPtr<ND::_2D, uchar3> raw_u8x3(const void* d, int w, int h, int pitch) {
+    return RawPtr<ND::_2D, uchar3>{reinterpret_cast<uchar3*>(const_cast<void*>(d)), PtrDims<ND::_2D>((uint)w, (uint)h, (uint)pitch)};
+}
+template <typename T> RawPtr<ND::_3D, T> raw_tensor(void* d, int w, int h, int planes, int color_planes) {
+    return RawPtr<ND::_3D, T>{reinterpret_cast<T*>(d), PtrDims<ND::_3D>((uint)w, (uint)h, (uint)planes, (uint)color_planes, (uint)(sizeof(T) * w))};
+}
+float3 f3(const float* p) { return float3{p[0], p[1], p[2]}; }
+
+/* mode 0: execute through the binding; mode 1: lower only */
+template <typename... IOps> int run(int mode, void* stream, const IOps&... iops) {
+    try {
+        if (mode == 1) {
+            g_last = fkb200::binding::lower(iops...);
+            (void)g_last.desc();
+        } else {
+            Stream_<ParArch::GPU_NVIDIA> s(static_cast<cudaStream_t>(stream));
+            executeOperations<fkb200::TransformDPP>(s, iops...);
+        }
+        return 0;
+    } catch (const std::exception& e) {
+        g_error = e.what();
+        return -1;
+    }
+}
+
+template <size_t B, AspectRatio AR>
+auto cropped_resized(const void* const* frames, int w, int h, int pitch, const int* rects, int dw, int dh, const float* bg) {
+    std::array<RawPtr<ND::_2D, uchar3>, B> srcs;
+    std::array<Rect, B> crops;
+    for (size_t i = 0; i < B; ++i) {
+        srcs[i] = raw_u8x3(frames[i], w, h, pitch);
+        crops[i] = Rect(rects[4 * i + 0], rects[4 * i + 1], rects[4 * i + 2], rects[4 * i + 3]);
+    }
+    const auto cropped = PerThreadRead<ND::_2D, uchar3>::build(srcs).then(Crop<>::build(crops));
+    if constexpr (AR == AspectRatio::IGNORE_AR) return cropped.then(Resize<LINEAR, AR>::build(Size(dw, dh)));
+    else return cropped.then(Resize<LINEAR, AR>::build(Size(dw, dh), f3(bg)));
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* fklbind_last_error(void) { return g_error.c_str(); }
+
+/* the README example (README.md; tests/examples/readme_test_code.h:25-71): one frame, five crops, 60x60 */
+int fklbind_readme5(int mode, const void* frame, int w, int h, int pitch, const int* rects, const float* bg, const float* mul,
+                    const float* sub, const float* div, float* out, void* stream) {
+    const void* frames[5] = {frame, frame, frame, frame, frame};
+    const auto sender = cropped_resized<5, AspectRatio::PRESERVE_AR>(frames, w, h, pitch, rects, 60, 60, bg)
+                            .then(Mul<float3>::build(f3(mul)))
+                            .then(Sub<float3>::build(f3(sub)))
+                            .then(Div<float3>::build(f3(div)))
+                            .then(ColorConversion<ColorConversionCodes::COLOR_RGB2BGR, float3, float3>::build());
+    const auto receiver = TensorWrite<float3>::build(raw_tensor<float3>(out, 60, 60, 5, 1));
+    return run(mode, stream, sender, receiver);
+}
+
+/* 16 crops of several frames -> PRESERVE_AR dw x dh -> Div, Sub, Div -> TensorSplit (16 x 3 x dh x dw) */
+int fklbind_norm_planar16(int mode, const void* const* frames, int w, int h, int pitch, const int* rects, int dw, int dh,
+                          const float* bg, const float* d0, const float* mean, const float* stdv, float* out, void* stream) {
+    const auto sender = cropped_resized<16, AspectRatio::PRESERVE_AR>(frames, w, h, pitch, rects, dw, dh, bg)
+                            .then(Div<float3>::build(f3(d0)))
+                            .then(Sub<float3>::build(f3(mean)))
+                            .then(Div<float3>::build(f3(stdv)));
+    const auto receiver = TensorSplit<float3>::build(raw_tensor<float>(out, dw, dh, 16, 3));
+    return run(mode, stream, sender, receiver);
+}
+
+/* two NV12 frames -> ConvertYUVToRGB<Full, bt709> -> Resize dw x dh -> Div -> TensorWrite<float3> */
+int fklbind_nv12_2(int mode, const void* const* frames, int w, int h, int pitch, int dw, int dh, const float* div, float* out,
+                   void* stream) {
+    using Img = Image<PixelFormat::NV12>;
+    auto make = [&](size_t i) {
+        Ptr<ND::_2D, uchar> view(reinterpret_cast<uchar*>(const_cast<void*>(frames[i])), PtrDims<ND::_2D>((uint)w, (uint)h, (uint)pitch),
+                                 MemType::Device, 0);
+        return Img(view, (uint)w, (uint)h);
+    };
+    std::array<Img, 2> imgs{make(0), make(1)};
+    const auto sender = ReadYUV<PixelFormat::NV12>::build(imgs)
+                            .then(ConvertYUVToRGB<PixelFormat::NV12, ColorRange::Full, ColorPrimitives::bt709, false, float3>::build())
+                            .then(Resize<LINEAR>::build(Size(dw, dh)))
+                            .then(Div<float3>::build(f3(div)));
+    const auto receiver = TensorWrite<float3>::build(raw_tensor<float3>(out, dw, dh, 2, 1));
+    return run(mode, stream, sender, receiver);
+}
+
+/* one image, the operations handed over one by one (the parameter-pack form of fused_kernel.h:22-25) */
+int fklbind_cast_mul_sub_div(int mode, const void* src, int w, int h, int spitch, const float* mul, const float* sub, const float* div,
+                             float* dst, int dpitch, void* stream) {
+    const auto read = PerThreadRead<ND::_2D, uchar3>::build(raw_u8x3(src, w, h, spitch));
+    const auto write = PerThreadWrite<ND::_2D, float3>::build(
+        RawPtr<ND::_2D, float3>{reinterpret_cast<float3*>(dst), PtrDims<ND::_2D>((uint)w, (uint)h, (uint)dpitch)});
+    return run(mode, stream, read, Cast<uchar3, float3>::build(), Mul<float3>::build(f3(mul)), Sub<float3>::build(f3(sub)),
+               Div<float3>::build(f3(div)), write);
+}
+
+/* the shape of the reference's run-time test (tests/operation/test_instantiable_operations.h:236-264):
+   Cast -> Resize -> Add -> Cast<float3,uint3> -> PerThreadWrite<uint3> */
+int fklbind_cast_resize_add_cast_uint3(int mode, const void* src, int w, int h, int spitch, int dw, int dh, const float* add,
+                                       uint32_t* dst, int dpitch, void* stream) {
+    const auto sender = PerThreadRead<ND::_2D, uchar3>::build(raw_u8x3(src, w, h, spitch))
+                            .then(Cast<uchar3, float3>::build())
+                            .then(Resize<LINEAR>::build(Size(dw, dh)))
+                            .then(Add<float3>::build(f3(add)))
+                            .then(Cast<float3, uint3>::build());
+    const auto write = PerThreadWrite<ND::_2D, uint3>::build(
+        RawPtr<ND::_2D, uint3>{reinterpret_cast<uint3*>(dst), PtrDims<ND::_2D>((uint)dw, (uint)dh, (uint)dpitch)});
+    return run(mode, stream, sender, write);
+}
+
+/* RGB2BGR(uchar3) -> Cast -> Mul -> SaturateCast<float3,uchar3> -> PerThreadWrite<uchar3> */
+int fklbind_bgr_cast_mul_saturate(int mode, const void* src, int w, int h, int spitch, const float* mul, uint8_t* dst, int dpitch,
+                                  void* stream) {
+    const auto sender = PerThreadRead<ND::_2D, uchar3>::build(raw_u8x3(src, w, h, spitch))
+                            .then(ColorConversion<ColorConversionCodes::COLOR_RGB2BGR, uchar3, uchar3>::build())
+                            .then(Cast<uchar3, float3>::build())
+                            .then(Mul<float3>::build(f3(mul)))
+                            .then(SaturateCast<float3, uchar3>::build());
+    return run(mode, stream, sender, PerThreadWrite<ND::_2D, uchar3>::build(raw_u8x3(dst, w, h, dpitch)));
+}
+
+/* ---- inspection of the plan of the last mode-1 call on this thread ---- */
+int fklbind_last_counts(int* n_planes, int* n_sequences) {
+    *n_planes = (int)g_last.planes.size();
+    *n_sequences = (int)g_last.sequences.size();
+    return 0;
+}
+int fklbind_last_plane(int i, fkb_plane* out) {
+    if (i < 0 || i >= (int)g_last.planes.size()) return -1;
+    *out = g_last.planes[i];
+    return 0;
+}
+/* ops_out receives up to `capacity` operations; returns the sequence's operation count */
+int fklbind_last_sequence(int s, fkb_sequence* out, fkb_op* ops_out, int capacity) {
+    if (s < 0 || s >= (int)g_last.sequences.size()) return -1;
+    *out = g_last.sequences[s];
+    out->ops = nullptr;
+    const int n = (int)g_last.sequence_ops[s].size();
+    for (int k = 0; k < n && k < capacity; ++k) ops_out[k] = g_last.sequence_ops[s][k];
+    return n;
+}
+/* what the reference's own Resize::build stored in the operation (resize.h:105-166) for plane i */
+int fklbind_last_reference_resize(int i, fkb_resize_params* out) {
+    if (i < 0 || i >= (int)g_last.states.size() || !g_last.states[i].has_reference_resize) return -1;
+    *out = g_last.states[i].reference_resize;
+    return 0;
+}
+
+}  // extern "C"

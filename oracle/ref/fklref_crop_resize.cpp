@@ -61,6 +61,10 @@ void crop_resize_all(const uint8_t* const* frames, int w, int h, int pitch, cons
                      float* out) {
     const size_t plane_floats = (size_t)dw * dh * 3;
     int i = 0;
+    if (batch == 5) { /* the README example's own batch size (README.md; tests/examples/readme_test_code.h): one launch */
+        crop_resize_chunk<5, AR, TAIL>(frames, w, h, pitch, rects, dw, dh, bg, p0, p1, p2, out);
+        return;
+    }
 #if FKLREF_BIG_CHUNK > 16
     for (; i + FKLREF_BIG_CHUNK <= batch; i += FKLREF_BIG_CHUNK) {
         crop_resize_chunk<FKLREF_BIG_CHUNK, AR, TAIL>(frames + i, w, h, pitch, rects + 4 * i, dw, dh, bg, p0, p1, p2,

@@ -1,0 +1,157 @@
+"""include/fkb200_executor.h - the binding a maintainer of the reference adds next to executors.h - compiled
+against the reference's REAL operation types (oracle/ref/fklref_binding.cpp, built where the reference tree is
+present into oracle/_ref/libfklref_binding.so).
+
+CPU part: the plan the binding fills from `PerThreadRead<_2D,uchar3>::build(...).then(Crop<>::build(...))
+.then(Resize<...>::build(...))...` equals, field by field, the plan the Python harness builds for the same chain,
+and the resize factors and region of interest that the reference's Resize::build stored in its operation
+(resize.h:105-166) equal what the library derives (fkb_derive_resize), bit for bit.
+
+GPU part: fk::executeOperations<fkb200::TransformDPP>(stream, sender, receiver) produces, through libfkb200's
+kernels, the output of the reference's own CPU backend (oracle/_ref, device branch) bit for bit.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from fusedkernellibrary_b200 import abi, chains
+from fusedkernellibrary_b200.abi import op
+from oracle import binding_check as bc
+from oracle import reference as ref
+
+pytestmark = pytest.mark.skipif(not bc.available(), reason="oracle/_ref/libfklref_binding.so not built (reference tree absent)")
+
+PLANE_FIELDS = [f for f, _ in abi.Plane._fields_ if f != "reserved"]
+
+
+def _assert_same_plan(expected: abi.HostPlan, fkb_lib):
+    planes, seqs = bc.last_plan()
+    assert len(planes) == expected.n_planes
+    for i, (a, b) in enumerate(zip(planes, expected.planes)):
+        for f in PLANE_FIELDS:
+            assert getattr(a, f) == getattr(b, f), f"plane {i}.{f}: binding {getattr(a, f)} != harness {getattr(b, f)}"
+    d = expected.desc()
+    assert len(seqs) == d.n_sequences
+    for s, (q, ops) in enumerate(seqs):
+        e = d.sequences[s]
+        assert (q.src_format, q.dst_format, q.resize_mode, q.n_ops, q.n_pre_ops) == \
+               (e.src_format, e.dst_format, e.resize_mode, e.n_ops, e.n_pre_ops)
+        assert list(q.background) == list(e.background)
+        for k, o in enumerate(ops):
+            assert o.opcode == e.ops[k].opcode
+            if o.opcode in (abi.OP_MUL, abi.OP_SUB, abi.OP_DIV, abi.OP_ADD):
+                assert list(o.p) == list(e.ops[k].p)
+    # what the reference's Resize::build computed on the host == what the library derives
+    for i, p in enumerate(expected.planes):
+        rr = bc.last_reference_resize(i)
+        mode = d.sequences[p.sequence].resize_mode
+        if mode == abi.RESIZE_NONE:
+            assert rr is None
+            continue
+        ours = abi.ResizeParams()
+        assert fkb_lib.fkb_derive_resize(p.crop_width, p.crop_height, p.dst_width, p.dst_height, mode, C.byref(ours)) == 0
+        bits = lambda f: np.float32(f).view(np.uint32)
+        assert (bits(rr.fx), bits(rr.fy), rr.x1, rr.y1, rr.x2, rr.y2) == (bits(ours.fx), bits(ours.fy), ours.x1, ours.y1, ours.x2, ours.y2), i
+
+
+def test_readme_chain_lowers_to_the_harness_plan(fkb_lib):
+    frame, out = 0x10000000, 0x20000000       # never dereferenced when lowering
+    bc.readme5(bc.DESCRIBE, frame, 3840, 2160, 11520, chains.README_RECTS, (0, 0, 0), 1.4, 0.5, 255.0, out)
+    want = chains.crop_resize_batch(frame_ptrs=[frame], frame_index=[0] * 5, rects=chains.README_RECTS, src_width=3840,
+                                    src_height=2160, src_pitch=11520, dst=out, dst_width=60, dst_height=60,
+                                    post_ops=chains.readme_ops(), planar=False)
+    _assert_same_plan(want, fkb_lib)
+
+
+def test_batched_planar_chain_lowers_to_the_harness_plan(fkb_lib):
+    rng = np.random.default_rng(301)
+    rects = chains.random_rects(rng, 16, 3840, 2160, lo=16, hi=512)
+    rects[3] = (0, 0, 2, 1000)            # a target that rounds to zero columns (infinite factor in the reference)
+    frames = [0x10000000 + 0x2000000 * (i % 8) for i in range(8)]
+    fi = [i % 8 for i in range(16)]
+    out = 0x70000000
+    bc.norm_planar16(bc.DESCRIBE, [frames[i] for i in fi], 3840, 2160, 11520, rects, 224, 224, (0, 0, 0), 255.0,
+                     chains.IMAGENET_MEAN, chains.IMAGENET_STD, out)
+    want = chains.crop_resize_batch(frame_ptrs=frames, frame_index=fi, rects=rects, src_width=3840, src_height=2160,
+                                    src_pitch=11520, dst=out, dst_width=224, dst_height=224, post_ops=chains.normalize_ops(),
+                                    planar=True)
+    _assert_same_plan(want, fkb_lib)
+
+
+def test_nv12_chain_and_single_image_chains_lower_to_the_harness_plans(fkb_lib):
+    f0, f1, out = 0x10000000, 0x18000000, 0x20000000
+    bc.nv12_2(bc.DESCRIBE, [f0, f1], 3840, 2160, 3840, 1280, 720, 255.0, out)
+    _assert_same_plan(chains.nv12_resize_batch(frame_ptrs=[f0, f1], width=3840, height=2160, pitch=3840, dst=out, dst_width=1280,
+                                               dst_height=720), fkb_lib)
+    bc.cast_mul_sub_div(bc.DESCRIBE, f0, 1920, 1080, 5760, 1.4, 0.5, 255.0, out, 23040)
+    _assert_same_plan(chains.elementwise(chains.cast_mul_sub_div_ops(), src=f0, dst=out, width=1920, height=1080), fkb_lib)
+    bc.cast_resize_add_cast_uint3(bc.DESCRIBE, f0, 128, 128, 384, 32, 32, (3.0, 1.0, 32.0), out, 384)
+    want = abi.HostPlan()
+    s = want.add_sequence(abi.SRC_U8X3, abi.DST_U32X3_PACKED, abi.RESIZE_IGNORE_AR,
+                          [op(abi.OP_CAST_F32), op(abi.OP_ADD, (3.0, 1.0, 32.0)), op(abi.OP_CAST_U32)], n_pre_ops=1)
+    want.add_plane(src=f0, src_width=128, src_height=128, src_pitch=384, dst=out, dst_width=32, dst_height=32, dst_pitch=384, sequence=s)
+    _assert_same_plan(want, fkb_lib)
+    bc.bgr_cast_mul_saturate(bc.DESCRIBE, f0, 64, 32, 192, 1.4, out, 192)
+    _assert_same_plan(chains.elementwise([op(abi.OP_SWAP_RB), op(abi.OP_CAST_F32), op(abi.OP_MUL, 1.4), op(abi.OP_SATURATE_CAST_U8)],
+                                         src=f0, dst=out, width=64, height=32, dst_format=abi.DST_U8X3_PACKED), fkb_lib)
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(not ref.available(), reason="oracle/_ref not built")
+def test_reference_chains_through_the_binding_equal_the_reference_cpu_backend(fkb_lib):
+    torch = pytest.importorskip("torch")
+    rng = np.random.default_rng(302)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    same = lambda a, b: np.array_equal(np.ascontiguousarray(a).view(np.uint32), np.ascontiguousarray(b).view(np.uint32))
+    stream = torch.cuda.Stream()
+    sh = stream.cuda_stream
+
+    # README chain on a 4K frame
+    fw, fh = 3840, 2160
+    frame = rng.integers(0, 256, (fh, fw, 3), dtype=np.uint8)
+    d_frame = dev(frame)
+    d_out = torch.zeros((5, 60, 60, 3), dtype=torch.float32, device="cuda")
+    bc.readme5(bc.EXECUTE, d_frame.data_ptr(), fw, fh, fw * 3, chains.README_RECTS, (0, 0, 0), 1.4, 0.5, 255.0, d_out.data_ptr(), sh)
+    assert abi.async_check(sh) == 0
+    assert same(d_out.cpu().numpy(), ref.crop_resize_readme([frame], [0] * 5, chains.README_RECTS, 60, 60, (0, 0, 0), 1.4, 0.5, 255.0))
+
+    # batched crop -> resize -> normalise -> planar, 16 planes over 8 frames
+    frames = [rng.integers(0, 256, (540, 960, 3), dtype=np.uint8) for _ in range(8)]
+    rects = chains.random_rects(rng, 16, 960, 540, lo=16, hi=512)
+    rects[3] = (0, 0, 1, 500)
+    fi = [i % 8 for i in range(16)]
+    d_frames = [dev(f) for f in frames]
+    d_out = torch.zeros((16, 3, 224, 224), dtype=torch.float32, device="cuda")
+    bc.norm_planar16(bc.EXECUTE, [d_frames[i].data_ptr() for i in fi], 960, 540, 960 * 3, rects, 224, 224, (0, 0, 0), 255.0,
+                     chains.IMAGENET_MEAN, chains.IMAGENET_STD, d_out.data_ptr(), sh)
+    assert abi.async_check(sh) == 0
+    assert same(d_out.cpu().numpy(), ref.crop_resize_norm_planar(frames, fi, rects, 224, 224, (0, 0, 0), 255.0, chains.IMAGENET_MEAN,
+                                                                 chains.IMAGENET_STD))
+
+    # NV12 -> RGB -> resize
+    w, h, dw, dh = 1920, 1080, 640, 360
+    nv = [rng.integers(0, 256, (h + h // 2, w), dtype=np.uint8) for _ in range(2)]
+    d_nv = [dev(f) for f in nv]
+    d_out = torch.zeros((2, dh, dw, 3), dtype=torch.float32, device="cuda")
+    bc.nv12_2(bc.EXECUTE, [t.data_ptr() for t in d_nv], w, h, w, dw, dh, 255.0, d_out.data_ptr(), sh)
+    assert abi.async_check(sh) == 0
+    assert same(d_out.cpu().numpy(), ref.nv12_resize(nv, w, h, dw, dh, 255.0))
+
+    # one image, operations handed over one by one; and the uint3 ending of the reference's run-time test
+    img = rng.integers(0, 256, (270, 480, 3), dtype=np.uint8)
+    d_img = dev(img)
+    d_out = torch.zeros((270, 480, 3), dtype=torch.float32, device="cuda")
+    bc.cast_mul_sub_div(bc.EXECUTE, d_img.data_ptr(), 480, 270, 1440, 1.4, 0.5, 255.0, d_out.data_ptr(), 5760, sh)
+    assert abi.async_check(sh) == 0
+    assert same(d_out.cpu().numpy(), ref.cast_mul_sub_div(img, 1.4, 0.5, 255.0))
+    zero = torch.zeros((128, 128, 3), dtype=torch.uint8, device="cuda")
+    d_u = torch.zeros((32, 32, 3), dtype=torch.int32, device="cuda")
+    bc.cast_resize_add_cast_uint3(bc.EXECUTE, zero.data_ptr(), 128, 128, 384, 32, 32, (3.0, 1.0, 32.0), d_u.data_ptr(), 384, sh)
+    assert abi.async_check(sh) == 0
+    got = d_u.cpu().numpy()
+    assert (got[..., 0] == 3).all() and (got[..., 1] == 1).all() and (got[..., 2] == 32).all()
+    d_u8 = torch.zeros((270, 480, 3), dtype=torch.uint8, device="cuda")
+    bc.bgr_cast_mul_saturate(bc.EXECUTE, d_img.data_ptr(), 480, 270, 1440, 1.4, d_u8.data_ptr(), 1440, sh)
+    assert abi.async_check(sh) == 0
+    assert np.array_equal(d_u8.cpu().numpy(), ref.bgr_cast_mul_saturate(img, 1.4))
