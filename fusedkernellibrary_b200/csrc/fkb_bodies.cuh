@@ -1073,8 +1073,8 @@ __device__ __forceinline__ void body_nv12_staged(const DevPlane& P, const DevSeq
         return;
     }
 
-    /* shared memory: | mbarrier (16 B) | row table (32 B per row of the band) | luma flags | chroma
-       flags | luma rows | chroma rows | */
+    /* shared memory: | mbarrier (8 B) | row counts (8 B) | row table (32 B per row of the band) | luma flags |
+       chroma flags | the luma rows that are read, packed | the chroma rows that are read, packed | */
     uint64_t* const mbar_ptr = reinterpret_cast<uint64_t*>(staged_mem);
     float4* const row_tab = reinterpret_cast<float4*>(staged_mem + 16);
     unsigned char* const need_l = staged_mem + STAGED_HEADER_BYTES;
@@ -1105,43 +1105,85 @@ __device__ __forceinline__ void body_nv12_staged(const DevPlane& P, const DevSeq
     const uint32_t l_span = (uint32_t)(l_last - l_first + 1);
     const int c_first = l_first >> 1;
     const uint32_t c_span = (uint32_t)((l_last >> 1) - c_first + 1);
-    const uint32_t chroma_addr = stage_addr + l_span * row_len;
 
     if (tid == 0) {
         mbar_init(mbar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (tid < l_span) need_l[tid] = 0;
-    if (tid < c_span) need_c[tid] = 0;
+    /* flags over the band's span of source rows, in whole 8-byte words for the scan below */
+    if (tid < NV12_MAX_SPAN / 8) {
+        reinterpret_cast<uint2*>(need_l)[tid] = make_uint2(0u, 0u);
+        reinterpret_cast<uint2*>(need_c)[tid] = make_uint2(0u, 0u);
+    }
     __syncthreads();
-    if (tid <= (uint32_t)(yb - ya)) {
-        const Axis ay = make_axis(ya + (int)tid - y1, fy, crop_h);
+    const bool row_thread = tid <= (uint32_t)(yb - ya);
+    Axis ay = {0, 0, 0.0f, 0.0f};
+    if (row_thread) {
+        ay = make_axis(ya + (int)tid - y1, fy, crop_h);
         const int r0 = crop_y + ay.i0, r1 = crop_y + ay.i1;
         need_l[r0 - l_first] = 1;
         need_c[(r0 >> 1) - c_first] = 1;
         if (ay.w1 != 0.0f) { need_l[r1 - l_first] = 1; need_c[(r1 >> 1) - c_first] = 1; }
-        /* luma and chroma row addresses of the two vertical taps (16-bit offsets from the stage) */
-        const uint32_t a0 = (uint32_t)(r0 - l_first) * row_len, a1 = (uint32_t)(r1 - l_first) * row_len;
-        const uint32_t b0 = l_span * row_len + (uint32_t)((r0 >> 1) - c_first) * row_len;
-        const uint32_t b1 = l_span * row_len + (uint32_t)((r1 >> 1) - c_first) * row_len;
-        row_tab[2 * tid] = make_float4(__uint_as_float(stage_addr + a0), __uint_as_float(stage_addr + a1),
-                                       __uint_as_float(stage_addr + b0), __uint_as_float(stage_addr + b1));
-        row_tab[2 * tid + 1] = make_float4(ay.w0, ay.w0, ay.w1, ay.w1);
     }
     __syncthreads();
+    /* The rows that are read are packed in the stage: a flag becomes 1 + the row's slot (an exclusive prefix sum
+       over the flags; warp 0 takes the luma span, warp 1 the chroma span, eight flags per lane). */
+    uint32_t* const counts = reinterpret_cast<uint32_t*>(staged_mem + 8); /* needed luma rows, needed chroma rows */
+    if (tid < 64) {
+        unsigned char* const flags = tid < 32 ? need_l : need_c;
+        const uint32_t lane = tid & 31u;
+        const uint2 w = reinterpret_cast<const uint2*>(flags)[lane];
+        uint32_t f[8];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) { f[k] = (w.x >> (8 * k)) & 1u; f[4 + k] = (w.y >> (8 * k)) & 1u; }
+        uint32_t mine = 0;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) mine += f[k];
+        uint32_t incl = mine;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+            if (lane >= (uint32_t)d) incl += up;
+        }
+        uint32_t slot = incl - mine; /* rows needed before this lane's eight */
+        uint32_t o[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) { o[k] = f[k] ? slot + 1u : 0u; slot += f[k]; }
+        reinterpret_cast<uint2*>(flags)[lane] = make_uint2(o[0] | (o[1] << 8) | (o[2] << 16) | (o[3] << 24),
+                                                           o[4] | (o[5] << 8) | (o[6] << 16) | (o[7] << 24));
+        if (lane == 31) counts[tid >> 5] = incl;
+    }
+    __syncthreads();
+    const uint32_t n_luma = counts[0];
+    const uint32_t chroma_addr = stage_addr + n_luma * row_len;
+    if (row_thread) {
+        const int r0 = crop_y + ay.i0, r1 = crop_y + ay.i1;
+        /* shared-memory addresses of the luma and chroma rows of the two vertical taps; a second tap that is never
+           read (weight zero) points at the first tap's rows */
+        const bool two = ay.w1 != 0.0f;
+        const uint32_t a0 = (uint32_t)(need_l[r0 - l_first] - 1u) * row_len;
+        const uint32_t a1 = two ? (uint32_t)(need_l[r1 - l_first] - 1u) * row_len : a0;
+        const uint32_t b0 = (uint32_t)(need_c[(r0 >> 1) - c_first] - 1u) * row_len;
+        const uint32_t b1 = two ? (uint32_t)(need_c[(r1 >> 1) - c_first] - 1u) * row_len : b0;
+        row_tab[2 * tid] = make_float4(__uint_as_float(stage_addr + a0), __uint_as_float(stage_addr + a1),
+                                       __uint_as_float(chroma_addr + b0), __uint_as_float(chroma_addr + b1));
+        row_tab[2 * tid + 1] = make_float4(ay.w0, ay.w0, ay.w1, ay.w1);
+    }
     {
         const uint8_t* luma = P.src + (size_t)l_first * P.src_pitch + byte0;
         const uint8_t* chroma = P.src + (size_t)P.src_pitch * P.src_height + (size_t)c_first * P.src_pitch + byte0;
         for (uint32_t r = tid; r < l_span; r += nthreads) {
-            if (need_l[r]) {
+            const uint32_t s1 = need_l[r];
+            if (s1) {
                 mbar_expect_tx_only(mbar, row_len);
-                bulk_copy_g2s(stage_addr + r * row_len, luma + (size_t)r * P.src_pitch, row_len, mbar);
+                bulk_copy_g2s(stage_addr + (s1 - 1u) * row_len, luma + (size_t)r * P.src_pitch, row_len, mbar);
             }
         }
         for (uint32_t r = tid; r < c_span; r += nthreads) {
-            if (need_c[r]) {
+            const uint32_t s1 = need_c[r];
+            if (s1) {
                 mbar_expect_tx_only(mbar, row_len);
-                bulk_copy_g2s(chroma_addr + r * row_len, chroma + (size_t)r * P.src_pitch, row_len, mbar);
+                bulk_copy_g2s(chroma_addr + (s1 - 1u) * row_len, chroma + (size_t)r * P.src_pitch, row_len, mbar);
             }
         }
     }
@@ -1329,7 +1371,7 @@ __device__ __forceinline__ void run_body(uint32_t cls, const DevPlane& P, const 
  * five blocks (48 registers, no spills in the compiled chains): a 4K float3 Add took 37.6 us
  * unconstrained (three to four blocks) and 35.9 us at five, 64 alternating Add/Mul 76.6 and 65.7. */
 constexpr int min_blocks_of(uint32_t cls) {
-    return (cls == CLASS_RESIZE_U8_PLANAR_STAGED || cls == CLASS_RESIZE_U8_PACKED_STAGED) ? 4
+    return (cls == CLASS_RESIZE_U8_PLANAR_STAGED || cls == CLASS_RESIZE_U8_PACKED_STAGED) ? 5
            : cls == CLASS_RESIZE_NV12_PACKED_STAGED ? 5
            : cls == CLASS_MIXED ? 4
            : (cls == CLASS_FLAT_U8_F32 || cls == CLASS_FLAT_U8_U8 || cls == CLASS_FLAT_F32_F32) ? 5 : 1;

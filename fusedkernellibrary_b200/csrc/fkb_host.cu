@@ -724,6 +724,20 @@ static Nv12Tiling nv12_staged_tiling(const DevPlane& dp, uint32_t block_threads)
         const uint32_t byte0 = (uint32_t)sx_first & ~15u;
         row_len = std::max(row_len, std::min(((uint32_t)sx_last + 2u + 15u) & ~15u, dp.src_pitch) - byte0);
     }
+    /* Per output row, as the kernel finds them (binary32 product, floor, weight of the second tap): the source row
+       of the first vertical tap and whether the second tap is read at all (a weight of exactly zero is skipped). */
+    std::vector<int> tap0(n_rows);
+    std::vector<unsigned char> second(n_rows);
+    for (uint32_t r = 0; r < n_rows; ++r) {
+        volatile float s = (float)r * dp.fy;
+        const int i0 = (int)std::floor(s);
+        volatile float w1 = s - (float)i0;
+        tap0[r] = dp.crop_y + i0;
+        second[r] = w1 != 0.0f && i0 + 1 <= dp.crop_h - 1 ? 1 : 0; /* a clamped second tap is the first tap's row */
+    }
+    /* Rows a band must hold: the distinct luma rows and the distinct chroma rows its taps read (only those are
+       copied and they are packed); `span` is the distance between its first and last luma row, which sizes the
+       kernel's row-flag arrays. */
     auto worst = [&](uint32_t band, uint32_t& span) {
         uint32_t rows = 0;
         span = 0;
@@ -731,16 +745,24 @@ static Nv12Tiling nv12_staged_tiling(const DevPlane& dp, uint32_t block_threads)
             const uint32_t b = std::min(a + band, n_rows) - 1;
             const int first = dp.crop_y + staged_src_row((int)a, dp.fy);
             const int last = dp.crop_y + std::min(staged_src_row((int)b, dp.fy) + 1, dp.crop_h - 1);
-            const uint32_t l_span = (uint32_t)(last - first + 1), c_span = (uint32_t)((last >> 1) - (first >> 1) + 1);
-            rows = std::max(rows, l_span + c_span);
-            span = std::max(span, l_span);
+            uint32_t n_l = 0, n_c = 0;
+            int last_l = -1, last_c = -1;
+            for (uint32_t r = a; r <= b; ++r) {
+                for (int k = 0; k <= (int)second[r]; ++k) { /* rows come in non-decreasing order */
+                    const int l = tap0[r] + k;
+                    if (l > last_l) { ++n_l; last_l = l; }
+                    if ((l >> 1) > last_c) { ++n_c; last_c = l >> 1; }
+                }
+            }
+            rows = std::max(rows, n_l + n_c);
+            span = std::max(span, (uint32_t)(last - first + 1));
         }
         return rows;
     };
     uint32_t band = std::min<uint32_t>(STAGED_MAX_ROWS, n_rows), span = 0;
-    while (band > 1 && (worst(band, span) * row_len > NV12_MAX_STAGE_BYTES || span > NV12_MAX_SPAN)) --band;
-    const uint32_t rows = worst(band, span);
-    if (rows * row_len > NV12_MAX_STAGE_BYTES || span > NV12_MAX_SPAN) return t;
+    auto too_big = [&](uint32_t b) { const uint32_t rows = worst(b, span); return rows * row_len > NV12_MAX_STAGE_BYTES || rows > 250u || span > NV12_MAX_SPAN; };
+    while (band > 1 && too_big(band)) --band;
+    if (too_big(band)) return t;
     if (band > t.rs) band -= band % t.rs;
     t.band_rows = band;
     t.n_bands = (n_rows + band - 1) / band;
