@@ -108,6 +108,15 @@ class DebugCounters(C.Structure):
                 ("plans_lowered", C.c_uint64), ("plans_reused", C.c_uint64)]
 
 
+class MultiGpuShard(C.Structure):
+    _fields_ = [("device", C.c_int32), ("available", C.c_int32), ("first_plane", C.c_int32), ("n_planes", C.c_int32),
+                ("consolidated_output", C.c_void_p), ("consolidated_bytes", C.c_uint64), ("last_step_ms", C.c_float),
+                ("reserved", C.c_int32)]
+
+
+MULTI_GPU_DOWNLOAD, MULTI_GPU_GATHER = 1, 2
+
+
 def op(opcode: int, p=(0.0, 0.0, 0.0)) -> Op:
     if isinstance(p, (int, float)):
         p = (p, p, p)
@@ -189,7 +198,9 @@ EXPORTS = [
     "fkb_plan_get_resize_params", "fkb_plan_destroy", "fkb_execute", "fkb_host_session_create",
     "fkb_host_session_run", "fkb_host_session_get_traffic", "fkb_host_session_destroy",
     "fkb_execute_host", "fkb_execute_static", "fkb_plan_check", "fkb_plan_set_option", "fkb_execute_async",
-    "fkb_async_check", "fkb_debug_get_counters",
+    "fkb_async_check", "fkb_debug_get_counters", "fkb_assign_planes", "fkb_multi_gpu_session_create",
+    "fkb_multi_gpu_session_run", "fkb_multi_gpu_session_get_shard", "fkb_multi_gpu_session_destroy",
+    "fkb_debug_set_device_unavailable",
 ]
 
 
@@ -222,6 +233,12 @@ def load_library(path: os.PathLike | None = None) -> C.CDLL:
     lib.fkb_execute_async.argtypes = [C.POINTER(PlanDesc), C.c_void_p]
     lib.fkb_async_check.argtypes = [C.c_void_p, C.POINTER(C.c_uint32)]
     lib.fkb_debug_get_counters.argtypes = [C.POINTER(DebugCounters)]
+    lib.fkb_assign_planes.argtypes = [C.c_int32, C.c_int32, C.POINTER(C.c_uint8), C.POINTER(C.c_int32), C.POINTER(C.c_int32)]
+    lib.fkb_multi_gpu_session_create.argtypes = [C.POINTER(PlanDesc), C.c_int32, C.POINTER(C.c_int32), C.c_uint32, C.POINTER(C.c_void_p)]
+    lib.fkb_multi_gpu_session_run.argtypes = [C.c_void_p]
+    lib.fkb_multi_gpu_session_get_shard.argtypes = [C.c_void_p, C.c_int32, C.POINTER(MultiGpuShard)]
+    lib.fkb_multi_gpu_session_destroy.argtypes = [C.c_void_p]
+    lib.fkb_debug_set_device_unavailable.argtypes = [C.c_int32, C.c_int32]
     lib.fkb_execute.argtypes = [C.POINTER(PlanDesc), C.c_void_p]
     lib.fkb_execute_host.argtypes = [C.POINTER(PlanDesc), C.c_void_p]
     lib.fkb_execute_static.argtypes = [C.POINTER(PlanDesc), C.c_void_p]
@@ -361,6 +378,48 @@ class HostSession:
     def destroy(self) -> None:
         if self._h:
             self._lib.fkb_host_session_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
+
+
+def assign_planes(n_planes: int, n_devices: int, available=None) -> list[tuple[int, int]]:
+    """fkb_assign_planes: (first, count) per device; devices whose `available` entry is false get no planes."""
+    lib = load_library()
+    first, count = (C.c_int32 * n_devices)(), (C.c_int32 * n_devices)()
+    avail = None if available is None else (C.c_uint8 * n_devices)(*[1 if a else 0 for a in available])
+    check(lib.fkb_assign_planes(n_planes, n_devices, avail, first, count), "fkb_assign_planes")
+    return [(first[d], count[d]) for d in range(n_devices)]
+
+
+class MultiGpuSession:
+    """One batch over several GPUs of one box (fkb_multi_gpu_session_*): host buffers in, shards by plane."""
+
+    def __init__(self, host_plan: HostPlan, devices, flags: int = MULTI_GPU_DOWNLOAD):
+        self._lib = load_library()
+        self._h = C.c_void_p()
+        self.devices = list(devices)
+        desc = host_plan.desc()
+        arr = (C.c_int32 * len(self.devices))(*self.devices)
+        check(self._lib.fkb_multi_gpu_session_create(C.byref(desc), len(self.devices), arr, flags, C.byref(self._h)),
+              "fkb_multi_gpu_session_create")
+
+    def run(self) -> None:
+        check(self._lib.fkb_multi_gpu_session_run(self._h), "fkb_multi_gpu_session_run")
+
+    def shard(self, index: int) -> MultiGpuShard:
+        sh = MultiGpuShard()
+        check(self._lib.fkb_multi_gpu_session_get_shard(self._h, index, C.byref(sh)), "fkb_multi_gpu_session_get_shard")
+        return sh
+
+    def destroy(self) -> None:
+        if self._h:
+            self._lib.fkb_multi_gpu_session_destroy(self._h)
             self._h = C.c_void_p()
 
     def __del__(self):

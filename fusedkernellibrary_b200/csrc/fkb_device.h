@@ -213,6 +213,8 @@ inline ResizeTiling resize_tiling(uint32_t dst_w, uint32_t dst_h, int x1, int y1
  * all columns; its source footprint (whole crop rows, widened to 16-byte boundaries) sits in
  * shared memory behind a 16-byte mbarrier slot and a table of per-row vertical taps. */
 constexpr uint32_t STAGED_BAND_PIXELS = 7168; /* output pixels per band, about         */
+constexpr uint32_t STAGED_MIN_BAND_PIXELS = 448; /* bands of a plan with a small grid are halved down to this       */
+constexpr uint32_t SMALL_GRID_BLOCKS = 148;      /* fewer blocks than this (one per SM of a B200): shorter bands        */
 constexpr uint32_t STAGED_MAX_ROWS = 64;          /* output rows per band                        */
 constexpr uint32_t STAGED_MAX_STAGE_BYTES = 40 * 1024u; /* four blocks of it fit one SM */
 constexpr uint32_t STAGED_HEADER_BYTES = 16 + STAGED_MAX_ROWS * 32;

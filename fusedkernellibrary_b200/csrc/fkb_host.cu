@@ -6,8 +6,12 @@
  */
 #include <cuda_runtime.h>
 
+#include <dlfcn.h>
+
 #include <algorithm>
 #include <atomic>
+#include <condition_variable>
+#include <thread>
 #include <deque>
 #include <cstdarg>
 #include <cstdio>
@@ -636,7 +640,7 @@ static int staged_src_row(int r, float fy) { return (int)std::floor((float)r * f
 
 static bool region_empty(const DevPlane& dp) { return dp.x2 < dp.x1 || dp.y2 < dp.y1; }
 
-static StagedTiling staged_tiling(const DevPlane& dp, uint32_t block_threads) {
+static StagedTiling staged_tiling(const DevPlane& dp, uint32_t block_threads, uint32_t band_pixels = STAGED_BAND_PIXELS) {
     StagedTiling t;
     if (region_empty(dp)) { /* nothing to interpolate: store-only items alone */
         t.ok = true; t.gw = block_threads; t.rs = 1;
@@ -669,7 +673,7 @@ static StagedTiling staged_tiling(const DevPlane& dp, uint32_t block_threads) {
     /* Height limit: STAGED_MAX_ROWS rows, and about STAGED_BAND_PIXELS output pixels, so that a wide
        region is cut into more, shorter bands (their copies and arithmetic overlap across the blocks
        of an SM) while a narrow one stays in one block. */
-    const uint32_t by_pixels = std::max<uint32_t>(t.rs, (STAGED_BAND_PIXELS / (2u * pairs) + t.rs - 1) / t.rs * t.rs);
+    const uint32_t by_pixels = std::max<uint32_t>(t.rs, (band_pixels / (2u * pairs) + t.rs - 1) / t.rs * t.rs);
     uint32_t band = std::min<uint32_t>(std::min<uint32_t>(STAGED_MAX_ROWS, by_pixels), n_rows);
     {   /* first guess from the step, then exact */
         const double guess = ((double)max_src_rows - 2.0) / std::max((double)dp.fy, 1e-6) + 1.0;
@@ -993,11 +997,20 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
         std::vector<StagedTiling> st(img.planes.size());
         bool all = any_resize;
         uint32_t stage = 0;
-        for (size_t i = 0; i < img.planes.size() && all; ++i) {
-            if (kept_items[i] != 0) continue;
-            st[i] = staged_tiling(img.planes[i], staged_threads);
-            all = st[i].ok;
-            stage = std::max(stage, st[i].stage_bytes);
+        /* A plan with fewer blocks than the GPU has SMs (the README example: five planes of 60 x 60) is cut into
+           shorter bands, down to a few hundred pixels each: the launch is then bound by one short block per SM
+           instead of by a handful of long ones. */
+        for (uint32_t band_pixels = STAGED_BAND_PIXELS;; band_pixels /= 2) {
+            uint64_t bands = 0;
+            stage = 0;
+            for (size_t i = 0; i < img.planes.size() && all; ++i) {
+                if (kept_items[i] != 0) { bands += kept_items[i]; continue; }
+                st[i] = staged_tiling(img.planes[i], staged_threads, band_pixels);
+                all = st[i].ok;
+                stage = std::max(stage, st[i].stage_bytes);
+                bands += st[i].n_bands;
+            }
+            if (!all || bands >= SMALL_GRID_BLOCKS || band_pixels <= STAGED_MIN_BAND_PIXELS) break;
         }
         if (!all) img.planes = user_planes; /* the body that reads taps from global memory takes whole planes */
         if (all) {
@@ -1444,6 +1457,7 @@ struct fkb_host_session {
     };
     std::vector<Group> groups;
     std::vector<void*> dev_outputs;
+    bool external_output = false;      /* the output mirror belongs to the caller (multi-GPU session) */
     cudaStream_t out_stream = nullptr;
     cudaEvent_t start = nullptr, downloaded = nullptr;
     uint64_t h2d_bytes = 0, d2h_bytes = 0;
@@ -1456,7 +1470,7 @@ extern "C" FKB_API int fkb_host_session_destroy(fkb_host_session* s) {
         if (g.dev_src) device_free(g.dev_src);
         if (g.computed) cudaEventDestroy(g.computed);
     }
-    for (void* p : s->dev_outputs) if (p) device_free(p);
+    if (!s->external_output) for (void* p : s->dev_outputs) if (p) device_free(p);
     if (s->start) cudaEventDestroy(s->start);
     if (s->downloaded) cudaEventDestroy(s->downloaded);
     if (s->out_stream) cudaStreamDestroy(s->out_stream);
@@ -1464,7 +1478,16 @@ extern "C" FKB_API int fkb_host_session_destroy(fkb_host_session* s) {
     return FKB_OK;
 }
 
+/* ext_block != nullptr: the outputs are mirrored inside a device buffer of the caller's in which host address
+   ext_lo corresponds to ext_block (the consolidated tensor of a multi-GPU session); the outputs must then tile
+   one host range. */
+static int host_session_create(const fkb_plan_desc* desc, fkb_host_session** out, unsigned char* ext_block, uintptr_t ext_lo);
+
 extern "C" FKB_API int fkb_host_session_create(const fkb_plan_desc* desc, fkb_host_session** out) {
+    return host_session_create(desc, out, nullptr, 0);
+}
+
+static int host_session_create(const fkb_plan_desc* desc, fkb_host_session** out, unsigned char* ext_block, uintptr_t ext_lo) {
     if (!out) return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_host_session_create: out is NULL");
     *out = nullptr;
     {
@@ -1501,7 +1524,11 @@ extern "C" FKB_API int fkb_host_session_create(const fkb_plan_desc* desc, fkb_ho
        anything else is mirrored and copied plane by plane, row-exact. */
     const bool one_block = (hi - lo) == sum;
     unsigned char* block = nullptr;
-    if (one_block) {
+    if (ext_block) {
+        if (!one_block) return bail(fail(FKB_ERR_UNSUPPORTED, "a consolidated output needs outputs that tile one dense tensor"));
+        block = ext_block + (lo - ext_lo);
+        s->external_output = true;
+    } else if (one_block) {
         void* b = nullptr;
         const cudaError_t e = device_alloc(&b, hi - lo);
         if (e != cudaSuccess) return bail(fail_cuda(e, "output mirror allocation", __LINE__));
@@ -1610,9 +1637,23 @@ extern "C" FKB_API int fkb_host_session_create(const fkb_plan_desc* desc, fkb_ho
     return FKB_OK;
 }
 
+/* Uploads, launches and (if asked) copies back, without synchronising; `stream` ends up behind all of it. */
+static int host_session_enqueue(fkb_host_session* s, cudaStream_t stream, bool downloads);
+
 extern "C" FKB_API int fkb_host_session_run(fkb_host_session* s, void* stream_) {
     if (!s) return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_host_session_run: session is NULL");
     cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    const int rc = host_session_enqueue(s, stream, true);
+    if (rc) return rc;
+    FKB_CUDA(cudaStreamSynchronize(stream));
+    for (auto& g : s->groups) {
+        const int rs = fkb_plan_check(g.plan, stream, nullptr);
+        if (rs) return rs;
+    }
+    return FKB_OK;
+}
+
+static int host_session_enqueue(fkb_host_session* s, cudaStream_t stream, bool downloads) {
     /* the copy-back stream starts after whatever the caller already queued on `stream` */
     FKB_CUDA(cudaEventRecord(s->start, stream));
     FKB_CUDA(cudaStreamWaitEvent(s->out_stream, s->start, 0));
@@ -1620,6 +1661,7 @@ extern "C" FKB_API int fkb_host_session_run(fkb_host_session* s, void* stream_) 
         FKB_CUDA(cudaMemcpyAsync(g.dev_src, g.host_src, g.src_bytes, cudaMemcpyHostToDevice, stream));
         const int rc = fkb_plan_launch(g.plan, stream);
         if (rc) return rc;
+        if (!downloads) continue;
         FKB_CUDA(cudaEventRecord(g.computed, stream));
         FKB_CUDA(cudaStreamWaitEvent(s->out_stream, g.computed, 0));
         for (const auto& d : g.downloads) {
@@ -1629,11 +1671,6 @@ extern "C" FKB_API int fkb_host_session_run(fkb_host_session* s, void* stream_) 
     }
     FKB_CUDA(cudaEventRecord(s->downloaded, s->out_stream));
     FKB_CUDA(cudaStreamWaitEvent(stream, s->downloaded, 0));
-    FKB_CUDA(cudaStreamSynchronize(stream));
-    for (auto& g : s->groups) {
-        const int rc = fkb_plan_check(g.plan, stream, nullptr);
-        if (rc) return rc;
-    }
     return FKB_OK;
 }
 
@@ -1651,6 +1688,322 @@ extern "C" FKB_API int fkb_execute_host(const fkb_plan_desc* desc, void* stream)
     rc = fkb_host_session_run(s, stream);
     fkb_host_session_destroy(s);
     return rc;
+}
+
+/* ------------------------------------------------------------------------------------ */
+/* several GPUs of one box                                                              */
+/* ------------------------------------------------------------------------------------ */
+/* Every output plane depends on its own descriptor and one source image only (the reference indexes
+ * opData[thread.z] and nothing else, operation_model/batch_operations.h:153-160), so a batch shards by plane
+ * with no exchange step.  The reference's own multi-GPU support ends at a device ordinal on Ptr
+ * (core/data/ptr_nd.h:153-165); this session is the dispatcher around it: contiguous plane ranges, one host
+ * thread and one stream per device, each device uploads the images its planes read, runs its planes and - on
+ * request - copies its outputs back or exchanges them, so that every device holds the consolidated tensor. */
+
+extern "C" FKB_API int fkb_assign_planes(int32_t n_planes, int32_t n_devices, const uint8_t* available, int32_t* first,
+                                         int32_t* count) {
+    if (n_planes < 0 || n_devices <= 0 || !first || !count)
+        return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_assign_planes: bad argument");
+    int32_t usable = 0;
+    for (int32_t d = 0; d < n_devices; ++d) usable += (!available || available[d]) ? 1 : 0;
+    if (usable == 0) return fail(FKB_ERR_NO_DEVICE, "fkb_assign_planes: none of the %d devices is available", n_devices);
+    /* contiguous ranges in device order over the devices that answer; sizes differ by at most one plane, so the
+       outputs of consecutive devices are consecutive slabs of one tensor */
+    const int32_t base = n_planes / usable, extra = n_planes % usable;
+    int32_t next = 0, k = 0;
+    for (int32_t d = 0; d < n_devices; ++d) {
+        if (available && !available[d]) { first[d] = next; count[d] = 0; continue; }
+        first[d] = next;
+        count[d] = base + (k < extra ? 1 : 0);
+        next += count[d];
+        ++k;
+    }
+    return FKB_OK;
+}
+
+/* devices a test has declared unavailable (host-side failure injection; no GPU is touched to fake it) */
+static std::atomic<uint64_t> g_unavailable_mask{0};
+extern "C" FKB_API int fkb_debug_set_device_unavailable(int32_t device, int32_t unavailable) {
+    if (device < 0 || device >= 64) return FKB_ERR_INVALID_ARGUMENT;
+    if (unavailable) g_unavailable_mask.fetch_or(1ull << device);
+    else g_unavailable_mask.fetch_and(~(1ull << device));
+    return FKB_OK;
+}
+
+namespace {
+
+/* The handful of NCCL entry points the exchange needs, bound at run time so that the library loads where NCCL
+   is absent (the exchange is then refused, everything else works). */
+struct Nccl {
+    typedef struct ncclComm* comm_t;
+    int (*CommInitAll)(comm_t*, int, const int*) = nullptr;
+    int (*CommDestroy)(comm_t) = nullptr;
+    int (*GroupStart)() = nullptr;
+    int (*GroupEnd)() = nullptr;
+    int (*Broadcast)(const void*, void*, size_t, int /*ncclDataType_t*/, int, comm_t, cudaStream_t) = nullptr;
+    const char* (*GetErrorString)(int) = nullptr;
+    bool ok = false;
+};
+const Nccl& nccl() {
+    static Nccl n;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+        if (!h) return;
+        n.CommInitAll = reinterpret_cast<decltype(n.CommInitAll)>(dlsym(h, "ncclCommInitAll"));
+        n.CommDestroy = reinterpret_cast<decltype(n.CommDestroy)>(dlsym(h, "ncclCommDestroy"));
+        n.GroupStart = reinterpret_cast<decltype(n.GroupStart)>(dlsym(h, "ncclGroupStart"));
+        n.GroupEnd = reinterpret_cast<decltype(n.GroupEnd)>(dlsym(h, "ncclGroupEnd"));
+        n.Broadcast = reinterpret_cast<decltype(n.Broadcast)>(dlsym(h, "ncclBroadcast"));
+        n.GetErrorString = reinterpret_cast<decltype(n.GetErrorString)>(dlsym(h, "ncclGetErrorString"));
+        n.ok = n.CommInitAll && n.CommDestroy && n.GroupStart && n.GroupEnd && n.Broadcast && n.GetErrorString;
+    });
+    return n;
+}
+
+}  // namespace
+
+struct fkb_multi_gpu_session {
+    struct Shard {
+        int device = -1;
+        int32_t first = 0, count = 0;
+        fkb_host_session* session = nullptr;
+        unsigned char* consolidated = nullptr;  /* FKB_MULTI_GPU_GATHER: the whole output tensor on this device */
+        cudaStream_t stream = nullptr;
+        cudaEvent_t t0 = nullptr, t1 = nullptr;
+        Nccl::comm_t comm = nullptr;
+        std::thread worker;
+        int rc = FKB_OK;
+        std::string error;
+        float ms = 0.0f;
+    };
+    std::vector<Shard> shards;              /* one per device that takes part */
+    std::vector<int32_t> requested;         /* the devices as the caller listed them */
+    std::vector<int32_t> first, count;      /* per requested device */
+    uint32_t flags = 0;
+    uintptr_t host_lo = 0;
+    size_t out_bytes = 0;
+    std::vector<size_t> slab_off, slab_bytes; /* per shard: its slab of the consolidated tensor */
+    /* workers wait for `generation` to advance, run one step, and report through `done` */
+    std::mutex mu;
+    std::condition_variable cv_go, cv_done;
+    uint64_t generation = 0;
+    int done = 0;
+    bool quit = false;
+};
+
+static void multi_gpu_step(fkb_multi_gpu_session* m, size_t k) {
+    fkb_multi_gpu_session::Shard& sh = m->shards[k];
+    auto cuda = [&](cudaError_t e, const char* what) {
+        if (e != cudaSuccess && sh.rc == FKB_OK) { sh.rc = FKB_ERR_CUDA; sh.error = std::string(what) + ": " + cudaGetErrorString(e); }
+        return e == cudaSuccess;
+    };
+    sh.rc = FKB_OK;
+    sh.error.clear();
+    if (!cuda(cudaSetDevice(sh.device), "cudaSetDevice")) return;
+    cuda(cudaEventRecord(sh.t0, sh.stream), "cudaEventRecord");
+    if (sh.session) {
+        const int rc = host_session_enqueue(sh.session, sh.stream, (m->flags & FKB_MULTI_GPU_DOWNLOAD) != 0);
+        if (rc) { sh.rc = rc; sh.error = fkb_last_error(); }
+    }
+    if ((m->flags & FKB_MULTI_GPU_GATHER) && m->shards.size() > 1 && sh.rc == FKB_OK) {
+        /* every slab travels from the device that computed it into the same place of every other device's tensor:
+           one broadcast per slab, all of them in one group (an all-gather of slabs of unequal size), NCCL moves
+           them over NVLink into local memory; no kernel of this library ever reads a peer's memory */
+        const Nccl& n = nccl();
+        int e = n.GroupStart();
+        for (size_t r = 0; r < m->shards.size() && e == 0; ++r)
+            if (m->slab_bytes[r]) e = n.Broadcast(sh.consolidated + m->slab_off[r], sh.consolidated + m->slab_off[r], m->slab_bytes[r], 0 /* ncclChar */, (int)r, sh.comm, sh.stream);
+        const int e2 = n.GroupEnd();
+        if (e == 0) e = e2;
+        if (e != 0) { sh.rc = FKB_ERR_CUDA; sh.error = std::string("NCCL: ") + n.GetErrorString(e); }
+    }
+    cuda(cudaEventRecord(sh.t1, sh.stream), "cudaEventRecord");
+    cuda(cudaStreamSynchronize(sh.stream), "cudaStreamSynchronize");
+    if (sh.rc == FKB_OK) cuda(cudaEventElapsedTime(&sh.ms, sh.t0, sh.t1), "cudaEventElapsedTime");
+    if (sh.rc == FKB_OK && sh.session) {
+        for (auto& g : sh.session->groups) {
+            const int rc = fkb_plan_check(g.plan, sh.stream, nullptr);
+            if (rc) { sh.rc = rc; sh.error = fkb_last_error(); break; }
+        }
+    }
+}
+
+static void multi_gpu_worker(fkb_multi_gpu_session* m, size_t k) {
+    uint64_t seen = 0;
+    for (;;) {
+        {
+            std::unique_lock<std::mutex> lock(m->mu);
+            m->cv_go.wait(lock, [&] { return m->quit || m->generation != seen; });
+            if (m->quit) return;
+            seen = m->generation;
+        }
+        multi_gpu_step(m, k);
+        {
+            std::lock_guard<std::mutex> lock(m->mu);
+            ++m->done;
+        }
+        m->cv_done.notify_one();
+    }
+}
+
+extern "C" FKB_API int fkb_multi_gpu_session_destroy(fkb_multi_gpu_session* m) {
+    if (!m) return FKB_OK;
+    {
+        std::lock_guard<std::mutex> lock(m->mu);
+        m->quit = true;
+    }
+    m->cv_go.notify_all();
+    for (auto& sh : m->shards) if (sh.worker.joinable()) sh.worker.join();
+    for (auto& sh : m->shards) {
+        if (cudaSetDevice(sh.device) != cudaSuccess) { (void)cudaGetLastError(); continue; }
+        if (sh.comm) nccl().CommDestroy(sh.comm);
+        if (sh.session) fkb_host_session_destroy(sh.session);
+        if (sh.consolidated) device_free(sh.consolidated);
+        if (sh.t0) cudaEventDestroy(sh.t0);
+        if (sh.t1) cudaEventDestroy(sh.t1);
+        if (sh.stream) cudaStreamDestroy(sh.stream);
+    }
+    delete m;
+    return FKB_OK;
+}
+
+extern "C" FKB_API int fkb_multi_gpu_session_create(const fkb_plan_desc* desc, int32_t n_devices, const int32_t* devices, uint32_t flags,
+                                                    fkb_multi_gpu_session** out) {
+    if (!out) return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_multi_gpu_session_create: out is NULL");
+    *out = nullptr;
+    if (n_devices <= 0 || n_devices > 64 || !devices) return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_multi_gpu_session_create: between 1 and 64 devices");
+    if (flags & ~(uint32_t)(FKB_MULTI_GPU_DOWNLOAD | FKB_MULTI_GPU_GATHER)) return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_multi_gpu_session_create: unknown flag");
+    {
+        HostImage probe; /* validates the whole description before anything is allocated */
+        const int rc = lower(desc, probe);
+        if (rc) return rc;
+    }
+    int present = 0;
+    if (cudaGetDeviceCount(&present) != cudaSuccess) { (void)cudaGetLastError(); present = 0; }
+    int previous = -1;
+    if (present > 0) (void)cudaGetDevice(&previous);
+    /* which of the requested devices answer: a device that is missing, that a test declared unavailable, or
+       whose context cannot be created is left out and its planes go to the others */
+    std::vector<uint8_t> available((size_t)n_devices, 0);
+    for (int32_t d = 0; d < n_devices; ++d) {
+        const int32_t dev = devices[d];
+        if (dev < 0 || dev >= present || dev >= 64) continue;
+        if (g_unavailable_mask.load() & (1ull << dev)) continue;
+        if (cudaSetDevice(dev) != cudaSuccess || cudaFree(nullptr) != cudaSuccess) { (void)cudaGetLastError(); continue; }
+        available[d] = 1;
+    }
+    fkb_multi_gpu_session* m = new (std::nothrow) fkb_multi_gpu_session();
+    if (!m) return fail(FKB_ERR_INVALID_ARGUMENT, "out of host memory");
+    m->flags = flags;
+    m->requested.assign(devices, devices + n_devices);
+    m->first.assign((size_t)n_devices, 0);
+    m->count.assign((size_t)n_devices, 0);
+    int rc = fkb_assign_planes(desc->n_planes, n_devices, available.data(), m->first.data(), m->count.data());
+    auto bail = [&](int code) {
+        fkb_multi_gpu_session_destroy(m);
+        if (previous >= 0) (void)cudaSetDevice(previous);
+        return code;
+    };
+    if (rc) return bail(rc);
+
+    /* the consolidated tensor: the outputs must tile one host range; a device's slab is the range of its planes */
+    uintptr_t lo = UINTPTR_MAX, hi = 0;
+    std::vector<uintptr_t> plane_lo((size_t)desc->n_planes), plane_hi((size_t)desc->n_planes);
+    for (int i = 0; i < desc->n_planes; ++i) {
+        const fkb_plane& p = desc->planes[i];
+        const fkb_sequence& q = desc->sequences[p.sequence];
+        const size_t row = (size_t)p.dst_width * dst_pixel_bytes(q.dst_format);
+        const size_t bytes = (q.dst_format == FKB_DST_F32_PLANAR3 ? 2 * (size_t)p.dst_channel_stride : 0) + (size_t)p.dst_pitch * (p.dst_height - 1) + row;
+        plane_lo[i] = reinterpret_cast<uintptr_t>(p.dst);
+        plane_hi[i] = plane_lo[i] + bytes;
+        lo = std::min(lo, plane_lo[i]);
+        hi = std::max(hi, plane_hi[i]);
+    }
+    m->host_lo = lo;
+    m->out_bytes = hi - lo;
+    const bool gather = (flags & FKB_MULTI_GPU_GATHER) != 0;
+    if (gather && !nccl().ok) return bail(fail(FKB_ERR_UNSUPPORTED, "a consolidated output needs NCCL (libnccl.so.2 was not found)"));
+
+    for (int32_t d = 0; d < n_devices; ++d) {
+        if (!available[d]) continue;
+        m->shards.emplace_back();
+        fkb_multi_gpu_session::Shard& sh = m->shards.back();
+        sh.device = devices[d]; sh.first = m->first[d]; sh.count = m->count[d];
+    }
+    for (auto& sh : m->shards) {
+        uintptr_t a = UINTPTR_MAX, b = 0;
+        for (int32_t i = sh.first; i < sh.first + sh.count; ++i) { a = std::min(a, plane_lo[i]); b = std::max(b, plane_hi[i]); }
+        m->slab_off.push_back(sh.count ? a - lo : 0);
+        m->slab_bytes.push_back(sh.count ? b - a : 0);
+    }
+    for (auto& sh : m->shards) {
+        cudaError_t e = cudaSetDevice(sh.device);
+        if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&sh.stream, cudaStreamNonBlocking);
+        if (e == cudaSuccess) e = cudaEventCreate(&sh.t0);
+        if (e == cudaSuccess) e = cudaEventCreate(&sh.t1);
+        if (e == cudaSuccess && gather) {
+            void* p = nullptr;
+            e = device_alloc(&p, m->out_bytes);
+            sh.consolidated = static_cast<unsigned char*>(p);
+        }
+        if (e != cudaSuccess) return bail(fail_cuda(e, "multi-GPU session set-up", __LINE__));
+        if (sh.count > 0) {
+            fkb_plan_desc sub = *desc;
+            sub.planes = desc->planes + sh.first;
+            sub.n_planes = sh.count;
+            rc = host_session_create(&sub, &sh.session, sh.consolidated, lo);
+            if (rc) return bail(rc);
+        }
+    }
+    if (gather && m->shards.size() > 1) {
+        std::vector<Nccl::comm_t> comms(m->shards.size());
+        std::vector<int> devs;
+        for (auto& sh : m->shards) devs.push_back(sh.device);
+        const int e = nccl().CommInitAll(comms.data(), (int)devs.size(), devs.data());
+        if (e != 0) return bail(fail(FKB_ERR_CUDA, "ncclCommInitAll: %s", nccl().GetErrorString(e)));
+        for (size_t k = 0; k < m->shards.size(); ++k) m->shards[k].comm = comms[k];
+    }
+    for (size_t k = 0; k < m->shards.size(); ++k) m->shards[k].worker = std::thread(multi_gpu_worker, m, k);
+    if (previous >= 0) (void)cudaSetDevice(previous);
+    *out = m;
+    return FKB_OK;
+}
+
+extern "C" FKB_API int fkb_multi_gpu_session_run(fkb_multi_gpu_session* m) {
+    if (!m) return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_multi_gpu_session_run: session is NULL");
+    {
+        std::lock_guard<std::mutex> lock(m->mu);
+        m->done = 0;
+        ++m->generation;
+    }
+    m->cv_go.notify_all();
+    {
+        std::unique_lock<std::mutex> lock(m->mu);
+        m->cv_done.wait(lock, [&] { return m->done == (int)m->shards.size(); });
+    }
+    for (auto& sh : m->shards)
+        if (sh.rc != FKB_OK) return fail(sh.rc, "device %d: %s", sh.device, sh.error.c_str());
+    return FKB_OK;
+}
+
+extern "C" FKB_API int fkb_multi_gpu_session_get_shard(const fkb_multi_gpu_session* m, int32_t index, fkb_multi_gpu_shard* out) {
+    if (!m || !out) return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_multi_gpu_session_get_shard: NULL argument");
+    if (index < 0 || (size_t)index >= m->requested.size())
+        return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_multi_gpu_session_get_shard: device slot %d outside [0, %zu)", index, m->requested.size());
+    std::memset(out, 0, sizeof *out);
+    out->device = m->requested[(size_t)index];
+    out->first_plane = m->first[(size_t)index];
+    out->n_planes = m->count[(size_t)index];
+    for (const auto& sh : m->shards) {
+        if (sh.device != out->device) continue;
+        out->available = 1;
+        out->consolidated_output = sh.consolidated;
+        out->consolidated_bytes = sh.consolidated ? m->out_bytes : 0;
+        out->last_step_ms = sh.ms;
+    }
+    return FKB_OK;
 }
 
 /* ------------------------------------------------------------------------------------ */

@@ -8,15 +8,15 @@ launches a plan over its own planes only.
 from __future__ import annotations
 
 
-def plane_range(n_planes: int, world: int, rank: int) -> tuple[int, int]:
-    """Contiguous [first, first+count) of rank `rank`: sizes differ by at most one plane, and the
-    ranges of ranks 0..world-1 tile [0, n_planes) in order, so that each rank's outputs form one
-    contiguous slab of a consolidated tensor."""
+def plane_range(n_planes: int, world: int, rank: int, available=None) -> tuple[int, int]:
+    """Contiguous [first, first+count) of rank `rank` (the library's fkb_assign_planes): sizes differ by at
+    most one plane, and the ranges of ranks 0..world-1 tile [0, n_planes) in order, so that each rank's
+    outputs form one contiguous slab of a consolidated tensor.  Ranks whose `available` entry is false get
+    no planes; theirs go to the others."""
     if world <= 0 or not (0 <= rank < world) or n_planes < 0:
         raise ValueError("bad sharding arguments")
-    base, extra = divmod(n_planes, world)
-    first = rank * base + min(rank, extra)
-    return first, base + (1 if rank < extra else 0)
+    from . import abi
+    return abi.assign_planes(n_planes, world, available)[rank]
 
 
 def interleaved_planes(n_planes: int, world: int, rank: int) -> list[int]:

@@ -292,6 +292,46 @@ FKB_API int fkb_host_session_run(fkb_host_session* session, void* stream);
 FKB_API int fkb_host_session_get_traffic(const fkb_host_session* session, uint64_t* h2d_bytes, uint64_t* d2h_bytes);
 FKB_API int fkb_host_session_destroy(fkb_host_session* session);
 
+/* Several GPUs of one box.  Planes are independent (the reference indexes opData[thread.z] alone,
+ * operation_model/batch_operations.h:153-160), so a batch shards by plane with no exchange on the hot
+ * path; the reference itself stops at a device ordinal on Ptr (core/data/ptr_nd.h:153-165).
+ *
+ * fkb_assign_planes: contiguous plane ranges over the devices whose `available` byte is non-zero (NULL: all
+ * of them), sizes differing by at most one; a device that is not available gets count 0 and its planes go
+ * to the others.  Pure host arithmetic.
+ *
+ * A session takes a description with HOST pointers (like fkb_host_session_create) and a list of CUDA device
+ * ordinals.  Devices that do not answer when the session is made are left out and the planes are assigned
+ * over the rest (FKB_ERR_NO_DEVICE if none is left).  Each device that takes part gets one host thread and
+ * one stream; a step uploads the source images its planes read, launches its planes and, by flag,
+ *   FKB_MULTI_GPU_DOWNLOAD  copies its outputs back into the host buffers of the description,
+ *   FKB_MULTI_GPU_GATHER    exchanges the output slabs through NCCL (one broadcast per slab, in one group:
+ *                           an all-gather of slabs that may differ in size), so that every device holds the
+ *                           whole output tensor in its own memory; the outputs must tile one dense host range.
+ * run returns when every device has finished its step; times are per device, CUDA events on its stream. */
+#define FKB_MULTI_GPU_DOWNLOAD 1u
+#define FKB_MULTI_GPU_GATHER 2u
+typedef struct fkb_multi_gpu_session fkb_multi_gpu_session;
+typedef struct fkb_multi_gpu_shard {
+    int32_t device;            /* CUDA ordinal as listed at creation                                   */
+    int32_t available;         /* 0: left out (its planes were given to the others)                     */
+    int32_t first_plane;       /* the planes of the description this device runs                        */
+    int32_t n_planes;
+    void* consolidated_output; /* FKB_MULTI_GPU_GATHER: the whole output tensor in this device's memory */
+    uint64_t consolidated_bytes;
+    float last_step_ms;        /* device time of this device's part of the last run                     */
+    int32_t reserved;
+} fkb_multi_gpu_shard;
+FKB_API int fkb_assign_planes(int32_t n_planes, int32_t n_devices, const uint8_t* available, int32_t* first, int32_t* count);
+FKB_API int fkb_multi_gpu_session_create(const fkb_plan_desc* desc, int32_t n_devices, const int32_t* devices, uint32_t flags,
+                                         fkb_multi_gpu_session** out_session);
+FKB_API int fkb_multi_gpu_session_run(fkb_multi_gpu_session* session);
+FKB_API int fkb_multi_gpu_session_get_shard(const fkb_multi_gpu_session* session, int32_t index, fkb_multi_gpu_shard* out);
+FKB_API int fkb_multi_gpu_session_destroy(fkb_multi_gpu_session* session);
+/* For tests: declares a device ordinal unavailable to sessions made from now on (host-side failure
+ * injection; the device itself is not touched). */
+FKB_API int fkb_debug_set_device_unavailable(int32_t device, int32_t unavailable);
+
 /* One-shot fkb_host_session_create + run + destroy. */
 FKB_API int fkb_execute_host(const fkb_plan_desc* desc, void* stream);
 
