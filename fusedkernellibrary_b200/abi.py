@@ -23,11 +23,13 @@ ERR_NO_DEVICE = 5
 ERR_DEVICE_WAIT = 6
 
 # vocabulary ---------------------------------------------------------------------------
-SRC_U8X3, SRC_F32X3, SRC_NV12 = 1, 2, 3
+SRC_U8X3, SRC_F32X3, SRC_NV12, SRC_NV21 = 1, 2, 3, 4
 DST_F32X3_PACKED, DST_F32_PLANAR3, DST_U8X3_PACKED, DST_I32X3_PACKED, DST_U32X3_PACKED = 1, 2, 3, 4, 5
-RESIZE_NONE, RESIZE_IGNORE_AR, RESIZE_PRESERVE_AR = 0, 1, 2
+RESIZE_NONE, RESIZE_IGNORE_AR, RESIZE_PRESERVE_AR, RESIZE_PRESERVE_AR_RN_EVEN, RESIZE_PRESERVE_AR_LEFT = 0, 1, 2, 3, 4
+PLANE_DEFAULT_VALUE = 1
 (OP_MUL, OP_SUB, OP_DIV, OP_ADD, OP_CAST_F32, OP_SWAP_RB, OP_SATURATE_CAST_U8,
  OP_YUV_TO_RGB_BT709_FULL, OP_CAST_I32, OP_CAST_U32) = range(1, 11)
+OP_YUV_TO_RGB_BT601_FULL, OP_YUV_TO_RGB_BT2020_FULL = 11, 12
 PLAN_WAIT_LIMIT_US, PLAN_TEST_EXPECT_EXTRA_BYTES = 1, 2
 DEFAULT_WAIT_LIMIT_US = 100000
 ASYNC_ARENA_BYTES = 8 * 1024 * 1024
@@ -65,7 +67,7 @@ class Plane(C.Structure):
         ("dst_pitch", C.c_uint32),
         ("dst_channel_stride", C.c_uint32),
         ("sequence", C.c_int32),
-        ("reserved", C.c_int32),
+        ("flags", C.c_int32),
     ]
 
 
@@ -149,13 +151,13 @@ class HostPlan:
         return len(self._seqs) - 1
 
     def add_plane(self, *, src, src_width, src_height, src_pitch, dst, dst_width, dst_height,
-                  dst_pitch, dst_channel_stride=0, crop=None, sequence=0) -> int:
+                  dst_pitch, dst_channel_stride=0, crop=None, sequence=0, flags=0) -> int:
         p = Plane()
         p.src, p.src_width, p.src_height, p.src_pitch = src, src_width, src_height, src_pitch
         cx, cy, cw, ch = crop if crop is not None else (0, 0, src_width, src_height)
         p.crop_x, p.crop_y, p.crop_width, p.crop_height = int(cx), int(cy), int(cw), int(ch)
         p.dst, p.dst_width, p.dst_height, p.dst_pitch = dst, dst_width, dst_height, dst_pitch
-        p.dst_channel_stride, p.sequence, p.reserved = dst_channel_stride, sequence, 0
+        p.dst_channel_stride, p.sequence, p.flags = dst_channel_stride, sequence, flags
         self._planes.append(p)
         self._desc = None
         return len(self._planes) - 1

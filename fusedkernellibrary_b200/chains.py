@@ -72,12 +72,13 @@ def normalize_ops(mean=IMAGENET_MEAN, std=IMAGENET_STD):
 
 
 def nv12_resize_batch(*, frame_ptrs, width, height, pitch, dst, dst_width, dst_height, div=255.0, plan=None,
-                      mode=RESIZE_IGNORE_AR, background=(0.0, 0.0, 0.0), crops=None):
+                      mode=RESIZE_IGNORE_AR, background=(0.0, 0.0, 0.0), crops=None, src_format=SRC_NV12,
+                      conversion=OP_YUV_TO_RGB_BT709_FULL):
     """Config 4: ReadYUV<NV12>[B] -> ConvertYUVToRGB<bt709, Full, float3> -> Resize(IGNORE_AR) -> Div
-    -> TensorWrite<float3>.  `crops` (one rect per frame) and PRESERVE_AR are variations for tests."""
+    -> TensorWrite<float3>.  `crops` (one rect per frame), PRESERVE_AR, NV21 and the other matrices are variations."""
     plan = plan or abi.HostPlan()
-    seq = plan.add_sequence(SRC_NV12, DST_F32X3_PACKED, mode,
-                            [op(OP_YUV_TO_RGB_BT709_FULL), op(OP_DIV, div)], n_pre_ops=1, background=background)
+    seq = plan.add_sequence(src_format, DST_F32X3_PACKED, mode,
+                            [op(conversion), op(OP_DIV, div)], n_pre_ops=1, background=background)
     plane_bytes = dst_width * dst_height * 12
     for i, p in enumerate(frame_ptrs):
         plan.add_plane(src=p, src_width=width, src_height=height, src_pitch=pitch, dst=dst + i * plane_bytes,

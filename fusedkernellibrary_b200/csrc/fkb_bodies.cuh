@@ -93,6 +93,29 @@ __device__ __forceinline__ void yuv_to_rgb_bt709_full(float& a, float& b, float&
     c = __fadd_rn(y, __fmul_rn(u, 1.8556f));
 }
 
+/* ConvertYUVToRGB<PF, Full, bt601, false, float3>: the luma offset 16 is subtracted as well (:266-269), matrix :137-140.
+ * The dropped terms are no-ops for the same reasons: (y-16)*k is +0 or non-zero, so adding u*0 = +-0 leaves it; a sum
+ * of two finite terms is never -0 unless both are, and (y-16)*k is never -0. */
+__device__ __forceinline__ void yuv_to_rgb_bt601_full(float& a, float& b, float& c) {
+    const float y = __fmul_rn(__fsub_rn(a, 16.0f), 1.164383562f), u = __fsub_rn(b, 128.0f), v = __fsub_rn(c, 128.0f);
+    a = __fadd_rn(y, __fmul_rn(v, 1.596026786f));
+    b = __fadd_rn(__fadd_rn(y, __fmul_rn(u, -0.39176229f)), __fmul_rn(v, -0.812967647f));
+    c = __fadd_rn(y, __fmul_rn(u, 2.017232143f));
+}
+/* ConvertYUVToRGB<PF, Full, bt2020, false, float3>: matrix :165-168, otherwise as bt709. */
+__device__ __forceinline__ void yuv_to_rgb_bt2020_full(float& a, float& b, float& c) {
+    const float y = a, u = __fsub_rn(b, 128.0f), v = __fsub_rn(c, 128.0f);
+    a = __fadd_rn(y, __fmul_rn(v, 1.4746f));
+    b = __fadd_rn(__fadd_rn(y, __fmul_rn(u, -0.16455312684366f)), __fmul_rn(v, -0.57135312684366f));
+    c = __fadd_rn(y, __fmul_rn(u, 1.8814f));
+}
+/* The conversion a sequence asks for before the interpolation (block-uniform). */
+__device__ __forceinline__ void yuv_to_rgb(int pre_kind, float& a, float& b, float& c) {
+    if (pre_kind == PRE_YUV_BT709) yuv_to_rgb_bt709_full(a, b, c);
+    else if (pre_kind == PRE_YUV_BT601) yuv_to_rgb_bt601_full(a, b, c);
+    else if (pre_kind == PRE_YUV_BT2020) yuv_to_rgb_bt2020_full(a, b, c);
+}
+
 /* Packed binary32 arithmetic (sm_100): one instruction rounds two independent products, sums
  * or fused multiply-adds, each to nearest even exactly like the scalar instruction.  Values
  * travel as pairs of horizontally adjacent pixels, one pair per channel. */
@@ -140,7 +163,7 @@ __device__ __forceinline__ void apply_one(float2 (&v)[NPAIR * 3], const OpSlot* 
         }
         return;
     }
-    if (CODE == CH_SWAP || CODE == CH_SAT || CODE == CH_YUV) {
+    if (CODE == CH_SWAP || CODE == CH_SAT || CODE == CH_YUV || CODE == CH_YUV601 || CODE == CH_YUV2020) {
 #pragma unroll
         for (int j = 0; j < NPAIR; ++j) {
             float2& a = v[3 * j + 0];
@@ -152,8 +175,9 @@ __device__ __forceinline__ void apply_one(float2 (&v)[NPAIR * 3], const OpSlot* 
                 b = make_float2(saturate_round_u8(b.x), saturate_round_u8(b.y));
                 c = make_float2(saturate_round_u8(c.x), saturate_round_u8(c.y));
             } else {
-                yuv_to_rgb_bt709_full(a.x, b.x, c.x);
-                yuv_to_rgb_bt709_full(a.y, b.y, c.y);
+                constexpr int KIND = CODE == CH_YUV ? PRE_YUV_BT709 : CODE == CH_YUV601 ? PRE_YUV_BT601 : PRE_YUV_BT2020;
+                yuv_to_rgb(KIND, a.x, b.x, c.x);
+                yuv_to_rgb(KIND, a.y, b.y, c.y);
             }
         }
         return;
@@ -243,6 +267,8 @@ __device__ __forceinline__ void interpret_ops(float2 (&v)[NPAIR * 3], const OpSl
             case FKB_OP_SWAP_RB: apply_one<CH_SWAP, NPAIR>(v, sops + k, one); break;
             case FKB_OP_SATURATE_CAST_U8: apply_one<CH_SAT, NPAIR>(v, sops + k, one); break;
             case FKB_OP_YUV_TO_RGB_BT709_FULL: apply_one<CH_YUV, NPAIR>(v, sops + k, one); break;
+            case FKB_OP_YUV_TO_RGB_BT601_FULL: apply_one<CH_YUV601, NPAIR>(v, sops + k, one); break;
+            case FKB_OP_YUV_TO_RGB_BT2020_FULL: apply_one<CH_YUV2020, NPAIR>(v, sops + k, one); break;
             case FKB_OP_CAST_I32: apply_one<CH_CASTI, NPAIR>(v, sops + k, one); break;
             case FKB_OP_CAST_U32: apply_one<CH_CASTU, NPAIR>(v, sops + k, one); break;
             default: break;
@@ -286,7 +312,7 @@ __device__ __forceinline__ void run_ops_1(float (&v)[3], const OpSlot* __restric
  * and the U,V pair at (x>>1, y>>1) of the plane starting at base + pitch*height
  * (color_conversion.h:329-346). */
 template <int SRC>
-__device__ __forceinline__ void read_tap(const DevPlane& P, int a, int b, float& r0, float& r1, float& r2) {
+__device__ __forceinline__ void read_tap(const DevPlane& P, int a, int b, float& r0, float& r1, float& r2, bool swap_uv = false) {
     const int x = a + P.crop_x, y = b + P.crop_y;
     if (SRC == FKB_SRC_U8X3) {
         const uint8_t* p = P.src + (size_t)y * P.src_pitch + (size_t)x * 3;
@@ -298,15 +324,17 @@ __device__ __forceinline__ void read_tap(const DevPlane& P, int a, int b, float&
         const uint8_t* luma = P.src + (size_t)y * P.src_pitch + (size_t)x;
         const uint8_t* chroma = P.src + (size_t)P.src_pitch * P.src_height + (size_t)(y >> 1) * P.src_pitch +
                                 (size_t)(x >> 1) * 2;
-        r0 = u8_to_float(__ldg(luma)); r1 = u8_to_float(__ldg(chroma)); r2 = u8_to_float(__ldg(chroma + 1));
+        r0 = u8_to_float(__ldg(luma));
+        r1 = u8_to_float(__ldg(chroma + (swap_uv ? 1 : 0))); /* NV21 stores the pair as V,U (color_conversion.h:357-359) */
+        r2 = u8_to_float(__ldg(chroma + (swap_uv ? 0 : 1)));
     }
 }
 
-__device__ __forceinline__ void read_tap_any(int src_format, const DevPlane& P, int a, int b, float& r0, float& r1,
+__device__ __forceinline__ void read_tap_any(const DevSeq& S, const DevPlane& P, int a, int b, float& r0, float& r1,
                                              float& r2) {
-    if (src_format == FKB_SRC_U8X3) read_tap<FKB_SRC_U8X3>(P, a, b, r0, r1, r2);
-    else if (src_format == FKB_SRC_F32X3) read_tap<FKB_SRC_F32X3>(P, a, b, r0, r1, r2);
-    else read_tap<FKB_SRC_NV12>(P, a, b, r0, r1, r2);
+    if (S.src_format == FKB_SRC_U8X3) read_tap<FKB_SRC_U8X3>(P, a, b, r0, r1, r2);
+    else if (S.src_format == FKB_SRC_F32X3) read_tap<FKB_SRC_F32X3>(P, a, b, r0, r1, r2);
+    else read_tap<FKB_SRC_NV12>(P, a, b, r0, r1, r2, S.swap_uv != 0);
 }
 
 /* Bilinear geometry of one output coordinate: Resize::exec_resize (resize.h:183-194) and
@@ -345,8 +373,9 @@ __device__ __forceinline__ void body_generic(const DevPlane& P, const DevSeq& S,
     const float2 one = dup2(S.one);
     float v[3];
     int first_post = 0;
-    if (S.resize_mode == FKB_RESIZE_NONE) {
-        read_tap_any(S.src_format, P, x, y, v[0], v[1], v[2]);
+    /* a plane whose region is empty (a default-value plane, batch_operations.h:236-241) has no geometry stage either way */
+    if (S.resize_mode == FKB_RESIZE_NONE && P.x2 >= P.x1) {
+        read_tap_any(S, P, x, y, v[0], v[1], v[2]);
     } else {
         first_post = S.n_pre;
         /* Resize::exec (resize.h:75-87): outside the region of interest return the default */
@@ -356,10 +385,10 @@ __device__ __forceinline__ void body_generic(const DevPlane& P, const DevSeq& S,
             const Axis ax = make_axis(x - P.x1, P.fx, P.crop_w);
             const Axis ay = make_axis(y - P.y1, P.fy, P.crop_h);
             float t[4][3];
-            read_tap_any(S.src_format, P, ax.i0, ay.i0, t[0][0], t[0][1], t[0][2]);
-            read_tap_any(S.src_format, P, ax.i1, ay.i0, t[1][0], t[1][1], t[1][2]);
-            read_tap_any(S.src_format, P, ax.i0, ay.i1, t[2][0], t[2][1], t[2][2]);
-            read_tap_any(S.src_format, P, ax.i1, ay.i1, t[3][0], t[3][1], t[3][2]);
+            read_tap_any(S, P, ax.i0, ay.i0, t[0][0], t[0][1], t[0][2]);
+            read_tap_any(S, P, ax.i1, ay.i0, t[1][0], t[1][1], t[1][2]);
+            read_tap_any(S, P, ax.i0, ay.i1, t[2][0], t[2][1], t[2][2]);
+            read_tap_any(S, P, ax.i1, ay.i1, t[3][0], t[3][1], t[3][2]);
             if (S.pre_kind != PRE_IDENTITY) {
 #pragma unroll
                 for (int k = 0; k < 4; ++k) run_ops_1<CHAIN_INTERPRET>(t[k], sops, 0, S.n_pre, one);
@@ -653,7 +682,8 @@ __device__ __forceinline__ void body_resize(const DevPlane& P, const DevSeq& S, 
         const int crop_h = P.crop_h, crop_y = P.crop_y;
         const uint8_t* const src0 = SRC == FKB_SRC_NV12 ? P.src : P.src + (size_t)crop_y * src_pitch + (size_t)P.crop_x * 3;
         const uint8_t* const chroma0 = P.src + (size_t)src_pitch * P.src_height;
-        const bool yuv = S.pre_kind == PRE_YUV_BT709;
+        const int yuv = S.pre_kind; /* PRE_IDENTITY: no conversion */
+        const uint32_t u_at = S.swap_uv ? 1u : 0u, v_at = 1u - u_at; /* NV21: the pair is V,U */
 
 #pragma unroll 1
         for (int j = 0; j < RESIZE_ROWS_PER_THREAD; ++j) {
@@ -701,26 +731,26 @@ __device__ __forceinline__ void body_resize(const DevPlane& P, const DevSeq& S, 
                     const uint32_t xa = off0[i], xb = off1[i];
                     const uint32_t ca = (xa >> 1) * 2u, cb = (xb >> 1) * 2u;
                     float t[3];
-                    t[0] = u8_to_float(__ldg(l0 + xa)); t[1] = u8_to_float(__ldg(c0 + ca)); t[2] = u8_to_float(__ldg(c0 + ca + 1));
-                    if (yuv) yuv_to_rgb_bt709_full(t[0], t[1], t[2]);
+                    t[0] = u8_to_float(__ldg(l0 + xa)); t[1] = u8_to_float(__ldg(c0 + ca + u_at)); t[2] = u8_to_float(__ldg(c0 + ca + v_at));
+                    yuv_to_rgb(yuv, t[0], t[1], t[2]);
                     const float w00 = __fmul_rn(wxa, ay.w0);
                     float acc[3] = {__fmul_rn(t[0], w00), __fmul_rn(t[1], w00), __fmul_rn(t[2], w00)};
                     if (need_col1) {
-                        t[0] = u8_to_float(__ldg(l0 + xb)); t[1] = u8_to_float(__ldg(c0 + cb)); t[2] = u8_to_float(__ldg(c0 + cb + 1));
-                        if (yuv) yuv_to_rgb_bt709_full(t[0], t[1], t[2]);
+                        t[0] = u8_to_float(__ldg(l0 + xb)); t[1] = u8_to_float(__ldg(c0 + cb + u_at)); t[2] = u8_to_float(__ldg(c0 + cb + v_at));
+                        yuv_to_rgb(yuv, t[0], t[1], t[2]);
                         const float w10 = __fmul_rn(wxb, ay.w0);
 #pragma unroll
                         for (int c = 0; c < 3; ++c) acc[c] = __fadd_rn(acc[c], __fmul_rn(t[c], w10));
                     }
                     if (need_row1) {
-                        t[0] = u8_to_float(__ldg(l1 + xa)); t[1] = u8_to_float(__ldg(c1 + ca)); t[2] = u8_to_float(__ldg(c1 + ca + 1));
-                        if (yuv) yuv_to_rgb_bt709_full(t[0], t[1], t[2]);
+                        t[0] = u8_to_float(__ldg(l1 + xa)); t[1] = u8_to_float(__ldg(c1 + ca + u_at)); t[2] = u8_to_float(__ldg(c1 + ca + v_at));
+                        yuv_to_rgb(yuv, t[0], t[1], t[2]);
                         const float w01 = __fmul_rn(wxa, ay.w1);
 #pragma unroll
                         for (int c = 0; c < 3; ++c) acc[c] = __fadd_rn(acc[c], __fmul_rn(t[c], w01));
                         if (need_col1) {
-                            t[0] = u8_to_float(__ldg(l1 + xb)); t[1] = u8_to_float(__ldg(c1 + cb)); t[2] = u8_to_float(__ldg(c1 + cb + 1));
-                            if (yuv) yuv_to_rgb_bt709_full(t[0], t[1], t[2]);
+                            t[0] = u8_to_float(__ldg(l1 + xb)); t[1] = u8_to_float(__ldg(c1 + cb + u_at)); t[2] = u8_to_float(__ldg(c1 + cb + v_at));
+                            yuv_to_rgb(yuv, t[0], t[1], t[2]);
                             const float w11 = __fmul_rn(wxb, ay.w1);
 #pragma unroll
                             for (int c = 0; c < 3; ++c) acc[c] = __fadd_rn(acc[c], __fmul_rn(t[c], w11));
@@ -1206,7 +1236,8 @@ __device__ __forceinline__ void body_nv12_staged(const DevPlane& P, const DevSeq
     const uint32_t ca0 = (((uint32_t)(crop_x + axa.i0) >> 1) << 1) - byte0, ca1 = (((uint32_t)(crop_x + axa.i1) >> 1) << 1) - byte0;
     const uint32_t cb0 = (((uint32_t)(crop_x + axb.i0) >> 1) << 1) - byte0, cb1 = (((uint32_t)(crop_x + axb.i1) >> 1) << 1) - byte0;
     const bool col1_a = axa.w1 != 0.0f, col1_b = axb.w1 != 0.0f;
-    const bool yuv = S.pre_kind == PRE_YUV_BT709;
+    const int yuv = S.pre_kind; /* PRE_IDENTITY: no conversion */
+    const uint32_t u_shift = S.swap_uv ? 8u : 0u, v_shift = 8u - u_shift; /* NV21: the pair is V,U */
 
     if (!mbar_wait_bounded(mbar, 0, wc.limit_us)) {
         atomicExch(wc.status, STATUS_STAGED_WAIT_TIMEOUT);
@@ -1218,9 +1249,9 @@ __device__ __forceinline__ void body_nv12_staged(const DevPlane& P, const DevSeq
     auto tap = [&](uint32_t l_addr, uint32_t c_addr, float (&t)[3]) {
         const uint32_t uv = lds_u16(c_addr);
         t[0] = byte_to_float(lds_u8(l_addr));
-        t[1] = byte_to_float(uv);
-        t[2] = byte_to_float(uv >> 8);
-        if (yuv) yuv_to_rgb_bt709_full(t[0], t[1], t[2]);
+        t[1] = byte_to_float(uv >> u_shift);
+        t[2] = byte_to_float(uv >> v_shift);
+        yuv_to_rgb(yuv, t[0], t[1], t[2]);
     };
     /* interpolated value of one column in the row described by rows / wy */
     auto column = [&](const float4& rows, const float4& wy, uint32_t l0, uint32_t l1, uint32_t c0, uint32_t c1, float w0x,

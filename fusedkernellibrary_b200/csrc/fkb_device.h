@@ -73,14 +73,16 @@ struct alignas(16) DevSeq {
     float bg[3];
     float one;                       /* 1.0f, read at run time by the packed additions         */
     float bg_out[3];                 /* bg after the operations that follow the geometry stage  */
-    float pad;
+    uint32_t swap_uv;                /* 1: the chroma pair of a tap is stored V,U (NV21)         */
 };
 static_assert(sizeof(DevSeq) == 64, "DevSeq layout");
 
 enum PreKind : int32_t {
     PRE_IDENTITY = 0, /* nothing, or only exact uchar->float casts, before interpolation      */
     PRE_YUV_BT709 = 1,/* exactly ConvertYUVToRGB<NV12,Full,bt709,false,float3>                */
-    PRE_GENERAL = 2   /* any other chain: interpreted per tap (generic class only)           */
+    PRE_GENERAL = 2,  /* any other chain: interpreted per tap (generic class only)           */
+    PRE_YUV_BT601 = 3,/* exactly ConvertYUVToRGB<PF,Full,bt601,false,float3>                   */
+    PRE_YUV_BT2020 = 4/* exactly ConvertYUVToRGB<PF,Full,bt2020,false,float3>                  */
 };
 
 constexpr int INLINE_MAX_OPS = 16;
@@ -228,7 +230,7 @@ constexpr uint32_t STATUS_STAGED_WAIT_TIMEOUT = 1; /* a bulk copy did not comple
  * FKB_CHAIN_MENU; any other sequence runs through the interpreter (CHAIN_INTERPRET). */
 
 constexpr uint32_t CH_MUL = 1, CH_SUB = 2, CH_DIV = 3, CH_ADD = 4, CH_SWAP = 6, CH_SAT = 7, CH_YUV = 8, CH_DIVC = 9,
-                   CH_CASTI = 10, CH_CASTU = 11;
+                   CH_CASTI = 10, CH_CASTU = 11, CH_YUV601 = 12, CH_YUV2020 = 13;
 #if defined(__CUDACC__)
 __host__ __device__
 #endif

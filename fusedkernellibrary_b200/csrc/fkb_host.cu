@@ -205,19 +205,22 @@ extern "C" FKB_API int fkb_derive_resize(int32_t sw, int32_t sh, int32_t dw, int
         return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_derive_resize: sizes must be positive (%d x %d -> %d x %d)", sw, sh,
                     dw, dh);
     int tw = dw, th = dh;
-    if (mode == FKB_RESIZE_PRESERVE_AR) {
+    if (mode == FKB_RESIZE_PRESERVE_AR || mode == FKB_RESIZE_PRESERVE_AR_RN_EVEN || mode == FKB_RESIZE_PRESERVE_AR_LEFT) {
         /* compute_target_size (resize.h:196-221): fit the height first, fall back to fitting
-           the width when the scaled width overflows. */
+           the width when the scaled width overflows.  RN_EVEN rounds the fitted width down to an
+           even number before the comparison, and the fitted height when the width is the limit. */
         volatile float scale = static_cast<float>(dh) / static_cast<float>(sh);
         volatile float scaled_w = scale * static_cast<float>(sw);
         tw = static_cast<int>(round_half_away(scaled_w));
+        if (mode == FKB_RESIZE_PRESERVE_AR_RN_EVEN) tw -= tw % 2;
         if (tw > dw) {
             volatile float scale_w = static_cast<float>(dw) / static_cast<float>(sw);
             volatile float scaled_h = scale_w * static_cast<float>(sh);
             tw = dw;
             th = static_cast<int>(round_half_away(scaled_h));
+            if (mode == FKB_RESIZE_PRESERVE_AR_RN_EVEN) th -= th % 2;
         }
-        out->x1 = (dw - tw) / 2; /* resize.h:150-151 */
+        out->x1 = mode == FKB_RESIZE_PRESERVE_AR_LEFT ? 0 : (dw - tw) / 2; /* resize.h:132-133,150-151 */
         out->y1 = (dh - th) / 2;
         out->x2 = out->x1 + tw - 1;
         out->y2 = out->y1 + th - 1;
@@ -380,6 +383,10 @@ static bool advance_range(ValueRange& v, const fkb_op& op) {
                coefficient is 0.1873, so every product and sum is a multiple of 2^-26 */
             if (v.known) v = ValueRange{true, 512.0, -26, -26, false, false};
             break;
+        case FKB_OP_YUV_TO_RGB_BT601_FULL: case FKB_OP_YUV_TO_RGB_BT2020_FULL:
+            /* the same with coefficients down to 0.16 and up to 2.02: multiples of 2^-26 below 1024 */
+            if (v.known) v = ValueRange{true, 1024.0, -26, -26, false, false};
+            break;
         default: /* CAST_F32, SWAP_RB: values unchanged */
             break;
     }
@@ -459,6 +466,8 @@ static uint32_t chain_code_of(int dev_opcode) {
         case FKB_OP_SWAP_RB: return CH_SWAP;
         case FKB_OP_SATURATE_CAST_U8: return CH_SAT;
         case FKB_OP_YUV_TO_RGB_BT709_FULL: return CH_YUV;
+        case FKB_OP_YUV_TO_RGB_BT601_FULL: return CH_YUV601;
+        case FKB_OP_YUV_TO_RGB_BT2020_FULL: return CH_YUV2020;
         case DEV_OP_DIV_BY_CONSTANT: return CH_DIVC;
         case FKB_OP_CAST_I32: return CH_CASTI;
         case FKB_OP_CAST_U32: return CH_CASTU;
@@ -478,7 +487,7 @@ static uint32_t lower_ops(const fkb_sequence& s, int n_pre, int step_exp_x, int 
     int chain_len = 0;
     for (int k = 0; k <= s.n_ops; ++k) {
         if (k == n_pre && s.resize_mode != FKB_RESIZE_NONE) {
-            advance_range_resize(v, step_exp_x, step_exp_y, s.resize_mode == FKB_RESIZE_PRESERVE_AR, s.background);
+            advance_range_resize(v, step_exp_x, step_exp_y, s.resize_mode >= FKB_RESIZE_PRESERVE_AR, s.background);
             dev_n_pre = (int)out.size();
             chain = 0; chain_len = 0;
         }
@@ -555,16 +564,20 @@ static uint32_t lower_ops(const fkb_sequence& s, int n_pre, int step_exp_x, int 
 enum ValueType { VT_U8 = 0, VT_F32 = 1, VT_YUV8 = 2, VT_I32 = 3, VT_U32 = 4 };
 
 static uint32_t src_pixel_bytes(int f) { return f == FKB_SRC_U8X3 ? 3u : f == FKB_SRC_F32X3 ? 12u : 1u; }
+static bool is_yuv_source(int f) { return f == FKB_SRC_NV12 || f == FKB_SRC_NV21; }
+static bool is_yuv_conversion(int opcode) {
+    return opcode == FKB_OP_YUV_TO_RGB_BT709_FULL || opcode == FKB_OP_YUV_TO_RGB_BT601_FULL || opcode == FKB_OP_YUV_TO_RGB_BT2020_FULL;
+}
 static uint32_t dst_pixel_bytes(int f) { return f == FKB_DST_U8X3_PACKED ? 3u : f == FKB_DST_F32_PLANAR3 ? 4u : 12u; }
 
 /* Walks a sequence's operations with the value type the reference's templates would have
    (a mismatch there is a compile error; here it is FKB_ERR_INVALID_ARGUMENT). */
 static int check_sequence(const fkb_sequence& s, int index, DevSeq& ds) {
-    if (s.src_format < FKB_SRC_U8X3 || s.src_format > FKB_SRC_NV12)
+    if (s.src_format < FKB_SRC_U8X3 || s.src_format > FKB_SRC_NV21)
         return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d: unknown source format %d", index, s.src_format);
     if (s.dst_format < FKB_DST_F32X3_PACKED || s.dst_format > FKB_DST_U32X3_PACKED)
         return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d: unknown destination format %d", index, s.dst_format);
-    if (s.resize_mode < FKB_RESIZE_NONE || s.resize_mode > FKB_RESIZE_PRESERVE_AR)
+    if (s.resize_mode < FKB_RESIZE_NONE || s.resize_mode > FKB_RESIZE_PRESERVE_AR_LEFT)
         return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d: unknown resize mode %d", index, s.resize_mode);
     if (s.n_ops < 0 || s.n_ops > 4096) return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d: n_ops %d outside [0, 4096]", index, s.n_ops);
     if (s.n_ops > 0 && !s.ops) return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d: ops is NULL", index);
@@ -574,13 +587,15 @@ static int check_sequence(const fkb_sequence& s, int index, DevSeq& ds) {
 
     ValueType t = s.src_format == FKB_SRC_U8X3 ? VT_U8 : s.src_format == FKB_SRC_F32X3 ? VT_F32 : VT_YUV8;
     bool pre_only_casts = true, pre_is_yuv = (n_pre == 1);
+    int yuv_opcode = 0;
     for (int k = 0; k <= s.n_ops; ++k) {
         if (k == n_pre && s.resize_mode != FKB_RESIZE_NONE) t = VT_F32; /* Interpolate returns float (interpolation.h:55-57) */
         if (k == s.n_ops) break;
         const int oc = s.ops[k].opcode;
         if (k < n_pre) {
             if (oc != FKB_OP_CAST_F32) pre_only_casts = false;
-            if (oc != FKB_OP_YUV_TO_RGB_BT709_FULL) pre_is_yuv = false;
+            if (!is_yuv_conversion(oc)) pre_is_yuv = false;
+            else yuv_opcode = oc;
         }
         if (t == VT_I32 || t == VT_U32)
             return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d op %d: nothing but the receiver may follow a cast to int3 / uint3", index, k);
@@ -602,7 +617,7 @@ static int check_sequence(const fkb_sequence& s, int index, DevSeq& ds) {
                 if (t != VT_F32) return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d op %d: SaturateCast<float3,uchar3> needs a float value", index, k);
                 t = VT_U8;
                 break;
-            case FKB_OP_YUV_TO_RGB_BT709_FULL:
+            case FKB_OP_YUV_TO_RGB_BT709_FULL: case FKB_OP_YUV_TO_RGB_BT601_FULL: case FKB_OP_YUV_TO_RGB_BT2020_FULL:
                 if (t != VT_YUV8) return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d op %d: ConvertYUVToRGB needs the value read by ReadYUV", index, k);
                 t = VT_F32;
                 break;
@@ -619,13 +634,20 @@ static int check_sequence(const fkb_sequence& s, int index, DevSeq& ds) {
     }
 
     ds.src_format = s.src_format; ds.dst_format = s.dst_format; ds.resize_mode = s.resize_mode;
+    /* NV21 is NV12 with the two chroma bytes exchanged (color_conversion.h:347-359): the kernels read it as NV12
+       and swap the pair of every tap */
+    ds.swap_uv = s.src_format == FKB_SRC_NV21 ? 1u : 0u;
+    if (s.src_format == FKB_SRC_NV21) ds.src_format = FKB_SRC_NV12;
     /* int3 / uint3 pixels are twelve bytes like float3 and their values travel as bit patterns: the
        kernels store them through the float3 receiver */
     if (want == VT_I32 || want == VT_U32) ds.dst_format = FKB_DST_F32X3_PACKED;
     ds.n_ops = s.n_ops; ds.n_pre = n_pre; ds.ops_begin = 0; ds.chain = CHAIN_INTERPRET;
-    ds.pre_kind = (n_pre == 0 || pre_only_casts) ? PRE_IDENTITY : pre_is_yuv ? PRE_YUV_BT709 : PRE_GENERAL;
+    ds.pre_kind = (n_pre == 0 || pre_only_casts) ? PRE_IDENTITY
+                  : !pre_is_yuv ? PRE_GENERAL
+                  : yuv_opcode == FKB_OP_YUV_TO_RGB_BT709_FULL ? PRE_YUV_BT709
+                  : yuv_opcode == FKB_OP_YUV_TO_RGB_BT601_FULL ? PRE_YUV_BT601 : PRE_YUV_BT2020;
     ds.bg[0] = s.background[0]; ds.bg[1] = s.background[1]; ds.bg[2] = s.background[2]; ds.one = 1.0f;
-    background_after_ops(s, n_pre, ds.bg_out); ds.pad = 0.0f;
+    background_after_ops(s, n_pre, ds.bg_out);
     return FKB_OK;
 }
 
@@ -804,26 +826,30 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
         if (p.sequence < 0 || p.sequence >= d->n_sequences)
             return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: sequence index %d outside [0, %d)", i, p.sequence, d->n_sequences);
         const DevSeq& s = img.seqs[p.sequence];
-        if (!p.src || !p.dst) return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: null image pointer", i);
-        if (p.src_width == 0 || p.src_height == 0 || p.dst_width == 0 || p.dst_height == 0)
+        const bool is_default = (p.flags & FKB_PLANE_DEFAULT_VALUE) != 0; /* reads the default value, never its image */
+        if (p.flags & ~FKB_PLANE_DEFAULT_VALUE) return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: unknown flag bits 0x%x", i, p.flags);
+        if (!p.dst || (!p.src && !is_default)) return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: null image pointer", i);
+        if (p.dst_width == 0 || p.dst_height == 0 || (!is_default && (p.src_width == 0 || p.src_height == 0)))
             return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: zero-sized image", i);
         if (p.src_width > (1u << 24) || p.src_height > (1u << 24) || p.dst_width > (1u << 24) || p.dst_height > (1u << 24))
             return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: image side beyond 2^24", i);
         const uint32_t spx = src_pixel_bytes(s.src_format), dpx = dst_pixel_bytes(s.dst_format);
-        const uint64_t src_row = s.src_format == FKB_SRC_NV12 ? 2ull * ((p.src_width + 1) / 2) : (uint64_t)p.src_width * spx;
-        if (p.src_pitch < src_row)
-            return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: source pitch %u is less than a row of %llu bytes", i, p.src_pitch, (unsigned long long)src_row);
-        if ((uint64_t)p.src_pitch * p.src_height * 2 > 0xFFFFFFFFull)
-            return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: source image beyond 2 GiB", i);
+        if (!is_default) {
+            const uint64_t src_row = s.src_format == FKB_SRC_NV12 ? 2ull * ((p.src_width + 1) / 2) : (uint64_t)p.src_width * spx;
+            if (p.src_pitch < src_row)
+                return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: source pitch %u is less than a row of %llu bytes", i, p.src_pitch, (unsigned long long)src_row);
+            if ((uint64_t)p.src_pitch * p.src_height * 2 > 0xFFFFFFFFull)
+                return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: source image beyond 2 GiB", i);
+            if (p.crop_x < 0 || p.crop_y < 0 || p.crop_width <= 0 || p.crop_height <= 0 ||
+                (uint64_t)p.crop_x + (uint64_t)p.crop_width > p.src_width || (uint64_t)p.crop_y + (uint64_t)p.crop_height > p.src_height)
+                return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: crop rect (%d,%d,%d,%d) outside its %ux%u image", i, p.crop_x, p.crop_y, p.crop_width, p.crop_height, p.src_width, p.src_height);
+            if (s.resize_mode == FKB_RESIZE_NONE && ((uint32_t)p.crop_width != p.dst_width || (uint32_t)p.crop_height != p.dst_height))
+                return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: without a resize the output (%ux%u) must have the size of the crop (%dx%d)", i, p.dst_width, p.dst_height, p.crop_width, p.crop_height);
+            if (s.src_format == FKB_SRC_F32X3 && (!aligned(p.src, 4) || p.src_pitch % 4))
+                return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: float source must be 4-byte aligned", i);
+        }
         if (p.dst_pitch < (uint64_t)p.dst_width * dpx)
             return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: destination pitch %u is less than a row of %llu bytes", i, p.dst_pitch, (unsigned long long)p.dst_width * dpx);
-        if (p.crop_x < 0 || p.crop_y < 0 || p.crop_width <= 0 || p.crop_height <= 0 ||
-            (uint64_t)p.crop_x + (uint64_t)p.crop_width > p.src_width || (uint64_t)p.crop_y + (uint64_t)p.crop_height > p.src_height)
-            return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: crop rect (%d,%d,%d,%d) outside its %ux%u image", i, p.crop_x, p.crop_y, p.crop_width, p.crop_height, p.src_width, p.src_height);
-        if (s.resize_mode == FKB_RESIZE_NONE && ((uint32_t)p.crop_width != p.dst_width || (uint32_t)p.crop_height != p.dst_height))
-            return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: without a resize the output (%ux%u) must have the size of the crop (%dx%d)", i, p.dst_width, p.dst_height, p.crop_width, p.crop_height);
-        if (s.src_format == FKB_SRC_F32X3 && (!aligned(p.src, 4) || p.src_pitch % 4))
-            return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: float source must be 4-byte aligned", i);
         if (s.dst_format != FKB_DST_U8X3_PACKED && (!aligned(p.dst, 4) || p.dst_pitch % 4 || p.dst_channel_stride % 4))
             return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: float destination must be 4-byte aligned", i);
         if (s.dst_format == FKB_DST_F32_PLANAR3 && p.dst_channel_stride < (uint64_t)p.dst_pitch * (p.dst_height - 1) + (uint64_t)p.dst_width * 4)
@@ -839,7 +865,12 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
         dp.seq = (uint32_t)p.sequence;
         dp.fx = dp.fy = 1.0f;
         dp.x2 = (int32_t)p.dst_width - 1; dp.y2 = (int32_t)p.dst_height - 1;
-        if (s.resize_mode != FKB_RESIZE_NONE) {
+        if (is_default) {
+            /* every element is the default value: an empty region of interest, store-only work; the image is never read */
+            dp.src = nullptr; dp.src_pitch = 0; dp.src_height = 0;
+            dp.crop_x = dp.crop_y = 0; dp.crop_w = dp.crop_h = 1;
+            dp.x1 = 0; dp.y1 = 0; dp.x2 = -1; dp.y2 = -1;
+        } else if (s.resize_mode != FKB_RESIZE_NONE) {
             fkb_resize_params& rp = img.resize[i];
             const int rc = fkb_derive_resize(p.crop_width, p.crop_height, (int32_t)p.dst_width, (int32_t)p.dst_height, s.resize_mode, &rp);
             if (rc) return rc;
@@ -861,7 +892,7 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
         const uint64_t out_px = (uint64_t)p.dst_width * p.dst_height;
         uint32_t cls = CLASS_GENERIC;
         uint64_t items = 0;
-        if (s.resize_mode == FKB_RESIZE_NONE && s.dst_format != FKB_DST_F32_PLANAR3 && s.src_format != FKB_SRC_NV12) {
+        if (s.resize_mode == FKB_RESIZE_NONE && !is_default && s.dst_format != FKB_DST_F32_PLANAR3 && s.src_format != FKB_SRC_NV12) {
             const bool src_u8 = s.src_format == FKB_SRC_U8X3, dst_u8 = s.dst_format == FKB_DST_U8X3_PACKED;
             const uintptr_t sa = src_u8 ? 4 : 16, da = dst_u8 ? 4 : 16;
             const uint8_t* src0 = dp.src + (size_t)p.crop_y * p.src_pitch + (size_t)p.crop_x * spx;
@@ -876,7 +907,7 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
                 const uint32_t item_px = (uint32_t)flat_item_pixels(src_u8);
                 items = (uint64_t)dp.n_segs * ((dp.seg_pixels + item_px - 1) / item_px);
             }
-        } else if (s.resize_mode != FKB_RESIZE_NONE && (p.dst_width % PX_PER_THREAD) == 0 && aligned(dp.dst, 16) && (p.dst_pitch % 16) == 0 &&
+        } else if ((s.resize_mode != FKB_RESIZE_NONE || is_default) && (p.dst_width % PX_PER_THREAD) == 0 && aligned(dp.dst, 16) && (p.dst_pitch % 16) == 0 &&
                    s.pre_kind != PRE_GENERAL) {
             if (s.src_format == FKB_SRC_U8X3 && s.dst_format == FKB_DST_F32_PLANAR3 && (p.dst_channel_stride % 16) == 0) cls = CLASS_RESIZE_U8_PLANAR;
             else if (s.src_format == FKB_SRC_U8X3 && s.dst_format == FKB_DST_F32X3_PACKED) cls = CLASS_RESIZE_U8_PACKED;
@@ -900,7 +931,7 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
         if (total > 0x7FFFFFFFull) return fail(FKB_ERR_INVALID_ARGUMENT, "plan needs more than 2^31 thread blocks");
 
         img.output_pixels += out_px;
-        const uint64_t crop_px = (uint64_t)p.crop_width * p.crop_height;
+        const uint64_t crop_px = is_default ? 0 : (uint64_t)p.crop_width * p.crop_height;
         img.algorithmic_bytes += (s.src_format == FKB_SRC_NV12 ? crop_px + crop_px / 2 : crop_px * spx) + out_px * (s.dst_format == FKB_DST_F32_PLANAR3 ? 12 : dpx);
     }
     uint32_t common_chain = 0;
@@ -1542,19 +1573,20 @@ static int host_session_create(const fkb_plan_desc* desc, fkb_host_session** out
     for (int i = 0; i < n; ++i) {
         const fkb_plane& p = desc->planes[i];
         const fkb_sequence& q = desc->sequences[p.sequence];
-        const size_t rows = q.src_format == FKB_SRC_NV12 ? (size_t)p.src_height + (p.src_height + 1) / 2 : p.src_height;
-        const size_t bytes = (size_t)p.src_pitch * rows;
-        auto it = group_of.find(p.src);
+        const bool is_default = (p.flags & FKB_PLANE_DEFAULT_VALUE) != 0; /* reads no image: a group without an upload */
+        const size_t rows = is_yuv_source(q.src_format) ? (size_t)p.src_height + (p.src_height + 1) / 2 : p.src_height;
+        const size_t bytes = is_default ? 0 : (size_t)p.src_pitch * rows;
+        auto it = group_of.find(is_default ? nullptr : p.src);
         if (it == group_of.end()) {
             fkb_host_session::Group g;
-            g.host_src = p.src;
+            g.host_src = is_default ? nullptr : p.src;
             g.src_bytes = bytes;
-            const cudaError_t e = device_alloc(&g.dev_src, bytes);
+            const cudaError_t e = bytes ? device_alloc(&g.dev_src, bytes) : cudaSuccess;
             if (e != cudaSuccess) return bail(fail_cuda(e, "source mirror allocation", __LINE__));
             s->groups.push_back(g);
             members.emplace_back();
             s->h2d_bytes += bytes;
-            it = group_of.emplace(p.src, s->groups.size() - 1).first;
+            it = group_of.emplace(is_default ? nullptr : p.src, s->groups.size() - 1).first;
         } else if (s->groups[it->second].src_bytes != bytes) {
             return bail(fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: one source pointer is described with two sizes", i));
         }
@@ -1658,7 +1690,7 @@ static int host_session_enqueue(fkb_host_session* s, cudaStream_t stream, bool d
     FKB_CUDA(cudaEventRecord(s->start, stream));
     FKB_CUDA(cudaStreamWaitEvent(s->out_stream, s->start, 0));
     for (auto& g : s->groups) {
-        FKB_CUDA(cudaMemcpyAsync(g.dev_src, g.host_src, g.src_bytes, cudaMemcpyHostToDevice, stream));
+        if (g.src_bytes) FKB_CUDA(cudaMemcpyAsync(g.dev_src, g.host_src, g.src_bytes, cudaMemcpyHostToDevice, stream));
         const int rc = fkb_plan_launch(g.plan, stream);
         if (rc) return rc;
         if (!downloads) continue;

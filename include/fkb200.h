@@ -53,8 +53,9 @@ typedef enum fkb_status {
 typedef enum fkb_src_format {
     FKB_SRC_U8X3 = 1,  /* PerThreadRead<_2D, uchar3>  (memory_operations.h:71-112)            */
     FKB_SRC_F32X3 = 2, /* PerThreadRead<_2D, float3>                                          */
-    FKB_SRC_NV12 = 3   /* ReadYUV<NV12> (color_conversion.h:314-346): `height` luma rows then */
+    FKB_SRC_NV12 = 3,  /* ReadYUV<NV12> (color_conversion.h:314-346): `height` luma rows then */
                        /* height/2 rows of interleaved U,V, chroma at data + pitch*height     */
+    FKB_SRC_NV21 = 4   /* ReadYUV<NV21> (color_conversion.h:347-359): the same with V,U pairs */
 } fkb_src_format;
 
 /* Layout written by the receiver. */
@@ -72,7 +73,10 @@ typedef enum fkb_dst_format {
 typedef enum fkb_resize_mode {
     FKB_RESIZE_NONE = 0,        /* output element (x,y) reads source element (x,y) of the crop */
     FKB_RESIZE_IGNORE_AR = 1,   /* Resize<INTER_LINEAR, IGNORE_AR>   (resize.h:105-119)         */
-    FKB_RESIZE_PRESERVE_AR = 2  /* Resize<INTER_LINEAR, PRESERVE_AR> (resize.h:121-166)         */
+    FKB_RESIZE_PRESERVE_AR = 2, /* Resize<INTER_LINEAR, PRESERVE_AR> (resize.h:121-166)         */
+    FKB_RESIZE_PRESERVE_AR_RN_EVEN = 3, /* PRESERVE_AR_RN_EVEN: target width (or, when the width is    */
+                                /* the limit, height) rounded down to an even number (resize.h:200-210) */
+    FKB_RESIZE_PRESERVE_AR_LEFT = 4 /* PRESERVE_AR_LEFT: the region starts at column 0 (resize.h:132-147) */
 } fkb_resize_mode;
 
 /* Element-wise operations, applied per channel in IEEE-754 binary32 with no contraction.   */
@@ -90,6 +94,9 @@ typedef enum fkb_opcode {
     FKB_OP_CAST_I32 = 9,        /* Cast<float3,int3>: per-channel static_cast, truncation toward  */
                                 /* zero (basic_ops/cast_base.h:20-30, cast.h:23-33).  Last        */
                                 /* operation of a sequence only; the receiver is an I32X3 format. */
+    FKB_OP_YUV_TO_RGB_BT601_FULL = 11, /* ConvertYUVToRGB<PF,Full,bt601,false,float3>: (Y-16, U-128, V-128) */
+                                /* times the matrix of color_conversion.h:137-140 (:266-269)    */
+    FKB_OP_YUV_TO_RGB_BT2020_FULL = 12, /* ConvertYUVToRGB<PF,Full,bt2020,false,float3> (:165-168) */
     FKB_OP_CAST_U32 = 10        /* Cast<float3,uint3> (the ending of the reference's run-time test,*/
                                 /* tests/operation/test_instantiable_operations.h:241-264).  C++   */
                                 /* leaves static_cast of a negative or too large float undefined;  */
@@ -113,7 +120,8 @@ typedef struct fkb_sequence {
     int32_t n_ops;
     int32_t n_pre_ops;
     float background[3];  /* PRESERVE_AR default value (resize.h:53, :158); the continuation */
-                          /* still applies to it (resize.h:84-86)                            */
+                          /* still applies to it (resize.h:84-86).  Also the value that      */
+                          /* planes flagged FKB_PLANE_DEFAULT_VALUE read.                    */
     const fkb_op* ops;    /* HOST pointer, n_ops entries (may be NULL when n_ops == 0)       */
 } fkb_sequence;
 
@@ -134,8 +142,14 @@ typedef struct fkb_plane {
     uint32_t dst_channel_stride; /* FKB_DST_F32_PLANAR3: bytes between channel planes         */
     int32_t sequence;       /* index into fkb_plan_desc.sequences (divergent horizontal fusion,*/
                             /* data_parallel_patterns.h:315-323); 0 for an ordinary batch     */
-    int32_t reserved;
+    int32_t flags;          /* FKB_PLANE_* below; 0 for an ordinary plane                      */
 } fkb_plane;
+
+/* A plane of a partly filled batch (BatchRead<B, CONDITIONAL_WITH_DEFAULT>, batch_operations.h:217-241:
+ * planes at or beyond usedPlanes read `default_value` instead of their image): every element of the read
+ * stage is the sequence's `background`, the operations after the geometry stage still apply to it, and
+ * the source image is never touched (src may be NULL; the crop is ignored). */
+#define FKB_PLANE_DEFAULT_VALUE 1
 
 typedef struct fkb_plan_desc {
     const fkb_sequence* sequences; /* HOST pointer */
@@ -185,7 +199,7 @@ FKB_API const char* fkb_last_error(void);
 
 /* Restates Resize::build's host arithmetic (resize.h:105-166) and compute_target_size
  * (resize.h:196-221): float scale, cxp::round (constexpr_cmath.h:119-130), double
- * reciprocal narrowed once.  mode is FKB_RESIZE_IGNORE_AR or FKB_RESIZE_PRESERVE_AR. */
+ * reciprocal narrowed once.  mode is any fkb_resize_mode but FKB_RESIZE_NONE. */
 FKB_API int fkb_derive_resize(int32_t src_width, int32_t src_height, int32_t dst_width, int32_t dst_height,
                       int32_t mode, fkb_resize_params* out);
 

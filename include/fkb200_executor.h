@@ -26,12 +26,14 @@
  * core/execution_model/stream.h:50).  Needs only include/fkb200.h beside the reference's headers.
  *
  * Operations understood (anything else: static_assert):
- *   reads      PerThreadRead<_2D, uchar3|float3>, ReadYUV<NV12>, Crop<Back>, Resize<INTER_LINEAR,
- *              IGNORE_AR|PRESERVE_AR, Back>, BatchRead<B, PROCESS_ALL, ...>, FusedOperation_<...>
+ *   reads      PerThreadRead<_2D, uchar3|float3>, ReadYUV<NV12|NV21>, Crop<Back>, Resize<INTER_LINEAR,
+ *              IGNORE_AR|PRESERVE_AR|PRESERVE_AR_RN_EVEN|PRESERVE_AR_LEFT, Back>, FusedOperation_<...>,
+ *              BatchRead<B, PROCESS_ALL, ...>, BatchRead<B, CONDITIONAL_WITH_DEFAULT, ...>
  *   compute    Mul / Sub / Div / Add <float3>, Cast<uchar3,float3>, Cast<float3,int3|uint3>,
  *              SaturateCast<float3,uchar3>, VectorReorder<T,2,1,0> (COLOR_RGB2BGR / COLOR_BGR2RGB),
- *              ConvertYUVToRGB<NV12, Full, bt709, false, float3>
- *   receivers  PerThreadWrite<_2D|_3D, T>, TensorWrite<T>, TensorSplit<float3>
+ *              ConvertYUVToRGB<NV12|NV21, Full, bt709|bt601|bt2020, false, float3>
+ *   receivers  PerThreadWrite<_2D|_3D, T>, TensorWrite<T>, TensorSplit<float3>, TensorTSplit<float3>,
+ *              SplitWrite<_2D, float3> over three equally spaced images of one pitch
  */
 #ifndef FKB200_EXECUTOR_H
 #define FKB200_EXECUTOR_H
@@ -98,8 +100,14 @@ template <> struct LowerCompute<fk::Cast<float3, int3>> { static void apply(Plan
 template <> struct LowerCompute<fk::Cast<float3, uint3>> { static void apply(PlaneState& st) { st.ops.push_back(make_op(FKB_OP_CAST_U32)); } };
 template <> struct LowerCompute<fk::SaturateCast<float3, uchar3>> { static void apply(PlaneState& st) { st.ops.push_back(make_op(FKB_OP_SATURATE_CAST_U8)); } };
 template <typename T> struct LowerCompute<fk::VectorReorder<T, 2, 1, 0>> { static void apply(PlaneState& st) { st.ops.push_back(make_op(FKB_OP_SWAP_RB)); } };
-template <> struct LowerCompute<fk::ConvertYUVToRGB<fk::PixelFormat::NV12, fk::ColorRange::Full, fk::ColorPrimitives::bt709, false, float3>> {
-    static void apply(PlaneState& st) { st.ops.push_back(make_op(FKB_OP_YUV_TO_RGB_BT709_FULL)); }
+template <fk::PixelFormat PF, fk::ColorPrimitives CP> struct LowerCompute<fk::ConvertYUVToRGB<PF, fk::ColorRange::Full, CP, false, float3>> {
+    static_assert(PF == fk::PixelFormat::NV12 || PF == fk::PixelFormat::NV21, "fkb200: only NV12 and NV21 conversions are on the accelerated path");
+    static_assert(CP == fk::ColorPrimitives::bt709 || CP == fk::ColorPrimitives::bt601 || CP == fk::ColorPrimitives::bt2020,
+                  "fkb200: this colour matrix is not on the accelerated path");
+    static void apply(PlaneState& st) {
+        st.ops.push_back(make_op(CP == fk::ColorPrimitives::bt709 ? FKB_OP_YUV_TO_RGB_BT709_FULL
+                                 : CP == fk::ColorPrimitives::bt601 ? FKB_OP_YUV_TO_RGB_BT601_FULL : FKB_OP_YUV_TO_RGB_BT2020_FULL));
+    }
 };
 
 template <typename Op, typename Data>
@@ -132,9 +140,10 @@ template <typename T> struct LowerRead<fk::PerThreadRead<fk::ND::_2D, T>> {
 };
 /* ReadYUV<NV12> (color_conversion.h:314-400): params is a RawImage whose luma RawPtr has dims.height rows and
    whose chroma plane lies at data + pitch * dims.height (:336-341) */
-template <> struct LowerRead<fk::ReadYUV<fk::PixelFormat::NV12>> {
+template <fk::PixelFormat PF> struct LowerRead<fk::ReadYUV<PF>> {
+    static_assert(PF == fk::PixelFormat::NV12 || PF == fk::PixelFormat::NV21, "fkb200: only NV12 and NV21 reads are on the accelerated path");
     template <typename D> static void apply(PlaneState& st, const D& d) {
-        st.src_format = FKB_SRC_NV12;
+        st.src_format = PF == fk::PixelFormat::NV12 ? FKB_SRC_NV12 : FKB_SRC_NV21;
         st.plane.src = d.params.data.data;
         st.plane.src_width = d.params.width; st.plane.src_height = d.params.data.dims.height; st.plane.src_pitch = d.params.data.dims.pitch;
         st.plane.crop_x = 0; st.plane.crop_y = 0;
@@ -156,8 +165,7 @@ template <typename Back> struct LowerRead<fk::Crop<Back>> {
 /* Resize<INTER_LINEAR, AR, Back> (resize.h:61-222): params holds dstSize, the factors and - for PRESERVE_AR - the
    region of interest and the default value that Resize::build computed on the host */
 template <fk::AspectRatio AR, typename Back> struct LowerRead<fk::Resize<fk::InterpolationType::INTER_LINEAR, AR, Back>> {
-    static_assert(AR == fk::AspectRatio::IGNORE_AR || AR == fk::AspectRatio::PRESERVE_AR,
-                  "fkb200: only IGNORE_AR and PRESERVE_AR resizes are on the accelerated path");
+
     template <typename D> static void apply(PlaneState& st, const D& d) {
         LowerRead<typename Back::Operation>::apply(st, d.backIOp);
         if (st.resize_mode != FKB_RESIZE_NONE) throw std::runtime_error("fkb200: two Resize operations in one chain are not on the accelerated path");
@@ -166,8 +174,9 @@ template <fk::AspectRatio AR, typename Back> struct LowerRead<fk::Resize<fk::Int
         st.reference_resize.fx = d.params.src_conv_factors.x; st.reference_resize.fy = d.params.src_conv_factors.y;
         st.reference_resize.x1 = 0; st.reference_resize.y1 = 0;
         st.reference_resize.x2 = d.params.dstSize.width - 1; st.reference_resize.y2 = d.params.dstSize.height - 1;
-        if constexpr (AR == fk::AspectRatio::PRESERVE_AR) {
-            st.resize_mode = FKB_RESIZE_PRESERVE_AR;
+        if constexpr (AR != fk::AspectRatio::IGNORE_AR) {
+            st.resize_mode = AR == fk::AspectRatio::PRESERVE_AR ? FKB_RESIZE_PRESERVE_AR
+                             : AR == fk::AspectRatio::PRESERVE_AR_RN_EVEN ? FKB_RESIZE_PRESERVE_AR_RN_EVEN : FKB_RESIZE_PRESERVE_AR_LEFT;
             st.background[0] = d.params.defaultValue.x; st.background[1] = d.params.defaultValue.y; st.background[2] = d.params.defaultValue.z;
             st.reference_resize.x1 = d.params.x1; st.reference_resize.y1 = d.params.y1;
             st.reference_resize.x2 = d.params.x2; st.reference_resize.y2 = d.params.y2;
@@ -268,6 +277,33 @@ template <> struct LowerWrite<fk::TensorSplit<float3>> {
     }
 };
 
+/* TensorTSplit<float3> (memory_operations.h:228-255): channel-major over the whole batch, [C][N][H][W]; plane z at
+   plane_pitch * z, channel c a further color_planes_pitch * c (core/data/rawptr.h:231-239) */
+template <> struct LowerWrite<fk::TensorTSplit<float3>> {
+    template <typename D> static Receiver apply(const D& d) {
+        Receiver r;
+        r.data = d.params.data; r.width = d.params.dims.width; r.height = d.params.dims.height; r.pitch = d.params.dims.pitch;
+        r.planes = d.params.dims.planes; r.plane_bytes = d.params.dims.plane_pitch; r.channel_stride = d.params.dims.color_planes_pitch;
+        r.dst_format = FKB_DST_F32_PLANAR3;
+        return r;
+    }
+};
+/* SplitWrite<_2D, float3> (memory_operations.h:374-407): three images; expressible when they share one pitch and lie at
+   equal distances (the planar receiver has one channel stride) */
+template <> struct LowerWrite<fk::SplitWrite<fk::ND::_2D, float3>> {
+    template <typename D> static Receiver apply(const D& d) {
+        const auto& x = d.params.x; const auto& y = d.params.y; const auto& z = d.params.z;
+        const ptrdiff_t s1 = reinterpret_cast<const char*>(y.data) - reinterpret_cast<const char*>(x.data);
+        const ptrdiff_t s2 = reinterpret_cast<const char*>(z.data) - reinterpret_cast<const char*>(y.data);
+        if (s1 <= 0 || s1 != s2 || s1 > 0xFFFFFFFFll || x.dims.pitch != y.dims.pitch || y.dims.pitch != z.dims.pitch)
+            throw std::runtime_error("fkb200: SplitWrite needs three images of one pitch at equal, increasing distances below 4 GiB");
+        Receiver r;
+        r.data = x.data; r.width = x.dims.width; r.height = x.dims.height; r.pitch = x.dims.pitch;
+        r.planes = 1; r.plane_bytes = 0; r.channel_stride = (uint32_t)s1; r.dst_format = FKB_DST_F32_PLANAR3;
+        return r;
+    }
+};
+
 /* ---- the whole call ---- */
 struct LoweredPlan {
     std::vector<PlaneState> states;
@@ -295,6 +331,26 @@ template <size_t B, typename Op, typename Out> struct LowerFirst<fk::BatchRead<B
         for (size_t z = 0; z < B; ++z) {
             states.emplace_back();
             LowerRead<Op>::apply(states.back(), d.params.opData[z]);
+        }
+    }
+};
+
+/* BatchRead<B, CONDITIONAL_WITH_DEFAULT, Op, Out> (batch_operations.h:217-287): planes at or beyond usedPlanes return
+   default_value in place of Op's result over the whole active area; operations that follow the batch still apply */
+template <size_t B, typename Op, typename Out> struct LowerFirst<fk::BatchRead<B, fk::PlanePolicy::CONDITIONAL_WITH_DEFAULT, Op, Out>> {
+    template <typename D> static void apply(std::vector<PlaneState>& states, const D& d) {
+        states.reserve(B);
+        for (size_t z = 0; z < B; ++z) {
+            states.emplace_back();
+            PlaneState& st = states.back();
+            if ((int)z < d.params.usedPlanes) { LowerRead<Op>::apply(st, d.params.opData[z]); continue; }
+            using DV = std::decay_t<decltype(d.params.default_value)>;
+            st.plane.flags = FKB_PLANE_DEFAULT_VALUE;
+            st.src_format = source_format_of<DV>();
+            st.background[0] = (float)d.params.default_value.x; st.background[1] = (float)d.params.default_value.y;
+            st.background[2] = (float)d.params.default_value.z;
+            st.plane.crop_width = (int32_t)d.params.activeThreads.x; st.plane.crop_height = (int32_t)d.params.activeThreads.y;
+            st.plane.src_width = d.params.activeThreads.x; st.plane.src_height = d.params.activeThreads.y;
         }
     }
 };

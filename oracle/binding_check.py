@@ -80,6 +80,24 @@ def bgr_cast_mul_saturate(mode, src, w, h, spitch, mul, dst, dpitch, stream=None
     _check(lib().fklbind_bgr_cast_mul_saturate(mode, _p(src), w, h, spitch, _f3(mul), _p(dst), dpitch, _p(stream)))
 
 
+def nv21_bt601_2(mode, frames2, w, h, pitch, dw, dh, div, out, stream=None):
+    ptrs = (C.c_void_p * 2)(*[int(p) for p in frames2])
+    _check(lib().fklbind_nv21_bt601_2(mode, ptrs, w, h, pitch, dw, dh, _f3(div), _p(out), _p(stream)))
+
+
+def left_tsplit4(mode, frames4, w, h, pitch, rects, dw, dh, bg, d0, mean, std, out, stream=None):
+    r = np.ascontiguousarray(rects, np.int32)
+    ptrs = (C.c_void_p * 4)(*[int(p) for p in frames4])
+    _check(lib().fklbind_left_tsplit4(mode, ptrs, w, h, pitch, r.ctypes.data_as(C.POINTER(C.c_int)), dw, dh, _f3(bg), _f3(d0), _f3(mean),
+                                      _f3(std), _p(out), _p(stream)))
+
+
+def batch4_default_cast_mul(mode, srcs4, w, h, spitch, used, default_value, mul, dst, stream=None):
+    ptrs = (C.c_void_p * 4)(*[int(p) for p in srcs4])
+    dv = (C.c_uint8 * 3)(*[int(v) for v in default_value])
+    _check(lib().fklbind_batch4_default_cast_mul(mode, ptrs, w, h, spitch, used, dv, _f3(mul), _p(dst), _p(stream)))
+
+
 def last_plan():
     """(planes, sequences) of the last DESCRIBE call: planes as abi.Plane, sequences as (abi.Sequence, [abi.Op])."""
     n_p, n_s = C.c_int(), C.c_int()

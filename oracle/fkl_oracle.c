@@ -32,16 +32,18 @@ static float cxp_roundf(float x) {
 int fkl_oracle_derive_resize(int sw, int sh, int dw, int dh, int mode, fkb_resize_params* out) {
     int tw = dw, th = dh;
     if (sw <= 0 || sh <= 0 || dw <= 0 || dh <= 0 || !out) return 1;
-    if (mode == FKB_RESIZE_PRESERVE_AR) {
+    if (mode == FKB_RESIZE_PRESERVE_AR || mode == FKB_RESIZE_PRESERVE_AR_RN_EVEN || mode == FKB_RESIZE_PRESERVE_AR_LEFT) {
         const float scale = (float)dh / (float)sh;             /* resize.h:197 */
         th = dh;
         tw = (int)cxp_roundf(scale * (float)sw);               /* resize.h:199 */
-        if (tw > dw) {                                         /* resize.h:212-216 */
+        if (mode == FKB_RESIZE_PRESERVE_AR_RN_EVEN) tw -= tw % 2;  /* resize.h:200-202 */
+        if (tw > dw) {                                         /* resize.h:203-207, 212-216 */
             const float scale2 = (float)dw / (float)sw;
             tw = dw;
             th = (int)cxp_roundf(scale2 * (float)sh);
+            if (mode == FKB_RESIZE_PRESERVE_AR_RN_EVEN) th -= th % 2;
         }
-        out->x1 = (dw - tw) / 2;                               /* resize.h:150-151 */
+        out->x1 = mode == FKB_RESIZE_PRESERVE_AR_LEFT ? 0 : (dw - tw) / 2;  /* resize.h:132-133, 150-151 */
         out->y1 = (dh - th) / 2;
         out->x2 = out->x1 + tw - 1;
         out->y2 = out->y1 + th - 1;
@@ -78,11 +80,12 @@ static px3 read_tap(const fkb_plane* pl, int src_format, int a, int b) {
     } else if (src_format == FKB_SRC_F32X3) {
         const float* p = (const float*)(base + (size_t)y * pl->src_pitch + (size_t)x * 12);
         r.v[0] = p[0]; r.v[1] = p[1]; r.v[2] = p[2];
-    } else { /* FKB_SRC_NV12 */
+    } else { /* FKB_SRC_NV12, FKB_SRC_NV21 (the pair is stored V,U: color_conversion.h:357-359) */
         const uint8_t* luma = base + (size_t)y * pl->src_pitch + (size_t)x;
         const uint8_t* chroma = base + (size_t)pl->src_pitch * pl->src_height +
                                 (size_t)(y >> 1) * pl->src_pitch + (size_t)(x >> 1) * 2;
-        r.v[0] = (float)luma[0]; r.v[1] = (float)chroma[0]; r.v[2] = (float)chroma[1];
+        const int u_at = src_format == FKB_SRC_NV21 ? 1 : 0;
+        r.v[0] = (float)luma[0]; r.v[1] = (float)chroma[u_at]; r.v[2] = (float)chroma[1 - u_at];
     }
     return r;
 }
@@ -118,6 +121,20 @@ static px3 apply_op(px3 in, const fkb_op* op) {
             o.v[0] = ((y * 1.0f + u * 0.0f) + v * 1.5748f) * 1.0f;
             o.v[1] = ((y * 1.0f + u * -0.1873f) + v * -0.4681f) * 1.0f;
             o.v[2] = ((y * 1.0f + u * 1.8556f) + v * 0.0f) * 1.0f;
+            break;
+        }
+        case FKB_OP_YUV_TO_RGB_BT601_FULL: {             /* :137-140, luma offset :266-269 */
+            const float y = in.v[0] - 16.0f, u = in.v[1] - 128.0f, v = in.v[2] - 128.0f;
+            o.v[0] = ((y * 1.164383562f + u * 0.0f) + v * 1.596026786f) * 1.0f;
+            o.v[1] = ((y * 1.164383562f + u * -0.39176229f) + v * -0.812967647f) * 1.0f;
+            o.v[2] = ((y * 1.164383562f + u * 2.017232143f) + v * 0.0f) * 1.0f;
+            break;
+        }
+        case FKB_OP_YUV_TO_RGB_BT2020_FULL: {            /* :165-168 */
+            const float y = in.v[0], u = in.v[1] - 128.0f, v = in.v[2] - 128.0f;
+            o.v[0] = ((y * 1.0f + u * 0.0f) + v * 1.4746f) * 1.0f;
+            o.v[1] = ((y * 1.0f + u * -0.16455312684366f) + v * -0.57135312684366f) * 1.0f;
+            o.v[2] = ((y * 1.0f + u * 1.8814f) + v * 0.0f) * 1.0f;
             break;
         }
         default: break;
@@ -194,7 +211,8 @@ int fkl_oracle_run_range(const fkb_plan_desc* d, int first, int count, int host_
         if (pl->sequence < 0 || pl->sequence >= d->n_sequences) return 1;
         sq = &d->sequences[pl->sequence];
         memset(&rp, 0, sizeof rp);
-        if (sq->resize_mode != FKB_RESIZE_NONE) {
+        const int is_default = (pl->flags & FKB_PLANE_DEFAULT_VALUE) != 0;  /* batch_operations.h:236-241 */
+        if (sq->resize_mode != FKB_RESIZE_NONE && !is_default) {
             if (fkl_oracle_derive_resize(pl->crop_width, pl->crop_height, (int)pl->dst_width,
                                          (int)pl->dst_height, sq->resize_mode, &rp)) return 1;
         }
@@ -202,12 +220,15 @@ int fkl_oracle_run_range(const fkb_plan_desc* d, int first, int count, int host_
             for (x = 0; x < (int)pl->dst_width; ++x) {
                 px3 v;
                 int first_post = 0;
-                if (sq->resize_mode == FKB_RESIZE_NONE) {
+                if (is_default) {
+                    first_post = sq->resize_mode == FKB_RESIZE_NONE ? 0 : sq->n_pre_ops;
+                    v.v[0] = sq->background[0]; v.v[1] = sq->background[1]; v.v[2] = sq->background[2];
+                } else if (sq->resize_mode == FKB_RESIZE_NONE) {
                     v = read_tap(pl, sq->src_format, x, y);
                 } else {
                     first_post = sq->n_pre_ops;
                     /* Resize::exec, resize.h:75-87 */
-                    if (sq->resize_mode == FKB_RESIZE_PRESERVE_AR &&
+                    if (sq->resize_mode != FKB_RESIZE_IGNORE_AR &&
                         !(x >= rp.x1 && x <= rp.x2 && y >= rp.y1 && y <= rp.y2)) {
                         v.v[0] = sq->background[0]; v.v[1] = sq->background[1]; v.v[2] = sq->background[2];
                     } else {

@@ -152,6 +152,49 @@ int fklbind_bgr_cast_mul_saturate(int mode, const void* src, int w, int h, int s
     return run(mode, stream, sender, PerThreadWrite<ND::_2D, uchar3>::build(raw_u8x3(dst, w, h, dpitch)));
 }
 
+/* two NV21 frames -> ConvertYUVToRGB<Full, bt601> -> Resize dw x dh -> Div -> TensorWrite<float3> */
+int fklbind_nv21_bt601_2(int mode, const void* const* frames, int w, int h, int pitch, int dw, int dh, const float* div, float* out,
+                         void* stream) {
+    using Img = Image<PixelFormat::NV21>;
+    auto make = [&](size_t i) {
+        Ptr<ND::_2D, uchar> view(reinterpret_cast<uchar*>(const_cast<void*>(frames[i])), PtrDims<ND::_2D>((uint)w, (uint)h, (uint)pitch),
+                                 MemType::Device, 0);
+        return Img(view, (uint)w, (uint)h);
+    };
+    std::array<Img, 2> imgs{make(0), make(1)};
+    const auto sender = ReadYUV<PixelFormat::NV21>::build(imgs)
+                            .then(ConvertYUVToRGB<PixelFormat::NV21, ColorRange::Full, ColorPrimitives::bt601, false, float3>::build())
+                            .then(Resize<LINEAR>::build(Size(dw, dh)))
+                            .then(Div<float3>::build(f3(div)));
+    return run(mode, stream, sender, TensorWrite<float3>::build(raw_tensor<float3>(out, dw, dh, 2, 1)));
+}
+
+/* four crops -> PRESERVE_AR_LEFT dw x dh -> Div, Sub, Div -> TensorTSplit (3 x 4 x dh x dw, channel-major over the batch) */
+int fklbind_left_tsplit4(int mode, const void* const* frames, int w, int h, int pitch, const int* rects, int dw, int dh, const float* bg,
+                         const float* d0, const float* mean, const float* stdv, float* out, void* stream) {
+    const auto sender = cropped_resized<4, AspectRatio::PRESERVE_AR_LEFT>(frames, w, h, pitch, rects, dw, dh, bg)
+                            .then(Div<float3>::build(f3(d0)))
+                            .then(Sub<float3>::build(f3(mean)))
+                            .then(Div<float3>::build(f3(stdv)));
+    PtrDims<ND::T3D> dims((uint)dw, (uint)dh, 4u, 3u);
+    dims.pitch = (uint)(dw * sizeof(float));
+    dims.plane_pitch = dims.pitch * (uint)dh;
+    dims.color_planes_pitch = dims.plane_pitch * 4u;
+    const auto receiver = TensorTSplit<float3>::build(RawPtr<ND::T3D, float>{out, dims});
+    return run(mode, stream, sender, receiver);
+}
+
+/* a partly filled batch of four images (BatchRead<4, CONDITIONAL_WITH_DEFAULT>): Cast -> Mul -> TensorWrite<float3> */
+int fklbind_batch4_default_cast_mul(int mode, const void* const* srcs, int w, int h, int spitch, int used, const uint8_t* default_value,
+                                    const float* mul, float* dst, void* stream) {
+    std::array<RawPtr<ND::_2D, uchar3>, 4> a;
+    for (size_t i = 0; i < 4; ++i) a[i] = raw_u8x3(srcs[i], w, h, spitch);
+    const uchar3 dv{default_value[0], default_value[1], default_value[2]};
+    const auto read = PerThreadRead<ND::_2D, uchar3>::build(used, dv, a);
+    return run(mode, stream, read, Cast<uchar3, float3>::build(), Mul<float3>::build(f3(mul)),
+               TensorWrite<float3>::build(raw_tensor<float3>(dst, w, h, 4, 1)));
+}
+
 /* ---- inspection of the plan of the last mode-1 call on this thread ---- */
 int fklbind_last_counts(int* n_planes, int* n_sequences) {
     *n_planes = (int)g_last.planes.size();

@@ -142,4 +142,17 @@ void FKLREF_FN(crop_resize_readme_ignore_ar)(const uint8_t* const* frames, int w
 }
 #endif
 
+#if FKLREF_ONLY == 0 && !defined(FKLREF_GPU)
+/* The normalise-planar chain with the other aspect-ratio modes: mode 3 = PRESERVE_AR_RN_EVEN (target rounded down to an
+   even size, resize.h:200-210), 4 = PRESERVE_AR_LEFT (region at column 0, resize.h:132-147).  Host build only. */
+int FKLREF_FN(crop_resize_norm_planar_mode)(const uint8_t* const* frames, int w, int h, int pitch, const int* rects, int batch,
+                                            int dw, int dh, int mode, const float* bg, const float* d0, const float* mean,
+                                            const float* stdv, float* out) {
+    if (mode == 3) crop_resize_all<AspectRatio::PRESERVE_AR_RN_EVEN, Tail::NORM_PLANAR>(frames, w, h, pitch, rects, batch, dw, dh, bg, d0, mean, stdv, out);
+    else if (mode == 4) crop_resize_all<AspectRatio::PRESERVE_AR_LEFT, Tail::NORM_PLANAR>(frames, w, h, pitch, rects, batch, dw, dh, bg, d0, mean, stdv, out);
+    else return -1;
+    return 0;
+}
+#endif
+
 }  // extern "C"

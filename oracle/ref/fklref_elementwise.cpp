@@ -101,6 +101,21 @@ void FKLREF_FN(cast_resize_batch16)(const uint8_t* const* srcs, int w, int h, in
     finish(stream);
 }
 
+#ifndef FKLREF_GPU
+/* A partly filled batch of four images: planes at or beyond `used` read `default_value` instead of their image
+   (BatchRead<4, CONDITIONAL_WITH_DEFAULT>, batch_operations.h:217-241); Cast -> Mul -> TensorWrite<float3>, the
+   continuation handed over operation by operation so that it applies to the default value as well. */
+void FKLREF_FN(batch4_default_cast_mul)(const uint8_t* const* srcs, int w, int h, int spitch, int used, const uint8_t* default_value,
+                                        const float* mul, float* dst) {
+    RefStream stream = make_stream();
+    const uchar3 dv{default_value[0], default_value[1], default_value[2]};
+    const auto read = PerThreadRead<ND::_2D, uchar3>::build(used, dv, batch_u8x3<4>(srcs, w, h, spitch));
+    executeOperations<RefDPP>(stream, read, Cast<uchar3, float3>::build(), Mul<float3>::build(f3(mul)),
+                              TensorWrite<float3>::build(raw_tensor<float3>(dst, w, h, 4, 1)));
+    finish(stream);
+}
+#endif
+
 /* 1 when this library was built with the device-branch prelude, 0 for the literal CPU build. */
 int FKLREF_FN(is_device_branch)(void) {
 #ifdef FKLREF_DEVICE_BRANCH_PRELUDE_H

@@ -16,11 +16,11 @@ namespace {
 
 /* ---- NV12 -> RGB -> resize -> Div -> TensorWrite, one chunk ------------------------ */
 
-template <size_t B>
+template <size_t B, PixelFormat PF = PixelFormat::NV12, ColorPrimitives CP = ColorPrimitives::bt709>
 void nv12_chunk(const uint8_t* const* frames, int w, int h, int pitch, int dw, int dh, const float* div,
                 float* out) {
     RefStream stream = make_stream();
-    using Img = Image<PixelFormat::NV12>;
+    using Img = Image<PF>;
     /* Wrap each frame as a view whose data height equals the image height so that the chroma
        plane is addressed at data + pitch*h (color_conversion.h:336-341, image.h:35-38). */
     auto make = [&](size_t i) {
@@ -32,8 +32,8 @@ void nv12_chunk(const uint8_t* const* frames, int w, int h, int pitch, int dw, i
         return std::array<Img, B>{make(I)...};
     }(std::make_index_sequence<B>{});
     const auto sender =
-        ReadYUV<PixelFormat::NV12>::build(imgs)
-            .then(ConvertYUVToRGB<PixelFormat::NV12, ColorRange::Full, ColorPrimitives::bt709, false, float3>::build())
+        ReadYUV<PF>::build(imgs)
+            .then(ConvertYUVToRGB<PF, ColorRange::Full, CP, false, float3>::build())
             .then(Resize<LINEAR>::build(Size(dw, dh)))
             .then(Div<float3>::build(f3(div)));
     const auto receiver = TensorWrite<float3>::build(raw_tensor<float3>(out, dw, dh, (int)B, 1));
@@ -70,5 +70,24 @@ void FKLREF_FN(nv12_resize)(const uint8_t* const* frames, int w, int h, int pitc
         }
     }
 }
+
+#ifndef FKLREF_GPU
+/* The same chain for other layouts and matrices, pairs of frames: layout 0 = NV12, 1 = NV21 (color_conversion.h:347-359);
+   primitives 0 = bt709, 1 = bt601 (:137-140, luma offset :266-269), 2 = bt2020 (:165-168).  Host build only; batch even. */
+int FKLREF_FN(nv_resize_ex)(const uint8_t* const* frames, int w, int h, int pitch, int batch, int dw, int dh, int layout,
+                            int primitives, const float* div, float* out) {
+    const size_t plane_floats = (size_t)dw * dh * 3;
+    if (batch % 2) return -1;
+    for (int i = 0; i < batch; i += 2) {
+        float* o = out + plane_floats * i;
+        if (layout == 0 && primitives == 1) nv12_chunk<2, PixelFormat::NV12, ColorPrimitives::bt601>(frames + i, w, h, pitch, dw, dh, div, o);
+        else if (layout == 0 && primitives == 2) nv12_chunk<2, PixelFormat::NV12, ColorPrimitives::bt2020>(frames + i, w, h, pitch, dw, dh, div, o);
+        else if (layout == 1 && primitives == 0) nv12_chunk<2, PixelFormat::NV21, ColorPrimitives::bt709>(frames + i, w, h, pitch, dw, dh, div, o);
+        else if (layout == 1 && primitives == 1) nv12_chunk<2, PixelFormat::NV21, ColorPrimitives::bt601>(frames + i, w, h, pitch, dw, dh, div, o);
+        else return -1;
+    }
+    return 0;
+}
+#endif
 
 }  // extern "C"

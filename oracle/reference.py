@@ -164,6 +164,41 @@ def nv12_resize(frames, w, h, dw, dh, div, flavour="device_branch", out=None):
     return out
 
 
+def crop_resize_norm_planar_mode(frames, frame_index, rects, dw, dh, mode, bg, d0, mean, std, flavour="device_branch"):
+    """mode: 3 = PRESERVE_AR_RN_EVEN, 4 = PRESERVE_AR_LEFT.  Returns (B, 3, dh, dw) float32."""
+    h, w, _ = frames[0].shape
+    rects = np.ascontiguousarray(rects, np.int32)
+    b = len(frame_index)
+    out = np.empty((b, 3, dh, dw), np.float32)
+    rc = lib(flavour).fklref_crop_resize_norm_planar_mode(_frames_arg(frames, frame_index), w, h, frames[0].strides[0],
+                                                         rects.ctypes.data_as(_i32p), b, dw, dh, mode, _f3(bg), _f3(d0), _f3(mean),
+                                                         _f3(std), _f32(out))
+    if rc != 0:
+        raise ValueError(f"aspect-ratio mode {mode} is not instantiated in the reference wrapper")
+    return out
+
+
+def nv_resize_ex(frames, w, h, dw, dh, div, layout, primitives, flavour="device_branch"):
+    """layout 0 = NV12, 1 = NV21; primitives 0 = bt709, 1 = bt601, 2 = bt2020.  Returns (B, dh, dw, 3) float32; B even."""
+    b = len(frames)
+    out = np.empty((b, dh, dw, 3), np.float32)
+    ptrs = (C.c_void_p * b)(*[f.ctypes.data for f in frames])
+    rc = lib(flavour).fklref_nv_resize_ex(ptrs, w, h, frames[0].strides[0], b, dw, dh, layout, primitives, _f3(div), _f32(out))
+    if rc != 0:
+        raise ValueError("this layout / matrix pair is not instantiated in the reference wrapper")
+    return out
+
+
+def batch4_default_cast_mul(srcs, used, default_value, mul, flavour="device_branch"):
+    """Four (h,w,3) uint8 images, planes >= used read default_value (3 bytes).  Returns (4, h, w, 3) float32."""
+    h, w, _ = srcs[0].shape
+    out = np.empty((4, h, w, 3), np.float32)
+    ptrs = (C.c_void_p * 4)(*[s.ctypes.data for s in srcs])
+    dv = (C.c_uint8 * 3)(*[int(v) for v in default_value])
+    lib(flavour).fklref_batch4_default_cast_mul(ptrs, w, h, srcs[0].strides[0], used, dv, _f3(mul), _f32(out))
+    return out
+
+
 def resize_params(sw, sh, dw, dh, preserve_ar, flavour="device_branch"):
     fxy = (C.c_float * 2)()
     roi = (C.c_int * 4)()

@@ -85,7 +85,7 @@ def crop_resize_case(name, seed, n_frames, fw, fh, n_planes, dw, dh, planar, pos
 
 
 def nv12_case(name, seed, n_frames, w, h, dw, dh, pitch=None, mode=abi.RESIZE_IGNORE_AR, background=(0.0, 0.0, 0.0),
-              crops=None):
+              crops=None, src_format=abi.SRC_NV12, conversion=abi.OP_YUV_TO_RGB_BT709_FULL):
     rng = np.random.default_rng(seed)
     pitch = pitch or w
     sources = {}
@@ -98,9 +98,31 @@ def nv12_case(name, seed, n_frames, w, h, dw, dh, pitch=None, mode=abi.RESIZE_IG
     def build(ptr):
         return chains.nv12_resize_batch(frame_ptrs=[ptr(f"frame{i}") for i in range(n_frames)], width=w, height=h,
                                         pitch=pitch, dst=ptr("out"), dst_width=dw, dst_height=dh, mode=mode,
-                                        background=background, crops=crops)
+                                        background=background, crops=crops, src_format=src_format, conversion=conversion)
 
     return Case(name, sources, {"out": out}, build)
+
+
+def default_planes_case(name, seed, w, h, mode, dst_fmt, n=5, used=3):
+    """A partly filled batch: planes at or beyond `used` carry FKB_PLANE_DEFAULT_VALUE (and no image at all)."""
+    rng = np.random.default_rng(seed)
+    sources = {f"img{i}": _u8(rng, h, w * 3) for i in range(used)}
+    dw, dh = (w, h) if mode == abi.RESIZE_NONE else (40, 28)
+    dpx = 3 if dst_fmt == abi.DST_U8X3_PACKED else 12
+    out = np.zeros((n, dh, dw * dpx), np.uint8)
+    ops = [op(abi.OP_CAST_F32), op(abi.OP_MUL, (1.5, 0.25, 2.0))] + ([op(abi.OP_SATURATE_CAST_U8)] if dpx == 3 else [])
+
+    def build(ptr):
+        plan = abi.HostPlan()
+        seq = plan.add_sequence(abi.SRC_U8X3, dst_fmt, mode, ops, n_pre_ops=1 if mode != abi.RESIZE_NONE else 0,
+                                background=(7.0, 200.0, 33.0))
+        for i in range(n):
+            plan.add_plane(src=ptr(f"img{i}") if i < used else 0, src_width=w, src_height=h, src_pitch=w * 3,
+                           dst=ptr("out") + i * dh * dw * dpx, dst_width=dw, dst_height=dh, dst_pitch=dw * dpx, sequence=seq,
+                           flags=0 if i < used else abi.PLANE_DEFAULT_VALUE)
+        return plan
+
+    return Case(name, sources, {"out": out}, build, float_outputs=dpx == 12)
 
 
 def resize_any_case(name, seed, src_fmt, dst_fmt, w, h, dw, dh, pre_ops, post_ops, mode=abi.RESIZE_IGNORE_AR):
@@ -232,6 +254,20 @@ def small_cases():
         resize_any_case("resize_then_saturate_u8", 72, abi.SRC_U8X3, abi.DST_U8X3_PACKED, 64, 48, 32, 20,
                         [op(abi.OP_CAST_F32)], [op(abi.OP_MUL, 1.1), op(abi.OP_SATURATE_CAST_U8)]),
         resize_any_case("planar_ignore_ar", 73, abi.SRC_U8X3, abi.DST_F32_PLANAR3, 64, 48, 40, 28, [], chains.normalize_ops()),
+        # the other aspect-ratio modes; NV21 and the bt601 / bt2020 matrices; planes of a partly filled batch
+        crop_resize_case("ar_rn_even", 84, 2, 480, 270, 21, 48, 32, True, chains.normalize_ops(), mode=abi.RESIZE_PRESERVE_AR_RN_EVEN,
+                         background=(3.0, 5.0, 7.0)),
+        crop_resize_case("ar_left_packed", 85, 2, 480, 270, 21, 60, 44, False, chains.readme_ops(), mode=abi.RESIZE_PRESERVE_AR_LEFT,
+                         background=(3.0, 5.0, 7.0)),
+        crop_resize_case("ar_left_odd_dst", 86, 1, 300, 200, 7, 45, 31, True, chains.normalize_ops(), mode=abi.RESIZE_PRESERVE_AR_LEFT),
+        nv12_case("nv21_bt709", 87, 2, 96, 54, 40, 22, src_format=abi.SRC_NV21),
+        nv12_case("nv21_bt601_exact3", 88, 2, 96, 54, 32, 18, src_format=abi.SRC_NV21, conversion=abi.OP_YUV_TO_RGB_BT601_FULL),
+        nv12_case("nv12_bt2020_odd_dst", 89, 2, 96, 54, 37, 21, conversion=abi.OP_YUV_TO_RGB_BT2020_FULL),
+        nv12_case("nv12_bt601_pitched_preserve_ar", 90, 2, 98, 54, 48, 48, pitch=128, mode=abi.RESIZE_PRESERVE_AR_LEFT,
+                  background=(16.0, 128.0, 240.0), conversion=abi.OP_YUV_TO_RGB_BT601_FULL),
+        default_planes_case("default_planes_flat", 91, 64, 32, abi.RESIZE_NONE, abi.DST_F32X3_PACKED),
+        default_planes_case("default_planes_flat_u8", 92, 53, 37, abi.RESIZE_NONE, abi.DST_U8X3_PACKED),
+        default_planes_case("default_planes_resize", 93, 64, 48, abi.RESIZE_PRESERVE_AR, abi.DST_F32X3_PACKED),
         # Cast<float3,int3> / Cast<float3,uint3> closing a chain (truncation toward zero)
         elementwise_case("cast_int3_after_arithmetic", 81, 64, 33, [op(abi.OP_CAST_F32), op(abi.OP_MUL, (1.37, 0.5, 2.25)),
                                                                     op(abi.OP_SUB, (100.5, 3.25, 7.0)), op(abi.OP_CAST_I32)],

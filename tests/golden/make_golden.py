@@ -7,7 +7,8 @@ Run where the reference tree is present, after `make -C oracle ref`:
 Every fixture stores the seeded inputs and the output of oracle/_ref/libfklref_device_branch.so
 (the reference's unmodified source with its device branch selected on the host, see
 oracle/ref/device_branch_prelude.h).  For chains that contain Resize the output of the literal
-CPU build is stored next to it under `literal_*`, to document where the two differ.
+CPU build is stored next to it under `literal_*`, to document where the two differ (that build reads rows
+outside the image, interpolation.h:70, so its values vary from run to run and no test compares them).
 The fixtures are what travels: tests never read the reference tree.
 """
 import sys
@@ -95,6 +96,27 @@ def main():
     np.savez_compressed(OUT / "int_casts.npz", src=img2,
                         cast_mul_sub_cast_int3=ref.cast_mul_sub_cast_int3(img2, (1.37, 0.5, 2.25), (100.5, 3.25, 7.0)),
                         cast_resize_mul_cast_uint3_30x20=ref.cast_resize_mul_cast_uint3(img2, 30, 20, (3.7, 1.0, 0.01)))
+    # --- the other aspect-ratio modes, NV21 and the bt601 / bt2020 matrices, a partly filled batch (own seed) ---
+    rng3 = np.random.default_rng(20240609)
+    frames3 = [u8(rng3, 120, 200, 3) for _ in range(2)]
+    rects4 = chains.random_rects(rng3, 12, 200, 120, lo=3, hi=110)
+    fi4 = [i % 2 for i in range(12)]
+    np.savez_compressed(
+        OUT / "ar_modes.npz", frames=np.stack(frames3), rects=rects4, frame_index=np.array(fi4),
+        rn_even=ref.crop_resize_norm_planar_mode(frames3, fi4, rects4, 44, 30, 3, (3.0, 5.0, 7.0), 255.0, chains.IMAGENET_MEAN,
+                                                 chains.IMAGENET_STD),
+        left=ref.crop_resize_norm_planar_mode(frames3, fi4, rects4, 44, 30, 4, (3.0, 5.0, 7.0), 255.0, chains.IMAGENET_MEAN,
+                                              chains.IMAGENET_STD))
+    nv3 = [u8(rng3, 81, 96) for _ in range(2)]
+    np.savez_compressed(OUT / "nv_layouts.npz", frames=np.stack(nv3),
+                        nv12_bt601=ref.nv_resize_ex(nv3, 96, 54, 40, 22, 255.0, 0, 1),
+                        nv12_bt2020=ref.nv_resize_ex(nv3, 96, 54, 40, 22, 255.0, 0, 2),
+                        nv21_bt709=ref.nv_resize_ex(nv3, 96, 54, 40, 22, 255.0, 1, 0),
+                        nv21_bt601=ref.nv_resize_ex(nv3, 96, 54, 32, 18, 255.0, 1, 1))
+    imgs4 = [u8(rng3, 20, 36, 3) for _ in range(4)]
+    np.savez_compressed(OUT / "default_planes.npz", srcs=np.stack(imgs4),
+                        used2=ref.batch4_default_cast_mul(imgs4, 2, (7, 200, 33), (1.5, 0.25, 2.0)),
+                        used0=ref.batch4_default_cast_mul(imgs4, 0, (7, 200, 33), (1.5, 0.25, 2.0)))
     print("golden vectors written to", OUT)
 
 

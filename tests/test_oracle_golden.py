@@ -207,3 +207,53 @@ def test_port_matches_reference_build_on_empty_regions(oracle_port):
                 for c in range(3):
                     assert np.unique(expect[i, c]).size == 1
         assert n_empty >= 2
+
+
+def test_other_aspect_ratio_modes(oracle_port):
+    """PRESERVE_AR_RN_EVEN and PRESERVE_AR_LEFT (resize.h:42,132-147,200-210) against the reference build's output."""
+    g = np.load(GOLD / "ar_modes.npz")
+    frames = [np.ascontiguousarray(f) for f in g["frames"]]
+    fi = [int(i) for i in g["frame_index"]]
+    for key, mode in (("rn_even", abi.RESIZE_PRESERVE_AR_RN_EVEN), ("left", abi.RESIZE_PRESERVE_AR_LEFT)):
+        out = np.zeros((len(fi), 3, 30, 44), np.float32)
+        plan = chains.crop_resize_batch(frame_ptrs=[f.ctypes.data for f in frames], frame_index=fi, rects=g["rects"], src_width=200,
+                                        src_height=120, src_pitch=600, dst=out.ctypes.data, dst_width=44, dst_height=30,
+                                        post_ops=chains.normalize_ops(), planar=True, mode=mode, background=(3.0, 5.0, 7.0))
+        oracle_port.run(plan)
+        assert _same(out, g[key]), key
+    assert not _same(g["rn_even"], g["left"])
+    # worked examples: 10x7 -> 44x30: height fits (scale 30/7): width round(42.857) = 43 -> even 42, centred at 1; LEFT keeps 43 at 0
+    a = oracle_port.derive_resize(10, 7, 44, 30, abi.RESIZE_PRESERVE_AR_RN_EVEN)
+    b = oracle_port.derive_resize(10, 7, 44, 30, abi.RESIZE_PRESERVE_AR_LEFT)
+    assert (a.target_width, a.x1, a.x2) == (42, 1, 42) and (b.target_width, b.x1, b.x2) == (43, 0, 42)
+
+
+def test_nv21_and_the_other_matrices(oracle_port):
+    g = np.load(GOLD / "nv_layouts.npz")
+    frames = [np.ascontiguousarray(f) for f in g["frames"]]
+    for key, fmt, conv, (dw, dh) in (("nv12_bt601", abi.SRC_NV12, abi.OP_YUV_TO_RGB_BT601_FULL, (40, 22)),
+                                     ("nv12_bt2020", abi.SRC_NV12, abi.OP_YUV_TO_RGB_BT2020_FULL, (40, 22)),
+                                     ("nv21_bt709", abi.SRC_NV21, abi.OP_YUV_TO_RGB_BT709_FULL, (40, 22)),
+                                     ("nv21_bt601", abi.SRC_NV21, abi.OP_YUV_TO_RGB_BT601_FULL, (32, 18))):
+        out = np.zeros((2, dh, dw, 3), np.float32)
+        plan = chains.nv12_resize_batch(frame_ptrs=[f.ctypes.data for f in frames], width=96, height=54, pitch=96,
+                                        dst=out.ctypes.data, dst_width=dw, dst_height=dh, src_format=fmt, conversion=conv)
+        oracle_port.run(plan)
+        assert _same(out, g[key]), key
+
+
+def test_planes_of_a_partly_filled_batch_read_the_default_value(oracle_port):
+    """BatchRead<4, CONDITIONAL_WITH_DEFAULT> (batch_operations.h:217-241) followed by Cast and Mul."""
+    g = np.load(GOLD / "default_planes.npz")
+    srcs = [np.ascontiguousarray(s) for s in g["srcs"]]
+    for key, used in (("used2", 2), ("used0", 0)):
+        out = np.zeros((4, 20, 36, 3), np.float32)
+        plan = abi.HostPlan()
+        seq = plan.add_sequence(abi.SRC_U8X3, abi.DST_F32X3_PACKED, abi.RESIZE_NONE, [op(abi.OP_CAST_F32), op(abi.OP_MUL, (1.5, 0.25, 2.0))],
+                                background=(7.0, 200.0, 33.0))
+        for i in range(4):
+            plan.add_plane(src=srcs[i].ctypes.data if i < used else 0, src_width=36, src_height=20, src_pitch=108,
+                           dst=out.ctypes.data + i * out[0].nbytes, dst_width=36, dst_height=20, dst_pitch=432, sequence=seq,
+                           flags=0 if i < used else abi.PLANE_DEFAULT_VALUE)
+        oracle_port.run(plan)
+        assert _same(out, g[key]), key

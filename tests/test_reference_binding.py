@@ -22,7 +22,7 @@ from oracle import reference as ref
 
 pytestmark = pytest.mark.skipif(not bc.available(), reason="oracle/_ref/libfklref_binding.so not built (reference tree absent)")
 
-PLANE_FIELDS = [f for f, _ in abi.Plane._fields_ if f != "reserved"]
+PLANE_FIELDS = [f for f, _ in abi.Plane._fields_]
 
 
 def _assert_same_plan(expected: abi.HostPlan, fkb_lib):
@@ -97,6 +97,31 @@ def test_nv12_chain_and_single_image_chains_lower_to_the_harness_plans(fkb_lib):
                                          src=f0, dst=out, width=64, height=32, dst_format=abi.DST_U8X3_PACKED), fkb_lib)
 
 
+def test_nv21_left_tsplit_and_partly_filled_batches_lower_to_the_harness_plans(fkb_lib):
+    f0, f1, out = 0x10000000, 0x18000000, 0x20000000
+    bc.nv21_bt601_2(bc.DESCRIBE, [f0, f1], 1920, 1080, 1920, 640, 360, 255.0, out)
+    _assert_same_plan(chains.nv12_resize_batch(frame_ptrs=[f0, f1], width=1920, height=1080, pitch=1920, dst=out, dst_width=640,
+                                               dst_height=360, src_format=abi.SRC_NV21, conversion=abi.OP_YUV_TO_RGB_BT601_FULL), fkb_lib)
+    # PRESERVE_AR_LEFT into a channel-major tensor [3][4][dh][dw] (TensorTSplit)
+    rng = np.random.default_rng(303)
+    rects = chains.random_rects(rng, 4, 960, 540, lo=16, hi=300)
+    dw, dh = 64, 48
+    bc.left_tsplit4(bc.DESCRIBE, [f0, f1, f0, f1], 960, 540, 2880, rects, dw, dh, (1.0, 2.0, 3.0), 255.0, chains.IMAGENET_MEAN,
+                    chains.IMAGENET_STD, out)
+    want = abi.HostPlan()
+    seq = want.add_sequence(abi.SRC_U8X3, abi.DST_F32_PLANAR3, abi.RESIZE_PRESERVE_AR_LEFT, chains.normalize_ops(), background=(1.0, 2.0, 3.0))
+    for i in range(4):
+        want.add_plane(src=[f0, f1][i % 2], src_width=960, src_height=540, src_pitch=2880, crop=tuple(int(v) for v in rects[i]),
+                       dst=out + i * dw * dh * 4, dst_width=dw, dst_height=dh, dst_pitch=dw * 4, dst_channel_stride=4 * dw * dh * 4, sequence=seq)
+    _assert_same_plan(want, fkb_lib)
+    # BatchRead<4, CONDITIONAL_WITH_DEFAULT>: planes 2 and 3 read the default value
+    bc.batch4_default_cast_mul(bc.DESCRIBE, [f0, f1, f0, f1], 64, 32, 192, 2, (7, 200, 33), (1.5, 0.25, 2.0), out)
+    planes, seqs = bc.last_plan()
+    assert [p.flags for p in planes] == [0, 0, abi.PLANE_DEFAULT_VALUE, abi.PLANE_DEFAULT_VALUE]
+    assert [p.sequence for p in planes] == [0, 0, 1, 1] and list(seqs[1][0].background) == [7.0, 200.0, 33.0]
+    assert [(p.dst_width, p.dst_height, p.dst - out) for p in planes] == [(64, 32, i * 64 * 32 * 12) for i in range(4)]
+
+
 @pytest.mark.gpu
 @pytest.mark.skipif(not ref.available(), reason="oracle/_ref not built")
 def test_reference_chains_through_the_binding_equal_the_reference_cpu_backend(fkb_lib):
@@ -155,3 +180,23 @@ def test_reference_chains_through_the_binding_equal_the_reference_cpu_backend(fk
     bc.bgr_cast_mul_saturate(bc.EXECUTE, d_img.data_ptr(), 480, 270, 1440, 1.4, d_u8.data_ptr(), 1440, sh)
     assert abi.async_check(sh) == 0
     assert np.array_equal(d_u8.cpu().numpy(), ref.bgr_cast_mul_saturate(img, 1.4))
+
+    # NV21 + bt601; PRESERVE_AR_LEFT into a channel-major tensor; a partly filled batch
+    d_out = torch.zeros((2, dh, dw, 3), dtype=torch.float32, device="cuda")
+    bc.nv21_bt601_2(bc.EXECUTE, [t.data_ptr() for t in d_nv], w, h, w, dw, dh, 255.0, d_out.data_ptr(), sh)
+    assert abi.async_check(sh) == 0
+    assert same(d_out.cpu().numpy(), ref.nv_resize_ex(nv, w, h, dw, dh, 255.0, 1, 1))
+    rects4 = chains.random_rects(rng, 4, 960, 540, lo=16, hi=300)
+    d_out = torch.zeros((3, 4, 48, 64), dtype=torch.float32, device="cuda")
+    bc.left_tsplit4(bc.EXECUTE, [d_frames[i].data_ptr() for i in range(4)], 960, 540, 2880, rects4, 64, 48, (1.0, 2.0, 3.0), 255.0,
+                    chains.IMAGENET_MEAN, chains.IMAGENET_STD, d_out.data_ptr(), sh)
+    assert abi.async_check(sh) == 0
+    want = ref.crop_resize_norm_planar_mode(frames, [0, 1, 2, 3], rects4, 64, 48, 4, (1.0, 2.0, 3.0), 255.0, chains.IMAGENET_MEAN,
+                                            chains.IMAGENET_STD)              # (4, 3, dh, dw)
+    assert same(d_out.cpu().numpy(), np.ascontiguousarray(want.transpose(1, 0, 2, 3)))
+    imgs = [rng.integers(0, 256, (32, 64, 3), dtype=np.uint8) for _ in range(4)]
+    d_imgs = [dev(a) for a in imgs]
+    d_out = torch.zeros((4, 32, 64, 3), dtype=torch.float32, device="cuda")
+    bc.batch4_default_cast_mul(bc.EXECUTE, [t.data_ptr() for t in d_imgs], 64, 32, 192, 2, (7, 200, 33), (1.5, 0.25, 2.0), d_out.data_ptr(), sh)
+    assert abi.async_check(sh) == 0
+    assert same(d_out.cpu().numpy(), ref.batch4_default_cast_mul(imgs, 2, (7, 200, 33), (1.5, 0.25, 2.0)))
