@@ -12,9 +12,14 @@ One JSON line is printed by rank 0.  `value` is output Mpix/s with inputs reside
 `e2e` is the same metric through the host-buffer C-ABI call (pinned host -> device copies,
 launch, device -> pinned host copy back, every step); `roofline` relates the kernel's
 algorithmic bytes to the measured HBM copy bandwidth; `cpu_baseline` is the reference's own
-CPU code for the same chain, compiled from its headers, timed on this box's host cores.
+CPU code for the same chain, compiled from its headers, timed on this box's host cores;
+`reference_gpu` is the reference's own CUDA kernel, compiled from its headers for sm_100a, on
+the same device buffers; `sustained` repeats the launch for over a second with clocks and power
+sampled; `other_workloads` times the other configurations the same way; with N > 1 `strong`
+splits ONE batch over the ranks, with and without gathering the consolidated tensor by NCCL.
 
-`--impl reference` times that CPU implementation instead (all host threads, rank 0 only).
+`--impl reference` times the reference's CPU implementation instead (all host threads, rank 0 only).
+`--kernel-only` runs the timed region alone (what the profiler captures use).
 """
 from __future__ import annotations
 
@@ -39,7 +44,7 @@ L2_BYTES = 126 * 1024 * 1024
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the workload's kernel, from the ncu
 # capture summarised under profiles/ (None = not captured).
-TRAFFIC_BYTES_PER_LAUNCH = {"c3": 773.3e6, "c4": 472.9e6}
+TRAFFIC_BYTES_PER_LAUNCH = {"c3": 778.8e6, "c4": 470.3e6}
 
 
 # --------------------------------------------------------------------------------------

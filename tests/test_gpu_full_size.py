@@ -1,15 +1,20 @@
 """The configurations at their full sizes on the GPU, through the C ABI.
 
-The checker is too slow to redo a whole configuration in a test, so each case compares a seeded
-sample of planes (or rows) bit for bit and checks the rest through properties that do not depend
-on the size: every output element outside a plane's region of interest holds the one value the
-default takes after the continuation, linearity of the element-wise chains in their input, and a
+The CPU checkers are too slow to redo a whole configuration in a test, so each case compares a seeded
+sample of planes (or rows) bit for bit - with the plain-C checker and, where oracle/_ref is present,
+with the reference's own CPU backend directly - compares EVERY plane with the reference's own CUDA
+kernel (built with -fmad=false; itself compared with the reference's CPU backend in
+test_gpu_reference_kernel.py), and checks the rest through properties that do not depend on the size:
+every output element outside a plane's region of interest holds the one value the default takes
+after the continuation, linearity of the element-wise chains in their input, and a
 second launch that reproduces the first exactly.
 """
 import numpy as np
 import pytest
 
 from fusedkernellibrary_b200 import abi, chains
+from oracle import reference as ref
+from oracle import reference_gpu as refgpu
 from tests import cases as tc
 
 pytestmark = pytest.mark.gpu
@@ -56,6 +61,18 @@ def test_c3_full_size_sampled_planes_and_background(fkb_lib, oracle_port):
     got = d_out[torch.tensor(sel, device="cuda")].cpu().numpy()
     bad = np.flatnonzero(tc.bits(got).reshape(-1) != tc.bits(want).reshape(-1))
     assert bad.size == 0, f"{bad.size} differing words in the sampled planes, first at {bad[:5]}"
+    if ref.available():   # the same planes through the reference's own CPU backend
+        frames3 = [f.reshape(fh, fw, 3) for f in frames]
+        want_ref = ref.crop_resize_norm_planar(frames3, [fi[i] for i in sel], rects[sel], dw, dh, (0, 0, 0), 255.0,
+                                               chains.IMAGENET_MEAN, chains.IMAGENET_STD)
+        assert np.array_equal(tc.bits(got), tc.bits(want_ref)), "sampled planes differ from the reference CPU backend"
+    if refgpu.available("nofma"):   # every plane through the reference's own CUDA kernel
+        d_ref = torch.full((n, 3, dh, dw), float("nan"), dtype=torch.float32, device="cuda")
+        refgpu.set_stream(0, "nofma")
+        refgpu.crop_resize_norm_planar([t.data_ptr() for t in d_frames], fi, fw, fh, fw * 3, rects, dw, dh, (0, 0, 0), 255.0,
+                                       chains.IMAGENET_MEAN, chains.IMAGENET_STD, d_ref.data_ptr(), flavour="nofma")
+        torch.cuda.synchronize()
+        assert torch.equal(_bits(d_ref), _bits(d_out)), "a plane differs from the reference's CUDA kernel"
 
     # every plane: outside its region of interest, the default value after Div, Sub, Div
     host = d_out.cpu().numpy()
@@ -78,6 +95,28 @@ def test_c4_full_size_two_frames(fkb_lib, oracle_port):
     got, info = run_cuda(case, fkb_lib)
     assert info.n_launches == 1
     assert np.array_equal(tc.bits(got["out"]), tc.bits(expected["out"]))
+    if ref.available():
+        want_ref = ref.nv12_resize([case.sources["frame0"], case.sources["frame1"]], 3840, 2160, 1280, 720, 255.0)
+        assert np.array_equal(tc.bits(got["out"]), tc.bits(want_ref)), "differs from the reference CPU backend"
+
+
+@pytest.mark.skipif(not refgpu.available("nofma"), reason="reference CUDA build not present")
+def test_c4_full_size_all_32_frames_against_the_reference_kernel(fkb_lib):
+    rng = np.random.default_rng(1007)
+    n, w, h, dw, dh = 32, 3840, 2160, 1280, 720
+    d_frames = [torch.from_numpy(rng.integers(0, 256, (h + h // 2, w), dtype=np.uint8)).cuda() for _ in range(n)]
+    ptrs = [t.data_ptr() for t in d_frames]
+    d_out = torch.full((n, dh, dw, 3), float("nan"), dtype=torch.float32, device="cuda")
+    d_ref = torch.full((n, dh, dw, 3), float("nan"), dtype=torch.float32, device="cuda")
+    plan = abi.DevicePlan(chains.nv12_resize_batch(frame_ptrs=ptrs, width=w, height=h, pitch=w, dst=d_out.data_ptr(), dst_width=dw,
+                                                   dst_height=dh))
+    plan.launch()
+    assert plan.check() == 0
+    plan.destroy()
+    refgpu.set_stream(0, "nofma")
+    refgpu.nv12_resize(ptrs, w, h, w, dw, dh, 255.0, d_ref.data_ptr(), flavour="nofma")
+    torch.cuda.synchronize()
+    assert torch.equal(_bits(d_ref), _bits(d_out))
 
 
 def test_c1_and_c5a_full_size(fkb_lib, oracle_port):
@@ -98,6 +137,12 @@ def test_c5b_full_resolution_two_images_per_group(fkb_lib, oracle_port):
     assert info.n_launches == 1 and info.n_sequences == 4
     for k in expected:
         assert np.array_equal(tc.bits(got[k]), tc.bits(expected[k])), k
+    if ref.available():   # one image of each group through the reference's own CPU backend
+        img = lambda g: case.sources[f"img{g * 2}"].reshape(1080, 1920, 3)
+        assert np.array_equal(tc.bits(got["g0"][0]), tc.bits(ref.cast_mul_sub(img(0), 1.4, 0.5)))
+        assert np.array_equal(tc.bits(got["g1"][0]), tc.bits(ref.cast_add_div(img(1), 0.5, 255.0)))
+        assert np.array_equal(got["g2"][0], ref.bgr_cast_mul_saturate(img(2), 1.4))
+        assert np.array_equal(tc.bits(got["g3"][0]), tc.bits(ref.cast_resize(img(3), 960, 540)))
 
 
 def test_c2_scaled_readme_rects_over_many_planes(fkb_lib, oracle_port):
@@ -122,5 +167,8 @@ def test_c2_scaled_readme_rects_over_many_planes(fkb_lib, oracle_port):
                                              src_width=fw, src_height=fh, src_pitch=fw * 3, dst=want.ctypes.data, dst_width=60,
                                              dst_height=60, post_ops=chains.readme_ops(), planar=False))
     assert np.array_equal(tc.bits(got[:40]), tc.bits(want))
+    if ref.available():
+        want_ref = ref.crop_resize_readme([f.reshape(fh, fw, 3) for f in frames], fi[:40], rects[:40], 60, 60, (0, 0, 0), 1.4, 0.5, 255.0)
+        assert np.array_equal(tc.bits(got[:40]), tc.bits(want_ref)), "differs from the reference CPU backend"
     for i in range(40, n):
         assert np.array_equal(tc.bits(got[i]), tc.bits(got[i % 40])), f"plane {i} differs from its twin {i % 40}"
