@@ -26,6 +26,9 @@ ERR_DEVICE_WAIT = 6
 SRC_U8X3, SRC_F32X3, SRC_NV12, SRC_NV21 = 1, 2, 3, 4
 DST_F32X3_PACKED, DST_F32_PLANAR3, DST_U8X3_PACKED, DST_I32X3_PACKED, DST_U32X3_PACKED = 1, 2, 3, 4, 5
 RESIZE_NONE, RESIZE_IGNORE_AR, RESIZE_PRESERVE_AR, RESIZE_PRESERVE_AR_RN_EVEN, RESIZE_PRESERVE_AR_LEFT = 0, 1, 2, 3, 4
+GEOMETRY_WARP_AFFINE, GEOMETRY_WARP_PERSPECTIVE = 5, 6
+BORDER_NONE, BORDER_CONSTANT, BORDER_REPLICATE, BORDER_REFLECT, BORDER_WRAP, BORDER_REFLECT_101 = range(6)
+DEINTERLACE_NONE, DEINTERLACE_BLEND, DEINTERLACE_LINEAR_EVEN, DEINTERLACE_LINEAR_ODD = range(4)
 PLANE_DEFAULT_VALUE = 1
 (OP_MUL, OP_SUB, OP_DIV, OP_ADD, OP_CAST_F32, OP_SWAP_RB, OP_SATURATE_CAST_U8,
  OP_YUV_TO_RGB_BT709_FULL, OP_CAST_I32, OP_CAST_U32) = range(1, 11)
@@ -48,6 +51,10 @@ class Sequence(C.Structure):
         ("n_pre_ops", C.c_int32),
         ("background", C.c_float * 3),
         ("ops", C.POINTER(Op)),
+        ("border_mode", C.c_int32),
+        ("border_value", C.c_float * 3),
+        ("deinterlace", C.c_int32),
+        ("transform", C.c_float * 9),
     ]
 
 
@@ -138,7 +145,8 @@ class HostPlan:
         self._desc = None
 
     def add_sequence(self, src_format, dst_format, resize_mode, ops, n_pre_ops=0,
-                     background=(0.0, 0.0, 0.0)) -> int:
+                     background=(0.0, 0.0, 0.0), border_mode=0, border_value=(0.0, 0.0, 0.0), deinterlace=0,
+                     transform=None) -> int:
         arr = (Op * max(len(ops), 1))(*ops)
         self._op_arrays.append(arr)
         s = Sequence()
@@ -146,6 +154,10 @@ class HostPlan:
         s.n_ops, s.n_pre_ops = len(ops), n_pre_ops
         s.background[0], s.background[1], s.background[2] = (float(v) for v in background)
         s.ops = C.cast(arr, C.POINTER(Op))
+        s.border_mode, s.deinterlace = border_mode, deinterlace
+        s.border_value[0], s.border_value[1], s.border_value[2] = (float(v) for v in border_value)
+        for k, v in enumerate(transform if transform is not None else [0.0] * 9):
+            s.transform[k] = float(v)
         self._seqs.append(s)
         self._desc = None
         return len(self._seqs) - 1

@@ -366,6 +366,84 @@ __device__ __forceinline__ float blend(float p00, float p10, float p01, float p1
 /* ------------------------------------------------------------------------------------ */
 /* body: generic, one output pixel per thread                                           */
 /* ------------------------------------------------------------------------------------ */
+/* BorderReader's index maps (border_reader.h:163-273): idx_low(idx_high(i)), for an axis of n elements. */
+__device__ __forceinline__ int border_index(int mode, int i, int n) {
+    const int last = n - 1;
+    switch (mode) {
+        case FKB_BORDER_REPLICATE: return max(min(i, last), 0);
+        case FKB_BORDER_REFLECT: {
+            const int v = last - abs(last - i) + (i > last ? 1 : 0);
+            return (abs(v) - (v < 0 ? 1 : 0)) % n;
+        }
+        case FKB_BORDER_WRAP: {
+            const int v = i < n ? i : i % n;
+            return v >= 0 ? v : v - ((v - n + 1) / n) * n;
+        }
+        case FKB_BORDER_REFLECT_101: {
+            const int v = abs(last - abs(last - i)) % n;
+            return abs(v) % n;
+        }
+        default: return i;
+    }
+}
+
+/* The source element at image coordinates (x, y), inside the image. */
+__device__ __forceinline__ void read_image(const DevSeq& S, const DevPlane& P, int x, int y, float (&r)[3]) {
+    if (S.src_format == FKB_SRC_U8X3) {
+        const uint8_t* p = P.src + (size_t)y * P.src_pitch + (size_t)x * 3;
+        r[0] = u8_to_float(__ldg(p)); r[1] = u8_to_float(__ldg(p + 1)); r[2] = u8_to_float(__ldg(p + 2));
+    } else {
+        const float* p = reinterpret_cast<const float*>(P.src + (size_t)y * P.src_pitch + (size_t)x * 12);
+        r[0] = __ldg(p); r[1] = __ldg(p + 1); r[2] = __ldg(p + 2);
+    }
+}
+
+/* The read chain of the one-pixel-per-thread body at crop-relative (a, b): PerThreadRead, then BorderReader or
+ * Deinterlace if the sequence has one, then Crop (crop.h:35-38 adds the rect origin on the way down). */
+__device__ __forceinline__ void fetch_generic(const DevSeq& S, const DevPlane& P, int a, int b, float (&r)[3]) {
+    if (S.border_mode == FKB_BORDER_NONE && S.deinterlace == FKB_DEINTERLACE_NONE) {
+        read_tap_any(S, P, a, b, r[0], r[1], r[2]);
+        return;
+    }
+    const int x = a + P.crop_x, y = b + P.crop_y, w = (int)P.gw, h = (int)P.src_height;
+    if (S.border_mode != FKB_BORDER_NONE) {
+        if (S.border_mode == FKB_BORDER_CONSTANT) { /* border_reader.h:140-148 */
+            if (x >= 0 && x < w && y >= 0 && y < h) read_image(S, P, x, y, r);
+            else { r[0] = S.border_value[0]; r[1] = S.border_value[1]; r[2] = S.border_value[2]; }
+        } else {
+            read_image(S, P, border_index(S.border_mode, x, w), border_index(S.border_mode, y, h), r);
+        }
+        return;
+    }
+    /* Deinterlace (deinterlace.h:91-131): the row, or the mean of two rows with the reference's +1: for uchar3 the sum
+       is an integer sum (exact in binary32), for float3 two rounded additions; then * 0.5f */
+    const bool blend_mode = S.deinterlace == FKB_DEINTERLACE_BLEND;
+    bool two;
+    int ya, yb;
+    if (blend_mode) { two = y > 0; ya = y; yb = y - 1; }
+    else {
+        const bool even = (y & 1) == 0;
+        two = S.deinterlace == FKB_DEINTERLACE_LINEAR_EVEN ? (!even && y != h - 1) : (even && y != 0);
+        ya = y - 1; yb = y + 1;
+    }
+    if (!two) { read_image(S, P, x, y, r); return; }
+    float p[3], q[3];
+    read_image(S, P, x, ya, p);
+    read_image(S, P, x, yb, q);
+#pragma unroll
+    for (int c = 0; c < 3; ++c) r[c] = __fmul_rn(__fadd_rn(__fadd_rn(p[c], q[c]), 1.0f), 0.5f);
+}
+
+/* Bilinear geometry at a source coordinate that is already known (Warping, warping.h:89-92 -> interpolation.h:61-96). */
+__device__ __forceinline__ Axis make_axis_at(float s, int src_extent) {
+    Axis ax;
+    ax.i0 = __float2int_rd(s);
+    ax.i1 = min(ax.i0 + 1, src_extent - 1);
+    ax.w0 = __fsub_rn((float)(ax.i0 + 1), s);
+    ax.w1 = __fsub_rn(s, (float)ax.i0);
+    return ax;
+}
+
 __device__ __forceinline__ void body_generic(const DevPlane& P, const DevSeq& S, const OpSlot* sops, uint32_t local) {
     const uint32_t idx = local * ITEM_PIXELS_GENERIC + threadIdx.x;
     if (idx >= P.dst_w * P.dst_h) return;
@@ -375,21 +453,42 @@ __device__ __forceinline__ void body_generic(const DevPlane& P, const DevSeq& S,
     int first_post = 0;
     /* a plane whose region is empty (a default-value plane, batch_operations.h:236-241) has no geometry stage either way */
     if (S.resize_mode == FKB_RESIZE_NONE && P.x2 >= P.x1) {
-        read_tap_any(S, P, x, y, v[0], v[1], v[2]);
+        fetch_generic(S, P, x, y, v);
     } else {
         first_post = S.n_pre;
-        /* Resize::exec (resize.h:75-87): outside the region of interest return the default */
-        if (!(x >= P.x1 && x <= P.x2 && y >= P.y1 && y <= P.y2)) {
-            v[0] = S.bg[0]; v[1] = S.bg[1]; v[2] = S.bg[2];
+        const bool warp = S.resize_mode == FKB_GEOMETRY_WARP_AFFINE || S.resize_mode == FKB_GEOMETRY_WARP_PERSPECTIVE;
+        bool inside;
+        Axis ax, ay;
+        if (warp) {
+            /* WarpingCoords (warping.h:49-69): every product and sum rounded, int coordinates converted to float */
+            const float* m = S.transform;
+            const float fx = (float)x, fy = (float)y;
+            float cx = __fadd_rn(__fadd_rn(__fmul_rn(m[0], fx), __fmul_rn(m[1], fy)), m[2]);
+            float cy = __fadd_rn(__fadd_rn(__fmul_rn(m[3], fx), __fmul_rn(m[4], fy)), m[5]);
+            if (S.resize_mode == FKB_GEOMETRY_WARP_PERSPECTIVE) {
+                const float coeff = __fdiv_rn(1.0f, __fadd_rn(__fadd_rn(__fmul_rn(m[6], fx), __fmul_rn(m[7], fy)), m[8]));
+                cx = __fmul_rn(coeff, cx);
+                cy = __fmul_rn(coeff, cy);
+            }
+            inside = cx >= 0.0f && cx < (float)P.crop_w && cy >= 0.0f && cy < (float)P.crop_h; /* warping.h:89 */
+            ax = make_axis_at(inside ? cx : 0.0f, P.crop_w);
+            ay = make_axis_at(inside ? cy : 0.0f, P.crop_h);
         } else {
-            const Axis ax = make_axis(x - P.x1, P.fx, P.crop_w);
-            const Axis ay = make_axis(y - P.y1, P.fy, P.crop_h);
+            /* Resize::exec (resize.h:75-87): outside the region of interest return the default */
+            inside = x >= P.x1 && x <= P.x2 && y >= P.y1 && y <= P.y2;
+            ax = make_axis(inside ? x - P.x1 : 0, P.fx, P.crop_w);
+            ay = make_axis(inside ? y - P.y1 : 0, P.fy, P.crop_h);
+        }
+        if (!inside) {
+            if (warp) { v[0] = 0.0f; v[1] = 0.0f; v[2] = 0.0f; } /* warping.h:92 */
+            else { v[0] = S.bg[0]; v[1] = S.bg[1]; v[2] = S.bg[2]; }
+        } else {
             float t[4][3];
-            read_tap_any(S, P, ax.i0, ay.i0, t[0][0], t[0][1], t[0][2]);
-            read_tap_any(S, P, ax.i1, ay.i0, t[1][0], t[1][1], t[1][2]);
-            read_tap_any(S, P, ax.i0, ay.i1, t[2][0], t[2][1], t[2][2]);
-            read_tap_any(S, P, ax.i1, ay.i1, t[3][0], t[3][1], t[3][2]);
-            if (S.pre_kind != PRE_IDENTITY) {
+            fetch_generic(S, P, ax.i0, ay.i0, t[0]);
+            fetch_generic(S, P, ax.i1, ay.i0, t[1]);
+            fetch_generic(S, P, ax.i0, ay.i1, t[2]);
+            fetch_generic(S, P, ax.i1, ay.i1, t[3]);
+            if (S.pre_kind != PRE_IDENTITY && S.n_pre > 0) {
 #pragma unroll
                 for (int k = 0; k < 4; ++k) run_ops_1<CHAIN_INTERPRET>(t[k], sops, 0, S.n_pre, one);
             }

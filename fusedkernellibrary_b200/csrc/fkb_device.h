@@ -54,7 +54,7 @@ struct alignas(16) DevPlane {
     /* RESIZE classes: tiling of the region of interest (see ResizeTiling) */
     uint32_t roi_items;      /* work items that interpolate; the rest fill background rows    */
     uint32_t tiles_x;        /* STAGED classes: output rows per work item (band)               */
-    uint32_t gw;
+    uint32_t gw;             /* CLASS_GENERIC: the source image's width (border handling)      */
     uint32_t rs;
 };
 static_assert(sizeof(DevPlane) == 112, "DevPlane layout");
@@ -74,8 +74,14 @@ struct alignas(16) DevSeq {
     float one;                       /* 1.0f, read at run time by the packed additions         */
     float bg_out[3];                 /* bg after the operations that follow the geometry stage  */
     uint32_t swap_uv;                /* 1: the chroma pair of a tap is stored V,U (NV21)         */
+    /* read-back operations that only the one-pixel-per-thread body takes */
+    int32_t border_mode;             /* fkb_border_mode                                          */
+    int32_t deinterlace;             /* fkb_deinterlace_mode                                     */
+    float border_value[3];
+    float transform[9];              /* FKB_GEOMETRY_WARP_*: rows of three                        */
+    uint32_t pad[2];
 };
-static_assert(sizeof(DevSeq) == 64, "DevSeq layout");
+static_assert(sizeof(DevSeq) == 128, "DevSeq layout");
 
 enum PreKind : int32_t {
     PRE_IDENTITY = 0, /* nothing, or only exact uchar->float casts, before interpolation      */

@@ -489,13 +489,15 @@ static uint32_t chain_code_of(int dev_opcode) {
 static uint32_t lower_ops(const fkb_sequence& s, int n_pre, int step_exp_x, int step_exp_y, std::vector<DevOp>& out,
                           int& dev_n_pre) {
     ValueRange v;
-    if (s.src_format != FKB_SRC_F32X3) v = ValueRange{true, 255.0, 0, 0, true, false};
+    const bool extras = s.border_mode != FKB_BORDER_NONE || s.deinterlace != FKB_DEINTERLACE_NONE || s.resize_mode >= FKB_GEOMETRY_WARP_AFFINE;
+    if (s.src_format != FKB_SRC_F32X3 && !extras) v = ValueRange{true, 255.0, 0, 0, true, false};
     dev_n_pre = (int)out.size();
     uint32_t chain = 0;
     int chain_len = 0;
     for (int k = 0; k <= s.n_ops; ++k) {
         if (k == n_pre && s.resize_mode != FKB_RESIZE_NONE) {
             advance_range_resize(v, step_exp_x, step_exp_y, s.resize_mode >= FKB_RESIZE_PRESERVE_AR, s.background);
+            if (extras) v.known = false;
             dev_n_pre = (int)out.size();
             chain = 0; chain_len = 0;
         }
@@ -585,8 +587,16 @@ static int check_sequence(const fkb_sequence& s, int index, DevSeq& ds) {
         return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d: unknown source format %d", index, s.src_format);
     if (s.dst_format < FKB_DST_F32X3_PACKED || s.dst_format > FKB_DST_U32X3_PACKED)
         return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d: unknown destination format %d", index, s.dst_format);
-    if (s.resize_mode < FKB_RESIZE_NONE || s.resize_mode > FKB_RESIZE_PRESERVE_AR_LEFT)
+    if (s.resize_mode < FKB_RESIZE_NONE || s.resize_mode > FKB_GEOMETRY_WARP_PERSPECTIVE)
         return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d: unknown resize mode %d", index, s.resize_mode);
+    if (s.border_mode < FKB_BORDER_NONE || s.border_mode > FKB_BORDER_REFLECT_101)
+        return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d: unknown border mode %d", index, s.border_mode);
+    if (s.deinterlace < FKB_DEINTERLACE_NONE || s.deinterlace > FKB_DEINTERLACE_LINEAR_ODD)
+        return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d: unknown deinterlace mode %d", index, s.deinterlace);
+    if ((s.border_mode != FKB_BORDER_NONE || s.deinterlace != FKB_DEINTERLACE_NONE) && is_yuv_source(s.src_format))
+        return fail(FKB_ERR_UNSUPPORTED, "sequence %d: BorderReader and Deinterlace over a YUV read are not on this path", index);
+    if (s.border_mode != FKB_BORDER_NONE && s.deinterlace != FKB_DEINTERLACE_NONE)
+        return fail(FKB_ERR_UNSUPPORTED, "sequence %d: BorderReader together with Deinterlace is not on this path", index);
     if (s.n_ops < 0 || s.n_ops > 4096) return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d: n_ops %d outside [0, 4096]", index, s.n_ops);
     if (s.n_ops > 0 && !s.ops) return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d: ops is NULL", index);
     const int n_pre = s.resize_mode == FKB_RESIZE_NONE ? 0 : s.n_pre_ops;
@@ -594,6 +604,7 @@ static int check_sequence(const fkb_sequence& s, int index, DevSeq& ds) {
         return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d: n_pre_ops %d outside [0, n_ops]", index, s.n_pre_ops);
 
     ValueType t = s.src_format == FKB_SRC_U8X3 ? VT_U8 : s.src_format == FKB_SRC_F32X3 ? VT_F32 : VT_YUV8;
+    if (s.deinterlace != FKB_DEINTERLACE_NONE) t = VT_F32; /* Deinterlace returns float3 (deinterlace.h:47-50) */
     bool pre_only_casts = true, pre_is_yuv = (n_pre == 1);
     int yuv_opcode = 0;
     for (int k = 0; k <= s.n_ops; ++k) {
@@ -650,7 +661,15 @@ static int check_sequence(const fkb_sequence& s, int index, DevSeq& ds) {
        kernels store them through the float3 receiver */
     if (want == VT_I32 || want == VT_U32) ds.dst_format = FKB_DST_F32X3_PACKED;
     ds.n_ops = s.n_ops; ds.n_pre = n_pre; ds.ops_begin = 0; ds.chain = CHAIN_INTERPRET;
-    ds.pre_kind = (n_pre == 0 || pre_only_casts) ? PRE_IDENTITY
+    const bool read_back_extras = s.border_mode != FKB_BORDER_NONE || s.deinterlace != FKB_DEINTERLACE_NONE ||
+                                  s.resize_mode >= FKB_GEOMETRY_WARP_AFFINE;
+    ds.border_mode = s.border_mode; ds.deinterlace = s.deinterlace;
+    for (int c = 0; c < 3; ++c) ds.border_value[c] = s.border_value[c];
+    for (int k = 0; k < 9; ++k) ds.transform[k] = s.transform[k];
+    ds.pad[0] = ds.pad[1] = 0;
+    /* BorderReader, Deinterlace and Warping run in the one-pixel-per-thread body only */
+    ds.pre_kind = read_back_extras ? PRE_GENERAL
+                  : (n_pre == 0 || pre_only_casts) ? PRE_IDENTITY
                   : !pre_is_yuv ? PRE_GENERAL
                   : yuv_opcode == FKB_OP_YUV_TO_RGB_BT709_FULL ? PRE_YUV_BT709
                   : yuv_opcode == FKB_OP_YUV_TO_RGB_BT601_FULL ? PRE_YUV_BT601 : PRE_YUV_BT2020;
@@ -848,8 +867,11 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
                 return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: source pitch %u is less than a row of %llu bytes", i, p.src_pitch, (unsigned long long)src_row);
             if ((uint64_t)p.src_pitch * p.src_height * 2 > 0xFFFFFFFFull)
                 return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: source image beyond 2 GiB", i);
-            if (p.crop_x < 0 || p.crop_y < 0 || p.crop_width <= 0 || p.crop_height <= 0 ||
-                (uint64_t)p.crop_x + (uint64_t)p.crop_width > p.src_width || (uint64_t)p.crop_y + (uint64_t)p.crop_height > p.src_height)
+            const bool padded = s.border_mode != FKB_BORDER_NONE; /* BorderReader below the Crop: the rect may reach beyond the image */
+            if (p.crop_width <= 0 || p.crop_height <= 0 || p.crop_width > (1 << 24) || p.crop_height > (1 << 24) ||
+                (padded ? (p.crop_x < -(1 << 24) || p.crop_y < -(1 << 24) || p.crop_x > (1 << 24) || p.crop_y > (1 << 24))
+                        : (p.crop_x < 0 || p.crop_y < 0 || (uint64_t)p.crop_x + (uint64_t)p.crop_width > p.src_width ||
+                           (uint64_t)p.crop_y + (uint64_t)p.crop_height > p.src_height)))
                 return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: crop rect (%d,%d,%d,%d) outside its %ux%u image", i, p.crop_x, p.crop_y, p.crop_width, p.crop_height, p.src_width, p.src_height);
             if (s.resize_mode == FKB_RESIZE_NONE && ((uint32_t)p.crop_width != p.dst_width || (uint32_t)p.crop_height != p.dst_height))
                 return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: without a resize the output (%ux%u) must have the size of the crop (%dx%d)", i, p.dst_width, p.dst_height, p.crop_width, p.crop_height);
@@ -878,6 +900,8 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
             dp.src = nullptr; dp.src_pitch = 0; dp.src_height = 0;
             dp.crop_x = dp.crop_y = 0; dp.crop_w = dp.crop_h = 1;
             dp.x1 = 0; dp.y1 = 0; dp.x2 = -1; dp.y2 = -1;
+        } else if (s.resize_mode >= FKB_GEOMETRY_WARP_AFFINE) {
+            /* Warping: every output element is computed (inside the source or 0); no host-derived factors */
         } else if (s.resize_mode != FKB_RESIZE_NONE) {
             fkb_resize_params& rp = img.resize[i];
             const int rc = fkb_derive_resize(p.crop_width, p.crop_height, (int32_t)p.dst_width, (int32_t)p.dst_height, s.resize_mode, &rp);
@@ -900,7 +924,8 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
         const uint64_t out_px = (uint64_t)p.dst_width * p.dst_height;
         uint32_t cls = CLASS_GENERIC;
         uint64_t items = 0;
-        if (s.resize_mode == FKB_RESIZE_NONE && !is_default && s.dst_format != FKB_DST_F32_PLANAR3 && s.src_format != FKB_SRC_NV12) {
+        if (s.resize_mode == FKB_RESIZE_NONE && !is_default && s.dst_format != FKB_DST_F32_PLANAR3 && s.src_format != FKB_SRC_NV12 &&
+            s.pre_kind != PRE_GENERAL) {
             const bool src_u8 = s.src_format == FKB_SRC_U8X3, dst_u8 = s.dst_format == FKB_DST_U8X3_PACKED;
             const uintptr_t sa = src_u8 ? 4 : 16, da = dst_u8 ? 4 : 16;
             const uint8_t* src0 = dp.src + (size_t)p.crop_y * p.src_pitch + (size_t)p.crop_x * spx;
@@ -928,7 +953,10 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
                 else if (t.n_groups != first_groups) same_groups = false;
             }
         }
-        if (cls == CLASS_GENERIC) items = (out_px + ITEM_PIXELS_GENERIC - 1) / ITEM_PIXELS_GENERIC;
+        if (cls == CLASS_GENERIC) {
+            items = (out_px + ITEM_PIXELS_GENERIC - 1) / ITEM_PIXELS_GENERIC;
+            dp.gw = p.src_width; /* the generic body's border handling needs the image width */
+        }
         dp.plane_class = cls;
         if (i == 0) common_class = cls;
         else {
@@ -1359,7 +1387,7 @@ bool ranges_overlap(size_t a, size_t an, size_t b, size_t bn) { return a < b + b
 /* The description as one byte string (pointers included: the same chain over other buffers is another plan). */
 void description_key(const fkb_plan_desc* d, std::vector<unsigned char>& key) {
     size_t n = 2 * sizeof(int32_t) + (size_t)d->n_planes * sizeof(fkb_plane);
-    for (int s = 0; s < d->n_sequences; ++s) n += 8 * sizeof(int32_t) + (size_t)std::max(d->sequences[s].n_ops, 0) * sizeof(fkb_op);
+    for (int s = 0; s < d->n_sequences; ++s) n += 22 * sizeof(int32_t) + (size_t)std::max(d->sequences[s].n_ops, 0) * sizeof(fkb_op);
     key.resize(n);
     unsigned char* o = key.data();
     auto put = [&](const void* p, size_t bytes) { std::memcpy(o, p, bytes); o += bytes; };
@@ -1368,6 +1396,7 @@ void description_key(const fkb_plan_desc* d, std::vector<unsigned char>& key) {
         const fkb_sequence& q = d->sequences[s];
         put(&q.src_format, 4); put(&q.dst_format, 4); put(&q.resize_mode, 4); put(&q.n_ops, 4); put(&q.n_pre_ops, 4);
         put(q.background, 12);
+        put(&q.border_mode, 4); put(q.border_value, 12); put(&q.deinterlace, 4); put(q.transform, 36);
         if (q.n_ops > 0) put(q.ops, (size_t)q.n_ops * sizeof(fkb_op));
     }
     put(d->planes, (size_t)d->n_planes * sizeof(fkb_plane));

@@ -76,8 +76,33 @@ typedef enum fkb_resize_mode {
     FKB_RESIZE_PRESERVE_AR = 2, /* Resize<INTER_LINEAR, PRESERVE_AR> (resize.h:121-166)         */
     FKB_RESIZE_PRESERVE_AR_RN_EVEN = 3, /* PRESERVE_AR_RN_EVEN: target width (or, when the width is    */
                                 /* the limit, height) rounded down to an even number (resize.h:200-210) */
-    FKB_RESIZE_PRESERVE_AR_LEFT = 4 /* PRESERVE_AR_LEFT: the region starts at column 0 (resize.h:132-147) */
+    FKB_RESIZE_PRESERVE_AR_LEFT = 4, /* PRESERVE_AR_LEFT: the region starts at column 0 (resize.h:132-147) */
+    FKB_GEOMETRY_WARP_AFFINE = 5,   /* Warping<WarpType::Affine> (image_processing/warping.h:43-104): output (x,y)   */
+                                /* reads the source at (m00 x + m01 y + m02, m10 x + m11 y + m12), bilinear like   */
+                                /* the resize, 0 where that point lies outside the source                          */
+    FKB_GEOMETRY_WARP_PERSPECTIVE = 6 /* Warping<WarpType::Perspective>: the same through a 3x3 matrix (:55-61)   */
 } fkb_resize_mode;
+
+/* How the read operation answers coordinates outside its image: BorderReader<BT, Read> (border_reader.h:136-279).
+ * With a border mode the crop rect may reach beyond the image (a padded crop): the read chain is
+ * PerThreadRead -> BorderReader -> Crop -> geometry stage. */
+typedef enum fkb_border_mode {
+    FKB_BORDER_NONE = 0,        /* no BorderReader: the crop must lie inside the image                 */
+    FKB_BORDER_CONSTANT = 1,    /* `iiiiii|abcdefgh|iiiiiii` with border_value                          */
+    FKB_BORDER_REPLICATE = 2,   /* `aaaaaa|abcdefgh|hhhhhhh`                                            */
+    FKB_BORDER_REFLECT = 3,     /* `fedcba|abcdefgh|hgfedcb`                                            */
+    FKB_BORDER_WRAP = 4,        /* `cdefgh|abcdefgh|abcdefg`                                            */
+    FKB_BORDER_REFLECT_101 = 5  /* `gfedcb|abcdefgh|gfedcba`                                            */
+} fkb_border_mode;
+
+/* Deinterlace<DType, Read> (deinterlace.h:41-132) between the read and the crop, in image rows. */
+typedef enum fkb_deinterlace_mode {
+    FKB_DEINTERLACE_NONE = 0,
+    FKB_DEINTERLACE_BLEND = 1,        /* (row + row above + 1) * 0.5, the first row as it is (:91-103)   */
+    FKB_DEINTERLACE_LINEAR_EVEN = 2,  /* INTER_LINEAR keeping the even rows: odd rows but the last are   */
+                                      /* (above + below + 1) * 0.5 (:105-131)                            */
+    FKB_DEINTERLACE_LINEAR_ODD = 3    /* keeping the odd rows: even rows but the first are interpolated  */
+} fkb_deinterlace_mode;
 
 /* Element-wise operations, applied per channel in IEEE-754 binary32 with no contraction.   */
 typedef enum fkb_opcode {
@@ -123,6 +148,10 @@ typedef struct fkb_sequence {
                           /* still applies to it (resize.h:84-86).  Also the value that      */
                           /* planes flagged FKB_PLANE_DEFAULT_VALUE read.                    */
     const fkb_op* ops;    /* HOST pointer, n_ops entries (may be NULL when n_ops == 0)       */
+    int32_t border_mode;  /* fkb_border_mode                                                  */
+    float border_value[3];/* FKB_BORDER_CONSTANT: the value outside the image (source type)   */
+    int32_t deinterlace;  /* fkb_deinterlace_mode; the read then returns float3               */
+    float transform[9];   /* FKB_GEOMETRY_WARP_*: the matrix, rows of three (affine: two rows) */
 } fkb_sequence;
 
 /* One output plane (the reference's thread.z / blockIdx.z, data_parallel_patterns.h:260). */
@@ -358,7 +387,7 @@ FKB_API int fkb_execute_host(const fkb_plan_desc* desc, void* stream);
  * image pointers are the caller's, as everywhere else.  Behaviour:
  *  - validates and lowers `desc` exactly like fkb_plan_create, copies the table into the fixed
  *    array on `stream`, launches, and synchronises `stream` before returning;
- *  - a plan whose table (112 B per plane + 64 B per sequence + 16 B per operation + 16 or 32 B
+ *  - a plan whose table (112 B per plane + 128 B per sequence + 16 B per operation + 16 or 32 B
  *    per thread block of its launch) exceeds FKB_STATIC_TABLE_BYTES is refused with
  *    FKB_ERR_TOO_LARGE, nothing runs;
  *  - calls cudaMalloc, cudaFree or an allocating library routine never; host memory only;

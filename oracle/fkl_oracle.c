@@ -90,6 +90,58 @@ static px3 read_tap(const fkb_plane* pl, int src_format, int a, int b) {
     return r;
 }
 
+/* BorderReader's index maps: idx_low(idx_high(i)) for an axis of n elements (border_reader.h:163-273). */
+static int border_index(int mode, int i, int n) {
+    const int last = n - 1;
+    int v;
+    switch (mode) {
+        case FKB_BORDER_REPLICATE: v = i < last ? i : last; return v > 0 ? v : 0;               /* :169-186 */
+        case FKB_BORDER_REFLECT:                                                                /* :198-215 */
+            v = last - abs(last - i) + (i > last);
+            return (abs(v) - (v < 0)) % (last + 1);
+        case FKB_BORDER_WRAP:                                                                   /* :232-249 */
+            v = (i < n) ? i : (i % n);
+            return (v >= 0) ? v : (v - ((v - n + 1) / n) * n);
+        case FKB_BORDER_REFLECT_101:                                                            /* :261-272 */
+            v = abs(last - abs(last - i)) % (last + 1);
+            return abs(v) % (last + 1);
+        default: return i;
+    }
+}
+
+/* The read chain at crop-relative (a, b): PerThreadRead -> [BorderReader | Deinterlace] -> Crop. */
+static px3 read_chain(const fkb_plane* pl, const fkb_sequence* sq, int a, int b) {
+    px3 r, p, q;
+    int c;
+    if (sq->border_mode == FKB_BORDER_NONE && sq->deinterlace == FKB_DEINTERLACE_NONE) return read_tap(pl, sq->src_format, a, b);
+    {
+        /* image coordinates; read_tap adds the crop origin, so hand it coordinates relative to the crop */
+        const int x = a + pl->crop_x, y = b + pl->crop_y, w = (int)pl->src_width, h = (int)pl->src_height;
+        if (sq->border_mode == FKB_BORDER_CONSTANT) {                                           /* :140-148 */
+            if (x >= 0 && x < w && y >= 0 && y < h) return read_tap(pl, sq->src_format, a, b);
+            r.v[0] = sq->border_value[0]; r.v[1] = sq->border_value[1]; r.v[2] = sq->border_value[2];
+            return r;
+        }
+        if (sq->border_mode != FKB_BORDER_NONE)
+            return read_tap(pl, sq->src_format, border_index(sq->border_mode, x, w) - pl->crop_x, border_index(sq->border_mode, y, h) - pl->crop_y);
+        /* Deinterlace, deinterlace.h:91-131 */
+        if (sq->deinterlace == FKB_DEINTERLACE_BLEND) {
+            if (y <= 0) return read_tap(pl, sq->src_format, a, b);
+            p = read_tap(pl, sq->src_format, a, b);
+            q = read_tap(pl, sq->src_format, a, b - 1);
+        } else {
+            const int even = (y % 2) == 0;
+            const int interpolate = sq->deinterlace == FKB_DEINTERLACE_LINEAR_EVEN ? (!even && y != h - 1) : (even && y != 0);
+            if (!interpolate) return read_tap(pl, sq->src_format, a, b);
+            p = read_tap(pl, sq->src_format, a, b - 1);
+            q = read_tap(pl, sq->src_format, a, b + 1);
+        }
+        /* (p + q + 1) * 0.5f: an integer sum for uchar3 (exact in binary32), two rounded additions for float3 */
+        for (c = 0; c < 3; ++c) r.v[c] = ((p.v[c] + q.v[c]) + 1.0f) * 0.5f;
+        return r;
+    }
+}
+
 static px3 apply_op(px3 in, const fkb_op* op) {
     px3 o = in;
     int c;
@@ -143,7 +195,7 @@ static px3 apply_op(px3 in, const fkb_op* op) {
 }
 
 static px3 read_pre(const fkb_plane* pl, const fkb_sequence* sq, int n_pre, int a, int b) {
-    px3 t = read_tap(pl, sq->src_format, a, b);
+    px3 t = read_chain(pl, sq, a, b);
     int k;
     for (k = 0; k < n_pre; ++k) t = apply_op(t, &sq->ops[k]);
     return t;
@@ -212,7 +264,8 @@ int fkl_oracle_run_range(const fkb_plan_desc* d, int first, int count, int host_
         sq = &d->sequences[pl->sequence];
         memset(&rp, 0, sizeof rp);
         const int is_default = (pl->flags & FKB_PLANE_DEFAULT_VALUE) != 0;  /* batch_operations.h:236-241 */
-        if (sq->resize_mode != FKB_RESIZE_NONE && !is_default) {
+        const int warp = sq->resize_mode == FKB_GEOMETRY_WARP_AFFINE || sq->resize_mode == FKB_GEOMETRY_WARP_PERSPECTIVE;
+        if (sq->resize_mode != FKB_RESIZE_NONE && !is_default && !warp) {
             if (fkl_oracle_derive_resize(pl->crop_width, pl->crop_height, (int)pl->dst_width,
                                          (int)pl->dst_height, sq->resize_mode, &rp)) return 1;
         }
@@ -224,7 +277,23 @@ int fkl_oracle_run_range(const fkb_plan_desc* d, int first, int count, int host_
                     first_post = sq->resize_mode == FKB_RESIZE_NONE ? 0 : sq->n_pre_ops;
                     v.v[0] = sq->background[0]; v.v[1] = sq->background[1]; v.v[2] = sq->background[2];
                 } else if (sq->resize_mode == FKB_RESIZE_NONE) {
-                    v = read_tap(pl, sq->src_format, x, y);
+                    v = read_chain(pl, sq, x, y);
+                } else if (warp) {
+                    /* WarpingCoords + Warping::exec, warping.h:49-69, 86-94 */
+                    const float* m = sq->transform;
+                    float cx = (m[0] * (float)x + m[1] * (float)y) + m[2];
+                    float cy = (m[3] * (float)x + m[4] * (float)y) + m[5];
+                    first_post = sq->n_pre_ops;
+                    if (sq->resize_mode == FKB_GEOMETRY_WARP_PERSPECTIVE) {
+                        const float coeff = 1.0f / ((m[6] * (float)x + m[7] * (float)y) + m[8]);
+                        cx = coeff * cx;
+                        cy = coeff * cy;
+                    }
+                    if (cx >= 0.0f && cx < (float)pl->crop_width && cy >= 0.0f && cy < (float)pl->crop_height) {
+                        v = interpolate(pl, sq, sq->n_pre_ops, cx, cy, 0);
+                    } else {
+                        v.v[0] = 0.0f; v.v[1] = 0.0f; v.v[2] = 0.0f;
+                    }
                 } else {
                     first_post = sq->n_pre_ops;
                     /* Resize::exec, resize.h:75-87 */

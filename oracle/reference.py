@@ -199,6 +199,46 @@ def batch4_default_cast_mul(srcs, used, default_value, mul, flavour="device_bran
     return out
 
 
+def border_crop(src, border, value, rect, flavour="device_branch"):
+    """PerThreadRead<uchar3> -> BorderReader<border> -> Crop(rect) -> PerThreadWrite<uchar3>; border 1..5 as fkb_border_mode."""
+    h, w, _ = src.shape
+    out = np.empty((rect[3], rect[2], 3), np.uint8)
+    r = (C.c_int * 4)(*[int(v) for v in rect])
+    v = (C.c_uint8 * 3)(*[int(x) for x in value])
+    if lib(flavour).fklref_border_crop(_u8(src), w, h, src.strides[0], border, v, r, _u8(out)) != 0:
+        raise ValueError("unknown border type")
+    return out
+
+
+def border_crop_resize(src, border, value, rect, dw, dh, flavour="device_branch"):
+    """... -> Crop(rect) -> Resize<INTER_LINEAR>(dw, dh) -> PerThreadWrite<float3>."""
+    h, w, _ = src.shape
+    out = np.empty((dh, dw, 3), np.float32)
+    r = (C.c_int * 4)(*[int(v) for v in rect])
+    v = (C.c_uint8 * 3)(*[int(x) for x in value])
+    if lib(flavour).fklref_border_crop_resize(_u8(src), w, h, src.strides[0], border, v, r, dw, dh, _f32(out)) != 0:
+        raise ValueError("unknown border type")
+    return out
+
+
+def warp(src, perspective, matrix, dw, dh, mul, flavour="device_branch"):
+    """PerThreadRead<uchar3> -> Warping<Affine|Perspective>(matrix, dw x dh) -> Mul -> PerThreadWrite<float3>."""
+    h, w, _ = src.shape
+    out = np.empty((dh, dw, 3), np.float32)
+    m = (C.c_float * 9)(*[float(x) for x in matrix])
+    lib(flavour).fklref_warp(_u8(src), w, h, src.strides[0], int(perspective), m, dw, dh, _f3(mul), _f32(out))
+    return out
+
+
+def deinterlace(src, kind, mul, flavour="device_branch"):
+    """PerThreadRead<uchar3> -> Deinterlace -> Mul -> PerThreadWrite<float3>; kind 1 BLEND, 2 / 3 INTER_LINEAR even / odd."""
+    h, w, _ = src.shape
+    out = np.empty((h, w, 3), np.float32)
+    if lib(flavour).fklref_deinterlace(_u8(src), w, h, src.strides[0], kind, _f3(mul), _f32(out)) != 0:
+        raise ValueError("unknown deinterlace kind")
+    return out
+
+
 def resize_params(sw, sh, dw, dh, preserve_ar, flavour="device_branch"):
     fxy = (C.c_float * 2)()
     roi = (C.c_int * 4)()

@@ -125,6 +125,31 @@ def default_planes_case(name, seed, w, h, mode, dst_fmt, n=5, used=3):
     return Case(name, sources, {"out": out}, build, float_outputs=dpx == 12)
 
 
+def readback_case(name, seed, w, h, dw, dh, mode, dst_fmt=abi.DST_F32X3_PACKED, ops=(), n_pre=0, crop=None, border=0,
+                  border_value=(0.0, 0.0, 0.0), deinterlace=0, transform=None, src_fmt=abi.SRC_U8X3, n=2):
+    """BorderReader / Deinterlace / Warping chains on a small batch of images (the one-pixel-per-thread body)."""
+    rng = np.random.default_rng(seed)
+    if src_fmt == abi.SRC_U8X3:
+        sources = {f"img{i}": _u8(rng, h, w * 3) for i in range(n)}
+        spx = 3
+    else:
+        sources = {f"img{i}": (rng.random((h, w * 3), dtype=np.float32) * 255).astype(np.float32) for i in range(n)}
+        spx = 12
+    dpx = 3 if dst_fmt == abi.DST_U8X3_PACKED else 12
+    out = np.zeros((n, dh, dw * dpx), np.uint8)
+
+    def build(ptr):
+        plan = abi.HostPlan()
+        seq = plan.add_sequence(src_fmt, dst_fmt, mode, list(ops), n_pre_ops=n_pre, border_mode=border, border_value=border_value,
+                                deinterlace=deinterlace, transform=transform, background=(5.0, 6.0, 7.0))
+        for i in range(n):
+            plan.add_plane(src=ptr(f"img{i}"), src_width=w, src_height=h, src_pitch=w * spx, crop=crop, dst=ptr("out") + i * dh * dw * dpx,
+                           dst_width=dw, dst_height=dh, dst_pitch=dw * dpx, sequence=seq)
+        return plan
+
+    return Case(name, sources, {"out": out}, build, float_outputs=dpx == 12)
+
+
 def resize_any_case(name, seed, src_fmt, dst_fmt, w, h, dw, dh, pre_ops, post_ops, mode=abi.RESIZE_IGNORE_AR):
     """One image -> pre_ops on every tap -> Resize -> post_ops -> receiver, any source / destination format."""
     rng = np.random.default_rng(seed)
@@ -268,6 +293,22 @@ def small_cases():
         default_planes_case("default_planes_flat", 91, 64, 32, abi.RESIZE_NONE, abi.DST_F32X3_PACKED),
         default_planes_case("default_planes_flat_u8", 92, 53, 37, abi.RESIZE_NONE, abi.DST_U8X3_PACKED),
         default_planes_case("default_planes_resize", 93, 64, 48, abi.RESIZE_PRESERVE_AR, abi.DST_F32X3_PACKED),
+        # BorderReader under a padded crop, Warping, Deinterlace
+        *[readback_case(f"border{b}_padded_crop_u8", 100 + b, 40, 24, 60, 37, abi.RESIZE_NONE, dst_fmt=abi.DST_U8X3_PACKED,
+                        crop=(-7, -5, 60, 37), border=b, border_value=(9.0, 99.0, 199.0)) for b in range(1, 6)],
+        *[readback_case(f"border{b}_padded_crop_resize", 110 + b, 40, 24, 36, 28, abi.RESIZE_PRESERVE_AR, crop=(-45, -30, 130, 90),
+                        border=b, border_value=(9.0, 99.0, 199.0), ops=[op(abi.OP_CAST_F32), op(abi.OP_MUL, 0.5)], n_pre=1)
+          for b in range(1, 6)],
+        readback_case("border_constant_float_source", 116, 33, 21, 50, 30, abi.RESIZE_NONE, crop=(-9, -4, 50, 30), border=1,
+                      border_value=(0.5, 1.5, 2.5), src_fmt=abi.SRC_F32X3, ops=[op(abi.OP_ADD, 1.0)]),
+        readback_case("warp_affine", 117, 40, 24, 48, 32, abi.GEOMETRY_WARP_AFFINE, ops=[op(abi.OP_MUL, (1.0, 0.5, 2.0))],
+                      transform=(0.8, 0.25, -3.0, -0.2, 0.7, 2.5, 0, 0, 1)),
+        readback_case("warp_perspective_crop", 118, 64, 48, 45, 31, abi.GEOMETRY_WARP_PERSPECTIVE, crop=(8, 6, 40, 30),
+                      ops=[op(abi.OP_CAST_F32), op(abi.OP_SUB, 3.0)], n_pre=1, transform=(0.9, 0.1, -2.0, 0.05, 0.8, 1.0, 0.002, 0.001, 1.0)),
+        *[readback_case(f"deinterlace{k}", 120 + k, 40, 24, 40, 24, abi.RESIZE_NONE, ops=[op(abi.OP_MUL, (1.0, 0.5, 2.0))],
+                        deinterlace=k) for k in (1, 2, 3)],
+        readback_case("deinterlace_blend_float_then_resize", 124, 40, 24, 28, 20, abi.RESIZE_IGNORE_AR, deinterlace=1,
+                      src_fmt=abi.SRC_F32X3, ops=[op(abi.OP_MUL, 0.25)]),
         # Cast<float3,int3> / Cast<float3,uint3> closing a chain (truncation toward zero)
         elementwise_case("cast_int3_after_arithmetic", 81, 64, 33, [op(abi.OP_CAST_F32), op(abi.OP_MUL, (1.37, 0.5, 2.25)),
                                                                     op(abi.OP_SUB, (100.5, 3.25, 7.0)), op(abi.OP_CAST_I32)],

@@ -24,6 +24,11 @@ from oracle import reference as ref  # noqa: E402
 
 OUT = Path(__file__).resolve().parent
 
+# a crop that reaches beyond a 40x24 image on every side; an affine and a perspective matrix (rows of three)
+READBACK_RECT = (-7, -5, 60, 37)
+READBACK_AFFINE = (0.8, 0.25, -3.0, -0.2, 0.7, 2.5, 0.0, 0.0, 1.0)
+READBACK_PERSPECTIVE = (0.9, 0.1, -2.0, 0.05, 0.8, 1.0, 0.002, 0.001, 1.0)
+
 
 def u8(rng, *shape):
     return rng.integers(0, 256, shape, dtype=np.uint8)
@@ -117,6 +122,19 @@ def main():
     np.savez_compressed(OUT / "default_planes.npz", srcs=np.stack(imgs4),
                         used2=ref.batch4_default_cast_mul(imgs4, 2, (7, 200, 33), (1.5, 0.25, 2.0)),
                         used0=ref.batch4_default_cast_mul(imgs4, 0, (7, 200, 33), (1.5, 0.25, 2.0)))
+    # --- BorderReader, Warping, Deinterlace (own seed) ---------------------------------------------------------
+    rng4 = np.random.default_rng(20240610)
+    img4 = u8(rng4, 24, 40, 3)
+    fix = {"src": img4, "rect": np.array(READBACK_RECT), "affine": np.array(READBACK_AFFINE, np.float32),
+           "perspective": np.array(READBACK_PERSPECTIVE, np.float32)}
+    for b in range(1, 6):
+        fix[f"border{b}_crop"] = ref.border_crop(img4, b, (9, 99, 199), READBACK_RECT)
+        fix[f"border{b}_crop_resize"] = ref.border_crop_resize(img4, b, (9, 99, 199), READBACK_RECT, 36, 28)
+    fix["warp_affine"] = ref.warp(img4, False, READBACK_AFFINE, 48, 32, (1.0, 0.5, 2.0))
+    fix["warp_perspective"] = ref.warp(img4, True, READBACK_PERSPECTIVE, 48, 32, (1.0, 0.5, 2.0))
+    for k in (1, 2, 3):
+        fix[f"deinterlace{k}"] = ref.deinterlace(img4, k, (1.0, 0.5, 2.0))
+    np.savez_compressed(OUT / "readback_ops.npz", **fix)
     print("golden vectors written to", OUT)
 
 

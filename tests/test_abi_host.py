@@ -29,7 +29,7 @@ def test_every_declared_symbol_is_exported(fkb_lib):
 def test_struct_sizes_match_header():
     # sizes implied by the C declarations on LP64
     assert C.sizeof(abi.Op) == 16
-    assert C.sizeof(abi.Sequence) == 40
+    assert C.sizeof(abi.Sequence) == 96
     assert C.sizeof(abi.Plane) == 72
     assert C.sizeof(abi.PlanDesc) == 32
     assert C.sizeof(abi.ResizeParams) == 32
@@ -208,7 +208,7 @@ def test_staged_plans_have_two_table_entries_per_block(fkb_lib):
                                         src_pitch=pitch, dst=1 << 30, dst_width=64, dst_height=64,
                                         post_ops=chains.normalize_ops(), planar=True)
         return abi.validate(plan)
-    fixed = 2 * 112 + 64 + 5 * 16 + 16              # planes, sequence, operations (two divisions take two slots), status
+    fixed = 2 * 112 + 128 + 5 * 16 + 16             # planes, sequence, operations (two divisions take two slots), status
     staged, direct = info(608), info(600)
     assert staged.device_bytes == fixed + 32 * staged.grid_x
     assert direct.device_bytes == fixed + 16 * direct.grid_x
@@ -224,7 +224,7 @@ def test_wide_regions_are_cut_into_column_tiles_for_the_staged_body(fkb_lib):
                    dst_height=540, dst_pitch=960 * 12, sequence=seq)
     info = abi.validate(plan)
     assert info.n_planes == 1
-    fixed = 2 * 112 + 64 + 16 + 16                   # two tiles, sequence, empty operation table, status
+    fixed = 2 * 112 + 128 + 16 + 16                  # two tiles, sequence, empty operation table, status
     assert info.device_bytes == fixed + 32 * info.grid_x
 
 
@@ -237,7 +237,7 @@ def test_plans_of_several_classes_stage_their_uchar3_resize_planes(fkb_lib):
                                         dst_ptrs=[(1 << 32) + g * (1 << 30) for g in range(4)], per_group=16)
     info = abi.validate(plan)
     assert info.n_planes == 64 and info.n_sequences == 4 and info.n_launches == 1
-    fixed = (48 + 2 * 16) * 112 + 4 * 64 + 8 * 16 + 16    # planes, sequences, operations, status
+    fixed = (48 + 2 * 16) * 112 + 4 * 128 + 8 * 16 + 16   # planes, sequences, operations, status
     assert info.device_bytes == fixed + 32 * info.grid_x
 
 

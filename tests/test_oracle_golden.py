@@ -257,3 +257,43 @@ def test_planes_of_a_partly_filled_batch_read_the_default_value(oracle_port):
                            flags=0 if i < used else abi.PLANE_DEFAULT_VALUE)
         oracle_port.run(plan)
         assert _same(out, g[key]), key
+
+
+def _readback_plan(src, out, *, dst_fmt, mode, dw, dh, ops, n_pre=0, crop=None, border=0, border_value=(0, 0, 0), deinterlace=0,
+                   transform=None):
+    h, w, _ = src.shape
+    plan = abi.HostPlan()
+    seq = plan.add_sequence(abi.SRC_U8X3, dst_fmt, mode, ops, n_pre_ops=n_pre, border_mode=border, border_value=border_value,
+                            deinterlace=deinterlace, transform=transform)
+    dpx = 3 if dst_fmt == abi.DST_U8X3_PACKED else 12
+    plan.add_plane(src=src.ctypes.data, src_width=w, src_height=h, src_pitch=w * 3, crop=crop, dst=out.ctypes.data, dst_width=dw,
+                   dst_height=dh, dst_pitch=dw * dpx, sequence=seq)
+    return plan
+
+
+def test_border_reader_warping_and_deinterlace(oracle_port):
+    """BorderReader under a crop that reaches beyond the image (border_reader.h:136-279), Warping<Affine|Perspective>
+    (warping.h:43-104) and Deinterlace<BLEND|INTER_LINEAR> (deinterlace.h:41-132) against the reference build's output."""
+    g = np.load(GOLD / "readback_ops.npz")
+    src = np.ascontiguousarray(g["src"])
+    rect = tuple(int(v) for v in g["rect"])
+    for b in range(1, 6):
+        out = np.zeros((rect[3], rect[2], 3), np.uint8)
+        oracle_port.run(_readback_plan(src, out, dst_fmt=abi.DST_U8X3_PACKED, mode=abi.RESIZE_NONE, dw=rect[2], dh=rect[3], ops=[],
+                                       crop=rect, border=b, border_value=(9, 99, 199)))
+        assert np.array_equal(out, g[f"border{b}_crop"]), f"border {b}"
+        outf = np.zeros((28, 36, 3), np.float32)
+        oracle_port.run(_readback_plan(src, outf, dst_fmt=abi.DST_F32X3_PACKED, mode=abi.RESIZE_IGNORE_AR, dw=36, dh=28, ops=[],
+                                       crop=rect, border=b, border_value=(9, 99, 199)))
+        assert _same(outf, g[f"border{b}_crop_resize"]), f"border {b} + resize"
+    mul = [op(abi.OP_MUL, (1.0, 0.5, 2.0))]
+    for key, mode in (("affine", abi.GEOMETRY_WARP_AFFINE), ("perspective", abi.GEOMETRY_WARP_PERSPECTIVE)):
+        outf = np.zeros((32, 48, 3), np.float32)
+        oracle_port.run(_readback_plan(src, outf, dst_fmt=abi.DST_F32X3_PACKED, mode=mode, dw=48, dh=32, ops=mul, transform=g[key]))
+        assert _same(outf, g[f"warp_{key}"]), key
+        assert (g[f"warp_{key}"] == 0).any() and (g[f"warp_{key}"] != 0).any()      # some of the output lies outside the source
+    for k in (1, 2, 3):
+        outf = np.zeros(src.shape, np.float32)
+        oracle_port.run(_readback_plan(src, outf, dst_fmt=abi.DST_F32X3_PACKED, mode=abi.RESIZE_NONE, dw=src.shape[1], dh=src.shape[0],
+                                       ops=mul, deinterlace=k))
+        assert _same(outf, g[f"deinterlace{k}"]), f"deinterlace {k}"
