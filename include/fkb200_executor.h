@@ -28,7 +28,10 @@
  * Operations understood (anything else: static_assert):
  *   reads      PerThreadRead<_2D, uchar3|float3>, ReadYUV<NV12|NV21>, Crop<Back>, Resize<INTER_LINEAR,
  *              IGNORE_AR|PRESERVE_AR|PRESERVE_AR_RN_EVEN|PRESERVE_AR_LEFT, Back>, FusedOperation_<...>,
- *              BatchRead<B, PROCESS_ALL, ...>, BatchRead<B, CONDITIONAL_WITH_DEFAULT, ...>
+ *              BatchRead<B, PROCESS_ALL, ...>, BatchRead<B, CONDITIONAL_WITH_DEFAULT, ...>,
+ *              BorderReader<BT, Read> directly above the PerThreadRead (a Crop above it may reach beyond the image),
+ *              Deinterlace<BLEND|INTER_LINEAR, Read> directly above the PerThreadRead,
+ *              Warping<Affine|Perspective, Back> in the place of a Resize
  *   compute    Mul / Sub / Div / Add <float3>, Cast<uchar3,float3>, Cast<float3,int3|uint3>,
  *              SaturateCast<float3,uchar3>, VectorReorder<T,2,1,0> (COLOR_RGB2BGR / COLOR_BGR2RGB),
  *              ConvertYUVToRGB<NV12|NV21, Full, bt709|bt601|bt2020, false, float3>
@@ -66,6 +69,10 @@ struct PlaneState {
     std::vector<fkb_op> ops;
     int n_pre_ops = 0;
     bool has_crop = false;
+    int border_mode = FKB_BORDER_NONE;
+    float border_value[3] = {0.f, 0.f, 0.f};
+    int deinterlace = FKB_DEINTERLACE_NONE;
+    float transform[9] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     /* what the reference's Resize::build derived on the host (resize.h:105-166), kept so that a caller
        can compare it with what the library derives (fkb_derive_resize) */
     fkb_resize_params reference_resize{};
@@ -186,6 +193,51 @@ template <fk::AspectRatio AR, typename Back> struct LowerRead<fk::Resize<fk::Int
         st.reference_resize.target_width = st.reference_resize.x2 - st.reference_resize.x1 + 1;
         st.reference_resize.target_height = st.reference_resize.y2 - st.reference_resize.y1 + 1;
         st.has_reference_resize = true;
+    }
+};
+
+/* BorderReader<BT, Back> (border_reader.h:136-279): params holds the value of a CONSTANT border, backIOp the read whose
+   coordinates it folds back into the image.  Only directly above the image read: the library applies the border to
+   image coordinates, below the crop. */
+template <fk::BorderType BT, typename Back, typename E>
+struct LowerRead<fk::BorderReader<BT, Back, E>, std::enable_if_t<!std::is_void_v<Back>>> {
+    template <typename D> static void apply(PlaneState& st, const D& d) {
+        LowerRead<typename Back::Operation>::apply(st, d.backIOp);
+        if (st.has_crop || st.resize_mode != FKB_RESIZE_NONE || !st.ops.empty() || st.border_mode != FKB_BORDER_NONE ||
+            st.deinterlace != FKB_DEINTERLACE_NONE)
+            throw std::runtime_error("fkb200: a BorderReader anywhere but directly above the image read is not on the accelerated path");
+        st.border_mode = BT == fk::BorderType::CONSTANT ? FKB_BORDER_CONSTANT : BT == fk::BorderType::REPLICATE ? FKB_BORDER_REPLICATE
+                         : BT == fk::BorderType::REFLECT ? FKB_BORDER_REFLECT : BT == fk::BorderType::WRAP ? FKB_BORDER_WRAP
+                         : FKB_BORDER_REFLECT_101;
+        if constexpr (BT == fk::BorderType::CONSTANT) {
+            st.border_value[0] = (float)d.params.value.x; st.border_value[1] = (float)d.params.value.y; st.border_value[2] = (float)d.params.value.z;
+        }
+    }
+};
+/* Deinterlace<DT, Back> (deinterlace.h:41-131): INTER_LINEAR's params say which field is kept; returns float3 */
+template <fk::DeinterlaceType DT, typename Back>
+struct LowerRead<fk::Deinterlace<DT, Back>, std::enable_if_t<!std::is_void_v<Back>>> {
+    template <typename D> static void apply(PlaneState& st, const D& d) {
+        LowerRead<typename Back::Operation>::apply(st, d.backIOp);
+        if (st.has_crop || st.resize_mode != FKB_RESIZE_NONE || !st.ops.empty() || st.border_mode != FKB_BORDER_NONE ||
+            st.deinterlace != FKB_DEINTERLACE_NONE)
+            throw std::runtime_error("fkb200: a Deinterlace anywhere but directly above the image read is not on the accelerated path");
+        if constexpr (DT == fk::DeinterlaceType::BLEND) st.deinterlace = FKB_DEINTERLACE_BLEND;
+        else st.deinterlace = d.params.useEvenLines ? FKB_DEINTERLACE_LINEAR_EVEN : FKB_DEINTERLACE_LINEAR_ODD;
+    }
+};
+/* Warping<WT, Back> (warping.h:43-104): params holds the inverse map (2x3 or 3x3) and the output size */
+template <fk::WarpType WT, typename Back>
+struct LowerRead<fk::Warping<WT, Back>, std::enable_if_t<!std::is_void_v<Back>>> {
+    template <typename D> static void apply(PlaneState& st, const D& d) {
+        LowerRead<typename Back::Operation>::apply(st, d.backIOp);
+        if (st.resize_mode != FKB_RESIZE_NONE) throw std::runtime_error("fkb200: a Warping above a Resize or another Warping is not on the accelerated path");
+        st.n_pre_ops = (int)st.ops.size();
+        st.resize_mode = WT == fk::WarpType::Affine ? FKB_GEOMETRY_WARP_AFFINE : FKB_GEOMETRY_WARP_PERSPECTIVE;
+        constexpr int rows = WT == fk::WarpType::Affine ? 2 : 3;
+        for (int r = 0; r < rows; ++r) for (int c = 0; c < 3; ++c) st.transform[3 * r + c] = d.params.transformMatrix.data[r][c];
+        if (rows == 2) { st.transform[6] = 0.f; st.transform[7] = 0.f; st.transform[8] = 1.f; }
+        st.plane.dst_width = (uint32_t)d.params.dstSize.width; st.plane.dst_height = (uint32_t)d.params.dstSize.height;
     }
 };
 
@@ -363,6 +415,8 @@ inline bool same_sequence(const PlaneState& a, const fkb_sequence& q, const std:
     if (a.src_format != q.src_format || dst_format != q.dst_format || a.resize_mode != q.resize_mode) return false;
     if ((int)a.ops.size() != q.n_ops || (a.resize_mode == FKB_RESIZE_NONE ? 0 : a.n_pre_ops) != q.n_pre_ops) return false;
     if (std::memcmp(a.background, q.background, sizeof a.background) != 0) return false;
+    if (a.border_mode != q.border_mode || a.deinterlace != q.deinterlace || std::memcmp(a.border_value, q.border_value, sizeof a.border_value) != 0 ||
+        std::memcmp(a.transform, q.transform, sizeof a.transform) != 0) return false;
     for (size_t k = 0; k < ops.size(); ++k)
         if (a.ops[k].opcode != ops[k].opcode || std::memcmp(a.ops[k].p, ops[k].p, sizeof ops[k].p) != 0) return false;
     return true;
@@ -404,6 +458,9 @@ inline LoweredPlan lower(const First& first, const Rest&... rest) {
             q.src_format = st.src_format; q.dst_format = recv.dst_format; q.resize_mode = st.resize_mode;
             q.n_ops = (int32_t)st.ops.size(); q.n_pre_ops = st.resize_mode == FKB_RESIZE_NONE ? 0 : st.n_pre_ops;
             std::memcpy(q.background, st.background, sizeof q.background);
+            q.border_mode = st.border_mode; q.deinterlace = st.deinterlace;
+            std::memcpy(q.border_value, st.border_value, sizeof q.border_value);
+            std::memcpy(q.transform, st.transform, sizeof q.transform);
             plan.sequences.push_back(q);
             plan.sequence_ops.push_back(st.ops);
         }

@@ -20,10 +20,11 @@
  * non-owning views (RawPtr, core/data/rawptr.h:124-157) over memory the caller allocated - the owning
  * Ptr2D/Tensor classes of the reference (core/data/ptr_nd.h) are outside this path.
  *
- * Only the operations of the fused-execution path are here: PerThreadRead, ReadYUV<NV12> +
- * ConvertYUVToRGB<NV12, Full, bt709>, Crop, Resize<INTER_LINEAR, IGNORE_AR | PRESERVE_AR>,
- * Mul/Sub/Div/Add, Cast, SaturateCast, ColorConversion<RGB2BGR | BGR2RGB>, PerThreadWrite,
- * TensorWrite, TensorSplit, batches, and divergent batches (several chains in one launch).
+ * Only the operations of the fused-execution path are here: PerThreadRead, ReadYUV<NV12 | NV21> +
+ * ConvertYUVToRGB<PF, Full, bt709 | bt601 | bt2020>, Crop, Resize<INTER_LINEAR, IGNORE_AR | PRESERVE_AR |
+ * PRESERVE_AR_RN_EVEN | PRESERVE_AR_LEFT>, BorderReader, Deinterlace, Warping, Mul/Sub/Div/Add, Cast,
+ * SaturateCast, ColorConversion<RGB2BGR | BGR2RGB>, PerThreadWrite, TensorWrite, TensorSplit, batches, and
+ * divergent batches (several chains in one launch).
  */
 #ifndef FKB200_FK_HPP
 #define FKB200_FK_HPP
@@ -64,15 +65,21 @@ template <typename T> inline T make_(float x, float y, float z);
 template <> inline float3 make_<float3>(float x, float y, float z) { return float3{x, y, z}; }
 
 struct Size { int width, height; Size(int w = 0, int h = 0) : width(w), height(h) {} };
+/* x and y are unsigned as in the reference (core/data/rect.h:38); a crop above a BorderReader that starts outside the
+   image is written Rect(-7, -5, w, h) there too, and the origin wraps back when it is added to the signed thread index */
 struct Rect { unsigned x, y; int width, height; Rect(unsigned x_ = 0, unsigned y_ = 0, int w = 0, int h = 0) : x(x_), y(y_), width(w), height(h) {} };
 
 enum class ND { _2D, _3D };
 enum class InterpolationType { INTER_LINEAR };
-enum class AspectRatio { PRESERVE_AR, IGNORE_AR };
+enum class AspectRatio { PRESERVE_AR, IGNORE_AR, PRESERVE_AR_RN_EVEN, PRESERVE_AR_LEFT };
 enum class ColorConversionCodes { COLOR_RGB2BGR, COLOR_BGR2RGB };
-enum class PixelFormat { NV12 };
+enum class PixelFormat { NV12, NV21 };
 enum class ColorRange { Full };
-enum class ColorPrimitives { bt709 };
+enum class ColorPrimitives { bt601, bt709, bt2020 };
+enum class BorderType { CONSTANT, REPLICATE, REFLECT, WRAP, REFLECT_101 };
+enum class DeinterlaceType { BLEND, INTER_LINEAR };
+enum class DeinterlaceLinear : bool { USE_EVEN = true, USE_ODD = false };
+enum class WarpType { Affine, Perspective };
 enum class ParArch { GPU_NVIDIA };
 template <ParArch PA = ParArch::GPU_NVIDIA> struct TransformDPP {};
 
@@ -82,6 +89,7 @@ template <typename T> struct RawTensor { T* data; unsigned width, height, planes
 /* An NV12 frame: `height` luma rows, then height/2 rows of interleaved U,V, same pitch
    (color_conversion.h:336-341 with an Image whose dims.height is the frame height). */
 struct ImageNV12 { const unsigned char* data; unsigned width, height, pitch; };
+using ImageNV21 = ImageNV12; /* the same layout with V before U in the chroma rows */
 
 inline void check(int status) {
     if (status != FKB_OK) throw std::runtime_error(std::string(fkb_last_error()[0] ? fkb_last_error() : fkb_status_string(status)));
@@ -112,6 +120,9 @@ struct Sender {
     std::vector<fkb_op> ops;
     int n_pre_ops = 0;
     bool value_is_float = false, value_is_yuv = false;
+    int border_mode = FKB_BORDER_NONE, deinterlace = FKB_DEINTERLACE_NONE;
+    float border_value[3] = {0.f, 0.f, 0.f};
+    float transform[9] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 
     template <typename Continuation> Sender then(const Continuation& c) const { Sender s = *this; c.apply(s); return s; }
 };
@@ -146,10 +157,9 @@ template <> struct PerThreadRead<ND::_2D, float3> {
     }
 };
 template <PixelFormat PF> struct ReadYUV {
-    static_assert(PF == PixelFormat::NV12, "only NV12 is on this path");
     static Sender build(const ImageNV12& img) { return build(std::array<ImageNV12, 1>{img}); }
     template <size_t B> static Sender build(const std::array<ImageNV12, B>& imgs) {
-        Sender s; s.src_format = FKB_SRC_NV12; s.value_is_yuv = true;
+        Sender s; s.src_format = PF == PixelFormat::NV12 ? FKB_SRC_NV12 : FKB_SRC_NV21; s.value_is_yuv = true;
         for (const auto& i : imgs) s.planes.push_back(SourcePlane{i.data, i.width, i.height, i.pitch, Rect(), false});
         return s;
     }
@@ -177,11 +187,64 @@ struct ResizeContinuation { int mode; Size size; float3 background;
         s.value_is_float = true; s.value_is_yuv = false; /* Interpolate returns float (interpolation.h:55-57) */
     } };
 template <InterpolationType I, AspectRatio AR = AspectRatio::IGNORE_AR> struct Resize {
-    static ResizeContinuation build(const Size& dst) { return ResizeContinuation{AR == AspectRatio::PRESERVE_AR ? FKB_RESIZE_PRESERVE_AR : FKB_RESIZE_IGNORE_AR, dst, float3{0.f, 0.f, 0.f}}; }
-    static ResizeContinuation build(const Size& dst, const float3& background) {
-        return ResizeContinuation{AR == AspectRatio::PRESERVE_AR ? FKB_RESIZE_PRESERVE_AR : FKB_RESIZE_IGNORE_AR, dst, background};
+    static constexpr int MODE = AR == AspectRatio::PRESERVE_AR ? FKB_RESIZE_PRESERVE_AR
+                                : AR == AspectRatio::PRESERVE_AR_RN_EVEN ? FKB_RESIZE_PRESERVE_AR_RN_EVEN
+                                : AR == AspectRatio::PRESERVE_AR_LEFT ? FKB_RESIZE_PRESERVE_AR_LEFT : FKB_RESIZE_IGNORE_AR;
+    static ResizeContinuation build(const Size& dst) { return ResizeContinuation{MODE, dst, float3{0.f, 0.f, 0.f}}; }
+    static ResizeContinuation build(const Size& dst, const float3& background) { return ResizeContinuation{MODE, dst, background}; }
+};
+/* BorderReader<BT>::build(read[, value]) (image_processing/border_reader.h:46-87): wraps the image read, so that a Crop
+   above it may reach beyond the image */
+template <BorderType BT> struct BorderReader {
+    static constexpr int MODE = BT == BorderType::CONSTANT ? FKB_BORDER_CONSTANT : BT == BorderType::REPLICATE ? FKB_BORDER_REPLICATE
+                                : BT == BorderType::REFLECT ? FKB_BORDER_REFLECT : BT == BorderType::WRAP ? FKB_BORDER_WRAP : FKB_BORDER_REFLECT_101;
+    static Sender wrap(const Sender& read) {
+        if (read.value_is_yuv || !read.ops.empty() || read.resize_mode != FKB_RESIZE_NONE || read.border_mode != FKB_BORDER_NONE ||
+            read.deinterlace != FKB_DEINTERLACE_NONE)
+            throw std::runtime_error("fkb200: BorderReader anywhere but directly above PerThreadRead is not on this path");
+        for (const auto& p : read.planes) if (p.cropped) throw std::runtime_error("fkb200: BorderReader above a Crop is not on this path");
+        Sender s = read; s.border_mode = MODE; return s;
+    }
+    static Sender build(const Sender& read) {
+        static_assert(BT != BorderType::CONSTANT, "a CONSTANT border needs its value");
+        return wrap(read);
+    }
+    template <typename V> static Sender build(const Sender& read, const V& value) {
+        static_assert(BT == BorderType::CONSTANT, "only a CONSTANT border takes a value");
+        Sender s = wrap(read); s.border_value[0] = (float)value.x; s.border_value[1] = (float)value.y; s.border_value[2] = (float)value.z; return s;
     }
 };
+/* Deinterlace<DT>::build([which field,] read) (image_processing/deinterlace.h:133-183); the value becomes float3 */
+template <DeinterlaceType DT> struct Deinterlace {
+    static Sender wrap(const Sender& read, int mode) {
+        if (read.value_is_yuv || !read.ops.empty() || read.resize_mode != FKB_RESIZE_NONE || read.border_mode != FKB_BORDER_NONE ||
+            read.deinterlace != FKB_DEINTERLACE_NONE)
+            throw std::runtime_error("fkb200: Deinterlace anywhere but directly above PerThreadRead is not on this path");
+        for (const auto& p : read.planes) if (p.cropped) throw std::runtime_error("fkb200: Deinterlace above a Crop is not on this path");
+        Sender s = read; s.deinterlace = mode; s.value_is_float = true; return s;
+    }
+    static Sender build(const Sender& read) {
+        static_assert(DT == DeinterlaceType::BLEND, "INTER_LINEAR needs DeinterlaceLinear::USE_EVEN or USE_ODD");
+        return wrap(read, FKB_DEINTERLACE_BLEND);
+    }
+    static Sender build(DeinterlaceLinear field, const Sender& read) {
+        static_assert(DT == DeinterlaceType::INTER_LINEAR, "only INTER_LINEAR chooses a field");
+        return wrap(read, field == DeinterlaceLinear::USE_EVEN ? FKB_DEINTERLACE_LINEAR_EVEN : FKB_DEINTERLACE_LINEAR_ODD);
+    }
+};
+/* Warping<WT>::build(params) (image_processing/warping.h:25-141): the matrix maps output to source coordinates */
+template <WarpType WT> struct WarpingParameters { float transformMatrix[WT == WarpType::Affine ? 2 : 3][3]; Size dstSize; };
+template <WarpType WT> struct WarpingContinuation { WarpingParameters<WT> params;
+    void apply(Sender& s) const {
+        if (s.resize_mode != FKB_RESIZE_NONE) throw std::runtime_error("fkb200: Warping after a Resize or another Warping is not on this path");
+        if (s.value_is_yuv) throw std::runtime_error("fkb200: Warping over a YUV value is not on this path");
+        s.resize_mode = WT == WarpType::Affine ? FKB_GEOMETRY_WARP_AFFINE : FKB_GEOMETRY_WARP_PERSPECTIVE;
+        constexpr int rows = WT == WarpType::Affine ? 2 : 3;
+        for (int r = 0; r < rows; ++r) for (int c = 0; c < 3; ++c) s.transform[3 * r + c] = params.transformMatrix[r][c];
+        if (rows == 2) { s.transform[6] = 0.f; s.transform[7] = 0.f; s.transform[8] = 1.f; }
+        s.dst_size = params.dstSize; s.n_pre_ops = (int)s.ops.size(); s.value_is_float = true;
+    } };
+template <WarpType WT> struct Warping { static WarpingContinuation<WT> build(const WarpingParameters<WT>& p) { return WarpingContinuation<WT>{p}; } };
 
 /* ---- element-wise operations (basic_ops/arithmetic.h, cast.h, image_processing/saturate.h, color_conversion.h) ---- */
 template <typename T> struct Mul { static detail::Continuation build(const float3& p) { return {detail::make_op(FKB_OP_MUL, p), true, false, false}; } };
@@ -196,10 +259,13 @@ template <ColorConversionCodes CODE, typename I, typename O = I> struct ColorCon
     static detail::Continuation build() { return {detail::make_op(FKB_OP_SWAP_RB), false, false, false}; }
 };
 template <PixelFormat PF, ColorRange CR, ColorPrimitives CP, bool ALPHA = false, typename O = float3> struct ConvertYUVToRGB {
-    static_assert(PF == PixelFormat::NV12 && CR == ColorRange::Full && CP == ColorPrimitives::bt709 && !ALPHA, "only NV12 / Full / bt709 is on this path");
+    static_assert(CR == ColorRange::Full && !ALPHA, "only full-range conversions without alpha are on this path");
     struct C { void apply(Sender& s) const {
         if (!s.value_is_yuv) throw std::runtime_error("fkb200: ConvertYUVToRGB needs the value read by ReadYUV");
-        s.ops.push_back(detail::make_op(FKB_OP_YUV_TO_RGB_BT709_FULL)); s.value_is_yuv = false; s.value_is_float = true;
+        if (s.src_format != (PF == PixelFormat::NV12 ? FKB_SRC_NV12 : FKB_SRC_NV21)) throw std::runtime_error("fkb200: ConvertYUVToRGB's pixel format differs from ReadYUV's");
+        s.ops.push_back(detail::make_op(CP == ColorPrimitives::bt709 ? FKB_OP_YUV_TO_RGB_BT709_FULL
+                                        : CP == ColorPrimitives::bt601 ? FKB_OP_YUV_TO_RGB_BT601_FULL : FKB_OP_YUV_TO_RGB_BT2020_FULL));
+        s.value_is_yuv = false; s.value_is_float = true;
     } };
     static C build() { return C{}; }
 };
@@ -229,6 +295,9 @@ inline void lower_into(const Sender& s, const Receiver& r, Lowered& out, std::ve
     q.src_format = s.src_format; q.dst_format = r.dst_format; q.resize_mode = s.resize_mode;
     q.n_ops = (int32_t)s.ops.size(); q.n_pre_ops = s.resize_mode == FKB_RESIZE_NONE ? 0 : s.n_pre_ops;
     q.background[0] = s.background[0]; q.background[1] = s.background[1]; q.background[2] = s.background[2];
+    q.border_mode = s.border_mode; q.deinterlace = s.deinterlace;
+    for (int k = 0; k < 3; ++k) q.border_value[k] = s.border_value[k];
+    for (int k = 0; k < 9; ++k) q.transform[k] = s.transform[k];
     q.ops = nullptr; /* fixed up by the caller once op_store stops growing */
     const int seq_index = (int)out.seqs.size();
     out.seqs.push_back(q);

@@ -98,6 +98,21 @@ def batch4_default_cast_mul(mode, srcs4, w, h, spitch, used, default_value, mul,
     _check(lib().fklbind_batch4_default_cast_mul(mode, ptrs, w, h, spitch, used, dv, _f3(mul), _p(dst), _p(stream)))
 
 
+def border_crop_resize(mode, src, w, h, pitch, border, value, rect, dw, dh, out, stream=None):
+    v = (C.c_uint8 * 3)(*[int(x) for x in value])
+    r = (C.c_int * 4)(*[int(x) for x in rect])
+    _check(lib().fklbind_border_crop_resize(mode, _p(src), w, h, pitch, border, v, r, dw, dh, _p(out), _p(stream)))
+
+
+def warp(mode, src, w, h, pitch, perspective, matrix, dw, dh, mul, out, stream=None):
+    m = (C.c_float * 9)(*[float(x) for x in np.asarray(matrix, np.float32).reshape(-1)])
+    _check(lib().fklbind_warp(mode, _p(src), w, h, pitch, int(perspective), m, dw, dh, _f3(mul), _p(out), _p(stream)))
+
+
+def deinterlace(mode, src, w, h, pitch, kind, mul, out, stream=None):
+    _check(lib().fklbind_deinterlace(mode, _p(src), w, h, pitch, kind, _f3(mul), _p(out), _p(stream)))
+
+
 def last_plan():
     """(planes, sequences) of the last DESCRIBE call: planes as abi.Plane, sequences as (abi.Sequence, [abi.Op])."""
     n_p, n_s = C.c_int(), C.c_int()

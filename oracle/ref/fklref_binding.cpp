@@ -69,6 +69,22 @@ auto cropped_resized(const void* const* frames, int w, int h, int pitch, const i
     else return cropped.then(Resize<LINEAR, AR>::build(Size(dw, dh), f3(bg)));
 }
 
+/* PerThreadRead -> BorderReader<border> -> Crop(rect beyond the image) -> Resize dw x dh -> PerThreadWrite<float3>.
+   border: 1 CONSTANT(value) 2 REPLICATE 3 REFLECT 4 WRAP 5 REFLECT_101 */
+template <BorderType BT>
+int border_crop_resize(int mode, const void* src, int w, int h, int pitch, const uint8_t* value, const int* rect, int dw, int dh,
+                              float* out, void* stream) {
+    const auto read = PerThreadRead<ND::_2D, uchar3>::build(raw_u8x3(src, w, h, pitch));
+    using ReadIOp = std::decay_t<decltype(read)>;
+    const auto bordered = [&] {
+        if constexpr (BT == BorderType::CONSTANT) return BorderReader<BT, ReadIOp>::build(read, uchar3{value[0], value[1], value[2]});
+        else return BorderReader<BT, ReadIOp>::build(read);
+    }();
+    const auto sender = bordered.then(Crop<>::build(Rect(rect[0], rect[1], rect[2], rect[3]))).then(Resize<LINEAR>::build(Size(dw, dh)));
+    return run(mode, stream, sender, PerThreadWrite<ND::_2D, float3>::build(
+        RawPtr<ND::_2D, float3>{reinterpret_cast<float3*>(out), PtrDims<ND::_2D>((uint)dw, (uint)dh, (uint)(dw * 12))}));
+}
+
 }  // namespace
 
 extern "C" {
@@ -193,6 +209,47 @@ int fklbind_batch4_default_cast_mul(int mode, const void* const* srcs, int w, in
     const auto read = PerThreadRead<ND::_2D, uchar3>::build(used, dv, a);
     return run(mode, stream, read, Cast<uchar3, float3>::build(), Mul<float3>::build(f3(mul)),
                TensorWrite<float3>::build(raw_tensor<float3>(dst, w, h, 4, 1)));
+}
+
+/* border: 1 CONSTANT(value) 2 REPLICATE 3 REFLECT 4 WRAP 5 REFLECT_101 */
+int fklbind_border_crop_resize(int mode, const void* src, int w, int h, int pitch, int border, const uint8_t* value, const int* rect, int dw,
+                               int dh, float* out, void* stream) {
+    switch (border) {
+        case 1: return border_crop_resize<BorderType::CONSTANT>(mode, src, w, h, pitch, value, rect, dw, dh, out, stream);
+        case 2: return border_crop_resize<BorderType::REPLICATE>(mode, src, w, h, pitch, value, rect, dw, dh, out, stream);
+        case 3: return border_crop_resize<BorderType::REFLECT>(mode, src, w, h, pitch, value, rect, dw, dh, out, stream);
+        case 4: return border_crop_resize<BorderType::WRAP>(mode, src, w, h, pitch, value, rect, dw, dh, out, stream);
+        case 5: return border_crop_resize<BorderType::REFLECT_101>(mode, src, w, h, pitch, value, rect, dw, dh, out, stream);
+        default: g_error = "unknown border"; return -1;
+    }
+}
+
+/* PerThreadRead -> Warping<Affine | Perspective>(matrix, dw x dh) -> Mul -> PerThreadWrite<float3> */
+int fklbind_warp(int mode, const void* src, int w, int h, int pitch, int perspective, const float* matrix, int dw, int dh, const float* mul,
+                 float* out, void* stream) {
+    const auto read = PerThreadRead<ND::_2D, uchar3>::build(raw_u8x3(src, w, h, pitch));
+    const auto write = PerThreadWrite<ND::_2D, float3>::build(
+        RawPtr<ND::_2D, float3>{reinterpret_cast<float3*>(out), PtrDims<ND::_2D>((uint)dw, (uint)dh, (uint)(dw * 12))});
+    if (perspective) {
+        WarpingParameters<WarpType::Perspective> p{};
+        for (int r = 0; r < 3; ++r) for (int c = 0; c < 3; ++c) p.transformMatrix.data[r][c] = matrix[3 * r + c];
+        p.dstSize = Size(dw, dh);
+        return run(mode, stream, read.then(Warping<WarpType::Perspective>::build(p)).then(Mul<float3>::build(f3(mul))), write);
+    }
+    WarpingParameters<WarpType::Affine> p{};
+    for (int r = 0; r < 2; ++r) for (int c = 0; c < 3; ++c) p.transformMatrix.data[r][c] = matrix[3 * r + c];
+    p.dstSize = Size(dw, dh);
+    return run(mode, stream, read.then(Warping<WarpType::Affine>::build(p)).then(Mul<float3>::build(f3(mul))), write);
+}
+
+/* PerThreadRead -> Deinterlace -> Mul -> PerThreadWrite<float3>.  kind: 1 BLEND, 2 INTER_LINEAR keeping even lines, 3 odd */
+int fklbind_deinterlace(int mode, const void* src, int w, int h, int pitch, int kind, const float* mul, float* out, void* stream) {
+    const auto read = PerThreadRead<ND::_2D, uchar3>::build(raw_u8x3(src, w, h, pitch));
+    const auto write = PerThreadWrite<ND::_2D, float3>::build(
+        RawPtr<ND::_2D, float3>{reinterpret_cast<float3*>(out), PtrDims<ND::_2D>((uint)w, (uint)h, (uint)(w * 12))});
+    if (kind == 1) return run(mode, stream, Deinterlace<DeinterlaceType::BLEND>::build(read).then(Mul<float3>::build(f3(mul))), write);
+    const auto lin = kind == 2 ? DeinterlaceLinear::USE_EVEN : DeinterlaceLinear::USE_ODD;
+    return run(mode, stream, Deinterlace<DeinterlaceType::INTER_LINEAR>::build(lin, read).then(Mul<float3>::build(f3(mul))), write);
 }
 
 /* ---- inspection of the plan of the last mode-1 call on this thread ---- */

@@ -52,6 +52,10 @@ static int host_only() {
         const RawPtr2D<uchar3> bad{reinterpret_cast<uchar3*>(dummy_in), 8, 8, 24};
         executeOperations<TransformDPP<>>(s, PerThreadRead<ND::_2D, uchar3>::build(img).then(Cast<uchar3, float3>::build()), PerThreadWrite<ND::_2D, uchar3>::build(bad));
     }, "does not match the receiver");
+    // a border reader wraps the image read, not a crop of it
+    expect_throw("border above crop", [&] {
+        (void)BorderReader<BorderType::WRAP>::build(PerThreadRead<ND::_2D, uchar3>::build(img).then(Crop<>::build(Rect(1, 1, 4, 4))));
+    }, "above a Crop");
     int n = 0;
     if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) {
         // no CPU fallback: the launch reports the missing device as an exception, like the reference's gpuErrchk
@@ -129,7 +133,39 @@ int main(int argc, char** argv) {
             PerThreadWrite<ND::_2D, uchar3>::build(RawPtr2D<uchar3>{d_div1, 384, 216, 384 * 3}));
         executeDivergentOperations<TransformDPP<>>(stream, {seq0, seq1});
 
+        // --- a padded crop under a reflecting border, resized (BorderReader -> Crop -> Resize) ---
+        float3* d_border = device_zeros<float3>((size_t)70 * 45 * 12);
+        const auto padded = BorderReader<BorderType::REFLECT_101>::build(PerThreadRead<ND::_2D, uchar3>::build(inputImage))
+            .then(Crop<>::build(Rect(-20, -11, 430, 240)))
+            .then(Resize<InterpolationType::INTER_LINEAR, AspectRatio::PRESERVE_AR_LEFT>::build(Size(70, 45), make_<float3>(1.f, 2.f, 3.f)));
+        executeOperations<TransformDPP<>>(stream, padded, PerThreadWrite<ND::_2D, float3>::build(RawPtr2D<float3>{d_border, 70, 45, 70 * 12}));
+
+        // --- a perspective warp, then Mul ---
+        float3* d_warp = device_zeros<float3>((size_t)100 * 64 * 12);
+        WarpingParameters<WarpType::Perspective> wp{{{0.9f, 0.1f, -2.0f}, {0.05f, 0.8f, 1.0f}, {0.002f, 0.001f, 1.0f}}, Size(100, 64)};
+        const auto warped = PerThreadRead<ND::_2D, uchar3>::build(inputImage).then(Warping<WarpType::Perspective>::build(wp))
+            .then(Mul<float3>::build(make_<float3>(1.f, 0.5f, 2.f)));
+        executeOperations<TransformDPP<>>(stream, warped, PerThreadWrite<ND::_2D, float3>::build(RawPtr2D<float3>{d_warp, 100, 64, 100 * 12}));
+
+        // --- Deinterlace<INTER_LINEAR> keeping the odd lines, then Mul ---
+        float3* d_deint = device_zeros<float3>((size_t)384 * 216 * 12);
+        const auto deint = Deinterlace<DeinterlaceType::INTER_LINEAR>::build(DeinterlaceLinear::USE_ODD, PerThreadRead<ND::_2D, uchar3>::build(inputImage))
+            .then(Mul<float3>::build(make_<float3>(1.f, 0.5f, 2.f)));
+        executeOperations<TransformDPP<>>(stream, deint, PerThreadWrite<ND::_2D, float3>::build(RawPtr2D<float3>{d_deint, 384, 216, 384 * 12}));
+
+        // --- NV21 -> BT.601 RGB -> resize ---
+        float3* d_rgb21 = device_zeros<float3>((size_t)2 * 40 * 22 * 12);
+        const auto fromNV21 = ReadYUV<PixelFormat::NV21>::build(yuv)
+            .then(ConvertYUVToRGB<PixelFormat::NV21, ColorRange::Full, ColorPrimitives::bt601, false, float3>::build())
+            .then(Resize<InterpolationType::INTER_LINEAR>::build(Size(40, 22)))
+            .then(Div<float3>::build(make_set<float3>(255.f)));
+        executeOperations<TransformDPP<>>(stream, fromNV21, TensorWrite<float3>::build(RawTensor<float3>{d_rgb21, 40, 22, 2, 40 * 12}));
+
         stream.sync();   // everything above was asynchronous on the stream
+        download(dir + "/out_border.bin", d_border, (size_t)70 * 45 * 12);
+        download(dir + "/out_warp.bin", d_warp, (size_t)100 * 64 * 12);
+        download(dir + "/out_deint.bin", d_deint, (size_t)384 * 216 * 12);
+        download(dir + "/out_nv21.bin", d_rgb21, (size_t)2 * 40 * 22 * 12);
         download(dir + "/out_readme.bin", d_readme, (size_t)BATCH * 60 * 60 * 12);
         download(dir + "/out_planar.bin", d_planar, (size_t)4 * 3 * 64 * 48 * 4);
         download(dir + "/out_nv12.bin", d_rgb, (size_t)2 * 40 * 22 * 12);

@@ -37,7 +37,7 @@ def shim_program(fkb_lib, tmp_path_factory):
 def test_front_end_error_behaviour(shim_program):
     r = subprocess.run([str(shim_program), "--host-only"], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0, r.stdout + r.stderr
-    assert "ok arithmetic on uchar3" in r.stdout and "ok receiver type" in r.stdout
+    assert "ok arithmetic on uchar3" in r.stdout and "ok receiver type" in r.stdout and "ok border above crop" in r.stdout
 
 
 @pytest.mark.gpu
@@ -80,3 +80,25 @@ def test_front_end_chains_match_the_checker(shim_program, oracle_port, tmp_path)
                                        src=f1.ctypes.data, dst=w1.ctypes.data, width=384, height=216, dst_format=abi.DST_U8X3_PACKED))
     assert np.array_equal(tc.bits(got("out_div0.bin", np.float32, w0.shape)), tc.bits(w0))
     assert np.array_equal(got("out_div1.bin", np.uint8, w1.shape), w1)
+    # widened vocabulary: padded crop under REFLECT_101 + PRESERVE_AR_LEFT, perspective warp, INTER_LINEAR deinterlace, NV21 + bt601
+    def one(out, dst_w, dst_h, mode, ops, crop=None, **extras):
+        plan = abi.HostPlan()
+        seq = plan.add_sequence(abi.SRC_U8X3, abi.DST_F32X3_PACKED, mode, ops, **extras)
+        plan.add_plane(src=f0.ctypes.data, src_width=384, src_height=216, src_pitch=1152, crop=crop, dst=out.ctypes.data, dst_width=dst_w,
+                       dst_height=dst_h, dst_pitch=dst_w * 12, sequence=seq)
+        oracle_port.run(plan)
+        return out
+
+    mul = [op(abi.OP_MUL, (1.0, 0.5, 2.0))]
+    want = one(np.zeros((45, 70, 3), np.float32), 70, 45, abi.RESIZE_PRESERVE_AR_LEFT, [], crop=(-20, -11, 430, 240), border_mode=abi.BORDER_REFLECT_101,
+               background=(1.0, 2.0, 3.0))
+    assert np.array_equal(tc.bits(got("out_border.bin", np.float32, want.shape)), tc.bits(want))
+    want = one(np.zeros((64, 100, 3), np.float32), 100, 64, abi.GEOMETRY_WARP_PERSPECTIVE, mul,
+               transform=(0.9, 0.1, -2.0, 0.05, 0.8, 1.0, 0.002, 0.001, 1.0))
+    assert np.array_equal(tc.bits(got("out_warp.bin", np.float32, want.shape)), tc.bits(want))
+    want = one(np.zeros((216, 384, 3), np.float32), 384, 216, abi.RESIZE_NONE, mul, deinterlace=abi.DEINTERLACE_LINEAR_ODD)
+    assert np.array_equal(tc.bits(got("out_deint.bin", np.float32, want.shape)), tc.bits(want))
+    want = np.zeros((2, 22, 40, 3), np.float32)
+    oracle_port.run(chains.nv12_resize_batch(frame_ptrs=[a.ctypes.data for a in nv], width=96, height=54, pitch=96, dst=want.ctypes.data,
+                                             dst_width=40, dst_height=22, src_format=abi.SRC_NV21, conversion=abi.OP_YUV_TO_RGB_BT601_FULL))
+    assert np.array_equal(tc.bits(got("out_nv21.bin", np.float32, want.shape)), tc.bits(want))

@@ -38,6 +38,9 @@ def _assert_same_plan(expected: abi.HostPlan, fkb_lib):
         assert (q.src_format, q.dst_format, q.resize_mode, q.n_ops, q.n_pre_ops) == \
                (e.src_format, e.dst_format, e.resize_mode, e.n_ops, e.n_pre_ops)
         assert list(q.background) == list(e.background)
+        assert (q.border_mode, list(q.border_value), q.deinterlace) == (e.border_mode, list(e.border_value), e.deinterlace)
+        if q.resize_mode in (abi.GEOMETRY_WARP_AFFINE, abi.GEOMETRY_WARP_PERSPECTIVE):
+            assert list(q.transform) == list(e.transform)
         for k, o in enumerate(ops):
             assert o.opcode == e.ops[k].opcode
             if o.opcode in (abi.OP_MUL, abi.OP_SUB, abi.OP_DIV, abi.OP_ADD):
@@ -46,7 +49,7 @@ def _assert_same_plan(expected: abi.HostPlan, fkb_lib):
     for i, p in enumerate(expected.planes):
         rr = bc.last_reference_resize(i)
         mode = d.sequences[p.sequence].resize_mode
-        if mode == abi.RESIZE_NONE:
+        if mode in (abi.RESIZE_NONE, abi.GEOMETRY_WARP_AFFINE, abi.GEOMETRY_WARP_PERSPECTIVE):
             assert rr is None
             continue
         ours = abi.ResizeParams()
@@ -120,6 +123,63 @@ def test_nv21_left_tsplit_and_partly_filled_batches_lower_to_the_harness_plans(f
     assert [p.flags for p in planes] == [0, 0, abi.PLANE_DEFAULT_VALUE, abi.PLANE_DEFAULT_VALUE]
     assert [p.sequence for p in planes] == [0, 0, 1, 1] and list(seqs[1][0].background) == [7.0, 200.0, 33.0]
     assert [(p.dst_width, p.dst_height, p.dst - out) for p in planes] == [(64, 32, i * 64 * 32 * 12) for i in range(4)]
+
+
+READBACK_RECT = (-7, -5, 60, 37)
+AFFINE = (0.8, 0.25, -3.0, -0.2, 0.7, 2.5, 0.0, 0.0, 1.0)
+PERSPECTIVE = (0.9, 0.1, -2.0, 0.05, 0.8, 1.0, 0.002, 0.001, 1.0)
+
+
+def _readback_plan(src, out, w, h, dw, dh, mode, ops, crop=None, **extras):
+    want = abi.HostPlan()
+    seq = want.add_sequence(abi.SRC_U8X3, abi.DST_F32X3_PACKED, mode, ops, **extras)
+    want.add_plane(src=src, src_width=w, src_height=h, src_pitch=w * 3, crop=crop, dst=out, dst_width=dw, dst_height=dh,
+                   dst_pitch=dw * 12, sequence=seq)
+    return want
+
+
+def test_border_reader_warping_and_deinterlace_lower_to_the_harness_plans(fkb_lib):
+    src, out = 0x10000000, 0x20000000
+    mul = [op(abi.OP_MUL, (1.0, 0.5, 2.0))]
+    for b in range(1, 6):
+        bc.border_crop_resize(bc.DESCRIBE, src, 40, 24, 120, b, (9, 99, 199), READBACK_RECT, 36, 28, out)
+        _assert_same_plan(_readback_plan(src, out, 40, 24, 36, 28, abi.RESIZE_IGNORE_AR, [], crop=READBACK_RECT, border_mode=b,
+                                         border_value=(9.0, 99.0, 199.0) if b == 1 else (0.0, 0.0, 0.0)), fkb_lib)
+    bc.warp(bc.DESCRIBE, src, 40, 24, 120, False, AFFINE, 48, 32, (1.0, 0.5, 2.0), out)
+    _assert_same_plan(_readback_plan(src, out, 40, 24, 48, 32, abi.GEOMETRY_WARP_AFFINE, mul, transform=AFFINE), fkb_lib)
+    bc.warp(bc.DESCRIBE, src, 40, 24, 120, True, PERSPECTIVE, 48, 32, (1.0, 0.5, 2.0), out)
+    _assert_same_plan(_readback_plan(src, out, 40, 24, 48, 32, abi.GEOMETRY_WARP_PERSPECTIVE, mul, transform=PERSPECTIVE), fkb_lib)
+    for k in (1, 2, 3):
+        bc.deinterlace(bc.DESCRIBE, src, 40, 24, 120, k, (1.0, 0.5, 2.0), out)
+        _assert_same_plan(_readback_plan(src, out, 40, 24, 40, 24, abi.RESIZE_NONE, mul, deinterlace=k), fkb_lib)
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(not ref.available(), reason="oracle/_ref not built")
+def test_read_back_operations_through_the_binding_equal_the_reference_cpu_backend(fkb_lib):
+    torch = pytest.importorskip("torch")
+    rng = np.random.default_rng(304)
+    same = lambda a, b: np.array_equal(np.ascontiguousarray(a).view(np.uint32), np.ascontiguousarray(b).view(np.uint32))
+    stream = torch.cuda.Stream()
+    sh = stream.cuda_stream
+    img = rng.integers(0, 256, (54, 96, 3), dtype=np.uint8)
+    d_img = torch.from_numpy(img).cuda()
+    rect = (-20, -11, 140, 80)
+    for b in range(1, 6):
+        d_out = torch.zeros((45, 70, 3), dtype=torch.float32, device="cuda")
+        bc.border_crop_resize(bc.EXECUTE, d_img.data_ptr(), 96, 54, 288, b, (9, 99, 199), rect, 70, 45, d_out.data_ptr(), sh)
+        assert abi.async_check(sh) == 0
+        assert same(d_out.cpu().numpy(), ref.border_crop_resize(img, b, (9, 99, 199), rect, 70, 45)), b
+    for persp, m in ((False, AFFINE), (True, PERSPECTIVE)):
+        d_out = torch.zeros((64, 100, 3), dtype=torch.float32, device="cuda")
+        bc.warp(bc.EXECUTE, d_img.data_ptr(), 96, 54, 288, persp, m, 100, 64, (1.0, 0.5, 2.0), d_out.data_ptr(), sh)
+        assert abi.async_check(sh) == 0
+        assert same(d_out.cpu().numpy(), ref.warp(img, persp, m, 100, 64, (1.0, 0.5, 2.0))), persp
+    for k in (1, 2, 3):
+        d_out = torch.zeros((54, 96, 3), dtype=torch.float32, device="cuda")
+        bc.deinterlace(bc.EXECUTE, d_img.data_ptr(), 96, 54, 288, k, (1.0, 0.5, 2.0), d_out.data_ptr(), sh)
+        assert abi.async_check(sh) == 0
+        assert same(d_out.cpu().numpy(), ref.deinterlace(img, k, (1.0, 0.5, 2.0))), k
 
 
 @pytest.mark.gpu
