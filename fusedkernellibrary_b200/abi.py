@@ -126,6 +126,14 @@ class MultiGpuShard(C.Structure):
 MULTI_GPU_DOWNLOAD, MULTI_GPU_GATHER = 1, 2
 
 
+class CircularTensorDesc(C.Structure):
+    _fields_ = [("width", C.c_uint32), ("height", C.c_uint32), ("batch", C.c_int32), ("order", C.c_int32),
+                ("dst_format", C.c_int32), ("sliding", C.c_int32), ("tensor", C.c_void_p), ("ring", C.c_void_p)]
+
+
+CIRCULAR_NEWEST_FIRST, CIRCULAR_OLDEST_FIRST = 0, 1
+
+
 def op(opcode: int, p=(0.0, 0.0, 0.0)) -> Op:
     if isinstance(p, (int, float)):
         p = (p, p, p)
@@ -214,7 +222,8 @@ EXPORTS = [
     "fkb_execute_host", "fkb_execute_static", "fkb_plan_check", "fkb_plan_set_option", "fkb_execute_async",
     "fkb_async_check", "fkb_debug_get_counters", "fkb_assign_planes", "fkb_multi_gpu_session_create",
     "fkb_multi_gpu_session_run", "fkb_multi_gpu_session_get_shard", "fkb_multi_gpu_session_destroy",
-    "fkb_debug_set_device_unavailable",
+    "fkb_debug_set_device_unavailable", "fkb_circular_tensor_sizes", "fkb_circular_tensor_create", "fkb_circular_tensor_data",
+    "fkb_circular_tensor_next_index", "fkb_circular_tensor_plan_update", "fkb_circular_tensor_update", "fkb_circular_tensor_destroy",
 ]
 
 
@@ -260,6 +269,16 @@ def load_library(path: os.PathLike | None = None) -> C.CDLL:
     lib.fkb_host_session_run.argtypes = [C.c_void_p, C.c_void_p]
     lib.fkb_host_session_get_traffic.argtypes = [C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]
     lib.fkb_host_session_destroy.argtypes = [C.c_void_p]
+    lib.fkb_circular_tensor_sizes.argtypes = [C.POINTER(CircularTensorDesc)] + [C.POINTER(C.c_size_t)] * 3
+    lib.fkb_circular_tensor_create.argtypes = [C.POINTER(CircularTensorDesc), C.POINTER(C.c_void_p)]
+    lib.fkb_circular_tensor_data.argtypes = [C.c_void_p]
+    lib.fkb_circular_tensor_data.restype = C.c_void_p
+    lib.fkb_circular_tensor_next_index.argtypes = [C.c_void_p]
+    lib.fkb_circular_tensor_next_index.restype = C.c_int32
+    lib.fkb_circular_tensor_plan_update.argtypes = [C.c_void_p, C.POINTER(Sequence), C.POINTER(Plane), C.POINTER(Sequence),
+                                                    C.POINTER(C.c_int32), C.POINTER(Plane), C.POINTER(C.c_int32), C.c_int32]
+    lib.fkb_circular_tensor_update.argtypes = [C.c_void_p, C.POINTER(Sequence), C.POINTER(Plane), C.c_void_p]
+    lib.fkb_circular_tensor_destroy.argtypes = [C.c_void_p]
     if path is None:
         _lib = lib
     return lib
@@ -434,6 +453,75 @@ class MultiGpuSession:
     def destroy(self) -> None:
         if self._h:
             self._lib.fkb_multi_gpu_session_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
+
+class CircularTensor:
+    """fkb_circular_tensor_*: the newest `batch` results of a chain, kept in order (the reference's CircularTensor::update,
+    core/data/circular_tensor.h:111-161).  `tensor` / `ring` are the caller's buffers (device pointers, or host pointers when
+    only plans are wanted); None lets the library allocate on the current device."""
+
+    def __init__(self, width, height, batch, dst_format, order=CIRCULAR_NEWEST_FIRST, sliding=False, tensor=None, ring=None):
+        self._lib = load_library()
+        self._h = C.c_void_p()
+        d = CircularTensorDesc(width, height, batch, order, dst_format, 1 if sliding else 0, tensor, ring)
+        self.desc = d
+        pb, tb, rb = C.c_size_t(), C.c_size_t(), C.c_size_t()
+        check(self._lib.fkb_circular_tensor_sizes(C.byref(d), C.byref(pb), C.byref(tb), C.byref(rb)), "fkb_circular_tensor_sizes")
+        self.plane_bytes, self.tensor_bytes, self.ring_bytes = pb.value, tb.value, rb.value
+        check(self._lib.fkb_circular_tensor_create(C.byref(d), C.byref(self._h)), "fkb_circular_tensor_create")
+
+    @staticmethod
+    def sizes(width, height, batch, dst_format, sliding=False) -> tuple[int, int, int]:
+        """(plane, tensor buffer, ring buffer) in bytes."""
+        lib = load_library()
+        d = CircularTensorDesc(width, height, batch, CIRCULAR_NEWEST_FIRST, dst_format, 1 if sliding else 0, None, None)
+        pb, tb, rb = C.c_size_t(), C.c_size_t(), C.c_size_t()
+        check(lib.fkb_circular_tensor_sizes(C.byref(d), C.byref(pb), C.byref(tb), C.byref(rb)), "fkb_circular_tensor_sizes")
+        return pb.value, tb.value, rb.value
+
+    @property
+    def data(self) -> int:
+        return self._lib.fkb_circular_tensor_data(self._h)
+
+    @property
+    def next_index(self) -> int:
+        return self._lib.fkb_circular_tensor_next_index(self._h)
+
+    @staticmethod
+    def _chain(host_plan: "HostPlan"):
+        d = host_plan.desc()
+        if d.n_sequences != 1 or d.n_planes != 1:
+            raise ValueError("an update takes one sequence and one plane (the new image)")
+        return d
+
+    def plan_update(self, host_plan: "HostPlan", advance=True) -> "HostPlan":
+        """The plan of the next update as a HostPlan; `host_plan` holds the chain and the plane of the new image."""
+        d = self._chain(host_plan)
+        seqs = (Sequence * 2)()
+        planes = (Plane * (self.desc.batch + 1))()
+        ns, np_ = C.c_int32(), C.c_int32()
+        check(self._lib.fkb_circular_tensor_plan_update(self._h, d.sequences, d.planes, seqs, C.byref(ns), planes, C.byref(np_),
+                                                        1 if advance else 0), "fkb_circular_tensor_plan_update")
+        out = HostPlan()
+        out._keep = (host_plan, seqs, planes)     # the chain's operation array lives in host_plan
+        out._seqs = [seqs[i] for i in range(ns.value)]
+        out._planes = [planes[i] for i in range(np_.value)]
+        return out
+
+    def update(self, host_plan: "HostPlan", stream: int | None = None) -> None:
+        d = self._chain(host_plan)
+        check(self._lib.fkb_circular_tensor_update(self._h, d.sequences, d.planes, stream), "fkb_circular_tensor_update")
+
+    def destroy(self) -> None:
+        if self._h:
+            self._lib.fkb_circular_tensor_destroy(self._h)
             self._h = C.c_void_p()
 
     def __del__(self):

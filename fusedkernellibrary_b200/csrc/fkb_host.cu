@@ -2081,6 +2081,172 @@ extern "C" FKB_API int fkb_multi_gpu_session_get_shard(const fkb_multi_gpu_sessi
 }
 
 /* ------------------------------------------------------------------------------------ */
+/* circular tensor                                                                      */
+/* ------------------------------------------------------------------------------------ */
+struct fkb_circular_tensor {
+    fkb_circular_tensor_desc desc{};
+    unsigned char* tensor = nullptr;
+    unsigned char* ring = nullptr;
+    bool own_tensor = false, own_ring = false;
+    size_t plane_bytes = 0;
+    uint32_t pitch = 0, channel_stride = 0;
+    int32_t first = 0;   /* the reference's m_nextUpdateIdx (circular_tensor.h:160) */
+    int32_t pos = 0;     /* sliding: first plane of the window */
+};
+
+static int check_circular_desc(const fkb_circular_tensor_desc* d) {
+    if (!d) return fail(FKB_ERR_INVALID_ARGUMENT, "circular tensor: desc is NULL");
+    if (d->width == 0 || d->height == 0 || d->width > 65536 || d->height > 65536)
+        return fail(FKB_ERR_INVALID_ARGUMENT, "circular tensor: plane size %ux%u outside [1, 65536]", d->width, d->height);
+    if (d->batch < 1 || d->batch > 4096) return fail(FKB_ERR_INVALID_ARGUMENT, "circular tensor: batch %d outside [1, 4096]", d->batch);
+    if (d->order != FKB_CIRCULAR_NEWEST_FIRST && d->order != FKB_CIRCULAR_OLDEST_FIRST)
+        return fail(FKB_ERR_INVALID_ARGUMENT, "circular tensor: unknown order %d", d->order);
+    if (d->dst_format < FKB_DST_F32X3_PACKED || d->dst_format > FKB_DST_U32X3_PACKED)
+        return fail(FKB_ERR_INVALID_ARGUMENT, "circular tensor: unknown plane format %d", d->dst_format);
+    return FKB_OK;
+}
+
+extern "C" FKB_API int fkb_circular_tensor_sizes(const fkb_circular_tensor_desc* d, size_t* plane_bytes, size_t* tensor_bytes,
+                                                 size_t* ring_bytes) {
+    const int rc = check_circular_desc(d);
+    if (rc) return rc;
+    const size_t pb = (size_t)d->width * d->height * (d->dst_format == FKB_DST_F32_PLANAR3 ? 12u : dst_pixel_bytes(d->dst_format));
+    if (plane_bytes) *plane_bytes = pb;
+    if (tensor_bytes) *tensor_bytes = pb * (size_t)d->batch * (d->sliding ? 2 : 1);
+    if (ring_bytes) *ring_bytes = d->sliding ? 0 : pb * (size_t)d->batch;
+    return FKB_OK;
+}
+
+extern "C" FKB_API int fkb_circular_tensor_create(const fkb_circular_tensor_desc* d, fkb_circular_tensor** out) {
+    if (!out) return fail(FKB_ERR_INVALID_ARGUMENT, "circular tensor: out is NULL");
+    *out = nullptr;
+    size_t pb = 0, tb = 0, rb = 0;
+    int rc = fkb_circular_tensor_sizes(d, &pb, &tb, &rb);
+    if (rc) return rc;
+    std::unique_ptr<fkb_circular_tensor> ct(new fkb_circular_tensor());
+    ct->desc = *d;
+    ct->plane_bytes = pb;
+    ct->pitch = d->width * dst_pixel_bytes(d->dst_format);
+    ct->channel_stride = d->dst_format == FKB_DST_F32_PLANAR3 ? d->width * d->height * 4u : 0u;
+    ct->tensor = static_cast<unsigned char*>(d->tensor);
+    ct->ring = d->sliding ? nullptr : static_cast<unsigned char*>(d->ring);
+    const bool need_ring = !d->sliding && !ct->ring;
+    if (!ct->tensor || need_ring) {
+        int device = -1;
+        rc = require_device(&device);
+        if (rc) return rc;
+        void* p = nullptr;
+        if (!ct->tensor) {
+            FKB_CUDA(device_alloc(&p, tb));
+            ct->tensor = static_cast<unsigned char*>(p); ct->own_tensor = true;
+            const cudaError_t e = cudaMemset(p, 0, tb);
+            if (e != cudaSuccess) { device_free(p); return fail_cuda(e, "cudaMemset", __LINE__); }
+        }
+        if (need_ring) {
+            cudaError_t e = device_alloc(&p, rb);
+            if (e == cudaSuccess) { e = cudaMemset(p, 0, rb); if (e != cudaSuccess) device_free(p); }
+            if (e != cudaSuccess) { if (ct->own_tensor) device_free(ct->tensor); return fail_cuda(e, "ring allocation", __LINE__); }
+            ct->ring = static_cast<unsigned char*>(p); ct->own_ring = true;
+        }
+    }
+    /* the sliding window starts where the first update can move it one plane towards its newest end */
+    ct->pos = d->sliding ? (d->order == FKB_CIRCULAR_NEWEST_FIRST ? d->batch : 0) : 0;
+    *out = ct.release();
+    return FKB_OK;
+}
+
+extern "C" FKB_API void* fkb_circular_tensor_data(const fkb_circular_tensor* ct) {
+    if (!ct) return nullptr;
+    return ct->tensor + (ct->desc.sliding ? (size_t)ct->pos * ct->plane_bytes : 0);
+}
+
+extern "C" FKB_API int32_t fkb_circular_tensor_next_index(const fkb_circular_tensor* ct) { return ct ? ct->first : -1; }
+
+extern "C" FKB_API int fkb_circular_tensor_plan_update(fkb_circular_tensor* ct, const fkb_sequence* chain, const fkb_plane* source,
+                                                       fkb_sequence* out_sequences, int32_t* n_sequences, fkb_plane* out_planes,
+                                                       int32_t* n_planes, int32_t advance) {
+    if (!ct || !chain || !source || !out_sequences || !n_sequences || !out_planes || !n_planes)
+        return fail(FKB_ERR_INVALID_ARGUMENT, "circular tensor update: NULL argument");
+    if (chain->dst_format != ct->desc.dst_format)
+        return fail(FKB_ERR_INVALID_ARGUMENT, "circular tensor update: the chain's receiver (format %d) is not the tensor's (%d)",
+                    chain->dst_format, ct->desc.dst_format);
+    const int32_t B = ct->desc.batch;
+    const bool newest_first = ct->desc.order == FKB_CIRCULAR_NEWEST_FIRST;
+    auto chain_plane = [&](unsigned char* dst) {
+        fkb_plane p = *source;
+        p.dst = dst; p.dst_width = ct->desc.width; p.dst_height = ct->desc.height;
+        p.dst_pitch = ct->pitch; p.dst_channel_stride = ct->channel_stride; p.sequence = 0;
+        return p;
+    };
+    out_sequences[0] = *chain;
+    *n_sequences = 1;
+    int32_t n = 0;
+    if (ct->desc.sliding) {
+        /* window [pos, pos + B) of 2B planes; every result lies at p and p +- B, so the two halves always agree */
+        int32_t pos = ct->pos, w;
+        if (newest_first) { if (pos == 0) pos = B; pos -= 1; w = pos; }
+        else { if (pos == B) pos = 0; pos += 1; w = pos + B - 1; }
+        out_planes[n++] = chain_plane(ct->tensor + (size_t)w * ct->plane_bytes);
+        out_planes[n++] = chain_plane(ct->tensor + (size_t)(w >= B ? w - B : w + B) * ct->plane_bytes);
+        if (advance) ct->pos = pos;
+    } else {
+        const int32_t first = ct->first;
+        const int32_t zu = newest_first ? 0 : B - 1;                  /* SequenceSelectorType (circular_tensor.h:26-35) */
+        const int32_t ring_u = (zu + first) % B;                      /* CircularTensorWrite<Ascendent> (memory_operations.h:438-440) */
+        /* a copy moves one plane as it lies: whatever the receiver's layout, plane_bytes bytes seen as a packed image */
+        fkb_sequence copy{};
+        const bool bytes3 = ct->desc.dst_format == FKB_DST_U8X3_PACKED;
+        copy.src_format = bytes3 ? FKB_SRC_U8X3 : FKB_SRC_F32X3;
+        copy.dst_format = bytes3 ? FKB_DST_U8X3_PACKED : FKB_DST_F32X3_PACKED;
+        copy.resize_mode = FKB_RESIZE_NONE;
+        const uint32_t copy_pitch = ct->desc.width * (bytes3 ? 3u : 12u);
+        for (int32_t z = 0; z < B; ++z) {
+            if (z == zu) { out_planes[n++] = chain_plane(ct->tensor + (size_t)z * ct->plane_bytes); continue; }
+            int32_t r = newest_first ? first - z : z + first;         /* Descendent / Ascendent (memory_operations.h:437-445) */
+            r = r < 0 ? r + B : r >= B ? r - B : r;
+            fkb_plane p{};
+            p.src = ct->ring + (size_t)r * ct->plane_bytes;
+            p.src_width = ct->desc.width; p.src_height = ct->desc.height; p.src_pitch = copy_pitch;
+            p.crop_x = 0; p.crop_y = 0; p.crop_width = (int32_t)ct->desc.width; p.crop_height = (int32_t)ct->desc.height;
+            p.dst = ct->tensor + (size_t)z * ct->plane_bytes;
+            p.dst_width = ct->desc.width; p.dst_height = ct->desc.height; p.dst_pitch = copy_pitch; p.dst_channel_stride = 0;
+            p.sequence = 1;
+            out_planes[n++] = p;
+        }
+        out_planes[n++] = chain_plane(ct->ring + (size_t)ring_u * ct->plane_bytes);
+        if (B > 1) { out_sequences[1] = copy; *n_sequences = 2; }
+        if (advance) ct->first = (first + 1) % B;
+    }
+    *n_planes = n;
+    return FKB_OK;
+}
+
+extern "C" FKB_API int fkb_circular_tensor_update(fkb_circular_tensor* ct, const fkb_sequence* chain, const fkb_plane* source, void* stream) {
+    if (!ct) return fail(FKB_ERR_INVALID_ARGUMENT, "circular tensor update: NULL tensor");
+    NvtxRange range("fkb_circular_tensor_update");
+    fkb_sequence seqs[2];
+    std::vector<fkb_plane> planes((size_t)ct->desc.batch + 1);
+    int32_t ns = 0, np = 0;
+    const int32_t first = ct->first, pos = ct->pos;
+    int rc = fkb_circular_tensor_plan_update(ct, chain, source, seqs, &ns, planes.data(), &np, 1);
+    if (rc) return rc;
+    const fkb_plan_desc d{seqs, ns, planes.data(), np};
+    rc = fkb_execute_async(&d, stream);
+    if (rc) { ct->first = first; ct->pos = pos; } /* nothing ran: the tensor has not moved */
+    return rc;
+}
+
+extern "C" FKB_API int fkb_circular_tensor_destroy(fkb_circular_tensor* ct) {
+    if (!ct) return FKB_OK;
+    cudaError_t e = cudaSuccess;
+    if (ct->own_tensor) e = device_free(ct->tensor);
+    if (ct->own_ring) { const cudaError_t e2 = device_free(ct->ring); if (e == cudaSuccess) e = e2; }
+    delete ct;
+    if (e != cudaSuccess) return fail_cuda(e, "cudaFree", __LINE__);
+    return FKB_OK;
+}
+
+/* ------------------------------------------------------------------------------------ */
 /* allocation-free variant                                                              */
 /* ------------------------------------------------------------------------------------ */
 /* fkb_execute_static runs a plan like fkb_execute, but its descriptor table - the only device

@@ -378,6 +378,67 @@ FKB_API int fkb_debug_set_device_unavailable(int32_t device, int32_t unavailable
 /* One-shot fkb_host_session_create + run + destroy. */
 FKB_API int fkb_execute_host(const fkb_plan_desc* desc, void* stream);
 
+/* ---- a circular tensor: the newest BATCH outputs of a chain, kept in order ----
+ * The reference's CircularTensor<T, COLOR_PLANES, BATCH, CT_ORDER, ColorPlanes::Standard>::update
+ * (core/data/circular_tensor.h:86-161): every update runs the caller's chain once for one new image and leaves
+ * a BATCH-plane tensor whose planes are the last BATCH results, newest first or oldest first, for a
+ * model that takes a window of frames.  The reference does it in one divergent launch over BATCH
+ * planes (:111-156): one plane runs the chain and stores its result twice - into a hidden ring
+ * tensor at plane (z + first) mod BATCH (CircularTensorWrite<Ascendent>, memory_operations.h:436-446,
+ * :566-590) and into the visible tensor - and the other BATCH-1 planes copy ring planes into their new
+ * visible positions (CircularTensorRead, :531-563: plane z reads ring plane first - z for NewestFirst,
+ * z + first for OldestFirst, both mod BATCH); `first` then advances by one (:158).  The plane that
+ * runs the chain is 0 for NewestFirst and BATCH-1 for OldestFirst (SequenceSelectorType, :26-35).
+ *
+ * fkb_circular_tensor_update does the same in one launch of this library's multi-class kernel: a plan of
+ * BATCH+1 planes (the chain into the visible plane, the chain into the ring plane, BATCH-1 copies).
+ * With `sliding` set the copies disappear: the tensor is a window of BATCH planes inside a buffer
+ * of 2*BATCH planes, every result is stored at plane p and p +- BATCH, and the window moves by one plane
+ * per update - two stores per update whatever BATCH is, at the price of a data pointer that changes
+ * (fkb_circular_tensor_data after every update).  The reference has no such mode.
+ * Only the Standard colour-plane mode (plane-major tensors) is built; Transposed needs TensorTSplit
+ * windows per channel.  The reference ships no launcher for its divergent kernel (executors.h has
+ * no Executor<DivergentBatchTransformDPP>), so update() does not compile there; parity of this
+ * entry point is against a restatement of the index arithmetic above. */
+typedef enum fkb_circular_order {
+    FKB_CIRCULAR_NEWEST_FIRST = 0, /* plane 0 is the latest result */
+    FKB_CIRCULAR_OLDEST_FIRST = 1  /* plane BATCH-1 is the latest result */
+} fkb_circular_order;
+
+typedef struct fkb_circular_tensor_desc {
+    uint32_t width, height; /* of one plane, in pixels                                                   */
+    int32_t batch;          /* planes of the visible tensor (1 .. 4096)                                  */
+    int32_t order;          /* fkb_circular_order                                                        */
+    int32_t dst_format;     /* fkb_dst_format of the planes: the receiver every update's chain ends in   */
+    int32_t sliding;        /* 0: the reference's scheme, the tensor stays where it is; 1: sliding window */
+    void* tensor;           /* memory for the visible tensor (fkb_circular_tensor_sizes), or NULL to let  */
+                            /* the library allocate it on the current device; must hold zeros or earlier  */
+                            /* results                                                                   */
+    void* ring;             /* memory for the hidden ring, or NULL; unused with `sliding`                 */
+} fkb_circular_tensor_desc;
+
+typedef struct fkb_circular_tensor fkb_circular_tensor;
+
+/* Bytes of one plane, of the visible tensor's buffer and of the ring for this description. */
+FKB_API int fkb_circular_tensor_sizes(const fkb_circular_tensor_desc* desc, size_t* plane_bytes, size_t* tensor_bytes, size_t* ring_bytes);
+/* With both buffers given by the caller nothing is allocated and no CUDA call is made. */
+FKB_API int fkb_circular_tensor_create(const fkb_circular_tensor_desc* desc, fkb_circular_tensor** out);
+/* First plane of the visible tensor as it is after the latest update; planes are dense (pitch = width * pixel bytes). */
+FKB_API void* fkb_circular_tensor_data(const fkb_circular_tensor* ct);
+/* The reference's m_nextUpdateIdx (number of updates so far, mod BATCH). */
+FKB_API int32_t fkb_circular_tensor_next_index(const fkb_circular_tensor* ct);
+/* The plan of the next update, without running it: `chain` is the sender chain and receiver kind of the new image
+ * (dst_format must be the tensor's), `source` its plane (source image and crop; destination fields are ignored).
+ * out_sequences holds 2 entries, out_planes batch+1.  With `advance` non-zero the tensor moves on as if the plan had
+ * run (for callers that run the plan themselves, e.g. together with other planes). */
+FKB_API int fkb_circular_tensor_plan_update(fkb_circular_tensor* ct, const fkb_sequence* chain, const fkb_plane* source,
+                                            fkb_sequence* out_sequences, int32_t* n_sequences, fkb_plane* out_planes,
+                                            int32_t* n_planes, int32_t advance);
+/* One update: plans it, runs it with fkb_execute_async on `stream` (asynchronous, no allocation after the
+ * library's first call on the device) and advances.  fkb_async_check(stream) waits for it. */
+FKB_API int fkb_circular_tensor_update(fkb_circular_tensor* ct, const fkb_sequence* chain, const fkb_plane* source, void* stream);
+FKB_API int fkb_circular_tensor_destroy(fkb_circular_tensor* ct);
+
 /* fkb_execute without any device allocation.  No counterpart in the reference (its launch
  * passes all parameters as kernel arguments and never allocates).  Meant for hosts that cannot
  * call cudaMalloc while running: plug-ins inside a server whose framework has taken all of HBM

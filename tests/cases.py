@@ -333,5 +333,12 @@ def run_on_host(case: Case, port, host_branch=False):
     return case.outputs
 
 
+def cuda_copy_to_host(host: np.ndarray, device_ptr: int) -> None:
+    """Synchronous device-to-host copy from a raw device pointer (memory the library allocated)."""
+    from cuda.bindings import runtime
+    (err,) = runtime.cudaMemcpy(host.ctypes.data, int(device_ptr), host.nbytes, runtime.cudaMemcpyKind.cudaMemcpyDeviceToHost)
+    assert int(err) == 0, err
+
+
 def bits(a: np.ndarray) -> np.ndarray:
     return a.view(np.uint32) if a.dtype == np.float32 else a
