@@ -657,6 +657,49 @@ def side_workload(torch, stream, name, steps, warmup, peak):
     return rec
 
 
+def circular_tensor_record(torch, stream, updates: int = 128):
+    """fkb_circular_tensor_update: a window of the newest 16 normalised 3x224x224 crops of 4K frames, one update per new
+    crop.  Time per update with the updates queued back to back (device_us: the host prepares each update's plan, so this
+    is the larger of host and kernel time) and the kernel of one update alone (kernel_us), in the reference's scheme (15
+    planes copied per update) and as a sliding window."""
+    rng = np.random.default_rng(1000)
+    fw, fh, w, h, batch = 3840, 2160, 224, 224, 16
+    frames = [torch.from_numpy(_u8(rng, fh, fw * 3)).cuda() for _ in range(4)]
+    rects = chains.random_rects(rng, 64, fw, fh, lo=16, hi=512)
+    plans = []
+    for k in range(64):
+        p = abi.HostPlan()
+        seq = p.add_sequence(abi.SRC_U8X3, abi.DST_F32_PLANAR3, abi.RESIZE_PRESERVE_AR, chains.normalize_ops())
+        p.add_plane(src=frames[k % 4].data_ptr(), src_width=fw, src_height=fh, src_pitch=fw * 3, crop=tuple(int(v) for v in rects[k]),
+                    dst=0, dst_width=w, dst_height=h, dst_pitch=w * 4, dst_channel_stride=w * h * 4, sequence=seq)
+        plans.append(p)
+    sh = stream.cuda_stream
+    rec = {"name": "circular", "workload": f"circular tensor of the newest {batch} 3x{h}x{w} float planes, one 4K crop per update",
+           "unit": "us/update"}
+    for key, sliding in (("reference_scheme", False), ("sliding_window", True)):
+        ct = abi.CircularTensor(w, h, batch, abi.DST_F32_PLANAR3, abi.CIRCULAR_NEWEST_FIRST, sliding)
+        for k in range(32):
+            ct.update(plans[k], sh)
+        abi.async_check(sh)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        t0 = time.perf_counter()
+        for k in range(updates):
+            ct.update(plans[k % 64], sh)
+        host = (time.perf_counter() - t0) / updates * 1e6
+        e1.record(stream)
+        abi.async_check(sh)
+        one = abi.DevicePlan(ct.plan_update(plans[0], advance=False))   # one update's plan alone: the kernel's own time
+        per, _ = time_launches(torch, stream, lambda i: one.launch(sh), 20, 3)
+        one.check(sh)
+        one.destroy()
+        rec[key] = {"kernel_us": float(np.mean(per)) * 1e3, "device_us": e0.elapsed_time(e1) / updates * 1e3, "host_us_per_call": host,
+                    "planes_per_update": 2 if sliding else batch + 1,
+                    "bytes_stored_per_update": ct.plane_bytes * (2 if sliding else batch + 1)}
+        ct.destroy()
+    return rec
+
+
 def run_ours(args, rank: int, world: int, local_rank: int):
     import torch
     import torch.distributed as dist
@@ -803,6 +846,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             if not args.no_others and args.workload == "c3":
                 dw.destroy()
                 others = [side_workload(torch, stream, n, 20, 3, peak) for n in ("c2s", "c2", "c4", "c5b", "c1b", "c1", "c5a16")]
+                others.append(circular_tensor_record(torch, stream))
         if not args.no_cpu:
             cpu = cpu_baseline(wl)
 

@@ -37,6 +37,15 @@
  *              ConvertYUVToRGB<NV12|NV21, Full, bt709|bt601|bt2020, false, float3>
  *   receivers  PerThreadWrite<_2D|_3D, T>, TensorWrite<T>, TensorSplit<float3>, TensorTSplit<float3>,
  *              SplitWrite<_2D, float3> over three equally spaced images of one pitch
+ *
+ * The header also supplies the executor the reference declares a pattern for but never defines:
+ * fk::Executor<fk::DivergentBatchTransformDPP<ParArch::GPU_NVIDIA, SequenceSelector>> (the pattern:
+ * data_parallel_patterns.h:301-353; its only caller: CircularTensor::update, core/data/circular_tensor.h:146).  With this
+ * header included, fk::CircularTensor<float, 3, BATCH, order, ColorPlanes::Standard>::update(stream, iops...) compiles
+ * and runs as one launch of this library: plane z is lowered from the sequence SequenceSelector::at(z) names, a
+ * MidWrite<CircularTensorWrite<...>> directly before the receiver becomes a second store of the plane's result, and
+ * CircularTensorRead<dir, TensorRead<T> | TensorPack<float3>, BATCH> becomes BATCH planes that move tensor planes as
+ * they lie.  Any other set of sequences closed by receivers works the same way.
  */
 #ifndef FKB200_EXECUTOR_H
 #define FKB200_EXECUTOR_H
@@ -73,6 +82,7 @@ struct PlaneState {
     float border_value[3] = {0.f, 0.f, 0.f};
     int deinterlace = FKB_DEINTERLACE_NONE;
     float transform[9] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    bool raw_planar = false; /* the source is one dense planar float plane (3 x H x W) that is moved as it lies */
     /* what the reference's Resize::build derived on the host (resize.h:105-166), kept so that a caller
        can compare it with what the library derives (fkb_derive_resize) */
     fkb_resize_params reference_resize{};
@@ -407,6 +417,54 @@ template <size_t B, typename Op, typename Out> struct LowerFirst<fk::BatchRead<B
     }
 };
 
+/* computeCircularThreadIdx (memory_operations.h:436-446) */
+inline int circular_plane(bool ascendent, int z, int first, int batch) {
+    if (ascendent) { const int p = z + first; return p >= batch ? p - batch : p; }
+    const int p = first - z;
+    return p < 0 ? batch + p : p;
+}
+/* one plane of a tensor as the source of a plane that only moves it */
+template <typename Op> struct TensorSource {
+    static_assert(dependent_false<Op>::value, "fkb200: this tensor read is not on the accelerated path");
+};
+template <typename T> struct TensorSource<fk::TensorRead<T>> {
+    template <typename Raw> static void fill(PlaneState& st, const Raw& t, int plane) {
+        st.src_format = source_format_of<T>();
+        st.plane.src = reinterpret_cast<const unsigned char*>(t.data) + (size_t)t.dims.plane_pitch * t.dims.color_planes * plane;
+        st.plane.src_width = t.dims.width; st.plane.src_height = t.dims.height; st.plane.src_pitch = t.dims.pitch;
+        st.plane.crop_x = 0; st.plane.crop_y = 0; st.plane.crop_width = (int32_t)t.dims.width; st.plane.crop_height = (int32_t)t.dims.height;
+    }
+};
+/* TensorPack<float3> (memory_operations.h:257-289) reads what TensorSplit<float3> wrote: three float planes */
+template <> struct TensorSource<fk::TensorPack<float3>> {
+    template <typename Raw> static void fill(PlaneState& st, const Raw& t, int plane) {
+        if (t.dims.pitch != t.dims.width * sizeof(float) || t.dims.plane_pitch != t.dims.pitch * t.dims.height || t.dims.color_planes != 3)
+            throw std::runtime_error("fkb200: a planar tensor that is read back must be dense (pitch = width * 4, three colour planes)");
+        st.raw_planar = true;
+        st.src_format = FKB_SRC_F32X3;
+        st.plane.src = reinterpret_cast<const unsigned char*>(t.data) + (size_t)t.dims.plane_pitch * 3 * plane;
+        st.plane.src_width = t.dims.width; st.plane.src_height = t.dims.height; st.plane.src_pitch = t.dims.width * 12;
+        st.plane.crop_x = 0; st.plane.crop_y = 0; st.plane.crop_width = (int32_t)t.dims.width; st.plane.crop_height = (int32_t)t.dims.height;
+    }
+};
+/* CircularTensorRead<dir, Op, BATCH> (memory_operations.h:531-563): plane z reads tensor plane first -+ z */
+template <fk::CircularDirection DIR, typename Op, int B> struct LowerFirst<fk::CircularTensorRead<DIR, Op, B>> {
+    template <typename D> static void apply(std::vector<PlaneState>& states, const D& d) {
+        states.reserve(B);
+        for (int z = 0; z < B; ++z) {
+            states.emplace_back();
+            TensorSource<Op>::fill(states.back(), d.params.opData.params, circular_plane(DIR == fk::CircularDirection::Ascendent, z, d.params.first, B));
+        }
+    }
+};
+/* MidWrite<CircularTensorWrite<dir, WriteOp, BATCH>> (memory_operations.h:566-590): a second store of the value */
+template <typename Op> struct CircularWriteTraits : std::false_type {};
+template <fk::CircularDirection DIR, typename WOp, int B> struct CircularWriteTraits<fk::CircularTensorWrite<DIR, WOp, B>> : std::true_type {
+    using Write = WOp;
+    static constexpr bool ascendent = DIR == fk::CircularDirection::Ascendent;
+    static constexpr int batch = B;
+};
+
 template <typename IOp> inline void lower_middle(std::vector<PlaneState>& states, const IOp& iop) {
     for (PlaneState& st : states) lower_compute<typename IOp::Operation>(st, iop);
 }
@@ -422,40 +480,64 @@ inline bool same_sequence(const PlaneState& a, const fkb_sequence& q, const std:
     return true;
 }
 
+/* only_plane < 0: every plane of the chain; otherwise the chain as the reference's plane `only_plane` runs it (thread.z =
+   only_plane): that plane of a batched read, or a single-image read, stored at that plane of the receiver */
 template <typename First, typename... Rest>
-inline LoweredPlan lower(const First& first, const Rest&... rest) {
+inline LoweredPlan lower_planes(int only_plane, const First& first, const Rest&... rest) {
     static_assert(sizeof...(Rest) >= 1, "fkb200: a sender chain must be closed by a receiver");
     LoweredPlan plan;
     LowerFirst<typename First::Operation>::apply(plan.states, first);
+    if (only_plane >= 0 && plan.states.size() > 1) {
+        if ((size_t)only_plane >= plan.states.size()) throw std::runtime_error("fkb200: the sequence selected for a plane has fewer planes");
+        PlaneState keep = plan.states[(size_t)only_plane];
+        plan.states.assign(1, keep);
+    }
     /* everything between the read and the receiver continues every plane; the last one is the receiver */
-    Receiver recv;
+    Receiver recv, mid_recv;
+    bool has_mid = false, mid_ascendent = true;
+    int mid_first = 0, mid_batch = 1;
     size_t index = 0;
     auto visit = [&](const auto& iop) {
         using IOp = std::decay_t<decltype(iop)>;
+        using Op = typename IOp::Operation;
         if (++index == sizeof...(Rest)) {
-            if constexpr (fk::isWriteType<typename IOp::Operation>) recv = LowerWrite<typename IOp::Operation>::apply(iop);
+            if constexpr (fk::isWriteType<Op> && !CircularWriteTraits<Op>::value) recv = LowerWrite<Op>::apply(iop);
             else throw std::runtime_error("fkb200: the last operation must be a receiver");
         } else {
-            if constexpr (fk::isWriteType<typename IOp::Operation>) throw std::runtime_error("fkb200: mid-chain writes are not on the accelerated path");
+            if constexpr (CircularWriteTraits<Op>::value) {
+                if (index + 1 != sizeof...(Rest)) throw std::runtime_error("fkb200: a mid-chain write anywhere but directly before the receiver is not on the accelerated path");
+                mid_recv = LowerWrite<typename CircularWriteTraits<Op>::Write>::apply(iop.params.opData);
+                has_mid = true; mid_ascendent = CircularWriteTraits<Op>::ascendent; mid_batch = CircularWriteTraits<Op>::batch;
+                mid_first = iop.params.first;
+            } else if constexpr (fk::isWriteType<Op>) throw std::runtime_error("fkb200: mid-chain writes are not on the accelerated path");
             else lower_middle(plan.states, iop);
         }
     };
     (visit(rest), ...);
-    if (recv.planes < plan.states.size()) throw std::runtime_error("fkb200: the receiver has fewer planes than the batch");
-    for (size_t z = 0; z < plan.states.size(); ++z) {
-        PlaneState& st = plan.states[z];
+    if (only_plane < 0 && recv.planes < plan.states.size()) throw std::runtime_error("fkb200: the receiver has fewer planes than the batch");
+    if (only_plane >= 0 && recv.planes <= (size_t)only_plane) throw std::runtime_error("fkb200: the receiver has no such plane");
+    if (has_mid && (mid_recv.dst_format != recv.dst_format || mid_recv.planes < (uint32_t)mid_batch))
+        throw std::runtime_error("fkb200: the mid-chain write must use the receiver's layout and hold BATCH planes");
+    for (size_t i = 0; i < plan.states.size(); ++i) {
+        PlaneState& st = plan.states[i];
+        const size_t z = only_plane >= 0 ? (size_t)only_plane : i;
         if (st.resize_mode == FKB_RESIZE_NONE) { st.plane.dst_width = (uint32_t)st.plane.crop_width; st.plane.dst_height = (uint32_t)st.plane.crop_height; }
         if (st.plane.dst_width > recv.width || st.plane.dst_height > recv.height)
             throw std::runtime_error("fkb200: the sender's output is larger than the receiver");
-        st.plane.dst = static_cast<unsigned char*>(recv.data) + z * recv.plane_bytes;
-        st.plane.dst_pitch = recv.pitch;
-        st.plane.dst_channel_stride = recv.channel_stride;
+        int dst_format = recv.dst_format;
+        uint32_t pitch = recv.pitch, channel_stride = recv.channel_stride;
+        if (st.raw_planar) { /* moved as it lies: only into a receiver of the same dense planar layout, with nothing in between */
+            if (!st.ops.empty() || st.resize_mode != FKB_RESIZE_NONE || recv.dst_format != FKB_DST_F32_PLANAR3 || recv.pitch != recv.width * 4u ||
+                recv.channel_stride != recv.width * recv.height * 4u || st.plane.dst_width != recv.width || st.plane.dst_height != recv.height)
+                throw std::runtime_error("fkb200: a planar tensor plane can only be moved into a dense TensorSplit receiver of the same size");
+            dst_format = FKB_DST_F32X3_PACKED; pitch = recv.width * 12u; channel_stride = 0;
+        }
         size_t s = 0;
         for (; s < plan.sequences.size(); ++s)
-            if (same_sequence(st, plan.sequences[s], plan.sequence_ops[s], recv.dst_format)) break;
+            if (same_sequence(st, plan.sequences[s], plan.sequence_ops[s], dst_format)) break;
         if (s == plan.sequences.size()) {
             fkb_sequence q{};
-            q.src_format = st.src_format; q.dst_format = recv.dst_format; q.resize_mode = st.resize_mode;
+            q.src_format = st.src_format; q.dst_format = dst_format; q.resize_mode = st.resize_mode;
             q.n_ops = (int32_t)st.ops.size(); q.n_pre_ops = st.resize_mode == FKB_RESIZE_NONE ? 0 : st.n_pre_ops;
             std::memcpy(q.background, st.background, sizeof q.background);
             q.border_mode = st.border_mode; q.deinterlace = st.deinterlace;
@@ -465,8 +547,63 @@ inline LoweredPlan lower(const First& first, const Rest&... rest) {
             plan.sequence_ops.push_back(st.ops);
         }
         st.plane.sequence = (int32_t)s;
+        st.plane.dst = static_cast<unsigned char*>(recv.data) + z * recv.plane_bytes;
+        st.plane.dst_pitch = pitch;
+        st.plane.dst_channel_stride = channel_stride;
         plan.planes.push_back(st.plane);
+        if (has_mid) {
+            fkb_plane second = st.plane;
+            second.dst = static_cast<unsigned char*>(mid_recv.data) + (size_t)circular_plane(mid_ascendent, (int)z, mid_first, mid_batch) * mid_recv.plane_bytes;
+            second.dst_pitch = mid_recv.pitch; second.dst_channel_stride = mid_recv.channel_stride;
+            plan.planes.push_back(second);
+        }
     }
+    return plan;
+}
+
+template <typename First, typename... Rest>
+inline LoweredPlan lower(const First& first, const Rest&... rest) { return lower_planes(-1, first, rest...); }
+
+/* Several sequences in one launch (DivergentBatchTransformDPP, data_parallel_patterns.h:301-353): plane z runs the
+   sequence whose 1-based number SequenceSelector::at(z) returns (:316-325); a plane no sequence claims does nothing. */
+template <typename SequenceSelector, typename... Sequences>
+inline LoweredPlan lower_divergent(const Sequences&... sequences) {
+    size_t n_planes = 0;
+    auto count = [&](const auto& seq) {
+        const LoweredPlan all = fk::apply([](const auto&... iops) { return lower_planes(-1, iops...); }, seq.instantiableOperations);
+        if (all.states.size() > n_planes) n_planes = all.states.size();
+    };
+    (count(sequences), ...);
+    LoweredPlan plan;
+    for (size_t z = 0; z < n_planes; ++z) {
+        const unsigned chosen = SequenceSelector::at((unsigned)z);
+        unsigned number = 0;
+        auto take = [&](const auto& seq) {
+            if (++number != chosen) return;
+            LoweredPlan one = fk::apply([&](const auto&... iops) { return lower_planes((int)z, iops...); }, seq.instantiableOperations);
+            for (fkb_plane p : one.planes) {
+                const fkb_sequence& q = one.sequences[(size_t)p.sequence];
+                const std::vector<fkb_op>& ops = one.sequence_ops[(size_t)p.sequence];
+                size_t s = 0;
+                for (; s < plan.sequences.size(); ++s) {
+                    const fkb_sequence& e = plan.sequences[s];
+                    if (e.src_format != q.src_format || e.dst_format != q.dst_format || e.resize_mode != q.resize_mode || e.n_ops != q.n_ops ||
+                        e.n_pre_ops != q.n_pre_ops || e.border_mode != q.border_mode || e.deinterlace != q.deinterlace ||
+                        std::memcmp(e.background, q.background, sizeof q.background) != 0 || std::memcmp(e.border_value, q.border_value, sizeof q.border_value) != 0 ||
+                        std::memcmp(e.transform, q.transform, sizeof q.transform) != 0) continue;
+                    bool same = true;
+                    for (size_t k = 0; k < ops.size() && same; ++k)
+                        same = plan.sequence_ops[s][k].opcode == ops[k].opcode && std::memcmp(plan.sequence_ops[s][k].p, ops[k].p, sizeof ops[k].p) == 0;
+                    if (same) break;
+                }
+                if (s == plan.sequences.size()) { plan.sequences.push_back(q); plan.sequence_ops.push_back(ops); }
+                p.sequence = (int32_t)s;
+                plan.planes.push_back(p);
+            }
+        };
+        (take(sequences), ...);
+    }
+    if (plan.planes.empty()) throw std::runtime_error("fkb200: no plane selects any of the sequences");
     return plan;
 }
 
@@ -498,6 +635,31 @@ private:
 public:
     FK_HOST_FUSE ParArch parArch() { return ParArch::GPU_NVIDIA; }
     DECLARE_EXECUTOR_PARENT_IMPL
+};
+
+/* The executor that CircularTensor::update calls (core/data/circular_tensor.h:146) and the reference leaves undefined:
+   several operation sequences, one launch, plane z running the sequence SequenceSelector::at(z) names. */
+template <typename SequenceSelector>
+struct Executor<DivergentBatchTransformDPP<ParArch::GPU_NVIDIA, SequenceSelector>> {
+    FK_STATIC_STRUCT(Executor, Executor)
+    template <typename... Sequences>
+    FK_HOST_FUSE void executeOperations(const Stream_<ParArch::GPU_NVIDIA>& stream_, const Sequences&... sequences) {
+        fkb200::binding::LoweredPlan plan = fkb200::binding::lower_divergent<SequenceSelector>(sequences...);
+        const fkb_plan_desc desc = plan.desc();
+        fkb200::binding::check(fkb_execute_async(&desc, stream_.getCUDAStream()));
+    }
+    FK_HOST_FUSE ParArch parArch() { return ParArch::GPU_NVIDIA; }
+};
+/* update() names the host variant in the other branch of a run-time test (:152), so it must exist to compile;
+   this library has no CPU path */
+template <typename SequenceSelector>
+struct Executor<DivergentBatchTransformDPP<ParArch::CPU, SequenceSelector>> {
+    FK_STATIC_STRUCT(Executor, Executor)
+    template <typename StreamType, typename... Sequences>
+    FK_HOST_FUSE void executeOperations(const StreamType&, const Sequences&...) {
+        throw std::runtime_error("fkb200: divergent sequences run on device memory only (no CPU path)");
+    }
+    FK_HOST_FUSE ParArch parArch() { return ParArch::CPU; }
 };
 
 }  // namespace fk

@@ -113,6 +113,41 @@ def deinterlace(mode, src, w, h, pitch, kind, mul, out, stream=None):
     _check(lib().fklbind_deinterlace(mode, _p(src), w, h, pitch, kind, _f3(mul), _p(out), _p(stream)))
 
 
+def circular_describe6(order, frame, w, h, pitch, rect, dw, dh, bg, d0, mean, std, visible, hidden, first):
+    """Lowers the two sequences CircularTensor::update builds for a 6-plane planar tensor; the plan is kept for last_plan()."""
+    r = (C.c_int * 4)(*[int(x) for x in rect])
+    _check(lib().fklbind_circular_describe6(order, _p(frame), w, h, pitch, r, dw, dh, _f3(bg), _f3(d0), _f3(mean), _f3(std), _p(visible),
+                                            _p(hidden), first))
+
+
+class ReferenceCircularTensor:
+    """fk::CircularTensor<float, 3, 6, order, ColorPlanes::Standard> itself (device memory it allocates); update() runs through
+    the Executor<DivergentBatchTransformDPP> that include/fkb200_executor.h supplies."""
+
+    def __init__(self, order, w, h):
+        l = lib()
+        l.fklbind_circular_create.restype = C.c_void_p
+        l.fklbind_circular_data.restype = C.c_void_p
+        l.fklbind_circular_data.argtypes = [C.c_void_p]
+        l.fklbind_circular_destroy.argtypes = [C.c_void_p]
+        self._h = l.fklbind_circular_create(order, w, h)
+        if not self._h:
+            raise RuntimeError(l.fklbind_last_error().decode())
+
+    @property
+    def data(self) -> int:
+        return lib().fklbind_circular_data(self._h)
+
+    def update(self, frame, w, h, pitch, rect, bg, d0, mean, std, stream=None):
+        r = (C.c_int * 4)(*[int(x) for x in rect])
+        _check(lib().fklbind_circular_update(C.c_void_p(self._h), _p(frame), w, h, pitch, r, _f3(bg), _f3(d0), _f3(mean), _f3(std), _p(stream)))
+
+    def destroy(self):
+        if self._h:
+            lib().fklbind_circular_destroy(self._h)
+            self._h = None
+
+
 def last_plan():
     """(planes, sequences) of the last DESCRIBE call: planes as abi.Plane, sequences as (abi.Sequence, [abi.Op])."""
     n_p, n_s = C.c_int(), C.c_int()

@@ -11,8 +11,10 @@ planes one by one with the reference's index arithmetic:
   (OldestFirst: plane z + first), both mod BATCH (:436-446, 531-563), and stores at visible plane z;
 * first advances by one, mod BATCH (circular_tensor.h:158).
 
-The reference has no host launcher for its divergent kernel, so update() cannot be built from its headers and this
-model is not pinned by a run of the reference: parity of the circular tensor is "unpinned" beyond this restatement.
+The reference has no host launcher for its divergent kernel, so update() itself cannot be built from its headers and
+this model cannot be checked against the reference on the CPU.  On a GPU the library's updates are compared with the
+reference's divergent kernel itself (oracle/ref/fklref_circular.cpp launches it with the sequences update() builds);
+this model covers the layouts, orders and batch sizes that unit is not built for.
 The hidden tensor starts as zeros here (the reference leaves it as allocated).
 """
 from __future__ import annotations

@@ -19,6 +19,7 @@
 #include <fused_kernel/fused_kernel.h>
 #include <fused_kernel/algorithms/algorithms.h>
 #include <fused_kernel/algorithms/image_processing/image.h>
+#include <fused_kernel/core/data/circular_tensor.h>
 
 #include <fkb200_executor.h>
 
@@ -250,6 +251,76 @@ int fklbind_deinterlace(int mode, const void* src, int w, int h, int pitch, int 
     if (kind == 1) return run(mode, stream, Deinterlace<DeinterlaceType::BLEND>::build(read).then(Mul<float3>::build(f3(mul))), write);
     const auto lin = kind == 2 ? DeinterlaceLinear::USE_EVEN : DeinterlaceLinear::USE_ODD;
     return run(mode, stream, Deinterlace<DeinterlaceType::INTER_LINEAR>::build(lin, read).then(Mul<float3>::build(f3(mul))), write);
+}
+
+/* ---- the reference's own CircularTensor class (core/data/circular_tensor.h), its update() running through the binding ---- */
+using RefCircularNewest = CircularTensor<float, 3, 6, CircularTensorOrder::NewestFirst, ColorPlanes::Standard>;
+using RefCircularOldest = CircularTensor<float, 3, 6, CircularTensorOrder::OldestFirst, ColorPlanes::Standard>;
+struct CircularHandle { int order; RefCircularNewest newest; RefCircularOldest oldest; };
+
+/* a 6-plane tensor of 3 x h x w floats in device memory that the reference's Tensor class allocates */
+void* fklbind_circular_create(int order, int w, int h) {
+    try {
+        auto* c = new CircularHandle{order, {}, {}};
+        if (order == 0) c->newest.Alloc((uint)w, (uint)h, MemType::Device); else c->oldest.Alloc((uint)w, (uint)h, MemType::Device);
+        return c;
+    } catch (const std::exception& e) { g_error = e.what(); return nullptr; }
+}
+void* fklbind_circular_data(void* handle) {
+    auto* c = static_cast<CircularHandle*>(handle);
+    return c->order == 0 ? (void*)c->newest.ptr().data : (void*)c->oldest.ptr().data;
+}
+/* CircularTensor::update(stream, crop -> PRESERVE_AR resize -> Div, Sub, Div, TensorSplit(this tensor)) */
+int fklbind_circular_update(void* handle, const void* frame, int w, int h, int pitch, const int* rect, const float* bg, const float* d0,
+                            const float* mean, const float* stdv, void* stream) {
+    auto* c = static_cast<CircularHandle*>(handle);
+    try {
+        Stream_<ParArch::GPU_NVIDIA> s(static_cast<cudaStream_t>(stream));
+        auto run = [&](auto& tensor) {
+            const auto dims = tensor.ptr().dims;
+            const auto sender = PerThreadRead<ND::_2D, uchar3>::build(raw_u8x3(frame, w, h, pitch))
+                                    .then(Crop<>::build(Rect(rect[0], rect[1], rect[2], rect[3])))
+                                    .then(Resize<LINEAR, AspectRatio::PRESERVE_AR>::build(Size((int)dims.width, (int)dims.height), f3(bg)))
+                                    .then(Div<float3>::build(f3(d0)))
+                                    .then(Sub<float3>::build(f3(mean)))
+                                    .then(Div<float3>::build(f3(stdv)));
+            tensor.update(s, sender, TensorSplit<float3>::build(tensor.ptr()));
+        };
+        if (c->order == 0) run(c->newest); else run(c->oldest);
+        return 0;
+    } catch (const std::exception& e) { g_error = e.what(); return -1; }
+}
+void fklbind_circular_destroy(void* handle) { delete static_cast<CircularHandle*>(handle); }
+
+/* The two sequences update() builds (circular_tensor.h:121-134) over tensors of the caller, lowered only: for the
+   comparison of the plan with fkb_circular_tensor_plan_update on a machine without a GPU. */
+int fklbind_circular_describe6(int order, const void* frame, int w, int h, int pitch, const int* rect, int dw, int dh, const float* bg,
+                               const float* d0, const float* mean, const float* stdv, float* visible, float* hidden, int first) {
+    try {
+        const auto v = raw_tensor<float>(visible, dw, dh, 6, 3), t = raw_tensor<float>(hidden, dw, dh, 6, 3);
+        const auto sender = PerThreadRead<ND::_2D, uchar3>::build(raw_u8x3(frame, w, h, pitch))
+                                .then(Crop<>::build(Rect(rect[0], rect[1], rect[2], rect[3])))
+                                .then(Resize<LINEAR, AspectRatio::PRESERVE_AR>::build(Size(dw, dh), f3(bg)))
+                                .then(Div<float3>::build(f3(d0)))
+                                .then(Sub<float3>::build(f3(mean)))
+                                .then(Div<float3>::build(f3(stdv)));
+        const auto write = TensorSplit<float3>::build(v);
+        MidWrite<CircularTensorWrite<CircularDirection::Ascendent, TensorSplit<float3>, 6>> toHidden;
+        toHidden.params.first = first;
+        toHidden.params.opData.params = t;
+        const auto updateOps = buildOperationSequence(sender, toHidden, write);
+        if (order == 0) {
+            Read<CircularTensorRead<CircularDirection::Descendent, TensorPack<float3>, 6>> fromHidden;
+            fromHidden.params.first = first; fromHidden.params.opData.params = t;
+            g_last = fkb200::binding::lower_divergent<SequenceSelectorType<CircularTensorOrder::NewestFirst, 6>>(updateOps, buildOperationSequence(fromHidden, write));
+        } else {
+            Read<CircularTensorRead<CircularDirection::Ascendent, TensorPack<float3>, 6>> fromHidden;
+            fromHidden.params.first = first; fromHidden.params.opData.params = t;
+            g_last = fkb200::binding::lower_divergent<SequenceSelectorType<CircularTensorOrder::OldestFirst, 6>>(updateOps, buildOperationSequence(fromHidden, write));
+        }
+        (void)g_last.desc();
+        return 0;
+    } catch (const std::exception& e) { g_error = e.what(); return -1; }
 }
 
 /* ---- inspection of the plan of the last mode-1 call on this thread ---- */

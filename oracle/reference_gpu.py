@@ -120,3 +120,13 @@ def crop_resize_norm_planar(frame_ptrs, frame_index, w, h, pitch, rects, dw, dh,
 def nv12_resize(frame_ptrs, w, h, pitch, dw, dh, div, dst, flavour="default"):
     """dst: device tensor B x dh x dw x 3 float32; B >= 2."""
     lib(flavour).fklref_gpu_nv12_resize(_ptrs(frame_ptrs), w, h, pitch, len(frame_ptrs), dw, dh, _f3(div), _p(dst))
+
+
+def circular_update6(frame, w, h, pitch, rect, dw, dh, bg, d0, mean, std, visible, hidden, first, order, planar=True, flavour="default"):
+    """One update of a 6-plane circular tensor by the reference's divergent kernel (oracle/ref/fklref_circular.cpp): the
+    sequences CircularTensor::update builds (core/data/circular_tensor.h:121-134), launched as its comment does (:136-142).
+    `visible` / `hidden` are device tensors of 6 planes; `first` is the caller's m_nextUpdateIdx; order 0 newest first."""
+    r = (C.c_int * 4)(*[int(v) for v in rect])
+    fn = lib(flavour).fklref_gpu_circular_update_planar6 if planar else lib(flavour).fklref_gpu_circular_update_packed6
+    if fn(_p(frame), w, h, pitch, r, dw, dh, _f3(bg), _f3(d0), _f3(mean), _f3(std), _p(visible), _p(hidden), int(first), int(order)) != 0:
+        raise RuntimeError("the reference's divergent kernel did not launch")

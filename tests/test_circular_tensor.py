@@ -5,7 +5,9 @@ plain-C checker, and the visible tensor is compared after every update with a re
 arithmetic (oracle/circular_model.py) fed with the chain's result computed alone.  The sliding-window mode, which the
 reference does not have, must show the same visible tensor without a single copy plane.
 GPU part: the same through fkb_circular_tensor_update on device memory the library allocates, with the allocation
-counters still after the first updates.
+counters still after the first updates; and, update by update, the visible tensor AND the hidden ring against the
+reference's own divergent kernel running the two operation sequences that CircularTensor::update builds
+(oracle/ref/fklref_circular.cpp; the reference lacks only the host launcher for that kernel).
 """
 import numpy as np
 import pytest
@@ -13,6 +15,7 @@ import pytest
 from fusedkernellibrary_b200 import abi, chains
 from fusedkernellibrary_b200.abi import op
 from oracle import circular_model as cm
+from oracle import reference_gpu as refgpu
 from tests import cases as tc
 
 W, H = 40, 28   # plane size
@@ -131,4 +134,39 @@ def test_updates_on_the_gpu(fkb_lib, oracle_port, fmt_name, order, sliding):
     after = abi.debug_counters()
     assert (after.device_allocations, after.device_frees, after.host_pinned_allocations) == \
            (counters.device_allocations, counters.device_frees, counters.host_pinned_allocations), "an update allocated memory"
+    ct.destroy()
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(not refgpu.available("nofma"), reason="reference CUDA build not present")
+@pytest.mark.parametrize("planar", [True, False])
+@pytest.mark.parametrize("order", [abi.CIRCULAR_NEWEST_FIRST, abi.CIRCULAR_OLDEST_FIRST])
+def test_updates_equal_the_reference_divergent_kernel(fkb_lib, planar, order):
+    torch = pytest.importorskip("torch")
+    batch, dw, dh = 6, 70, 45           # the reference unit is built for BATCH = 6
+    rng = np.random.default_rng(700)
+    frames = [torch.from_numpy(rng.integers(0, 256, (540, 960 * 3), dtype=np.uint8)).cuda() for _ in range(3)]
+    rects = chains.random_rects(rng, 15, 960, 540, lo=10, hi=400)
+    dst_fmt = abi.DST_F32_PLANAR3 if planar else abi.DST_F32X3_PACKED
+    shape = (batch, 3, dh, dw) if planar else (batch, dh, dw, 3)
+    ours_v, ours_h, ref_v, ref_h = (torch.zeros(shape, dtype=torch.float32, device="cuda") for _ in range(4))
+    ct = abi.CircularTensor(dw, dh, batch, dst_fmt, order, False, ours_v.data_ptr(), ours_h.data_ptr())
+    stream = torch.cuda.Stream()
+    refgpu.set_stream(stream.cuda_stream, "nofma")
+    bg = (0.5, 0.25, 0.125)
+    for k in range(15):
+        rect = tuple(int(v) for v in rects[k])
+        plan = abi.HostPlan()
+        seq = plan.add_sequence(abi.SRC_U8X3, dst_fmt, abi.RESIZE_PRESERVE_AR, chains.normalize_ops(), background=bg)
+        plan.add_plane(src=frames[k % 3].data_ptr(), src_width=960, src_height=540, src_pitch=2880, crop=rect, dst=0, dst_width=dw,
+                       dst_height=dh, dst_pitch=0, sequence=seq)
+        first = ct.next_index
+        assert first == k % batch
+        ct.update(plan, stream.cuda_stream)
+        refgpu.circular_update6(frames[k % 3].data_ptr(), 960, 540, 2880, rect, dw, dh, bg, 255.0, chains.IMAGENET_MEAN, chains.IMAGENET_STD,
+                                ref_v.data_ptr(), ref_h.data_ptr(), first, order, planar, flavour="nofma")
+        assert abi.async_check(stream.cuda_stream) == 0
+        assert torch.equal(ours_v.view(torch.int32), ref_v.view(torch.int32)), f"update {k}: visible tensor differs"
+        assert torch.equal(ours_h.view(torch.int32), ref_h.view(torch.int32)), f"update {k}: hidden ring differs"
+    assert ours_v.abs().sum().item() > 0
     ct.destroy()

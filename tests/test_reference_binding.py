@@ -125,6 +125,35 @@ def test_nv21_left_tsplit_and_partly_filled_batches_lower_to_the_harness_plans(f
     assert [(p.dst_width, p.dst_height, p.dst - out) for p in planes] == [(64, 32, i * 64 * 32 * 12) for i in range(4)]
 
 
+def test_circular_tensor_update_sequences_lower_to_the_library_plan(fkb_lib):
+    """The two operation sequences of CircularTensor::update (core/data/circular_tensor.h:121-134), lowered by the
+    Executor<DivergentBatchTransformDPP> of the binding, give the planes fkb_circular_tensor_plan_update gives."""
+    frame, visible, hidden = 0x10000000, 0x20000000, 0x30000000
+    dw, dh, bg = 70, 45, (0.5, 0.25, 0.125)
+    for order in (abi.CIRCULAR_NEWEST_FIRST, abi.CIRCULAR_OLDEST_FIRST):
+        ct = abi.CircularTensor(dw, dh, 6, abi.DST_F32_PLANAR3, order, False, visible, hidden)
+        for first in range(8):
+            rect = (3 + first, 5, 200 + 7 * first, 100)
+            chain = abi.HostPlan()
+            seq = chain.add_sequence(abi.SRC_U8X3, abi.DST_F32_PLANAR3, abi.RESIZE_PRESERVE_AR, chains.normalize_ops(), background=bg)
+            chain.add_plane(src=frame, src_width=960, src_height=540, src_pitch=2880, crop=rect, dst=0, dst_width=dw, dst_height=dh,
+                            dst_pitch=0, sequence=seq)
+            assert ct.next_index == first % 6
+            want = ct.plan_update(chain)
+            bc.circular_describe6(order, frame, 960, 540, 2880, rect, dw, dh, bg, 255.0, chains.IMAGENET_MEAN, chains.IMAGENET_STD,
+                                  visible, hidden, first % 6)
+            planes, seqs = bc.last_plan()
+            assert len(planes) == 7 and len(seqs) == 2
+            key = lambda p, q: (p.src, p.src_width, p.src_height, p.src_pitch, p.crop_x, p.crop_y, p.crop_width, p.crop_height, p.dst,
+                                p.dst_width, p.dst_height, p.dst_pitch, p.dst_channel_stride, q.src_format, q.dst_format, q.resize_mode,
+                                q.n_ops, tuple(q.background))
+            d = want.desc()
+            ours = sorted(key(p, d.sequences[p.sequence]) for p in want.planes)
+            theirs = sorted(key(p, seqs[p.sequence][0]) for p in planes)
+            assert ours == theirs, (order, first)
+        ct.destroy()
+
+
 READBACK_RECT = (-7, -5, 60, 37)
 AFFINE = (0.8, 0.25, -3.0, -0.2, 0.7, 2.5, 0.0, 0.0, 1.0)
 PERSPECTIVE = (0.9, 0.1, -2.0, 0.05, 0.8, 1.0, 0.002, 0.001, 1.0)
@@ -152,6 +181,50 @@ def test_border_reader_warping_and_deinterlace_lower_to_the_harness_plans(fkb_li
     for k in (1, 2, 3):
         bc.deinterlace(bc.DESCRIBE, src, 40, 24, 120, k, (1.0, 0.5, 2.0), out)
         _assert_same_plan(_readback_plan(src, out, 40, 24, 40, 24, abi.RESIZE_NONE, mul, deinterlace=k), fkb_lib)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("order", [abi.CIRCULAR_NEWEST_FIRST, abi.CIRCULAR_OLDEST_FIRST])
+def test_the_reference_circular_tensor_class_updates_through_the_binding(fkb_lib, order):
+    """fk::CircularTensor::update, compiled from the reference's header, against fkb_circular_tensor_update and - where the
+    reference CUDA build is present - against the reference's own divergent kernel."""
+    torch = pytest.importorskip("torch")
+    from oracle import reference_gpu as refgpu
+    from tests import cases as tc
+    dw, dh, batch, bg = 70, 45, 6, (0.5, 0.25, 0.125)
+    rng = np.random.default_rng(305)
+    frames = [torch.from_numpy(rng.integers(0, 256, (540, 960 * 3), dtype=np.uint8)).cuda() for _ in range(3)]
+    rects = chains.random_rects(rng, 14, 960, 540, lo=10, hi=400)
+    stream = torch.cuda.Stream()
+    theirs = bc.ReferenceCircularTensor(order, dw, dh)
+    ours = abi.CircularTensor(dw, dh, batch, abi.DST_F32_PLANAR3, order)
+    use_kernel = refgpu.available("nofma")
+    ref_v, ref_h = (torch.zeros((batch, 3, dh, dw), dtype=torch.float32, device="cuda") for _ in range(2))
+    if use_kernel:
+        refgpu.set_stream(stream.cuda_stream, "nofma")
+    a, b = np.empty((batch, 3, dh, dw), np.float32), np.empty((batch, 3, dh, dw), np.float32)
+    for k in range(14):
+        rect = tuple(int(v) for v in rects[k])
+        chain = abi.HostPlan()
+        seq = chain.add_sequence(abi.SRC_U8X3, abi.DST_F32_PLANAR3, abi.RESIZE_PRESERVE_AR, chains.normalize_ops(), background=bg)
+        chain.add_plane(src=frames[k % 3].data_ptr(), src_width=960, src_height=540, src_pitch=2880, crop=rect, dst=0, dst_width=dw,
+                        dst_height=dh, dst_pitch=0, sequence=seq)
+        ours.update(chain, stream.cuda_stream)
+        theirs.update(frames[k % 3].data_ptr(), 960, 540, 2880, rect, bg, 255.0, chains.IMAGENET_MEAN, chains.IMAGENET_STD, stream.cuda_stream)
+        if use_kernel:
+            refgpu.circular_update6(frames[k % 3].data_ptr(), 960, 540, 2880, rect, dw, dh, bg, 255.0, chains.IMAGENET_MEAN, chains.IMAGENET_STD,
+                                    ref_v.data_ptr(), ref_h.data_ptr(), k % batch, order, True, flavour="nofma")
+        assert abi.async_check(stream.cuda_stream) == 0
+        tc.cuda_copy_to_host(a, ours.data)
+        tc.cuda_copy_to_host(b, theirs.data)
+        # planes that no update has reached yet hold whatever the reference's allocation held: compare the ones written
+        written = min(k + 1, batch)
+        sel = slice(0, written) if order == abi.CIRCULAR_NEWEST_FIRST else slice(batch - written, batch)
+        assert np.array_equal(tc.bits(a[sel]), tc.bits(b[sel])), f"update {k}"
+        if use_kernel:
+            assert np.array_equal(tc.bits(b[sel]), tc.bits(ref_v.cpu().numpy()[sel])), f"update {k}: differs from the reference kernel"
+    theirs.destroy()
+    ours.destroy()
 
 
 @pytest.mark.gpu
