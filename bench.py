@@ -379,6 +379,16 @@ class Divergent(Workload):
         rg.cast_resize_batch16(p[48:64], w, h, w * 3, w // 2, h // 2, ptr("g3"))
         return True
 
+    def reference_gpu_one_launch(self, ptr, s=0):
+        """The reference's divergent kernel (executor_kernels.h:20-23) launched directly with the four sequences."""
+        from oracle import reference_gpu as rg
+        if self.pg != 16:
+            return False
+        w, h = self.w, self.h
+        rg.divergent_four_groups64([ptr(f"img{i}") for i in range(64)], w, h, w * 3, 1.4, 0.5, 0.5, 255.0, w // 2, h // 2,
+                                   ptr("g0"), ptr("g1"), ptr("g2"), ptr("g3"))
+        return True
+
 
 def make_workload(name: str, seed: int) -> Workload:
     if name == "c3":
@@ -593,10 +603,19 @@ def reference_gpu_record(torch, stream, dw: DeviceWorkload, steps, warmup):
     per, total = time_launches(torch, stream, dw.reference_gpu, steps, warmup)
     launches = (rg.launches() - n0) / (steps + warmup)
     ms = total / steps
-    return {"ms_per_step": ms, "value": dw.wl.out_pixels / (ms * 1e-3) / 1e6, "unit": "Mpix/s",
-            "launches_per_step": launches,
-            "what": "launchTransformDPP_Kernel from the reference's headers, nvcc -O3 sm_100a, default flags; batches in "
-                    "chunks of at most 128 planes per launch (its per-plane parameters are kernel arguments)"}
+    rec = {"ms_per_step": ms, "value": dw.wl.out_pixels / (ms * 1e-3) / 1e6, "unit": "Mpix/s",
+           "launches_per_step": launches,
+           "what": "launchTransformDPP_Kernel from the reference's headers, nvcc -O3 sm_100a, default flags; batches in "
+                   "chunks of at most 128 planes per launch (its per-plane parameters are kernel arguments)"}
+    if hasattr(dw.wl, "reference_gpu_one_launch"):
+        d = dw.sets[0]
+        one = lambda i: dw.wl.reference_gpu_one_launch(lambda n: d[n].data_ptr(), 0)
+        if one(0):
+            _, total = time_launches(torch, stream, one, steps, warmup)
+            rec["one_divergent_launch_ms"] = total / steps
+            rec["one_divergent_launch_what"] = ("launchDivergentBatchTransformDPP_Kernel launched directly with the four sequences "
+                                                "(the reference ships the kernel without a host launcher)")
+    return rec
 
 
 def call_overhead(torch, stream, dw: DeviceWorkload, calls: int = 200):

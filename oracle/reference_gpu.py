@@ -130,3 +130,11 @@ def circular_update6(frame, w, h, pitch, rect, dw, dh, bg, d0, mean, std, visibl
     fn = lib(flavour).fklref_gpu_circular_update_planar6 if planar else lib(flavour).fklref_gpu_circular_update_packed6
     if fn(_p(frame), w, h, pitch, r, dw, dh, _f3(bg), _f3(d0), _f3(mean), _f3(std), _p(visible), _p(hidden), int(first), int(order)) != 0:
         raise RuntimeError("the reference's divergent kernel did not launch")
+
+
+def divergent_four_groups64(srcs, w, h, pitch, mul, sub, add, div, dw, dh, g0, g1, g2, g3, flavour="default"):
+    """Configuration 5B as one launch of the reference's divergent kernel (oracle/ref/fklref_circular.cpp): 64 images, four
+    chains on four groups of 16; g0..g3 are the groups' dense output tensors."""
+    if lib(flavour).fklref_gpu_divergent_four_groups64(_ptrs(srcs), w, h, pitch, _f3(mul), _f3(sub), _f3(add), _f3(div), dw, dh,
+                                                       _p(g0), _p(g1), _p(g2), _p(g3)) != 0:
+        raise RuntimeError("the reference's divergent kernel did not launch")

@@ -197,3 +197,9 @@ def test_config5_long_chain_and_divergent_groups(fkb_lib):
     for g in range(4):
         assert _same(got["nofma"][g], cpu[g]), f"group {g}: reference CUDA vs reference CPU"
         assert _same(got["ours"][g], cpu[g]), f"group {g}: this package vs reference CPU"
+    # the same four chains as ONE launch of the reference's divergent kernel (it ships without a host launcher)
+    o = outputs()
+    refgpu.divergent_four_groups64(p, w, h, w * 3, 1.4, 0.5, 0.5, 255.0, w // 2, h // 2, *[t.data_ptr() for t in o], flavour="nofma")
+    torch.cuda.synchronize()
+    for g in range(4):
+        assert _same(o[g].cpu().numpy(), cpu[g]), f"group {g}: the reference's divergent kernel vs reference CPU"
