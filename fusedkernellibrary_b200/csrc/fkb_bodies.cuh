@@ -1033,6 +1033,34 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
     const uint32_t second_b = axb.i1 == axb.i0 ? 0x3210u : 0x3543u;
     const float2 wx0 = make_float2(axa.w0, axb.w0), wx1 = make_float2(axa.w1, axb.w1);
 
+    /* Stores that need no source byte: the default value to the left and right of this band's rows and, for a plane
+       with few rows outside its region (no store-only items), those rows by its last band.  The planar receiver does
+       them before it waits for the band's copies, the packed one after its pixels (measured: 1024 crops into planar
+       224x224 158.3 -> 154.3 us with the stores first, 8190 crops into packed 60x60 91.4 -> 95.1 us). */
+    auto fill_background = [&]() {
+        const uint32_t n_side = groups_per_row - n_groups;
+        if (n_side != 0) {
+            const uint32_t total = (uint32_t)(yb - ya + 1) * n_side;
+            CellWalk w(threadIdx.x, nthreads, n_side, total > nthreads);
+#pragma unroll 1
+            for (uint32_t idx = threadIdx.x; idx < total; idx += nthreads, w.advance()) {
+                const uint32_t g = w.c < g_lo ? w.c : w.c + n_groups;
+                store_group<PLANAR>(dst, dst_pitch, dst_cstride, (int)(g * PX_PER_THREAD), ya + (int)w.r, bg4);
+            }
+        }
+        if (P.n_segs != 0 && local == P.roi_items - 1) {
+            const uint32_t total = (P.dst_h - n_rows) * groups_per_row;
+            CellWalk w(threadIdx.x, nthreads, groups_per_row, total > nthreads);
+#pragma unroll 1
+            for (uint32_t idx = threadIdx.x; idx < total; idx += nthreads, w.advance()) {
+                const int y = (int)w.r < y1 ? (int)w.r : (int)(w.r + n_rows);
+                store_group<PLANAR>(dst, dst_pitch, dst_cstride, (int)(w.c * PX_PER_THREAD), y, bg4);
+            }
+        }
+    };
+    constexpr bool early_fill = PLANAR;
+    if (early_fill) fill_background();
+
     const bool arrived = mbar_wait_bounded(mbar, 0, wc.limit_us);
     if (!arrived) {
         /* never expected: record it and give the copies one more bounded chance to land before
@@ -1121,27 +1149,7 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
         }
     }
 
-    /* background to the left and right of this band's rows */
-    const uint32_t n_side = groups_per_row - n_groups;
-    if (n_side != 0) {
-        const uint32_t total = (uint32_t)(yb - ya + 1) * n_side;
-        CellWalk w(threadIdx.x, nthreads, n_side, total > nthreads);
-#pragma unroll 1
-        for (uint32_t idx = threadIdx.x; idx < total; idx += nthreads, w.advance()) {
-            const uint32_t g = w.c < g_lo ? w.c : w.c + n_groups;
-            store_group<PLANAR>(dst, dst_pitch, dst_cstride, (int)(g * PX_PER_THREAD), ya + (int)w.r, bg4);
-        }
-    }
-    /* a plane with few rows outside its region has no store-only items: its last band fills them */
-    if (P.n_segs != 0 && local == P.roi_items - 1) {
-        const uint32_t total = (P.dst_h - n_rows) * groups_per_row;
-        CellWalk w(threadIdx.x, nthreads, groups_per_row, total > nthreads);
-#pragma unroll 1
-        for (uint32_t idx = threadIdx.x; idx < total; idx += nthreads, w.advance()) {
-            const int y = (int)w.r < y1 ? (int)w.r : (int)(w.r + n_rows);
-            store_group<PLANAR>(dst, dst_pitch, dst_cstride, (int)(w.c * PX_PER_THREAD), y, bg4);
-        }
-    }
+    if (!early_fill) fill_background();
 }
 
 /* ------------------------------------------------------------------------------------ */
