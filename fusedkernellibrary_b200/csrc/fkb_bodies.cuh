@@ -713,6 +713,48 @@ __device__ __forceinline__ void store_pixel_at(uint8_t* d, uint32_t cstride, flo
     }
 }
 
+/* Default value over cells of the output, a walk of `step` threads starting at cell `first`.  A planar cell is a group
+ * of four pixels (one 16-byte word in each channel plane); a packed cell is one of the group's three 16-byte words, so
+ * that the words a warp stores with one instruction lie side by side (a thread that stores the three words of its own
+ * four pixels leaves every 32-byte sector to two instructions: 3.8 against 6.7 TB/s on a batch of nothing but default
+ * planes).  Rows are `groups_per_row` groups long after `skip_groups` groups from group `skip_lo` on have been left
+ * out (the region of interest); row_of(r) is the output row of the walk's r-th row.  `groups` bounds a thread's share,
+ * counted in groups. */
+template <bool PLANAR, typename RowOf>
+__device__ __forceinline__ void fill_cells(uint8_t* dst, uint32_t pitch, uint32_t cstride, uint32_t first_group, uint32_t lane_in_walk,
+                                           uint32_t step, uint32_t groups, uint32_t rows, uint32_t groups_per_row, uint32_t skip_lo,
+                                           uint32_t skip_groups, const float (&bg)[3], RowOf row_of) {
+    constexpr uint32_t UNITS = PLANAR ? 1u : 3u;
+    const uint32_t per_row = groups_per_row * UNITS, total = rows * per_row, lo = skip_lo * UNITS, skip = skip_groups * UNITS;
+    uint32_t idx = first_group * UNITS + lane_in_walk;
+    const uint32_t iters = groups * UNITS;
+    CellWalk w(idx, step, per_row, total > step);
+#pragma unroll 1
+    for (uint32_t k = 0; k < iters && idx < total; ++k, idx += step, w.advance()) {
+        const uint32_t c = w.c < lo ? w.c : w.c + skip;
+        uint8_t* const d = dst + (size_t)row_of(w.r) * pitch + (size_t)c * 16u;
+        if (PLANAR) {
+#pragma unroll
+            for (int ch = 0; ch < 3; ++ch) *reinterpret_cast<float4*>(d + (size_t)ch * cstride) = make_float4(bg[ch], bg[ch], bg[ch], bg[ch]);
+        } else { /* word c of a row holds the channels (c, c+1, c+2, c) mod 3 */
+            const uint32_t k3 = c % 3u;
+            const float a = k3 == 0 ? bg[0] : k3 == 1 ? bg[1] : bg[2];
+            const float b = k3 == 0 ? bg[1] : k3 == 1 ? bg[2] : bg[0];
+            const float e = k3 == 0 ? bg[2] : k3 == 1 ? bg[0] : bg[1];
+            *reinterpret_cast<float4*>(d) = make_float4(a, b, e, a);
+        }
+    }
+}
+
+/* One row of a warp's 32 side-by-side packed float3 pixels: every lane leaves its pixel in the warp's buffer, then lanes
+ * 0..23 store the 384 bytes as whole 16-byte words.  `words` = how many of the 24 words are inside the row piece. */
+__device__ __forceinline__ void turn_put(float* buf, uint32_t lane, float a, float b, float c) {
+    buf[3u * lane] = a; buf[3u * lane + 1u] = b; buf[3u * lane + 2u] = c;
+}
+__device__ __forceinline__ void turn_flush(const float* buf, uint32_t lane, uint32_t words, uint8_t* run) {
+    if (lane < words) reinterpret_cast<float4*>(run)[lane] = reinterpret_cast<const float4*>(buf)[lane];
+}
+
 template <uint32_t CHAIN, int SRC, bool PLANAR>
 __device__ __forceinline__ void body_resize(const DevPlane& P, const DevSeq& S, const OpSlot* sops, uint32_t local) {
     /* plane fields used inside loops, copied out of shared memory once */
@@ -731,20 +773,12 @@ __device__ __forceinline__ void body_resize(const DevPlane& P, const DevSeq& S, 
        after the continuation (resize.h:84-86), evaluated once when the plan was made */
     const float bgv[3] = {S.bg_out[0], S.bg_out[1], S.bg_out[2]};
     const float2 one = dup2(S.one);
-    float bg4[12];
-#pragma unroll
-    for (int i = 0; i < PX_PER_THREAD; ++i) { bg4[3 * i] = bgv[0]; bg4[3 * i + 1] = bgv[1]; bg4[3 * i + 2] = bgv[2]; }
 
     if (local >= P.roi_items) {
         /* store-only item: rows above and below the region of interest */
-        const uint32_t total = (P.dst_h - n_rows) * groups_per_row;
-        uint32_t idx = (local - P.roi_items) * (nthreads * BG_GROUPS_PER_THREAD) + threadIdx.x;
-        CellWalk w(idx, nthreads, groups_per_row);
-#pragma unroll 1
-        for (int k = 0; k < BG_GROUPS_PER_THREAD && idx < total; ++k, idx += nthreads, w.advance()) {
-            const int y = (int)w.r < y1 ? (int)w.r : (int)(w.r + n_rows);
-            store_group<PLANAR>(dst, dst_pitch, dst_cstride, (int)(w.c * PX_PER_THREAD), y, bg4);
-        }
+        fill_cells<PLANAR>(dst, dst_pitch, dst_cstride, (local - P.roi_items) * (nthreads * BG_GROUPS_PER_THREAD), threadIdx.x, nthreads,
+                           BG_GROUPS_PER_THREAD, P.dst_h - n_rows, groups_per_row, 0u, 0u, bgv,
+                           [&](uint32_t r) { return (int)r < y1 ? r : r + n_rows; });
         return;
     }
 
@@ -876,13 +910,8 @@ __device__ __forceinline__ void body_resize(const DevPlane& P, const DevSeq& S, 
     const uint32_t n_band = groups_per_row - n_groups;
     if (tile_x == 0 && n_band != 0) {
         const uint32_t rows_here = min(rs * RESIZE_ROWS_PER_THREAD, (uint32_t)(y2 - row0 + 1));
-        const uint32_t total = rows_here * n_band;
-#pragma unroll 1
-        for (uint32_t idx = threadIdx.x; idx < total; idx += nthreads) {
-            const uint32_t r = idx / n_band, b = idx - r * n_band;
-            const uint32_t g = b < g_lo ? b : b + n_groups;
-            store_group<PLANAR>(dst, dst_pitch, dst_cstride, (int)(g * PX_PER_THREAD), row0 + (int)r, bg4);
-        }
+        fill_cells<PLANAR>(dst, dst_pitch, dst_cstride, 0u, threadIdx.x, nthreads, 0xFFFFFFu, rows_here, n_band, g_lo, n_groups, bgv,
+                           [&](uint32_t r) { return (uint32_t)row0 + r; });
     }
 }
 
@@ -967,20 +996,12 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
        after the continuation (resize.h:84-86), evaluated once when the plan was made */
     const float bgv[3] = {S.bg_out[0], S.bg_out[1], S.bg_out[2]};
     const float2 one = dup2(S.one);
-    float bg4[12];
-#pragma unroll
-    for (int i = 0; i < PX_PER_THREAD; ++i) { bg4[3 * i] = bgv[0]; bg4[3 * i + 1] = bgv[1]; bg4[3 * i + 2] = bgv[2]; }
 
     if (local >= P.roi_items) {
         /* store-only item: rows above and below the region of interest */
-        const uint32_t total = (P.dst_h - n_rows) * groups_per_row;
-        uint32_t idx = (local - P.roi_items) * (nthreads * BG_GROUPS_PER_THREAD) + threadIdx.x;
-        CellWalk w(idx, nthreads, groups_per_row);
-#pragma unroll 1
-        for (int k = 0; k < BG_GROUPS_PER_THREAD && idx < total; ++k, idx += nthreads, w.advance()) {
-            const int y = (int)w.r < y1 ? (int)w.r : (int)(w.r + n_rows);
-            store_group<PLANAR>(dst, dst_pitch, dst_cstride, (int)(w.c * PX_PER_THREAD), y, bg4);
-        }
+        fill_cells<PLANAR>(dst, dst_pitch, dst_cstride, (local - P.roi_items) * (nthreads * BG_GROUPS_PER_THREAD), threadIdx.x, nthreads,
+                           BG_GROUPS_PER_THREAD, P.dst_h - n_rows, groups_per_row, 0u, 0u, bgv,
+                           [&](uint32_t r) { return (int)r < y1 ? r : r + n_rows; });
         return;
     }
 
@@ -1039,24 +1060,12 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
        224x224 158.3 -> 154.3 us with the stores first, 8190 crops into packed 60x60 91.4 -> 95.1 us). */
     auto fill_background = [&]() {
         const uint32_t n_side = groups_per_row - n_groups;
-        if (n_side != 0) {
-            const uint32_t total = (uint32_t)(yb - ya + 1) * n_side;
-            CellWalk w(threadIdx.x, nthreads, n_side, total > nthreads);
-#pragma unroll 1
-            for (uint32_t idx = threadIdx.x; idx < total; idx += nthreads, w.advance()) {
-                const uint32_t g = w.c < g_lo ? w.c : w.c + n_groups;
-                store_group<PLANAR>(dst, dst_pitch, dst_cstride, (int)(g * PX_PER_THREAD), ya + (int)w.r, bg4);
-            }
-        }
-        if (P.n_segs != 0 && local == P.roi_items - 1) {
-            const uint32_t total = (P.dst_h - n_rows) * groups_per_row;
-            CellWalk w(threadIdx.x, nthreads, groups_per_row, total > nthreads);
-#pragma unroll 1
-            for (uint32_t idx = threadIdx.x; idx < total; idx += nthreads, w.advance()) {
-                const int y = (int)w.r < y1 ? (int)w.r : (int)(w.r + n_rows);
-                store_group<PLANAR>(dst, dst_pitch, dst_cstride, (int)(w.c * PX_PER_THREAD), y, bg4);
-            }
-        }
+        if (n_side != 0)
+            fill_cells<PLANAR>(dst, dst_pitch, dst_cstride, 0u, threadIdx.x, nthreads, 0xFFFFFFu, (uint32_t)(yb - ya + 1), n_side, g_lo, n_groups, bgv,
+                               [&](uint32_t r) { return (uint32_t)ya + r; });
+        if (P.n_segs != 0 && local == P.roi_items - 1)
+            fill_cells<PLANAR>(dst, dst_pitch, dst_cstride, 0u, threadIdx.x, nthreads, 0xFFFFFFu, P.dst_h - n_rows, groups_per_row, 0u, 0u, bgv,
+                               [&](uint32_t r) { return (int)r < y1 ? r : r + n_rows; });
     };
     constexpr bool early_fill = PLANAR;
     if (early_fill) fill_background();
@@ -1193,20 +1202,12 @@ __device__ __forceinline__ void body_nv12_staged(const DevPlane& P, const DevSeq
     const uint32_t nthreads = blockDim.x, tid = threadIdx.x;
     const float bgv[3] = {S.bg_out[0], S.bg_out[1], S.bg_out[2]};
     const float2 one = dup2(S.one);
-    float bg4[12];
-#pragma unroll
-    for (int i = 0; i < PX_PER_THREAD; ++i) { bg4[3 * i] = bgv[0]; bg4[3 * i + 1] = bgv[1]; bg4[3 * i + 2] = bgv[2]; }
 
     if (local >= P.roi_items) {
         /* store-only item: rows above and below the region of interest */
-        const uint32_t total = (P.dst_h - n_rows) * groups_per_row;
-        uint32_t idx = (local - P.roi_items) * (nthreads * BG_GROUPS_PER_THREAD) + tid;
-        CellWalk w(idx, nthreads, groups_per_row);
-#pragma unroll 1
-        for (int k = 0; k < BG_GROUPS_PER_THREAD && idx < total; ++k, idx += nthreads, w.advance()) {
-            const int y = (int)w.r < y1 ? (int)w.r : (int)(w.r + n_rows);
-            store_group<PLANAR>(dst, dst_pitch, dst_cstride, (int)(w.c * PX_PER_THREAD), y, bg4);
-        }
+        fill_cells<PLANAR>(dst, dst_pitch, dst_cstride, (local - P.roi_items) * (nthreads * BG_GROUPS_PER_THREAD), tid, nthreads,
+                           BG_GROUPS_PER_THREAD, P.dst_h - n_rows, groups_per_row, 0u, 0u, bgv,
+                           [&](uint32_t r) { return (int)r < y1 ? r : r + n_rows; });
         return;
     }
 
@@ -1410,15 +1411,9 @@ __device__ __forceinline__ void body_nv12_staged(const DevPlane& P, const DevSeq
 
     /* background to the left and right of this band's rows (first column tile only) */
     const uint32_t n_side = groups_per_row - n_groups;
-    if (tile_x == 0 && n_side != 0) {
-        const uint32_t total = (uint32_t)(yb - ya + 1) * n_side;
-        CellWalk w(tid, nthreads, n_side, total > nthreads);
-#pragma unroll 1
-        for (uint32_t idx = tid; idx < total; idx += nthreads, w.advance()) {
-            const uint32_t g = w.c < g_lo ? w.c : w.c + n_groups;
-            store_group<PLANAR>(dst, dst_pitch, dst_cstride, (int)(g * PX_PER_THREAD), ya + (int)w.r, bg4);
-        }
-    }
+    if (tile_x == 0 && n_side != 0)
+        fill_cells<PLANAR>(dst, dst_pitch, dst_cstride, 0u, tid, nthreads, 0xFFFFFFu, (uint32_t)(yb - ya + 1), n_side, g_lo, n_groups, bgv,
+                           [&](uint32_t r) { return (uint32_t)ya + r; });
 }
 
 /* ------------------------------------------------------------------------------------ */
