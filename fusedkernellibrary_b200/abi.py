@@ -11,6 +11,7 @@ import os
 from pathlib import Path
 
 PKG_DIR = Path(__file__).resolve().parent
+CHECK_LIB_PATH = Path(__file__).resolve().parent / "lib" / "libfkb200_check.so"   # the bounds-checking build (tests only)
 LIB_PATH = PKG_DIR / "lib" / "libfkb200.so"
 
 # status codes -------------------------------------------------------------------------
@@ -21,6 +22,7 @@ ERR_CUDA = 3
 ERR_TOO_LARGE = 4
 ERR_NO_DEVICE = 5
 ERR_DEVICE_WAIT = 6
+ERR_DEVICE_BOUNDS = 7
 
 # vocabulary ---------------------------------------------------------------------------
 SRC_U8X3, SRC_F32X3, SRC_NV12, SRC_NV21 = 1, 2, 3, 4
@@ -33,7 +35,7 @@ PLANE_DEFAULT_VALUE = 1
 (OP_MUL, OP_SUB, OP_DIV, OP_ADD, OP_CAST_F32, OP_SWAP_RB, OP_SATURATE_CAST_U8,
  OP_YUV_TO_RGB_BT709_FULL, OP_CAST_I32, OP_CAST_U32) = range(1, 11)
 OP_YUV_TO_RGB_BT601_FULL, OP_YUV_TO_RGB_BT2020_FULL = 11, 12
-PLAN_WAIT_LIMIT_US, PLAN_TEST_EXPECT_EXTRA_BYTES = 1, 2
+PLAN_WAIT_LIMIT_US, PLAN_TEST_EXPECT_EXTRA_BYTES, PLAN_TEST_SHRINK_BOUNDS = 1, 2, 3
 DEFAULT_WAIT_LIMIT_US = 100000
 ASYNC_ARENA_BYTES = 8 * 1024 * 1024
 
@@ -223,7 +225,7 @@ EXPORTS = [
     "fkb_async_check", "fkb_debug_get_counters", "fkb_assign_planes", "fkb_multi_gpu_session_create",
     "fkb_multi_gpu_session_run", "fkb_multi_gpu_session_get_shard", "fkb_multi_gpu_session_destroy",
     "fkb_debug_set_device_unavailable", "fkb_circular_tensor_sizes", "fkb_circular_tensor_create", "fkb_circular_tensor_data",
-    "fkb_circular_tensor_next_index", "fkb_circular_tensor_plan_update", "fkb_circular_tensor_update", "fkb_circular_tensor_destroy",
+    "fkb_circular_tensor_next_index", "fkb_debug_bounds_checked", "fkb_circular_tensor_plan_update", "fkb_circular_tensor_update", "fkb_circular_tensor_destroy",
 ]
 
 

@@ -1,9 +1,12 @@
 """Builds libfkb200.so in-tree with nvcc for sm_100a (cross-compiles without a GPU).
 
-    python -m fusedkernellibrary_b200.build [--force] [--verbose]
+    python -m fusedkernellibrary_b200.build [--force] [--verbose] [--check]
 
 Every translation unit under csrc/ is compiled to an object file on its own (in parallel; only
-the stale ones) and the objects are linked into one shared library.
+the stale ones) and the objects are linked into one shared library.  --check builds
+libfkb200_check.so instead: the same sources with -DFKB_CHECK_BOUNDS, in which every access of a
+kernel to an image or to shared memory is compared with what its plane allows before it is made
+(tests only; see fkb_debug_bounds_checked in include/fkb200.h).
 """
 from __future__ import annotations
 
@@ -17,6 +20,8 @@ ROOT = PKG.parent
 CSRC = PKG / "csrc"
 OBJ = PKG / "lib" / "obj"
 OUT = PKG / "lib" / "libfkb200.so"
+OBJ_CHECK = PKG / "lib" / "obj_check"
+OUT_CHECK = PKG / "lib" / "libfkb200_check.so"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -42,21 +47,24 @@ def _stale(target: Path, deps: list[Path]) -> bool:
     return any(d.stat().st_mtime > t for d in deps)
 
 
-def needs_build() -> bool:
-    return _stale(OUT, sources() + _headers())
+def needs_build(check: bool = False) -> bool:
+    return _stale(OUT_CHECK if check else OUT, sources() + _headers())
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
-    if not force and not needs_build():
-        return OUT
-    OBJ.mkdir(parents=True, exist_ok=True)
+def build(force: bool = False, verbose: bool = False, check: bool = False) -> Path:
+    out, obj_dir = (OUT_CHECK, OBJ_CHECK) if check else (OUT, OBJ)
+    if not force and not needs_build(check):
+        return out
+    obj_dir.mkdir(parents=True, exist_ok=True)
     headers = _headers()
 
     def compile_one(src: Path):
-        obj = OBJ / (src.stem + ".o")
+        obj = obj_dir / (src.stem + ".o")
         if not force and not _stale(obj, [src] + headers):
             return obj, ""
         cmd = ["nvcc", *NVCC_FLAGS, f"-I{ROOT / 'include'}", f"-I{CSRC}"]
+        if check:
+            cmd += ["-DFKB_CHECK_BOUNDS"]
         if verbose:
             cmd += ["-Xptxas", "-v"]
         cmd += ["-c", str(src), "-o", str(obj)]
@@ -71,12 +79,12 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         for _, log in results:
             sys.stderr.write(log)
     objs = [str(o) for o, _ in results]
-    r = subprocess.run(["nvcc", *LINK_FLAGS, *objs, "-o", str(OUT)], capture_output=True, text=True)
+    r = subprocess.run(["nvcc", *LINK_FLAGS, *objs, "-o", str(out)], capture_output=True, text=True)
     if r.returncode != 0:
         sys.stderr.write(r.stdout + r.stderr)
-        raise RuntimeError("linking libfkb200.so failed")
-    return OUT
+        raise RuntimeError(f"linking {out.name} failed")
+    return out
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv, check="--check" in sys.argv))

@@ -303,6 +303,56 @@ __device__ __forceinline__ void run_ops_1(float (&v)[3], const OpSlot* __restric
 }
 
 /* ------------------------------------------------------------------------------------ */
+/* checked accesses                                                                     */
+/* ------------------------------------------------------------------------------------ */
+/* Every load from a source image goes through gld(), every store to a destination through gst(), every shared-memory
+ * access of the staged bodies through the lds helpers.  In the ordinary build they are the plain instruction.  Built
+ * with -DFKB_CHECK_BOUNDS (libfkb200_check.so, the stand-in for a memory checker) each access is first compared with
+ * what the block's plane allows - the source image's rows, the destination's rows (row by row: padding between rows
+ * counts as outside), the block's shared memory - and an access outside is NOT made: the plan's status word receives
+ * STATUS_BOUNDS_* and the access is skipped (a load gives zero), so that nothing faults and the host reads the
+ * status like that of a wait that ran out. */
+#ifdef FKB_CHECK_BOUNDS
+struct CheckCtx {
+    const uint8_t* src_lo; const uint8_t* src_hi;   /* all rows of the source image (luma and chroma for NV12) */
+    uint8_t* dst;                                   /* first byte of the destination plane (or column tile) */
+    uint32_t dst_pitch, dst_rows, dst_row_bytes, dst_cstride, dst_channels;
+    uint32_t smem_lo, smem_hi;                      /* the block's dynamic shared memory, as shared-window addresses */
+    uint32_t* status;
+};
+static __shared__ CheckCtx s_check;
+__device__ __forceinline__ bool check_fail(uint32_t code) { atomicMax(s_check.status, code); return false; }
+__device__ __forceinline__ bool check_src(const void* p, uint32_t n) {
+    const uint8_t* b = static_cast<const uint8_t*>(p);
+    return (b >= s_check.src_lo && b + n <= s_check.src_hi) ? true : check_fail(STATUS_BOUNDS_SOURCE);
+}
+__device__ __forceinline__ bool check_dst(const void* p, uint32_t n) {
+    const uint8_t* b = static_cast<const uint8_t*>(p);
+    if (b < s_check.dst) return check_fail(STATUS_BOUNDS_DESTINATION);
+    size_t off = (size_t)(b - s_check.dst);
+    if (s_check.dst_channels > 1) { /* planar: channel planes dst_cstride apart */
+        const size_t ch = off / s_check.dst_cstride;
+        if (ch >= s_check.dst_channels) return check_fail(STATUS_BOUNDS_DESTINATION);
+        off -= ch * s_check.dst_cstride;
+    }
+    if (s_check.dst_pitch == s_check.dst_row_bytes) /* dense rows: one run of bytes, a 16-byte word may straddle two rows */
+        return off + n <= (size_t)s_check.dst_rows * s_check.dst_pitch ? true : check_fail(STATUS_BOUNDS_DESTINATION);
+    const size_t row = off / s_check.dst_pitch, in_row = off - row * s_check.dst_pitch;
+    return (row < s_check.dst_rows && in_row + n <= s_check.dst_row_bytes) ? true : check_fail(STATUS_BOUNDS_DESTINATION);
+}
+__device__ __forceinline__ bool check_smem(uint32_t addr, uint32_t n) {
+    return (addr >= s_check.smem_lo && addr + n <= s_check.smem_hi) ? true : check_fail(STATUS_BOUNDS_SHARED);
+}
+template <typename T> __device__ __forceinline__ T gld(const T* p) { return check_src(p, (uint32_t)sizeof(T)) ? __ldg(p) : T{}; }
+template <typename T> __device__ __forceinline__ void gst(T* p, const T& v) { if (check_dst(p, (uint32_t)sizeof(T))) *p = v; }
+#else
+template <typename T> __device__ __forceinline__ T gld(const T* p) { return __ldg(p); }
+template <typename T> __device__ __forceinline__ void gst(T* p, const T& v) { *p = v; }
+__device__ __forceinline__ bool check_src(const void*, uint32_t) { return true; }
+__device__ __forceinline__ bool check_smem(uint32_t, uint32_t) { return true; }
+#endif
+
+/* ------------------------------------------------------------------------------------ */
 /* reads                                                                                */
 /* ------------------------------------------------------------------------------------ */
 
@@ -316,17 +366,17 @@ __device__ __forceinline__ void read_tap(const DevPlane& P, int a, int b, float&
     const int x = a + P.crop_x, y = b + P.crop_y;
     if (SRC == FKB_SRC_U8X3) {
         const uint8_t* p = P.src + (size_t)y * P.src_pitch + (size_t)x * 3;
-        r0 = u8_to_float(__ldg(p)); r1 = u8_to_float(__ldg(p + 1)); r2 = u8_to_float(__ldg(p + 2));
+        r0 = u8_to_float(gld(p)); r1 = u8_to_float(gld(p + 1)); r2 = u8_to_float(gld(p + 2));
     } else if (SRC == FKB_SRC_F32X3) {
         const float* p = reinterpret_cast<const float*>(P.src + (size_t)y * P.src_pitch + (size_t)x * 12);
-        r0 = __ldg(p); r1 = __ldg(p + 1); r2 = __ldg(p + 2);
+        r0 = gld(p); r1 = gld(p + 1); r2 = gld(p + 2);
     } else {
         const uint8_t* luma = P.src + (size_t)y * P.src_pitch + (size_t)x;
         const uint8_t* chroma = P.src + (size_t)P.src_pitch * P.src_height + (size_t)(y >> 1) * P.src_pitch +
                                 (size_t)(x >> 1) * 2;
-        r0 = u8_to_float(__ldg(luma));
-        r1 = u8_to_float(__ldg(chroma + (swap_uv ? 1 : 0))); /* NV21 stores the pair as V,U (color_conversion.h:357-359) */
-        r2 = u8_to_float(__ldg(chroma + (swap_uv ? 0 : 1)));
+        r0 = u8_to_float(gld(luma));
+        r1 = u8_to_float(gld(chroma + (swap_uv ? 1 : 0))); /* NV21 stores the pair as V,U (color_conversion.h:357-359) */
+        r2 = u8_to_float(gld(chroma + (swap_uv ? 0 : 1)));
     }
 }
 
@@ -391,10 +441,10 @@ __device__ __forceinline__ int border_index(int mode, int i, int n) {
 __device__ __forceinline__ void read_image(const DevSeq& S, const DevPlane& P, int x, int y, float (&r)[3]) {
     if (S.src_format == FKB_SRC_U8X3) {
         const uint8_t* p = P.src + (size_t)y * P.src_pitch + (size_t)x * 3;
-        r[0] = u8_to_float(__ldg(p)); r[1] = u8_to_float(__ldg(p + 1)); r[2] = u8_to_float(__ldg(p + 2));
+        r[0] = u8_to_float(gld(p)); r[1] = u8_to_float(gld(p + 1)); r[2] = u8_to_float(gld(p + 2));
     } else {
         const float* p = reinterpret_cast<const float*>(P.src + (size_t)y * P.src_pitch + (size_t)x * 12);
-        r[0] = __ldg(p); r[1] = __ldg(p + 1); r[2] = __ldg(p + 2);
+        r[0] = gld(p); r[1] = gld(p + 1); r[2] = gld(p + 2);
     }
 }
 
@@ -503,16 +553,15 @@ __device__ __forceinline__ void body_generic(const DevPlane& P, const DevSeq& S,
        :203-219 (TensorSplit) */
     if (S.dst_format == FKB_DST_F32X3_PACKED) {
         float* p = reinterpret_cast<float*>(P.dst + (size_t)y * P.dst_pitch + (size_t)x * 12);
-        p[0] = v[0]; p[1] = v[1]; p[2] = v[2];
+        gst(p, v[0]); gst(p + 1, v[1]); gst(p + 2, v[2]);
     } else if (S.dst_format == FKB_DST_F32_PLANAR3) {
 #pragma unroll
         for (int c = 0; c < 3; ++c) {
-            *reinterpret_cast<float*>(P.dst + (size_t)c * P.dst_cstride + (size_t)y * P.dst_pitch + (size_t)x * 4) =
-                v[c];
+            gst(reinterpret_cast<float*>(P.dst + (size_t)c * P.dst_cstride + (size_t)y * P.dst_pitch + (size_t)x * 4), v[c]);
         }
     } else {
         uint8_t* p = P.dst + (size_t)y * P.dst_pitch + (size_t)x * 3;
-        p[0] = (uint8_t)v[0]; p[1] = (uint8_t)v[1]; p[2] = (uint8_t)v[2];
+        gst(p, (uint8_t)v[0]); gst(p + 1, (uint8_t)v[1]); gst(p + 2, (uint8_t)v[2]);
     }
 }
 
@@ -558,12 +607,12 @@ __device__ __forceinline__ void body_flat(const DevPlane& P, const DevSeq& S, co
             if constexpr (SRC_IS_U8) {
                 const uint32_t* s4 = reinterpret_cast<const uint32_t*>(src);
 #pragma unroll
-                for (int k = 0; k < 3; ++k) raw[r][k] = __ldg(s4 + k);
+                for (int k = 0; k < 3; ++k) raw[r][k] = gld(s4 + k);
             } else {
                 const uint4* s4 = reinterpret_cast<const uint4*>(src);
 #pragma unroll
                 for (int k = 0; k < 3; ++k) {
-                    const uint4 w = __ldg(s4 + k);
+                    const uint4 w = gld(s4 + k);
                     raw[r][4 * k + 0] = w.x; raw[r][4 * k + 1] = w.y; raw[r][4 * k + 2] = w.z; raw[r][4 * k + 3] = w.w;
                 }
             }
@@ -574,8 +623,8 @@ __device__ __forceinline__ void body_flat(const DevPlane& P, const DevSeq& S, co
 #pragma unroll
             for (int i = 0; i < 12; ++i) {
                 if (i < (int)n[r] * 3) {
-                    if constexpr (SRC_IS_U8) raw[r][i / 4] |= (uint32_t)__ldg(src + i) << (8 * (i % 4));
-                    else raw[r][i] = __ldg(reinterpret_cast<const uint32_t*>(src) + i);
+                    if constexpr (SRC_IS_U8) raw[r][i / 4] |= (uint32_t)gld(src + i) << (8 * (i % 4));
+                    else raw[r][i] = gld(reinterpret_cast<const uint32_t*>(src) + i);
                 }
             }
         }
@@ -629,19 +678,19 @@ __device__ __forceinline__ void body_flat(const DevPlane& P, const DevSeq& S, co
                 __syncwarp();
                 OutWord* const warp_dst = reinterpret_cast<OutWord*>(dst) - lane * 3;
 #pragma unroll
-                for (int k = 0; k < 3; ++k) warp_dst[k * 32 + lane] = my_turn[k * 32 + lane];
+                for (int k = 0; k < 3; ++k) gst(warp_dst + (k * 32 + lane), my_turn[k * 32 + lane]);
                 __syncwarp();
             } else {
                 OutWord* d4 = reinterpret_cast<OutWord*>(dst);
 #pragma unroll
-                for (int k = 0; k < 3; ++k) d4[k] = w[k];
+                for (int k = 0; k < 3; ++k) gst(d4 + k, w[k]);
             }
         } else {
 #pragma unroll
             for (int i = 0; i < 12; ++i) {
                 if (i < (int)n[r] * 3) {
-                    if (DST_IS_U8) dst[i] = (uint8_t)v[i];
-                    else reinterpret_cast<float*>(dst)[i] = v[i];
+                    if (DST_IS_U8) gst(dst + i, (uint8_t)v[i]);
+                    else gst(reinterpret_cast<float*>(dst) + i, v[i]);
                 }
             }
         }
@@ -676,12 +725,12 @@ __device__ __forceinline__ void store_group(uint8_t* dst, uint32_t pitch, uint32
         uint8_t* d = dst + (size_t)y * pitch + (size_t)x0 * 4;
 #pragma unroll
         for (int c = 0; c < 3; ++c) {
-            *reinterpret_cast<float4*>(d + (size_t)c * cstride) = make_float4(v[c], v[3 + c], v[6 + c], v[9 + c]);
+            gst(reinterpret_cast<float4*>(d + (size_t)c * cstride), make_float4(v[c], v[3 + c], v[6 + c], v[9 + c]));
         }
     } else {
         float4* d = reinterpret_cast<float4*>(dst + (size_t)y * pitch + (size_t)x0 * 12);
 #pragma unroll
-        for (int k = 0; k < 3; ++k) d[k] = make_float4(v[4 * k + 0], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
+        for (int k = 0; k < 3; ++k) gst(d + k, make_float4(v[4 * k + 0], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]));
     }
 }
 
@@ -691,12 +740,12 @@ __device__ __forceinline__ void store_pixel(uint8_t* dst, uint32_t pitch, uint32
                                             float b, float c) {
     if (PLANAR) {
         uint8_t* d = dst + (size_t)y * pitch + (size_t)x * 4;
-        *reinterpret_cast<float*>(d) = a;
-        *reinterpret_cast<float*>(d + (size_t)cstride) = b;
-        *reinterpret_cast<float*>(d + 2 * (size_t)cstride) = c;
+        gst(reinterpret_cast<float*>(d), a);
+        gst(reinterpret_cast<float*>(d + (size_t)cstride), b);
+        gst(reinterpret_cast<float*>(d + 2 * (size_t)cstride), c);
     } else {
         float* d = reinterpret_cast<float*>(dst + (size_t)y * pitch + (size_t)x * 12);
-        d[0] = a; d[1] = b; d[2] = c;
+        gst(d, a); gst(d + 1, b); gst(d + 2, c);
     }
 }
 
@@ -704,12 +753,12 @@ __device__ __forceinline__ void store_pixel(uint8_t* dst, uint32_t pitch, uint32
 template <bool PLANAR>
 __device__ __forceinline__ void store_pixel_at(uint8_t* d, uint32_t cstride, float a, float b, float c) {
     if (PLANAR) {
-        *reinterpret_cast<float*>(d) = a;
-        *reinterpret_cast<float*>(d + (size_t)cstride) = b;
-        *reinterpret_cast<float*>(d + 2 * (size_t)cstride) = c;
+        gst(reinterpret_cast<float*>(d), a);
+        gst(reinterpret_cast<float*>(d + (size_t)cstride), b);
+        gst(reinterpret_cast<float*>(d + 2 * (size_t)cstride), c);
     } else {
         float* f = reinterpret_cast<float*>(d);
-        f[0] = a; f[1] = b; f[2] = c;
+        gst(f, a); gst(f + 1, b); gst(f + 2, c);
     }
 }
 
@@ -735,24 +784,15 @@ __device__ __forceinline__ void fill_cells(uint8_t* dst, uint32_t pitch, uint32_
         uint8_t* const d = dst + (size_t)row_of(w.r) * pitch + (size_t)c * 16u;
         if (PLANAR) {
 #pragma unroll
-            for (int ch = 0; ch < 3; ++ch) *reinterpret_cast<float4*>(d + (size_t)ch * cstride) = make_float4(bg[ch], bg[ch], bg[ch], bg[ch]);
+            for (int ch = 0; ch < 3; ++ch) gst(reinterpret_cast<float4*>(d + (size_t)ch * cstride), make_float4(bg[ch], bg[ch], bg[ch], bg[ch]));
         } else { /* word c of a row holds the channels (c, c+1, c+2, c) mod 3 */
             const uint32_t k3 = c % 3u;
             const float a = k3 == 0 ? bg[0] : k3 == 1 ? bg[1] : bg[2];
             const float b = k3 == 0 ? bg[1] : k3 == 1 ? bg[2] : bg[0];
             const float e = k3 == 0 ? bg[2] : k3 == 1 ? bg[0] : bg[1];
-            *reinterpret_cast<float4*>(d) = make_float4(a, b, e, a);
+            gst(reinterpret_cast<float4*>(d), make_float4(a, b, e, a));
         }
     }
-}
-
-/* One row of a warp's 32 side-by-side packed float3 pixels: every lane leaves its pixel in the warp's buffer, then lanes
- * 0..23 store the 384 bytes as whole 16-byte words.  `words` = how many of the 24 words are inside the row piece. */
-__device__ __forceinline__ void turn_put(float* buf, uint32_t lane, float a, float b, float c) {
-    buf[3u * lane] = a; buf[3u * lane + 1u] = b; buf[3u * lane + 2u] = c;
-}
-__device__ __forceinline__ void turn_flush(const float* buf, uint32_t lane, uint32_t words, uint8_t* run) {
-    if (lane < words) reinterpret_cast<float4*>(run)[lane] = reinterpret_cast<const float4*>(buf)[lane];
 }
 
 template <uint32_t CHAIN, int SRC, bool PLANAR>
@@ -838,10 +878,10 @@ __device__ __forceinline__ void body_resize(const DevPlane& P, const DevSeq& S, 
                     const float2 w01 = mul2(wx0[k], wy1), w11 = mul2(wx1[k], wy1);
 #pragma unroll
                     for (int c = 0; c < 3; ++c) {
-                        const float2 p00 = make_float2(u8_to_float(__ldg(a00 + c)), u8_to_float(__ldg(b00 + c)));
-                        const float2 p10 = make_float2(u8_to_float(__ldg(a10 + c)), u8_to_float(__ldg(b10 + c)));
-                        const float2 p01 = make_float2(u8_to_float(__ldg(a01 + c)), u8_to_float(__ldg(b01 + c)));
-                        const float2 p11 = make_float2(u8_to_float(__ldg(a11 + c)), u8_to_float(__ldg(b11 + c)));
+                        const float2 p00 = make_float2(u8_to_float(gld(a00 + c)), u8_to_float(gld(b00 + c)));
+                        const float2 p10 = make_float2(u8_to_float(gld(a10 + c)), u8_to_float(gld(b10 + c)));
+                        const float2 p01 = make_float2(u8_to_float(gld(a01 + c)), u8_to_float(gld(b01 + c)));
+                        const float2 p11 = make_float2(u8_to_float(gld(a11 + c)), u8_to_float(gld(b11 + c)));
                         /* ((p00*w00 + p10*w10) + p01*w01) + p11*w11, every product and sum rounded */
                         v[3 * k + c] = add2(add2(add2(mul2(p00, w00), mul2(p10, w10), one), mul2(p01, w01), one), mul2(p11, w11), one);
                     }
@@ -864,25 +904,25 @@ __device__ __forceinline__ void body_resize(const DevPlane& P, const DevSeq& S, 
                     const uint32_t xa = off0[i], xb = off1[i];
                     const uint32_t ca = (xa >> 1) * 2u, cb = (xb >> 1) * 2u;
                     float t[3];
-                    t[0] = u8_to_float(__ldg(l0 + xa)); t[1] = u8_to_float(__ldg(c0 + ca + u_at)); t[2] = u8_to_float(__ldg(c0 + ca + v_at));
+                    t[0] = u8_to_float(gld(l0 + xa)); t[1] = u8_to_float(gld(c0 + ca + u_at)); t[2] = u8_to_float(gld(c0 + ca + v_at));
                     yuv_to_rgb(yuv, t[0], t[1], t[2]);
                     const float w00 = __fmul_rn(wxa, ay.w0);
                     float acc[3] = {__fmul_rn(t[0], w00), __fmul_rn(t[1], w00), __fmul_rn(t[2], w00)};
                     if (need_col1) {
-                        t[0] = u8_to_float(__ldg(l0 + xb)); t[1] = u8_to_float(__ldg(c0 + cb + u_at)); t[2] = u8_to_float(__ldg(c0 + cb + v_at));
+                        t[0] = u8_to_float(gld(l0 + xb)); t[1] = u8_to_float(gld(c0 + cb + u_at)); t[2] = u8_to_float(gld(c0 + cb + v_at));
                         yuv_to_rgb(yuv, t[0], t[1], t[2]);
                         const float w10 = __fmul_rn(wxb, ay.w0);
 #pragma unroll
                         for (int c = 0; c < 3; ++c) acc[c] = __fadd_rn(acc[c], __fmul_rn(t[c], w10));
                     }
                     if (need_row1) {
-                        t[0] = u8_to_float(__ldg(l1 + xa)); t[1] = u8_to_float(__ldg(c1 + ca + u_at)); t[2] = u8_to_float(__ldg(c1 + ca + v_at));
+                        t[0] = u8_to_float(gld(l1 + xa)); t[1] = u8_to_float(gld(c1 + ca + u_at)); t[2] = u8_to_float(gld(c1 + ca + v_at));
                         yuv_to_rgb(yuv, t[0], t[1], t[2]);
                         const float w01 = __fmul_rn(wxa, ay.w1);
 #pragma unroll
                         for (int c = 0; c < 3; ++c) acc[c] = __fadd_rn(acc[c], __fmul_rn(t[c], w01));
                         if (need_col1) {
-                            t[0] = u8_to_float(__ldg(l1 + xb)); t[1] = u8_to_float(__ldg(c1 + cb + u_at)); t[2] = u8_to_float(__ldg(c1 + cb + v_at));
+                            t[0] = u8_to_float(gld(l1 + xb)); t[1] = u8_to_float(gld(c1 + cb + u_at)); t[2] = u8_to_float(gld(c1 + cb + v_at));
                             yuv_to_rgb(yuv, t[0], t[1], t[2]);
                             const float w11 = __fmul_rn(wxb, ay.w1);
 #pragma unroll
@@ -925,6 +965,7 @@ __device__ __forceinline__ void body_resize(const DevPlane& P, const DevSeq& S, 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 /* Three consecutive aligned words of shared memory at a 32-bit shared-window address. */
 __device__ __forceinline__ void lds32x3(uint32_t addr, uint32_t& w0, uint32_t& w1, uint32_t& w2) {
+    if (!check_smem(addr, 12u)) { w0 = w1 = w2 = 0u; return; }
     asm volatile("ld.shared.b32 %0, [%3];\n\tld.shared.b32 %1, [%3+4];\n\tld.shared.b32 %2, [%3+8];"
                  : "=r"(w0), "=r"(w1), "=r"(w2)
                  : "r"(addr));
@@ -936,6 +977,9 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t mbar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(mbar), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t mbar) {
+    /* checked build: a copy that would leave the image or the block's shared memory is not issued; its bytes then never
+       arrive, the block's bounded wait runs out and the status word keeps the larger code */
+    if (!check_src(src, bytes) || !check_smem(dst, bytes)) return;
     asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
                  "r"(bytes), "r"(mbar)
                  : "memory");
@@ -1169,11 +1213,13 @@ __device__ __forceinline__ void mbar_arrive(uint32_t mbar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(mbar) : "memory");
 }
 __device__ __forceinline__ uint32_t lds_u8(uint32_t addr) {
+    if (!check_smem(addr, 1u)) return 0u;
     uint32_t v;
     asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(addr));
     return v;
 }
 __device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+    if (!check_smem(addr, 2u)) return 0u;
     uint32_t v;
     asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(addr));
     return v;
@@ -1493,6 +1539,35 @@ __device__ __forceinline__ void run_body(uint32_t cls, const DevPlane& P, const 
     }
 }
 
+/* Checked build: what this block's plane allows, written once the plane is known (the bulk copies of the staged uchar3
+   classes, which the ordinary build starts before that, start after it). */
+#ifdef FKB_CHECK_BOUNDS
+__device__ __forceinline__ void check_begin(const DevPlane& P, const DevSeq& S, const LaunchArgs& a, const unsigned char* smem_raw) {
+    if (threadIdx.x == 0) {
+        const bool yuv = S.src_format == FKB_SRC_NV12 || S.src_format == FKB_SRC_NV21;
+        const size_t src_rows = yuv ? (size_t)P.src_height + (P.src_height + 1) / 2 : (size_t)P.src_height;
+        s_check.src_lo = P.src;
+        s_check.src_hi = P.src ? P.src + src_rows * P.src_pitch : P.src;
+        s_check.dst = P.dst;
+        s_check.dst_pitch = P.dst_pitch; s_check.dst_rows = P.dst_h;
+        const bool planar = S.dst_format == FKB_DST_F32_PLANAR3;
+        const uint32_t px = S.dst_format == FKB_DST_U8X3_PACKED ? 3u : planar ? 4u : 12u;
+        s_check.dst_row_bytes = P.dst_w * px;
+        s_check.dst_cstride = P.dst_cstride; s_check.dst_channels = planar ? 3u : 1u;
+        uint32_t dyn;
+        asm volatile("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn));
+        s_check.smem_lo = smem_addr(smem_raw); s_check.smem_hi = s_check.smem_lo + dyn;
+        s_check.status = a.status;
+        if (a.test_shrink_bounds) { /* TEST ONLY: pretend the destination has fewer rows, so that the checker has something to refuse */
+            s_check.dst_rows = P.dst_h > a.test_shrink_bounds ? P.dst_h - a.test_shrink_bounds : 0u;
+        }
+    }
+    __syncthreads();
+}
+#else
+__device__ __forceinline__ void check_begin(const DevPlane&, const DevSeq&, const LaunchArgs&, const unsigned char*) {}
+#endif
+
 /* Resident blocks per SM that the compiler must leave registers for.  Measured on B200: the staged
  * uchar3 resize is fastest with four blocks (64 registers), the staged NV12 resize with five, plans
  * of several classes with four as well (the flat bodies hold four runs per thread and the
@@ -1522,6 +1597,7 @@ __global__ void __launch_bounds__(BLOCK_THREADS, min_blocks_of(CLASS)) fused_pla
         const uint32_t n_ops = (uint32_t)a.seq0.n_ops;
         if (threadIdx.x < n_ops) expand_op(*reinterpret_cast<const uint4*>(&a.ops0[threadIdx.x]), sops + threadIdx.x);
         __syncthreads();
+        check_begin(a.plane0, a.seq0, a, smem_raw);
         run_body<CLASS, CHAIN>(a.plane0.plane_class, a.plane0, a.seq0, sops, blockIdx.x, nullptr, s_turn,
                                WaitCtl{a.status, a.wait_limit_us, a.test_extra_bytes});
         return;
@@ -1533,22 +1609,27 @@ __global__ void __launch_bounds__(BLOCK_THREADS, min_blocks_of(CLASS)) fused_pla
     const bool EARLY_COPIES = CLASS == CLASS_RESIZE_U8_PLANAR_STAGED || CLASS == CLASS_RESIZE_U8_PACKED_STAGED ||
                               (CLASS == CLASS_MIXED && a.staged_bytes != 0); /* a plan of several classes with staged planes */
     const uint4 entry = __ldg(a.items + (EARLY_COPIES ? 2u * blockIdx.x : blockIdx.x));
-    if (EARLY_COPIES && threadIdx.x < 32) {
-        const uint4 cp = __ldg(a.items + 2u * blockIdx.x + 1u); /* source pointer, rows | row bytes << 16, pitch */
-        const uint32_t n_src = cp.z & 0xFFFFu, row_len = cp.z >> 16;
-        if (n_src != 0) {
-            unsigned char* const staged = smem_raw + (((a.max_seq_ops > 0 ? a.max_seq_ops : 1u) * (uint32_t)sizeof(OpSlot) + 127u) & ~127u);
-            const uint32_t mbar = smem_addr(staged), stage_addr = smem_addr(staged + STAGED_HEADER_BYTES);
-            if (threadIdx.x == 0) {
-                mbar_init(mbar, 1);
-                asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-                mbar_expect_tx(mbar, n_src * row_len + a.test_extra_bytes);
+    auto start_band_copies = [&]() {
+        if (EARLY_COPIES && threadIdx.x < 32) {
+            const uint4 cp = __ldg(a.items + 2u * blockIdx.x + 1u); /* source pointer, rows | row bytes << 16, pitch */
+            const uint32_t n_src = cp.z & 0xFFFFu, row_len = cp.z >> 16;
+            if (n_src != 0) {
+                unsigned char* const staged = smem_raw + (((a.max_seq_ops > 0 ? a.max_seq_ops : 1u) * (uint32_t)sizeof(OpSlot) + 127u) & ~127u);
+                const uint32_t mbar = smem_addr(staged), stage_addr = smem_addr(staged + STAGED_HEADER_BYTES);
+                if (threadIdx.x == 0) {
+                    mbar_init(mbar, 1);
+                    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+                    mbar_expect_tx(mbar, n_src * row_len + a.test_extra_bytes);
+                }
+                __syncwarp();
+                const uint8_t* g = reinterpret_cast<const uint8_t*>((size_t)cp.x | ((size_t)cp.y << 32));
+                for (uint32_t r = threadIdx.x; r < n_src; r += 32) bulk_copy_g2s(stage_addr + r * row_len, g + (size_t)r * cp.w, row_len, mbar);
             }
-            __syncwarp();
-            const uint8_t* g = reinterpret_cast<const uint8_t*>((size_t)cp.x | ((size_t)cp.y << 32));
-            for (uint32_t r = threadIdx.x; r < n_src; r += 32) bulk_copy_g2s(stage_addr + r * row_len, g + (size_t)r * cp.w, row_len, mbar);
         }
-    }
+    };
+#ifndef FKB_CHECK_BOUNDS
+    start_band_copies();
+#endif
     const uint32_t plane_idx = entry.x, local = entry.y, seq = entry.z & 0xFFFFu, n_ops = entry.z >> 16, ops_begin = entry.w;
     if (threadIdx.x < sizeof(DevPlane) / 16) {
         reinterpret_cast<uint4*>(&s_plane)[threadIdx.x] =
@@ -1560,6 +1641,10 @@ __global__ void __launch_bounds__(BLOCK_THREADS, min_blocks_of(CLASS)) fused_pla
             expand_op(__ldg(reinterpret_cast<const uint4*>(a.ops + ops_begin + k)), sops + k);
     }
     __syncthreads();
+    check_begin(s_plane, s_seq, a, smem_raw);
+#ifdef FKB_CHECK_BOUNDS
+    start_band_copies(); /* the checked build starts them once it knows what the plane allows */
+#endif
     /* staged classes: the region after the operation cache, on a 128-byte boundary */
     unsigned char* staged_mem = smem_raw + (((a.max_seq_ops > 0 ? a.max_seq_ops : 1u) * (uint32_t)sizeof(OpSlot) + 127u) & ~127u);
     run_body<CLASS, CHAIN>(s_plane.plane_class, s_plane, s_seq, sops, local, staged_mem, s_turn,

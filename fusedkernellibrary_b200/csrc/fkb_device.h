@@ -111,6 +111,7 @@ struct LaunchArgs {
     uint32_t inline_plane;      /* 1: a plan of one plane whose descriptors travel in the      */
                                 /* kernel arguments below; block b is tile b of that plane     */
     uint32_t test_extra_bytes;  /* TEST ONLY: bytes a block expects beyond what its copies deliver   */
+    uint32_t test_shrink_bounds;/* TEST ONLY, bounds-checking build: destination rows the checker pretends are missing */
     uint32_t* status;           /* one word in the plan's device block: 0, or a STATUS_* code  */
     DevPlane plane0;            /* inline_plane: the plane, its sequence and its operations    */
     DevSeq seq0;
@@ -236,6 +237,8 @@ constexpr uint32_t NV12_MAX_STAGE_BYTES = 40 * 1024u; /* luma and chroma rows of
 constexpr uint32_t NV12_MAX_SPAN = 256;           /* source rows between a band's first and last tap */
 constexpr uint32_t STAGED_FOLD_BG_GROUPS = 1024;  /* at most this many outside groups: no store-only items */
 constexpr uint32_t STATUS_STAGED_WAIT_TIMEOUT = 1; /* a bulk copy did not complete in time        */
+/* bounds-checking build only: an access outside what the block's plane allows was refused (the largest code is kept) */
+constexpr uint32_t STATUS_BOUNDS_SOURCE = 2, STATUS_BOUNDS_DESTINATION = 3, STATUS_BOUNDS_SHARED = 4;
 
 /* Compile-time operation chains.  A chain is a list of 4-bit operation codes, first operation
  * in the lowest nibble, 0 terminates.  Kernels are instantiated for the chains in

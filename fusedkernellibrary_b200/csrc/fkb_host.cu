@@ -1170,6 +1170,14 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
 /* ------------------------------------------------------------------------------------ */
 extern "C" FKB_API int fkb_version(void) { return 100; }
 
+extern "C" FKB_API int fkb_debug_bounds_checked(void) {
+#ifdef FKB_CHECK_BOUNDS
+    return 1;
+#else
+    return 0;
+#endif
+}
+
 extern "C" FKB_API const char* fkb_status_string(int status) {
     switch (status) {
         case FKB_OK: return "ok";
@@ -1179,6 +1187,7 @@ extern "C" FKB_API const char* fkb_status_string(int status) {
         case FKB_ERR_TOO_LARGE: return "too large";
         case FKB_ERR_NO_DEVICE: return "no CUDA device";
         case FKB_ERR_DEVICE_WAIT: return "a device-side wait ran out";
+        case FKB_ERR_DEVICE_BOUNDS: return "an access outside an image was refused (bounds-checking build)";
         default: return "unknown status";
     }
 }
@@ -1286,6 +1295,9 @@ static int read_status(const uint32_t* d_status, cudaStream_t stream, uint32_t* 
     FKB_CUDA(cudaStreamSynchronize(stream));
     if (out) *out = st;
     if (st != 0) (void)cudaMemsetAsync(const_cast<uint32_t*>(d_status), 0, sizeof st, stream); /* reported once */
+    if (st >= STATUS_BOUNDS_SOURCE)
+        return fail(FKB_ERR_DEVICE_BOUNDS, "the bounds-checking build refused an access outside %s (status %u); outputs are incomplete",
+                    st == STATUS_BOUNDS_SOURCE ? "a source image" : st == STATUS_BOUNDS_DESTINATION ? "a destination image" : "a block's shared memory", st);
     if (st != 0) return fail(FKB_ERR_DEVICE_WAIT, "a thread block gave up waiting for its asynchronous copies (status %u); outputs are incomplete", st);
     return FKB_OK;
 }
@@ -1305,6 +1317,10 @@ extern "C" FKB_API int fkb_plan_set_option(fkb_plan* plan, int option, uint32_t 
         case FKB_PLAN_TEST_EXPECT_EXTRA_BYTES:
             if (value % 16 != 0 || value > 1024u) return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_plan_set_option: surplus of %u bytes is not a multiple of 16 up to 1024", value);
             plan->args.test_extra_bytes = value;
+            return FKB_OK;
+        case FKB_PLAN_TEST_SHRINK_BOUNDS:
+            if (value > 64u) return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_plan_set_option: %u rows to hide is more than 64", value);
+            plan->args.test_shrink_bounds = value;
             return FKB_OK;
         default:
             return fail(FKB_ERR_INVALID_ARGUMENT, "fkb_plan_set_option: unknown option %d", option);
@@ -2315,6 +2331,9 @@ extern "C" FKB_API int fkb_execute_static(const fkb_plan_desc* desc, void* strea
     if (le != cudaSuccess) return fail_cuda(le, "kernel launch", __LINE__);
     if (ce != cudaSuccess) return fail_cuda(ce, "status read-back", __LINE__);
     if (se != cudaSuccess) return fail_cuda(se, "cudaStreamSynchronize", __LINE__);
+    if (st >= STATUS_BOUNDS_SOURCE)
+        return fail(FKB_ERR_DEVICE_BOUNDS, "the bounds-checking build refused an access outside %s (status %u); outputs are incomplete",
+                    st == STATUS_BOUNDS_SOURCE ? "a source image" : st == STATUS_BOUNDS_DESTINATION ? "a destination image" : "a block's shared memory", st);
     if (st != 0) return fail(FKB_ERR_DEVICE_WAIT, "a thread block gave up waiting for its asynchronous copies (status %u); outputs are incomplete", st);
     return FKB_OK;
 }

@@ -42,7 +42,9 @@ typedef enum fkb_status {
     FKB_ERR_CUDA = 3,             /* a CUDA runtime call failed; see fkb_last_error()         */
     FKB_ERR_TOO_LARGE = 4,        /* beyond a stated capacity (fixed-scratch entry point)     */
     FKB_ERR_NO_DEVICE = 5,        /* no usable CUDA device: there is no CPU fallback          */
-    FKB_ERR_DEVICE_WAIT = 6       /* a kernel gave up a bounded wait; outputs are incomplete  */
+    FKB_ERR_DEVICE_WAIT = 6,      /* a kernel gave up a bounded wait; outputs are incomplete  */
+    FKB_ERR_DEVICE_BOUNDS = 7     /* bounds-checking build only: a kernel refused an access   */
+                                  /* outside its plane's images; outputs are incomplete       */
 } fkb_status;
 
 /* ------------------------------------------------------------------------------------ */
@@ -270,6 +272,13 @@ FKB_API int fkb_plan_get_resize_params(const fkb_plan* plan, int32_t index, fkb_
  * launch-site check is cudaGetLastError alone (executors.h:285), which fkb_plan_launch keeps. */
 FKB_API int fkb_plan_check(const fkb_plan* plan, void* stream, uint32_t* device_status);
 
+/* 1 when this library is the bounds-checking build (libfkb200_check.so: the same sources compiled with
+ * -DFKB_CHECK_BOUNDS, every access of a kernel to a source image, a destination or shared memory compared with what
+ * the block's plane allows before it is made; an access outside is skipped and reported through the status word as
+ * FKB_ERR_DEVICE_BOUNDS, never a fault).  It stands in for a memory checker where none can be run; several times
+ * slower, for tests only.  0 in the ordinary build. */
+FKB_API int fkb_debug_bounds_checked(void);
+
 /* Run-time options of a plan (fkb_plan_set_option). */
 typedef enum fkb_plan_option {
     FKB_PLAN_WAIT_LIMIT_US = 1,       /* longest a thread block waits for its asynchronous copies before it   */
@@ -278,9 +287,13 @@ typedef enum fkb_plan_option {
                                       /* A block that gives up waits once more, as long, for copies still in   */
                                       /* flight towards its shared memory, so it holds an SM for at most twice */
                                       /* the limit.                                                            */
-    FKB_PLAN_TEST_EXPECT_EXTRA_BYTES = 2 /* TEST ONLY: every block expects this many bytes more than its copies */
+    FKB_PLAN_TEST_EXPECT_EXTRA_BYTES = 2,/* TEST ONLY: every block expects this many bytes more than its copies */
                                       /* deliver (a multiple of 16), so that its wait runs out although every  */
                                       /* copy completed; exercises the give-up path without a fault or a hang. */
+    FKB_PLAN_TEST_SHRINK_BOUNDS = 3   /* TEST ONLY, bounds-checking build: the checker treats the last `value`   */
+                                      /* rows of every destination as outside, refuses the stores into them and */
+                                      /* reports FKB_ERR_DEVICE_BOUNDS; no access outside an image is ever made. */
+                                      /* Ignored by the ordinary build.                                         */
 } fkb_plan_option;
 #define FKB_DEFAULT_WAIT_LIMIT_US 100000u
 FKB_API int fkb_plan_set_option(fkb_plan* plan, int option, uint32_t value);
