@@ -25,7 +25,7 @@ ERR_DEVICE_WAIT = 6
 ERR_DEVICE_BOUNDS = 7
 
 # vocabulary ---------------------------------------------------------------------------
-SRC_U8X3, SRC_F32X3, SRC_NV12, SRC_NV21 = 1, 2, 3, 4
+SRC_U8X3, SRC_F32X3, SRC_NV12, SRC_NV21, SRC_P010, SRC_P210, SRC_Y210, SRC_UYVY = 1, 2, 3, 4, 5, 6, 7, 8
 DST_F32X3_PACKED, DST_F32_PLANAR3, DST_U8X3_PACKED, DST_I32X3_PACKED, DST_U32X3_PACKED = 1, 2, 3, 4, 5
 RESIZE_NONE, RESIZE_IGNORE_AR, RESIZE_PRESERVE_AR, RESIZE_PRESERVE_AR_RN_EVEN, RESIZE_PRESERVE_AR_LEFT = 0, 1, 2, 3, 4
 GEOMETRY_WARP_AFFINE, GEOMETRY_WARP_PERSPECTIVE = 5, 6

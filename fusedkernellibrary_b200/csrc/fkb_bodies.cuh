@@ -380,10 +380,56 @@ __device__ __forceinline__ void read_tap(const DevPlane& P, int a, int b, float&
     }
 }
 
+/* ConvertYUVToRGB<PF, Full, CP, false, float3> on a pixel of a 10-bit layout (color_conversion.h:284-309): the words were
+ * shifted right by 6 when they were read (:292); the chroma offset is 512 and, for bt601, the luma offset 64 (:187-191);
+ * the result is multiplied by 64 (NormalizeColorRangeDepth, :234-252).  The matrix rows are evaluated as in the 8-bit
+ * functions above, whose reasoning about the dropped zero terms holds for any non-negative integer luma. */
+__device__ __forceinline__ void yuv_to_rgb_10bit(int kind, float& a, float& b, float& c) {
+    const float u = __fsub_rn(b, 512.0f), v = __fsub_rn(c, 512.0f);
+    float r, g, bl;
+    if (kind == PRE_YUV_BT601) {
+        const float y = __fmul_rn(__fsub_rn(a, 64.0f), 1.164383562f);
+        r = __fadd_rn(y, __fmul_rn(v, 1.596026786f));
+        g = __fadd_rn(__fadd_rn(y, __fmul_rn(u, -0.39176229f)), __fmul_rn(v, -0.812967647f));
+        bl = __fadd_rn(y, __fmul_rn(u, 2.017232143f));
+    } else if (kind == PRE_YUV_BT709) {
+        r = __fadd_rn(a, __fmul_rn(v, 1.5748f));
+        g = __fadd_rn(__fadd_rn(a, __fmul_rn(u, -0.1873f)), __fmul_rn(v, -0.4681f));
+        bl = __fadd_rn(a, __fmul_rn(u, 1.8556f));
+    } else {
+        r = __fadd_rn(a, __fmul_rn(v, 1.4746f));
+        g = __fadd_rn(__fadd_rn(a, __fmul_rn(u, -0.16455312684366f)), __fmul_rn(v, -0.57135312684366f));
+        bl = __fadd_rn(a, __fmul_rn(u, 1.8814f));
+    }
+    a = __fmul_rn(r, 64.0f); b = __fmul_rn(g, 64.0f); c = __fmul_rn(bl, 64.0f);
+}
+
+/* ReadYUV<P010 | P210 | Y210 | UYVY> at image (x, y) followed by the sequence's conversion (color_conversion.h:329-372). */
+__device__ __forceinline__ void read_converted_yuv(const DevSeq& S, const DevPlane& P, int x, int y, float& r0, float& r1, float& r2) {
+    const uint8_t* const row = P.src + (size_t)y * P.src_pitch;
+    uint32_t Y, U, V;
+    if (S.src_format == FKB_SRC_P010 || S.src_format == FKB_SRC_P210) {
+        Y = gld(reinterpret_cast<const uint16_t*>(row) + x);
+        const int cy = S.src_format == FKB_SRC_P010 ? (y >> 1) : y; /* 4:2:0 halves the chroma rows, 4:2:2 does not (:343-344) */
+        const uint16_t* uv = reinterpret_cast<const uint16_t*>(P.src + (size_t)P.src_pitch * P.src_height + (size_t)cy * P.src_pitch) + 2 * (x >> 1);
+        U = gld(uv); V = gld(uv + 1);
+    } else if (S.src_format == FKB_SRC_Y210) {
+        const uint16_t* q = reinterpret_cast<const uint16_t*>(row) + 4 * (x >> 1); /* Y0 U Y1 V */
+        Y = gld(q + ((x & 1) ? 2 : 0)); U = gld(q + 1); V = gld(q + 3);
+    } else { /* UYVY: U Y0 V Y1 */
+        const uint8_t* q = row + 4 * (x >> 1);
+        Y = gld(q + ((x & 1) ? 3 : 1)); U = gld(q); V = gld(q + 2);
+    }
+    r0 = (float)(Y >> S.yuv_shift); r1 = (float)(U >> S.yuv_shift); r2 = (float)(V >> S.yuv_shift);
+    if (S.yuv_shift) yuv_to_rgb_10bit(S.yuv_kind, r0, r1, r2);
+    else yuv_to_rgb(S.yuv_kind, r0, r1, r2);
+}
+
 __device__ __forceinline__ void read_tap_any(const DevSeq& S, const DevPlane& P, int a, int b, float& r0, float& r1,
                                              float& r2) {
     if (S.src_format == FKB_SRC_U8X3) read_tap<FKB_SRC_U8X3>(P, a, b, r0, r1, r2);
     else if (S.src_format == FKB_SRC_F32X3) read_tap<FKB_SRC_F32X3>(P, a, b, r0, r1, r2);
+    else if (S.src_format >= FKB_SRC_P010) read_converted_yuv(S, P, a + P.crop_x, b + P.crop_y, r0, r1, r2);
     else read_tap<FKB_SRC_NV12>(P, a, b, r0, r1, r2, S.swap_uv != 0);
 }
 
@@ -666,8 +712,12 @@ __device__ __forceinline__ void body_flat(const DevPlane& P, const DevSeq& S, co
 #pragma unroll
             for (int k = 0; k < 3; ++k) {
                 if constexpr (DST_IS_U8) {
-                    w[k] = (uint32_t)(uint8_t)v[4 * k + 0] | ((uint32_t)(uint8_t)v[4 * k + 1] << 8) |
-                           ((uint32_t)(uint8_t)v[4 * k + 2] << 16) | ((uint32_t)(uint8_t)v[4 * k + 3] << 24);
+                    /* The values are whole numbers 0..255 (bytes that were never touched, or SaturateCast's result):
+                       2^23 + v is exact and carries v in its lowest byte, so four additions and three byte permutes
+                       pack the word without four trips through the quarter-rate conversion unit. */
+                    const uint32_t b0 = __float_as_uint(__fadd_rn(v[4 * k + 0], 8388608.0f)), b1 = __float_as_uint(__fadd_rn(v[4 * k + 1], 8388608.0f));
+                    const uint32_t b2 = __float_as_uint(__fadd_rn(v[4 * k + 2], 8388608.0f)), b3 = __float_as_uint(__fadd_rn(v[4 * k + 3], 8388608.0f));
+                    w[k] = __byte_perm(__byte_perm(b0, b1, 0x0040), __byte_perm(b2, b3, 0x0040), 0x5410);
                 } else {
                     w[k] = make_float4(v[4 * k + 0], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
                 }
@@ -1397,59 +1447,76 @@ __device__ __forceinline__ void body_nv12_staged(const DevPlane& P, const DevSeq
         return;
     }
 
-    /* one tap: Y, U, V as floats, converted when the chain says so */
-    auto tap = [&](uint32_t l_addr, uint32_t c_addr, float (&t)[3]) {
-        const uint32_t uv = lds_u16(c_addr);
-        t[0] = byte_to_float(lds_u8(l_addr));
-        t[1] = byte_to_float(uv >> u_shift);
-        t[2] = byte_to_float(uv >> v_shift);
-        yuv_to_rgb(yuv, t[0], t[1], t[2]);
-    };
-    /* interpolated value of one column in the row described by rows / wy */
-    auto column = [&](const float4& rows, const float4& wy, uint32_t l0, uint32_t l1, uint32_t c0, uint32_t c1, float w0x,
-                      float w1x, bool col1, float (&acc)[3]) {
-        const uint32_t lr0 = __float_as_uint(rows.x), lr1 = __float_as_uint(rows.y);
-        const uint32_t cr0 = __float_as_uint(rows.z), cr1 = __float_as_uint(rows.w);
-        float t[3];
-        tap(lr0 + l0, cr0 + c0, t);
-        const float w00 = __fmul_rn(w0x, wy.x);
-#pragma unroll
-        for (int c = 0; c < 3; ++c) acc[c] = __fmul_rn(t[c], w00);
-        if (col1) {
-            tap(lr0 + l1, cr0 + c1, t);
-            const float w10 = __fmul_rn(w1x, wy.x);
-#pragma unroll
-            for (int c = 0; c < 3; ++c) acc[c] = __fadd_rn(acc[c], __fmul_rn(t[c], w10));
-        }
-        if (wy.z != 0.0f) {
-            tap(lr1 + l0, cr1 + c0, t);
-            const float w01 = __fmul_rn(w0x, wy.z);
-#pragma unroll
-            for (int c = 0; c < 3; ++c) acc[c] = __fadd_rn(acc[c], __fmul_rn(t[c], w01));
-            if (col1) {
-                tap(lr1 + l1, cr1 + c1, t);
-                const float w11 = __fmul_rn(w1x, wy.z);
-#pragma unroll
-                for (int c = 0; c < 3; ++c) acc[c] = __fadd_rn(acc[c], __fmul_rn(t[c], w11));
-            }
-        }
+    /* One tap of the thread's two columns at once: (Y, U, V) pairs as floats, converted when the chain says so.  The
+       two columns travel as the halves of packed values, so that every product and sum of the conversion and of the
+       blend is one instruction for both (each half rounded like the scalar instruction). */
+    const float2 m128 = dup2(-128.0f);
+    auto tap2 = [&](uint32_t l_a, uint32_t c_a, uint32_t l_b, uint32_t c_b, float2 (&t)[3]) {
+        const uint32_t uva = lds_u16(c_a), uvb = lds_u16(c_b);
+        t[0] = make_float2(byte_to_float(lds_u8(l_a)), byte_to_float(lds_u8(l_b)));
+        t[1] = make_float2(byte_to_float(uva >> u_shift), byte_to_float(uvb >> u_shift));
+        t[2] = make_float2(byte_to_float(uva >> v_shift), byte_to_float(uvb >> v_shift));
+        if (yuv == PRE_IDENTITY) return;
+        /* the three full-range matrices as in yuv_to_rgb_*_full above, terms that cannot change a bit dropped */
+        const float2 u = add2(t[1], m128, one), v = add2(t[2], m128, one);
+        float2 y = t[0];
+        float kr, kgu, kgv, kb;
+        if (yuv == PRE_YUV_BT709) { kr = 1.5748f; kgu = -0.1873f; kgv = -0.4681f; kb = 1.8556f; }
+        else if (yuv == PRE_YUV_BT601) {
+            y = mul2(add2(y, dup2(-16.0f), one), dup2(1.164383562f));
+            kr = 1.596026786f; kgu = -0.39176229f; kgv = -0.812967647f; kb = 2.017232143f;
+        } else { kr = 1.4746f; kgu = -0.16455312684366f; kgv = -0.57135312684366f; kb = 1.8814f; }
+        t[0] = add2(mul2(v, dup2(kr)), y, one);
+        t[1] = add2(mul2(v, dup2(kgv)), add2(mul2(u, dup2(kgu)), y, one), one);
+        t[2] = add2(mul2(u, dup2(kb)), y, one);
     };
 
     if (slot < rs && valid_a) {
         uint8_t* out_a = dst + (size_t)(ya + (int)slot) * dst_pitch + (size_t)xa * 12;
         const size_t b_off = (size_t)gw * 12, row_step = (size_t)rs * dst_pitch;
         const float4* rt = row_tab + 2 * slot;
+        /* a second column tap is read for both columns when either has a weight for it: the other's weight is zero and its
+           product a zero that changes no bit of the sum (the tap lies inside the staged row either way) */
+        const bool col1 = col1_a || col1_b;
+        const float2 wx0 = make_float2(axa.w0, axb.w0), wx1 = make_float2(axa.w1, axb.w1);
+        const bool plain = in_a && in_b && valid_b;
 #pragma unroll 1
         for (int y = ya + (int)slot; y <= yb; y += (int)rs, rt += 2 * rs, out_a += row_step) {
             const float4 rows = rt[0], wy = rt[1];
-            float va[3], vb[3] = {0.0f, 0.0f, 0.0f};
-            column(rows, wy, la0, la1, ca0, ca1, axa.w0, axa.w1, col1_a, va);
-            if (valid_b) column(rows, wy, lb0, lb1, cb0, cb1, axb.w0, axb.w1, col1_b, vb);
-            float2 v[3] = {make_float2(va[0], vb[0]), make_float2(va[1], vb[1]), make_float2(va[2], vb[2])};
+            const uint32_t lr0 = __float_as_uint(rows.x), lr1 = __float_as_uint(rows.y);
+            const uint32_t cr0 = __float_as_uint(rows.z), cr1 = __float_as_uint(rows.w);
+            float2 t[3], v[3];
+            tap2(lr0 + la0, cr0 + ca0, lr0 + lb0, cr0 + cb0, t);
+            const float2 w00 = mul2(wx0, dup2(wy.x));
+#pragma unroll
+            for (int c = 0; c < 3; ++c) v[c] = mul2(t[c], w00);
+            if (col1) {
+                tap2(lr0 + la1, cr0 + ca1, lr0 + lb1, cr0 + cb1, t);
+                const float2 w10 = mul2(wx1, dup2(wy.x));
+#pragma unroll
+                for (int c = 0; c < 3; ++c) v[c] = add2(mul2(t[c], w10), v[c], one);
+            }
+            if (wy.z != 0.0f) {
+                tap2(lr1 + la0, cr1 + ca0, lr1 + lb0, cr1 + cb0, t);
+                const float2 w01 = mul2(wx0, dup2(wy.z));
+#pragma unroll
+                for (int c = 0; c < 3; ++c) v[c] = add2(mul2(t[c], w01), v[c], one);
+                if (col1) {
+                    tap2(lr1 + la1, cr1 + ca1, lr1 + lb1, cr1 + cb1, t);
+                    const float2 w11 = mul2(wx1, dup2(wy.z));
+#pragma unroll
+                    for (int c = 0; c < 3; ++c) v[c] = add2(mul2(t[c], w11), v[c], one);
+                }
+            }
             run_ops<CHAIN, 1>(v, sops, S.n_pre, S.n_ops, one);
-            store_pixel_at<PLANAR>(out_a, dst_cstride, in_a ? v[0].x : bgv[0], in_a ? v[1].x : bgv[1], in_a ? v[2].x : bgv[2]);
-            if (valid_b)
-                store_pixel_at<PLANAR>(out_a + b_off, dst_cstride, in_b ? v[0].y : bgv[0], in_b ? v[1].y : bgv[1], in_b ? v[2].y : bgv[2]);
+            if (plain) {
+                store_pixel_at<PLANAR>(out_a, dst_cstride, v[0].x, v[1].x, v[2].x);
+                store_pixel_at<PLANAR>(out_a + b_off, dst_cstride, v[0].y, v[1].y, v[2].y);
+            } else {
+                store_pixel_at<PLANAR>(out_a, dst_cstride, in_a ? v[0].x : bgv[0], in_a ? v[1].x : bgv[1], in_a ? v[2].x : bgv[2]);
+                if (valid_b)
+                    store_pixel_at<PLANAR>(out_a + b_off, dst_cstride, in_b ? v[0].y : bgv[0], in_b ? v[1].y : bgv[1], in_b ? v[2].y : bgv[2]);
+            }
         }
     }
 
@@ -1544,8 +1611,7 @@ __device__ __forceinline__ void run_body(uint32_t cls, const DevPlane& P, const 
 #ifdef FKB_CHECK_BOUNDS
 __device__ __forceinline__ void check_begin(const DevPlane& P, const DevSeq& S, const LaunchArgs& a, const unsigned char* smem_raw) {
     if (threadIdx.x == 0) {
-        const bool yuv = S.src_format == FKB_SRC_NV12 || S.src_format == FKB_SRC_NV21;
-        const size_t src_rows = yuv ? (size_t)P.src_height + (P.src_height + 1) / 2 : (size_t)P.src_height;
+        const size_t src_rows = source_rows(S.src_format, P.src_height);
         s_check.src_lo = P.src;
         s_check.src_hi = P.src ? P.src + src_rows * P.src_pitch : P.src;
         s_check.dst = P.dst;

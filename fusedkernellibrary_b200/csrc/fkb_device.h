@@ -79,7 +79,10 @@ struct alignas(16) DevSeq {
     int32_t deinterlace;             /* fkb_deinterlace_mode                                     */
     float border_value[3];
     float transform[9];              /* FKB_GEOMETRY_WARP_*: rows of three                        */
-    uint32_t pad[2];
+    /* FKB_SRC_P010 / P210 / Y210 / UYVY: the read converts to RGB itself (the conversion is dropped from the
+       operation list) */
+    int32_t yuv_kind;                /* PRE_YUV_* of that conversion, 0 for the other formats    */
+    uint32_t yuv_shift;              /* 6 for the 10-bit layouts, else 0                         */
 };
 static_assert(sizeof(DevSeq) == 128, "DevSeq layout");
 
@@ -90,6 +93,24 @@ enum PreKind : int32_t {
     PRE_YUV_BT601 = 3,/* exactly ConvertYUVToRGB<PF,Full,bt601,false,float3>                   */
     PRE_YUV_BT2020 = 4/* exactly ConvertYUVToRGB<PF,Full,bt2020,false,float3>                  */
 };
+
+/* Rows of `pitch` bytes that a source image of `height` pixel rows occupies, by format. */
+__host__ __device__ inline uint32_t source_rows(int src_format, uint32_t height) {
+    return (src_format == FKB_SRC_NV12 || src_format == FKB_SRC_NV21 || src_format == FKB_SRC_P010) ? height + (height + 1u) / 2u
+           : src_format == FKB_SRC_P210 ? 2u * height : height;
+}
+/* Bytes of the longest row of any plane of the image. */
+__host__ __device__ inline uint64_t source_row_bytes(int src_format, uint32_t width) {
+    const uint64_t pairs = ((uint64_t)width + 1u) / 2u;
+    switch (src_format) {
+        case FKB_SRC_U8X3: return 3ull * width;
+        case FKB_SRC_F32X3: return 12ull * width;
+        case FKB_SRC_NV12: case FKB_SRC_NV21: return 2ull * pairs;
+        case FKB_SRC_P010: case FKB_SRC_P210: return 4ull * pairs;
+        case FKB_SRC_Y210: return 8ull * pairs;
+        default: return 4ull * pairs; /* FKB_SRC_UYVY */
+    }
+}
 
 constexpr int INLINE_MAX_OPS = 16;
 
@@ -221,7 +242,7 @@ inline ResizeTiling resize_tiling(uint32_t dst_w, uint32_t dst_h, int x1, int y1
 /* STAGED classes: a work item is a band of `band_rows` output rows of the region of interest,
  * all columns; its source footprint (whole crop rows, widened to 16-byte boundaries) sits in
  * shared memory behind a 16-byte mbarrier slot and a table of per-row vertical taps. */
-constexpr uint32_t STAGED_BAND_PIXELS = 7168; /* output pixels per band, about         */
+constexpr uint32_t STAGED_BAND_PIXELS = 5376; /* output pixels per band, about (4480 / 5376 / 6272 / 7168 / 8960: 152.0 / 152.6 / 153.3 / 154.2 / 156.1 us on the 1024-crop batch) */
 constexpr uint32_t STAGED_MIN_BAND_PIXELS = 448; /* bands of a plan with a small grid are halved down to this       */
 constexpr uint32_t SMALL_GRID_BLOCKS = 148;      /* fewer blocks than this (one per SM of a B200): shorter bands        */
 constexpr uint32_t STAGED_MAX_ROWS = 64;          /* output rows per band                        */

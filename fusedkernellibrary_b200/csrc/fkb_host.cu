@@ -483,6 +483,9 @@ static uint32_t chain_code_of(int dev_opcode) {
     }
 }
 
+/* layouts that only the one-pixel-per-thread body reads, together with their conversion to RGB */
+static bool read_converts(int f) { return f >= FKB_SRC_P010 && f <= FKB_SRC_UYVY; }
+
 /* Lowers one sequence into `out`; Cast<uchar3,float3> is exact on values already held as float and
    leaves no device operation.  Returns the chain code of the operations after the geometry stage
    (CHAIN_INTERPRET when it does not fit eight nibbles). */
@@ -503,6 +506,7 @@ static uint32_t lower_ops(const fkb_sequence& s, int n_pre, int step_exp_x, int 
         }
         if (k == s.n_ops) break;
         const fkb_op& op = s.ops[k];
+        if (k == 0 && read_converts(s.src_format)) { v.known = false; continue; } /* the read converts: nothing on the device's list */
         const bool fast = advance_range(v, op);
         if (op.opcode == FKB_OP_CAST_F32) continue;
         {
@@ -574,7 +578,8 @@ static uint32_t lower_ops(const fkb_sequence& s, int n_pre, int step_exp_x, int 
 enum ValueType { VT_U8 = 0, VT_F32 = 1, VT_YUV8 = 2, VT_I32 = 3, VT_U32 = 4 };
 
 static uint32_t src_pixel_bytes(int f) { return f == FKB_SRC_U8X3 ? 3u : f == FKB_SRC_F32X3 ? 12u : 1u; }
-static bool is_yuv_source(int f) { return f == FKB_SRC_NV12 || f == FKB_SRC_NV21; }
+static bool is_yuv_source(int f) { return f >= FKB_SRC_NV12 && f <= FKB_SRC_UYVY; }
+
 static bool is_yuv_conversion(int opcode) {
     return opcode == FKB_OP_YUV_TO_RGB_BT709_FULL || opcode == FKB_OP_YUV_TO_RGB_BT601_FULL || opcode == FKB_OP_YUV_TO_RGB_BT2020_FULL;
 }
@@ -583,7 +588,7 @@ static uint32_t dst_pixel_bytes(int f) { return f == FKB_DST_U8X3_PACKED ? 3u : 
 /* Walks a sequence's operations with the value type the reference's templates would have
    (a mismatch there is a compile error; here it is FKB_ERR_INVALID_ARGUMENT). */
 static int check_sequence(const fkb_sequence& s, int index, DevSeq& ds) {
-    if (s.src_format < FKB_SRC_U8X3 || s.src_format > FKB_SRC_NV21)
+    if (s.src_format < FKB_SRC_U8X3 || s.src_format > FKB_SRC_UYVY)
         return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d: unknown source format %d", index, s.src_format);
     if (s.dst_format < FKB_DST_F32X3_PACKED || s.dst_format > FKB_DST_U32X3_PACKED)
         return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d: unknown destination format %d", index, s.dst_format);
@@ -644,6 +649,8 @@ static int check_sequence(const fkb_sequence& s, int index, DevSeq& ds) {
                 return fail(FKB_ERR_INVALID_ARGUMENT, "sequence %d op %d: unknown opcode %d", index, k, oc);
         }
     }
+    if (read_converts(s.src_format) && (s.n_ops < 1 || !is_yuv_conversion(s.ops[0].opcode) || (s.resize_mode != FKB_RESIZE_NONE && n_pre < 1)))
+        return fail(FKB_ERR_UNSUPPORTED, "sequence %d: a P010 / P210 / Y210 / UYVY read must be followed at once by its conversion to RGB", index);
     const bool dst_u8 = s.dst_format == FKB_DST_U8X3_PACKED;
     const ValueType want = dst_u8 ? VT_U8 : s.dst_format == FKB_DST_I32X3_PACKED ? VT_I32 : s.dst_format == FKB_DST_U32X3_PACKED ? VT_U32 : VT_F32;
     if (want != (t == VT_YUV8 ? VT_U8 : t)) {
@@ -666,9 +673,14 @@ static int check_sequence(const fkb_sequence& s, int index, DevSeq& ds) {
     ds.border_mode = s.border_mode; ds.deinterlace = s.deinterlace;
     for (int c = 0; c < 3; ++c) ds.border_value[c] = s.border_value[c];
     for (int k = 0; k < 9; ++k) ds.transform[k] = s.transform[k];
-    ds.pad[0] = ds.pad[1] = 0;
-    /* BorderReader, Deinterlace and Warping run in the one-pixel-per-thread body only */
-    ds.pre_kind = read_back_extras ? PRE_GENERAL
+    ds.yuv_kind = 0; ds.yuv_shift = 0;
+    if (read_converts(s.src_format)) {
+        const int oc = s.ops[0].opcode;
+        ds.yuv_kind = oc == FKB_OP_YUV_TO_RGB_BT709_FULL ? PRE_YUV_BT709 : oc == FKB_OP_YUV_TO_RGB_BT601_FULL ? PRE_YUV_BT601 : PRE_YUV_BT2020;
+        ds.yuv_shift = s.src_format == FKB_SRC_UYVY ? 0u : 6u;
+    }
+    /* BorderReader, Deinterlace, Warping and the layouts whose read converts run in the one-pixel-per-thread body only */
+    ds.pre_kind = (read_back_extras || read_converts(s.src_format)) ? PRE_GENERAL
                   : (n_pre == 0 || pre_only_casts) ? PRE_IDENTITY
                   : !pre_is_yuv ? PRE_GENERAL
                   : yuv_opcode == FKB_OP_YUV_TO_RGB_BT709_FULL ? PRE_YUV_BT709
@@ -862,7 +874,7 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
             return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: image side beyond 2^24", i);
         const uint32_t spx = src_pixel_bytes(s.src_format), dpx = dst_pixel_bytes(s.dst_format);
         if (!is_default) {
-            const uint64_t src_row = s.src_format == FKB_SRC_NV12 ? 2ull * ((p.src_width + 1) / 2) : (uint64_t)p.src_width * spx;
+            const uint64_t src_row = source_row_bytes(s.src_format, p.src_width);
             if (p.src_pitch < src_row)
                 return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: source pitch %u is less than a row of %llu bytes", i, p.src_pitch, (unsigned long long)src_row);
             if ((uint64_t)p.src_pitch * p.src_height * 2 > 0xFFFFFFFFull)
@@ -877,6 +889,8 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
                 return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: without a resize the output (%ux%u) must have the size of the crop (%dx%d)", i, p.dst_width, p.dst_height, p.crop_width, p.crop_height);
             if (s.src_format == FKB_SRC_F32X3 && (!aligned(p.src, 4) || p.src_pitch % 4))
                 return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: float source must be 4-byte aligned", i);
+            if (read_converts(s.src_format) && (!aligned(p.src, 8) || p.src_pitch % 8))
+                return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: a P010 / P210 / Y210 / UYVY image and its pitch must be 8-byte aligned", i);
         }
         if (p.dst_pitch < (uint64_t)p.dst_width * dpx)
             return fail(FKB_ERR_INVALID_ARGUMENT, "plane %d: destination pitch %u is less than a row of %llu bytes", i, p.dst_pitch, (unsigned long long)p.dst_width * dpx);
@@ -968,7 +982,10 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
 
         img.output_pixels += out_px;
         const uint64_t crop_px = is_default ? 0 : (uint64_t)p.crop_width * p.crop_height;
-        img.algorithmic_bytes += (s.src_format == FKB_SRC_NV12 ? crop_px + crop_px / 2 : crop_px * spx) + out_px * (s.dst_format == FKB_DST_F32_PLANAR3 ? 12 : dpx);
+        const uint64_t src_bytes = s.src_format == FKB_SRC_NV12 ? crop_px + crop_px / 2 : s.src_format == FKB_SRC_P010 ? 3 * crop_px
+                                   : (s.src_format == FKB_SRC_P210 || s.src_format == FKB_SRC_Y210) ? 4 * crop_px
+                                   : s.src_format == FKB_SRC_UYVY ? 2 * crop_px : crop_px * spx;
+        img.algorithmic_bytes += src_bytes + out_px * (s.dst_format == FKB_DST_F32_PLANAR3 ? 12 : dpx);
     }
     uint32_t common_chain = 0;
     for (int s = 0; s < d->n_sequences; ++s) {
@@ -1630,7 +1647,7 @@ static int host_session_create(const fkb_plan_desc* desc, fkb_host_session** out
         const fkb_plane& p = desc->planes[i];
         const fkb_sequence& q = desc->sequences[p.sequence];
         const bool is_default = (p.flags & FKB_PLANE_DEFAULT_VALUE) != 0; /* reads no image: a group without an upload */
-        const size_t rows = is_yuv_source(q.src_format) ? (size_t)p.src_height + (p.src_height + 1) / 2 : p.src_height;
+        const size_t rows = source_rows(q.src_format, p.src_height);
         const size_t bytes = is_default ? 0 : (size_t)p.src_pitch * rows;
         auto it = group_of.find(is_default ? nullptr : p.src);
         if (it == group_of.end()) {

@@ -57,7 +57,17 @@ typedef enum fkb_src_format {
     FKB_SRC_F32X3 = 2, /* PerThreadRead<_2D, float3>                                          */
     FKB_SRC_NV12 = 3,  /* ReadYUV<NV12> (color_conversion.h:314-346): `height` luma rows then */
                        /* height/2 rows of interleaved U,V, chroma at data + pitch*height     */
-    FKB_SRC_NV21 = 4   /* ReadYUV<NV21> (color_conversion.h:347-359): the same with V,U pairs */
+    FKB_SRC_NV21 = 4,  /* ReadYUV<NV21> (color_conversion.h:347-359): the same with V,U pairs */
+    /* The layouts below are read by the one-pixel-per-thread body only, and only as ReadYUV<PF> followed at once by
+       ConvertYUVToRGB<PF, Full, ...> (ops[0] is the conversion; its result is float3).  src_width / src_height are
+       the image's size in pixels, src_pitch the bytes between rows of its first plane. */
+    FKB_SRC_P010 = 5,  /* 4:2:0, 10 bits in the top of 16-bit words: `height` rows of luma words, then height/2    */
+                       /* rows of interleaved U,V words at data + pitch*height (color_conversion.h:329-346); the  */
+                       /* conversion works on the words shifted right by 6, with chroma offset 512 (luma 64 for    */
+                       /* bt601), and multiplies its result by 64 (:284-309, :187-200)                             */
+    FKB_SRC_P210 = 6,  /* the same, 4:2:2: `height` rows of chroma                                                 */
+    FKB_SRC_Y210 = 7,  /* packed 4:2:2 of 16-bit words Y0 U Y1 V per two pixels (:360-372), 10 bits as above       */
+    FKB_SRC_UYVY = 8   /* packed 4:2:2 of bytes U Y0 V Y1 per two pixels (:360-372)                                */
 } fkb_src_format;
 
 /* Layout written by the receiver. */

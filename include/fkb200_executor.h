@@ -26,7 +26,7 @@
  * core/execution_model/stream.h:50).  Needs only include/fkb200.h beside the reference's headers.
  *
  * Operations understood (anything else: static_assert):
- *   reads      PerThreadRead<_2D, uchar3|float3>, ReadYUV<NV12|NV21>, Crop<Back>, Resize<INTER_LINEAR,
+ *   reads      PerThreadRead<_2D, uchar3|float3>, ReadYUV<NV12|NV21|P010|P210|Y210|UYVY>, Crop<Back>, Resize<INTER_LINEAR,
  *              IGNORE_AR|PRESERVE_AR|PRESERVE_AR_RN_EVEN|PRESERVE_AR_LEFT, Back>, FusedOperation_<...>,
  *              BatchRead<B, PROCESS_ALL, ...>, BatchRead<B, CONDITIONAL_WITH_DEFAULT, ...>,
  *              BorderReader<BT, Read> directly above the PerThreadRead (a Crop above it may reach beyond the image),
@@ -34,7 +34,8 @@
  *              Warping<Affine|Perspective, Back> in the place of a Resize
  *   compute    Mul / Sub / Div / Add <float3>, Cast<uchar3,float3>, Cast<float3,int3|uint3>,
  *              SaturateCast<float3,uchar3>, VectorReorder<T,2,1,0> (COLOR_RGB2BGR / COLOR_BGR2RGB),
- *              ConvertYUVToRGB<NV12|NV21, Full, bt709|bt601|bt2020, false, float3>
+ *              ConvertYUVToRGB<PF, Full, bt709|bt601|bt2020, false, float3> for the layouts above (directly behind the
+ *              read for the four that are not NV12 / NV21)
  *   receivers  PerThreadWrite<_2D|_3D, T>, TensorWrite<T>, TensorSplit<float3>, TensorTSplit<float3>,
  *              SplitWrite<_2D, float3> over three equally spaced images of one pitch
  *
@@ -117,8 +118,12 @@ template <> struct LowerCompute<fk::Cast<float3, int3>> { static void apply(Plan
 template <> struct LowerCompute<fk::Cast<float3, uint3>> { static void apply(PlaneState& st) { st.ops.push_back(make_op(FKB_OP_CAST_U32)); } };
 template <> struct LowerCompute<fk::SaturateCast<float3, uchar3>> { static void apply(PlaneState& st) { st.ops.push_back(make_op(FKB_OP_SATURATE_CAST_U8)); } };
 template <typename T> struct LowerCompute<fk::VectorReorder<T, 2, 1, 0>> { static void apply(PlaneState& st) { st.ops.push_back(make_op(FKB_OP_SWAP_RB)); } };
+template <fk::PixelFormat PF> constexpr int yuv_source_format() {
+    return PF == fk::PixelFormat::NV12 ? FKB_SRC_NV12 : PF == fk::PixelFormat::NV21 ? FKB_SRC_NV21 : PF == fk::PixelFormat::P010 ? FKB_SRC_P010
+           : PF == fk::PixelFormat::P210 ? FKB_SRC_P210 : PF == fk::PixelFormat::Y210 ? FKB_SRC_Y210 : PF == fk::PixelFormat::UYVY ? FKB_SRC_UYVY : 0;
+}
 template <fk::PixelFormat PF, fk::ColorPrimitives CP> struct LowerCompute<fk::ConvertYUVToRGB<PF, fk::ColorRange::Full, CP, false, float3>> {
-    static_assert(PF == fk::PixelFormat::NV12 || PF == fk::PixelFormat::NV21, "fkb200: only NV12 and NV21 conversions are on the accelerated path");
+    static_assert(yuv_source_format<PF>() != 0, "fkb200: conversions from this pixel format are not on the accelerated path");
     static_assert(CP == fk::ColorPrimitives::bt709 || CP == fk::ColorPrimitives::bt601 || CP == fk::ColorPrimitives::bt2020,
                   "fkb200: this colour matrix is not on the accelerated path");
     static void apply(PlaneState& st) {
@@ -158,9 +163,9 @@ template <typename T> struct LowerRead<fk::PerThreadRead<fk::ND::_2D, T>> {
 /* ReadYUV<NV12> (color_conversion.h:314-400): params is a RawImage whose luma RawPtr has dims.height rows and
    whose chroma plane lies at data + pitch * dims.height (:336-341) */
 template <fk::PixelFormat PF> struct LowerRead<fk::ReadYUV<PF>> {
-    static_assert(PF == fk::PixelFormat::NV12 || PF == fk::PixelFormat::NV21, "fkb200: only NV12 and NV21 reads are on the accelerated path");
+    static_assert(yuv_source_format<PF>() != 0, "fkb200: reads of this pixel format are not on the accelerated path");
     template <typename D> static void apply(PlaneState& st, const D& d) {
-        st.src_format = PF == fk::PixelFormat::NV12 ? FKB_SRC_NV12 : FKB_SRC_NV21;
+        st.src_format = yuv_source_format<PF>();
         st.plane.src = d.params.data.data;
         st.plane.src_width = d.params.width; st.plane.src_height = d.params.data.dims.height; st.plane.src_pitch = d.params.data.dims.pitch;
         st.plane.crop_x = 0; st.plane.crop_y = 0;

@@ -20,7 +20,7 @@
  * non-owning views (RawPtr, core/data/rawptr.h:124-157) over memory the caller allocated - the owning
  * Ptr2D/Tensor classes of the reference (core/data/ptr_nd.h) are outside this path.
  *
- * Only the operations of the fused-execution path are here: PerThreadRead, ReadYUV<NV12 | NV21> +
+ * Only the operations of the fused-execution path are here: PerThreadRead, ReadYUV<NV12 | NV21 | P010 | P210 | Y210 | UYVY> +
  * ConvertYUVToRGB<PF, Full, bt709 | bt601 | bt2020>, Crop, Resize<INTER_LINEAR, IGNORE_AR | PRESERVE_AR |
  * PRESERVE_AR_RN_EVEN | PRESERVE_AR_LEFT>, BorderReader, Deinterlace, Warping, Mul/Sub/Div/Add, Cast,
  * SaturateCast, ColorConversion<RGB2BGR | BGR2RGB>, PerThreadWrite, TensorWrite, TensorSplit, batches, and
@@ -73,7 +73,7 @@ enum class ND { _2D, _3D };
 enum class InterpolationType { INTER_LINEAR };
 enum class AspectRatio { PRESERVE_AR, IGNORE_AR, PRESERVE_AR_RN_EVEN, PRESERVE_AR_LEFT };
 enum class ColorConversionCodes { COLOR_RGB2BGR, COLOR_BGR2RGB };
-enum class PixelFormat { NV12, NV21 };
+enum class PixelFormat { NV12, NV21, P010, P210, Y210, UYVY };
 enum class ColorRange { Full };
 enum class ColorPrimitives { bt601, bt709, bt2020 };
 enum class BorderType { CONSTANT, REPLICATE, REFLECT, WRAP, REFLECT_101 };
@@ -90,6 +90,9 @@ template <typename T> struct RawTensor { T* data; unsigned width, height, planes
    (color_conversion.h:336-341 with an Image whose dims.height is the frame height). */
 struct ImageNV12 { const unsigned char* data; unsigned width, height, pitch; };
 using ImageNV21 = ImageNV12; /* the same layout with V before U in the chroma rows */
+/* Any other layout of ReadYUV (raw_image.h:48-106): `data` is the first plane, `pitch` the bytes between its rows; P010 and
+   P210 keep their interleaved chroma rows behind the `height` luma rows, Y210 and UYVY are one packed plane. */
+using ImageYUV = ImageNV12;
 
 inline void check(int status) {
     if (status != FKB_OK) throw std::runtime_error(std::string(fkb_last_error()[0] ? fkb_last_error() : fkb_status_string(status)));
@@ -159,7 +162,9 @@ template <> struct PerThreadRead<ND::_2D, float3> {
 template <PixelFormat PF> struct ReadYUV {
     static Sender build(const ImageNV12& img) { return build(std::array<ImageNV12, 1>{img}); }
     template <size_t B> static Sender build(const std::array<ImageNV12, B>& imgs) {
-        Sender s; s.src_format = PF == PixelFormat::NV12 ? FKB_SRC_NV12 : FKB_SRC_NV21; s.value_is_yuv = true;
+        Sender s; s.value_is_yuv = true;
+        s.src_format = PF == PixelFormat::NV12 ? FKB_SRC_NV12 : PF == PixelFormat::NV21 ? FKB_SRC_NV21 : PF == PixelFormat::P010 ? FKB_SRC_P010
+                       : PF == PixelFormat::P210 ? FKB_SRC_P210 : PF == PixelFormat::Y210 ? FKB_SRC_Y210 : FKB_SRC_UYVY;
         for (const auto& i : imgs) s.planes.push_back(SourcePlane{i.data, i.width, i.height, i.pitch, Rect(), false});
         return s;
     }
@@ -262,7 +267,9 @@ template <PixelFormat PF, ColorRange CR, ColorPrimitives CP, bool ALPHA = false,
     static_assert(CR == ColorRange::Full && !ALPHA, "only full-range conversions without alpha are on this path");
     struct C { void apply(Sender& s) const {
         if (!s.value_is_yuv) throw std::runtime_error("fkb200: ConvertYUVToRGB needs the value read by ReadYUV");
-        if (s.src_format != (PF == PixelFormat::NV12 ? FKB_SRC_NV12 : FKB_SRC_NV21)) throw std::runtime_error("fkb200: ConvertYUVToRGB's pixel format differs from ReadYUV's");
+        const int want = PF == PixelFormat::NV12 ? FKB_SRC_NV12 : PF == PixelFormat::NV21 ? FKB_SRC_NV21 : PF == PixelFormat::P010 ? FKB_SRC_P010
+                         : PF == PixelFormat::P210 ? FKB_SRC_P210 : PF == PixelFormat::Y210 ? FKB_SRC_Y210 : FKB_SRC_UYVY;
+        if (s.src_format != want) throw std::runtime_error("fkb200: ConvertYUVToRGB's pixel format differs from ReadYUV's");
         s.ops.push_back(detail::make_op(CP == ColorPrimitives::bt709 ? FKB_OP_YUV_TO_RGB_BT709_FULL
                                         : CP == ColorPrimitives::bt601 ? FKB_OP_YUV_TO_RGB_BT601_FULL : FKB_OP_YUV_TO_RGB_BT2020_FULL));
         s.value_is_yuv = false; s.value_is_float = true;

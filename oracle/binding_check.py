@@ -113,6 +113,10 @@ def deinterlace(mode, src, w, h, pitch, kind, mul, out, stream=None):
     _check(lib().fklbind_deinterlace(mode, _p(src), w, h, pitch, kind, _f3(mul), _p(out), _p(stream)))
 
 
+def yuv_layout(mode, fmt, frame, w, h, pitch, dw, dh, mul, out, stream=None):
+    _check(lib().fklbind_yuv_layout(mode, fmt, _p(frame), w, h, pitch, dw, dh, _f3(mul), _p(out), _p(stream)))
+
+
 def circular_describe6(order, frame, w, h, pitch, rect, dw, dh, bg, d0, mean, std, visible, hidden, first):
     """Lowers the two sequences CircularTensor::update builds for a 6-plane planar tensor; the plan is kept for last_plan()."""
     r = (C.c_int * 4)(*[int(x) for x in rect])

@@ -80,6 +80,19 @@ static px3 read_tap(const fkb_plane* pl, int src_format, int a, int b) {
     } else if (src_format == FKB_SRC_F32X3) {
         const float* p = (const float*)(base + (size_t)y * pl->src_pitch + (size_t)x * 12);
         r.v[0] = p[0]; r.v[1] = p[1]; r.v[2] = p[2];
+    } else if (src_format == FKB_SRC_P010 || src_format == FKB_SRC_P210) {
+        /* 16-bit luma plane, interleaved 16-bit chroma at data + pitch*height; 4:2:0 halves the chroma row, 4:2:2 does not
+           (color_conversion.h:329-346).  ConvertYUVToRGB first shifts the words right by 6 (:292, :177-180): done here. */
+        const uint16_t* luma = (const uint16_t*)(base + (size_t)y * pl->src_pitch) + x;
+        const int cy = src_format == FKB_SRC_P010 ? (y >> 1) : y;
+        const uint16_t* chroma = (const uint16_t*)(base + (size_t)pl->src_pitch * pl->src_height + (size_t)cy * pl->src_pitch) + 2 * (x >> 1);
+        r.v[0] = (float)(luma[0] >> 6); r.v[1] = (float)(chroma[0] >> 6); r.v[2] = (float)(chroma[1] >> 6);
+    } else if (src_format == FKB_SRC_Y210) { /* Y0 U Y1 V per two pixels (:360-372) */
+        const uint16_t* q = (const uint16_t*)(base + (size_t)y * pl->src_pitch) + 4 * (x >> 1);
+        r.v[0] = (float)(q[(x & 1) ? 2 : 0] >> 6); r.v[1] = (float)(q[1] >> 6); r.v[2] = (float)(q[3] >> 6);
+    } else if (src_format == FKB_SRC_UYVY) { /* U Y0 V Y1 per two pixels (:360-369) */
+        const uint8_t* q = base + (size_t)y * pl->src_pitch + 4 * (size_t)(x >> 1);
+        r.v[0] = (float)q[(x & 1) ? 3 : 1]; r.v[1] = (float)q[0]; r.v[2] = (float)q[2];
     } else { /* FKB_SRC_NV12, FKB_SRC_NV21 (the pair is stored V,U: color_conversion.h:357-359) */
         const uint8_t* luma = base + (size_t)y * pl->src_pitch + (size_t)x;
         const uint8_t* chroma = base + (size_t)pl->src_pitch * pl->src_height +
@@ -142,9 +155,13 @@ static px3 read_chain(const fkb_plane* pl, const fkb_sequence* sq, int a, int b)
     }
 }
 
-static px3 apply_op(px3 in, const fkb_op* op) {
+/* `src_format` matters to the YUV conversions only: the 10-bit layouts subtract 512 (and 64 from the luma for bt601)
+   instead of 128 (16) and scale the result by 64 instead of 1 (color_conversion.h:187-191, 234-252). */
+static px3 apply_op(px3 in, const fkb_op* op, int src_format) {
     px3 o = in;
     int c;
+    const int ten = src_format == FKB_SRC_P010 || src_format == FKB_SRC_P210 || src_format == FKB_SRC_Y210;
+    const float csub = ten ? 512.0f : 128.0f, ysub = ten ? 64.0f : 16.0f, scale = ten ? 64.0f : 1.0f;
     switch (op->opcode) {
         case FKB_OP_MUL: for (c = 0; c < 3; ++c) o.v[c] = in.v[c] * op->p[c]; break; /* arithmetic.h:71 */
         case FKB_OP_SUB: for (c = 0; c < 3; ++c) o.v[c] = in.v[c] - op->p[c]; break; /* arithmetic.h:58 */
@@ -169,24 +186,24 @@ static px3 apply_op(px3 in, const fkb_op* op) {
         case FKB_OP_YUV_TO_RGB_BT709_FULL: {             /* color_conversion.h:265-308, :143-146 */
             /* (Y, U-128, V-128) times the matrix rows, each row reduced left to right
                (algebraic.h:58-64, cuda_vector.h:113-126), then scaled by 1.0f (:241-243). */
-            const float y = in.v[0], u = in.v[1] - 128.0f, v = in.v[2] - 128.0f;
-            o.v[0] = ((y * 1.0f + u * 0.0f) + v * 1.5748f) * 1.0f;
-            o.v[1] = ((y * 1.0f + u * -0.1873f) + v * -0.4681f) * 1.0f;
-            o.v[2] = ((y * 1.0f + u * 1.8556f) + v * 0.0f) * 1.0f;
+            const float y = in.v[0], u = in.v[1] - csub, v = in.v[2] - csub;
+            o.v[0] = ((y * 1.0f + u * 0.0f) + v * 1.5748f) * scale;
+            o.v[1] = ((y * 1.0f + u * -0.1873f) + v * -0.4681f) * scale;
+            o.v[2] = ((y * 1.0f + u * 1.8556f) + v * 0.0f) * scale;
             break;
         }
         case FKB_OP_YUV_TO_RGB_BT601_FULL: {             /* :137-140, luma offset :266-269 */
-            const float y = in.v[0] - 16.0f, u = in.v[1] - 128.0f, v = in.v[2] - 128.0f;
-            o.v[0] = ((y * 1.164383562f + u * 0.0f) + v * 1.596026786f) * 1.0f;
-            o.v[1] = ((y * 1.164383562f + u * -0.39176229f) + v * -0.812967647f) * 1.0f;
-            o.v[2] = ((y * 1.164383562f + u * 2.017232143f) + v * 0.0f) * 1.0f;
+            const float y = in.v[0] - ysub, u = in.v[1] - csub, v = in.v[2] - csub;
+            o.v[0] = ((y * 1.164383562f + u * 0.0f) + v * 1.596026786f) * scale;
+            o.v[1] = ((y * 1.164383562f + u * -0.39176229f) + v * -0.812967647f) * scale;
+            o.v[2] = ((y * 1.164383562f + u * 2.017232143f) + v * 0.0f) * scale;
             break;
         }
         case FKB_OP_YUV_TO_RGB_BT2020_FULL: {            /* :165-168 */
-            const float y = in.v[0], u = in.v[1] - 128.0f, v = in.v[2] - 128.0f;
-            o.v[0] = ((y * 1.0f + u * 0.0f) + v * 1.4746f) * 1.0f;
-            o.v[1] = ((y * 1.0f + u * -0.16455312684366f) + v * -0.57135312684366f) * 1.0f;
-            o.v[2] = ((y * 1.0f + u * 1.8814f) + v * 0.0f) * 1.0f;
+            const float y = in.v[0], u = in.v[1] - csub, v = in.v[2] - csub;
+            o.v[0] = ((y * 1.0f + u * 0.0f) + v * 1.4746f) * scale;
+            o.v[1] = ((y * 1.0f + u * -0.16455312684366f) + v * -0.57135312684366f) * scale;
+            o.v[2] = ((y * 1.0f + u * 1.8814f) + v * 0.0f) * scale;
             break;
         }
         default: break;
@@ -197,7 +214,7 @@ static px3 apply_op(px3 in, const fkb_op* op) {
 static px3 read_pre(const fkb_plane* pl, const fkb_sequence* sq, int n_pre, int a, int b) {
     px3 t = read_chain(pl, sq, a, b);
     int k;
-    for (k = 0; k < n_pre; ++k) t = apply_op(t, &sq->ops[k]);
+    for (k = 0; k < n_pre; ++k) t = apply_op(t, &sq->ops[k], sq->src_format);
     return t;
 }
 
@@ -307,7 +324,7 @@ int fkl_oracle_run_range(const fkb_plan_desc* d, int first, int count, int host_
                         v = interpolate(pl, sq, sq->n_pre_ops, sx, sy, host_branch);
                     }
                 }
-                for (k = first_post; k < sq->n_ops; ++k) v = apply_op(v, &sq->ops[k]);
+                for (k = first_post; k < sq->n_ops; ++k) v = apply_op(v, &sq->ops[k], sq->src_format);
                 write_px(pl, sq->dst_format, x, y, v);
             }
         }

@@ -86,6 +86,22 @@ int border_crop_resize(int mode, const void* src, int w, int h, int pitch, const
         RawPtr<ND::_2D, float3>{reinterpret_cast<float3*>(out), PtrDims<ND::_2D>((uint)dw, (uint)dh, (uint)(dw * 12))}));
 }
 
+/* ReadYUV<PF> -> ConvertYUVToRGB<PF, Full, bt601, false, float3> -> Resize dw x dh -> Mul -> PerThreadWrite<float3>, one image of
+   a layout beyond NV12 / NV21.  format as fkb_src_format: 5 P010, 6 P210, 7 Y210, 8 UYVY. */
+template <PixelFormat PF>
+int yuv_layout_chain(int mode, const void* frame, int w, int h, int pitch, int dw, int dh, const float* mul, float* out, void* stream) {
+    using Img = Image<PF>;
+    using Base = typename Img::BaseType;
+    Ptr<ND::_2D, Base> view(reinterpret_cast<Base*>(const_cast<void*>(frame)), PtrDims<ND::_2D>((uint)w, (uint)h, (uint)pitch), MemType::Device, 0);
+    const Img img(view, (uint)w, (uint)h);
+    const auto sender = ReadYUV<PF>::build(img)
+                            .then(ConvertYUVToRGB<PF, ColorRange::Full, ColorPrimitives::bt601, false, float3>::build())
+                            .then(Resize<LINEAR>::build(Size(dw, dh)))
+                            .then(Mul<float3>::build(f3(mul)));
+    return run(mode, stream, sender, PerThreadWrite<ND::_2D, float3>::build(
+        RawPtr<ND::_2D, float3>{reinterpret_cast<float3*>(out), PtrDims<ND::_2D>((uint)dw, (uint)dh, (uint)(dw * 12))}));
+}
+
 }  // namespace
 
 extern "C" {
@@ -251,6 +267,18 @@ int fklbind_deinterlace(int mode, const void* src, int w, int h, int pitch, int 
     if (kind == 1) return run(mode, stream, Deinterlace<DeinterlaceType::BLEND>::build(read).then(Mul<float3>::build(f3(mul))), write);
     const auto lin = kind == 2 ? DeinterlaceLinear::USE_EVEN : DeinterlaceLinear::USE_ODD;
     return run(mode, stream, Deinterlace<DeinterlaceType::INTER_LINEAR>::build(lin, read).then(Mul<float3>::build(f3(mul))), write);
+}
+
+/* format as fkb_src_format: 5 P010, 6 P210, 7 Y210, 8 UYVY */
+int fklbind_yuv_layout(int mode, int format, const void* frame, int w, int h, int pitch, int dw, int dh, const float* mul, float* out,
+                       void* stream) {
+    switch (format) {
+        case 5: return yuv_layout_chain<PixelFormat::P010>(mode, frame, w, h, pitch, dw, dh, mul, out, stream);
+        case 6: return yuv_layout_chain<PixelFormat::P210>(mode, frame, w, h, pitch, dw, dh, mul, out, stream);
+        case 7: return yuv_layout_chain<PixelFormat::Y210>(mode, frame, w, h, pitch, dw, dh, mul, out, stream);
+        case 8: return yuv_layout_chain<PixelFormat::UYVY>(mode, frame, w, h, pitch, dw, dh, mul, out, stream);
+        default: g_error = "unknown layout"; return -1;
+    }
 }
 
 /* ---- the reference's own CircularTensor class (core/data/circular_tensor.h), its update() running through the binding ---- */

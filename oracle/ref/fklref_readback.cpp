@@ -41,9 +41,52 @@ int border_dispatch(int border, const uint8_t* src, int w, int h, int pitch, con
     }
 }
 
+/* ReadYUV<PF> -> ConvertYUVToRGB<PF, Full, CP, false, float3> [-> Resize(dw, dh)] -> Mul -> PerThreadWrite<float3>, one image.
+   The view's data height is the image height, so that a chroma plane is addressed at data + pitch * h
+   (color_conversion.h:336-341); its element type is the format's base type (uchar, or ushort for the 10-bit formats). */
+template <PixelFormat PF, ColorPrimitives CP>
+void yuv_chain(const void* frame, int w, int h, int pitch, int dw, int dh, const float* mul, float* out) {
+    RefStream stream = make_stream();
+    using Img = Image<PF>;
+    using Base = typename Img::BaseType;
+    Ptr<ND::_2D, Base> view(reinterpret_cast<Base*>(const_cast<void*>(frame)), PtrDims<ND::_2D>((uint)w, (uint)h, (uint)pitch), REF_MEM, 0);
+    const Img img(view, (uint)w, (uint)h);
+    const auto converted = ReadYUV<PF>::build(img).then(ConvertYUVToRGB<PF, ColorRange::Full, CP, false, float3>::build());
+    if (dw == w && dh == h) {
+        executeOperations<RefDPP>(stream, converted.then(Mul<float3>::build(f3(mul))), PerThreadWrite<ND::_2D, float3>::build(raw_f32x3(out, w, h, w * 12)));
+    } else {
+        executeOperations<RefDPP>(stream, converted.then(Resize<LINEAR>::build(Size(dw, dh))).then(Mul<float3>::build(f3(mul))),
+                                  PerThreadWrite<ND::_2D, float3>::build(raw_f32x3(out, dw, dh, dw * 12)));
+    }
+    finish(stream);
+}
+template <PixelFormat PF>
+int yuv_chain_primitives(int primitives, const void* frame, int w, int h, int pitch, int dw, int dh, const float* mul, float* out) {
+    switch (primitives) {
+        case 0: yuv_chain<PF, ColorPrimitives::bt709>(frame, w, h, pitch, dw, dh, mul, out); return 0;
+        case 1: yuv_chain<PF, ColorPrimitives::bt601>(frame, w, h, pitch, dw, dh, mul, out); return 0;
+        case 2: yuv_chain<PF, ColorPrimitives::bt2020>(frame, w, h, pitch, dw, dh, mul, out); return 0;
+        default: return -1;
+    }
+}
+
 }  // namespace
 
 extern "C" {
+
+/* One image of a YUV layout beyond NV12 / NV21, converted to RGB, optionally resized, multiplied.  format: 5 P010 (4:2:0,
+   10 bits in the top of 16, luma plane then interleaved chroma), 6 P210 (the same, 4:2:2), 7 Y210 (packed 4:2:2, 16-bit
+   Y0 U Y1 V), 8 UYVY (packed 4:2:2, 8-bit U Y0 V Y1); primitives 0 bt709, 1 bt601, 2 bt2020.  No resize when dw x dh = w x h. */
+int FKLREF_FN(yuv_format_chain)(int format, int primitives, const void* frame, int w, int h, int pitch, int dw, int dh, const float* mul,
+                                float* out) {
+    switch (format) {
+        case 5: return yuv_chain_primitives<PixelFormat::P010>(primitives, frame, w, h, pitch, dw, dh, mul, out);
+        case 6: return yuv_chain_primitives<PixelFormat::P210>(primitives, frame, w, h, pitch, dw, dh, mul, out);
+        case 7: return yuv_chain_primitives<PixelFormat::Y210>(primitives, frame, w, h, pitch, dw, dh, mul, out);
+        case 8: return yuv_chain_primitives<PixelFormat::UYVY>(primitives, frame, w, h, pitch, dw, dh, mul, out);
+        default: return -1;
+    }
+}
 
 /* PerThreadRead<uchar3> -> BorderReader<border> -> Crop(rect, may reach beyond the image) -> PerThreadWrite<uchar3>.
    border: 1 CONSTANT(value) 2 REPLICATE 3 REFLECT 4 WRAP 5 REFLECT_101. */

@@ -239,6 +239,16 @@ def deinterlace(src, kind, mul, flavour="device_branch"):
     return out
 
 
+def yuv_format_chain(frame, fmt, primitives, w, h, dw, dh, mul, flavour="device_branch"):
+    """ReadYUV<PF> -> ConvertYUVToRGB<PF, Full, CP, false, float3> [-> Resize(dw, dh)] -> Mul -> PerThreadWrite<float3>.
+    frame: 2-D array of the layout's words (uint16 for P010 / P210 / Y210, uint8 for UYVY), rows one pitch apart; fmt as
+    fkb_src_format (5 P010, 6 P210, 7 Y210, 8 UYVY); primitives 0 bt709, 1 bt601, 2 bt2020.  No resize when dw x dh = w x h."""
+    out = np.empty((dh, dw, 3), np.float32)
+    if lib(flavour).fklref_yuv_format_chain(fmt, primitives, C.c_void_p(frame.ctypes.data), w, h, frame.strides[0], dw, dh, _f3(mul), _f32(out)) != 0:
+        raise ValueError("this layout / matrix pair is not instantiated in the reference wrapper")
+    return out
+
+
 def resize_params(sw, sh, dw, dh, preserve_ar, flavour="device_branch"):
     fxy = (C.c_float * 2)()
     roi = (C.c_int * 4)()

@@ -125,6 +125,49 @@ def default_planes_case(name, seed, w, h, mode, dst_fmt, n=5, used=3):
     return Case(name, sources, {"out": out}, build, float_outputs=dpx == 12)
 
 
+def yuv_layout_image(rng, fmt, w, h, pitch_pad=0):
+    """A random image of one of the YUV layouts beyond NV12 / NV21 as a 2-D array of its words, rows one pitch apart
+    (pitch a multiple of 8 bytes).  The 10-bit layouts carry their value in the top ten bits and noise in the low six,
+    which the conversion must shift away."""
+    pairs = (w + 1) // 2
+    if fmt == abi.SRC_UYVY:
+        row_words, rows, dtype = 4 * pairs, h, np.uint8
+    elif fmt == abi.SRC_Y210:
+        row_words, rows, dtype = 4 * pairs, h, np.uint16
+    elif fmt == abi.SRC_P010:
+        row_words, rows, dtype = 2 * pairs, h + (h + 1) // 2, np.uint16
+    else:  # P210
+        row_words, rows, dtype = 2 * pairs, 2 * h, np.uint16
+    item = np.dtype(dtype).itemsize
+    pitch_words = (-(-(row_words * item + pitch_pad) // 8) * 8) // item
+    img = rng.integers(0, 256 if dtype == np.uint8 else 65536, (rows, pitch_words), dtype=dtype)
+    return img
+
+
+YUV_CONVERSIONS = (abi.OP_YUV_TO_RGB_BT709_FULL, abi.OP_YUV_TO_RGB_BT601_FULL, abi.OP_YUV_TO_RGB_BT2020_FULL)
+
+
+def yuv_layout_case(name, seed, fmt, primitives, w, h, dw, dh, post_ops, mode=None, crop=None, pitch_pad=0, n=2):
+    """ReadYUV<P010 | P210 | Y210 | UYVY> -> ConvertYUVToRGB -> [Resize] -> post_ops -> float3, a small batch."""
+    rng = np.random.default_rng(seed)
+    sources = {f"img{i}": yuv_layout_image(rng, fmt, w, h, pitch_pad) for i in range(n)}
+    pitch = sources["img0"].strides[0]
+    resize = (dw, dh) != ((crop[2], crop[3]) if crop else (w, h))
+    mode = mode if mode is not None else (abi.RESIZE_IGNORE_AR if resize else abi.RESIZE_NONE)
+    out = np.zeros((n, dh, dw * 12), np.uint8)
+
+    def build(ptr):
+        plan = abi.HostPlan()
+        seq = plan.add_sequence(fmt, abi.DST_F32X3_PACKED, mode, [op(YUV_CONVERSIONS[primitives])] + list(post_ops), n_pre_ops=1,
+                                background=(5.0, 6.0, 7.0))
+        for i in range(n):
+            plan.add_plane(src=ptr(f"img{i}"), src_width=w, src_height=h, src_pitch=pitch, crop=crop, dst=ptr("out") + i * dh * dw * 12,
+                           dst_width=dw, dst_height=dh, dst_pitch=dw * 12, sequence=seq)
+        return plan
+
+    return Case(name, sources, {"out": out}, build, float_outputs=True)
+
+
 def readback_case(name, seed, w, h, dw, dh, mode, dst_fmt=abi.DST_F32X3_PACKED, ops=(), n_pre=0, crop=None, border=0,
                   border_value=(0.0, 0.0, 0.0), deinterlace=0, transform=None, src_fmt=abi.SRC_U8X3, n=2):
     """BorderReader / Deinterlace / Warping chains on a small batch of images (the one-pixel-per-thread body)."""
@@ -293,6 +336,14 @@ def small_cases():
         default_planes_case("default_planes_flat", 91, 64, 32, abi.RESIZE_NONE, abi.DST_F32X3_PACKED),
         default_planes_case("default_planes_flat_u8", 92, 53, 37, abi.RESIZE_NONE, abi.DST_U8X3_PACKED),
         default_planes_case("default_planes_resize", 93, 64, 48, abi.RESIZE_PRESERVE_AR, abi.DST_F32X3_PACKED),
+        # YUV layouts beyond NV12 / NV21: read and converted by the one-pixel-per-thread body
+        *[yuv_layout_case(f"yuv_layout{f}_primitives{p}", 130 + 3 * f + p, f, p, 38, 22, 38, 22, [op(abi.OP_MUL, (1.0, 0.5, 2.0))])
+          for f in (abi.SRC_P010, abi.SRC_P210, abi.SRC_Y210, abi.SRC_UYVY) for p in (0, 1, 2)],
+        *[yuv_layout_case(f"yuv_layout{f}_resize", 160 + f, f, f % 3, 64, 36, 28, 20, [op(abi.OP_DIV, 255.0)], pitch_pad=24)
+          for f in (abi.SRC_P010, abi.SRC_P210, abi.SRC_Y210, abi.SRC_UYVY)],
+        yuv_layout_case("yuv_p010_crop_preserve_ar_odd", 170, abi.SRC_P010, 0, 41, 27, 36, 24, [op(abi.OP_SUB, 3.0)], mode=abi.RESIZE_PRESERVE_AR,
+                        crop=(3, 5, 31, 17)),
+        yuv_layout_case("yuv_uyvy_crop_odd_origin", 171, abi.SRC_UYVY, 1, 40, 24, 21, 13, [], crop=(7, 3, 21, 13)),
         # BorderReader under a padded crop, Warping, Deinterlace
         *[readback_case(f"border{b}_padded_crop_u8", 100 + b, 40, 24, 60, 37, abi.RESIZE_NONE, dst_fmt=abi.DST_U8X3_PACKED,
                         crop=(-7, -5, 60, 37), border=b, border_value=(9.0, 99.0, 199.0)) for b in range(1, 6)],

@@ -135,6 +135,18 @@ def main():
     for k in (1, 2, 3):
         fix[f"deinterlace{k}"] = ref.deinterlace(img4, k, (1.0, 0.5, 2.0))
     np.savez_compressed(OUT / "readback_ops.npz", **fix)
+    # --- YUV layouts beyond NV12 / NV21: P010, P210, Y210, UYVY (own seed) -------------------------------------
+    from fusedkernellibrary_b200 import abi
+    from tests import cases as tc
+    rng5 = np.random.default_rng(20240611)
+    fix = {}
+    for fmt in (abi.SRC_P010, abi.SRC_P210, abi.SRC_Y210, abi.SRC_UYVY):
+        img = tc.yuv_layout_image(rng5, fmt, 38, 22, pitch_pad=16)
+        fix[f"src{fmt}"] = img
+        for prim in (0, 1, 2):
+            fix[f"fmt{fmt}_prim{prim}"] = ref.yuv_format_chain(img, fmt, prim, 38, 22, 38, 22, (1.0, 0.5, 2.0))
+        fix[f"fmt{fmt}_resize"] = ref.yuv_format_chain(img, fmt, fmt % 3, 38, 22, 27, 15, (1.0, 0.5, 2.0))
+    np.savez_compressed(OUT / "yuv_layouts.npz", **fix)
     print("golden vectors written to", OUT)
 
 

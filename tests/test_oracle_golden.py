@@ -297,3 +297,26 @@ def test_border_reader_warping_and_deinterlace(oracle_port):
         oracle_port.run(_readback_plan(src, outf, dst_fmt=abi.DST_F32X3_PACKED, mode=abi.RESIZE_NONE, dw=src.shape[1], dh=src.shape[0],
                                        ops=mul, deinterlace=k))
         assert _same(outf, g[f"deinterlace{k}"]), f"deinterlace {k}"
+
+
+def test_yuv_layouts_beyond_nv12(oracle_port):
+    """ReadYUV<P010 | P210 | Y210 | UYVY> -> ConvertYUVToRGB<PF, Full, bt709 | bt601 | bt2020> (color_conversion.h:284-372):
+    the 10-bit layouts shifted right by 6, offsets 512 / 64, result times 64; against the reference build's output."""
+    g = np.load(GOLD / "yuv_layouts.npz")
+    conv = (abi.OP_YUV_TO_RGB_BT709_FULL, abi.OP_YUV_TO_RGB_BT601_FULL, abi.OP_YUV_TO_RGB_BT2020_FULL)
+    for fmt in (abi.SRC_P010, abi.SRC_P210, abi.SRC_Y210, abi.SRC_UYVY):
+        img = np.ascontiguousarray(g[f"src{fmt}"])
+
+        def run(prim, dw, dh):
+            out = np.zeros((dh, dw, 3), np.float32)
+            plan = abi.HostPlan()
+            mode = abi.RESIZE_NONE if (dw, dh) == (38, 22) else abi.RESIZE_IGNORE_AR
+            seq = plan.add_sequence(fmt, abi.DST_F32X3_PACKED, mode, [op(conv[prim]), op(abi.OP_MUL, (1.0, 0.5, 2.0))], n_pre_ops=1)
+            plan.add_plane(src=img.ctypes.data, src_width=38, src_height=22, src_pitch=img.strides[0], dst=out.ctypes.data, dst_width=dw,
+                           dst_height=dh, dst_pitch=dw * 12, sequence=seq)
+            oracle_port.run(plan)
+            return out
+
+        for prim in (0, 1, 2):
+            assert _same(run(prim, 38, 22), g[f"fmt{fmt}_prim{prim}"]), (fmt, prim)
+        assert _same(run(fmt % 3, 27, 15), g[f"fmt{fmt}_resize"]), fmt

@@ -154,6 +154,17 @@ def test_circular_tensor_update_sequences_lower_to_the_library_plan(fkb_lib):
         ct.destroy()
 
 
+def test_yuv_layouts_lower_to_the_harness_plans(fkb_lib):
+    frame, out = 0x10000000, 0x20000000
+    for fmt in (abi.SRC_P010, abi.SRC_P210, abi.SRC_Y210, abi.SRC_UYVY):
+        bc.yuv_layout(bc.DESCRIBE, fmt, frame, 64, 36, 256, 28, 20, (1.0, 0.5, 2.0), out)
+        want = abi.HostPlan()
+        seq = want.add_sequence(fmt, abi.DST_F32X3_PACKED, abi.RESIZE_IGNORE_AR, [op(abi.OP_YUV_TO_RGB_BT601_FULL), op(abi.OP_MUL, (1.0, 0.5, 2.0))],
+                                n_pre_ops=1)
+        want.add_plane(src=frame, src_width=64, src_height=36, src_pitch=256, dst=out, dst_width=28, dst_height=20, dst_pitch=28 * 12, sequence=seq)
+        _assert_same_plan(want, fkb_lib)
+
+
 READBACK_RECT = (-7, -5, 60, 37)
 AFFINE = (0.8, 0.25, -3.0, -0.2, 0.7, 2.5, 0.0, 0.0, 1.0)
 PERSPECTIVE = (0.9, 0.1, -2.0, 0.05, 0.8, 1.0, 0.002, 0.001, 1.0)
@@ -225,6 +236,23 @@ def test_the_reference_circular_tensor_class_updates_through_the_binding(fkb_lib
             assert np.array_equal(tc.bits(b[sel]), tc.bits(ref_v.cpu().numpy()[sel])), f"update {k}: differs from the reference kernel"
     theirs.destroy()
     ours.destroy()
+
+
+@pytest.mark.gpu
+@pytest.mark.skipif(not ref.available(), reason="oracle/_ref not built")
+def test_yuv_layouts_through_the_binding_equal_the_reference_cpu_backend(fkb_lib):
+    torch = pytest.importorskip("torch")
+    from tests import cases as tc
+    rng = np.random.default_rng(306)
+    stream = torch.cuda.Stream()
+    for fmt in (abi.SRC_P010, abi.SRC_P210, abi.SRC_Y210, abi.SRC_UYVY):
+        img = tc.yuv_layout_image(rng, fmt, 96, 54, pitch_pad=8)
+        d_img = torch.from_numpy(img.view(np.uint8).reshape(-1).copy()).cuda()
+        d_out = torch.zeros((30, 50, 3), dtype=torch.float32, device="cuda")
+        bc.yuv_layout(bc.EXECUTE, fmt, d_img.data_ptr(), 96, 54, img.strides[0], 50, 30, (1.0, 0.5, 2.0), d_out.data_ptr(), stream.cuda_stream)
+        assert abi.async_check(stream.cuda_stream) == 0
+        want = ref.yuv_format_chain(img, fmt, 1, 96, 54, 50, 30, (1.0, 0.5, 2.0))
+        assert np.array_equal(tc.bits(d_out.cpu().numpy()), tc.bits(want)), fmt
 
 
 @pytest.mark.gpu
