@@ -1480,7 +1480,7 @@ __device__ __forceinline__ void body_nv12_staged(const DevPlane& P, const DevSeq
         const bool col1 = col1_a || col1_b;
         const float2 wx0 = make_float2(axa.w0, axb.w0), wx1 = make_float2(axa.w1, axb.w1);
         const bool plain = in_a && in_b && valid_b;
-#pragma unroll 1
+#pragma unroll 2
         for (int y = ya + (int)slot; y <= yb; y += (int)rs, rt += 2 * rs, out_a += row_step) {
             const float4 rows = rt[0], wy = rt[1];
             const uint32_t lr0 = __float_as_uint(rows.x), lr1 = __float_as_uint(rows.y);
@@ -1635,8 +1635,9 @@ __device__ __forceinline__ void check_begin(const DevPlane&, const DevSeq&, cons
 #endif
 
 /* Resident blocks per SM that the compiler must leave registers for.  Measured on B200: the staged
- * uchar3 resize is fastest with four blocks (64 registers), the staged NV12 resize with five, plans
- * of several classes with four as well (the flat bodies hold four runs per thread and the
+ * uchar3 resize runs five blocks (48 registers; four at 64 registers take the same time), the staged NV12
+ * resize four (two rows of taps in flight per thread need 64 registers), plans
+ * of several classes four as well (the flat bodies hold four runs per thread and the
  * interpolating body its taps: at six blocks and 40 registers both spilled; four groups of 16 images
  * 1920x1080 took 0.319 ms at six, 0.294 at five, 0.285 at four); the bodies that read taps straight
  * from global memory keep all their loads in flight in registers instead.  The flat bodies run
@@ -1644,7 +1645,7 @@ __device__ __forceinline__ void check_begin(const DevPlane&, const DevSeq&, cons
  * unconstrained (three to four blocks) and 35.9 us at five, 64 alternating Add/Mul 76.6 and 65.7. */
 constexpr int min_blocks_of(uint32_t cls) {
     return (cls == CLASS_RESIZE_U8_PLANAR_STAGED || cls == CLASS_RESIZE_U8_PACKED_STAGED) ? 5
-           : cls == CLASS_RESIZE_NV12_PACKED_STAGED ? 5
+           : cls == CLASS_RESIZE_NV12_PACKED_STAGED ? 4
            : cls == CLASS_MIXED ? 4
            : (cls == CLASS_FLAT_U8_F32 || cls == CLASS_FLAT_U8_U8 || cls == CLASS_FLAT_F32_F32) ? 5 : 1;
 }

@@ -254,7 +254,11 @@ constexpr uint32_t STAGED_MAX_STAGE_BYTES = 40 * 1024u; /* five blocks of it fit
 constexpr uint32_t TURN_BYTES_PER_WARP_PACKED = 2 * 96 * 4;
 constexpr uint32_t STAGED_MAX_STAGE_BYTES_PACKED = 34 * 1024u;
 constexpr uint32_t STAGED_HEADER_BYTES = 16 + STAGED_MAX_ROWS * 32;
-constexpr uint32_t NV12_MAX_STAGE_BYTES = 40 * 1024u; /* luma and chroma rows of a band tile; five blocks per SM */
+constexpr uint32_t NV12_MAX_STAGE_BYTES = 50 * 1024u; /* luma and chroma rows of a band tile; four blocks per SM.  The body is bound
+                                                         by the latency of its shared-memory taps: two rows in flight per thread at 64 registers and
+                                                         four blocks measured 100.4 us on 32 4K frames against 102.5 with one row at 48 registers
+                                                         and five blocks (two rows at 48 registers spill: 106.2), and 97.5 with the larger stage
+                                                         that four blocks leave room for (three rows 103.2; four rows at three blocks 115.5). */
 constexpr uint32_t NV12_MAX_SPAN = 256;           /* source rows between a band's first and last tap */
 constexpr uint32_t STAGED_FOLD_BG_GROUPS = 1024;  /* at most this many outside groups: no store-only items */
 constexpr uint32_t STATUS_STAGED_WAIT_TIMEOUT = 1; /* a bulk copy did not complete in time        */
