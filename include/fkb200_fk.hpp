@@ -353,6 +353,49 @@ inline void executeDivergentOperations(Stream& stream, const std::vector<Operati
     detail::launch(stream, low, op_store);
 }
 
+/* ---- CircularTensor (core/data/circular_tensor.h:86-161): the newest BATCH results of a chain, kept in order ----
+ * update(stream, sender, receiver) runs the sender once for the new image and leaves the tensor's planes as the last
+ * BATCH results, newest first or oldest first, in one launch (fkb_circular_tensor_update).  The tensor owns its device
+ * memory, like the reference's; ptr() is what TensorWrite / TensorSplit take as the receiver of update().  Only the
+ * Standard colour-plane mode is here. */
+enum class CircularTensorOrder { NewestFirst, OldestFirst };
+enum class ColorPlanes { Standard };
+template <typename T, int COLOR_PLANES, int BATCH, CircularTensorOrder CT_ORDER, ColorPlanes CP_MODE = ColorPlanes::Standard>
+class CircularTensor {
+    static_assert(COLOR_PLANES == 3 || COLOR_PLANES == 1, "three colour planes of a base type (TensorSplit) or one plane of a three-channel type (TensorWrite)");
+public:
+    CircularTensor(unsigned width, unsigned height, int dst_format) : width_(width), height_(height), dst_format_(dst_format) {
+        fkb_circular_tensor_desc d{};
+        d.width = width; d.height = height; d.batch = BATCH;
+        d.order = CT_ORDER == CircularTensorOrder::NewestFirst ? FKB_CIRCULAR_NEWEST_FIRST : FKB_CIRCULAR_OLDEST_FIRST;
+        d.dst_format = dst_format;
+        check(fkb_circular_tensor_create(&d, &ct_));
+    }
+    CircularTensor(const CircularTensor&) = delete;
+    CircularTensor& operator=(const CircularTensor&) = delete;
+    ~CircularTensor() { fkb_circular_tensor_destroy(ct_); }
+    /* the visible tensor as a receiver's view: BATCH dense planes */
+    RawTensor<T> ptr() const {
+        const unsigned px = dst_format_ == FKB_DST_U8X3_PACKED ? 3u : dst_format_ == FKB_DST_F32_PLANAR3 ? 4u : 12u;
+        return RawTensor<T>{static_cast<T*>(fkb_circular_tensor_data(ct_)), width_, height_, (unsigned)BATCH, width_ * px};
+    }
+    void update(Stream& stream, const Sender& sender, const Receiver& receiver) {
+        if (receiver.data != fkb_circular_tensor_data(ct_) || receiver.dst_format != dst_format_)
+            throw std::runtime_error("fkb200: update() takes a receiver built on this tensor's ptr()");
+        if (sender.planes.size() != 1) throw std::runtime_error("fkb200: update() takes the chain of one new image");
+        detail::Lowered low;
+        std::vector<std::vector<fkb_op>> op_store;
+        Receiver one = receiver; one.planes = 1;
+        detail::lower_into(sender, one, low, op_store);
+        low.seqs[0].ops = op_store[0].empty() ? nullptr : op_store[0].data();
+        check(fkb_circular_tensor_update(ct_, &low.seqs[0], &low.planes[0], stream.getCUDAStream()));
+    }
+private:
+    fkb_circular_tensor* ct_ = nullptr;
+    unsigned width_, height_;
+    int dst_format_;
+};
+
 }  // namespace fk
 }  // namespace fkb200
 

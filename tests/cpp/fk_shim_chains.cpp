@@ -161,7 +161,20 @@ int main(int argc, char** argv) {
             .then(Div<float3>::build(make_set<float3>(255.f)));
         executeOperations<TransformDPP<>>(stream, fromNV21, TensorWrite<float3>::build(RawTensor<float3>{d_rgb21, 40, 22, 2, 40 * 12}));
 
+        // --- a circular tensor of the newest three normalised crops (CircularTensor::update, one launch per new image) ---
+        CircularTensor<float, 3, 3, CircularTensorOrder::NewestFirst> window(64, 48, FKB_DST_F32_PLANAR3);
+        for (int k = 0; k < 4; ++k) {
+            const auto newest = PerThreadRead<ND::_2D, uchar3>::build(k % 2 ? RawPtr2D<uchar3>{d_frame1, 384, 216, 384 * 3} : inputImage)
+                .then(Crop<>::build(rects[k]))
+                .then(Resize<InterpolationType::INTER_LINEAR, AspectRatio::PRESERVE_AR>::build(Size(64, 48), backgroundColor))
+                .then(Div<float3>::build(make_set<float3>(255.f)))
+                .then(Sub<float3>::build(make_<float3>(0.485f, 0.456f, 0.406f)))
+                .then(Div<float3>::build(make_<float3>(0.229f, 0.224f, 0.225f)));
+            window.update(stream, newest, TensorSplit<float3>::build(window.ptr()));
+        }
+
         stream.sync();   // everything above was asynchronous on the stream
+        download(dir + "/out_window.bin", window.ptr().data, (size_t)3 * 3 * 64 * 48 * 4);
         download(dir + "/out_border.bin", d_border, (size_t)70 * 45 * 12);
         download(dir + "/out_warp.bin", d_warp, (size_t)100 * 64 * 12);
         download(dir + "/out_deint.bin", d_deint, (size_t)384 * 216 * 12);

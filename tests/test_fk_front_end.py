@@ -102,3 +102,8 @@ def test_front_end_chains_match_the_checker(shim_program, oracle_port, tmp_path)
     oracle_port.run(chains.nv12_resize_batch(frame_ptrs=[a.ctypes.data for a in nv], width=96, height=54, pitch=96, dst=want.ctypes.data,
                                              dst_width=40, dst_height=22, src_format=abi.SRC_NV21, conversion=abi.OP_YUV_TO_RGB_BT601_FULL))
     assert np.array_equal(tc.bits(got("out_nv21.bin", np.float32, want.shape)), tc.bits(want))
+    # the circular tensor after four updates, newest first: planes = crops 3, 2, 1 of the planar batch above
+    window = got("out_window.bin", np.float32, (3, 3, 48, 64))
+    planar = got("out_planar.bin", np.float32, (4, 3, 48, 64))
+    for z, k in enumerate((3, 2, 1)):
+        assert np.array_equal(tc.bits(window[z]), tc.bits(planar[k])), (z, k)
