@@ -753,13 +753,26 @@ __device__ __forceinline__ void body_flat(const DevPlane& P, const DevSeq& S, co
 
 /* Position idx of a row-major walk over rows of `per_row` cells, advanced `step` cells at a time
    with one division at the start instead of one per step. */
+/* n / d for d > 0 and a quotient below 2^22 (row, slot and tile indices): the quotient of the two numbers as floats is off by
+   at most one, which the remainder tells; ten instructions where the integer division takes three times as many, in a
+   block's prologue that runs once per few thousand pixels. */
+__device__ __forceinline__ uint32_t div_small(uint32_t n, uint32_t d) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(__uint2float_rn(d)));
+    uint32_t q = __float2uint_rz(__fmul_rn(__uint2float_rn(n), r));
+    const int32_t rem = (int32_t)(n - q * d);
+    if (rem < 0) --q;
+    else if ((uint32_t)rem >= d) ++q;
+    return q;
+}
+
 struct CellWalk {
     uint32_t r, c, dr, dc, per_row;
     /* `more`: whether any walker will advance at all (uniform); the step's division is skipped if not */
     __device__ __forceinline__ CellWalk(uint32_t idx, uint32_t step, uint32_t per_row_, bool more = true) : per_row(per_row_) {
-        r = idx / per_row; c = idx - r * per_row;
+        r = div_small(idx, per_row); c = idx - r * per_row;
         dr = 0; dc = 0;
-        if (more) { dr = step / per_row; dc = step - dr * per_row; }
+        if (more) { dr = div_small(step, per_row); dc = step - dr * per_row; }
     }
     __device__ __forceinline__ void advance() {
         r += dr; c += dc;
@@ -845,6 +858,38 @@ __device__ __forceinline__ void fill_cells(uint8_t* dst, uint32_t pitch, uint32_
     }
 }
 
+/* Default value over every row outside the region's rows, for a plane whose rows lie side by side in memory (pitch =
+ * row bytes): the cells above and below the region are two runs of 16-byte words, walked by the whole block without any
+ * row or column arithmetic.  A packed row is a multiple of three words long, so the channels of a word follow from its
+ * index in the walk: (k, k+1, k+2, k) mod 3. */
+template <bool PLANAR>
+__device__ __forceinline__ void fill_outside_rows_dense(uint8_t* dst, uint32_t cstride, uint32_t words_per_row, uint32_t rows_above,
+                                                        uint32_t region_rows, uint32_t rows_total, const float (&bg)[3]) {
+    const uint32_t top = rows_above * words_per_row, skip = region_rows * words_per_row, total = (rows_total - region_rows) * words_per_row;
+    if (PLANAR) {
+        const uint32_t step = blockDim.x;
+#pragma unroll 1
+        for (uint32_t idx = threadIdx.x; idx < total; idx += step) {
+            uint8_t* const d = dst + (size_t)(idx < top ? idx : idx + skip) * 16u;
+#pragma unroll
+            for (int ch = 0; ch < 3; ++ch) gst(reinterpret_cast<float4*>(d + (size_t)ch * cstride), make_float4(bg[ch], bg[ch], bg[ch], bg[ch]));
+        }
+    } else {
+        /* The walk's step is the largest multiple of three threads (the one or two threads beyond it sit out), so that all
+           words of a thread hold the same channels and the loop is a store and its address: with a few words per thread,
+           what surrounds the loop counts as much as the loop. */
+        const uint32_t step = blockDim.x - blockDim.x % 3u;
+        if (threadIdx.x < step) {
+            const uint32_t k3 = threadIdx.x % 3u;
+            const float4 word = make_float4(k3 == 0 ? bg[0] : k3 == 1 ? bg[1] : bg[2], k3 == 0 ? bg[1] : k3 == 1 ? bg[2] : bg[0],
+                                            k3 == 0 ? bg[2] : k3 == 1 ? bg[0] : bg[1], k3 == 0 ? bg[0] : k3 == 1 ? bg[1] : bg[2]);
+#pragma unroll 1
+            for (uint32_t idx = threadIdx.x; idx < total; idx += step)
+                gst(reinterpret_cast<float4*>(dst + (size_t)(idx < top ? idx : idx + skip) * 16u), word);
+        }
+    }
+}
+
 template <uint32_t CHAIN, int SRC, bool PLANAR>
 __device__ __forceinline__ void body_resize(const DevPlane& P, const DevSeq& S, const OpSlot* sops, uint32_t local) {
     /* plane fields used inside loops, copied out of shared memory once */
@@ -873,8 +918,8 @@ __device__ __forceinline__ void body_resize(const DevPlane& P, const DevSeq& S, 
     }
 
     const uint32_t tiles_x = P.tiles_x, gw = P.gw, rs = P.rs;
-    const uint32_t tile_y = local / tiles_x, tile_x = local - tile_y * tiles_x;
-    const uint32_t slot = threadIdx.x / gw, gi = threadIdx.x - slot * gw;
+    const uint32_t tile_y = div_small(local, tiles_x), tile_x = local - tile_y * tiles_x;
+    const uint32_t slot = div_small(threadIdx.x, gw), gi = threadIdx.x - slot * gw;
     const int row0 = y1 + (int)(tile_y * rs * RESIZE_ROWS_PER_THREAD); /* first row of this tile */
 
     if (slot < rs) {
@@ -1134,7 +1179,7 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
        clamped onto the first, interpolation.h:76): they are fetched as the three aligned words
        that hold them, shifted down to byte 0, and each byte is turned into a float by one byte
        permute (2^23 + b) and half of a packed subtraction. */
-    const uint32_t slot = threadIdx.x / gw, gi = threadIdx.x - slot * gw;
+    const uint32_t slot = div_small(threadIdx.x, gw), gi = threadIdx.x - slot * gw;
     const int xa = (int)(g_lo * PX_PER_THREAD + gi), xb = xa + (int)gw;
     const int x_end = (int)((g_lo + n_groups) * PX_PER_THREAD);
     const bool in_a = xa >= x1 && xa <= x2, in_b = xb >= x1 && xb <= x2;
@@ -1157,9 +1202,14 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
         if (n_side != 0)
             fill_cells<PLANAR>(dst, dst_pitch, dst_cstride, 0u, threadIdx.x, nthreads, 0xFFFFFFu, (uint32_t)(yb - ya + 1), n_side, g_lo, n_groups, bgv,
                                [&](uint32_t r) { return (uint32_t)ya + r; });
-        if (P.n_segs != 0 && local == P.roi_items - 1)
-            fill_cells<PLANAR>(dst, dst_pitch, dst_cstride, 0u, threadIdx.x, nthreads, 0xFFFFFFu, P.dst_h - n_rows, groups_per_row, 0u, 0u, bgv,
-                               [&](uint32_t r) { return (int)r < y1 ? r : r + n_rows; });
+        if (P.n_segs != 0 && local == P.roi_items - 1) {
+            const uint32_t words_per_row = groups_per_row * (PLANAR ? 1u : 3u);
+            if (dst_pitch == words_per_row * 16u)
+                fill_outside_rows_dense<PLANAR>(dst, dst_cstride, words_per_row, (uint32_t)y1, n_rows, P.dst_h, bgv);
+            else
+                fill_cells<PLANAR>(dst, dst_pitch, dst_cstride, 0u, threadIdx.x, nthreads, 0xFFFFFFu, P.dst_h - n_rows, groups_per_row, 0u, 0u, bgv,
+                                   [&](uint32_t r) { return (int)r < y1 ? r : r + n_rows; });
+        }
     };
     fill_background();
 
@@ -1316,7 +1366,7 @@ __device__ __forceinline__ void body_nv12_staged(const DevPlane& P, const DevSeq
     const uint32_t mbar = smem_addr(mbar_ptr);
 
     const uint32_t tiles_x = P.tiles_x, band_rows = P.seg_pixels, gw = P.gw, rs = P.rs;
-    const uint32_t band = local / tiles_x, tile_x = local - band * tiles_x;
+    const uint32_t band = div_small(local, tiles_x), tile_x = local - band * tiles_x;
     const int ya = y1 + (int)(band * band_rows);
     const int yb = min(ya + (int)band_rows - 1, y2);
     const int crop_h = P.crop_h, crop_w = P.crop_w, crop_x = P.crop_x, crop_y = P.crop_y;
@@ -1426,7 +1476,7 @@ __device__ __forceinline__ void body_nv12_staged(const DevPlane& P, const DevSeq
     }
 
     /* the thread's two columns */
-    const uint32_t slot = tid / gw, gi = tid - slot * gw;
+    const uint32_t slot = div_small(tid, gw), gi = tid - slot * gw;
     const int xa = c_base + (int)gi, xb = xa + (int)gw;
     const bool in_a = xa >= x1 && xa <= x2, in_b = xb >= x1 && xb <= x2;
     const bool valid_a = xa < x_end, valid_b = xb < x_end;

@@ -247,12 +247,6 @@ constexpr uint32_t STAGED_MIN_BAND_PIXELS = 448; /* bands of a plan with a small
 constexpr uint32_t SMALL_GRID_BLOCKS = 148;      /* fewer blocks than this (one per SM of a B200): shorter bands        */
 constexpr uint32_t STAGED_MAX_ROWS = 64;          /* output rows per band                        */
 constexpr uint32_t STAGED_MAX_STAGE_BYTES = 40 * 1024u; /* five blocks of it fit one SM */
-/* Packed float3 receivers of the staged bodies: every warp turns its pixels around in 192 words of shared memory
-   (two runs of 32 pixels) so that a store instruction writes whole 16-byte words side by side; the stage gives
-   up what those buffers take, and the threads across a region are a multiple of 32 so that a warp's pixels lie
-   side by side in one row. */
-constexpr uint32_t TURN_BYTES_PER_WARP_PACKED = 2 * 96 * 4;
-constexpr uint32_t STAGED_MAX_STAGE_BYTES_PACKED = 34 * 1024u;
 constexpr uint32_t STAGED_HEADER_BYTES = 16 + STAGED_MAX_ROWS * 32;
 constexpr uint32_t NV12_MAX_STAGE_BYTES = 50 * 1024u; /* luma and chroma rows of a band tile; four blocks per SM.  The body is bound
                                                          by the latency of its shared-memory taps: two rows in flight per thread at 64 registers and
