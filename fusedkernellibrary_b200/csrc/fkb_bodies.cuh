@@ -614,9 +614,22 @@ __device__ __forceinline__ void body_generic(const DevPlane& P, const DevSeq& S,
 /* ------------------------------------------------------------------------------------ */
 /* body: no geometry stage, four whole pixels per thread                                */
 /* ------------------------------------------------------------------------------------ */
+/* n / d for d > 0 and a quotient below 2^22 (row, slot and tile indices): the quotient of the two numbers as floats is off by
+   at most one, which the remainder tells; ten instructions where the integer division takes three times as many, in a
+   block's prologue that runs once per few thousand pixels. */
+__device__ __forceinline__ uint32_t div_small(uint32_t n, uint32_t d) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(__uint2float_rn(d)));
+    uint32_t q = __float2uint_rz(__fmul_rn(__uint2float_rn(n), r));
+    const int32_t rem = (int32_t)(n - q * d);
+    if (rem < 0) --q;
+    else if ((uint32_t)rem >= d) ++q;
+    return q;
+}
+
 template <uint32_t CHAIN, bool SRC_IS_U8, bool DST_IS_U8>
 __device__ __forceinline__ void body_flat(const DevPlane& P, const DevSeq& S, const OpSlot* sops, uint32_t local,
-                                          unsigned char* turn_mem) {
+                                          unsigned char* turn_mem, uint32_t prefetch_items = 0) {
     constexpr int SPX = SRC_IS_U8 ? 3 : 12;
     constexpr int DPX = DST_IS_U8 ? 3 : 12;
     constexpr int Q = flat_quads(SRC_IS_U8);
@@ -631,6 +644,21 @@ __device__ __forceinline__ void body_flat(const DevPlane& P, const DevSeq& S, co
     const uint32_t base = (local - seg * items_per_seg) * ITEM + threadIdx.x * PX_PER_THREAD;
     const uint8_t* const src_seg = P.src + (size_t)(P.crop_y + seg) * P.src_pitch + (size_t)P.crop_x * SPX;
     uint8_t* const dst_seg = P.dst + (size_t)seg * P.dst_pitch;
+
+    /* A chain of tens of operations per value: a block computes far longer than it loads, and with one resident block in
+       five loading at any time an SM has a few KB in flight where the memory needs tens (a 4K float3 image through 64
+       operations took 68 us against 36 us for its bytes and 43 us for its arithmetic, nearly their sum).  The block
+       therefore asks the L2 for the bytes of the work item `prefetch_items` ahead, one bulk prefetch by one thread:
+       the memory then works at the rate at which blocks start, whatever they are doing, and a block's own loads
+       find their lines in the L2.  Dense planes only (one segment). */
+    if (!SRC_IS_U8 && prefetch_items != 0 && threadIdx.x == 0 && P.n_segs == 1u) {
+        const uint64_t px_ahead = ((uint64_t)local + prefetch_items) * ITEM;
+        if (px_ahead < P.seg_pixels) {
+            const uint32_t bytes = (uint32_t)min((uint64_t)ITEM, P.seg_pixels - px_ahead) * SPX & ~15u;
+            if (bytes != 0)
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src_seg + px_ahead * SPX), "r"(bytes) : "memory");
+        }
+    }
 
     /* Output of one run, warp by warp: a thread's four pixels are 48 (12) bytes, so stores straight
        from the registers would write a third of every sector per instruction, and that pattern was
@@ -753,19 +781,6 @@ __device__ __forceinline__ void body_flat(const DevPlane& P, const DevSeq& S, co
 
 /* Position idx of a row-major walk over rows of `per_row` cells, advanced `step` cells at a time
    with one division at the start instead of one per step. */
-/* n / d for d > 0 and a quotient below 2^22 (row, slot and tile indices): the quotient of the two numbers as floats is off by
-   at most one, which the remainder tells; ten instructions where the integer division takes three times as many, in a
-   block's prologue that runs once per few thousand pixels. */
-__device__ __forceinline__ uint32_t div_small(uint32_t n, uint32_t d) {
-    float r;
-    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(__uint2float_rn(d)));
-    uint32_t q = __float2uint_rz(__fmul_rn(__uint2float_rn(n), r));
-    const int32_t rem = (int32_t)(n - q * d);
-    if (rem < 0) --q;
-    else if ((uint32_t)rem >= d) ++q;
-    return q;
-}
-
 struct CellWalk {
     uint32_t r, c, dr, dc, per_row;
     /* `more`: whether any walker will advance at all (uniform); the step's division is skipped if not */
@@ -1057,8 +1072,8 @@ __device__ __forceinline__ void body_resize(const DevPlane& P, const DevSeq& S, 
 /* Asynchronous bulk copies (the copy engine that also serves tensor-map TMA) and the mbarrier
  * that counts their bytes.  Kernels are launched without clusters: every copy lands in the shared
  * memory of the block that issued it and nowhere else. */
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 /* Three consecutive aligned words of shared memory at a 32-bit shared-window address. */
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void lds32x3(uint32_t addr, uint32_t& w0, uint32_t& w1, uint32_t& w2) {
     if (!check_smem(addr, 12u)) { w0 = w1 = w2 = 0u; return; }
     asm volatile("ld.shared.b32 %0, [%3];\n\tld.shared.b32 %1, [%3+4];\n\tld.shared.b32 %2, [%3+8];"
@@ -1112,6 +1127,7 @@ struct WaitCtl {
     uint32_t* status;
     uint32_t limit_us;
     uint32_t test_extra_bytes;
+    uint32_t prefetch_items = 0; /* float3 -> float3 element-wise planes: LaunchArgs::prefetch_items */
 };
 
 /* A work item is a band of STAGED rows of one plane's region of interest, all columns.  The rows
@@ -1599,7 +1615,7 @@ __device__ __forceinline__ void run_class(uint32_t cls, const DevPlane& P, const
     if (CLASS != CLASS_MIXED) cls = CLASS;
     switch (cls) {
         case CLASS_FLAT_U8_F32: body_flat<CHAIN, true, false>(P, S, sops, local, turn_mem); break;
-        case CLASS_FLAT_F32_F32: body_flat<CHAIN, false, false>(P, S, sops, local, turn_mem); break;
+        case CLASS_FLAT_F32_F32: body_flat<CHAIN, false, false>(P, S, sops, local, turn_mem, status.prefetch_items); break;
         case CLASS_FLAT_U8_U8: body_flat<CHAIN, true, true>(P, S, sops, local, turn_mem); break;
         case CLASS_RESIZE_U8_PLANAR: body_resize<CHAIN, FKB_SRC_U8X3, true>(P, S, sops, local); break;
         case CLASS_RESIZE_U8_PACKED: body_resize<CHAIN, FKB_SRC_U8X3, false>(P, S, sops, local); break;
@@ -1716,7 +1732,7 @@ __global__ void __launch_bounds__(BLOCK_THREADS, min_blocks_of(CLASS)) fused_pla
         __syncthreads();
         check_begin(a.plane0, a.seq0, a, smem_raw);
         run_body<CLASS, CHAIN>(a.plane0.plane_class, a.plane0, a.seq0, sops, blockIdx.x, nullptr, s_turn,
-                               WaitCtl{a.status, a.wait_limit_us, a.test_extra_bytes});
+                               WaitCtl{a.status, a.wait_limit_us, a.test_extra_bytes, a.prefetch_items});
         return;
     }
     /* One 16-byte table entry tells the block its plane, its tile within the plane and where the

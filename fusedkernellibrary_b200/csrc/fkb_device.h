@@ -132,6 +132,8 @@ struct LaunchArgs {
     uint32_t inline_plane;      /* 1: a plan of one plane whose descriptors travel in the      */
                                 /* kernel arguments below; block b is tile b of that plane     */
     uint32_t test_extra_bytes;  /* TEST ONLY: bytes a block expects beyond what its copies deliver   */
+    uint32_t prefetch_items;    /* > 0: one dense float3 -> float3 element-wise plane with a long chain; a block asks the L2 */
+                                /* for the bytes of the work item this far ahead of its own                                   */
     uint32_t test_shrink_bounds;/* TEST ONLY, bounds-checking build: destination rows the checker pretends are missing */
     uint32_t* status;           /* one word in the plan's device block: 0, or a STATUS_* code  */
     DevPlane plane0;            /* inline_plane: the plane, its sequence and its operations    */
@@ -149,6 +151,10 @@ __host__ __device__ constexpr int flat_quads(bool src_is_u8) { return src_is_u8 
 /* FLAT classes: pixels per work item */
 __host__ __device__ constexpr int flat_item_pixels(bool src_is_u8) { return BLOCK_THREADS * PX_PER_THREAD * flat_quads(src_is_u8); }
 constexpr int ITEM_PIXELS_GENERIC = BLOCK_THREADS;
+/* FLAT float3 -> float3, one dense plane: from this many arithmetic operations per value a block prefetches the work item
+   FLAT_PREFETCH_ITEMS ahead into the L2 (the blocks a B200 holds at five per SM, 9 MB; twice and four times as far measured the same or worse) */
+constexpr uint32_t FLAT_PREFETCH_MIN_OPS = 12;
+constexpr uint32_t FLAT_PREFETCH_ITEMS = 148u * 5u;
 
 /* Device-only opcode: division by a plan-time constant, lowered from FKB_OP_DIV when the host
  * has proven the three-instruction form exact.  Takes two op slots: {-p}, then {1/p}. */

@@ -132,6 +132,23 @@ struct HostImage {
     size_t off_status() const { return off_items() + (size_t)total_items * (early_copies ? 32 : 16); }
     size_t bytes() const { return off_status() + 16; }
 
+    /* One dense float3 -> float3 element-wise plane whose chain is long: how many work items ahead of its own a block
+       prefetches into the L2 (LaunchArgs::prefetch_items), else 0. */
+    uint32_t prefetch_items() const {
+        if (launch_class != CLASS_FLAT_F32_F32 || planes.size() != 1 || seqs.size() != 1 || planes[0].n_segs != 1) return 0;
+        uint64_t n_arith = 0;
+        for (size_t k = 0; k < ops.size(); ++k) {
+            if (ops[k].opcode == DEV_OP_REPEAT) {
+                uint32_t count, period;
+                std::memcpy(&count, &ops[k].p[0], 4); std::memcpy(&period, &ops[k].p[1], 4);
+                n_arith += (uint64_t)count * period;
+                k += period;
+            } else ++n_arith;
+        }
+        if (n_arith < FLAT_PREFETCH_MIN_OPS || total_items <= FLAT_PREFETCH_ITEMS) return 0;
+        return FLAT_PREFETCH_ITEMS;
+    }
+
     void serialize(unsigned char* dst) const {
         std::memcpy(dst + off_planes(), planes.data(), planes.size() * sizeof(DevPlane));
         std::memcpy(dst + off_seqs(), seqs.data(), seqs.size() * sizeof(DevSeq));
@@ -192,6 +209,7 @@ struct HostImage {
             a.plane0 = planes[0];
             a.seq0 = seqs[0];
             for (size_t k = 0; k < ops.size(); ++k) a.ops0[k] = ops[k];
+            a.prefetch_items = prefetch_items();
         }
         return a;
     }

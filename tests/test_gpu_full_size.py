@@ -123,7 +123,9 @@ def test_c1_and_c5a_full_size(fkb_lib, oracle_port):
     from tests.test_gpu_parity import run_cuda
     c1 = tc.elementwise_case("c1_full", 1001, 1920, 1080, chains.cast_mul_sub_div_ops())
     c5a = tc.elementwise_case("c5a_full", 1005, 3840, 2160, chains.addmul_ops(64), src_fmt=abi.SRC_F32X3)
-    for case in (c1, c5a):
+    # a long chain on an image whose last work item is ragged: the blocks prefetch later work items, the last one in part
+    ragged = tc.elementwise_case("c5a_ragged", 1007, 3001, 1999, chains.addmul_ops(16), src_fmt=abi.SRC_F32X3)
+    for case in (c1, c5a, ragged):
         expected = {k: v.copy() for k, v in tc.run_on_host(case, oracle_port).items()}
         got, _ = run_cuda(case, fkb_lib)
         assert np.array_equal(tc.bits(got["out"]), tc.bits(expected["out"])), case.name
