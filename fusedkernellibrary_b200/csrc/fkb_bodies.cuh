@@ -1163,7 +1163,7 @@ __device__ __forceinline__ void body_resize_staged(const DevPlane& P, const DevS
     /* shared memory: | mbarrier (16 B) | row table (32 B per row of the band) | staged source rows | */
     uint64_t* const mbar_ptr = reinterpret_cast<uint64_t*>(staged_mem);
     float4* const row_tab = reinterpret_cast<float4*>(staged_mem + 16);
-    unsigned char* const stage = staged_mem + STAGED_HEADER_BYTES;
+    unsigned char* const stage = staged_mem + STAGED_U8_HEADER_BYTES;
     const uint32_t stage_addr = smem_addr(stage);
     const uint32_t mbar = smem_addr(mbar_ptr);
 
@@ -1745,10 +1745,26 @@ __global__ void __launch_bounds__(BLOCK_THREADS, min_blocks_of(CLASS)) fused_pla
     auto start_band_copies = [&]() {
         if (EARLY_COPIES && threadIdx.x < 32) {
             const uint4 cp = __ldg(a.items + 2u * blockIdx.x + 1u); /* source pointer, rows | row bytes << 16, pitch */
+            unsigned char* const staged = smem_raw + (((a.max_seq_ops > 0 ? a.max_seq_ops : 1u) * (uint32_t)sizeof(OpSlot) + 127u) & ~127u);
+            const uint32_t mbar = smem_addr(staged), stage_addr = smem_addr(staged + STAGED_U8_HEADER_BYTES);
+            if (a.tiled_copies) {
+                /* the whole footprint as one tile of the plane's tensor map: tensor map index, -, bytes of the box,
+                   x | y << 16 (x in eight-byte elements, even, so that the copy starts on a 16-byte boundary) */
+                if (threadIdx.x == 0 && cp.z != 0u) {
+                    mbar_init(mbar, 1);
+                    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+                    mbar_expect_tx(mbar, cp.z + a.test_extra_bytes);
+                    /* a tile lands on a 128-byte boundary and starts at an even element; anything else is never expected
+                       and is not issued (the block's wait then runs out and reports it) */
+                    if (((stage_addr & 127u) | (cp.w & 1u)) == 0u)
+                    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                                 ::"r"(stage_addr), "l"(a.tmaps + (size_t)cp.x * TENSOR_MAP_BYTES), "r"(cp.w & 0xFFFFu), "r"(cp.w >> 16), "r"(mbar)
+                                 : "memory");
+                }
+                return;
+            }
             const uint32_t n_src = cp.z & 0xFFFFu, row_len = cp.z >> 16;
             if (n_src != 0) {
-                unsigned char* const staged = smem_raw + (((a.max_seq_ops > 0 ? a.max_seq_ops : 1u) * (uint32_t)sizeof(OpSlot) + 127u) & ~127u);
-                const uint32_t mbar = smem_addr(staged), stage_addr = smem_addr(staged + STAGED_HEADER_BYTES);
                 if (threadIdx.x == 0) {
                     mbar_init(mbar, 1);
                     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");

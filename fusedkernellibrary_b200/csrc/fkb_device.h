@@ -134,6 +134,9 @@ struct LaunchArgs {
     uint32_t test_extra_bytes;  /* TEST ONLY: bytes a block expects beyond what its copies deliver   */
     uint32_t prefetch_items;    /* > 0: one dense float3 -> float3 element-wise plane with a long chain; a block asks the L2 */
                                 /* for the bytes of the work item this far ahead of its own                                   */
+    uint32_t tiled_copies;      /* staged uchar3 classes: 1 when a band's second table entry names a tensor map (index, 0,     */
+                                /* bytes of the box, x | y << 16) instead of the rows of per-row copies                       */
+    const unsigned char* tmaps; /* the plan's tensor maps, TENSOR_MAP_BYTES each                                             */
     uint32_t test_shrink_bounds;/* TEST ONLY, bounds-checking build: destination rows the checker pretends are missing */
     uint32_t* status;           /* one word in the plan's device block: 0, or a STATUS_* code  */
     DevPlane plane0;            /* inline_plane: the plane, its sequence and its operations    */
@@ -254,6 +257,13 @@ constexpr uint32_t SMALL_GRID_BLOCKS = 148;      /* fewer blocks than this (one 
 constexpr uint32_t STAGED_MAX_ROWS = 64;          /* output rows per band                        */
 constexpr uint32_t STAGED_MAX_STAGE_BYTES = 40 * 1024u; /* five blocks of it fit one SM */
 constexpr uint32_t STAGED_HEADER_BYTES = 16 + STAGED_MAX_ROWS * 32;
+/* the staged uchar3 classes round it up to 128 bytes: a tiled bulk copy wants its destination on such a boundary */
+constexpr uint32_t STAGED_U8_HEADER_BYTES = (STAGED_HEADER_BYTES + 127u) & ~127u;
+/* A band's source rows as ONE tiled bulk copy through a tensor map of its plane (box = row bytes x rows) instead of one
+   bulk copy per row: rows of at most 256 eight-byte elements, at most 256 rows, coordinates that fit 16 bits. */
+constexpr uint32_t TILED_MAX_ROW_BYTES = 256u * 8u;
+constexpr uint32_t TILED_MAX_ROWS = 256u;
+constexpr uint32_t TENSOR_MAP_BYTES = 128u;
 constexpr uint32_t NV12_MAX_STAGE_BYTES = 50 * 1024u; /* luma and chroma rows of a band tile; four blocks per SM.  The body is bound
                                                          by the latency of its shared-memory taps: two rows in flight per thread at 64 registers and
                                                          four blocks measured 100.4 us on 32 4K frames against 102.5 with one row at 48 registers
