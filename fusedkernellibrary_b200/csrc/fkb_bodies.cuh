@@ -1756,10 +1756,15 @@ __global__ void __launch_bounds__(BLOCK_THREADS, min_blocks_of(CLASS)) fused_pla
                     mbar_expect_tx(mbar, cp.z + a.test_extra_bytes);
                     /* a tile lands on a 128-byte boundary and starts at an even element; anything else is never expected
                        and is not issued (the block's wait then runs out and reports it) */
-                    if (((stage_addr & 127u) | (cp.w & 1u)) == 0u)
-                    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-                                 ::"r"(stage_addr), "l"(a.tmaps + (size_t)cp.x * TENSOR_MAP_BYTES), "r"(cp.w & 0xFFFFu), "r"(cp.w >> 16), "r"(mbar)
-                                 : "memory");
+                    if (((stage_addr & 127u) | (cp.w & 1u)) == 0u) {
+                        /* the map lies in global memory, written by the host when the plan was made, at an address that an
+                           earlier plan's map may have had: the copy engine's view of it is brought up to date first */
+                        const unsigned char* const tmap = a.tmaps + (size_t)cp.x * TENSOR_MAP_BYTES;
+                        asm volatile("fence.proxy.tensormap::generic.acquire.sys [%0], 128;" ::"l"(tmap) : "memory");
+                        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                                     ::"r"(stage_addr), "l"(tmap), "r"(cp.w & 0xFFFFu), "r"(cp.w >> 16), "r"(mbar)
+                                     : "memory");
+                    }
                 }
                 return;
             }

@@ -1381,6 +1381,11 @@ extern "C" FKB_API int fkb_plan_create(const fkb_plan_desc* desc, fkb_plan** out
     img.serialize(staging.data());
     cudaError_t e = device_alloc(&plan->d_block, plan->d_bytes);
     if (e == cudaSuccess) e = cudaMemcpy(plan->d_block, staging.data(), plan->d_bytes, cudaMemcpyHostToDevice);
+    /* A blocking copy from pageable memory returns once the bytes have left `staging`; their last piece may still be on its
+       way to the device.  The plan is launched on the caller's stream, which need not wait for the default stream, so the
+       table must have landed before this call returns: a kernel that read a table's unfinished end - its last work items,
+       its tensor maps - would run on whatever the allocation held before. */
+    if (e == cudaSuccess) e = cudaStreamSynchronize(cudaStreamLegacy);
     if (e != cudaSuccess) {
         if (plan->d_block) device_free(plan->d_block);
         delete plan;
