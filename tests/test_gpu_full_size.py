@@ -174,3 +174,31 @@ def test_c2_scaled_readme_rects_over_many_planes(fkb_lib, oracle_port):
         assert np.array_equal(tc.bits(got[:40]), tc.bits(want_ref)), "differs from the reference CPU backend"
     for i in range(40, n):
         assert np.array_equal(tc.bits(got[i]), tc.bits(got[i % 40])), f"plane {i} differs from its twin {i % 40}"
+
+
+def test_one_shot_call_launches_right_after_its_table_is_uploaded(fkb_lib):
+    """fkb_execute makes a plan, launches it on the caller's stream at once and destroys it: the kernel must find the
+    whole descriptor table (over a megabyte here: 8000 planes, with their tensor maps at its end) on the device even
+    though the caller's stream does not wait for the stream the upload used."""
+    rng = np.random.default_rng(1011)
+    fw, fh, nf, n = 3840, 2160, 8, 8000
+    d_frames = [torch.from_numpy(rng.integers(0, 256, (fh, fw * 3), dtype=np.uint8)).cuda() for _ in range(nf)]
+    rects = np.tile(chains.README_RECTS, (n // 5, 1))
+    fi = [(i // 5) % nf for i in range(n)]
+    d_out = torch.zeros((n, 60, 60, 3), dtype=torch.float32, device="cuda")
+    desc = chains.crop_resize_batch(frame_ptrs=[t.data_ptr() for t in d_frames], frame_index=fi, rects=rects, src_width=fw,
+                                    src_height=fh, src_pitch=fw * 3, dst=d_out.data_ptr(), dst_width=60, dst_height=60,
+                                    post_ops=chains.readme_ops(), planar=False)
+    plan = abi.DevicePlan(desc)
+    torch.cuda.synchronize()
+    plan.launch()
+    assert plan.check() == 0
+    want = d_out.clone()
+    plan.destroy()
+    stream = torch.cuda.Stream()   # non-blocking: not ordered behind the default stream
+    for _ in range(3):
+        d_out.zero_()
+        torch.cuda.synchronize()
+        abi.execute(desc, stream.cuda_stream)
+        torch.cuda.synchronize()
+        assert torch.equal(_bits(d_out), _bits(want))
