@@ -1128,6 +1128,7 @@ struct WaitCtl {
     uint32_t limit_us;
     uint32_t test_extra_bytes;
     uint32_t prefetch_items = 0; /* float3 -> float3 element-wise planes: LaunchArgs::prefetch_items */
+    uint32_t nv12_early = 0;     /* staged NV12: the kernel's first two warps have marked, packed and started the band's rows */
 };
 
 /* A work item is a band of STAGED rows of one plane's region of interest, all columns.  The rows
@@ -1404,6 +1405,8 @@ __device__ __forceinline__ void body_nv12_staged(const DevPlane& P, const DevSeq
     const int c_first = l_first >> 1;
     const uint32_t c_span = (uint32_t)((l_last >> 1) - c_first + 1);
 
+    const bool early = wc.nv12_early != 0u; /* rows marked, packed and on their way since the block began (uniform) */
+    if (!early) {
     if (tid == 0) {
         mbar_init(mbar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -1414,20 +1417,23 @@ __device__ __forceinline__ void body_nv12_staged(const DevPlane& P, const DevSeq
         reinterpret_cast<uint2*>(need_c)[tid] = make_uint2(0u, 0u);
     }
     __syncthreads();
+    }
     const bool row_thread = tid <= (uint32_t)(yb - ya);
     Axis ay = {0, 0, 0.0f, 0.0f};
     if (row_thread) {
         ay = make_axis(ya + (int)tid - y1, fy, crop_h);
+        if (!early) {
         const int r0 = crop_y + ay.i0, r1 = crop_y + ay.i1;
         need_l[r0 - l_first] = 1;
         need_c[(r0 >> 1) - c_first] = 1;
         if (ay.w1 != 0.0f) { need_l[r1 - l_first] = 1; need_c[(r1 >> 1) - c_first] = 1; }
+        }
     }
-    __syncthreads();
+    if (!early) __syncthreads();
     /* The rows that are read are packed in the stage: a flag becomes 1 + the row's slot (an exclusive prefix sum
        over the flags; warp 0 takes the luma span, warp 1 the chroma span, eight flags per lane). */
     uint32_t* const counts = reinterpret_cast<uint32_t*>(staged_mem + 8); /* needed luma rows, needed chroma rows */
-    if (tid < 64) {
+    if (!early && tid < 64) {
         unsigned char* const flags = tid < 32 ? need_l : need_c;
         const uint32_t lane = tid & 31u;
         const uint2 w = reinterpret_cast<const uint2*>(flags)[lane];
@@ -1451,7 +1457,7 @@ __device__ __forceinline__ void body_nv12_staged(const DevPlane& P, const DevSeq
                                                            o[4] | (o[5] << 8) | (o[6] << 16) | (o[7] << 24));
         if (lane == 31) counts[tid >> 5] = incl;
     }
-    __syncthreads();
+    if (!early) __syncthreads();
     const uint32_t n_luma = counts[0];
     const uint32_t chroma_addr = stage_addr + n_luma * row_len;
     if (row_thread) {
@@ -1467,7 +1473,7 @@ __device__ __forceinline__ void body_nv12_staged(const DevPlane& P, const DevSeq
                                        __uint_as_float(chroma_addr + b0), __uint_as_float(chroma_addr + b1));
         row_tab[2 * tid + 1] = make_float4(ay.w0, ay.w0, ay.w1, ay.w1);
     }
-    {
+    if (!early) {
         const uint8_t* luma = P.src + (size_t)l_first * P.src_pitch + byte0;
         const uint8_t* chroma = P.src + (size_t)P.src_pitch * P.src_height + (size_t)c_first * P.src_pitch + byte0;
         for (uint32_t r = tid; r < l_span; r += nthreads) {
@@ -1741,7 +1747,53 @@ __global__ void __launch_bounds__(BLOCK_THREADS, min_blocks_of(CLASS)) fused_pla
        the bulk copies of the source rows from it at once, before the plane's descriptor is known. */
     const bool EARLY_COPIES = CLASS == CLASS_RESIZE_U8_PLANAR_STAGED || CLASS == CLASS_RESIZE_U8_PACKED_STAGED ||
                               (CLASS == CLASS_MIXED && a.staged_bytes != 0); /* a plan of several classes with staged planes */
-    const uint4 entry = __ldg(a.items + (EARLY_COPIES ? 2u * blockIdx.x : blockIdx.x));
+    const bool NV12_EARLY = CLASS == CLASS_RESIZE_NV12_PACKED_STAGED && a.nv12_early != 0u;
+    const uint4 entry = __ldg(a.items + (EARLY_COPIES ? 2u * blockIdx.x : NV12_EARLY ? NV12_ITEM_WORDS * blockIdx.x : blockIdx.x));
+    if (NV12_EARLY && threadIdx.x < 64) {
+        /* The staged NV12 class: the work item's table words name the source rows that some tap of the band tile reads
+           (one bit per row of the luma and of the chroma span, found by the host with the kernel's own arithmetic).
+           Warp 0 takes the luma rows, warp 1 the chroma rows, eight per lane: a prefix sum over the bit counts gives every
+           row its slot in the stage, the row's copy starts, and the slots (plus one; zero = not read) are left in shared
+           memory for the row table.  The copies are on their way one round trip after the block began, instead of after
+           the plane's descriptor, the marking of the rows and three block barriers. */
+        const uint4* const words = a.items + NV12_ITEM_WORDS * blockIdx.x;
+        const uint4 ptrs = __ldg(words + 1), geo = __ldg(words + 2); /* luma, chroma bases; pitch, row bytes, luma span, luma rows */
+        const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+        const uint32_t bits = __ldg(reinterpret_cast<const unsigned char*>(words + 4 + 2u * warp) + lane);
+        unsigned char* const staged = smem_raw + (((a.max_seq_ops > 0 ? a.max_seq_ops : 1u) * (uint32_t)sizeof(OpSlot) + 127u) & ~127u);
+        const uint32_t mbar = smem_addr(staged);
+        unsigned char* const flags = staged + STAGED_HEADER_BYTES + warp * NV12_MAX_SPAN;
+        const uint32_t stage_addr = smem_addr(staged + STAGED_HEADER_BYTES + 2u * NV12_MAX_SPAN);
+        if (threadIdx.x == 0) {
+            mbar_init(mbar, 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        asm volatile("bar.sync 1, 64;" ::: "memory"); /* the barrier is initialised before warp 1 counts bytes on it */
+        const uint32_t pitch = geo.x, row_len = geo.y;
+        const uint32_t mine = __popc(bits);
+        uint32_t incl = mine;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+            if (lane >= (uint32_t)d) incl += up;
+        }
+        uint32_t slot = incl - mine; /* rows read before this lane's eight */
+        const uint8_t* const base = reinterpret_cast<const uint8_t*>(warp == 0 ? ((size_t)ptrs.x | ((size_t)ptrs.y << 32)) : ((size_t)ptrs.z | ((size_t)ptrs.w << 32)));
+        const uint32_t dst0 = stage_addr + (warp == 0 ? 0u : geo.w * row_len);
+        uint32_t o[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const bool read = (bits >> k) & 1u;
+            o[k] = read ? slot + 1u : 0u;
+            if (read) {
+                mbar_expect_tx_only(mbar, row_len);
+                bulk_copy_g2s(dst0 + slot * row_len, base + (size_t)(lane * 8u + (uint32_t)k) * pitch, row_len, mbar);
+                ++slot;
+            }
+        }
+        reinterpret_cast<uint2*>(flags)[lane] = make_uint2(o[0] | (o[1] << 8) | (o[2] << 16) | (o[3] << 24), o[4] | (o[5] << 8) | (o[6] << 16) | (o[7] << 24));
+        if (lane == 31) reinterpret_cast<uint32_t*>(staged + 8)[warp] = incl;
+    }
     auto start_band_copies = [&]() {
         if (EARLY_COPIES && threadIdx.x < 32) {
             const uint4 cp = __ldg(a.items + 2u * blockIdx.x + 1u); /* source pointer, rows | row bytes << 16, pitch */
@@ -1802,7 +1854,7 @@ __global__ void __launch_bounds__(BLOCK_THREADS, min_blocks_of(CLASS)) fused_pla
     /* staged classes: the region after the operation cache, on a 128-byte boundary */
     unsigned char* staged_mem = smem_raw + (((a.max_seq_ops > 0 ? a.max_seq_ops : 1u) * (uint32_t)sizeof(OpSlot) + 127u) & ~127u);
     run_body<CLASS, CHAIN>(s_plane.plane_class, s_plane, s_seq, sops, local, staged_mem, s_turn,
-                           WaitCtl{a.status, a.wait_limit_us, a.test_extra_bytes});
+                           WaitCtl{a.status, a.wait_limit_us, a.test_extra_bytes, 0u, NV12_EARLY ? 1u : 0u});
 }
 
 /* ------------------------------------------------------------------------------------ */

@@ -134,6 +134,9 @@ struct LaunchArgs {
     uint32_t test_extra_bytes;  /* TEST ONLY: bytes a block expects beyond what its copies deliver   */
     uint32_t prefetch_items;    /* > 0: one dense float3 -> float3 element-wise plane with a long chain; a block asks the L2 */
                                 /* for the bytes of the work item this far ahead of its own                                   */
+    uint32_t nv12_early;        /* staged NV12 class: 1 when a work item has NV12_ITEM_WORDS table words: the entry, then the     */
+                                /* luma and chroma base pointers, pitch / row bytes / spans / luma rows, and one bit per source */
+                                /* row of the luma and chroma spans for the rows to copy                                         */
     uint32_t tiled_copies;      /* staged uchar3 classes: 1 when a band's second table entry names a tensor map (index, 0,     */
                                 /* bytes of the box, x | y << 16) instead of the rows of per-row copies                       */
     const unsigned char* tmaps; /* the plan's tensor maps, TENSOR_MAP_BYTES each                                             */
@@ -269,6 +272,7 @@ constexpr uint32_t NV12_MAX_STAGE_BYTES = 50 * 1024u; /* luma and chroma rows of
                                                          four blocks measured 100.4 us on 32 4K frames against 102.5 with one row at 48 registers
                                                          and five blocks (two rows at 48 registers spill: 106.2), and 97.5 with the larger stage
                                                          that four blocks leave room for (three rows 103.2; four rows at three blocks 115.5). */
+constexpr uint32_t NV12_ITEM_WORDS = 8;           /* 16-byte table words per work item of a staged NV12 plan (LaunchArgs::nv12_early) */
 constexpr uint32_t NV12_MAX_SPAN = 256;           /* source rows between a band's first and last tap */
 constexpr uint32_t STAGED_FOLD_BG_GROUPS = 1024;  /* at most this many outside groups: no store-only items */
 constexpr uint32_t STATUS_STAGED_WAIT_TIMEOUT = 1; /* a bulk copy did not complete in time        */

@@ -123,6 +123,8 @@ struct HostImage {
     uint32_t max_seq_ops = 0;
     uint32_t staged_bytes = 0;          /* > 0: a STAGED class, this much shared memory per block */
     bool early_copies = false;          /* staged uchar3 classes: two table entries per block     */
+    bool nv12_early = false;            /* staged NV12 class: NV12_ITEM_WORDS table words per block, with the rows to copy */
+    size_t item_bytes() const { return early_copies ? 32 : nv12_early ? 16 * NV12_ITEM_WORDS : 16; }
     /* staged uchar3 classes, when every band can be one tiled copy: the tensor maps (one per distinct source image, row
        length and row count) and, per plane, the index of its map, its row bytes and its rows per tile */
     bool tiled_copies = false;
@@ -137,7 +139,7 @@ struct HostImage {
     size_t off_seqs() const { return planes.size() * sizeof(DevPlane); }
     size_t off_ops() const { return off_seqs() + seqs.size() * sizeof(DevSeq); }
     size_t off_items() const { return off_ops() + std::max<size_t>(ops.size(), 1) * sizeof(DevOp); }
-    size_t off_status() const { return off_items() + (size_t)total_items * (early_copies ? 32 : 16); }
+    size_t off_status() const { return off_items() + (size_t)total_items * item_bytes(); }
     size_t off_tmaps() const { return (off_status() + 16 + 127) & ~(size_t)127; }
     size_t bytes() const { return tiled_copies ? off_tmaps() + tmaps.size() * TENSOR_MAP_BYTES : off_status() + 16; }
 
@@ -156,6 +158,50 @@ struct HostImage {
         }
         if (n_arith < FLAT_PREFETCH_MIN_OPS || total_items <= FLAT_PREFETCH_ITEMS) return 0;
         return FLAT_PREFETCH_ITEMS;
+    }
+
+    /* The words behind a staged NV12 work item's entry (28 of 32 bits each): what the kernel's first two warps need to start
+       the band tile's copies before the plane's descriptor has arrived.  The same arithmetic as body_nv12_staged: binary32
+       product, floor, a second tap only where its weight is not zero and it is not clamped onto the first. */
+    static void nv12_item_words(const DevPlane& dp, uint32_t local, uint32_t* w) {
+        std::memset(w, 0, 4 * 4 * (NV12_ITEM_WORDS - 1));
+        if (local >= dp.roi_items) return; /* store-only item */
+        auto first_tap = [](int r, float f) { volatile float s = (float)r * f; return (int)std::floor(s); };
+        const uint32_t g_lo = (uint32_t)dp.x1 / PX_PER_THREAD;
+        const uint32_t n_groups = (uint32_t)dp.x2 / PX_PER_THREAD - g_lo + 1;
+        const uint32_t band = local / dp.tiles_x, tile_x = local - band * dp.tiles_x, band_rows = dp.seg_pixels, gw = dp.gw;
+        const int ya = dp.y1 + (int)(band * band_rows), yb = std::min(ya + (int)band_rows - 1, dp.y2);
+        const int c_base = (int)(g_lo * PX_PER_THREAD + tile_x * 2 * gw);
+        const int x_end = (int)std::min((g_lo + n_groups) * PX_PER_THREAD, (uint32_t)c_base + 2 * gw);
+        const int rc0 = std::min(std::max(c_base, dp.x1), dp.x2), rc1 = std::max(std::min(x_end - 1, dp.x2), rc0);
+        const int sx_first = dp.crop_x + first_tap(rc0 - dp.x1, dp.fx);
+        const int sx_last = dp.crop_x + std::min(first_tap(rc1 - dp.x1, dp.fx) + 1, dp.crop_w - 1);
+        const uint32_t byte0 = (uint32_t)sx_first & ~15u;
+        const uint32_t row_len = std::min(((uint32_t)sx_last + 2u + 15u) & ~15u, dp.src_pitch) - byte0;
+        const int l_first = dp.crop_y + first_tap(ya - dp.y1, dp.fy);
+        const int l_last = dp.crop_y + std::min(first_tap(yb - dp.y1, dp.fy) + 1, dp.crop_h - 1);
+        const int c_first = l_first >> 1;
+        unsigned char* const luma_bits = reinterpret_cast<unsigned char*>(w + 12);
+        unsigned char* const chroma_bits = reinterpret_cast<unsigned char*>(w + 20);
+        auto mark = [&](int row) {
+            const uint32_t a = (uint32_t)(row - l_first), b = (uint32_t)((row >> 1) - c_first);
+            luma_bits[a >> 3] |= (unsigned char)(1u << (a & 7u));
+            chroma_bits[b >> 3] |= (unsigned char)(1u << (b & 7u));
+        };
+        for (int y = ya; y <= yb; ++y) {
+            volatile float s = (float)(y - dp.y1) * dp.fy;
+            const int i0 = (int)std::floor(s);
+            volatile float w1 = s - (float)i0;
+            mark(dp.crop_y + i0);
+            if (w1 != 0.0f) mark(dp.crop_y + std::min(i0 + 1, dp.crop_h - 1));
+        }
+        uint32_t n_luma = 0;
+        for (int k = 0; k < 32; ++k) n_luma += (uint32_t)__builtin_popcount(luma_bits[k]);
+        const uintptr_t luma = reinterpret_cast<uintptr_t>(dp.src) + (size_t)l_first * dp.src_pitch + byte0;
+        const uintptr_t chroma = reinterpret_cast<uintptr_t>(dp.src) + (size_t)dp.src_pitch * dp.src_height + (size_t)c_first * dp.src_pitch + byte0;
+        w[0] = (uint32_t)(luma & 0xFFFFFFFFu); w[1] = (uint32_t)((uint64_t)luma >> 32);
+        w[2] = (uint32_t)(chroma & 0xFFFFFFFFu); w[3] = (uint32_t)((uint64_t)chroma >> 32);
+        w[4] = dp.src_pitch; w[5] = row_len; w[6] = (uint32_t)(l_last - l_first + 1); w[7] = n_luma;
     }
 
     void serialize(unsigned char* dst) const {
@@ -179,6 +225,11 @@ struct HostImage {
             const DevPlane& dp = planes[i];
             for (uint32_t l = 0, n = item_start[i + 1] - item_start[i]; l < n; ++l, e += 4) {
                 e[0] = (uint32_t)i; e[1] = l; e[2] = dp.seq | ((uint32_t)q.n_ops << 16); e[3] = (uint32_t)q.ops_begin;
+                if (nv12_early) {
+                    nv12_item_words(dp, l, e + 4);
+                    e += 4 * (NV12_ITEM_WORDS - 1);
+                    continue;
+                }
                 if (!early_copies) continue;
                 /* second entry: what the band's bulk copies need (nothing for a store-only item) */
                 e += 4;
@@ -219,6 +270,7 @@ struct HostImage {
         a.max_seq_ops = max_seq_ops;
         a.block_threads = block_threads;
         a.staged_bytes = staged_bytes;
+        a.nv12_early = nv12_early ? 1u : 0u;
         a.tiled_copies = tiled_copies ? 1u : 0u;
         a.tmaps = tiled_copies ? d_base + off_tmaps() : nullptr;
         a.wait_limit_us = FKB_DEFAULT_WAIT_LIMIT_US;
@@ -1270,6 +1322,9 @@ static int lower(const fkb_plan_desc* d, HostImage& img) {
             img.block_threads = BLOCK_THREADS;
             img.staged_bytes = STAGED_HEADER_BYTES + 2 * NV12_MAX_SPAN + stage;
             img.launch_class = common_class = CLASS_RESIZE_NV12_PACKED_STAGED;
+#ifndef FKB_CHECK_BOUNDS /* the checked build finds and copies the rows once it knows what the plane allows */
+            img.nv12_early = true;
+#endif
         }
     }
     /* A plan whose planes all have the same region width can run with exactly as many threads per
