@@ -1837,13 +1837,16 @@ __global__ void __launch_bounds__(BLOCK_THREADS, min_blocks_of(CLASS)) fused_pla
     start_band_copies();
 #endif
     const uint32_t plane_idx = entry.x, local = entry.y, seq = entry.z & 0xFFFFu, n_ops = entry.z >> 16, ops_begin = entry.w;
-    if (threadIdx.x < sizeof(DevPlane) / 16) {
-        reinterpret_cast<uint4*>(&s_plane)[threadIdx.x] =
-            __ldg(reinterpret_cast<const uint4*>(a.planes + plane_idx) + threadIdx.x);
-    } else if (threadIdx.x >= 32 && threadIdx.x < 32 + sizeof(DevSeq) / 16) {
-        reinterpret_cast<uint4*>(&s_seq)[threadIdx.x - 32] = __ldg(reinterpret_cast<const uint4*>(a.seqs + seq) + (threadIdx.x - 32));
-    } else if (threadIdx.x >= 64) {
-        for (uint32_t k = threadIdx.x - 64; k < n_ops; k += blockDim.x - 64)
+    /* the descriptors are fetched by the warps that do not issue copies (staged NV12: warps 2 and up of 8; staged uchar3:
+       warps 1 and up of 4 or 8), so that they travel while the copies are issued */
+    const uint32_t skip = NV12_EARLY ? 64u : EARLY_COPIES ? 32u : 0u;
+    const uint32_t t = threadIdx.x - skip;
+    if (t < sizeof(DevPlane) / 16) {
+        reinterpret_cast<uint4*>(&s_plane)[t] = __ldg(reinterpret_cast<const uint4*>(a.planes + plane_idx) + t);
+    } else if (t >= 32 && t < 32 + sizeof(DevSeq) / 16) {
+        reinterpret_cast<uint4*>(&s_seq)[t - 32] = __ldg(reinterpret_cast<const uint4*>(a.seqs + seq) + (t - 32));
+    } else if (t >= 64 && t < blockDim.x) {
+        for (uint32_t k = t - 64; k < n_ops; k += blockDim.x - 64 - skip)
             expand_op(__ldg(reinterpret_cast<const uint4*>(a.ops + ops_begin + k)), sops + k);
     }
     __syncthreads();
