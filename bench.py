@@ -44,7 +44,7 @@ L2_BYTES = 126 * 1024 * 1024
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the workload's kernel, from the ncu
 # capture summarised under profiles/ (None = not captured).
-TRAFFIC_BYTES_PER_LAUNCH = {"c3": 775.1e6, "c4": 469.9e6}
+TRAFFIC_BYTES_PER_LAUNCH = {"c3": 776.2e6, "c4": 470.6e6}
 
 
 # --------------------------------------------------------------------------------------
