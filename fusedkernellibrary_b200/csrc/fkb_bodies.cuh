@@ -46,6 +46,12 @@ __device__ __forceinline__ float saturate_round_u8(float f) {
     return __fadd_rn(__fadd_rd(t, 8388608.0f), -8388608.0f);
 }
 
+/* The same result still under the exponent of 2^23 (2^23 + the byte): for a chain whose last operation it is and whose
+   receiver packs bytes, which would add 2^23 again to get at the byte. */
+__device__ __forceinline__ float saturate_round_u8_biased(float f) {
+    return __fadd_rd(__fadd_rn(fminf(fmaxf(f, 0.0f), 255.0f), 0.5f), 8388608.0f);
+}
+
 /* Exact uchar -> float.  Converting from a 32-bit integer (not from an 8-bit one) keeps the
    conversion off the quarter-rate conversion unit. */
 __device__ __forceinline__ float u8_to_float(uint32_t b) { return __int2float_rn((int)b); }
@@ -151,7 +157,7 @@ __device__ __forceinline__ void expand_op(const uint4 g, OpSlot* slot) {
 
 /* One operation on NPAIR pixel pairs held as v[3*j + channel] = (pixel 2j, pixel 2j+1); `s` is the
    operation's slot (and s[1] the second slot of a two-slot operation). */
-template <int CODE, int NPAIR>
+template <int CODE, int NPAIR, bool BIASED = false>
 __device__ __forceinline__ void apply_one(float2 (&v)[NPAIR * 3], const OpSlot* __restrict__ s, const float2 one) {
     if (CODE == CH_CASTI || CODE == CH_CASTU) {
         /* Cast<float3,int3> / Cast<float3,uint3>: static_cast truncates toward zero (cast_base.h:20-30); the
@@ -170,7 +176,11 @@ __device__ __forceinline__ void apply_one(float2 (&v)[NPAIR * 3], const OpSlot* 
             float2& b = v[3 * j + 1];
             float2& c = v[3 * j + 2];
             if (CODE == CH_SWAP) { const float2 t = a; a = c; c = t; }
-            else if (CODE == CH_SAT) {
+            else if (CODE == CH_SAT && BIASED) {
+                a = make_float2(saturate_round_u8_biased(a.x), saturate_round_u8_biased(a.y));
+                b = make_float2(saturate_round_u8_biased(b.x), saturate_round_u8_biased(b.y));
+                c = make_float2(saturate_round_u8_biased(c.x), saturate_round_u8_biased(c.y));
+            } else if (CODE == CH_SAT) {
                 a = make_float2(saturate_round_u8(a.x), saturate_round_u8(a.y));
                 b = make_float2(saturate_round_u8(b.x), saturate_round_u8(b.y));
                 c = make_float2(saturate_round_u8(c.x), saturate_round_u8(c.y));
@@ -278,20 +288,28 @@ __device__ __forceinline__ void interpret_ops(float2 (&v)[NPAIR * 3], const OpSl
 
 /* A chain fixed at compile time: operation codes in the nibbles of CHAIN, parameters taken
    from consecutive slots of the cached operation table starting at `slot`. */
-template <uint32_t CHAIN, int NPAIR>
+/* BIASED_LAST: a SaturateCast that ends the chain leaves its results under the exponent of 2^23 (chain_ends_biased). */
+template <uint32_t CHAIN, int NPAIR, bool BIASED_LAST = false>
 __device__ __forceinline__ void apply_chain(float2 (&v)[NPAIR * 3], const OpSlot* __restrict__ sops, int slot, const float2 one) {
     constexpr uint32_t CODE = CHAIN & 0xFu;
     if constexpr (CODE != 0) {
-        apply_one<CODE, NPAIR>(v, sops + slot, one);
-        apply_chain<(CHAIN >> 4), NPAIR>(v, sops, slot + (CODE == CH_DIVC ? 2 : 1), one);
+        apply_one<CODE, NPAIR, (BIASED_LAST && CODE == CH_SAT && (CHAIN >> 4) == 0u)>(v, sops + slot, one);
+        apply_chain<(CHAIN >> 4), NPAIR, BIASED_LAST>(v, sops, slot + (CODE == CH_DIVC ? 2 : 1), one);
     }
 }
 
-template <uint32_t CHAIN, int NPAIR>
+/* Whether a compiled chain ends in SaturateCast: a receiver that packs bytes then takes them from under the exponent. */
+__host__ __device__ constexpr bool chain_ends_biased(uint32_t chain) {
+    if (chain == CHAIN_INTERPRET || chain == 0u) return false;
+    while ((chain >> 4) != 0u) chain >>= 4;
+    return chain == CH_SAT;
+}
+
+template <uint32_t CHAIN, int NPAIR, bool BIASED_LAST = false>
 __device__ __forceinline__ void run_ops(float2 (&v)[NPAIR * 3], const OpSlot* __restrict__ sops, int begin, int end,
                                         const float2 one) {
     if constexpr (CHAIN == CHAIN_INTERPRET) interpret_ops<NPAIR>(v, sops, begin, end, one);
-    else apply_chain<CHAIN, NPAIR>(v, sops, begin, one);
+    else apply_chain<CHAIN, NPAIR, BIASED_LAST>(v, sops, begin, one);
 }
 
 /* The same on one pixel (both halves of a pair carry it). */
@@ -727,7 +745,8 @@ __device__ __forceinline__ void body_flat(const DevPlane& P, const DevSeq& S, co
         for (int j = 0; j < 2; ++j)
 #pragma unroll
             for (int c = 0; c < 3; ++c) q[3 * j + c] = make_float2(v[6 * j + c], v[6 * j + 3 + c]);
-        run_ops<CHAIN, 2>(q, sops, 0, S.n_ops, one2);
+        constexpr bool BIASED = DST_IS_U8 && chain_ends_biased(CHAIN); /* v = 2^23 + byte from here on */
+        run_ops<CHAIN, 2, BIASED>(q, sops, 0, S.n_ops, one2);
 #pragma unroll
         for (int j = 0; j < 2; ++j)
 #pragma unroll
@@ -743,8 +762,9 @@ __device__ __forceinline__ void body_flat(const DevPlane& P, const DevSeq& S, co
                     /* The values are whole numbers 0..255 (bytes that were never touched, or SaturateCast's result):
                        2^23 + v is exact and carries v in its lowest byte, so four additions and three byte permutes
                        pack the word without four trips through the quarter-rate conversion unit. */
-                    const uint32_t b0 = __float_as_uint(__fadd_rn(v[4 * k + 0], 8388608.0f)), b1 = __float_as_uint(__fadd_rn(v[4 * k + 1], 8388608.0f));
-                    const uint32_t b2 = __float_as_uint(__fadd_rn(v[4 * k + 2], 8388608.0f)), b3 = __float_as_uint(__fadd_rn(v[4 * k + 3], 8388608.0f));
+                    const float bias = BIASED ? 0.0f : 8388608.0f; /* a chain that ends in SaturateCast left its bytes there already */
+                    const uint32_t b0 = __float_as_uint(BIASED ? v[4 * k + 0] : __fadd_rn(v[4 * k + 0], bias)), b1 = __float_as_uint(BIASED ? v[4 * k + 1] : __fadd_rn(v[4 * k + 1], bias));
+                    const uint32_t b2 = __float_as_uint(BIASED ? v[4 * k + 2] : __fadd_rn(v[4 * k + 2], bias)), b3 = __float_as_uint(BIASED ? v[4 * k + 3] : __fadd_rn(v[4 * k + 3], bias));
                     w[k] = __byte_perm(__byte_perm(b0, b1, 0x0040), __byte_perm(b2, b3, 0x0040), 0x5410);
                 } else {
                     w[k] = make_float4(v[4 * k + 0], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
@@ -767,7 +787,7 @@ __device__ __forceinline__ void body_flat(const DevPlane& P, const DevSeq& S, co
 #pragma unroll
             for (int i = 0; i < 12; ++i) {
                 if (i < (int)n[r] * 3) {
-                    if (DST_IS_U8) gst(dst + i, (uint8_t)v[i]);
+                    if (DST_IS_U8) gst(dst + i, BIASED ? (uint8_t)(__float_as_uint(v[i]) & 0xFFu) : (uint8_t)v[i]);
                     else gst(reinterpret_cast<float*>(dst) + i, v[i]);
                 }
             }
