@@ -158,8 +158,9 @@ __host__ __device__ constexpr int flat_quads(bool src_is_u8) { return src_is_u8 
 __host__ __device__ constexpr int flat_item_pixels(bool src_is_u8) { return BLOCK_THREADS * PX_PER_THREAD * flat_quads(src_is_u8); }
 constexpr int ITEM_PIXELS_GENERIC = BLOCK_THREADS;
 /* FLAT float3 -> float3, one dense plane: from this many arithmetic operations per value a block prefetches the work item
-   FLAT_PREFETCH_ITEMS ahead into the L2 (the blocks a B200 holds at five per SM, 9 MB; twice and four times as far measured the same or worse) */
-constexpr uint32_t FLAT_PREFETCH_MIN_OPS = 12;
+   FLAT_PREFETCH_ITEMS ahead into the L2 (the blocks a B200 holds at five per SM, 9 MB; twice and four times as far measured
+   the same or worse).  A 4K image: one operation 34.9 us with and without, four 38.0 -> 34.9, sixteen 38.6 -> 35.1. */
+constexpr uint32_t FLAT_PREFETCH_MIN_OPS = 2;
 constexpr uint32_t FLAT_PREFETCH_ITEMS = 148u * 5u;
 
 /* Device-only opcode: division by a plan-time constant, lowered from FKB_OP_DIV when the host

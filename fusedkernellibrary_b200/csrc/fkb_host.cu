@@ -621,7 +621,7 @@ static uint32_t lower_ops(const fkb_sequence& s, int n_pre, int step_exp_x, int 
     /* A long continuation that repeats one operation or a pair of them (the reference spells this
        StaticLoop, basic_ops/static_loop.h:22-44) runs as a counted loop on the device: the
        repeated part is stored once behind a header slot. */
-    if (chain == CHAIN_INTERPRET) {
+    if (chain == CHAIN_INTERPRET || !chain_is_compiled(chain)) { /* up to eight operations that are no compiled chain are interpreted too */
         const size_t begin = (size_t)dev_n_pre;
         std::vector<DevOp> packed(out.begin() + begin, out.end());
         std::vector<DevOp> res;
