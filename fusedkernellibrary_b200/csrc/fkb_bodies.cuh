@@ -157,7 +157,7 @@ __device__ __forceinline__ void expand_op(const uint4 g, OpSlot* slot) {
 
 /* One operation on NPAIR pixel pairs held as v[3*j + channel] = (pixel 2j, pixel 2j+1); `s` is the
    operation's slot (and s[1] the second slot of a two-slot operation). */
-template <int CODE, int NPAIR, bool BIASED = false>
+template <int CODE, int NPAIR, bool BIASED = false, bool UNIFORM = false>
 __device__ __forceinline__ void apply_one(float2 (&v)[NPAIR * 3], const OpSlot* __restrict__ s, const float2 one) {
     if (CODE == CH_CASTI || CODE == CH_CASTU) {
         /* Cast<float3,int3> / Cast<float3,uint3>: static_cast truncates toward zero (cast_base.h:20-30); the
@@ -192,7 +192,7 @@ __device__ __forceinline__ void apply_one(float2 (&v)[NPAIR * 3], const OpSlot* 
         }
         return;
     }
-    const float2 p0 = s[0].p[0], p1 = s[0].p[1], p2 = s[0].p[2];
+    const float2 p0 = s[0].p[0], p1 = UNIFORM ? p0 : s[0].p[1], p2 = UNIFORM ? p0 : s[0].p[2]; /* UNIFORM: one parameter for the three channels */
 #pragma unroll
     for (int j = 0; j < NPAIR; ++j) {
         float2& a = v[3 * j + 0];
@@ -205,7 +205,7 @@ __device__ __forceinline__ void apply_one(float2 (&v)[NPAIR * 3], const OpSlot* 
             c = make_float2(__fdiv_rn(c.x, p2.x), __fdiv_rn(c.y, p2.x));
         } else if (CODE == CH_ADD || CODE == CH_SUB) { a = add2(a, p0, one); b = add2(b, p1, one); c = add2(c, p2, one); }
         else if (CODE == CH_DIVC) { /* div_by_constant on both halves: p holds -divisor, r its reciprocal */
-            const float2 r0 = s[1].p[0], r1 = s[1].p[1], r2 = s[1].p[2];
+            const float2 r0 = s[1].p[0], r1 = UNIFORM ? r0 : s[1].p[1], r2 = UNIFORM ? r0 : s[1].p[2];
             const float2 qa = mul2(a, r0), qb = mul2(b, r1), qc = mul2(c, r2);
             a = fma2(fma2(p0, qa, a), r0, qa); b = fma2(fma2(p1, qb, b), r1, qb); c = fma2(fma2(p2, qc, c), r2, qc);
         }
@@ -289,18 +289,19 @@ __device__ __forceinline__ void interpret_ops(float2 (&v)[NPAIR * 3], const OpSl
 /* A chain fixed at compile time: operation codes in the nibbles of CHAIN, parameters taken
    from consecutive slots of the cached operation table starting at `slot`. */
 /* BIASED_LAST: a SaturateCast that ends the chain leaves its results under the exponent of 2^23 (chain_ends_biased). */
-template <uint32_t CHAIN, int NPAIR, bool BIASED_LAST = false>
+template <uint32_t CHAIN, int NPAIR, bool BIASED_LAST = false, bool UNIFORM = false>
 __device__ __forceinline__ void apply_chain(float2 (&v)[NPAIR * 3], const OpSlot* __restrict__ sops, int slot, const float2 one) {
     constexpr uint32_t CODE = CHAIN & 0xFu;
     if constexpr (CODE != 0) {
-        apply_one<CODE, NPAIR, (BIASED_LAST && CODE == CH_SAT && (CHAIN >> 4) == 0u)>(v, sops + slot, one);
-        apply_chain<(CHAIN >> 4), NPAIR, BIASED_LAST>(v, sops, slot + (CODE == CH_DIVC ? 2 : 1), one);
+        apply_one<CODE, NPAIR, (BIASED_LAST && CODE == CH_SAT && (CHAIN >> 4) == 0u), UNIFORM>(v, sops + slot, one);
+        apply_chain<(CHAIN >> 4), NPAIR, BIASED_LAST, UNIFORM>(v, sops, slot + (CODE == CH_DIVC ? 2 : 1), one);
     }
 }
 
 /* Whether a compiled chain ends in SaturateCast: a receiver that packs bytes then takes them from under the exponent. */
 __host__ __device__ constexpr bool chain_ends_biased(uint32_t chain) {
     if (chain == CHAIN_INTERPRET || chain == 0u) return false;
+    chain &= ~CHAIN_UNIFORM;
     while ((chain >> 4) != 0u) chain >>= 4;
     return chain == CH_SAT;
 }
@@ -309,7 +310,7 @@ template <uint32_t CHAIN, int NPAIR, bool BIASED_LAST = false>
 __device__ __forceinline__ void run_ops(float2 (&v)[NPAIR * 3], const OpSlot* __restrict__ sops, int begin, int end,
                                         const float2 one) {
     if constexpr (CHAIN == CHAIN_INTERPRET) interpret_ops<NPAIR>(v, sops, begin, end, one);
-    else apply_chain<CHAIN, NPAIR, BIASED_LAST>(v, sops, begin, one);
+    else apply_chain<(CHAIN & ~CHAIN_UNIFORM), NPAIR, BIASED_LAST, (CHAIN & CHAIN_UNIFORM) != 0u>(v, sops, begin, one);
 }
 
 /* The same on one pixel (both halves of a pair carry it). */
@@ -1629,6 +1630,7 @@ __device__ __forceinline__ void body_nv12_staged(const DevPlane& P, const DevSeq
     X(chain_of(CH_DIVC))                          /* Div                                                       */ \
     X(chain_of(CH_DIVC, CH_SUB, CH_DIVC))         /* Div, Sub, Div: normalise with mean and std                */ \
     X(chain_of(CH_MUL, CH_SUB, CH_DIVC, CH_SWAP)) /* Mul, Sub, Div, RGB2BGR                                    */ \
+    X(chain_of(CH_MUL, CH_SUB, CH_DIVC, CH_SWAP) | CHAIN_UNIFORM) /* the same with one parameter for the three channels */ \
     X(chain_of(CH_MUL, CH_SUB, CH_DIVC))          /* Mul, Sub, Div                                             */ \
     X(chain_of(CH_MUL, CH_SUB))                   /* Mul, Sub                                                  */ \
     X(chain_of(CH_ADD, CH_DIVC))                  /* Add, Div                                                  */ \

@@ -14,6 +14,10 @@
 namespace fkb {
 
 constexpr uint32_t CHAIN_INTERPRET = 0xFFFFFFFFu; /* see the end of this file */
+/* Flag on a compiled chain of at most seven operations: every arithmetic operation has the same parameter for the three
+   channels (Mul by 1.4, Sub 0.5, Div by 255: the common case), so that the kernel fetches one parameter pair per operation
+   instead of three. */
+constexpr uint32_t CHAIN_UNIFORM = 0x80000000u;
 
 /* How a plane is processed (chosen on the host from formats, sizes and alignment). */
 enum PlaneClass : uint32_t {

@@ -642,6 +642,14 @@ static uint32_t lower_ops(const fkb_sequence& s, int n_pre, int step_exp_x, int 
             out.push_back(o);
         }
     }
+    /* The same parameter for the three channels in every arithmetic operation of a compiled chain: its uniform variant,
+       if that is compiled too (CHAIN_UNIFORM). */
+    if (chain != CHAIN_INTERPRET && chain_len < 8 && chain_is_compiled(chain | CHAIN_UNIFORM)) {
+        bool uniform = true;
+        for (size_t k = (size_t)dev_n_pre; k < out.size(); ++k)
+            uniform = uniform && std::memcmp(&out[k].p[0], &out[k].p[1], 4) == 0 && std::memcmp(&out[k].p[0], &out[k].p[2], 4) == 0;
+        if (uniform) chain |= CHAIN_UNIFORM;
+    }
     /* A long continuation that repeats one operation or a pair of them (the reference spells this
        StaticLoop, basic_ops/static_loop.h:22-44) runs as a counted loop on the device: the
        repeated part is stored once behind a header slot. */
