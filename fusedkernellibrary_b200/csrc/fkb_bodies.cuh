@@ -1628,6 +1628,7 @@ __device__ __forceinline__ void body_nv12_staged(const DevPlane& P, const DevSeq
 #define FKB_CHAIN_MENU(X)                                                                                         \
     X(chain_of())                                 /* no continuation (copy, Cast -> Resize)                    */ \
     X(chain_of(CH_DIVC))                          /* Div                                                       */ \
+    X(chain_of(CH_DIVC) | CHAIN_UNIFORM)          /* the same with one parameter for the three channels        */ \
     X(chain_of(CH_DIVC, CH_SUB, CH_DIVC))         /* Div, Sub, Div: normalise with mean and std                */ \
     X(chain_of(CH_MUL, CH_SUB, CH_DIVC, CH_SWAP)) /* Mul, Sub, Div, RGB2BGR                                    */ \
     X(chain_of(CH_MUL, CH_SUB, CH_DIVC, CH_SWAP) | CHAIN_UNIFORM) /* the same with one parameter for the three channels */ \
